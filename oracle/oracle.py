@@ -1,0 +1,299 @@
+"""numpy front end of the CPU oracle (test infrastructure, never part of the product).
+
+Only ``tests/``, the smoke check and the CPU-baseline leg of the benchmark import
+this module.  It loads ``libcforacle.so`` (built by ``build_oracle.py`` from
+``cf_oracle.c``) and exposes one function per routine of the restatement.  Each
+function takes and returns numpy arrays; ``dtype=np.float64`` selects the double
+build, which is used to decide which side of a float disagreement is closer to
+the exact value.
+
+The host-side glue of the reference that sits between its kernels (allocation,
+argmax over an atom's pairs, Gram-Schmidt, scaling by the two coefficients) is
+restated here and in ``cf_oracle.c``; each function cites the reference lines.
+"""
+import ctypes
+import dataclasses
+import math
+import os
+
+import numpy as np
+
+from . import build_oracle
+
+_lib = None
+
+
+class _CConfig(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in
+                ("H", "head_dim", "D_dist", "D_ang", "lattice_range", "minimum_range", "cos_abs",
+                 "win_dist", "win_ang", "cut_sigma")] + \
+               [(n, ctypes.c_float) for n in
+                ("dist_max", "wscale_dist", "angle_sigma", "c_dist", "c_ang", "cutoff_radius",
+                 "symm_break_noise")]
+
+
+@dataclasses.dataclass
+class Config:
+    """Hyper-parameters the reference bakes into its kernels by text substitution
+    (models/cuda_funcs/kernel_manager.py:116-149) plus the scalars its Functions pass
+    at launch (models/cuda_funcs/real_space_framed_proj.py:35-40).  Defaults are those
+    of params/crystalframer/default_jarvis.json."""
+    H: int = 8
+    head_dim: int = 16
+    D_dist: int = 64
+    D_ang: int = 64
+    lattice_range: int = 2
+    minimum_range: int = 2
+    cos_abs: int = 0
+    cut_sigma: int = 4
+    dist_max: float = 14.0
+    wscale_dist: float = 1.0
+    wscale_ang: float = 4.0
+    c_dist: float = 1.0
+    c_ang: float = 1.0
+    cutoff_radius: float = -3.5
+    symm_break_noise: float = 0.0
+
+    @property
+    def win_dist(self):
+        return math.ceil(2 * self.wscale_dist * self.cut_sigma + 1)
+
+    @property
+    def win_ang(self):
+        return math.ceil(2 * self.wscale_ang * self.cut_sigma + 1)
+
+    @property
+    def angle_sigma(self):
+        if self.D_ang <= 1:
+            return 1.0
+        span = 1.0 if self.cos_abs else 2.0
+        return span * self.wscale_ang / (self.D_ang - 1)
+
+    def c(self):
+        return _CConfig(self.H, self.head_dim, self.D_dist, self.D_ang, self.lattice_range,
+                        self.minimum_range, self.cos_abs, self.win_dist, self.win_ang, self.cut_sigma,
+                        self.dist_max, self.wscale_dist, self.angle_sigma, self.c_dist, self.c_ang,
+                        self.cutoff_radius, self.symm_break_noise)
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = build_oracle.LIB
+        if not os.path.exists(path):
+            build_oracle.build_restatement()
+        _lib = ctypes.CDLL(path)
+    return _lib
+
+
+def _fn(name, dtype):
+    f = getattr(lib(), name + ("_f64" if np.dtype(dtype) == np.float64 else "_f32"))
+    f.restype = None
+    return f
+
+
+def _p(x):
+    return None if x is None else x.ctypes.data_as(ctypes.c_void_p)
+
+
+def _r(x, dtype):
+    return None if x is None else np.ascontiguousarray(x, dtype=dtype)
+
+
+def _i64(x):
+    return np.ascontiguousarray(x, dtype=np.int64)
+
+
+def _f32(x):
+    return np.ascontiguousarray(x, dtype=np.float32)
+
+
+def edge_index(sizes):
+    """models/indexed_latticeformer_encoder.py:15-32 and the CSR offsets of
+    models/cuda_funcs/fused_dpa.py:24-26."""
+    sizes = _i64(sizes)
+    N = int(sizes.sum())
+    E = int((sizes * sizes).sum())
+    edges = np.empty((2, E), np.int64)
+    e_start = np.empty(N + 1, np.int64)
+    _fn("cfo_edge_index", np.float32)(_p(sizes), ctypes.c_int64(len(sizes)), _p(edges), _p(e_start),
+                                      ctypes.c_int64(E))
+    return edges, e_start
+
+
+def lattice_geometry(pos, trans_vec, sizes):
+    """pos_ij, reciprocal vectors, cell volume, batch index:
+    models/indexed_latticeformer_encoder.py:175-245 (float32, same operation order)."""
+    sizes = _i64(sizes)
+    pos = _f32(pos)
+    T = _f32(trans_vec)
+    edges, e_start = edge_index(sizes)
+    batch = np.repeat(np.arange(len(sizes), dtype=np.int64), sizes)
+    m = T
+    vcell = (m[:, 0, 0] * m[:, 1, 1] * m[:, 2, 2] + m[:, 0, 1] * m[:, 1, 2] * m[:, 2, 0]
+             + m[:, 0, 2] * m[:, 1, 0] * m[:, 2, 1] - m[:, 0, 2] * m[:, 1, 1] * m[:, 2, 0]
+             - m[:, 0, 0] * m[:, 1, 2] * m[:, 2, 1] - m[:, 0, 1] * m[:, 1, 0] * m[:, 2, 2]).astype(np.float32)
+    rec = np.stack([np.cross(T[:, 1], T[:, 2]), np.cross(T[:, 2], T[:, 0]), np.cross(T[:, 0], T[:, 1])],
+                   axis=1).astype(np.float32)
+    rec = (rec * (np.float32(2.0 * math.pi) / vcell)[:, None, None]).astype(np.float32)
+    pos_ij = (pos[edges[1]] - pos[edges[0]]).astype(np.float32)
+    rvlen = np.sqrt((rec * rec).sum(-1)).astype(np.float32)
+    return dict(edges=edges, e_start=e_start, batch=batch, pos_ij=pos_ij, rvecs=rec, vcell=vcell, rvlen=rvlen)
+
+
+def lattice_range(cfg, a_ik, rvlen, batch):
+    a_ik = _f32(a_ik)
+    N = a_ik.shape[0]
+    R = np.empty((N, cfg.H, 3), np.int32)
+    c = cfg.c()
+    _fn("cfo_lattice_range", np.float32)(ctypes.byref(c), _p(a_ik), _p(_f32(rvlen)), _p(_i64(batch)),
+                                         ctypes.c_int64(N), _p(R))
+    return R
+
+
+def framed_proj_fwd(cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, W_d, W_a, frames, dtype=np.float32,
+                    values=True):
+    """z (E,H) and values (E,H,head_dim).  W_d (H,hd,D_dist); W_a (3,H,hd,D_ang) or None;
+    frames (3,N,H,3) or None."""
+    a = _r(a_ik, dtype)
+    N, H = a.shape
+    E = edges.shape[1]
+    z = np.empty((E, H), dtype)
+    v = np.empty((E, H, cfg.head_dim), dtype) if values else None
+    c = cfg.c()
+    _fn("cfo_framed_proj_fwd", dtype)(
+        ctypes.byref(c), _p(a), _p(_r(pos_ij, dtype)), _p(_r(tvecs, dtype)), _p(_f32(rvlen)),
+        _p(_i64(batch)), _p(_i64(edges)), ctypes.c_int64(N), ctypes.c_int64(E),
+        _p(_r(W_d, dtype)), _p(_r(W_a, dtype)), _p(_r(frames, dtype)), _p(z), _p(v))
+    return z, v
+
+
+def framed_proj_bwd(cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, W_d, W_a, frames, z, gz, gv,
+                    dtype=np.float32):
+    a = _r(a_ik, dtype)
+    N, H = a.shape
+    E = edges.shape[1]
+    ga = np.empty((N, H), dtype)
+    gW_d = np.empty((H, cfg.head_dim, cfg.D_dist), dtype)
+    gW_a = np.empty((3, H, cfg.head_dim, cfg.D_ang), dtype) if W_a is not None else None
+    c = cfg.c()
+    _fn("cfo_framed_proj_bwd", dtype)(
+        ctypes.byref(c), _p(a), _p(_r(pos_ij, dtype)), _p(_r(tvecs, dtype)), _p(_f32(rvlen)),
+        _p(_i64(batch)), _p(_i64(edges)), _p(_i64(e_start)), ctypes.c_int64(N), ctypes.c_int64(E),
+        _p(_r(W_d, dtype)), _p(_r(W_a, dtype)), _p(_r(frames, dtype)), _p(_r(z, dtype)), _p(_r(gz, dtype)),
+        _p(_r(gv, dtype)), _p(ga), _p(gW_d), _p(gW_a))
+    return ga, gW_d, gW_a
+
+
+def _frame_edges(name, cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, seed, frame1, dtype):
+    a = _r(a_ik, dtype)
+    N, H = a.shape
+    E = edges.shape[1]
+    d = np.empty((E, H, 3), dtype)
+    val = np.empty((E, H), dtype)
+    img = np.empty((E, H), np.int32)
+    c = cfg.c()
+    args = [ctypes.byref(c), _p(a), _p(_r(pos_ij, dtype)), _p(_r(tvecs, dtype)), _p(_f32(rvlen)),
+            _p(_i64(batch)), _p(_i64(edges)), ctypes.c_int64(N), ctypes.c_int64(E), ctypes.c_uint64(seed)]
+    if frame1 is not None:
+        args.append(_p(_r(frame1, dtype)))
+    args += [_p(d), _p(val), _p(img)]
+    _fn(name, dtype)(*args)
+    return d, val, img
+
+
+def frame1_edges(cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, seed=0, dtype=np.float32):
+    return _frame_edges("cfo_frame1_edges", cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, seed, None, dtype)
+
+
+def frame2_edges(cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, frame1, seed=0, dtype=np.float32):
+    return _frame_edges("cfo_frame2_edges", cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, seed, frame1, dtype)
+
+
+def frame_select(cfg, q, k, edges, e_start, direction, value, dtype=np.float32):
+    q = _r(q, dtype)
+    N, H = q.shape[:2]
+    E = edges.shape[1]
+    frame = np.empty((N, H, 3), dtype)
+    sel = np.empty((N, H), np.int64)
+    c = cfg.c()
+    _fn("cfo_frame_select", dtype)(ctypes.byref(c), _p(q), _p(_r(k, dtype)), _p(_i64(edges)),
+                                   _p(_i64(e_start)), ctypes.c_int64(N), ctypes.c_int64(E),
+                                   _p(_r(direction, dtype)), _p(_r(value, dtype)), _p(frame), _p(sel))
+    return frame, sel
+
+
+def frame_complete(f1, f2max, dtype=np.float32):
+    f1 = _r(f1, dtype)
+    f2max = _r(f2max, dtype)
+    f2 = np.empty_like(f1)
+    f3 = np.empty_like(f1)
+    _fn("cfo_frame_complete", dtype)(_p(f1), _p(f2max), ctypes.c_int64(f1.size // 3), _p(f2), _p(f3))
+    return f2, f3
+
+
+def max_frames(cfg, q_scaled, k, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, seed1=0, seed2=0,
+               dtype=np.float32):
+    """The "max" frame method end to end
+    (models/indexed_lattice_multi_head_attention_cuda.py:435-493): first axis, second
+    axis, Gram-Schmidt.  ``q_scaled`` is q / sqrt(head_dim).  Returns the three frames
+    and the integer selections (pair and image for both axes)."""
+    d1, v1, img1 = frame1_edges(cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, seed1, dtype)
+    f1, sel1 = frame_select(cfg, q_scaled, k, edges, e_start, d1, v1, dtype)
+    d2, v2, img2 = frame2_edges(cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, f1, seed2, dtype)
+    f2max, sel2 = frame_select(cfg, q_scaled, k, edges, e_start, d2, v2, dtype)
+    f2, f3 = frame_complete(f1, f2max, dtype)
+    H = cfg.H
+    hh = np.arange(H)[None, :]
+    return dict(frame1=f1, frame2_max=f2max, frame2=f2, frame3=f3, sel_edge1=sel1, sel_edge2=sel2,
+                sel_image1=img1[sel1, hh], sel_image2=img2[sel2, hh])
+
+
+def dpa_fwd(cfg, q, k, v, aij, bij, edges, e_start, dtype=np.float32):
+    q = _r(q, dtype)
+    N, H, hd = q.shape
+    E = edges.shape[1]
+    prob = np.empty((E, H), dtype)
+    out = np.empty((N, H, hd), dtype)
+    c = cfg.c()
+    _fn("cfo_dpa_fwd", dtype)(ctypes.byref(c), _p(q), _p(_r(k, dtype)), _p(_r(v, dtype)), _p(_r(aij, dtype)),
+                              _p(_r(bij, dtype)), _p(_i64(edges)), _p(_i64(e_start)), ctypes.c_int64(N),
+                              ctypes.c_int64(E), _p(prob), _p(out))
+    return out, prob
+
+
+def dpa_bwd(cfg, q, k, v, bij, edges, e_start, prob, out, gout, dtype=np.float32):
+    q = _r(q, dtype)
+    N, H, hd = q.shape
+    E = edges.shape[1]
+    gq = np.empty((N, H, hd), dtype)
+    gk = np.empty((N, H, hd), dtype)
+    gv = np.empty((N, H, hd), dtype)
+    ga = np.empty((E, H), dtype)
+    gb = np.empty((E, H, hd), dtype) if bij is not None else None
+    c = cfg.c()
+    _fn("cfo_dpa_bwd", dtype)(ctypes.byref(c), _p(q), _p(_r(k, dtype)), _p(_r(v, dtype)), _p(_r(bij, dtype)),
+                              _p(_i64(edges)), _p(_i64(e_start)), ctypes.c_int64(N), ctypes.c_int64(E),
+                              _p(_r(prob, dtype)), _p(_r(out, dtype)), _p(_r(gout, dtype)),
+                              _p(gq), _p(gk), _p(gv), _p(ga), _p(gb))
+    return gq, gk, gv, ga, gb
+
+
+def mean_fwd(x, sizes, dtype=np.float32):
+    x = _r(x, dtype)
+    sizes = _i64(sizes)
+    start = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+    D = x.size // x.shape[0]
+    out = np.empty((len(sizes),) + x.shape[1:], dtype)
+    _fn("cfo_mean_fwd", dtype)(_p(x), _p(start), ctypes.c_int64(len(sizes)), ctypes.c_int64(D), _p(out))
+    return out
+
+
+def mean_bwd(gout, sizes, dtype=np.float32):
+    gout = _r(gout, dtype)
+    sizes = _i64(sizes)
+    start = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+    D = gout.size // gout.shape[0]
+    gx = np.empty((int(sizes.sum()),) + gout.shape[1:], dtype)
+    _fn("cfo_mean_bwd", dtype)(_p(gout), _p(start), ctypes.c_int64(len(sizes)), ctypes.c_int64(D), _p(gx))
+    return gx
