@@ -1,0 +1,92 @@
+"""ctypes binding of libcfb200.so.
+
+There is no fallback: if the shared library is missing or an entry point reports an error,
+an exception is raised.  Tensors handed to ``ptr`` must be contiguous CUDA tensors of the
+expected dtype; ``None`` becomes a NULL pointer.
+"""
+import ctypes
+import os
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libcfb200.so")
+
+_lib = None
+
+i64, f32, vp, u64, i32 = ctypes.c_int64, ctypes.c_float, ctypes.c_void_p, ctypes.c_uint64, ctypes.c_int32
+
+
+class Config(ctypes.Structure):
+    _fields_ = [("num_heads", i32), ("head_dim", i32), ("dist_dim", i32), ("angle_dim", i32),
+                ("lattice_range", i32), ("minimum_range", i32), ("cos_abs", i32), ("cut_sigma", i32),
+                ("dist_wscale", f32), ("angle_wscale", f32), ("dist_coef", f32), ("angle_coef", f32),
+                ("symm_break_noise", f32)]
+
+
+# name -> (restype, argtypes); one entry per declaration of include/cfb200.h
+SIGNATURES = {
+    "cfb200_configure": (ctypes.c_int, [ctypes.POINTER(Config)]),
+    "cfb200_get_config": (ctypes.c_int, [ctypes.POINTER(Config)]),
+    "cfb200_version": (ctypes.c_int, []),
+    "cfb200_error_string": (ctypes.c_char_p, [ctypes.c_int]),
+    "cfb200_status": (ctypes.c_int, [ctypes.POINTER(i32), vp]),
+    "cfb200_framed_proj_bwd_workspace_bytes": (i64, [i64, i64]),
+    "cfb200_edge_index": (ctypes.c_int, [vp, i64, i64, i64, vp, vp, vp, vp, vp]),
+    "cfb200_csr_offsets": (ctypes.c_int, [vp, i64, i64, vp, vp]),
+    "cfb200_max_frame": (ctypes.c_int, [ctypes.c_int] + [vp] * 9 + [i64, i64, f32, u64] + [vp] * 5),
+    "cfb200_max_frames": (ctypes.c_int, [vp] * 9 + [i64, i64, f32, u64, u64] + [vp] * 4),
+    "cfb200_framed_proj_fwd": (ctypes.c_int, [vp] * 6 + [i64, i64, f32, f32] + [vp] * 10),
+    "cfb200_framed_proj_bwd": (ctypes.c_int, [vp] * 7 + [i64, i64, f32, f32] + [vp] * 16 + [i64, vp]),
+    "cfb200_dpa_fwd": (ctypes.c_int, [vp] * 7 + [i64, i64] + [vp] * 4),
+    "cfb200_dpa_bwd": (ctypes.c_int, [vp] * 7 + [i64, i64] + [vp] * 9),
+    "cfb200_segment_mean_fwd": (ctypes.c_int, [vp, vp, i64, i64, vp, vp]),
+    "cfb200_segment_mean_bwd": (ctypes.c_int, [vp, vp, i64, i64, vp, vp]),
+}
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m crystalframer_b200.build` "
+                "(nvcc, sm_100a). There is no CPU or PyTorch fallback for these operators.")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(rc, what):
+    if rc != 0:
+        msg = lib().cfb200_error_string(rc).decode()
+        raise RuntimeError(f"{what} failed: {msg} (code {rc})")
+
+
+def ptr(t, dtype=torch.float32):
+    if t is None:
+        return None
+    if not (t.is_cuda and t.is_contiguous() and t.dtype == dtype):
+        raise ValueError(f"expected a contiguous CUDA tensor of {dtype}, got {t.dtype} on {t.device}, "
+                         f"contiguous={t.is_contiguous()}")
+    return t.data_ptr()
+
+
+def iptr(t):
+    return ptr(t, torch.int64)
+
+
+def stream(device):
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def read_status(device=None):
+    """Reads and clears the device status word (synchronises the current stream)."""
+    out = i32(0)
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        check(lib().cfb200_status(ctypes.byref(out), stream(device)), "cfb200_status")
+    return out.value

@@ -1,0 +1,216 @@
+"""Periodic lattice-sum multi-head attention: module and functional form.
+
+Drop-in for ``CrystalformerMultiheadAttentionCUDA`` and
+``crystalformer_multi_head_attention_forward_cuda`` of the reference
+(models/indexed_lattice_multi_head_attention_cuda.py:737-1269): same constructor and forward
+arguments, same parameter names, shapes and initialisation (so released checkpoints load), same
+data-dependent ``gauss_scale`` state.  Input / output projections and the Gaussian-coefficient
+pipeline stay in PyTorch; everything between them runs in libcfb200.
+
+Only the real-space domain with frame methods "max" (CrystalFramer) and "no" (plain
+Crystalformer distance encoding) is implemented.
+"""
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor
+from torch.nn import Module, Parameter
+from torch.nn.init import constant_, normal_, xavier_uniform_
+from torch.nn.modules.linear import NonDynamicallyQuantizableLinear
+
+from .cuda_funcs import (ComputeFrame1MaximumMethodCUDA, ComputeFrame2MaximumMethodCUDA,
+                         FusedDotProductAttentionCUDA, RealEncodingWithFramedProjFuncCUDA, max_frames_fused)
+from .latticeformer_params import LatticeformerParams
+
+# use the single-launch frame construction instead of the two Functions plus torch ops
+FUSED_FRAMES = True
+
+
+def _scaled_dot_product_attention(q, k, v, batch, batch_kv, edges, attn_weights=None, values=None, dropout_p=0.0):
+    """models/indexed_lattice_multi_head_attention_cuda.py:144-185 (the fused branch)."""
+    if dropout_p != 0.0 or batch is not batch_kv:
+        raise NotImplementedError("only dropout-free self-attention is implemented")
+    q = q / math.sqrt(q.shape[-1])
+    return FusedDotProductAttentionCUDA.apply(q, k, v, attn_weights, values, batch, edges), None, None
+
+
+def compute_frame_maximum_method_(q, k, v, alpha, pos, dist2_min, tvecs, batch, edges, proj, K, dist_max, wscale,
+                                  frame_method, this_epoch=None, rvecs=None, cutoff=None):
+    """models/indexed_lattice_multi_head_attention_cuda.py:435-493 for frame_method == "max"."""
+    if frame_method != "max":
+        raise NotImplementedError(f"frame_method={frame_method}")
+    rvlen = torch.norm(rvecs, 2, dim=-1) if cutoff is not None else None
+    qs = q / math.sqrt(q.shape[-1])
+    if FUSED_FRAMES:
+        with torch.no_grad():
+            return max_frames_fused(qs, k, alpha, pos, tvecs, batch, edges, rvlen, cutoff)
+    extra = (rvlen, cutoff) if cutoff is not None else ()
+    f1 = ComputeFrame1MaximumMethodCUDA.apply(qs, k, v, alpha, pos, dist2_min, tvecs, batch, edges, K, dist_max,
+                                              wscale, *extra)
+    f2m = ComputeFrame2MaximumMethodCUDA.apply(qs, k, v, alpha, pos, dist2_min, tvecs, batch, edges, K, dist_max,
+                                               wscale, f1, *extra)
+    dot = (f1 * f2m).sum(dim=-1, keepdim=True)
+    f2 = F.normalize(f2m - dot * f1, dim=2)
+    return f1, f2, torch.linalg.cross(f1, f2)
+
+
+def compute_real_domain_attn_frame_proj(q, k, v, batch_q, batch_kv, edges, pos, dist2_min, tvecs, rvecs,
+                                        pe_dist_proj, proj_angle1, proj_angle2, proj_angle3, alpha,
+                                        params: LatticeformerParams = None, this_epoch=None):
+    """models/indexed_lattice_multi_head_attention_cuda.py:589-734: logit bias (E,H) and value
+    bias (E,H,hd) of every pair."""
+    K = params.value_pe_dist_real
+    dist_max = params.value_pe_dist_max
+    if dist_max < 0:
+        dist_max = (-dist_max) * params.scale_real
+    wscale = params.value_pe_dist_wscale
+    adap = ()
+    if params.adaptive_cutoff_sigma < 0:
+        adap = (rvecs, params.adaptive_cutoff_sigma)
+    elif params.adaptive_cutoff_sigma > 0:
+        adap = (rvecs, params.scale_real * params.gauss_lb_real ** (-0.5) * params.adaptive_cutoff_sigma)
+    rv_args = (torch.norm(adap[0], 2, dim=-1), adap[1]) if adap else ()
+    if params.frame_method == "max":
+        f1, f2, f3 = compute_frame_maximum_method_(q, k, None, alpha, pos, dist2_min, tvecs, batch_q, edges,
+                                                   pe_dist_proj, K, dist_max, wscale, "max", this_epoch, *adap)
+        W1, W2, W3 = proj_angle1, proj_angle2, proj_angle3
+    elif params.frame_method == "no":
+        f1 = f2 = f3 = W1 = W2 = W3 = None
+    else:
+        raise NotImplementedError(f"frame_method={params.frame_method}")
+    out = RealEncodingWithFramedProjFuncCUDA.apply(
+        alpha, pos, dist2_min, tvecs, batch_q, edges, K, dist_max, wscale, pe_dist_proj, W1, W2, W3, f1, f2, f3,
+        params.value_pe_angle_real, params.value_pe_angle_wscale, params.cos_abs, params.value_pe_dist_coef,
+        params.value_pe_angle_coef, *rv_args)
+    return out[0], (out[1] if len(out) > 1 else None)
+
+
+def gaussian_coefficients(q, lattice_pos_weights, gauss_scale, params, training):
+    """models/indexed_lattice_multi_head_attention_cuda.py:896-940: per (atom, head) coefficient
+    a < 0 of exp(a d^2), from q and the learned per-head direction, normalised with statistics
+    that are measured once (first training forward) and then stored in ``gauss_scale``."""
+    N, H, hd = q.shape
+    if not params.gauss_state.startswith("q"):
+        raise NotImplementedError(f"gauss_state={params.gauss_state}")
+    alpha = (q.reshape(N, H, 1, hd) @ lattice_pos_weights.reshape(H, hd, 1)).view(N, H)
+    if params.normalize_gauss:
+        if bool(gauss_scale[0] > 0):
+            scale, shift = gauss_scale[0], gauss_scale[1]
+        else:
+            scale = torch.reciprocal(alpha.detach().std())
+            shift = -alpha.detach().mean()
+            if training:
+                with torch.no_grad():
+                    gauss_scale[0] = scale
+                    gauss_scale[1] = shift
+        alpha = (alpha + shift) * scale
+    lb, beta = params.gauss_lb_real, params.positive_func_beta
+    pos = (1.0 - lb) * F.elu(alpha * (beta / (1.0 - lb))) + 1.0
+    return pos * (-0.5 * params.scale_real ** -2)
+
+
+def crystalformer_multi_head_attention_forward_cuda(
+        query, key, value, batch_q, batch_kv, edges, pos, dist2_min, tvecs, kr_base, rvecs, vcell,
+        lattice_pos_weights, embed_dim_to_check, num_heads, q_proj_weight, k_proj_weight, v_proj_weight,
+        in_proj_bias, dropout_p, out_proj_weight, out_proj_bias, pe_dist_proj, pe_wave_proj, proj_angle1,
+        proj_angle2, proj_angle3, training=True, need_weights=True, gauss_scale=None, atten_scale=None,
+        onehot=None, params: LatticeformerParams = None, this_epoch=None) -> Tuple[Tensor, Optional[Tensor]]:
+    """models/indexed_lattice_multi_head_attention_cuda.py:737-996, real-space domain."""
+    N = query.shape[0]
+    hq, hk, hv = (w.shape[0] // num_heads for w in (q_proj_weight, k_proj_weight, v_proj_weight))
+    if in_proj_bias is None:
+        bq = bk = bv = None
+    else:
+        bq, bk, bv = in_proj_bias.split([q_proj_weight.size(0), k_proj_weight.size(0), v_proj_weight.size(0)])
+    q = F.linear(query, q_proj_weight, bq).view(N, num_heads, hq)
+    k = F.linear(key, k_proj_weight, bk).view(key.shape[0], num_heads, hk)
+    v = F.linear(value, v_proj_weight, bv).view(value.shape[0], num_heads, hv)
+    attn_weights = values = None
+    if params is not None and params.domain != "no":
+        if params.domain != "real":
+            raise NotImplementedError(f"domain={params.domain}: only the real-space domain is implemented")
+        alpha = gaussian_coefficients(q, lattice_pos_weights, gauss_scale, params, training)
+        attn_weights, values = compute_real_domain_attn_frame_proj(
+            q, k, v, batch_q, batch_kv, edges, pos, dist2_min, tvecs, rvecs, pe_dist_proj, proj_angle1,
+            proj_angle2, proj_angle3, alpha, params, this_epoch)
+    if not training:
+        dropout_p = 0.0
+    out, _, _ = _scaled_dot_product_attention(q, k, v, batch_q, batch_kv, edges, attn_weights, values, dropout_p)
+    out = F.linear(out.contiguous().view(N, hv * num_heads), out_proj_weight, out_proj_bias)
+    if need_weights:
+        raise NotImplementedError("need_weights=True: use cuda_funcs.attention_probabilities")
+    return out, values
+
+
+class CrystalformerMultiheadAttentionCUDA(Module):
+    """models/indexed_lattice_multi_head_attention_cuda.py:998-1269.  Parameters:
+    q_proj_weight, k_proj_weight, v_proj_weight, in_proj_bias, out_proj.{weight,bias},
+    lattice_pos_weights (H*hd), pe_dist_proj (1,H,hd,D_dist), proj_angle1..3 (1,H,hd,D_ang),
+    and the non-trainable gauss_scale (2), atten_scale (1)."""
+
+    def __init__(self, embed_dim, num_heads, dropout=0., bias=True, kdim=None, vdim=None,
+                 params=LatticeformerParams(), device=None, dtype=None) -> None:
+        kw = {"device": device, "dtype": dtype}
+        super().__init__()
+        if params.domain not in ("real", "no"):
+            raise NotImplementedError(f"domain={params.domain}")
+        self.embed_dim = embed_dim
+        self.kdim = kdim * num_heads if kdim is not None and kdim > 0 else embed_dim
+        self.vdim = vdim * num_heads if vdim is not None and vdim > 0 else embed_dim
+        self.params = params
+        self.num_heads = num_heads
+        self.dropout = dropout
+        self.head_dim = embed_dim // num_heads
+        assert self.head_dim * num_heads == embed_dim, "embed_dim must be divisible by num_heads"
+        self.gauss_scale = Parameter(torch.zeros(2, **kw), requires_grad=False)
+        self.atten_scale = Parameter(torch.zeros(1, **kw), requires_grad=False)
+        self.q_proj_weight = Parameter(torch.empty((self.kdim, embed_dim), **kw))
+        self.k_proj_weight = Parameter(torch.empty((self.kdim, embed_dim), **kw))
+        self.v_proj_weight = Parameter(torch.empty((self.vdim, embed_dim), **kw))
+        if bias:
+            self.in_proj_bias = Parameter(torch.empty(self.kdim * 2 + self.vdim, **kw))
+        else:
+            self.register_parameter("in_proj_bias", None)
+        self.out_proj = NonDynamicallyQuantizableLinear(self.vdim, embed_dim, bias=bias, **kw)
+        self.lattice_pos_weights = None
+        self.pe_dist_proj = self.pe_wave_proj = self.proj_angle1 = self.proj_angle2 = self.proj_angle3 = None
+        if params.domain == "real":
+            if not params.gauss_state.startswith("q"):
+                raise NotImplementedError(f"gauss_state={params.gauss_state}")
+            self.lattice_pos_weights = Parameter(torch.empty(self.kdim, **kw))
+            if params.value_pe_dist_real > 0:
+                self.pe_dist_proj = Parameter(torch.empty(1, num_heads, self.head_dim, params.value_pe_dist_real, **kw))
+            if params.value_pe_angle_real > 0:
+                shape = (1, num_heads, self.head_dim, params.value_pe_angle_real)
+                self.proj_angle1 = Parameter(torch.empty(*shape, **kw))
+                self.proj_angle2 = Parameter(torch.empty(*shape, **kw))
+                self.proj_angle3 = Parameter(torch.empty(*shape, **kw))
+        self._reset_parameters()
+
+    def _reset_parameters(self):
+        for w in (self.q_proj_weight, self.k_proj_weight, self.v_proj_weight, self.out_proj.weight):
+            xavier_uniform_(w)
+        if self.in_proj_bias is not None:
+            constant_(self.in_proj_bias, 0.)
+            constant_(self.out_proj.bias, 0.)
+        if self.lattice_pos_weights is not None:
+            std = (self.kdim) ** -0.5 if self.params.gauss_state == "q-kdim" else (self.kdim // self.num_heads) ** -0.5
+            normal_(self.lattice_pos_weights, 0., std)
+        with torch.no_grad():
+            for P in (self.pe_dist_proj, self.proj_angle1, self.proj_angle2, self.proj_angle3):
+                if P is not None:
+                    for W in P:
+                        W2 = W.view(-1, W.shape[-1])
+                        xavier_uniform_(W2, W2.shape[1] ** -0.5)
+
+    def forward(self, query, key, value, batch_q, batch_kv, edges, points, dist2_min, tvecs, kr_base=None,
+                rvecs=None, vcell=None, onehot=None, need_weights=True, this_epoch=None):
+        return crystalformer_multi_head_attention_forward_cuda(
+            query, key, value, batch_q, batch_kv, edges, points, dist2_min, tvecs, kr_base, rvecs, vcell,
+            self.lattice_pos_weights, self.embed_dim, self.num_heads, self.q_proj_weight, self.k_proj_weight,
+            self.v_proj_weight, self.in_proj_bias, self.dropout, self.out_proj.weight, self.out_proj.bias,
+            self.pe_dist_proj, self.pe_wave_proj, self.proj_angle1, self.proj_angle2, self.proj_angle3,
+            training=self.training, need_weights=need_weights, gauss_scale=self.gauss_scale,
+            atten_scale=self.atten_scale, onehot=onehot, params=self.params, this_epoch=this_epoch)

@@ -1,0 +1,296 @@
+// C ABI of libcfb200: argument checks, hyper-parameter binding and kernel launches.
+// The library is one translation unit; the kernel files are included below.
+#include <math.h>
+#include <string.h>
+#include "common.cuh"
+#include "framed_proj.cu"
+#include "frames.cu"
+#include "dpa.cu"
+#include "pool_index.cu"
+
+namespace {
+
+cfb200_config g_cfg;
+bool g_configured = false;
+
+// Same formulas as the reference host code: LENGTH_RANGE / ANGLE_RANGE
+// (models/cuda_funcs/kernel_manager.py:148-149), angle sigma
+// (models/cuda_funcs/real_space_framed_proj.py:37-40), and the per-kernel constants
+// (models/kernels/real_enc_frame_proj_fwd_length.cu:130-132, ..._fwd_angle.cu:136-143),
+// evaluated in float where the kernels evaluate them in float.
+int make_params(float dist_max, float cutoff_radius, cfb::Params& P)
+{
+    if (!g_configured) return CFB200_E_NOT_CONFIGURED;
+    const cfb200_config& c = g_cfg;
+    memset(&P, 0, sizeof(P));
+    P.H = c.num_heads; P.head_dim = c.head_dim; P.dist_dim = c.dist_dim; P.angle_dim = c.angle_dim;
+    P.lattice_range = c.lattice_range; P.minimum_range = c.minimum_range; P.cos_abs = c.cos_abs;
+    P.cutoff_radius = cutoff_radius;
+    P.c_dist = c.dist_coef; P.c_ang = c.angle_coef; P.noise = c.symm_break_noise;
+    P.win_dist = (int)ceil(2.0 * (double)c.dist_wscale * c.cut_sigma + 1.0);
+    P.windowed_dist = (c.dist_dim - P.win_dist > 8) ? 1 : 0;
+    if (!P.windowed_dist) P.win_dist = c.dist_dim;
+    P.d_interval = dist_max / (float)c.dist_dim;
+    P.d_step = 1.0f / (c.dist_wscale * sqrtf(2.0f));
+    P.d_cut = (float)c.cut_sigma * (P.d_interval * c.dist_wscale);
+    if (c.angle_dim > 1) {
+        P.win_ang = (int)ceil(2.0 * (double)c.angle_wscale * c.cut_sigma + 1.0);
+        P.windowed_ang = (c.angle_dim - P.win_ang > 8) ? 1 : 0;
+        if (!P.windowed_ang) P.win_ang = c.angle_dim;
+        const double span = c.cos_abs ? 1.0 : 2.0;
+        const float angle_sigma = (float)(span * (double)c.angle_wscale / (double)(c.angle_dim - 1));
+        const float spanf = (float)span;
+        P.a_step = spanf / ((float)(c.angle_dim - 1) * angle_sigma * sqrtf(2.0f));
+        P.a_interval = spanf / (float)(c.angle_dim - 1);
+        P.a_sigma_inv = 1.0f / (angle_sigma * sqrtf(2.0f));
+        P.a_cut = (float)c.cut_sigma * angle_sigma;
+    }
+    return CFB200_OK;
+}
+
+inline cudaStream_t S(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+}  // namespace
+
+extern "C" {
+
+int cfb200_version(void) { return 1; }
+
+const char* cfb200_error_string(int code)
+{
+    switch (code) {
+        case CFB200_OK: return "ok";
+        case CFB200_E_NULL: return "a required pointer is NULL";
+        case CFB200_E_SHAPE: return "negative or inconsistent extent";
+        case CFB200_E_UNSUPPORTED: return "no kernel instance for these hyper-parameters";
+        case CFB200_E_NOT_CONFIGURED: return "cfb200_configure has not been called";
+        case CFB200_E_WORKSPACE: return "scratch buffer missing or too small";
+        case CFB200_E_CUDA: return "CUDA launch failed";
+        default: return "unknown error";
+    }
+}
+
+int cfb200_configure(const cfb200_config* cfg)
+{
+    if (cfg == nullptr) return CFB200_E_NULL;
+    const cfb200_config& c = *cfg;
+    if (c.head_dim != 16 || c.dist_dim != 64 || !(c.angle_dim == 0 || c.angle_dim == 64)) return CFB200_E_UNSUPPORTED;
+    if (c.num_heads < 1 || c.num_heads > 32 || (32 % c.num_heads) != 0) return CFB200_E_UNSUPPORTED;
+    if (c.lattice_range < 0 || c.lattice_range > CFB200_MAX_RANGE || c.minimum_range < 0 ||
+        c.minimum_range > CFB200_MAX_RANGE) return CFB200_E_UNSUPPORTED;
+    if (c.cut_sigma < 1 || !(c.dist_wscale > 0.f) || (c.angle_dim > 0 && !(c.angle_wscale > 0.f))) return CFB200_E_UNSUPPORTED;
+    if (ceil(2.0 * c.dist_wscale * c.cut_sigma + 1.0) > 64.0 && c.dist_dim - ceil(2.0 * c.dist_wscale * c.cut_sigma + 1.0) > 8)
+        return CFB200_E_UNSUPPORTED;
+    g_cfg = c;
+    g_configured = true;
+    return CFB200_OK;
+}
+
+int cfb200_get_config(cfb200_config* out)
+{
+    if (out == nullptr) return CFB200_E_NULL;
+    if (!g_configured) return CFB200_E_NOT_CONFIGURED;
+    *out = g_cfg;
+    return CFB200_OK;
+}
+
+int cfb200_status(int32_t* status_out, void* stream)
+{
+    if (status_out == nullptr) return CFB200_E_NULL;
+    int v = 0;
+    if (cudaMemcpyFromSymbolAsync(&v, cfb::g_status, sizeof(int), 0, cudaMemcpyDeviceToHost, S(stream)) != cudaSuccess)
+        return CFB200_E_CUDA;
+    if (cudaStreamSynchronize(S(stream)) != cudaSuccess) return CFB200_E_CUDA;
+    const int zero = 0;
+    if (v != 0 && cudaMemcpyToSymbolAsync(cfb::g_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, S(stream)) != cudaSuccess)
+        return CFB200_E_CUDA;
+    if (v != 0) cudaStreamSynchronize(S(stream));
+    *status_out = v;
+    return CFB200_OK;
+}
+
+int64_t cfb200_framed_proj_bwd_workspace_bytes(int64_t N, int64_t E)
+{
+    if (!g_configured || N < 0 || E < 0) return -1;
+    return cfb::framed_proj_bwd_workspace_bytes(N, E, g_cfg.num_heads);
+}
+
+int cfb200_edge_index(const int64_t* sizes, int64_t B, int64_t N, int64_t E, int64_t* edges, int64_t* e_start,
+                      int64_t* batch, int64_t* crystal_start, void* stream)
+{
+    if (B < 0 || N < 0 || E < 0) return CFB200_E_SHAPE;
+    if ((B > 0 && sizes == nullptr) || e_start == nullptr || crystal_start == nullptr || (E > 0 && edges == nullptr))
+        return CFB200_E_NULL;
+    return cfb::edge_index(sizes, B, N, E, edges, e_start, batch, crystal_start, S(stream));
+}
+
+int cfb200_csr_offsets(const int64_t* edge_i, int64_t E, int64_t N, int64_t* e_start, void* stream)
+{
+    if (N < 0 || E < 0) return CFB200_E_SHAPE;
+    if (e_start == nullptr || (E > 0 && edge_i == nullptr)) return CFB200_E_NULL;
+    return cfb::csr_offsets(edge_i, E, N, e_start, S(stream));
+}
+
+static int frames_common(int mode, const float* q, const float* k, const float* a_ik, const float* pos_ij,
+                         const float* tvecs, const float* rvlen, const int64_t* batch, const int64_t* edges,
+                         const int64_t* e_start, int64_t N, int64_t E, float cutoff_radius, uint64_t seed1,
+                         uint64_t seed2, const float* frame1_in, float* f1, float* f2, float* f3, int64_t* sel_edge,
+                         int32_t* sel_image, void* stream)
+{
+    if (N < 0 || E < 0) return CFB200_E_SHAPE;
+    cfb::Params P;
+    int rc = make_params(1.0f, cutoff_radius, P);
+    if (rc != CFB200_OK) return rc;
+    if (N == 0) return CFB200_OK;
+    if (!q || !k || !a_ik || !pos_ij || !tvecs || !batch || !edges || !e_start) return CFB200_E_NULL;
+    if (cutoff_radius != 0.0f && rvlen == nullptr) return CFB200_E_NULL;
+    cfb::FrArgs A;
+    A.q = q; A.k = k; A.a_ik = a_ik; A.pos_ij = pos_ij; A.tvecs = tvecs; A.rvlen = rvlen;
+    A.batch = batch; A.edges = edges; A.e_start = e_start; A.N = N; A.E = E;
+    A.seed1 = seed1; A.seed2 = seed2; A.frame1_in = frame1_in;
+    A.frame1 = f1; A.frame2 = f2; A.frame3 = f3; A.sel_edge = sel_edge; A.sel_image = sel_image; A.mode = mode;
+    return cfb::max_frame(A, P, S(stream));
+}
+
+int cfb200_max_frame(int axis, const float* q_scaled, const float* k, const float* a_ik, const float* pos_ij,
+                     const float* tvecs, const float* rvlen, const int64_t* batch, const int64_t* edges,
+                     const int64_t* e_start, int64_t N, int64_t E, float cutoff_radius, uint64_t seed,
+                     const float* frame1, float* frame, int64_t* sel_edge, int32_t* sel_image, void* stream)
+{
+    if (axis != 1 && axis != 2) return CFB200_E_SHAPE;
+    if (N > 0 && (frame == nullptr || (axis == 2 && frame1 == nullptr))) return CFB200_E_NULL;
+    return frames_common(axis, q_scaled, k, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, N, E, cutoff_radius,
+                         seed, seed, frame1, axis == 1 ? frame : nullptr, axis == 2 ? frame : nullptr, nullptr,
+                         sel_edge, sel_image, stream);
+}
+
+int cfb200_max_frames(const float* q_scaled, const float* k, const float* a_ik, const float* pos_ij,
+                      const float* tvecs, const float* rvlen, const int64_t* batch, const int64_t* edges,
+                      const int64_t* e_start, int64_t N, int64_t E, float cutoff_radius, uint64_t seed1,
+                      uint64_t seed2, float* frame1, float* frame2, float* frame3, void* stream)
+{
+    if (N > 0 && (!frame1 || !frame2 || !frame3)) return CFB200_E_NULL;
+    return frames_common(3, q_scaled, k, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, N, E, cutoff_radius,
+                         seed1, seed2, nullptr, frame1, frame2, frame3, nullptr, nullptr, stream);
+}
+
+static int fp_args(cfb::FpArgs& A, const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                   const int64_t* batch, const int64_t* edges, int64_t N, int64_t E, float cutoff_radius,
+                   const float* W_dist, const float* W1, const float* W2, const float* W3, const float* f1,
+                   const float* f2, const float* f3)
+{
+    if (N < 0 || E < 0) return CFB200_E_SHAPE;
+    if (E > 0 && (!a_ik || !pos_ij || !tvecs || !batch || !edges)) return CFB200_E_NULL;
+    if (cutoff_radius != 0.0f && E > 0 && rvlen == nullptr) return CFB200_E_NULL;
+    const bool ang = W1 || W2 || W3;
+    if (ang && !(W1 && W2 && W3 && f1 && f2 && f3)) return CFB200_E_NULL;
+    if (ang && g_cfg.angle_dim == 0) return CFB200_E_UNSUPPORTED;
+    memset(&A, 0, sizeof(A));
+    A.a_ik = a_ik; A.pos_ij = pos_ij; A.tvecs = tvecs; A.rvlen = rvlen; A.batch = batch; A.edges = edges;
+    A.N = N; A.E = E;
+    A.W[0] = W_dist; A.W[1] = W1; A.W[2] = W2; A.W[3] = W3;
+    A.frame[0] = f1; A.frame[1] = f2; A.frame[2] = f3;
+    return CFB200_OK;
+}
+
+int cfb200_framed_proj_fwd(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                           const int64_t* batch, const int64_t* edges, int64_t N, int64_t E, float dist_max,
+                           float cutoff_radius, const float* W_dist, const float* W_ang1, const float* W_ang2,
+                           const float* W_ang3, const float* frame1, const float* frame2, const float* frame3,
+                           float* z, float* values, void* stream)
+{
+    cfb::Params P;
+    int rc = make_params(dist_max, cutoff_radius, P);
+    if (rc != CFB200_OK) return rc;
+    cfb::FpArgs A;
+    rc = fp_args(A, a_ik, pos_ij, tvecs, rvlen, batch, edges, N, E, cutoff_radius, W_dist, W_ang1, W_ang2, W_ang3,
+                 frame1, frame2, frame3);
+    if (rc != CFB200_OK) return rc;
+    if (E > 0 && z == nullptr) return CFB200_E_NULL;
+    if (values != nullptr && W_dist == nullptr) return CFB200_E_NULL;
+    A.z = z; A.values = values;
+    return cfb::framed_proj_fwd(A, P, S(stream));
+}
+
+int cfb200_framed_proj_bwd(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                           const int64_t* batch, const int64_t* edges, const int64_t* e_start, int64_t N, int64_t E,
+                           float dist_max, float cutoff_radius, const float* W_dist, const float* W_ang1,
+                           const float* W_ang2, const float* W_ang3, const float* frame1, const float* frame2,
+                           const float* frame3, const float* z, const float* gz, const float* gvalues, float* ga,
+                           float* gW_dist, float* gW_ang1, float* gW_ang2, float* gW_ang3, void* workspace,
+                           int64_t workspace_bytes, void* stream)
+{
+    cfb::Params P;
+    int rc = make_params(dist_max, cutoff_radius, P);
+    if (rc != CFB200_OK) return rc;
+    cfb::FpArgs A;
+    rc = fp_args(A, a_ik, pos_ij, tvecs, rvlen, batch, edges, N, E, cutoff_radius, W_dist, W_ang1, W_ang2, W_ang3,
+                 frame1, frame2, frame3);
+    if (rc != CFB200_OK) return rc;
+    if (E > 0 && (!z || !gz || !gvalues || !W_dist || !e_start)) return CFB200_E_NULL;
+    if (N > 0 && (ga == nullptr || e_start == nullptr)) return CFB200_E_NULL;
+    if (gW_dist == nullptr) return CFB200_E_NULL;
+    A.z_in = z; A.gz = gz; A.gv = gvalues;
+    float* gW[4] = {gW_dist, gW_ang1, gW_ang2, gW_ang3};
+    return cfb::framed_proj_bwd(A, P, e_start, ga, gW, workspace, workspace_bytes, S(stream));
+}
+
+static int dp_args(cfb::DpArgs& A, const float* q, const float* k, const float* v, const float* z, const float* b,
+                   const int64_t* edges, const int64_t* e_start, int64_t N, int64_t E)
+{
+    if (N < 0 || E < 0) return CFB200_E_SHAPE;
+    if (N > 0 && (!q || !k || !v || !e_start || (E > 0 && !edges))) return CFB200_E_NULL;
+    memset(&A, 0, sizeof(A));
+    A.q = q; A.k = k; A.v = v; A.z = z; A.b = b; A.edges = edges; A.e_start = e_start; A.N = N; A.E = E;
+    return CFB200_OK;
+}
+
+int cfb200_dpa_fwd(const float* q_scaled, const float* k, const float* v, const float* z, const float* values,
+                   const int64_t* edges, const int64_t* e_start, int64_t N, int64_t E, float* out, float* lse,
+                   float* prob, void* stream)
+{
+    cfb::Params P;
+    int rc = make_params(1.0f, 0.0f, P);
+    if (rc != CFB200_OK) return rc;
+    cfb::DpArgs A;
+    rc = dp_args(A, q_scaled, k, v, z, values, edges, e_start, N, E);
+    if (rc != CFB200_OK) return rc;
+    if (N > 0 && (!out || !lse)) return CFB200_E_NULL;
+    A.out = out; A.lse = lse; A.prob = prob;
+    return cfb::dpa_fwd(A, P, S(stream));
+}
+
+int cfb200_dpa_bwd(const float* q_scaled, const float* k, const float* v, const float* z, const float* values,
+                   const int64_t* edges, const int64_t* e_start, int64_t N, int64_t E, const float* out,
+                   const float* lse, const float* gout, float* gq, float* gk, float* gv, float* gz, float* gvalues,
+                   void* stream)
+{
+    cfb::Params P;
+    int rc = make_params(1.0f, 0.0f, P);
+    if (rc != CFB200_OK) return rc;
+    cfb::DpArgs A;
+    rc = dp_args(A, q_scaled, k, v, z, values, edges, e_start, N, E);
+    if (rc != CFB200_OK) return rc;
+    if (N > 0 && (!out || !lse || !gout || !gq || !gk || !gv)) return CFB200_E_NULL;
+    if (E > 0 && gz == nullptr) return CFB200_E_NULL;
+    if (values != nullptr && E > 0 && gvalues == nullptr) return CFB200_E_NULL;
+    A.out = const_cast<float*>(out); A.lse = const_cast<float*>(lse); A.gout = gout;
+    A.gq = gq; A.gk = gk; A.gv = gv; A.gz = gz; A.gb = values ? gvalues : nullptr;
+    return cfb::dpa_bwd(A, P, S(stream));
+}
+
+int cfb200_segment_mean_fwd(const float* x, const int64_t* start, int64_t B, int64_t D, float* out, void* stream)
+{
+    if (B < 0 || D < 0) return CFB200_E_SHAPE;
+    if (B * D > 0 && (!x || !start || !out)) return CFB200_E_NULL;
+    return cfb::segment_mean(false, x, start, B, D, out, S(stream));
+}
+
+int cfb200_segment_mean_bwd(const float* gout, const int64_t* start, int64_t B, int64_t D, float* gx, void* stream)
+{
+    if (B < 0 || D < 0) return CFB200_E_SHAPE;
+    if (B * D > 0 && (!gout || !start || !gx)) return CFB200_E_NULL;
+    return cfb::segment_mean(true, gout, start, B, D, gx, S(stream));
+}
+
+}  // extern "C"

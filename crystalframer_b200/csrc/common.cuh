@@ -1,0 +1,95 @@
+// Shared device helpers of libcfb200 (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "../../include/cfb200.h"
+
+#ifndef __CUDA_ARCH__
+#define CFB_ARCH_OK 1
+#elif __CUDA_ARCH__ >= 1000
+#define CFB_ARCH_OK 1
+#else
+#error "libcfb200 is written for sm_100a only"
+#endif
+
+namespace cfb {
+
+constexpr int kWarp = 32;
+constexpr float kPiF = 3.141592654f;          // float-rounded pi, as CUDART_PI_F
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kSqrtLog2e = 1.2011224087864498f;
+
+// Derived, launch-time view of cfb200_config (host fills it, kernels take it by value).
+struct Params {
+    int H, head_dim, dist_dim, angle_dim;
+    int lattice_range, minimum_range, cos_abs;
+    int win_dist, win_ang;        // LENGTH_RANGE / ANGLE_RANGE; == dim when the full range is computed
+    int windowed_dist, windowed_ang;
+    float cutoff_radius;
+    float c_dist, c_ang, noise;
+    // distance basis: b(dim) = (-d/interval + dim + 1) * step
+    float d_interval, d_step, d_cut;      // d_cut = cut_sigma * sigma
+    // angle basis: b(dim) = (1 - cos) * sigma_inv - (D - 1 - dim) * step
+    float a_interval, a_step, a_sigma_inv, a_cut;   // a_cut = cut_sigma * angle_sigma
+};
+
+// Device status word (bits CFB200_ST_*).  The library is built as one translation unit.
+__device__ int g_status = 0;
+
+__device__ __forceinline__ float ex2_approx(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_min(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Counter-based uniform in (0,1] for the symmetry-breaking noise of the frame search.
+// The reference draws from per-thread curand XORWOW streams whose seed comes from numpy's
+// global generator (models/cuda_funcs/calc_maximum_frame.py:43); nothing pins those streams,
+// so a stateless hash of (seed, pair*H+head, translation index) is used instead.
+__host__ __device__ __forceinline__ float hash_uniform(uint64_t seed, uint64_t tid, uint32_t draw)
+{
+    uint64_t x = seed ^ (tid * 0x9E3779B97F4A7C15ull) ^ ((uint64_t)draw * 0xD1B54A32D192ED03ull);
+    x ^= x >> 30; x *= 0xBF58476D1CE4E5B9ull;
+    x ^= x >> 27; x *= 0x94D049BB133111EBull;
+    x ^= x >> 31;
+    return (float)((uint32_t)(x >> 40) + 1u) * (1.0f / 16777216.0f);
+}
+
+// Lattice range along one reciprocal axis for Gaussian coefficient a (< 0):
+// models/kernels/real_enc_frame_proj_fwd_length.cu:59-86.  (cutoff + 0.01f) * rvl is a float
+// product, the division by 2.0 * CUDART_PI_F and the ceil are double, as in the reference.
+__device__ __forceinline__ int lattice_range_1d(const Params& P, float a, float rvl)
+{
+    int R = P.lattice_range;
+    float cutoff = P.cutoff_radius;
+    if (cutoff != 0.0f) {
+        if (cutoff < 0.0f) cutoff = __fmul_rn(__fsqrt_rn(__fdiv_rn(-0.5f, a)), -cutoff);
+        float num = __fmul_rn(__fadd_rn(cutoff, 0.01f), rvl);
+        double r = ceil((double)num / (2.0 * (double)kPiF));
+        // NaN (a >= 0) and runaway ranges are reported through the status word, never looped on
+        if (!(r <= (double)CFB200_MAX_RANGE)) {
+            atomicOr(&g_status, !(a < 0.0f) ? CFB200_ST_BAD_COEF : CFB200_ST_RANGE_CLAMPED);
+            r = !(a < 0.0f) ? (double)P.lattice_range : (double)CFB200_MAX_RANGE;
+        }
+        R = (int)r;
+        if (P.minimum_range > 0) R = max(R, P.minimum_range);
+    }
+    return R;
+}
+
+}  // namespace cfb

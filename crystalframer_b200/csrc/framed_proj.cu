@@ -1,0 +1,442 @@
+// Lattice-sum attention bias and frame-projected value position encoding, forward and
+// backward (replaces real_enc_frame_proj_{fwd,bwd}_{length,angle}.cu of the reference).
+//
+// Work decomposition
+//   grid  = (resident blocks, heads); a block owns one head and walks chunks of 32 pairs.
+//   warp  = one (pair, head) task at a time.  Lanes first evaluate 32 lattice translations in
+//           parallel (separation, weight w = exp(a (d^2 - d^2_min)), window positions), drop
+//           translations whose weight is below exp(-kPrune), and leave one record per surviving
+//           translation in shared memory.  Then the warp walks the survivors: lane l owns basis
+//           indices l and l+32 of each of the four 64-wide Gaussian bases (distance, three frame
+//           axes) and keeps their running sums in registers, so the data-dependent window offset
+//           becomes a per-lane predicate instead of an indexed shared-memory update.
+//   block = after 4 tasks per warp the 32 basis vectors (32 x 256) sit in shared memory and the
+//           block multiplies them with the head's 16 x 256 projection (forward) or accumulates
+//           the outer product with the upstream gradient (backward) -- the projection weights are
+//           read once per 32 pairs instead of once per pair.
+//
+// Numerics follow the reference's float expressions for every integer decision (lattice range,
+// window start / end); Gaussians use ex2.approx on pre-scaled arguments.
+#include "common.cuh"
+
+namespace cfb {
+
+constexpr int kFpWarps = 8;
+constexpr int kFpThreads = kFpWarps * 32;
+constexpr int kFpTasksPerWarp = 4;
+constexpr int kFpSlots = kFpWarps * kFpTasksPerWarp;   // pairs per chunk (== 32: one lane per pair in the projection)
+constexpr int kFpK = 256;                              // 4 bases x 64
+constexpr int kFpStageStride = 260;                    // padded row: conflict-free 128-bit reads by 32 lanes
+constexpr int kHd = 16;                                // head dimension of this instance
+constexpr float kPrune = 30.0f;                        // drop translations with weight < e^-30
+
+static_assert(kFpSlots == 32, "projection maps one lane to one staged pair");
+
+struct FpArgs {
+    const float* a_ik; const float* pos_ij; const float* tvecs; const float* rvlen;
+    const int64_t* batch; const int64_t* edges;
+    int64_t N, E;
+    const float* W[4];        // distance, axis 1..3; each (H,16,64)
+    const float* frame[3];    // each (N,H,3)
+    float* z; float* values;                     // forward outputs
+    const float* z_in; const float* gz; const float* gv;   // backward inputs
+    float* ga_e;              // (E,H) per-pair coefficient gradient (scratch)
+    float* gW_part;           // (gridDim.x, H, 16, 256) per-block weight gradient (scratch)
+};
+
+constexpr size_t kFpSmemFloats = (size_t)kHd * kFpK + (size_t)kFpSlots * kFpStageStride + (size_t)kFpWarps * 2 * 32 * 4 + 16 * 33;
+constexpr size_t kFpSmemBytes = kFpSmemFloats * sizeof(float);
+
+// q = t / L, r = t % L for small non-negative t and L (float reciprocal plus one correction step)
+__device__ __forceinline__ void divmod_small(int t, int L, float invL, int& q, int& r)
+{
+    q = __float2int_rz(__int2float_rn(t) * invL);
+    r = t - q * L;
+    if (r < 0) { q--; r += L; }
+    else if (r >= L) { q++; r -= L; }
+}
+
+template <bool BWD, bool ANG>
+__global__ void __launch_bounds__(kFpThreads, 2) framed_proj_kernel(const FpArgs A, const Params P)
+{
+    extern __shared__ __align__(16) float smem[];
+    float* W_s = smem;                                          // [16][256]
+    float* stage = W_s + kHd * kFpK;                            // [32][260]
+    float4* tbuf = reinterpret_cast<float4*>(stage + kFpSlots * kFpStageStride);  // [8][2][32]
+    float* side = reinterpret_cast<float*>(tbuf + kFpWarps * 2 * 32);             // fwd: out [16][33]; bwd: gv [32][16]
+
+    const int h = blockIdx.y, H = P.H;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // projection weights of this head: W_s[o][basis*64 + dim]
+    for (int idx = threadIdx.x; idx < kHd * kFpK / 4; idx += kFpThreads) {
+        const int o = idx >> 6, k4 = idx & 63, b = k4 >> 4, d4 = k4 & 15;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (A.W[b] != nullptr)
+            v = __ldg(reinterpret_cast<const float4*>(A.W[b] + ((size_t)h * kHd + o) * 64) + d4);
+        reinterpret_cast<float4*>(W_s)[idx] = v;
+    }
+
+    // per-lane basis constants, pre-scaled so that a Gaussian is ex2(-b*b)
+    const float dstep = P.d_step * kSqrtLog2e, astep = P.a_step * kSqrtLog2e;
+    const float cd_lo = (float)(lane + 1) * dstep, cd_hi = (float)(lane + 33) * dstep;
+    const float ca_lo = (float)(63 - lane) * astep, ca_hi = (float)(31 - lane) * astep;
+    const unsigned win_d = (unsigned)P.win_dist, win_a = (unsigned)P.win_ang;
+    const bool wide_d = P.win_dist > 32;
+
+    float gacc[2][8];
+    if (BWD) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) gacc[0][j] = gacc[1][j] = 0.f;
+    }
+    float4* tb = tbuf + warp * 64;
+    __syncthreads();
+
+    const int64_t nChunks = (A.E + kFpSlots - 1) / kFpSlots;
+    for (int64_t chunk = blockIdx.x; chunk < nChunks; chunk += gridDim.x) {
+        for (int tsk = 0; tsk < kFpTasksPerWarp; tsk++) {
+            const int slot = tsk * kFpWarps + warp;
+            const int64_t e = chunk * kFpSlots + slot;
+            float* srow = stage + slot * kFpStageStride;
+            if (e >= A.E) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) srow[j * 32 + lane] = 0.f;
+                if (BWD && lane < kHd) side[slot * kHd + lane] = 0.f;
+                continue;
+            }
+            const int64_t i = A.edges[e];
+            const int64_t c = A.batch[i];
+            const float rx = __ldg(A.pos_ij + 3 * e), ry = __ldg(A.pos_ij + 3 * e + 1), rz = __ldg(A.pos_ij + 3 * e + 2);
+            const float* Tc = A.tvecs + 9 * c;
+            const float t1x = __ldg(Tc), t1y = __ldg(Tc + 1), t1z = __ldg(Tc + 2);
+            const float t2x = __ldg(Tc + 3), t2y = __ldg(Tc + 4), t2z = __ldg(Tc + 5);
+            const float t3x = __ldg(Tc + 6), t3y = __ldg(Tc + 7), t3z = __ldg(Tc + 8);
+            const float a = __ldg(A.a_ik + i * H + h);
+            int Rl = 0;
+            if (lane < 3) Rl = lattice_range_1d(P, a, P.cutoff_radius != 0.0f ? __ldg(A.rvlen + 3 * c + lane) : 0.0f);
+            const int R1 = __shfl_sync(0xffffffffu, Rl, 0), R2 = __shfl_sync(0xffffffffu, Rl, 1), R3 = __shfl_sync(0xffffffffu, Rl, 2);
+            const int L2 = 2 * R2 + 1, L3 = 2 * R3 + 1, L23 = L2 * L3;
+            const int Ttot = (2 * R1 + 1) * L23;
+            const float invL23 = 1.0f / (float)L23, invL3 = 1.0f / (float)L3;
+            float fx[3], fy[3], fz[3];
+            if (ANG) {
+#pragma unroll
+                for (int x = 0; x < 3; x++) {
+                    const float* f = A.frame[x] + (i * H + h) * 3;
+                    fx[x] = __ldg(f); fy[x] = __ldg(f + 1); fz[x] = __ldg(f + 2);
+                }
+            }
+            float zin = 0.f;
+            if (BWD) zin = __ldg(A.z_in + e * H + h);
+
+            // ---- sweep A (forward only): minimum squared distance over the translations ----
+            float d2min = 1e10f;
+            if (!BWD) {
+                for (int base = 0; base < Ttot; base += 32) {
+                    const int t = base + lane;
+                    if (t < Ttot) {
+                        int q1, r1, q2, r2;
+                        divmod_small(t, L23, invL23, q1, r1);
+                        divmod_small(r1, L3, invL3, q2, r2);
+                        const float n1 = (float)(q1 - R1), n2 = (float)(q2 - R2), n3 = (float)(r2 - R3);
+                        const float dx = fmaf(t3x, n3, fmaf(t2x, n2, fmaf(t1x, n1, rx)));
+                        const float dy = fmaf(t3y, n3, fmaf(t2y, n2, fmaf(t1y, n1, ry)));
+                        const float dz = fmaf(t3z, n3, fmaf(t2z, n2, fmaf(t1z, n1, rz)));
+                        d2min = fminf(d2min, fmaf(dz, dz, fmaf(dy, dy, dx * dx)));
+                    }
+                }
+                d2min = warp_min(d2min);
+            }
+
+            // ---- sweep B: weights, window records, basis accumulation ----
+            float sd[2] = {0.f, 0.f}, sa[3][2] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+            float qd[2] = {0.f, 0.f}, qa[3][2] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};   // backward: sums of g*p*d2
+            float sum_l = 0.f, px_l = 0.f;
+            for (int base = 0; base < Ttot; base += 32) {
+                const int t = base + lane;
+                bool keep = false;
+                if (t < Ttot) {
+                    int q1, r1, q2, r2;
+                    divmod_small(t, L23, invL23, q1, r1);
+                    divmod_small(r1, L3, invL3, q2, r2);
+                    const float n1 = (float)(q1 - R1), n2 = (float)(q2 - R2), n3 = (float)(r2 - R3);
+                    const float dx = fmaf(t3x, n3, fmaf(t2x, n2, fmaf(t1x, n1, rx)));
+                    const float dy = fmaf(t3y, n3, fmaf(t2y, n2, fmaf(t1y, n1, ry)));
+                    const float dz = fmaf(t3z, n3, fmaf(t2z, n2, fmaf(t1z, n1, rz)));
+                    const float d2 = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
+                    const float arg = BWD ? fmaf(a, d2, -zin) : a * (d2 - d2min);
+                    const float w = ex2_approx(arg * kLog2e);
+                    sum_l += w;
+                    if (BWD) px_l = fmaf(w, d2, px_l);
+                    keep = arg > -kPrune;
+                    if (keep) {
+                        const float d = __fsqrt_rn(d2);
+                        int lo_d = 0;
+                        if (P.windowed_dist) {
+                            lo_d = (int)(__fdiv_rn(d - P.d_cut, P.d_interval) - 1.0f);
+                            lo_d = min(max(lo_d, 0), 64 - P.win_dist);
+                        }
+                        const float xd = __fdiv_rn(-d, P.d_interval) * dstep;
+                        float xa[3] = {0.f, 0.f, 0.f};
+                        int lo_pack = lo_d;
+                        if (ANG) {
+#pragma unroll
+                            for (int x = 0; x < 3; x++) {
+                                float cosv = 1e3f;
+                                if (d2 > 1e-5f) cosv = __fdiv_rn(fmaf(dz, fz[x], fmaf(dy, fy[x], dx * fx[x])), d);
+                                if (P.cos_abs) cosv = fabsf(cosv);
+                                int lo = 0;
+                                if (P.windowed_ang) {
+                                    float en = __fdiv_rn(cosv + 1.0f + P.a_cut, P.a_interval) + 1.0f;
+                                    int end = (int)fminf(en, 64.0f);
+                                    end = max(end, P.win_ang);
+                                    lo = end - P.win_ang;
+                                }
+                                xa[x] = (1.0f - cosv) * (P.a_sigma_inv * kSqrtLog2e);
+                                lo_pack |= lo << (8 * (x + 1));
+                            }
+                        }
+                        tb[lane] = make_float4(w, xd, xa[0], xa[1]);
+                        tb[32 + lane] = make_float4(xa[2], __int_as_float(lo_pack), d2, 0.f);
+                    }
+                }
+                unsigned mask = __ballot_sync(0xffffffffu, keep);
+                __syncwarp();
+                while (mask) {
+                    const int src = __ffs(mask) - 1;
+                    mask &= mask - 1;
+                    const float4 r0 = tb[src], r1 = tb[32 + src];
+                    const float w = r0.x, d2 = r1.z;
+                    const int lo_pack = __float_as_int(r1.y);
+                    {   // distance basis
+                        const int lo = lo_pack & 255;
+                        const bool in0 = (unsigned)(lane - lo) < win_d, in1 = (unsigned)(lane + 32 - lo) < win_d;
+                        if (!wide_d) {
+                            const float b = r0.y + (in1 ? cd_hi : cd_lo);
+                            const float g = ex2_approx(-b * b) * w;
+                            if (in0) { sd[0] += g; if (BWD) qd[0] = fmaf(g, d2, qd[0]); }
+                            if (in1) { sd[1] += g; if (BWD) qd[1] = fmaf(g, d2, qd[1]); }
+                        } else {
+                            const float b0 = r0.y + cd_lo, b1 = r0.y + cd_hi;
+                            const float g0 = ex2_approx(-b0 * b0) * w, g1 = ex2_approx(-b1 * b1) * w;
+                            if (in0) { sd[0] += g0; if (BWD) qd[0] = fmaf(g0, d2, qd[0]); }
+                            if (in1) { sd[1] += g1; if (BWD) qd[1] = fmaf(g1, d2, qd[1]); }
+                        }
+                    }
+                    if (ANG) {
+                        const float xa[3] = {r0.z, r0.w, r1.x};
+#pragma unroll
+                        for (int x = 0; x < 3; x++) {
+                            const int lo = (lo_pack >> (8 * (x + 1))) & 255;
+                            const float b0 = xa[x] - ca_lo, b1 = xa[x] - ca_hi;
+                            const float g0 = ex2_approx(-b0 * b0) * w, g1 = ex2_approx(-b1 * b1) * w;
+                            if ((unsigned)(lane - lo) < win_a) { sa[x][0] += g0; if (BWD) qa[x][0] = fmaf(g0, d2, qa[x][0]); }
+                            if ((unsigned)(lane + 32 - lo) < win_a) { sa[x][1] += g1; if (BWD) qa[x][1] = fmaf(g1, d2, qa[x][1]); }
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+
+            if (!BWD) {
+                const float sum = warp_sum(sum_l);
+                if (lane == 0) A.z[e * H + h] = logf(sum) + d2min * a;
+                const float inv = 1.0f / sum;
+                const float kd = P.c_dist * inv, ka = P.c_ang * inv;
+                srow[lane] = sd[0] * kd; srow[32 + lane] = sd[1] * kd;
+#pragma unroll
+                for (int x = 0; x < 3; x++) {
+                    srow[64 + 64 * x + lane] = sa[x][0] * ka;
+                    srow[96 + 64 * x + lane] = sa[x][1] * ka;
+                }
+            } else {
+                const float px = warp_sum(px_l);
+                // G = W^T gv restricted to this lane's eight basis indices
+                float gvr[kHd];
+                const float4* gv4 = reinterpret_cast<const float4*>(A.gv + (e * H + h) * kHd);
+#pragma unroll
+                for (int o4 = 0; o4 < kHd / 4; o4++) {
+                    const float4 v = __ldg(gv4 + o4);
+                    gvr[4 * o4] = v.x; gvr[4 * o4 + 1] = v.y; gvr[4 * o4 + 2] = v.z; gvr[4 * o4 + 3] = v.w;
+                }
+                float G[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) G[j] = 0.f;
+#pragma unroll
+                for (int o = 0; o < kHd; o++)
+#pragma unroll
+                    for (int j = 0; j < 8; j++) G[j] = fmaf(W_s[o * kFpK + j * 32 + lane], gvr[o], G[j]);
+                float Ad = fmaf(G[0], qd[0], G[1] * qd[1]), Bd = fmaf(G[0], sd[0], G[1] * sd[1]);
+                float Aa = 0.f, Ba = 0.f;
+#pragma unroll
+                for (int x = 0; x < 3; x++) {
+                    Aa = fmaf(G[2 + 2 * x], qa[x][0], fmaf(G[3 + 2 * x], qa[x][1], Aa));
+                    Ba = fmaf(G[2 + 2 * x], sa[x][0], fmaf(G[3 + 2 * x], sa[x][1], Ba));
+                }
+                Ad = warp_sum(Ad); Bd = warp_sum(Bd); Aa = warp_sum(Aa); Ba = warp_sum(Ba);
+                if (lane == 0) {
+                    // the reference scales the whole length-kernel result, gz term included, by the
+                    // distance coefficient (models/cuda_funcs/real_space_framed_proj.py:183)
+                    const float g_len = fmaf(px, __ldg(A.gz + e * H + h), Ad - px * Bd);
+                    const float g_ang = Aa - px * Ba;
+                    A.ga_e[e * H + h] = P.c_dist * g_len + P.c_ang * g_ang;
+                }
+                // stage the averaged bases for the weight-gradient outer product; the reference
+                // leaves the distance weights' gradient unscaled and scales the angle ones
+                srow[lane] = sd[0]; srow[32 + lane] = sd[1];
+#pragma unroll
+                for (int x = 0; x < 3; x++) {
+                    srow[64 + 64 * x + lane] = sa[x][0] * P.c_ang;
+                    srow[96 + 64 * x + lane] = sa[x][1] * P.c_ang;
+                }
+                if (lane < kHd) side[slot * kHd + lane] = __ldg(A.gv + (e * H + h) * kHd + lane);
+            }
+        }
+        __syncthreads();
+
+        if (!BWD) {
+            if (A.values != nullptr) {
+                // lane = staged pair, warp = output pair (2*warp, 2*warp+1)
+                const float4* st = reinterpret_cast<const float4*>(stage + lane * kFpStageStride);
+                const float4* w0 = reinterpret_cast<const float4*>(W_s + (2 * warp) * kFpK);
+                const float4* w1 = w0 + kFpK / 4;
+                float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll 8
+                for (int k4 = 0; k4 < kFpK / 4; k4++) {
+                    const float4 s = st[k4], u = w0[k4], v = w1[k4];
+                    acc0 = fmaf(s.x, u.x, fmaf(s.y, u.y, fmaf(s.z, u.z, fmaf(s.w, u.w, acc0))));
+                    acc1 = fmaf(s.x, v.x, fmaf(s.y, v.y, fmaf(s.z, v.z, fmaf(s.w, v.w, acc1))));
+                }
+                side[(2 * warp) * 33 + lane] = acc0;
+                side[(2 * warp + 1) * 33 + lane] = acc1;
+                __syncthreads();
+                const int p = threadIdx.x >> 3, q = threadIdx.x & 7;
+                const int64_t e = chunk * kFpSlots + p;
+                if (e < A.E) {
+                    float2 v = make_float2(side[(2 * q) * 33 + p], side[(2 * q + 1) * 33 + p]);
+                    *reinterpret_cast<float2*>(A.values + (e * H + h) * kHd + 2 * q) = v;
+                }
+            }
+        } else {
+            for (int slot = 0; slot < kFpSlots; slot++) {
+                const float2 g = *reinterpret_cast<const float2*>(side + slot * kHd + 2 * warp);
+                const float* srow = stage + slot * kFpStageStride + lane;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const float s = srow[j * 32];
+                    gacc[0][j] = fmaf(s, g.x, gacc[0][j]);
+                    gacc[1][j] = fmaf(s, g.y, gacc[1][j]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    if (BWD) {
+        float* dst = A.gW_part + (((size_t)blockIdx.x * H + h) * kHd + 2 * warp) * kFpK + lane;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            dst[j * 32] = gacc[0][j];
+            dst[kFpK + j * 32] = gacc[1][j];
+        }
+    }
+}
+
+// ga (N,H): ordered sum of the per-pair gradients of each atom's pairs
+__global__ void reduce_ga_kernel(const float* __restrict__ ga_e, const int64_t* __restrict__ e_start,
+                                 int64_t N, int H, float* __restrict__ ga)
+{
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (tid >= N * H) return;
+    const int64_t i = tid / H;
+    const int h = (int)(tid - i * H);
+    float s = 0.f;
+    for (int64_t e = e_start[i]; e < e_start[i + 1]; e++) s += ga_e[e * H + h];
+    ga[tid] = s;
+}
+
+// weight gradients: ordered sum over the per-block partials, split into the four tensors
+__global__ void reduce_gw_kernel(const float* __restrict__ part, int nPart, int H, float* gWd, float* gW1,
+                                 float* gW2, float* gW3)
+{
+    const int tid = blockIdx.x * blockDim.x + threadIdx.x;   // (h, o, k)
+    if (tid >= H * kHd * kFpK) return;
+    float s = 0.f;
+    for (int x = 0; x < nPart; x++) s += part[(size_t)x * H * kHd * kFpK + tid];
+    const int k = tid & (kFpK - 1), ho = tid >> 8, b = k >> 6, dim = k & 63;
+    float* dst = b == 0 ? gWd : (b == 1 ? gW1 : (b == 2 ? gW2 : gW3));
+    if (dst != nullptr) dst[ho * 64 + dim] = s;
+}
+
+// Resident blocks along x: the kernel is persistent (each block strides over the chunks), so the
+// grid is one wave of kFpBlocksPerSm blocks per SM, split evenly between the heads.
+constexpr int kFpBlocksPerSm = 2;
+
+static int grid_x_for(int64_t E, int H)
+{
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int64_t chunks = (E + kFpSlots - 1) / kFpSlots;
+    int64_t want = ((int64_t)sms * kFpBlocksPerSm) / H;
+    if (want < 1) want = 1;
+    if (chunks < want) want = chunks < 1 ? 1 : chunks;
+    return (int)want;
+}
+
+int64_t framed_proj_bwd_workspace_bytes(int64_t N, int64_t E, int H)
+{
+    (void)N;
+    const int gx = grid_x_for(E, H);
+    size_t ga_e = ((size_t)E * H * sizeof(float) + 255) / 256 * 256;
+    return (int64_t)(ga_e + (size_t)gx * H * kHd * kFpK * sizeof(float));
+}
+
+template <bool BWD, bool ANG>
+static int launch_fp(const FpArgs& A, const Params& P, int gx, cudaStream_t st)
+{
+    auto kern = framed_proj_kernel<BWD, ANG>;
+    static bool attr_done[64] = {false};   // per instantiation and device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_done[dev & 63]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFpSmemBytes) != cudaSuccess)
+            return CFB200_E_CUDA;
+        attr_done[dev & 63] = true;
+    }
+    kern<<<dim3(gx, P.H), kFpThreads, kFpSmemBytes, st>>>(A, P);
+    return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
+}
+
+int framed_proj_fwd(const FpArgs& A, const Params& P, cudaStream_t st)
+{
+    if (A.E == 0) return CFB200_OK;
+    const int gx = grid_x_for(A.E, P.H);
+    return A.W[1] != nullptr ? launch_fp<false, true>(A, P, gx, st) : launch_fp<false, false>(A, P, gx, st);
+}
+
+int framed_proj_bwd(FpArgs A, const Params& P, const int64_t* e_start, float* ga, float* gW[4], void* ws,
+                    int64_t ws_bytes, cudaStream_t st)
+{
+    if (ws_bytes < framed_proj_bwd_workspace_bytes(A.N, A.E, P.H) || ws == nullptr) return CFB200_E_WORKSPACE;
+    const int gx = grid_x_for(A.E, P.H);
+    size_t ga_e_bytes = ((size_t)A.E * P.H * sizeof(float) + 255) / 256 * 256;
+    A.ga_e = reinterpret_cast<float*>(ws);
+    A.gW_part = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + ga_e_bytes);
+    int nPart = gx;
+    if (A.E > 0) {
+        int rc = A.W[1] != nullptr ? launch_fp<true, true>(A, P, gx, st) : launch_fp<true, false>(A, P, gx, st);
+        if (rc != CFB200_OK) return rc;
+    } else {
+        nPart = 0;
+    }
+    if (A.N > 0) {
+        const int64_t nt = A.N * P.H;
+        reduce_ga_kernel<<<(unsigned)((nt + 255) / 256), 256, 0, st>>>(A.ga_e, e_start, A.N, P.H, ga);
+    }
+    const int nw = P.H * kHd * kFpK;
+    reduce_gw_kernel<<<(nw + 255) / 256, 256, 0, st>>>(A.gW_part, nPart, P.H, gW[0], gW[1], gW[2], gW[3]);
+    return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
+}
+
+}  // namespace cfb

@@ -1,0 +1,20 @@
+"""Drop-in autograd Functions with the names and signatures of the reference's
+``models/cuda_funcs`` package (models/cuda_funcs/__init__.py:12-47), backed by libcfb200.so."""
+from .kernel_manager import KernelManager, compile_kernels, current_config
+from .framed_proj import RealEncodingWithFramedProjFuncCUDA
+from .max_frame import (ComputeFrame1MaximumMethodCUDA, ComputeFrame2MaximumMethodCUDA,
+                        max_frame_with_selection, max_frames_fused)
+from .fused_dpa import FusedDotProductAttentionCUDA, attention_probabilities
+from .irregular_mean import IrregularMeanCUDA
+from .common import csr_offsets, register_csr
+
+# the reference exports this flag (models/cuda_funcs/__init__.py:2-9); here it says whether the
+# CUDA library can be used at all
+CUPY_AVAILABLE = True
+
+__all__ = [
+    "KernelManager", "compile_kernels", "current_config", "FusedDotProductAttentionCUDA",
+    "ComputeFrame1MaximumMethodCUDA", "ComputeFrame2MaximumMethodCUDA", "RealEncodingWithFramedProjFuncCUDA",
+    "IrregularMeanCUDA", "max_frame_with_selection", "max_frames_fused", "attention_probabilities",
+    "csr_offsets", "register_csr", "CUPY_AVAILABLE",
+]

@@ -1,0 +1,91 @@
+"""autograd Functions for the dynamic "max" frames (all outputs are non-differentiable)."""
+import numpy as np
+import torch
+
+from .. import _lib
+from .common import csr_offsets, f32c
+
+
+def _draw_seed():
+    """One draw from numpy's global generator per Function call, as the reference does
+    (models/cuda_funcs/calc_maximum_frame.py:43,121), so that numpy's state advances alike."""
+    return int(np.random.randint(np.iinfo(np.int64).min, np.iinfo(np.int64).max, dtype=np.int64)) & (2 ** 64 - 1)
+
+
+def _frame_call(axis, q, k, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_n, cutoff_radius, frame1,
+                want_selection=False):
+    N, H = a_ik.shape
+    E = edge_ij_e.shape[1]
+    dev = a_ik.device
+    a, qq, kk = f32c(a_ik), f32c(q), f32c(k)
+    pos, tv, rv = f32c(rpos_ij_e), f32c(tvecs_n), f32c(rvlen_n)
+    batch, edges = batch_i.contiguous(), edge_ij_e.contiguous()
+    e_start = csr_offsets(edges, N)
+    cutoff = 0.0 if cutoff_radius is None or rvlen_n is None else float(cutoff_radius)
+    seed = _draw_seed()
+    out = torch.empty((N, H, 3), device=dev, dtype=torch.float32)
+    sel_e = torch.empty((N, H), device=dev, dtype=torch.int64) if want_selection else None
+    sel_i = torch.empty((N, H), device=dev, dtype=torch.int32) if want_selection else None
+    p, ip = _lib.ptr, _lib.iptr
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().cfb200_max_frame(
+            axis, p(qq), p(kk), p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), ip(e_start), N, E, cutoff, seed,
+            p(f32c(frame1)), p(out), ip(sel_e), _lib.ptr(sel_i, torch.int32), _lib.stream(dev)), "cfb200_max_frame")
+    return (out, sel_e, sel_i) if want_selection else out
+
+
+class ComputeFrame1MaximumMethodCUDA(torch.autograd.Function):
+    """Drop-in for models/cuda_funcs/calc_maximum_frame.py:24-91: first axis (N,H,3), the unit
+    vector to the nearest periodic image of the pair that maximises q.k + a d^2_min."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, a_ik, rpos_ij_e, dist2_min_e, tvecs_n, batch_i, edge_ij_e, K, dist_max, wscale,
+                rvlen_n=None, cutoff_radius=None):
+        return _frame_call(1, q, k, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_n, cutoff_radius, None)
+
+    @staticmethod
+    def backward(ctx, gframevec):
+        return (None,) * 14
+
+
+class ComputeFrame2MaximumMethodCUDA(torch.autograd.Function):
+    """Drop-in for models/cuda_funcs/calc_maximum_frame.py:95-170: second axis (N,H,3), not yet
+    orthogonalised against the first."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, a_ik, rpos_ij_e, dist2_min_e, tvecs_n, batch_i, edge_ij_e, K, dist_max, wscale,
+                frame1, rvlen_n=None, cutoff_radius=None):
+        return _frame_call(2, q, k, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_n, cutoff_radius, frame1)
+
+    @staticmethod
+    def backward(ctx, gframevec):
+        return (None,) * 15
+
+
+def max_frame_with_selection(axis, q, k, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_n, cutoff_radius,
+                             frame1=None):
+    """Frame axis plus the integer selection behind it: (frame, pair index (N,H) int64,
+    linear translation index (N,H) int32)."""
+    return _frame_call(axis, q, k, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_n, cutoff_radius, frame1,
+                       want_selection=True)
+
+
+def max_frames_fused(q, k, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_n, cutoff_radius):
+    """Both axes and the Gram-Schmidt completion in one launch; returns frame1, frame2, frame3.
+    Draws two seeds, like the two reference Functions it stands for."""
+    N, H = a_ik.shape
+    E = edge_ij_e.shape[1]
+    dev = a_ik.device
+    a, qq, kk = f32c(a_ik), f32c(q), f32c(k)
+    pos, tv, rv = f32c(rpos_ij_e), f32c(tvecs_n), f32c(rvlen_n)
+    batch, edges = batch_i.contiguous(), edge_ij_e.contiguous()
+    e_start = csr_offsets(edges, N)
+    cutoff = 0.0 if cutoff_radius is None or rvlen_n is None else float(cutoff_radius)
+    s1, s2 = _draw_seed(), _draw_seed()
+    f = torch.empty((3, N, H, 3), device=dev, dtype=torch.float32)
+    p, ip = _lib.ptr, _lib.iptr
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().cfb200_max_frames(
+            p(qq), p(kk), p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), ip(e_start), N, E, cutoff, s1, s2,
+            p(f[0]), p(f[1]), p(f[2]), _lib.stream(dev)), "cfb200_max_frames")
+    return f[0], f[1], f[2]

@@ -1,0 +1,159 @@
+/*
+ * libcfb200 -- C ABI of the B200 (sm_100a) implementation of CrystalFramer's periodic
+ * lattice-sum attention path.
+ *
+ * Conventions (they replace those of the reference's CuPy RawKernel layer,
+ * models/cuda_funcs/kernel_manager.py:14-167 and the _to_cupy helpers of each Function):
+ *   - every pointer is a device pointer on the current device unless it says "host";
+ *     all reals are contiguous float32, all indices contiguous int64 (as the reference);
+ *   - the library allocates nothing and never synchronises: work is enqueued on `stream`
+ *     (a cudaStream_t passed as void*), scratch memory is passed in by the caller;
+ *   - a call returns 0 on success or a negative CFB200_E_* code; kernels never trap -- a
+ *     condition found on the device (non-negative Gaussian coefficient, clamped lattice
+ *     range) sets a bit in a status word read with cfb200_status();
+ *   - hyper-parameters the reference bakes into its kernel text (compile_kernels,
+ *     kernel_manager.py:116-167) are bound once per process with cfb200_configure().
+ *
+ * Each entry point names the reference interface it replaces by file:line (paths relative
+ * to the reference project root).
+ */
+#ifndef CFB200_H
+#define CFB200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CFB200_OK 0
+#define CFB200_E_NULL (-1)         /* a required pointer is NULL                               */
+#define CFB200_E_SHAPE (-2)        /* negative or inconsistent extent                          */
+#define CFB200_E_UNSUPPORTED (-3)  /* no kernel instance for the configured hyper-parameters   */
+#define CFB200_E_NOT_CONFIGURED (-4)
+#define CFB200_E_WORKSPACE (-5)    /* scratch buffer missing or too small                      */
+#define CFB200_E_CUDA (-6)         /* launch failed; see cudaGetLastError                      */
+
+/* bits of the device status word */
+#define CFB200_ST_BAD_COEF 1       /* a Gaussian coefficient a_ik was not negative             */
+#define CFB200_ST_RANGE_CLAMPED 2  /* a lattice range exceeded CFB200_MAX_RANGE and was clamped */
+#define CFB200_ST_SIZE_MISMATCH 4 /* sizes do not sum to the N and E passed to cfb200_edge_index */
+#define CFB200_MAX_RANGE 48
+
+typedef struct cfb200_config {
+    int32_t num_heads;        /* HEAD_NUM / THREAD_NUM                                  */
+    int32_t head_dim;         /* K_HEAD_DIM == V_HEAD_DIM                               */
+    int32_t dist_dim;         /* VPE_DIM: distance Gaussians                            */
+    int32_t angle_dim;        /* ANGLE_ENC_DIM: angle Gaussians per frame axis, 0 = off */
+    int32_t lattice_range;    /* LATTICE_RANGE                                          */
+    int32_t minimum_range;    /* MINIMUM_RANGE (0 = off)                                */
+    int32_t cos_abs;          /* COS_ABS                                                */
+    int32_t cut_sigma;        /* CUT_SIGMA (the reference fixes 4)                      */
+    float dist_wscale;        /* value_pe_dist_wscale  -> LENGTH_RANGE                  */
+    float angle_wscale;       /* value_pe_angle_wscale -> ANGLE_RANGE and angle sigma   */
+    float dist_coef;          /* value_pe_dist_coef  (length_rbf_mul)                   */
+    float angle_coef;         /* value_pe_angle_coef (angle_rbf_mul)                    */
+    float symm_break_noise;   /* SYMM_BREAK_NOISE                                       */
+} cfb200_config;
+
+/* Replaces compile_kernels(...) (models/cuda_funcs/kernel_manager.py:116-167): binds the
+ * hyper-parameters for all later calls of this process.  Returns CFB200_E_UNSUPPORTED when no
+ * kernel instance exists for them. */
+int cfb200_configure(const cfb200_config* cfg /* host */);
+int cfb200_get_config(cfb200_config* out /* host */);
+int cfb200_version(void);
+const char* cfb200_error_string(int code);
+
+/* Reads and clears the device status word (synchronises `stream`). */
+int cfb200_status(int32_t* status_out /* host */, void* stream);
+
+/* Number of resident thread blocks the lattice-sum kernels launch along x; the size of the
+ * backward scratch buffer depends on it. */
+int64_t cfb200_framed_proj_bwd_workspace_bytes(int64_t N, int64_t E);
+
+/* Replaces get_edge_index (models/indexed_latticeformer_encoder.py:15-32), the CSR offsets
+ * each Function rebuilds (models/cuda_funcs/fused_dpa.py:24-26) and the per-atom crystal
+ * index.  sizes (B); edges (2,E) row 0 = query atom, row 1 = key atom; e_start (N+1);
+ * batch (N); crystal_start (B+1) atom offsets.  N and E must equal sum(sizes), sum(sizes^2). */
+int cfb200_edge_index(const int64_t* sizes, int64_t B, int64_t N, int64_t E, int64_t* edges,
+                      int64_t* e_start, int64_t* batch, int64_t* crystal_start, void* stream);
+
+/* CSR offsets from a pair list sorted by query atom (models/cuda_funcs/fused_dpa.py:24-26). */
+int cfb200_csr_offsets(const int64_t* edge_i, int64_t E, int64_t N, int64_t* e_start, void* stream);
+
+/* Replaces ComputeFrame1MaximumMethodCUDA.forward / ComputeFrame2MaximumMethodCUDA.forward
+ * (models/cuda_funcs/calc_maximum_frame.py:24-170) with kernels
+ * compute_maximum_frame_each_edge.cu / compute_second_frame_each_edge.cu and the per-atom
+ * argmax.  axis = 1: nearest-image axis; axis = 2: second axis given frame1 (N,H,3).
+ * q_scaled is q / sqrt(head_dim).  Outputs: frame (N,H,3); optional sel_edge (N,H) int64 and
+ * sel_image (N,H) int32 (linear translation index) name the selected pair and image. */
+int cfb200_max_frame(int axis, const float* q_scaled, const float* k, const float* a_ik,
+                     const float* pos_ij, const float* tvecs, const float* rvlen,
+                     const int64_t* batch, const int64_t* edges, const int64_t* e_start,
+                     int64_t N, int64_t E, float cutoff_radius, uint64_t seed,
+                     const float* frame1, float* frame, int64_t* sel_edge, int32_t* sel_image,
+                     void* stream);
+
+/* Both axes plus the Gram-Schmidt completion
+ * (models/indexed_lattice_multi_head_attention_cuda.py:435-493) in one launch. */
+int cfb200_max_frames(const float* q_scaled, const float* k, const float* a_ik,
+                      const float* pos_ij, const float* tvecs, const float* rvlen,
+                      const int64_t* batch, const int64_t* edges, const int64_t* e_start,
+                      int64_t N, int64_t E, float cutoff_radius, uint64_t seed1, uint64_t seed2,
+                      float* frame1, float* frame2, float* frame3, void* stream);
+
+/* Replaces RealEncodingWithFramedProjFuncCUDA.forward
+ * (models/cuda_funcs/real_space_framed_proj.py:21-120; kernels
+ * real_enc_frame_proj_fwd_length.cu, real_enc_frame_proj_fwd_angle.cu).
+ * W_dist (H,head_dim,dist_dim); W_ang1..3 (H,head_dim,angle_dim) and frame1..3 (N,H,3) may all be
+ * NULL (no angle encoding).  Outputs z (E,H) and values (E,H,head_dim) (values may be NULL). */
+int cfb200_framed_proj_fwd(const float* a_ik, const float* pos_ij, const float* tvecs,
+                           const float* rvlen, const int64_t* batch, const int64_t* edges,
+                           int64_t N, int64_t E, float dist_max, float cutoff_radius,
+                           const float* W_dist, const float* W_ang1, const float* W_ang2,
+                           const float* W_ang3, const float* frame1, const float* frame2,
+                           const float* frame3, float* z, float* values, void* stream);
+
+/* Replaces RealEncodingWithFramedProjFuncCUDA.backward
+ * (models/cuda_funcs/real_space_framed_proj.py:123-221; kernels
+ * real_enc_frame_proj_bwd_length.cu, real_enc_frame_proj_bwd_angle.cu).
+ * Outputs ga (N,H) and the weight gradients already summed over atoms, gW_dist
+ * (H,head_dim,dist_dim), gW_ang1..3 (H,head_dim,angle_dim).  workspace: at least
+ * cfb200_framed_proj_bwd_workspace_bytes(N,E) bytes, 256-byte aligned; need not be cleared. */
+int cfb200_framed_proj_bwd(const float* a_ik, const float* pos_ij, const float* tvecs,
+                           const float* rvlen, const int64_t* batch, const int64_t* edges,
+                           const int64_t* e_start, int64_t N, int64_t E, float dist_max,
+                           float cutoff_radius, const float* W_dist, const float* W_ang1,
+                           const float* W_ang2, const float* W_ang3, const float* frame1,
+                           const float* frame2, const float* frame3, const float* z,
+                           const float* gz, const float* gvalues, float* ga, float* gW_dist,
+                           float* gW_ang1, float* gW_ang2, float* gW_ang3, void* workspace,
+                           int64_t workspace_bytes, void* stream);
+
+/* Replaces FusedDotProductAttentionCUDA.forward (models/cuda_funcs/fused_dpa.py:17-64;
+ * kernel fused_dpa_fwd.cu).  q_scaled, k, v (N,H,head_dim); z (E,H) or NULL; values
+ * (E,H,head_dim) or NULL.  Outputs out (N,H,head_dim), lse (N,H) = log-sum-exp of the logits
+ * (kept for the backward pass), prob (E,H) or NULL. */
+int cfb200_dpa_fwd(const float* q_scaled, const float* k, const float* v, const float* z,
+                   const float* values, const int64_t* edges, const int64_t* e_start, int64_t N,
+                   int64_t E, float* out, float* lse, float* prob, void* stream);
+
+/* Replaces FusedDotProductAttentionCUDA.backward (models/cuda_funcs/fused_dpa.py:66-168;
+ * kernels irregular_transpose.cu, fused_dpa_bwd.cu, fused_dpa_bwd_q.cu).  Outputs gq, gk, gv
+ * (N,H,head_dim), gz (E,H), gvalues (E,H,head_dim) (NULL when values is NULL). */
+int cfb200_dpa_bwd(const float* q_scaled, const float* k, const float* v, const float* z,
+                   const float* values, const int64_t* edges, const int64_t* e_start, int64_t N,
+                   int64_t E, const float* out, const float* lse, const float* gout, float* gq,
+                   float* gk, float* gv, float* gz, float* gvalues, void* stream);
+
+/* Replaces IrregularMeanCUDA (models/cuda_funcs/irregular_mean.py:19-69; kernel
+ * irregular_mean_fwd.cu).  x (N,D); start (B+1) atom offsets; out (B,D). */
+int cfb200_segment_mean_fwd(const float* x, const int64_t* start, int64_t B, int64_t D, float* out,
+                            void* stream);
+int cfb200_segment_mean_bwd(const float* gout, const int64_t* start, int64_t B, int64_t D,
+                            float* gx, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CFB200_H */

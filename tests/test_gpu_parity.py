@@ -1,0 +1,205 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle on identical seeded inputs.
+
+Tolerances: integer outputs (pair list, CSR offsets, selected pair / image) bit-exact; float
+outputs and gradients within 1e-4 relative + 1e-5 absolute, the bound the specification of
+this path states.
+"""
+import numpy as np
+import pytest
+import torch
+
+from conftest import make_problem
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 1e-4, 1e-5
+
+
+def _cuda():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return torch.device("cuda:0")
+
+
+def _close(name, got, want, rtol=RTOL, atol=ATOL, frac_ok=0.0):
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    assert got.shape == want.shape, (name, got.shape, want.shape)
+    assert np.isfinite(got).all(), name
+    err = np.abs(got - want)
+    bad = err > atol + rtol * np.abs(want)
+    assert bad.mean() <= frac_ok, f"{name}: {bad.sum()} of {bad.size} outside tolerance, max abs err {err.max():.3e}"
+
+
+def _close_reduction(name, got, want32, want64):
+    """Coefficient and weight gradients are sums over an atom's / the batch's pairs of terms that
+    largely cancel; float32 accumulation noise alone
+    (any summation order) reaches the elementwise bound on entries with heavy cancellation --
+    the float32 oracle itself is that far from the float64 oracle.  So the absolute term scales
+    with the largest entry, and the error against the float64 value must not exceed three times
+    the float32 oracle's own error."""
+    got = np.asarray(got, dtype=np.float64)
+    scale = max(1.0, float(np.abs(want64).max()))
+    _close(name, got, want32, RTOL, ATOL * scale)
+    ours, theirs = np.abs(got - want64).max(), np.abs(want32.astype(np.float64) - want64).max()
+    assert ours <= 3.0 * theirs + ATOL, f"{name}: error vs float64 {ours:.3e}, float32 oracle's {theirs:.3e}"
+
+
+def _configure(noise=0.0, angle_dim=64, c_dist=1.0, c_ang=1.0):
+    from crystalframer_b200 import cuda_funcs as F
+    F.compile_kernels(2, 8, 16, 64, angle_dim, 16, True, 0, 1.0, 4.0, c_dist, c_ang, noise)
+    return F
+
+
+def _t(x, dev):
+    return torch.from_numpy(np.ascontiguousarray(x)).to(dev)
+
+
+def _geometry(P, dev):
+    g, b = P["geo"], P["batch"]
+    return dict(pos_ij=_t(g["pos_ij"], dev), tvecs=_t(b.trans_vec, dev), batch=_t(g["batch"], dev),
+                edges=_t(g["edges"], dev), rvlen=_t(g["rvlen"], dev), sizes=_t(b.sizes, dev))
+
+
+@pytest.mark.parametrize("workload,nc", [("cfg1", None), ("cfg2", 24)])
+def test_pair_list_bit_exact(workload, nc):
+    dev = _cuda()
+    from crystalframer_b200.encoder import build_pair_list
+    from crystalframer_b200.cuda_funcs import csr_offsets
+    P = make_problem(workload, num_crystals=nc)
+    g = _geometry(P, dev)
+    edges, e_start, batch, cstart = build_pair_list(g["sizes"])
+    assert torch.equal(edges.cpu(), torch.from_numpy(P["geo"]["edges"]))
+    assert torch.equal(e_start.cpu(), torch.from_numpy(P["geo"]["e_start"]))
+    assert torch.equal(batch.cpu(), torch.from_numpy(P["geo"]["batch"]))
+    assert cstart[-1].item() == P["batch"].num_atoms
+    # CSR offsets rebuilt from a foreign pair list
+    e2 = csr_offsets(g["edges"], P["batch"].num_atoms)
+    assert torch.equal(e2.cpu(), torch.from_numpy(P["geo"]["e_start"]))
+
+
+@pytest.mark.parametrize("workload,nc", [("cfg1", None), ("cfg2", 24)])
+def test_max_frames(workload, nc):
+    dev = _cuda()
+    from oracle import oracle as O
+    F = _configure()
+    P = make_problem(workload, num_crystals=nc)
+    g = _geometry(P, dev)
+    qs = P["q"] / 4.0
+    want = O.max_frames(P["cfg"], qs, P["k"], P["a"], P["geo"]["pos_ij"], P["batch"].trans_vec, P["geo"]["rvlen"],
+                        P["geo"]["batch"], P["geo"]["edges"], P["geo"]["e_start"])
+    q, k, a = _t(qs, dev), _t(P["k"], dev), _t(P["a"], dev)
+    f1, se1, si1 = F.max_frame_with_selection(1, q, k, a, g["pos_ij"], g["tvecs"], g["batch"], g["edges"], g["rvlen"], -3.5)
+    assert np.array_equal(se1.cpu().numpy(), want["sel_edge1"])
+    assert np.array_equal(si1.cpu().numpy(), want["sel_image1"])
+    assert np.array_equal(f1.cpu().numpy(), want["frame1"])          # bit-exact: same IEEE operations
+    f2, se2, si2 = F.max_frame_with_selection(2, q, k, a, g["pos_ij"], g["tvecs"], g["batch"], g["edges"], g["rvlen"], -3.5, f1)
+    same = (se2.cpu().numpy() == want["sel_edge2"]) & (si2.cpu().numpy() == want["sel_image2"])
+    # the second axis' score contains logf, whose last bit differs between CUDA and glibc; a
+    # differing selection is only acceptable as a near-tie and must be very rare
+    assert same.mean() >= 0.999, f"second-axis selection differs on {(~same).sum()} of {same.size}"
+    _close("frame2_max", f2.cpu().numpy()[same], want["frame2_max"][same], 1e-6, 1e-6)
+    # fused launch: all three completed axes
+    g1, g2, g3 = F.max_frames_fused(q, k, a, g["pos_ij"], g["tvecs"], g["batch"], g["edges"], g["rvlen"], -3.5)
+    assert np.array_equal(g1.cpu().numpy(), want["frame1"])
+    _close("frame2", g2.cpu().numpy()[same], want["frame2"][same], 1e-5, 1e-6)
+    _close("frame3", g3.cpu().numpy()[same], want["frame3"][same], 1e-5, 1e-6)
+
+
+def _frames(P):
+    from oracle import oracle as O
+    fr = O.max_frames(P["cfg"], P["q"] / 4.0, P["k"], P["a"], P["geo"]["pos_ij"], P["batch"].trans_vec,
+                      P["geo"]["rvlen"], P["geo"]["batch"], P["geo"]["edges"], P["geo"]["e_start"])
+    return np.stack([fr["frame1"], fr["frame2"], fr["frame3"]])
+
+
+@pytest.mark.parametrize("workload,nc,angles", [("cfg1", None, True), ("cfg2", 24, True), ("cfg1", None, False)])
+def test_framed_proj_forward_backward(workload, nc, angles):
+    dev = _cuda()
+    from oracle import oracle as O
+    F = _configure(angle_dim=64 if angles else 0)
+    P = make_problem(workload, num_crystals=nc)
+    g = _geometry(P, dev)
+    frames = _frames(P) if angles else None
+    W_a = P["W_a"] if angles else None
+    geo, b = P["geo"], P["batch"]
+    z_w, v_w = O.framed_proj_fwd(P["cfg"], P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"],
+                                 P["W_d"], W_a, frames)
+    a = _t(P["a"], dev).requires_grad_(True)
+    Wd = _t(P["W_d"][None], dev).requires_grad_(True)
+    if angles:
+        Ws = [_t(P["W_a"][x][None], dev).requires_grad_(True) for x in range(3)]
+        fs = [_t(frames[x], dev) for x in range(3)]
+    else:
+        Ws, fs = [None] * 3, [None] * 3
+    z, v = F.RealEncodingWithFramedProjFuncCUDA.apply(
+        a, g["pos_ij"], None, g["tvecs"], g["batch"], g["edges"], 64, 14.0, 1.0, Wd, *Ws, *fs, 64, 4.0, 0, 1.0, 1.0,
+        g["rvlen"], -3.5)
+    _close("z", z.detach().cpu().numpy(), z_w)
+    _close("values", v.detach().cpu().numpy(), v_w)
+    rng = np.random.default_rng(7)
+    gz = rng.normal(size=z_w.shape).astype(np.float32)
+    gv = rng.normal(size=v_w.shape).astype(np.float32)
+    ga_w, gWd_w, gWa_w = O.framed_proj_bwd(P["cfg"], P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"],
+                                           geo["edges"], geo["e_start"], P["W_d"], W_a, frames, z_w, gz, gv)
+    z64, v64 = O.framed_proj_fwd(P["cfg"], P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"],
+                                 P["W_d"], W_a, frames, dtype=np.float64)
+    ga_64, gWd_64, gWa_64 = O.framed_proj_bwd(P["cfg"], P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"],
+                                          geo["edges"], geo["e_start"], P["W_d"], W_a, frames, z64, gz, gv,
+                                          dtype=np.float64)
+    (z * _t(gz, dev)).sum().add((v * _t(gv, dev)).sum()).backward()
+    _close_reduction("ga", a.grad.cpu().numpy(), ga_w, ga_64)
+    _close_reduction("gW_dist", Wd.grad.cpu().numpy()[0], gWd_w, gWd_64)
+    if angles:
+        for x in range(3):
+            _close_reduction(f"gW_ang{x + 1}", Ws[x].grad.cpu().numpy()[0], gWa_w[x], gWa_64[x])
+    from crystalframer_b200 import _lib
+    assert _lib.read_status() == 0
+
+
+@pytest.mark.parametrize("workload,nc", [("cfg1", None), ("cfg2", 24)])
+def test_attention_forward_backward(workload, nc):
+    dev = _cuda()
+    from oracle import oracle as O
+    F = _configure()
+    P = make_problem(workload, num_crystals=nc)
+    g = _geometry(P, dev)
+    geo = P["geo"]
+    rng = np.random.default_rng(11)
+    E = geo["edges"].shape[1]
+    zb = rng.normal(size=(E, 8)).astype(np.float32)
+    vb = rng.normal(size=(E, 8, 16)).astype(np.float32) * 0.1
+    qs = P["q"] / 4.0
+    out_w, prob_w = O.dpa_fwd(P["cfg"], qs, P["k"], P["v"], zb, vb, geo["edges"], geo["e_start"])
+    go = rng.normal(size=out_w.shape).astype(np.float32)
+    want = O.dpa_bwd(P["cfg"], qs, P["k"], P["v"], vb, geo["edges"], geo["e_start"], prob_w, out_w, go)
+    T = [_t(x, dev).requires_grad_(True) for x in (qs, P["k"], P["v"], zb, vb)]
+    out = F.FusedDotProductAttentionCUDA.apply(*T, g["batch"], g["edges"])
+    _close("out", out.detach().cpu().numpy(), out_w)
+    out.backward(_t(go, dev))
+    for name, t, w in zip(["gq", "gk", "gv", "gz", "gvalues"], T, want):
+        _close(name, t.grad.cpu().numpy(), w)
+    _, prob, _ = F.attention_probabilities(*[t.detach() for t in T], g["edges"])
+    _close("prob", prob.cpu().numpy(), prob_w)
+    # without biases
+    out2_w, _ = O.dpa_fwd(P["cfg"], qs, P["k"], P["v"], None, None, geo["edges"], geo["e_start"])
+    out2 = F.FusedDotProductAttentionCUDA.apply(T[0].detach(), T[1].detach(), T[2].detach(), None, None, g["batch"], g["edges"])
+    _close("out(no bias)", out2.cpu().numpy(), out2_w)
+
+
+def test_mean_pool():
+    dev = _cuda()
+    from oracle import oracle as O
+    from crystalframer_b200.cuda_funcs import IrregularMeanCUDA
+    P = make_problem("cfg2", num_crystals=40)
+    N = P["batch"].num_atoms
+    x = np.random.default_rng(3).normal(size=(N, 128)).astype(np.float32)
+    xt = _t(x, dev).requires_grad_(True)
+    g = _geometry(P, dev)
+    out = IrregularMeanCUDA.apply(xt, g["batch"], g["sizes"])
+    _close("mean", out.detach().cpu().numpy(), O.mean_fwd(x, P["batch"].sizes))
+    go = np.random.default_rng(4).normal(size=(len(P["batch"].sizes), 128)).astype(np.float32)
+    out.backward(_t(go, dev))
+    _close("mean grad", xt.grad.cpu().numpy(), O.mean_bwd(go, P["batch"].sizes))
+    out2 = IrregularMeanCUDA.apply(xt.detach(), g["batch"], None)
+    assert torch.equal(out2, out.detach())
