@@ -1,0 +1,390 @@
+"""Benchmark of the periodic lattice-sum attention path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one training step (forward, backward, gradient clipping, AdamW update) of the
+4-layer max-frame model on one synthetic batch of 256 crystals per GPU (atom counts log-normal
+with median 8, clipped to 1..64; see crystalframer_b200/synth.py).  The metric is crystals per
+second over all GPUs.  Rank 0 prints one JSON line.
+
+``value``   : batches already resident in HBM; device time of K steps (CUDA events), max over ranks.
+``e2e``     : the same step through the public API with HOST (pinned) buffers: the host-to-device
+              copy of the step's batch and the device-to-host read of the loss are inside the
+              timed region.
+``roofline``: the dominant kernel call (lattice-sum backward), algorithmic flops / CUDA-event time,
+              against the FP32 fused-multiply-add throughput measured on the same device by the
+              library's probe kernel; the special-function (ex2) figures sit beside it.
+``cpu_baseline`` / ``--impl reference``: the reference's own kernels compiled for the host cores
+              (oracle/_ref; else the C restatement) under the same model, on a bounded sample.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np
+import torch
+
+METRIC = "crystals/sec train fwd+bwd (4-layer max-frame)"
+UNIT = "crystals/s"
+WORKLOAD = "cfg3: 4-layer max-frame training step, 256 crystals/GPU, lognormal sizes (median 8, 1..64), fp32"
+BATCH = 256
+# algorithmic work per unit: one (pair, head, translation) term and one (pair, head) projection
+FLOP_TERM_FWD, FLOP_TERM_BWD, SFU_TERM = 516.0, 738.0, 110.0
+FLOP_PROJ_FWD, FLOP_PROJ_BWD = 8192.0, 16384.0
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-crystals", type=int, default=16, help="crystals per CPU-baseline step")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def make_model(seed):
+    from crystalframer_b200.latticeformer import Latticeformer, ModelParams
+    torch.manual_seed(seed)
+    return Latticeformer(ModelParams())
+
+
+def make_optimizer(model, fused):
+    decay = [p for n, p in model.named_parameters() if p.requires_grad and not n.endswith("bias")]
+    no_decay = [p for n, p in model.named_parameters() if p.requires_grad and n.endswith("bias")]
+    groups = [{"params": decay, "weight_decay": 1e-5}, {"params": no_decay, "weight_decay": 0.0}]
+    return torch.optim.AdamW(groups, lr=5e-4, betas=(0.9, 0.98), fused=fused)
+
+
+def synthetic_batches(n_batches, seed0, num_crystals):
+    from crystalframer_b200 import synth
+    out = []
+    for i in range(n_batches):
+        b = synth.make_workload("cfg3", seed=seed0 + i, num_crystals=num_crystals)
+        y = np.random.default_rng(seed0 + i).normal(size=(len(b.sizes), 1)).astype(np.float32)
+        out.append((b, y))
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) >= 9:
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+        load = sorted(sm)[len(sm) // 4:] if sm else []
+        return {"sm_mhz": (float(np.median(load)) if load else None), "sm_max_mhz": (max(mx) if mx else None),
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def measure_pipe_peaks(dev):
+    """FP32 fused-multiply-add and ex2 throughput of this device (library probe kernel)."""
+    from crystalframer_b200 import _lib
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    blocks, iters = sms * 16, 4096
+    sink = torch.empty(blocks * 256, device=dev)
+    out = {}
+    for kind, name, mul in ((0, "fp32_tflops", 2.0), (1, "sfu_tops", 1.0)):
+        best = 0.0
+        for rep in range(4):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            _lib.invoke("cfb200_probe_throughput", 1, dev, kind, blocks, iters, sink.data_ptr())
+            e1.record()
+            torch.cuda.synchronize()
+            ops = blocks * 256.0 * iters * 8.0 * mul
+            best = max(best, ops / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+        out[name] = best
+    return out
+
+
+def lattice_terms(model, tb):
+    """Number of (pair, head, translation) terms per layer for this batch and these weights."""
+    from crystalframer_b200 import attention
+    rec = []
+    orig = attention.gaussian_coefficients
+
+    def spy(*a, **k):
+        out = orig(*a, **k)
+        rec.append(out.detach())
+        return out
+    attention.gaussian_coefficients = spy
+    try:
+        with torch.no_grad():
+            model(tb)
+    finally:
+        attention.gaussian_coefficients = orig
+    T = tb.trans_vec
+    vcell = torch.linalg.det(T)
+    rec_v = torch.stack([torch.linalg.cross(T[:, 1], T[:, 2]), torch.linalg.cross(T[:, 2], T[:, 0]),
+                         torch.linalg.cross(T[:, 0], T[:, 1])], 1) * (2 * math.pi / vcell[:, None, None])
+    rvl = rec_v.norm(dim=-1)[tb.batch]                                     # (N,3)
+    n_of_atom = tb.sizes[tb.batch].double()
+    terms = []
+    for a in rec:
+        cutoff = torch.sqrt(-0.5 / a) * 3.5                                # (N,H)
+        R = torch.ceil((cutoff[:, :, None].double() + 0.01) * rvl[:, None, :].double() / (2 * math.pi)).clamp(min=2)
+        terms.append(float(((2 * R + 1).prod(-1) * n_of_atom[:, None]).sum()))
+    return terms
+
+
+# ---------------------------------------------------------------------------------------------
+def run_reference(args, rank, world):
+    """The reference's own kernels on the host cores under the same model and optimiser."""
+    if rank != 0:
+        return
+    from oracle import cpu_model, functions as OF, reference as R
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    os.environ.setdefault("OMP_NUM_THREADS", str(threads))
+    model = make_model(2).train()
+    opt = make_optimizer(model, fused=False)
+    backend = "reference" if R.available("cpu") else "port"
+    # size the per-step sample so that K + W steps take about two minutes on these cores
+    probe_b, _ = synthetic_batches(1, 1999, 4)[0]
+    t0 = time.perf_counter()
+    cpu_model.forward(model, probe_b, backend=backend).abs().mean().backward()
+    rate = 4.0 / (time.perf_counter() - t0)
+    for l in model.encoder.layers:
+        l.self_attn.gauss_scale.data.zero_()
+    nc = int(max(2, min(args.cpu_crystals, rate * 120.0 / max(1, args.steps + args.warmup))))
+    batches = synthetic_batches(max(2, min(args.steps, 4)), 2000, nc)
+
+    def step(i):
+        b, y = batches[i % len(batches)]
+        opt.zero_grad(set_to_none=True)
+        pred = cpu_model.forward(model, b, backend=backend)
+        loss = (pred - torch.from_numpy(y)).abs().mean()
+        loss.backward()
+        torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+        opt.step()
+        return float(loss.detach())
+
+    for i in range(args.warmup):
+        step(i)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        step(i)
+    dt = time.perf_counter() - t0
+    value = nc * args.steps / dt
+    sample = f"{nc} crystals per step of the same distribution ({args.steps} steps, {args.warmup} warm-up)"
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "crystals_per_step": nc, "device": "host cores"},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": backend, "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def cpu_baseline(nc, budget_s=20.0):
+    from oracle import cpu_model, reference as R
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    model = make_model(2).train()
+    opt = make_optimizer(model, fused=False)
+    backend = "reference" if R.available("cpu") else "port"
+    batches = synthetic_batches(2, 2000, nc)
+    n, t0 = 0, None
+    while True:
+        b, y = batches[n % 2]
+        opt.zero_grad(set_to_none=True)
+        loss = (cpu_model.forward(model, b, backend=backend) - torch.from_numpy(y)).abs().mean()
+        loss.backward()
+        opt.step()
+        n += 1
+        if n == 1:
+            t0 = time.perf_counter()       # first step is warm-up
+        elif time.perf_counter() - t0 > budget_s or n > 40:
+            break
+    dt = time.perf_counter() - t0
+    steps = n - 1
+    return {"value": nc * steps / dt, "unit": UNIT, "cores": threads, "kind": backend,
+            "sample": f"{steps} training steps of {nc} crystals each (same distribution and model) after 1 warm-up step"}
+
+
+# ---------------------------------------------------------------------------------------------
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+    from crystalframer_b200 import _lib, data
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    model = make_model(2).to(dev).train()
+    opt = make_optimizer(model, fused=True)
+    n_host = 4
+    host = [data.host_batch(b, y) for b, y in synthetic_batches(n_host, 2 + 1000 * rank, BATCH)]
+    resident = [hb.to(dev, non_blocking=False) for hb in host]
+    params = [p for p in model.parameters() if p.requires_grad]
+    flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)   # > L2 (126 MB)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # the Gaussian-coefficient normalisation is measured on the first training batch; all ranks
+    # take rank 0's, together with the (identically seeded) initial weights
+    with torch.no_grad():
+        model(resident[0])
+    if world > 1:
+        for t in list(model.parameters()) + list(model.buffers()):
+            dist.broadcast(t.data, 0)
+
+    def train_step(tb):
+        opt.zero_grad(set_to_none=True)
+        loss = (model(tb) - tb.y).abs().mean()
+        loss.backward()
+        if world > 1:
+            flat = torch._utils._flatten_dense_tensors([p.grad for p in params])
+            dist.all_reduce(flat)
+            flat.div_(world)
+            for p, g in zip(params, torch._utils._unflatten_dense_tensors(flat, [p.grad for p in params])):
+                p.grad.copy_(g)
+        torch.nn.utils.clip_grad_norm_(params, 1.0)
+        opt.step()
+        return loss
+
+    def timed(n_steps, from_host):
+        """Device time of n_steps back-to-back steps (CUDA events on the launching stream); with
+        host buffers the host-visible wall time is taken when it is longer."""
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        e0.record()
+        for i in range(n_steps):
+            flush_buf.zero_()                                     # evict L2 between timed steps
+            tb = host[i % n_host].to(dev) if from_host else resident[i % n_host]
+            loss = train_step(tb)
+            if from_host:
+                loss.item()                                       # device-to-host read of the result
+        e1.record()
+        torch.cuda.synchronize()
+        wall = (time.perf_counter() - t0) * 1e3
+        return max(e0.elapsed_time(e1), wall) if from_host else e0.elapsed_time(e1)
+
+    for i in range(args.warmup):
+        train_step(resident[i % n_host])
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = _lib.launch_count
+    with _lib.KernelTimer() as kt:
+        barrier()
+        ms = timed(args.steps, from_host=False)
+        barrier()
+        ktimes = kt.summary()
+    launches = _lib.launch_count - launches0
+    barrier()
+    ms_e2e = timed(args.steps, from_host=True)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = t.tolist()
+    status = _lib.read_status(dev)
+    if rank != 0:
+        return
+    value = BATCH * world * args.steps / (ms * 1e-3)
+    e2e = BATCH * world * args.steps / (ms_e2e * 1e-3)
+
+    # ---- roofline of the dominant kernel call ----
+    peaks = measure_pipe_peaks(dev)
+    terms = lattice_terms(model, resident[0])
+    avg_terms = sum(terms) / len(terms)
+    pairs_heads = float(np.mean([hb.num_pairs for hb in host])) * 8
+    kern = {}
+    for name, (calls, total) in ktimes.items():
+        kern[name] = {"calls": calls, "ms_total": round(total, 3), "ms_avg": round(total / max(calls, 1), 4)}
+    bwd_ms = ktimes["cfb200_framed_proj_bwd"][1] / ktimes["cfb200_framed_proj_bwd"][0]
+    fwd_ms = ktimes["cfb200_framed_proj_fwd"][1] / ktimes["cfb200_framed_proj_fwd"][0]
+    flops_bwd = avg_terms * FLOP_TERM_BWD + pairs_heads * FLOP_PROJ_BWD
+    flops_fwd = avg_terms * FLOP_TERM_FWD + pairs_heads * FLOP_PROJ_FWD
+    ach = flops_bwd / (bwd_ms * 1e-3) / 1e12
+    roofline = {"kernel": "framed_proj_kernel<backward> (cfb200_framed_proj_bwd)", "bound": "fp32+sfu",
+                "achieved": ach, "peak": peaks["fp32_tflops"], "unit": "TFLOP/s", "frac": ach / peaks["fp32_tflops"],
+                "peak_source": "FP32 FMA throughput measured on this device by cfb200_probe_throughput",
+                "algorithmic_flop_per_launch": flops_bwd, "terms_per_launch": avg_terms, "ms_per_launch": bwd_ms,
+                "sfu_achieved_tops": avg_terms * SFU_TERM / (bwd_ms * 1e-3) / 1e12, "sfu_peak_tops": peaks["sfu_tops"],
+                "traffic": None,
+                "forward": {"ms_per_launch": fwd_ms, "achieved": flops_fwd / (fwd_ms * 1e-3) / 1e12,
+                            "frac": flops_fwd / (fwd_ms * 1e-3) / 1e12 / peaks["fp32_tflops"]}}
+    pair_sums = avg_terms * 2 * len(terms) * args.steps / (ms * 1e-3)      # one fwd + one bwd sweep per layer
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "global_batch": BATCH * world, "parallelism": f"dp{world}",
+                       "l2": "256 MB buffer written between timed steps", "optimizer": "AdamW lr 5e-4, clip 1.0, L1 loss"},
+            "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": host[0].nbytes(), "d2h_bytes_per_step": 4},
+            "gpu_launches": launches, "pair_sums_per_s": pair_sums, "roofline": roofline, "kernels": kern,
+            "clocks": clocks, "device_status": status}
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(args.cpu_crystals)
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse()
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operators have no CPU fallback")
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

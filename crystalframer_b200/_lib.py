@@ -42,6 +42,7 @@ SIGNATURES = {
     "cfb200_dpa_bwd": (ctypes.c_int, [vp] * 7 + [i64, i64] + [vp] * 9),
     "cfb200_segment_mean_fwd": (ctypes.c_int, [vp, vp, i64, i64, vp, vp]),
     "cfb200_segment_mean_bwd": (ctypes.c_int, [vp, vp, i64, i64, vp, vp]),
+    "cfb200_probe_throughput": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, vp, vp]),
 }
 
 
@@ -82,6 +83,50 @@ def iptr(t):
 
 def stream(device):
     return torch.cuda.current_stream(device).cuda_stream
+
+
+# ---- launch accounting and optional per-call CUDA-event timing --------------------------------
+launch_count = 0          # kernels of this library enqueued since import (all entry points)
+_timer = None
+
+
+class KernelTimer:
+    """Brackets every entry-point call with CUDA events on the stream the kernels are enqueued
+    on; ``summary()`` synchronises and returns {entry point: (calls, total milliseconds)}."""
+
+    def __init__(self):
+        self.records = {}
+
+    def __enter__(self):
+        global _timer
+        _timer = self
+        return self
+
+    def __exit__(self, *exc):
+        global _timer
+        _timer = None
+
+    def summary(self):
+        torch.cuda.synchronize()
+        return {name: (len(ev), sum(a.elapsed_time(b) for a, b in ev)) for name, ev in self.records.items()}
+
+
+def invoke(name, n_kernels, device, *args):
+    """Calls entry point ``name`` with ``args`` followed by the current stream of ``device``."""
+    global launch_count
+    fn = getattr(lib(), name)
+    with torch.cuda.device(device):
+        st = torch.cuda.current_stream(device)
+        if _timer is not None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(st)
+            rc = fn(*args, st.cuda_stream)
+            e1.record(st)
+            _timer.records.setdefault(name, []).append((e0, e1))
+        else:
+            rc = fn(*args, st.cuda_stream)
+    check(rc, name)
+    launch_count += n_kernels
 
 
 def read_status(device=None):

@@ -8,6 +8,33 @@
 #include "dpa.cu"
 #include "pool_index.cu"
 
+namespace cfb {
+
+// Pipe-throughput probe: every thread runs `iters` rounds of 8 independent dependent-chains of
+// fused multiply-adds (kind 0) or ex2.approx (kind 1).
+__global__ void __launch_bounds__(256) probe_kernel(int kind, int iters, float* sink)
+{
+    float x[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) x[j] = 0.001f * (float)(threadIdx.x + j) - 0.5f;
+    const float m = 0.999f, c = 1e-3f;
+    if (kind == 0) {
+        for (int it = 0; it < iters; it++)
+#pragma unroll
+            for (int j = 0; j < 8; j++) x[j] = fmaf(x[j], m, c);
+    } else {
+        for (int it = 0; it < iters; it++)
+#pragma unroll
+            for (int j = 0; j < 8; j++) x[j] = ex2_approx(x[j]);
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) s += x[j];
+    sink[(size_t)blockIdx.x * blockDim.x + threadIdx.x] = s;
+}
+
+}  // namespace cfb
+
 namespace {
 
 cfb200_config g_cfg;
@@ -277,6 +304,14 @@ int cfb200_dpa_bwd(const float* q_scaled, const float* k, const float* v, const 
     A.out = const_cast<float*>(out); A.lse = const_cast<float*>(lse); A.gout = gout;
     A.gq = gq; A.gk = gk; A.gv = gv; A.gz = gz; A.gb = values ? gvalues : nullptr;
     return cfb::dpa_bwd(A, P, S(stream));
+}
+
+int cfb200_probe_throughput(int kind, int blocks, int iters, float* sink, void* stream)
+{
+    if (blocks < 1 || iters < 0 || (kind != 0 && kind != 1)) return CFB200_E_SHAPE;
+    if (sink == nullptr) return CFB200_E_NULL;
+    cfb::probe_kernel<<<blocks, 256, 0, S(stream)>>>(kind, iters, sink);
+    return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
 }
 
 int cfb200_segment_mean_fwd(const float* x, const int64_t* start, int64_t B, int64_t D, float* out, void* stream)

@@ -20,9 +20,7 @@ def csr_offsets(edge_ij_e, N):
             return out
     E = edge_ij_e.shape[1]
     out = torch.empty(N + 1, dtype=torch.int64, device=edge_ij_e.device)
-    with torch.cuda.device(edge_ij_e.device):
-        _lib.check(_lib.lib().cfb200_csr_offsets(_lib.iptr(edge_ij_e), E, N, _lib.iptr(out),
-                                                 _lib.stream(edge_ij_e.device)), "cfb200_csr_offsets")
+    _lib.invoke("cfb200_csr_offsets", 1, edge_ij_e.device, _lib.iptr(edge_ij_e), E, N, _lib.iptr(out))
     if len(_csr_cache) > 64:
         for k in [k for k, v in _csr_cache.items() if v[0]() is None]:
             del _csr_cache[k]

@@ -55,11 +55,9 @@ class RealEncodingWithFramedProjFuncCUDA(torch.autograd.Function):
         z = torch.empty((E, H), device=dev, dtype=torch.float32)
         v = torch.empty((E, H, Wd.shape[-2]), device=dev, dtype=torch.float32) if want_v else None
         p, ip = _lib.ptr, _lib.iptr
-        with torch.cuda.device(dev):
-            _lib.check(_lib.lib().cfb200_framed_proj_fwd(
-                p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), N, E, float(dist_max), cutoff,
-                p(Wd), p(W1), p(W2), p(W3), p(f1), p(f2), p(f3), p(z), p(v), _lib.stream(dev)),
-                "cfb200_framed_proj_fwd")
+        _lib.invoke("cfb200_framed_proj_fwd", 1, dev,
+                    p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), N, E, float(dist_max), cutoff,
+                    p(Wd), p(W1), p(W2), p(W3), p(f1), p(f2), p(f3), p(z), p(v))
         ctx.save_for_backward(a, pos, tv, batch, edges, rv, Wd, W1, W2, W3, f1, f2, f3, z)
         ctx.meta = (float(dist_max), cutoff, rvlen_n is not None,
                     None if W_k is None else tuple(W_k.shape), None if W_k1 is None else tuple(W_k1.shape))
@@ -90,12 +88,10 @@ class RealEncodingWithFramedProjFuncCUDA(torch.autograd.Function):
         nbytes = lib.cfb200_framed_proj_bwd_workspace_bytes(N, E)
         ws = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=dev)
         p, ip = _lib.ptr, _lib.iptr
-        with torch.cuda.device(dev):
-            _lib.check(lib.cfb200_framed_proj_bwd(
-                p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), ip(e_start), N, E, dist_max, cutoff,
-                p(Wd), p(W1), p(W2), p(W3), p(f1), p(f2), p(f3), p(z), p(gz), p(gv), p(ga),
-                p(gWd), p(gW1), p(gW2), p(gW3), ws.data_ptr(), int(nbytes), _lib.stream(dev)),
-                "cfb200_framed_proj_bwd")
+        _lib.invoke("cfb200_framed_proj_bwd", 3, dev,
+                    p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), ip(e_start), N, E, dist_max, cutoff,
+                    p(Wd), p(W1), p(W2), p(W3), p(f1), p(f2), p(f3), p(z), p(gz), p(gv), p(ga),
+                    p(gWd), p(gW1), p(gW2), p(gW3), ws.data_ptr(), int(nbytes))
         out[0] = ga
         out[9] = gWd.reshape(shape_d)
         if gW1 is not None:

@@ -22,9 +22,8 @@ class FusedDotProductAttentionCUDA(torch.autograd.Function):
         out = torch.empty_like(v)
         lse = torch.empty((N, H), device=dev, dtype=torch.float32)
         p, ip = _lib.ptr, _lib.iptr
-        with torch.cuda.device(dev):
-            _lib.check(_lib.lib().cfb200_dpa_fwd(p(q), p(k), p(v), p(a), p(b), ip(edges), ip(e_start), N, E,
-                                                 p(out), p(lse), None, _lib.stream(dev)), "cfb200_dpa_fwd")
+        _lib.invoke("cfb200_dpa_fwd", 1, dev, p(q), p(k), p(v), p(a), p(b), ip(edges), ip(e_start), N, E,
+                    p(out), p(lse), None)
         ctx.save_for_backward(q, k, v, a, b, edges, e_start, out, lse)
         return out
 
@@ -39,10 +38,8 @@ class FusedDotProductAttentionCUDA(torch.autograd.Function):
         gz = torch.empty((E, H), device=dev, dtype=torch.float32)
         gb = torch.empty_like(b) if b is not None else None
         p, ip = _lib.ptr, _lib.iptr
-        with torch.cuda.device(dev):
-            _lib.check(_lib.lib().cfb200_dpa_bwd(p(q), p(k), p(v), p(a), p(b), ip(edges), ip(e_start), N, E,
-                                                 p(out), p(lse), p(go), p(gq), p(gk), p(gv), p(gz), p(gb),
-                                                 _lib.stream(dev)), "cfb200_dpa_bwd")
+        _lib.invoke("cfb200_dpa_bwd", 2, dev, p(q), p(k), p(v), p(a), p(b), ip(edges), ip(e_start), N, E,
+                    p(out), p(lse), p(go), p(gq), p(gk), p(gv), p(gz), p(gb))
         return gq, gk, gv, (gz if a is not None else None), gb, None, None
 
 
@@ -59,7 +56,6 @@ def attention_probabilities(que_ihk, key_ihk, val_ihk, aij_eh, bij_ehk, edge_ij_
     lse = torch.empty((N, H), device=dev, dtype=torch.float32)
     prob = torch.empty((E, H), device=dev, dtype=torch.float32)
     p, ip = _lib.ptr, _lib.iptr
-    with torch.cuda.device(dev):
-        _lib.check(_lib.lib().cfb200_dpa_fwd(p(q), p(k), p(v), p(a), p(b), ip(edges), ip(e_start), N, E,
-                                             p(out), p(lse), p(prob), _lib.stream(dev)), "cfb200_dpa_fwd")
+    _lib.invoke("cfb200_dpa_fwd", 1, dev, p(q), p(k), p(v), p(a), p(b), ip(edges), ip(e_start), N, E,
+                p(out), p(lse), p(prob))
     return out, prob, lse

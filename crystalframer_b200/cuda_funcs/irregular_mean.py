@@ -21,9 +21,7 @@ class IrregularMeanCUDA(torch.autograd.Function):
         start[1:] = torch.cumsum(sizes, 0)
         x = x_ik.detach().contiguous().float()
         out = torch.empty((B,) + tuple(x.shape[1:]), device=dev, dtype=torch.float32)
-        with torch.cuda.device(dev):
-            _lib.check(_lib.lib().cfb200_segment_mean_fwd(_lib.ptr(x), _lib.iptr(start), B, D, _lib.ptr(out),
-                                                          _lib.stream(dev)), "cfb200_segment_mean_fwd")
+        _lib.invoke("cfb200_segment_mean_fwd", 1, dev, _lib.ptr(x), _lib.iptr(start), B, D, _lib.ptr(out))
         ctx.save_for_backward(start)
         ctx.shape = tuple(x.shape)
         return out
@@ -35,7 +33,5 @@ class IrregularMeanCUDA(torch.autograd.Function):
         go = go_nk.detach().contiguous().float()
         gx = torch.empty(ctx.shape, device=go.device, dtype=torch.float32)
         D = gx.numel() // max(gx.shape[0], 1)
-        with torch.cuda.device(go.device):
-            _lib.check(_lib.lib().cfb200_segment_mean_bwd(_lib.ptr(go), _lib.iptr(start), B, D, _lib.ptr(gx),
-                                                          _lib.stream(go.device)), "cfb200_segment_mean_bwd")
+        _lib.invoke("cfb200_segment_mean_bwd", 1, go.device, _lib.ptr(go), _lib.iptr(start), B, D, _lib.ptr(gx))
         return gx, None, None

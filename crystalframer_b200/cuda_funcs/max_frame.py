@@ -27,10 +27,9 @@ def _frame_call(axis, q, k, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_
     sel_e = torch.empty((N, H), device=dev, dtype=torch.int64) if want_selection else None
     sel_i = torch.empty((N, H), device=dev, dtype=torch.int32) if want_selection else None
     p, ip = _lib.ptr, _lib.iptr
-    with torch.cuda.device(dev):
-        _lib.check(_lib.lib().cfb200_max_frame(
-            axis, p(qq), p(kk), p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), ip(e_start), N, E, cutoff, seed,
-            p(f32c(frame1)), p(out), ip(sel_e), _lib.ptr(sel_i, torch.int32), _lib.stream(dev)), "cfb200_max_frame")
+    _lib.invoke("cfb200_max_frame", 1, dev,
+                axis, p(qq), p(kk), p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), ip(e_start), N, E, cutoff, seed,
+                p(f32c(frame1)), p(out), ip(sel_e), _lib.ptr(sel_i, torch.int32))
     return (out, sel_e, sel_i) if want_selection else out
 
 
@@ -84,8 +83,7 @@ def max_frames_fused(q, k, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_n
     s1, s2 = _draw_seed(), _draw_seed()
     f = torch.empty((3, N, H, 3), device=dev, dtype=torch.float32)
     p, ip = _lib.ptr, _lib.iptr
-    with torch.cuda.device(dev):
-        _lib.check(_lib.lib().cfb200_max_frames(
-            p(qq), p(kk), p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), ip(e_start), N, E, cutoff, s1, s2,
-            p(f[0]), p(f[1]), p(f[2]), _lib.stream(dev)), "cfb200_max_frames")
+    _lib.invoke("cfb200_max_frames", 1, dev,
+                p(qq), p(kk), p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), ip(e_start), N, E, cutoff, s1, s2,
+                p(f[0]), p(f[1]), p(f[2]))
     return f[0], f[1], f[2]

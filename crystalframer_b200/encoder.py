@@ -18,24 +18,27 @@ from .cuda_funcs import compile_kernels, register_csr
 from .latticeformer_params import LatticeformerParams
 
 
-def build_pair_list(sizes: Tensor):
+def build_pair_list(sizes: Tensor, counts=None):
     """Dense pair list of a batch of crystals on the GPU, in one call instead of the reference's
     Python loop over crystals.  Returns edges (2,E) int64, e_start (N+1), batch (N),
-    crystal_start (B+1); N and E are computed on the host from ``sizes``."""
+    crystal_start (B+1).  ``counts = (N, E)`` (atoms, pairs) spares the device-to-host read of
+    ``sizes`` when the caller already knows them."""
     if not sizes.is_cuda:
         raise RuntimeError("build_pair_list needs sizes on a CUDA device (there is no CPU path)")
     sizes = sizes.to(torch.int64).contiguous()
-    host = sizes.tolist()
-    B, N, E = len(host), sum(host), sum(s * s for s in host)
+    B = sizes.shape[0]
+    if counts is None:
+        host = sizes.tolist()
+        N, E = sum(host), sum(s * s for s in host)
+    else:
+        N, E = int(counts[0]), int(counts[1])
     dev = sizes.device
     edges = torch.empty((2, E), dtype=torch.int64, device=dev)
     e_start = torch.empty(N + 1, dtype=torch.int64, device=dev)
     batch = torch.empty(N, dtype=torch.int64, device=dev)
     crystal_start = torch.empty(B + 1, dtype=torch.int64, device=dev)
-    with torch.cuda.device(dev):
-        _lib.check(_lib.lib().cfb200_edge_index(_lib.iptr(sizes), B, N, E, _lib.iptr(edges), _lib.iptr(e_start),
-                                                _lib.iptr(batch), _lib.iptr(crystal_start), _lib.stream(dev)),
-                   "cfb200_edge_index")
+    _lib.invoke("cfb200_edge_index", 2, dev, _lib.iptr(sizes), B, N, E, _lib.iptr(edges), _lib.iptr(e_start),
+                _lib.iptr(batch), _lib.iptr(crystal_start))
     register_csr(edges, N, e_start)
     return edges, e_start, batch, crystal_start
 
@@ -54,7 +57,7 @@ def det_3x3(m):
 
 
 def compute_lattice_distances_for_cuda(pos, batch, trans_vec, sizes, lattice_range, cutoff_radius=0,
-                                       output_real=False, output_reci=False):
+                                       output_real=False, output_reci=False, num_pairs=None):
     """Relative positions of all pairs, reciprocal vectors and cell volumes; returns the
     reference's 6-tuple (pos_ij, dist2_min=None, kr_base, rvecs, vcell, edges)."""
     if sizes is None:
@@ -62,7 +65,8 @@ def compute_lattice_distances_for_cuda(pos, batch, trans_vec, sizes, lattice_ran
         sizes.scatter_add_(0, batch, torch.ones_like(batch))
     if not torch.is_tensor(sizes):
         sizes = torch.tensor(sizes, dtype=torch.int64)
-    edges = build_pair_list(sizes.to(pos.device))[0]
+    counts = (pos.shape[0], num_pairs) if num_pairs is not None else None
+    edges = build_pair_list(sizes.to(pos.device), counts)[0]
     vcell = det_3x3(trans_vec).contiguous()
     rvecs = torch.stack([torch.cross(trans_vec[:, 1], trans_vec[:, 2], dim=1),
                          torch.cross(trans_vec[:, 2], trans_vec[:, 0], dim=1),
@@ -163,10 +167,11 @@ class CrystalformerEncoderCUDA(Module):
                         P.value_pe_dist_wscale, P.value_pe_angle_wscale, P.value_pe_dist_coef,
                         P.value_pe_angle_coef, P.symm_break_noise)
 
-    def forward(self, src, pos, batch, trans, sizes, onehot=None, this_epoch=None):
+    def forward(self, src, pos, batch, trans, sizes, onehot=None, this_epoch=None, num_pairs=None):
         batch = batch - batch[0]
         pos_ij, dist2_min, kr_base, rvecs, vcell, edges = compute_lattice_distances_for_cuda(
-            pos, batch, trans, sizes, self.lattice_params.lattice_range, -1, output_real=True, output_reci=False)
+            pos, batch, trans, sizes, self.lattice_params.lattice_range, -1, output_real=True, output_reci=False,
+            num_pairs=num_pairs)
         if src.size(-1) != self.d_model:
             raise RuntimeError("the feature number of src must be equal to d_model")
         out = src

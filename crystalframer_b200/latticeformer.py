@@ -63,6 +63,7 @@ class Latticeformer(nn.Module):
 
     def forward(self, data, this_epoch=None):
         x = self.input_embeddings(data.x)
-        x = self.encoder(x, data.pos, data.batch, data.trans_vec, data.sizes, this_epoch=this_epoch)
+        x = self.encoder(x, data.pos, data.batch, data.trans_vec, data.sizes, this_epoch=this_epoch,
+                         num_pairs=getattr(data, "num_pairs", None))
         x = self.pooling_layer(x, data.batch, data.sizes)
         return self.mlp(x)

@@ -153,6 +153,12 @@ int cfb200_segment_mean_fwd(const float* x, const int64_t* start, int64_t B, int
 int cfb200_segment_mean_bwd(const float* gout, const int64_t* start, int64_t B, int64_t D,
                             float* gx, void* stream);
 
+/* Measurement aid with no counterpart in the reference: every thread of `blocks` x 256 threads
+ * runs `iters` rounds of 8 independent chains of fused multiply-adds (kind 0) or ex2.approx
+ * (kind 1) and writes one float to sink (blocks*256 floats).  Timed by the caller, it gives the
+ * FP32 and special-function pipe throughput of the device the roofline fractions refer to. */
+int cfb200_probe_throughput(int kind, int blocks, int iters, float* sink, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
