@@ -243,7 +243,7 @@ def cpu_baseline(nc, budget_s=20.0):
 # ---------------------------------------------------------------------------------------------
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
-    from crystalframer_b200 import _lib, data
+    from crystalframer_b200 import _lib, data, parallel
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     torch.backends.cuda.matmul.allow_tf32 = False
@@ -265,20 +265,13 @@ def run_ours(args, rank, world, local_rank):
     # take rank 0's, together with the (identically seeded) initial weights
     with torch.no_grad():
         model(resident[0])
-    if world > 1:
-        for t in list(model.parameters()) + list(model.buffers()):
-            dist.broadcast(t.data, 0)
+    parallel.broadcast_state(model)
 
     def train_step(tb):
         opt.zero_grad(set_to_none=True)
         loss = (model(tb) - tb.y).abs().mean()
         loss.backward()
-        if world > 1:
-            flat = torch._utils._flatten_dense_tensors([p.grad for p in params])
-            dist.all_reduce(flat)
-            flat.div_(world)
-            for p, g in zip(params, torch._utils._unflatten_dense_tensors(flat, [p.grad for p in params])):
-                p.grad.copy_(g)
+        parallel.allreduce_gradients(params)
         torch.nn.utils.clip_grad_norm_(params, 1.0)
         opt.step()
         return loss

@@ -1,0 +1,85 @@
+"""Host-side logic on CPU: synthetic data, module parameters, data-parallel plumbing (gloo)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_synthetic_workloads_are_seeded_and_in_range():
+    from crystalframer_b200 import synth
+    a, b = synth.make_workload("cfg2"), synth.make_workload("cfg2")
+    assert np.array_equal(a.pos, b.pos) and np.array_equal(a.sizes, b.sizes)
+    assert len(a.sizes) == 256 and a.sizes.min() >= 1 and a.sizes.max() <= 64
+    assert 6 <= np.median(a.sizes) <= 10
+    lengths = np.linalg.norm(a.trans_vec, axis=-1)
+    assert lengths.min() >= 3.0 - 1e-4 and lengths.max() <= 15.0 + 1e-4
+    assert abs(np.linalg.det(a.trans_vec.astype(np.float64))).min() > 1.0
+    c = synth.make_workload("cfg4", num_crystals=3)
+    assert c.sizes.min() >= 100 and c.sizes.max() <= 200
+    assert a.x.shape == (a.num_atoms, 98) and (a.x.sum(1) == 1).all()
+
+
+def test_model_has_reference_parameter_set():
+    from crystalframer_b200.latticeformer import Latticeformer, ModelParams
+    m = Latticeformer(ModelParams())
+    assert sum(p.numel() for p in m.parameters() if p.requires_grad) == 951809
+    sd = m.state_dict()
+    pre = "encoder.layers.0.self_attn."
+    shapes = {"q_proj_weight": (128, 128), "k_proj_weight": (128, 128), "v_proj_weight": (128, 128),
+              "in_proj_bias": (384,), "out_proj.weight": (128, 128), "out_proj.bias": (128,),
+              "lattice_pos_weights": (128,), "pe_dist_proj": (1, 8, 16, 64), "proj_angle1": (1, 8, 16, 64),
+              "proj_angle2": (1, 8, 16, 64), "proj_angle3": (1, 8, 16, 64), "gauss_scale": (2,), "atten_scale": (1,)}
+    for k, shp in shapes.items():
+        assert tuple(sd[pre + k].shape) == shp, k
+
+
+def test_partition_by_pair_count_balances():
+    from crystalframer_b200 import synth
+    from crystalframer_b200.parallel import partition_by_pair_count
+    sizes = synth.make_workload("cfg2").sizes
+    parts = partition_by_pair_count(sizes, 8)
+    assert sorted(np.concatenate(parts).tolist()) == list(range(len(sizes)))
+    loads = np.array([(sizes[p] ** 2).sum() for p in parts])
+    assert loads.max() - loads.min() <= (sizes ** 2).max()
+
+
+def _worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    sys.path.insert(0, ROOT)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from crystalframer_b200 import parallel
+    torch.manual_seed(100 + rank)                      # different initial weights per rank on purpose
+    model = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.Linear(5, 1))
+    parallel.broadcast_state(model)
+    w0 = torch.cat([p.detach().flatten() for p in model.parameters()])
+    x = torch.full((4, 6), float(rank + 1))
+    model(x).sum().backward()
+    local = torch.cat([p.grad.flatten() for p in model.parameters()]).clone()
+    parallel.allreduce_gradients(list(model.parameters()))
+    avg = torch.cat([p.grad.flatten() for p in model.parameters()])
+    gathered = [torch.zeros_like(local) for _ in range(world)]
+    dist.all_gather(gathered, local)
+    q.put((rank, w0, avg, torch.stack(gathered).mean(0)))
+    dist.destroy_process_group()
+
+
+def test_gradient_allreduce_two_ranks_gloo():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + os.getpid() % 1000
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted([q.get(timeout=120) for _ in procs], key=lambda t: t[0])
+    for p in procs:
+        p.join(60)
+    (_, w_a, g_a, m_a), (_, w_b, g_b, m_b) = res
+    assert torch.equal(w_a, w_b)                       # broadcast made the weights identical
+    assert torch.allclose(g_a, g_b) and torch.allclose(g_a, m_a, atol=1e-6)

@@ -1,0 +1,205 @@
+"""The CPU oracle against everything that pins it (no GPU needed):
+
+* committed golden fixtures produced by the reference's own code (tests/golden/make_golden.py);
+* the reference kernels' CPU build, when oracle/_ref is present on this machine;
+* finite differences of the float64 build;
+* edge cases: single-atom crystal, small cells with lattice range above the minimum.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import make_problem
+from oracle import oracle as O
+from oracle import reference as R
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def close(name, got, want, rtol=1e-4, atol=1e-5):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    assert got.shape == want.shape, name
+    err = np.abs(got - want)
+    bad = err > atol + rtol * np.abs(want)
+    assert not bad.any(), f"{name}: {bad.sum()} of {bad.size} outside tolerance, max abs {err.max():.3e}"
+
+
+def test_golden_reference_kernels():
+    G = np.load(os.path.join(GOLD, "ref_kernels_small.npz"))
+    cfg = O.Config()
+    g = O.lattice_geometry(G["pos"], G["cells"], G["sizes"])
+    assert np.array_equal(g["edges"], G["edges"]) and np.array_equal(g["e_start"], G["e_start"])
+    Rah = O.lattice_range(cfg, G["a"], g["rvlen"], g["batch"])
+    assert np.array_equal(Rah, G["R_ah"]) and Rah.max() > 2       # the small cell exercises ranges above the minimum
+    fr = O.max_frames(cfg, G["q"] / 4.0, G["k"], G["a"], g["pos_ij"], G["cells"], g["rvlen"], g["batch"], g["edges"],
+                      g["e_start"])
+    assert np.array_equal(fr["sel_edge1"], G["sel_edge1"]) and np.array_equal(fr["sel_edge2"], G["sel_edge2"])
+    assert np.array_equal(fr["frame1"], G["frame1"]) and np.array_equal(fr["frame2_max"], G["frame2_max"])
+    close("frame2", fr["frame2"], G["frame2"], 1e-6, 1e-6)
+    close("frame3", fr["frame3"], G["frame3"], 1e-6, 1e-6)
+    frames = np.stack([G["frame1"], G["frame2"], G["frame3"]])
+    z, v = O.framed_proj_fwd(cfg, G["a"], g["pos_ij"], G["cells"], g["rvlen"], g["batch"], g["edges"], G["W_d"],
+                             G["W_a"], frames)
+    close("z", z, G["z"], 1e-6, 1e-6)
+    close("values", v, G["values"], 1e-6, 1e-7)
+    ga, gWd, gWa = O.framed_proj_bwd(cfg, G["a"], g["pos_ij"], G["cells"], g["rvlen"], g["batch"], g["edges"],
+                                     g["e_start"], G["W_d"], G["W_a"], frames, G["z"], G["gz"], G["gv"])
+    close("ga", ga, G["ga"], 1e-4, 1e-5 * max(1.0, np.abs(G["ga"]).max()))
+    close("gW_d", gWd, G["gW_d"], 1e-4, 1e-5)
+    close("gW_a", gWa, G["gW_a"], 1e-4, 1e-5)
+    out, prob = O.dpa_fwd(cfg, G["q"] / 4.0, G["k"], G["v"], G["z"], G["values"], g["edges"], g["e_start"])
+    close("attention out", out, G["dpa_out"])
+    close("attention prob", prob, G["dpa_prob"])
+    res = O.dpa_bwd(cfg, G["q"] / 4.0, G["k"], G["v"], G["values"], g["edges"], g["e_start"], G["dpa_prob"], G["dpa_out"],
+                    G["go"])
+    for n, x in zip(("gq", "gk", "gvv", "gaij", "gbij"), res):
+        close(n, x, G[n])
+    close("mean", O.mean_fwd(G["mean_x"], G["sizes"]), G["mean"])
+
+
+def test_golden_pure_pytorch_twin():
+    """Fixed range 2, un-windowed Gaussians, no frames: the plain Crystalformer subset."""
+    G = np.load(os.path.join(GOLD, "ref_pure_small.npz"))
+    K = np.load(os.path.join(GOLD, "ref_kernels_small.npz"))
+    cfg = O.Config(cut_sigma=32, cutoff_radius=0.0, D_ang=0)        # window >= 64 -> full range of Gaussians
+    g = O.lattice_geometry(K["pos"], K["cells"], K["sizes"])
+    assert np.array_equal(g["edges"], G["edges"])
+    z, v = O.framed_proj_fwd(cfg, K["a"], g["pos_ij"], K["cells"], g["rvlen"], g["batch"], g["edges"], K["W_d"], None, None)
+    close("z", z, G["z"])
+    close("values", v, G["values"])
+    out, prob = O.dpa_fwd(cfg, K["q"] / 4.0, K["k"], K["v"], G["z"], G["values"], g["edges"], g["e_start"])
+    close("out", out, G["out"])
+    close("prob", prob, G["prob"])
+
+
+@pytest.mark.skipif(not R.available("cpu"), reason="oracle/_ref not built (reference tree absent)")
+def test_against_reference_cpu_build(problem_cfg1):
+    P = problem_cfg1
+    geo, b, cfg = P["geo"], P["batch"], P["cfg"]
+    rk = R.RefKernels("cpu")
+    T = lambda x: torch.from_numpy(np.ascontiguousarray(x))
+    a, q, k, v = T(P["a"]), T(P["q"] / 4.0), T(P["k"]), T(P["v"])
+    r, tv, bt, e, rv = T(geo["pos_ij"]), T(b.trans_vec), T(geo["batch"]), T(geo["edges"]), T(geo["rvlen"])
+    f1, s1 = rk.frame1(q, k, a, r, tv, bt, e, rv, -3.5)
+    f2m, s2 = rk.frame2(q, k, a, r, tv, bt, e, rv, -3.5, f1)
+    f2, f3 = rk.complete(f1, f2m)
+    fr = O.max_frames(cfg, P["q"] / 4.0, P["k"], P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"],
+                      geo["edges"], geo["e_start"])
+    assert np.array_equal(fr["sel_edge1"], s1.numpy()) and np.array_equal(fr["sel_edge2"], s2.numpy())
+    assert np.array_equal(fr["frame1"], f1.numpy())
+    frames = torch.stack([f1, f2, f3]).contiguous()
+    Wd, Wa = T(P["W_d"])[None].contiguous(), T(P["W_a"])[:, None].contiguous()
+    z, val = rk.framed_proj_fwd(a, r, tv, bt, e, 14.0, 1.0, Wd, Wa, frames, cfg.angle_sigma, 1.0, 1.0, rv, -3.5)
+    zo, vo = O.framed_proj_fwd(cfg, P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"],
+                               P["W_d"], P["W_a"], frames.numpy())
+    close("z", zo, z.numpy(), 1e-6, 1e-6)
+    close("values", vo, val.numpy(), 1e-6, 1e-7)
+    rng = np.random.default_rng(9)
+    gz, gv = rng.normal(size=zo.shape).astype(np.float32), rng.normal(size=vo.shape).astype(np.float32)
+    ga, gWd, gWa = rk.framed_proj_bwd(a, r, tv, bt, e, 14.0, 1.0, Wd, Wa, frames, cfg.angle_sigma, 1.0, 1.0, rv, -3.5,
+                                      z, T(gz), T(gv))
+    gao, gWdo, gWao = O.framed_proj_bwd(cfg, P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"],
+                                        geo["edges"], geo["e_start"], P["W_d"], P["W_a"], frames.numpy(), z.numpy(), gz, gv)
+    close("ga", gao, ga.numpy(), 1e-4, 1e-5 * max(1.0, float(ga.abs().max())))
+    close("gW_d", gWdo, gWd.numpy(), 1e-4, 1e-5 * max(1.0, float(gWd.abs().max())))
+    close("gW_a", gWao, gWa.numpy(), 1e-4, 1e-5 * max(1.0, float(gWa.abs().max())))
+
+
+def test_finite_differences_float64(problem_cfg1):
+    P = problem_cfg1
+    geo, b, cfg = P["geo"], P["batch"], P["cfg"]
+    fr = O.max_frames(cfg, P["q"] / 4.0, P["k"], P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"],
+                      geo["edges"], geo["e_start"])
+    frames = np.stack([fr["frame1"], fr["frame2"], fr["frame3"]])
+    rng = np.random.default_rng(1)
+    args = (geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"])
+
+    def fwd(a, Wd, Wa):
+        return O.framed_proj_fwd(cfg, a, *args, Wd, Wa, frames, dtype=np.float64)
+
+    a0, Wd0, Wa0 = P["a"].astype(np.float64), P["W_d"].astype(np.float64), P["W_a"].astype(np.float64)
+    z, v = fwd(a0, Wd0, Wa0)
+    gz, gv = rng.normal(size=z.shape), rng.normal(size=v.shape)
+    ga, gWd, gWa = O.framed_proj_bwd(cfg, a0, *args, geo["e_start"], Wd0, Wa0, frames, z, gz, gv, dtype=np.float64)
+    loss = lambda a, Wd, Wa: sum((x * g).sum() for x, g in zip(fwd(a, Wd, Wa), (gz, gv)))
+    eps = 1e-6
+    for idx in [(0, 0), (17, 3), (40, 7)]:
+        ap, am = a0.copy(), a0.copy()
+        ap[idx] += eps
+        am[idx] -= eps
+        fd = (loss(ap, Wd0, Wa0) - loss(am, Wd0, Wa0)) / (2 * eps)
+        assert abs(fd - ga[idx]) <= 1e-5 * max(1.0, abs(fd)), (idx, fd, ga[idx])
+    for idx in [(0, 0, 0), (3, 5, 20), (7, 15, 63)]:
+        Wp, Wm = Wd0.copy(), Wd0.copy()
+        Wp[idx] += eps
+        Wm[idx] -= eps
+        fd = (loss(a0, Wp, Wa0) - loss(a0, Wm, Wa0)) / (2 * eps)
+        assert abs(fd - gWd[idx]) <= 1e-5 * max(1.0, abs(fd)), (idx, fd, gWd[idx])
+    for idx in [(0, 0, 0, 40), (2, 6, 9, 33)]:
+        Wp, Wm = Wa0.copy(), Wa0.copy()
+        Wp[idx] += eps
+        Wm[idx] -= eps
+        fd = (loss(a0, Wd0, Wp) - loss(a0, Wd0, Wm)) / (2 * eps)
+        assert abs(fd - gWa[idx]) <= 1e-5 * max(1.0, abs(fd)), (idx, fd, gWa[idx])
+
+
+def test_attention_gradients_float64():
+    P = make_problem("cfg1")
+    geo, cfg = P["geo"], P["cfg"]
+    rng = np.random.default_rng(2)
+    E = geo["edges"].shape[1]
+    q, k, v = (P[n].astype(np.float64) for n in ("q", "k", "v"))
+    zb, vb = rng.normal(size=(E, 8)), rng.normal(size=(E, 8, 16))
+    out, prob = O.dpa_fwd(cfg, q, k, v, zb, vb, geo["edges"], geo["e_start"], dtype=np.float64)
+    go = rng.normal(size=out.shape)
+    gq, gk, gv, gz, gb = O.dpa_bwd(cfg, q, k, v, vb, geo["edges"], geo["e_start"], prob, out, go, dtype=np.float64)
+    loss = lambda q_, k_, z_: (O.dpa_fwd(cfg, q_, k_, v, z_, vb, geo["edges"], geo["e_start"], dtype=np.float64)[0] * go).sum()
+    eps = 1e-6
+    for idx in [(0, 0, 0), (30, 4, 9)]:
+        qp, qm = q.copy(), q.copy()
+        qp[idx] += eps
+        qm[idx] -= eps
+        assert abs((loss(qp, k, zb) - loss(qm, k, zb)) / (2 * eps) - gq[idx]) < 1e-6
+        kp, km = k.copy(), k.copy()
+        kp[idx] += eps
+        km[idx] -= eps
+        assert abs((loss(q, kp, zb) - loss(q, km, zb)) / (2 * eps) - gk[idx]) < 1e-6
+    zp, zm = zb.copy(), zb.copy()
+    zp[5, 2] += eps
+    zm[5, 2] -= eps
+    assert abs((loss(q, k, zp) - loss(q, k, zm)) / (2 * eps) - gz[5, 2]) < 1e-6
+
+
+def test_edge_cases():
+    cfg = O.Config()
+    # a single-atom crystal: one self pair; z is the lattice sum over the atom's own images
+    cell = np.array([[[3.0, 0, 0], [0, 3.2, 0], [0, 0, 3.4]]], np.float32)
+    g = O.lattice_geometry(np.zeros((1, 3), np.float32), cell, [1])
+    assert g["edges"].tolist() == [[0], [0]] and g["e_start"].tolist() == [0, 1]
+    a = np.full((1, 8), -0.2, np.float32)
+    z, _ = O.framed_proj_fwd(cfg, a, g["pos_ij"], cell, g["rvlen"], g["batch"], g["edges"], np.zeros((8, 16, 64), np.float32),
+                             None, None)
+    Rr = O.lattice_range(cfg, a, g["rvlen"], g["batch"])[0, 0]
+    n = [np.arange(-r, r + 1) for r in Rr]
+    d2 = (n[0][:, None, None] * 3.0) ** 2 + (n[1][None, :, None] * 3.2) ** 2 + (n[2][None, None, :] * 3.4) ** 2
+    assert abs(z[0, 0] - np.log(np.exp(-0.2 * d2).sum())) < 1e-5
+    # empty batch
+    e, s = O.edge_index(np.zeros(0, np.int64))
+    assert e.shape == (2, 0) and s.tolist() == [0]
+    # ragged sizes including 1
+    e, s = O.edge_index([2, 1, 3])
+    assert e.shape == (2, 14) and s.tolist() == [0, 2, 4, 5, 8, 11, 14]
+    assert e[:, 4].tolist() == [2, 2]
+
+
+def test_values_linear_in_weights(problem_cfg1):
+    P = problem_cfg1
+    geo, b, cfg = P["geo"], P["batch"], P["cfg"]
+    args = (cfg, P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"])
+    W2 = np.random.default_rng(3).normal(size=P["W_d"].shape).astype(np.float32) * 0.01
+    _, v1 = O.framed_proj_fwd(*args, P["W_d"], None, None)
+    _, v2 = O.framed_proj_fwd(*args, W2, None, None)
+    _, v12 = O.framed_proj_fwd(*args, P["W_d"] + W2, None, None)
+    close("linearity", v12, v1 + v2, 1e-4, 1e-6)
