@@ -93,6 +93,7 @@ const char* cfb200_error_string(int code)
         case CFB200_E_NOT_CONFIGURED: return "cfb200_configure has not been called";
         case CFB200_E_WORKSPACE: return "scratch buffer missing or too small";
         case CFB200_E_CUDA: return "CUDA launch failed";
+        case CFB200_E_TOO_LARGE: return "problem needs more scratch than the fixed array of the no-allocation entry point holds";
         default: return "unknown error";
     }
 }
@@ -329,3 +330,5 @@ int cfb200_segment_mean_bwd(const float* gout, const int64_t* start, int64_t B, 
 }
 
 }  // extern "C"
+
+#include "framed_proj_noalloc.cu"

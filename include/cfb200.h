@@ -33,6 +33,7 @@ extern "C" {
 #define CFB200_E_NOT_CONFIGURED (-4)
 #define CFB200_E_WORKSPACE (-5)    /* scratch buffer missing or too small                      */
 #define CFB200_E_CUDA (-6)         /* launch failed; see cudaGetLastError                      */
+#define CFB200_E_TOO_LARGE (-7)    /* problem exceeds the fixed scratch of a *_noalloc entry   */
 
 /* bits of the device status word */
 #define CFB200_ST_BAD_COEF 1       /* a Gaussian coefficient a_ik was not negative             */
@@ -129,6 +130,29 @@ int cfb200_framed_proj_bwd(const float* a_ik, const float* pos_ij, const float* 
                            const float* gz, const float* gvalues, float* ga, float* gW_dist,
                            float* gW_ang1, float* gW_ang2, float* gW_ang3, void* workspace,
                            int64_t workspace_bytes, void* stream);
+
+/* No counterpart in the reference (whose Functions allocate their temporaries with torch).
+ * Same computation, arguments and outputs as cfb200_framed_proj_bwd, for hosts that cannot
+ * provide a workspace: a plugin under a runtime that owns the device heap and passes only input
+ * and output buffers, or a service that forbids device allocation after start-up.  The scratch is
+ * a fixed device array of CFB200_NOALLOC_MAX_BYTES inside the library (held on every GPU the
+ * process uses it on, until exit); the call allocates nothing.
+ *  - Returns CFB200_E_TOO_LARGE when cfb200_framed_proj_bwd_workspace_bytes(N,E) exceeds
+ *    CFB200_NOALLOC_MAX_BYTES (about 340 000 pairs with 8 heads).
+ *  - The first call on each device looks up the array's device address (the device must be
+ *    current); make that first call before any stream capture.
+ *  - All calls share the one array: calls that may overlap on the GPU (different streams,
+ *    different host threads) race and must be serialised by the caller.  Nothing has to be
+ *    cleared between calls; the kernels overwrite what they later read. */
+#define CFB200_NOALLOC_MAX_BYTES (16 * 1024 * 1024)
+int cfb200_framed_proj_bwd_noalloc(const float* a_ik, const float* pos_ij, const float* tvecs,
+                                   const float* rvlen, const int64_t* batch, const int64_t* edges,
+                                   const int64_t* e_start, int64_t N, int64_t E, float dist_max,
+                                   float cutoff_radius, const float* W_dist, const float* W_ang1,
+                                   const float* W_ang2, const float* W_ang3, const float* frame1,
+                                   const float* frame2, const float* frame3, const float* z,
+                                   const float* gz, const float* gvalues, float* ga, float* gW_dist,
+                                   float* gW_ang1, float* gW_ang2, float* gW_ang3, void* stream);
 
 /* Replaces FusedDotProductAttentionCUDA.forward (models/cuda_funcs/fused_dpa.py:17-64;
  * kernel fused_dpa_fwd.cu).  q_scaled, k, v (N,H,head_dim); z (E,H) or NULL; values
