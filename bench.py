@@ -36,7 +36,7 @@ import torch
 METRIC = "crystals/sec train fwd+bwd (4-layer max-frame)"
 UNIT = "crystals/s"
 WORKLOAD = "cfg3: 4-layer max-frame training step, 256 crystals/GPU, lognormal sizes (median 8, 1..64), fp32"
-BATCH = 256
+BATCH = int(os.environ.get("CF_BENCH_BATCH", 256))   # 256 is the benchmark; other values are for diagnosis only
 # algorithmic work per unit: one (pair, head, translation) term and one (pair, head) projection
 FLOP_TERM_FWD, FLOP_TERM_BWD, SFU_TERM = 516.0, 738.0, 110.0
 FLOP_PROJ_FWD, FLOP_PROJ_BWD = 8192.0, 16384.0
@@ -276,6 +276,8 @@ def run_ours(args, rank, world, local_rank):
         opt.step()
         return loss
 
+    enqueue_ms = [0.0]
+
     def timed(n_steps, from_host):
         """Device time of n_steps back-to-back steps (CUDA events on the launching stream); with
         host buffers the host-visible wall time is taken when it is longer."""
@@ -290,6 +292,7 @@ def run_ours(args, rank, world, local_rank):
             if from_host:
                 loss.item()                                       # device-to-host read of the result
         e1.record()
+        enqueue_ms[0] = (time.perf_counter() - t0) * 1e3          # host time to enqueue the steps
         torch.cuda.synchronize()
         wall = (time.perf_counter() - t0) * 1e3
         return max(e0.elapsed_time(e1), wall) if from_host else e0.elapsed_time(e1)
@@ -304,6 +307,7 @@ def run_ours(args, rank, world, local_rank):
     with _lib.KernelTimer() as kt:
         barrier()
         ms = timed(args.steps, from_host=False)
+        host_ms = enqueue_ms[0]
         barrier()
         ktimes = kt.summary()
     launches = _lib.launch_count - launches0
@@ -351,7 +355,7 @@ def run_ours(args, rank, world, local_rank):
             "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": host[0].nbytes(), "d2h_bytes_per_step": 4},
             "gpu_launches": launches, "pair_sums_per_s": pair_sums, "roofline": roofline, "kernels": kern,
-            "clocks": clocks, "device_status": status}
+            "host_enqueue_ms_per_step": host_ms / args.steps, "clocks": clocks, "device_status": status}
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(args.cpu_crystals)
     print(json.dumps(line), flush=True)

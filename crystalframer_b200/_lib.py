@@ -10,7 +10,7 @@ import os
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libcfb200.so")
+LIB_PATH = os.environ.get("CFB200_LIB_PATH", os.path.join(HERE, "libcfb200.so"))
 
 _lib = None
 

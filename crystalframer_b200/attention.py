@@ -96,7 +96,13 @@ def gaussian_coefficients(q, lattice_pos_weights, gauss_scale, params, training)
         raise NotImplementedError(f"gauss_state={params.gauss_state}")
     alpha = (q.reshape(N, H, 1, hd) @ lattice_pos_weights.reshape(H, hd, 1)).view(N, H)
     if params.normalize_gauss:
-        if bool(gauss_scale[0] > 0):
+        # ``gauss_scale[0] > 0`` is a device-side fact; reading it every call would stall the host
+        # once per layer, so a positive answer is remembered on the tensor object.
+        ready = getattr(gauss_scale, "_cf_ready", False)
+        if not ready and bool(gauss_scale[0] > 0):
+            ready = True
+            gauss_scale._cf_ready = True
+        if ready:
             scale, shift = gauss_scale[0], gauss_scale[1]
         else:
             scale = torch.reciprocal(alpha.detach().std())
@@ -105,6 +111,7 @@ def gaussian_coefficients(q, lattice_pos_weights, gauss_scale, params, training)
                 with torch.no_grad():
                     gauss_scale[0] = scale
                     gauss_scale[1] = shift
+                gauss_scale._cf_ready = True
         alpha = (alpha + shift) * scale
     lb, beta = params.gauss_lb_real, params.positive_func_beta
     pos = (1.0 - lb) * F.elu(alpha * (beta / (1.0 - lb))) + 1.0

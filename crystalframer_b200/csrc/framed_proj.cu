@@ -2,10 +2,11 @@
 // backward (replaces real_enc_frame_proj_{fwd,bwd}_{length,angle}.cu of the reference).
 //
 // Work decomposition
-//   grid  = (resident blocks, heads); a block owns one head and walks chunks of 32 pairs.
+//   grid  = (resident blocks, heads); a block owns one head and a strided subset of the pairs,
+//           which it stages 32 at a time.
 //   warp  = one (pair, head) task at a time.  Lanes first evaluate 32 lattice translations in
 //           parallel (separation, weight w = exp(a (d^2 - d^2_min)), window positions), drop
-//           translations whose weight is below exp(-kPrune), and leave one record per surviving
+//           translations whose weight is below exp(-kPrune) of the largest, and leave one record per surviving
 //           translation in shared memory.  Then the warp walks the survivors: lane l owns basis
 //           indices l and l+32 of each of the four 64-wide Gaussian bases (distance, three frame
 //           axes) and keeps their running sums in registers, so the data-dependent window offset
@@ -28,7 +29,9 @@ constexpr int kFpSlots = kFpWarps * kFpTasksPerWarp;   // pairs per chunk (== 32
 constexpr int kFpK = 256;                              // 4 bases x 64
 constexpr int kFpStageStride = 260;                    // padded row: conflict-free 128-bit reads by 32 lanes
 constexpr int kHd = 16;                                // head dimension of this instance
-constexpr float kPrune = 30.0f;                        // drop translations with weight < e^-30
+// resident blocks per SM the kernels are compiled for (register budget): forward 3, backward 2
+__host__ __device__ constexpr int fp_blocks_per_sm(bool bwd) { return bwd ? 2 : 3; }
+constexpr float kPrune = 20.0f;                        // drop translations with weight < e^-20 (2e-9 of the normaliser)
 
 static_assert(kFpSlots == 32, "projection maps one lane to one staged pair");
 
@@ -47,17 +50,26 @@ struct FpArgs {
 constexpr size_t kFpSmemFloats = (size_t)kHd * kFpK + (size_t)kFpSlots * kFpStageStride + (size_t)kFpWarps * 2 * 32 * 4 + 16 * 33;
 constexpr size_t kFpSmemBytes = kFpSmemFloats * sizeof(float);
 
-// q = t / L, r = t % L for small non-negative t and L (float reciprocal plus one correction step)
-__device__ __forceinline__ void divmod_small(int t, int L, float invL, int& q, int& r)
+// q = t / L, r = t % L for 0 <= t < 2^20 and 1 <= L < 2^14: multiply-high by ceil(2^32 / L) plus
+// one correction step (integer pipe only; no int<->float conversion instructions)
+__device__ __forceinline__ void divmod_small(int t, int L, unsigned magic, int& q, int& r)
 {
-    q = __float2int_rz(__int2float_rn(t) * invL);
+    q = (int)__umulhi((unsigned)t, magic);
     r = t - q * L;
     if (r < 0) { q--; r += L; }
     else if (r >= L) { q++; r -= L; }
 }
 
+__device__ __forceinline__ unsigned div_magic(int L) { return (unsigned)(0xFFFFFFFFu / (unsigned)L) + 1u; }
+
+// exact float value of a small integer (|n| < 2^22) without a conversion instruction
+__device__ __forceinline__ float small_int_to_float(int n)
+{
+    return __int_as_float(0x4B400000 + n) - 12582912.0f;
+}
+
 template <bool BWD, bool ANG>
-__global__ void __launch_bounds__(kFpThreads, 2) framed_proj_kernel(const FpArgs A, const Params P)
+__global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj_kernel(const FpArgs A, const Params P)
 {
     extern __shared__ __align__(16) float smem[];
     float* W_s = smem;                                          // [16][256]
@@ -82,6 +94,10 @@ __global__ void __launch_bounds__(kFpThreads, 2) framed_proj_kernel(const FpArgs
     const float cd_lo = (float)(lane + 1) * dstep, cd_hi = (float)(lane + 33) * dstep;
     const float ca_lo = (float)(63 - lane) * astep, ca_hi = (float)(31 - lane) * astep;
     const unsigned win_d = (unsigned)P.win_dist, win_a = (unsigned)P.win_ang;
+    const float inv_d_interval = 1.0f / P.d_interval, d_cut_scaled = P.d_cut / P.d_interval;
+    const float xd_scale = dstep / P.d_interval;
+    const float inv_a_interval = P.angle_dim > 1 ? 1.0f / P.a_interval : 0.0f;
+    const float xa_scale = P.a_sigma_inv * kSqrtLog2e;
     const bool wide_d = P.win_dist > 32;
 
     float gacc[2][8];
@@ -92,11 +108,17 @@ __global__ void __launch_bounds__(kFpThreads, 2) framed_proj_kernel(const FpArgs
     float4* tb = tbuf + warp * 64;
     __syncthreads();
 
-    const int64_t nChunks = (A.E + kFpSlots - 1) / kFpSlots;
-    for (int64_t chunk = blockIdx.x; chunk < nChunks; chunk += gridDim.x) {
+    // Pair assignment: block b takes pairs b, b + G, b + 2G, ... (G = gridDim.x) and stages them 32
+    // at a time.  Every block therefore samples the whole batch evenly, which balances the very
+    // uneven per-pair cost (small cells keep hundreds of translations, large cells a dozen)
+    // without any dynamic scheduling -- the assignment, and with it every sum, stays deterministic.
+    const int64_t G = gridDim.x;
+    const int64_t myPairs = A.E > (int64_t)blockIdx.x ? (A.E - blockIdx.x + G - 1) / G : 0;
+    const int64_t nChunks = (myPairs + kFpSlots - 1) / kFpSlots;
+    for (int64_t chunk = 0; chunk < nChunks; chunk++) {
         for (int tsk = 0; tsk < kFpTasksPerWarp; tsk++) {
             const int slot = tsk * kFpWarps + warp;
-            const int64_t e = chunk * kFpSlots + slot;
+            const int64_t e = (chunk * kFpSlots + slot) * G + blockIdx.x;
             float* srow = stage + slot * kFpStageStride;
             if (e >= A.E) {
 #pragma unroll
@@ -117,7 +139,7 @@ __global__ void __launch_bounds__(kFpThreads, 2) framed_proj_kernel(const FpArgs
             const int R1 = __shfl_sync(0xffffffffu, Rl, 0), R2 = __shfl_sync(0xffffffffu, Rl, 1), R3 = __shfl_sync(0xffffffffu, Rl, 2);
             const int L2 = 2 * R2 + 1, L3 = 2 * R3 + 1, L23 = L2 * L3;
             const int Ttot = (2 * R1 + 1) * L23;
-            const float invL23 = 1.0f / (float)L23, invL3 = 1.0f / (float)L3;
+            const unsigned invL23 = div_magic(L23), invL3 = div_magic(L3);
             float fx[3], fy[3], fz[3];
             if (ANG) {
 #pragma unroll
@@ -138,7 +160,7 @@ __global__ void __launch_bounds__(kFpThreads, 2) framed_proj_kernel(const FpArgs
                         int q1, r1, q2, r2;
                         divmod_small(t, L23, invL23, q1, r1);
                         divmod_small(r1, L3, invL3, q2, r2);
-                        const float n1 = (float)(q1 - R1), n2 = (float)(q2 - R2), n3 = (float)(r2 - R3);
+                        const float n1 = small_int_to_float(q1 - R1), n2 = small_int_to_float(q2 - R2), n3 = small_int_to_float(r2 - R3);
                         const float dx = fmaf(t3x, n3, fmaf(t2x, n2, fmaf(t1x, n1, rx)));
                         const float dy = fmaf(t3y, n3, fmaf(t2y, n2, fmaf(t1y, n1, ry)));
                         const float dz = fmaf(t3z, n3, fmaf(t2z, n2, fmaf(t1z, n1, rz)));
@@ -159,7 +181,7 @@ __global__ void __launch_bounds__(kFpThreads, 2) framed_proj_kernel(const FpArgs
                     int q1, r1, q2, r2;
                     divmod_small(t, L23, invL23, q1, r1);
                     divmod_small(r1, L3, invL3, q2, r2);
-                    const float n1 = (float)(q1 - R1), n2 = (float)(q2 - R2), n3 = (float)(r2 - R3);
+                    const float n1 = small_int_to_float(q1 - R1), n2 = small_int_to_float(q2 - R2), n3 = small_int_to_float(r2 - R3);
                     const float dx = fmaf(t3x, n3, fmaf(t2x, n2, fmaf(t1x, n1, rx)));
                     const float dy = fmaf(t3y, n3, fmaf(t2y, n2, fmaf(t1y, n1, ry)));
                     const float dz = fmaf(t3z, n3, fmaf(t2z, n2, fmaf(t1z, n1, rz)));
@@ -170,29 +192,34 @@ __global__ void __launch_bounds__(kFpThreads, 2) framed_proj_kernel(const FpArgs
                     if (BWD) px_l = fmaf(w, d2, px_l);
                     keep = arg > -kPrune;
                     if (keep) {
-                        const float d = __fsqrt_rn(d2);
+                        // d and 1/d from one reciprocal square root plus a Newton step; quotients by
+                        // the basis spacings become products with their reciprocals.  These differ
+                        // from the reference's IEEE sqrt / divisions in the last bit only.
+                        float rinv = rsqrtf(fmaxf(d2, 1e-30f));
+                        rinv = rinv * fmaf(-0.5f * d2 * rinv, rinv, 1.5f);
+                        const float d = d2 * rinv;
                         int lo_d = 0;
                         if (P.windowed_dist) {
-                            lo_d = (int)(__fdiv_rn(d - P.d_cut, P.d_interval) - 1.0f);
+                            lo_d = (int)(fmaf(d, inv_d_interval, -d_cut_scaled) - 1.0f);
                             lo_d = min(max(lo_d, 0), 64 - P.win_dist);
                         }
-                        const float xd = __fdiv_rn(-d, P.d_interval) * dstep;
+                        const float xd = -d * xd_scale;
                         float xa[3] = {0.f, 0.f, 0.f};
                         int lo_pack = lo_d;
                         if (ANG) {
 #pragma unroll
                             for (int x = 0; x < 3; x++) {
                                 float cosv = 1e3f;
-                                if (d2 > 1e-5f) cosv = __fdiv_rn(fmaf(dz, fz[x], fmaf(dy, fy[x], dx * fx[x])), d);
+                                if (d2 > 1e-5f) cosv = fmaf(dz, fz[x], fmaf(dy, fy[x], dx * fx[x])) * rinv;
                                 if (P.cos_abs) cosv = fabsf(cosv);
                                 int lo = 0;
                                 if (P.windowed_ang) {
-                                    float en = __fdiv_rn(cosv + 1.0f + P.a_cut, P.a_interval) + 1.0f;
+                                    const float en = fmaf(cosv + 1.0f + P.a_cut, inv_a_interval, 1.0f);
                                     int end = (int)fminf(en, 64.0f);
                                     end = max(end, P.win_ang);
                                     lo = end - P.win_ang;
                                 }
-                                xa[x] = (1.0f - cosv) * (P.a_sigma_inv * kSqrtLog2e);
+                                xa[x] = (1.0f - cosv) * xa_scale;
                                 lo_pack |= lo << (8 * (x + 1));
                             }
                         }
@@ -209,7 +236,7 @@ __global__ void __launch_bounds__(kFpThreads, 2) framed_proj_kernel(const FpArgs
                     const float w = r0.x, d2 = r1.z;
                     const int lo_pack = __float_as_int(r1.y);
                     {   // distance basis
-                        const int lo = lo_pack & 255;
+                        const int lo = (int)__byte_perm((unsigned)lo_pack, 0u, 0x4440);
                         const bool in0 = (unsigned)(lane - lo) < win_d, in1 = (unsigned)(lane + 32 - lo) < win_d;
                         if (!wide_d) {
                             const float b = r0.y + (in1 ? cd_hi : cd_lo);
@@ -227,7 +254,7 @@ __global__ void __launch_bounds__(kFpThreads, 2) framed_proj_kernel(const FpArgs
                         const float xa[3] = {r0.z, r0.w, r1.x};
 #pragma unroll
                         for (int x = 0; x < 3; x++) {
-                            const int lo = (lo_pack >> (8 * (x + 1))) & 255;
+                            const int lo = (int)__byte_perm((unsigned)lo_pack, 0u, 0x4441 + x);
                             const float b0 = xa[x] - ca_lo, b1 = xa[x] - ca_hi;
                             const float g0 = ex2_approx(-b0 * b0) * w, g1 = ex2_approx(-b1 * b1) * w;
                             if ((unsigned)(lane - lo) < win_a) { sa[x][0] += g0; if (BWD) qa[x][0] = fmaf(g0, d2, qa[x][0]); }
@@ -311,7 +338,7 @@ __global__ void __launch_bounds__(kFpThreads, 2) framed_proj_kernel(const FpArgs
                 side[(2 * warp + 1) * 33 + lane] = acc1;
                 __syncthreads();
                 const int p = threadIdx.x >> 3, q = threadIdx.x & 7;
-                const int64_t e = chunk * kFpSlots + p;
+                const int64_t e = (chunk * kFpSlots + p) * G + blockIdx.x;
                 if (e < A.E) {
                     float2 v = make_float2(side[(2 * q) * 33 + p], side[(2 * q + 1) * 33 + p]);
                     *reinterpret_cast<float2*>(A.values + (e * H + h) * kHd + 2 * q) = v;
@@ -369,16 +396,15 @@ __global__ void reduce_gw_kernel(const float* __restrict__ part, int nPart, int 
 }
 
 // Resident blocks along x: the kernel is persistent (each block strides over the chunks), so the
-// grid is one wave of kFpBlocksPerSm blocks per SM, split evenly between the heads.
-constexpr int kFpBlocksPerSm = 2;
+// grid is one wave of fp_blocks_per_sm() blocks per SM, split evenly between the heads.
 
-static int grid_x_for(int64_t E, int H)
+static int grid_x_for(int64_t E, int H, bool bwd)
 {
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int64_t chunks = (E + kFpSlots - 1) / kFpSlots;
-    int64_t want = ((int64_t)sms * kFpBlocksPerSm) / H;
+    int64_t want = ((int64_t)sms * fp_blocks_per_sm(bwd)) / H;
     if (want < 1) want = 1;
     if (chunks < want) want = chunks < 1 ? 1 : chunks;
     return (int)want;
@@ -387,7 +413,7 @@ static int grid_x_for(int64_t E, int H)
 int64_t framed_proj_bwd_workspace_bytes(int64_t N, int64_t E, int H)
 {
     (void)N;
-    const int gx = grid_x_for(E, H);
+    const int gx = grid_x_for(E, H, true);
     size_t ga_e = ((size_t)E * H * sizeof(float) + 255) / 256 * 256;
     return (int64_t)(ga_e + (size_t)gx * H * kHd * kFpK * sizeof(float));
 }
@@ -411,7 +437,7 @@ static int launch_fp(const FpArgs& A, const Params& P, int gx, cudaStream_t st)
 int framed_proj_fwd(const FpArgs& A, const Params& P, cudaStream_t st)
 {
     if (A.E == 0) return CFB200_OK;
-    const int gx = grid_x_for(A.E, P.H);
+    const int gx = grid_x_for(A.E, P.H, false);
     return A.W[1] != nullptr ? launch_fp<false, true>(A, P, gx, st) : launch_fp<false, false>(A, P, gx, st);
 }
 
@@ -419,7 +445,7 @@ int framed_proj_bwd(FpArgs A, const Params& P, const int64_t* e_start, float* ga
                     int64_t ws_bytes, cudaStream_t st)
 {
     if (ws_bytes < framed_proj_bwd_workspace_bytes(A.N, A.E, P.H) || ws == nullptr) return CFB200_E_WORKSPACE;
-    const int gx = grid_x_for(A.E, P.H);
+    const int gx = grid_x_for(A.E, P.H, true);
     size_t ga_e_bytes = ((size_t)A.E * P.H * sizeof(float) + 255) / 256 * 256;
     A.ga_e = reinterpret_cast<float*>(ws);
     A.gW_part = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + ga_e_bytes);

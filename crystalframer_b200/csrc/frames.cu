@@ -4,17 +4,26 @@
 // models/cuda_funcs/calc_maximum_frame.py and the torch ops of
 // models/indexed_lattice_multi_head_attention_cuda.py:475-481 of the reference).
 //
-// One warp owns one (atom i, head h); lanes own the atom's pairs (i, j).  All pairs of one
-// (atom, head) share the lattice range, so the translation loops are uniform across the warp.
-// Per pair a lane finds its candidate image and score; a warp arg-max (lowest pair index on
-// ties) picks the atom's axis.  Every float operation that feeds a comparison is written with
-// explicit round-to-nearest intrinsics in the reference's evaluation order (no fused
-// multiply-add), so that the selected pair and image can be reproduced bit for bit on a CPU.
+// grid = (groups of kFrRows query atoms, heads).  The pairs of a group's atoms are contiguous
+// in the pair list, so the block's threads walk them one pair per thread regardless of crystal
+// size (small crystals do not leave lanes idle).  Each thread sweeps the lattice translations of
+// its pair, finds the pair's candidate image and score, and folds (score, pair index) into its
+// query atom's slot in shared memory with one 64-bit atomicMax -- an order-independent arg-max
+// with "lowest pair index wins" on equal scores.  One thread per atom then recomputes the
+// winning pair's candidate to recover its direction and image index.
+//
+// Every float operation that feeds a comparison is written with explicit round-to-nearest
+// intrinsics in the reference's evaluation order (no fused multiply-add), so the selected pair
+// and image can be reproduced bit for bit on a CPU.  Two exact short-cuts skip work that cannot
+// change the result: the symmetry-breaking noise is only drawn when the image could still win,
+// and the second axis' sqrt / divisions / logf are skipped when the Gaussian part of the score
+// alone is already below the running maximum (the logarithm term is never positive).
 #include "common.cuh"
 
 namespace cfb {
 
-constexpr int kFrWarps = 4;
+constexpr int kFrRows = 16;
+constexpr int kFrThreads = 256;
 constexpr int kFrHd = 16;
 
 struct FrArgs {
@@ -41,180 +50,212 @@ __device__ __forceinline__ void separation(const Cell& c, float n1, float n2, fl
 
 __device__ __forceinline__ float noise_term(float amp, uint64_t seed, uint64_t tid, uint32_t t)
 {
-    if (amp == 0.0f) return 0.0f;
     return (float)(((double)hash_uniform(seed, tid, t) - 0.5) * (double)amp);
 }
 
-struct Cand { float score; int64_t e; float ux, uy, uz; int img; };
+struct Cand { float value; float ux, uy, uz; int img; };
 
-// warp arg-max by (score desc, pair index asc); candidates with e < 0 never win
-__device__ __forceinline__ Cand warp_argmax(Cand c)
+// nearest image with d^2 > 1e-5 (compute_maximum_frame_each_edge.cu:81-111)
+__device__ __forceinline__ Cand first_axis_candidate(const Cell& cell, float a, int R1, int R2, int R3, float amp,
+                                                     uint64_t seed, uint64_t tid)
 {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float s = __shfl_xor_sync(0xffffffffu, c.score, o);
-        const long long e = __shfl_xor_sync(0xffffffffu, (long long)c.e, o);
-        const float ux = __shfl_xor_sync(0xffffffffu, c.ux, o), uy = __shfl_xor_sync(0xffffffffu, c.uy, o),
-                    uz = __shfl_xor_sync(0xffffffffu, c.uz, o);
-        const int img = __shfl_xor_sync(0xffffffffu, c.img, o);
-        const bool take = e >= 0 && (c.e < 0 || s > c.score || (s == c.score && e < (long long)c.e));
-        if (take) { c.score = s; c.e = e; c.ux = ux; c.uy = uy; c.uz = uz; c.img = img; }
-    }
+    Cand c; c.ux = c.uy = c.uz = 0.f; c.img = -1;
+    float d2_min = 1e10f;
+    const float half = 0.5f * amp;
+    int t = 0;
+    for (int n1 = -R1; n1 <= R1; n1++)
+        for (int n2 = -R2; n2 <= R2; n2++)
+            for (int n3 = -R3; n3 <= R3; n3++, t++) {
+                float dx, dy, dz, d2;
+                separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
+                if ((double)d2 > 1e-5 && __fadd_rn(d2, -half) < d2_min) {
+                    const float cand = amp == 0.0f ? d2 : __fadd_rn(d2, noise_term(amp, seed, tid, (uint32_t)t));
+                    if (d2_min > cand) {
+                        d2_min = cand;
+                        const float d = __fsqrt_rn(d2);
+                        c.ux = __fdiv_rn(dx, d); c.uy = __fdiv_rn(dy, d); c.uz = __fdiv_rn(dz, d);
+                        c.img = t;
+                    }
+                }
+            }
+    c.value = __fmul_rn(a, d2_min);
     return c;
 }
 
-__global__ void __launch_bounds__(kFrWarps * 32) max_frame_kernel(const FrArgs A, const Params P)
+// second axis (compute_second_frame_each_edge.cu:81-142)
+__device__ __forceinline__ Cand second_axis_candidate(const Cell& cell, float a, int R1, int R2, int R3, float amp,
+                                                      uint64_t seed, uint64_t tid, float f1x, float f1y, float f1z)
 {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t task = (int64_t)blockIdx.x * kFrWarps + warp;
-    const int H = P.H;
-    if (task >= A.N * H) return;
-    const int64_t i = task / H;
-    const int h = (int)(task - i * H);
-    const int64_t c = A.batch[i];
-    const int64_t e0 = A.e_start[i], e1 = A.e_start[i + 1];
-    const float a = __ldg(A.a_ik + i * H + h);
-    int Rl = 0;
-    if (lane < 3) Rl = lattice_range_1d(P, a, P.cutoff_radius != 0.0f ? __ldg(A.rvlen + 3 * c + lane) : 0.0f);
-    const int R1 = __shfl_sync(0xffffffffu, Rl, 0), R2 = __shfl_sync(0xffffffffu, Rl, 1), R3 = __shfl_sync(0xffffffffu, Rl, 2);
-    Cell cell;
-    {
-        const float* Tc = A.tvecs + 9 * c;
-        cell.t1x = __ldg(Tc); cell.t1y = __ldg(Tc + 1); cell.t1z = __ldg(Tc + 2);
-        cell.t2x = __ldg(Tc + 3); cell.t2y = __ldg(Tc + 4); cell.t2z = __ldg(Tc + 5);
-        cell.t3x = __ldg(Tc + 6); cell.t3y = __ldg(Tc + 7); cell.t3z = __ldg(Tc + 8);
-    }
-    float qv[kFrHd];
-    {
-        const float4* q4 = reinterpret_cast<const float4*>(A.q + (i * H + h) * kFrHd);
-#pragma unroll
-        for (int d4 = 0; d4 < kFrHd / 4; d4++) {
-            const float4 v = __ldg(q4 + d4);
-            qv[4 * d4] = v.x; qv[4 * d4 + 1] = v.y; qv[4 * d4 + 2] = v.z; qv[4 * d4 + 3] = v.w;
+    Cand c; c.ux = c.uy = c.uz = 0.f; c.img = -1; c.value = -1e15f;
+    float d2min = 1e10f;
+    for (int n1 = -R1; n1 <= R1; n1++)
+        for (int n2 = -R2; n2 <= R2; n2++)
+            for (int n3 = -R3; n3 <= R3; n3++) {
+                float dx, dy, dz, d2;
+                separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
+                if ((double)d2 > 1e-5) d2min = fminf(d2min, d2);
+            }
+    float max_val = -1e15f;
+    const float half = 0.5f * amp;
+    int t = 0;
+    for (int n1 = -R1; n1 <= R1; n1++)
+        for (int n2 = -R2; n2 <= R2; n2++)
+            for (int n3 = -R3; n3 <= R3; n3++, t++) {
+                float dx, dy, dz, d2;
+                separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
+                if (!((double)d2 > 1e-5)) continue;
+                const float gauss = __fmul_rn(a, __fsub_rn(d2, d2min));
+                if (gauss <= __fadd_rn(max_val, -half)) continue;      // score <= gauss cannot exceed the maximum
+                const float d = __fsqrt_rn(d2);
+                const float vx = __fdiv_rn(dx, d), vy = __fdiv_rn(dy, d), vz = __fdiv_rn(dz, d);
+                const float cs = __fadd_rn(__fadd_rn(__fmul_rn(vx, f1x), __fmul_rn(vy, f1y)), __fmul_rn(vz, f1z));
+                const float one_m = __fsub_rn(1.0f, fabsf(cs));
+                const float clipped = ((double)one_m > 1e-5) ? one_m : 1e-5f;
+                const float score = __fadd_rn(gauss, logf(clipped));
+                const float nz = amp == 0.0f ? 0.0f : noise_term(amp, seed, tid, (uint32_t)t);
+                if (score > __fadd_rn(max_val, nz) && (double)fabsf(cs) < 0.9999) {
+                    max_val = __fadd_rn(score, nz);
+                    c.ux = vx; c.uy = vy; c.uz = vz;
+                    c.value = __fadd_rn(score, __fmul_rn(a, d2min));
+                    c.img = t;
+                }
+            }
+    return c;
+}
+
+// (score, pair) -> 64-bit key whose unsigned order is (score ascending, pair index descending)
+__device__ __forceinline__ unsigned long long make_key(float score, unsigned local_pair)
+{
+    unsigned u = __float_as_uint(score);
+    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    return ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - local_pair);
+}
+
+__global__ void __launch_bounds__(kFrThreads, 2) max_frame_kernel(const FrArgs A, const Params P)
+{
+    __shared__ unsigned long long best[kFrRows];
+    __shared__ long long row_start[kFrRows + 1];
+    __shared__ float row_a[kFrRows];
+    __shared__ int row_R[kFrRows][3];
+    __shared__ float row_f1[kFrRows][3];
+
+    const int H = P.H, h = blockIdx.y, tid = threadIdx.x;
+    const int64_t i0 = (int64_t)blockIdx.x * kFrRows;
+    const int rows = (int)min((int64_t)kFrRows, A.N - i0);
+    if (tid <= rows) row_start[tid] = A.e_start[i0 + tid];
+    if (tid < rows) {
+        const int64_t i = i0 + tid;
+        const float a = __ldg(A.a_ik + i * H + h);
+        row_a[tid] = a;
+        const int64_t c = A.batch[i];
+        for (int d = 0; d < 3; d++)
+            row_R[tid][d] = lattice_range_1d(P, a, P.cutoff_radius != 0.0f ? __ldg(A.rvlen + 3 * c + d) : 0.0f);
+        if (A.mode == 2) {
+            const float* f = A.frame1_in + (i * H + h) * 3;
+            row_f1[tid][0] = __ldg(f); row_f1[tid][1] = __ldg(f + 1); row_f1[tid][2] = __ldg(f + 2);
         }
     }
-
-    float f1x = 0.f, f1y = 0.f, f1z = 0.f;
-    if (A.mode == 2) {
-        const float* f = A.frame1_in + (i * H + h) * 3;
-        f1x = __ldg(f); f1y = __ldg(f + 1); f1z = __ldg(f + 2);
-    }
+    __syncthreads();
+    const int64_t eb = row_start[0], ee = row_start[rows];
+    const unsigned long long none = make_key(-1e10f, 0u);      // a score must exceed -1e10 to be selected
 
     for (int axis = (A.mode == 2 ? 2 : 1); axis <= (A.mode == 1 ? 1 : 2); axis++) {
-        Cand best; best.score = -1e10f; best.e = -1; best.ux = best.uy = best.uz = 0.f; best.img = -1;
-        for (int64_t eb = e0; eb < e1; eb += 32) {
-            const int64_t e = eb + lane;
-            if (e < e1) {
-                const int64_t j = A.edges[A.E + e];
-                cell.rx = __ldg(A.pos_ij + 3 * e); cell.ry = __ldg(A.pos_ij + 3 * e + 1); cell.rz = __ldg(A.pos_ij + 3 * e + 2);
-                float dot = 0.f;
-                const float4* k4 = reinterpret_cast<const float4*>(A.k + (j * H + h) * kFrHd);
+        if (tid < rows) best[tid] = none;
+        __syncthreads();
+        // ---- every pair of the group: candidate image, score, arg-max per query atom ----
+        for (int64_t e = eb + tid; e < ee; e += kFrThreads) {
+            int r = 0;
 #pragma unroll
-                for (int d4 = 0; d4 < kFrHd / 4; d4++) {
-                    const float4 v = __ldg(k4 + d4);
-                    dot = __fmaf_rn(qv[4 * d4], v.x, dot); dot = __fmaf_rn(qv[4 * d4 + 1], v.y, dot);
-                    dot = __fmaf_rn(qv[4 * d4 + 2], v.z, dot); dot = __fmaf_rn(qv[4 * d4 + 3], v.w, dot);
-                }
-                const uint64_t tid = (uint64_t)(e * H + h);
-                float ux = 0.f, uy = 0.f, uz = 0.f, value;
-                int img = -1;
-                if (axis == 1) {
-                    // nearest image with d^2 > 1e-5 (compute_maximum_frame_each_edge.cu:81-111)
-                    float d2_min = 1e10f;
-                    int t = 0;
-                    for (int n1 = -R1; n1 <= R1; n1++)
-                        for (int n2 = -R2; n2 <= R2; n2++)
-                            for (int n3 = -R3; n3 <= R3; n3++, t++) {
-                                float dx, dy, dz, d2;
-                                separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
-                                if ((double)d2 > 1e-5) {
-                                    const float cand = __fadd_rn(d2, noise_term(P.noise, A.seed1, tid, (uint32_t)t));
-                                    if (d2_min > cand) {
-                                        d2_min = cand;
-                                        const float d = __fsqrt_rn(d2);
-                                        ux = __fdiv_rn(dx, d); uy = __fdiv_rn(dy, d); uz = __fdiv_rn(dz, d);
-                                        img = t;
-                                    }
-                                }
-                            }
-                    value = __fmul_rn(a, d2_min);
-                } else {
-                    // second axis (compute_second_frame_each_edge.cu:81-142)
-                    float d2min = 1e10f;
-                    for (int n1 = -R1; n1 <= R1; n1++)
-                        for (int n2 = -R2; n2 <= R2; n2++)
-                            for (int n3 = -R3; n3 <= R3; n3++) {
-                                float dx, dy, dz, d2;
-                                separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
-                                if ((double)d2 > 1e-5) d2min = fminf(d2min, d2);
-                            }
-                    float max_val = -1e15f;
-                    value = -1e15f;
-                    int t = 0;
-                    for (int n1 = -R1; n1 <= R1; n1++)
-                        for (int n2 = -R2; n2 <= R2; n2++)
-                            for (int n3 = -R3; n3 <= R3; n3++, t++) {
-                                float dx, dy, dz, d2;
-                                separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
-                                if ((double)d2 > 1e-5) {
-                                    const float d = __fsqrt_rn(d2);
-                                    const float vx = __fdiv_rn(dx, d), vy = __fdiv_rn(dy, d), vz = __fdiv_rn(dz, d);
-                                    const float cs = __fadd_rn(__fadd_rn(__fmul_rn(vx, f1x), __fmul_rn(vy, f1y)), __fmul_rn(vz, f1z));
-                                    const float one_m = __fsub_rn(1.0f, fabsf(cs));
-                                    const float clipped = ((double)one_m > 1e-5) ? one_m : 1e-5f;
-                                    const float score = __fadd_rn(__fmul_rn(a, __fsub_rn(d2, d2min)), logf(clipped));
-                                    const float nz = noise_term(P.noise, A.seed2, tid, (uint32_t)t);
-                                    if (score > __fadd_rn(max_val, nz) && (double)fabsf(cs) < 0.9999) {
-                                        max_val = __fadd_rn(score, nz);
-                                        ux = vx; uy = vy; uz = vz;
-                                        value = __fadd_rn(score, __fmul_rn(a, d2min));
-                                        img = t;
-                                    }
-                                }
-                            }
-                }
-                const float s = __fadd_rn(dot, value);
-                if (s > best.score) { best.score = s; best.e = e; best.ux = ux; best.uy = uy; best.uz = uz; best.img = img; }
+            for (int s = kFrRows / 2; s > 0; s >>= 1)
+                if (r + s < rows && row_start[r + s] <= e) r += s;
+            const int64_t i = i0 + r;
+            const int64_t j = A.edges[A.E + e];
+            const int64_t c = A.batch[i];
+            Cell cell;
+            const float* Tc = A.tvecs + 9 * c;
+            cell.t1x = __ldg(Tc); cell.t1y = __ldg(Tc + 1); cell.t1z = __ldg(Tc + 2);
+            cell.t2x = __ldg(Tc + 3); cell.t2y = __ldg(Tc + 4); cell.t2z = __ldg(Tc + 5);
+            cell.t3x = __ldg(Tc + 6); cell.t3y = __ldg(Tc + 7); cell.t3z = __ldg(Tc + 8);
+            cell.rx = __ldg(A.pos_ij + 3 * e); cell.ry = __ldg(A.pos_ij + 3 * e + 1); cell.rz = __ldg(A.pos_ij + 3 * e + 2);
+            float dot = 0.f;
+            const float4* q4 = reinterpret_cast<const float4*>(A.q + (i * H + h) * kFrHd);
+            const float4* k4 = reinterpret_cast<const float4*>(A.k + (j * H + h) * kFrHd);
+#pragma unroll
+            for (int d4 = 0; d4 < kFrHd / 4; d4++) {
+                const float4 u = __ldg(q4 + d4), v = __ldg(k4 + d4);
+                dot = __fmaf_rn(u.x, v.x, dot); dot = __fmaf_rn(u.y, v.y, dot);
+                dot = __fmaf_rn(u.z, v.z, dot); dot = __fmaf_rn(u.w, v.w, dot);
             }
+            const uint64_t noise_id = (uint64_t)(e * H + h);
+            const Cand cd = axis == 1
+                ? first_axis_candidate(cell, row_a[r], row_R[r][0], row_R[r][1], row_R[r][2], P.noise, A.seed1, noise_id)
+                : second_axis_candidate(cell, row_a[r], row_R[r][0], row_R[r][1], row_R[r][2], P.noise, A.seed2, noise_id,
+                                        row_f1[r][0], row_f1[r][1], row_f1[r][2]);
+            const float s = __fadd_rn(dot, cd.value);
+            if (s > -1e10f) atomicMax(&best[r], make_key(s, (unsigned)(e - row_start[r])));
         }
-        best = warp_argmax(best);
-        if (axis == 1) {
-            f1x = best.ux; f1y = best.uy; f1z = best.uz;
-            if (A.mode != 2 && lane == 0) {
-                float* o = A.frame1 + (i * H + h) * 3;
-                o[0] = f1x; o[1] = f1y; o[2] = f1z;
-                if (A.mode == 1 && A.sel_edge) A.sel_edge[i * H + h] = best.e;
-                if (A.mode == 1 && A.sel_image) A.sel_image[i * H + h] = best.img;
+        __syncthreads();
+        // ---- one thread per query atom: recover the winner's direction and image ----
+        if (tid < rows) {
+            const int64_t i = i0 + tid;
+            const unsigned long long key = best[tid];
+            Cand cd; cd.ux = cd.uy = cd.uz = 0.f; cd.img = -1; cd.value = 0.f;
+            int64_t e_win = -1;
+            if (key != none) {
+                e_win = row_start[tid] + (int64_t)(0xFFFFFFFFu - (unsigned)(key & 0xFFFFFFFFull));
+                const int64_t c = A.batch[i];
+                Cell cell;
+                const float* Tc = A.tvecs + 9 * c;
+                cell.t1x = __ldg(Tc); cell.t1y = __ldg(Tc + 1); cell.t1z = __ldg(Tc + 2);
+                cell.t2x = __ldg(Tc + 3); cell.t2y = __ldg(Tc + 4); cell.t2z = __ldg(Tc + 5);
+                cell.t3x = __ldg(Tc + 6); cell.t3y = __ldg(Tc + 7); cell.t3z = __ldg(Tc + 8);
+                cell.rx = __ldg(A.pos_ij + 3 * e_win); cell.ry = __ldg(A.pos_ij + 3 * e_win + 1); cell.rz = __ldg(A.pos_ij + 3 * e_win + 2);
+                const uint64_t noise_id = (uint64_t)(e_win * H + h);
+                cd = axis == 1
+                    ? first_axis_candidate(cell, row_a[tid], row_R[tid][0], row_R[tid][1], row_R[tid][2], P.noise, A.seed1, noise_id)
+                    : second_axis_candidate(cell, row_a[tid], row_R[tid][0], row_R[tid][1], row_R[tid][2], P.noise, A.seed2,
+                                            noise_id, row_f1[tid][0], row_f1[tid][1], row_f1[tid][2]);
             }
-        } else if (lane == 0) {
-            float* o2 = A.frame2 + (i * H + h) * 3;
-            if (A.mode == 2) {
-                o2[0] = best.ux; o2[1] = best.uy; o2[2] = best.uz;
-                if (A.sel_edge) A.sel_edge[i * H + h] = best.e;
-                if (A.sel_image) A.sel_image[i * H + h] = best.img;
+            if (axis == 1) {
+                row_f1[tid][0] = cd.ux; row_f1[tid][1] = cd.uy; row_f1[tid][2] = cd.uz;
+                if (A.mode != 2) {
+                    float* o = A.frame1 + (i * H + h) * 3;
+                    o[0] = cd.ux; o[1] = cd.uy; o[2] = cd.uz;
+                }
+                if (A.mode == 1 && A.sel_edge) A.sel_edge[i * H + h] = e_win;
+                if (A.mode == 1 && A.sel_image) A.sel_image[i * H + h] = cd.img;
             } else {
-                // Gram-Schmidt, normalisation with max(norm, 1e-12), cross product
-                const float dot = __fadd_rn(__fadd_rn(__fmul_rn(f1x, best.ux), __fmul_rn(f1y, best.uy)), __fmul_rn(f1z, best.uz));
-                const float wx = __fsub_rn(best.ux, __fmul_rn(dot, f1x)), wy = __fsub_rn(best.uy, __fmul_rn(dot, f1y)),
-                            wz = __fsub_rn(best.uz, __fmul_rn(dot, f1z));
-                float nrm = __fsqrt_rn(__fadd_rn(__fadd_rn(__fmul_rn(wx, wx), __fmul_rn(wy, wy)), __fmul_rn(wz, wz)));
-                nrm = fmaxf(nrm, 1e-12f);
-                const float gx = __fdiv_rn(wx, nrm), gy = __fdiv_rn(wy, nrm), gz = __fdiv_rn(wz, nrm);
-                o2[0] = gx; o2[1] = gy; o2[2] = gz;
-                float* o3 = A.frame3 + (i * H + h) * 3;
-                o3[0] = __fsub_rn(__fmul_rn(f1y, gz), __fmul_rn(f1z, gy));
-                o3[1] = __fsub_rn(__fmul_rn(f1z, gx), __fmul_rn(f1x, gz));
-                o3[2] = __fsub_rn(__fmul_rn(f1x, gy), __fmul_rn(f1y, gx));
+                float* o2 = A.frame2 + (i * H + h) * 3;
+                if (A.mode == 2) {
+                    o2[0] = cd.ux; o2[1] = cd.uy; o2[2] = cd.uz;
+                    if (A.sel_edge) A.sel_edge[i * H + h] = e_win;
+                    if (A.sel_image) A.sel_image[i * H + h] = cd.img;
+                } else {
+                    // Gram-Schmidt, normalisation with max(norm, 1e-12), cross product
+                    const float f1x = row_f1[tid][0], f1y = row_f1[tid][1], f1z = row_f1[tid][2];
+                    const float dot = __fadd_rn(__fadd_rn(__fmul_rn(f1x, cd.ux), __fmul_rn(f1y, cd.uy)), __fmul_rn(f1z, cd.uz));
+                    const float wx = __fsub_rn(cd.ux, __fmul_rn(dot, f1x)), wy = __fsub_rn(cd.uy, __fmul_rn(dot, f1y)),
+                                wz = __fsub_rn(cd.uz, __fmul_rn(dot, f1z));
+                    float nrm = __fsqrt_rn(__fadd_rn(__fadd_rn(__fmul_rn(wx, wx), __fmul_rn(wy, wy)), __fmul_rn(wz, wz)));
+                    nrm = fmaxf(nrm, 1e-12f);
+                    const float gx = __fdiv_rn(wx, nrm), gy = __fdiv_rn(wy, nrm), gz = __fdiv_rn(wz, nrm);
+                    o2[0] = gx; o2[1] = gy; o2[2] = gz;
+                    float* o3 = A.frame3 + (i * H + h) * 3;
+                    o3[0] = __fsub_rn(__fmul_rn(f1y, gz), __fmul_rn(f1z, gy));
+                    o3[1] = __fsub_rn(__fmul_rn(f1z, gx), __fmul_rn(f1x, gz));
+                    o3[2] = __fsub_rn(__fmul_rn(f1x, gy), __fmul_rn(f1y, gx));
+                }
             }
         }
+        __syncthreads();
     }
 }
 
 int max_frame(const FrArgs& A, const Params& P, cudaStream_t st)
 {
-    const int64_t tasks = A.N * P.H;
-    if (tasks == 0) return CFB200_OK;
-    max_frame_kernel<<<(unsigned)((tasks + kFrWarps - 1) / kFrWarps), kFrWarps * 32, 0, st>>>(A, P);
+    if (A.N == 0) return CFB200_OK;
+    const unsigned gx = (unsigned)((A.N + kFrRows - 1) / kFrRows);
+    max_frame_kernel<<<dim3(gx, P.H), kFrThreads, 0, st>>>(A, P);
     return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
 }
 
