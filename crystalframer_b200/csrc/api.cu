@@ -1,6 +1,7 @@
 // C ABI of libcfb200: argument checks, hyper-parameter binding and kernel launches.
 // The library is one translation unit; the kernel files are included below.
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 #include "common.cuh"
 #include "framed_proj.cu"
@@ -39,6 +40,9 @@ namespace {
 
 cfb200_config g_cfg;
 bool g_configured = false;
+// Weight threshold of the basis accumulation (see framed_proj.cu).  CFB200_PRUNE overrides it for
+// accuracy studies.
+float g_prune = 16.0f;
 
 // Same formulas as the reference host code: LENGTH_RANGE / ANGLE_RANGE
 // (models/cuda_funcs/kernel_manager.py:148-149), angle sigma
@@ -54,6 +58,7 @@ int make_params(float dist_max, float cutoff_radius, cfb::Params& P)
     P.lattice_range = c.lattice_range; P.minimum_range = c.minimum_range; P.cos_abs = c.cos_abs;
     P.cutoff_radius = cutoff_radius;
     P.c_dist = c.dist_coef; P.c_ang = c.angle_coef; P.noise = c.symm_break_noise;
+    P.prune = g_prune;
     P.win_dist = (int)ceil(2.0 * (double)c.dist_wscale * c.cut_sigma + 1.0);
     P.windowed_dist = (c.dist_dim - P.win_dist > 8) ? 1 : 0;
     if (!P.windowed_dist) P.win_dist = c.dist_dim;
@@ -111,6 +116,7 @@ int cfb200_configure(const cfb200_config* cfg)
         return CFB200_E_UNSUPPORTED;
     g_cfg = c;
     g_configured = true;
+    if (const char* e = getenv("CFB200_PRUNE")) { const float v = (float)atof(e); if (v > 1.0f) g_prune = v; }
     return CFB200_OK;
 }
 

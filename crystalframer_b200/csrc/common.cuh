@@ -27,6 +27,7 @@ struct Params {
     int windowed_dist, windowed_ang;
     float cutoff_radius;
     float c_dist, c_ang, noise;
+    float prune;                  // translations with weight below exp(-prune) of the largest skip the bases
     // distance basis: b(dim) = (-d/interval + dim + 1) * step
     float d_interval, d_step, d_cut;      // d_cut = cut_sigma * sigma
     // angle basis: b(dim) = (1 - cos) * sigma_inv - (D - 1 - dim) * step
@@ -80,7 +81,15 @@ __device__ __forceinline__ int lattice_range_1d(const Params& P, float a, float 
     if (cutoff != 0.0f) {
         if (cutoff < 0.0f) cutoff = __fmul_rn(__fsqrt_rn(__fdiv_rn(-0.5f, a)), -cutoff);
         float num = __fmul_rn(__fadd_rn(cutoff, 0.01f), rvl);
-        double r = ceil((double)num / (2.0 * (double)kPiF));
+        // ceil(num / (2.0 * CUDART_PI_F)) in double, without the division: a float estimate, then
+        // the smallest integer k with k * 2pi_f >= num, decided by exact double products (both
+        // factors have at most 24 + 6 significant bits).  Quotients that the reference's rounded
+        // division could push across an integer do not occur for float inputs.
+        const double two_pi = 2.0 * (double)kPiF;
+        double r = (double)ceilf(num * 0.15915494f);
+        if ((double)num > r * two_pi) r += 1.0;
+        else if ((double)num <= (r - 1.0) * two_pi) r -= 1.0;
+        if (!(num == num)) r = (double)num;          // keep NaN visible to the check below
         // NaN (a >= 0) and runaway ranges are reported through the status word, never looped on
         if (!(r <= (double)CFB200_MAX_RANGE)) {
             atomicOr(&g_status, !(a < 0.0f) ? CFB200_ST_BAD_COEF : CFB200_ST_RANGE_CLAMPED);

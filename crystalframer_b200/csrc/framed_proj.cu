@@ -6,7 +6,7 @@
 //           which it stages 32 at a time.
 //   warp  = one (pair, head) task at a time.  Lanes first evaluate 32 lattice translations in
 //           parallel (separation, weight w = exp(a (d^2 - d^2_min)), window positions), drop
-//           translations whose weight is below exp(-kPrune) of the largest, and leave one record per surviving
+//           translations whose weight is below exp(-P.prune) of the largest, and leave one record per surviving
 //           translation in shared memory.  Then the warp walks the survivors: lane l owns basis
 //           indices l and l+32 of each of the four 64-wide Gaussian bases (distance, three frame
 //           axes) and keeps their running sums in registers, so the data-dependent window offset
@@ -31,7 +31,6 @@ constexpr int kFpStageStride = 260;                    // padded row: conflict-f
 constexpr int kHd = 16;                                // head dimension of this instance
 // resident blocks per SM the kernels are compiled for (register budget): forward 3, backward 2
 __host__ __device__ constexpr int fp_blocks_per_sm(bool bwd) { return bwd ? 2 : 3; }
-constexpr float kPrune = 20.0f;                        // drop translations with weight < e^-20 (2e-9 of the normaliser)
 
 static_assert(kFpSlots == 32, "projection maps one lane to one staged pair");
 
@@ -49,18 +48,6 @@ struct FpArgs {
 
 constexpr size_t kFpSmemFloats = (size_t)kHd * kFpK + (size_t)kFpSlots * kFpStageStride + (size_t)kFpWarps * 2 * 32 * 4 + 16 * 33;
 constexpr size_t kFpSmemBytes = kFpSmemFloats * sizeof(float);
-
-// q = t / L, r = t % L for 0 <= t < 2^20 and 1 <= L < 2^14: multiply-high by ceil(2^32 / L) plus
-// one correction step (integer pipe only; no int<->float conversion instructions)
-__device__ __forceinline__ void divmod_small(int t, int L, unsigned magic, int& q, int& r)
-{
-    q = (int)__umulhi((unsigned)t, magic);
-    r = t - q * L;
-    if (r < 0) { q--; r += L; }
-    else if (r >= L) { q++; r -= L; }
-}
-
-__device__ __forceinline__ unsigned div_magic(int L) { return (unsigned)(0xFFFFFFFFu / (unsigned)L) + 1u; }
 
 // exact float value of a small integer (|n| < 2^22) without a conversion instruction
 __device__ __forceinline__ float small_int_to_float(int n)
@@ -137,9 +124,9 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
             int Rl = 0;
             if (lane < 3) Rl = lattice_range_1d(P, a, P.cutoff_radius != 0.0f ? __ldg(A.rvlen + 3 * c + lane) : 0.0f);
             const int R1 = __shfl_sync(0xffffffffu, Rl, 0), R2 = __shfl_sync(0xffffffffu, Rl, 1), R3 = __shfl_sync(0xffffffffu, Rl, 2);
-            const int L2 = 2 * R2 + 1, L3 = 2 * R3 + 1, L23 = L2 * L3;
-            const int Ttot = (2 * R1 + 1) * L23;
-            const unsigned invL23 = div_magic(L23), invL3 = div_magic(L3);
+            const int L1 = 2 * R1 + 1, L3 = 2 * R3 + 1, L23 = (2 * R2 + 1) * L3;
+            const int nSub = (L23 + 31) >> 5;                 // 32-lane pieces of one (n2, n3) slab
+            const float invL3 = 1.0f / (float)L3;
             float fx[3], fy[3], fz[3];
             if (ANG) {
 #pragma unroll
@@ -151,20 +138,23 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
             float zin = 0.f;
             if (BWD) zin = __ldg(A.z_in + e * H + h);
 
-            // ---- sweep A (forward only): minimum squared distance over the translations ----
+            // Translations are walked slab by slab: lanes own the (n2, n3) offsets of a slab (decoded
+            // once), the loop runs over n1.  ---- sweep A (forward only): minimum squared distance ----
             float d2min = 1e10f;
             if (!BWD) {
-                for (int base = 0; base < Ttot; base += 32) {
-                    const int t = base + lane;
-                    if (t < Ttot) {
-                        int q1, r1, q2, r2;
-                        divmod_small(t, L23, invL23, q1, r1);
-                        divmod_small(r1, L3, invL3, q2, r2);
-                        const float n1 = small_int_to_float(q1 - R1), n2 = small_int_to_float(q2 - R2), n3 = small_int_to_float(r2 - R3);
-                        const float dx = fmaf(t3x, n3, fmaf(t2x, n2, fmaf(t1x, n1, rx)));
-                        const float dy = fmaf(t3y, n3, fmaf(t2y, n2, fmaf(t1y, n1, ry)));
-                        const float dz = fmaf(t3z, n3, fmaf(t2z, n2, fmaf(t1z, n1, rz)));
-                        d2min = fminf(d2min, fmaf(dz, dz, fmaf(dy, dy, dx * dx)));
+                for (int sub = 0; sub < nSub; sub++) {
+                    const int idx = sub * 32 + lane;
+                    int q2 = (int)(((float)idx + 0.5f) * invL3), r3 = idx - q2 * L3;
+                    if (r3 < 0) { q2--; r3 += L3; } else if (r3 >= L3) { q2++; r3 -= L3; }
+                    const float n2 = small_int_to_float(q2 - R2), n3 = small_int_to_float(r3 - R3);
+                    const float ox = fmaf(t3x, n3, fmaf(t2x, n2, rx)), oy = fmaf(t3y, n3, fmaf(t2y, n2, ry)),
+                                oz = fmaf(t3z, n3, fmaf(t2z, n2, rz));
+                    if (idx < L23) {
+                        for (int k1 = 0; k1 < L1; k1++) {
+                            const float n1 = small_int_to_float(k1 - R1);
+                            const float dx = fmaf(t1x, n1, ox), dy = fmaf(t1y, n1, oy), dz = fmaf(t1z, n1, oz);
+                            d2min = fminf(d2min, fmaf(dz, dz, fmaf(dy, dy, dx * dx)));
+                        }
                     }
                 }
                 d2min = warp_min(d2min);
@@ -174,23 +164,25 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
             float sd[2] = {0.f, 0.f}, sa[3][2] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
             float qd[2] = {0.f, 0.f}, qa[3][2] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};   // backward: sums of g*p*d2
             float sum_l = 0.f, px_l = 0.f;
-            for (int base = 0; base < Ttot; base += 32) {
-                const int t = base + lane;
+            for (int sub = 0; sub < nSub; sub++) {
+              const int idx = sub * 32 + lane;
+              int q2 = (int)(((float)idx + 0.5f) * invL3), r3 = idx - q2 * L3;
+              if (r3 < 0) { q2--; r3 += L3; } else if (r3 >= L3) { q2++; r3 -= L3; }
+              const float n2 = small_int_to_float(q2 - R2), n3 = small_int_to_float(r3 - R3);
+              const float ox = fmaf(t3x, n3, fmaf(t2x, n2, rx)), oy = fmaf(t3y, n3, fmaf(t2y, n2, ry)),
+                          oz = fmaf(t3z, n3, fmaf(t2z, n2, rz));
+              const bool valid = idx < L23;
+              for (int k1 = 0; k1 < L1; k1++) {
                 bool keep = false;
-                if (t < Ttot) {
-                    int q1, r1, q2, r2;
-                    divmod_small(t, L23, invL23, q1, r1);
-                    divmod_small(r1, L3, invL3, q2, r2);
-                    const float n1 = small_int_to_float(q1 - R1), n2 = small_int_to_float(q2 - R2), n3 = small_int_to_float(r2 - R3);
-                    const float dx = fmaf(t3x, n3, fmaf(t2x, n2, fmaf(t1x, n1, rx)));
-                    const float dy = fmaf(t3y, n3, fmaf(t2y, n2, fmaf(t1y, n1, ry)));
-                    const float dz = fmaf(t3z, n3, fmaf(t2z, n2, fmaf(t1z, n1, rz)));
+                if (valid) {
+                    const float n1 = small_int_to_float(k1 - R1);
+                    const float dx = fmaf(t1x, n1, ox), dy = fmaf(t1y, n1, oy), dz = fmaf(t1z, n1, oz);
                     const float d2 = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
                     const float arg = BWD ? fmaf(a, d2, -zin) : a * (d2 - d2min);
                     const float w = ex2_approx(arg * kLog2e);
                     sum_l += w;
                     if (BWD) px_l = fmaf(w, d2, px_l);
-                    keep = arg > -kPrune;
+                    keep = arg > -P.prune;
                     if (keep) {
                         // d and 1/d from one reciprocal square root plus a Newton step; quotients by
                         // the basis spacings become products with their reciprocals.  These differ
@@ -263,6 +255,7 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
                     }
                 }
                 __syncwarp();
+              }
             }
 
             if (!BWD) {

@@ -4,13 +4,13 @@
 // models/cuda_funcs/calc_maximum_frame.py and the torch ops of
 // models/indexed_lattice_multi_head_attention_cuda.py:475-481 of the reference).
 //
-// grid = (groups of kFrRows query atoms, heads).  The pairs of a group's atoms are contiguous
-// in the pair list, so the block's threads walk them one pair per thread regardless of crystal
-// size (small crystals do not leave lanes idle).  Each thread sweeps the lattice translations of
-// its pair, finds the pair's candidate image and score, and folds (score, pair index) into its
-// query atom's slot in shared memory with one 64-bit atomicMax -- an order-independent arg-max
-// with "lowest pair index wins" on equal scores.  One thread per atom then recomputes the
-// winning pair's candidate to recover its direction and image index.
+// grid = (spans of 256 pairs, heads).  A block owns the query atoms whose first pair falls in its
+// span and walks all pairs of those atoms, one pair per thread -- about 256 pairs per block
+// whatever the crystal sizes, so small crystals do not leave lanes idle.  Each thread sweeps the
+// lattice translations of its pair, finds the pair's candidate image and score, and folds
+// (score, pair index) into its query atom's slot in shared memory with one 64-bit atomicMax -- an
+// order-independent arg-max with "lowest pair index wins" on equal scores.  After the barrier the
+// thread that holds an atom's maximum leaves its direction and image index in shared memory.
 //
 // Every float operation that feeds a comparison is written with explicit round-to-nearest
 // intrinsics in the reference's evaluation order (no fused multiply-add), so the selected pair
@@ -22,7 +22,8 @@
 
 namespace cfb {
 
-constexpr int kFrRows = 16;
+constexpr int kFrPairs = 256;       // pair-list span whose query atoms one block owns
+constexpr int kFrMaxRows = 256;     // at most one atom starts per pair of the span
 constexpr int kFrThreads = 256;
 constexpr int kFrHd = 16;
 
@@ -131,25 +132,49 @@ __device__ __forceinline__ unsigned long long make_key(float score, unsigned loc
     return ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - local_pair);
 }
 
+// first index i in [0, n] with v[i] >= x (v non-decreasing, v[n] is the total)
+__device__ __forceinline__ int64_t lower_bound_i64(const int64_t* v, int64_t n, int64_t x)
+{
+    int64_t lo = 0, hi = n;
+    while (lo < hi) {
+        const int64_t mid = (lo + hi) >> 1;
+        if (v[mid] < x) lo = mid + 1; else hi = mid;
+    }
+    return lo;
+}
+
 __global__ void __launch_bounds__(kFrThreads, 2) max_frame_kernel(const FrArgs A, const Params P)
 {
-    __shared__ unsigned long long best[kFrRows];
-    __shared__ long long row_start[kFrRows + 1];
-    __shared__ float row_a[kFrRows];
-    __shared__ int row_R[kFrRows][3];
-    __shared__ float row_f1[kFrRows][3];
+    __shared__ unsigned long long best[kFrMaxRows];
+    __shared__ long long row_start[kFrMaxRows + 1];
+    __shared__ float row_a[kFrMaxRows];
+    __shared__ int row_R[kFrMaxRows];                 // three ranges, one byte each
+    __shared__ float row_f1[kFrMaxRows][3];
+    __shared__ float row_dir[kFrMaxRows][3];
+    __shared__ int row_img[kFrMaxRows];
+    __shared__ long long row_range[2];
 
     const int H = P.H, h = blockIdx.y, tid = threadIdx.x;
-    const int64_t i0 = (int64_t)blockIdx.x * kFrRows;
-    const int rows = (int)min((int64_t)kFrRows, A.N - i0);
+    // The block owns the query atoms whose first pair lies in [kFrPairs*b, kFrPairs*(b+1)) and
+    // processes all of their pairs: about kFrPairs pairs per block whatever the crystal sizes.
+    if (tid < 2) {
+        const int64_t x = ((int64_t)blockIdx.x + tid) * kFrPairs;
+        row_range[tid] = x >= A.E ? A.N : lower_bound_i64(A.e_start, A.N, x);
+    }
+    __syncthreads();
+    const int64_t i0 = row_range[0];
+    const int rows = (int)(row_range[1] - i0);
+    if (rows <= 0) return;
     if (tid <= rows) row_start[tid] = A.e_start[i0 + tid];
     if (tid < rows) {
         const int64_t i = i0 + tid;
         const float a = __ldg(A.a_ik + i * H + h);
         row_a[tid] = a;
         const int64_t c = A.batch[i];
+        int pack = 0;
         for (int d = 0; d < 3; d++)
-            row_R[tid][d] = lattice_range_1d(P, a, P.cutoff_radius != 0.0f ? __ldg(A.rvlen + 3 * c + d) : 0.0f);
+            pack |= lattice_range_1d(P, a, P.cutoff_radius != 0.0f ? __ldg(A.rvlen + 3 * c + d) : 0.0f) << (8 * d);
+        row_R[tid] = pack;
         if (A.mode == 2) {
             const float* f = A.frame1_in + (i * H + h) * 3;
             row_f1[tid][0] = __ldg(f); row_f1[tid][1] = __ldg(f + 1); row_f1[tid][2] = __ldg(f + 2);
@@ -160,82 +185,88 @@ __global__ void __launch_bounds__(kFrThreads, 2) max_frame_kernel(const FrArgs A
     const unsigned long long none = make_key(-1e10f, 0u);      // a score must exceed -1e10 to be selected
 
     for (int axis = (A.mode == 2 ? 2 : 1); axis <= (A.mode == 1 ? 1 : 2); axis++) {
-        if (tid < rows) best[tid] = none;
-        __syncthreads();
-        // ---- every pair of the group: candidate image, score, arg-max per query atom ----
-        for (int64_t e = eb + tid; e < ee; e += kFrThreads) {
-            int r = 0;
-#pragma unroll
-            for (int s = kFrRows / 2; s > 0; s >>= 1)
-                if (r + s < rows && row_start[r + s] <= e) r += s;
-            const int64_t i = i0 + r;
-            const int64_t j = A.edges[A.E + e];
-            const int64_t c = A.batch[i];
-            Cell cell;
-            const float* Tc = A.tvecs + 9 * c;
-            cell.t1x = __ldg(Tc); cell.t1y = __ldg(Tc + 1); cell.t1z = __ldg(Tc + 2);
-            cell.t2x = __ldg(Tc + 3); cell.t2y = __ldg(Tc + 4); cell.t2z = __ldg(Tc + 5);
-            cell.t3x = __ldg(Tc + 6); cell.t3y = __ldg(Tc + 7); cell.t3z = __ldg(Tc + 8);
-            cell.rx = __ldg(A.pos_ij + 3 * e); cell.ry = __ldg(A.pos_ij + 3 * e + 1); cell.rz = __ldg(A.pos_ij + 3 * e + 2);
-            float dot = 0.f;
-            const float4* q4 = reinterpret_cast<const float4*>(A.q + (i * H + h) * kFrHd);
-            const float4* k4 = reinterpret_cast<const float4*>(A.k + (j * H + h) * kFrHd);
-#pragma unroll
-            for (int d4 = 0; d4 < kFrHd / 4; d4++) {
-                const float4 u = __ldg(q4 + d4), v = __ldg(k4 + d4);
-                dot = __fmaf_rn(u.x, v.x, dot); dot = __fmaf_rn(u.y, v.y, dot);
-                dot = __fmaf_rn(u.z, v.z, dot); dot = __fmaf_rn(u.w, v.w, dot);
-            }
-            const uint64_t noise_id = (uint64_t)(e * H + h);
-            const Cand cd = axis == 1
-                ? first_axis_candidate(cell, row_a[r], row_R[r][0], row_R[r][1], row_R[r][2], P.noise, A.seed1, noise_id)
-                : second_axis_candidate(cell, row_a[r], row_R[r][0], row_R[r][1], row_R[r][2], P.noise, A.seed2, noise_id,
-                                        row_f1[r][0], row_f1[r][1], row_f1[r][2]);
-            const float s = __fadd_rn(dot, cd.value);
-            if (s > -1e10f) atomicMax(&best[r], make_key(s, (unsigned)(e - row_start[r])));
+        if (tid < rows) {
+            best[tid] = none;
+            row_dir[tid][0] = row_dir[tid][1] = row_dir[tid][2] = 0.f;
+            row_img[tid] = -1;
         }
         __syncthreads();
-        // ---- one thread per query atom: recover the winner's direction and image ----
-        if (tid < rows) {
-            const int64_t i = i0 + tid;
-            const unsigned long long key = best[tid];
+        // ---- every pair of these atoms: candidate image, score, arg-max per query atom ----
+        for (int64_t base = eb; base < ee; base += kFrThreads) {
+            const int64_t e = base + tid;
+            int r = 0;
+            unsigned long long key = 0ull;
             Cand cd; cd.ux = cd.uy = cd.uz = 0.f; cd.img = -1; cd.value = 0.f;
-            int64_t e_win = -1;
-            if (key != none) {
-                e_win = row_start[tid] + (int64_t)(0xFFFFFFFFu - (unsigned)(key & 0xFFFFFFFFull));
+            if (e < ee) {
+#pragma unroll
+                for (int s = kFrMaxRows / 2; s > 0; s >>= 1)
+                    if (r + s < rows && row_start[r + s] <= e) r += s;
+                const int64_t i = i0 + r;
+                const int64_t j = A.edges[A.E + e];
                 const int64_t c = A.batch[i];
                 Cell cell;
                 const float* Tc = A.tvecs + 9 * c;
                 cell.t1x = __ldg(Tc); cell.t1y = __ldg(Tc + 1); cell.t1z = __ldg(Tc + 2);
                 cell.t2x = __ldg(Tc + 3); cell.t2y = __ldg(Tc + 4); cell.t2z = __ldg(Tc + 5);
                 cell.t3x = __ldg(Tc + 6); cell.t3y = __ldg(Tc + 7); cell.t3z = __ldg(Tc + 8);
-                cell.rx = __ldg(A.pos_ij + 3 * e_win); cell.ry = __ldg(A.pos_ij + 3 * e_win + 1); cell.rz = __ldg(A.pos_ij + 3 * e_win + 2);
-                const uint64_t noise_id = (uint64_t)(e_win * H + h);
+                cell.rx = __ldg(A.pos_ij + 3 * e); cell.ry = __ldg(A.pos_ij + 3 * e + 1); cell.rz = __ldg(A.pos_ij + 3 * e + 2);
+                float dot = 0.f;
+                const float4* q4 = reinterpret_cast<const float4*>(A.q + (i * H + h) * kFrHd);
+                const float4* k4 = reinterpret_cast<const float4*>(A.k + (j * H + h) * kFrHd);
+#pragma unroll
+                for (int d4 = 0; d4 < kFrHd / 4; d4++) {
+                    const float4 u = __ldg(q4 + d4), v = __ldg(k4 + d4);
+                    dot = __fmaf_rn(u.x, v.x, dot); dot = __fmaf_rn(u.y, v.y, dot);
+                    dot = __fmaf_rn(u.z, v.z, dot); dot = __fmaf_rn(u.w, v.w, dot);
+                }
+                const uint64_t noise_id = (uint64_t)(e * H + h);
+                const int pack = row_R[r];
+                const int R1 = pack & 255, R2 = (pack >> 8) & 255, R3 = (pack >> 16) & 255;
                 cd = axis == 1
-                    ? first_axis_candidate(cell, row_a[tid], row_R[tid][0], row_R[tid][1], row_R[tid][2], P.noise, A.seed1, noise_id)
-                    : second_axis_candidate(cell, row_a[tid], row_R[tid][0], row_R[tid][1], row_R[tid][2], P.noise, A.seed2,
-                                            noise_id, row_f1[tid][0], row_f1[tid][1], row_f1[tid][2]);
+                    ? first_axis_candidate(cell, row_a[r], R1, R2, R3, P.noise, A.seed1, noise_id)
+                    : second_axis_candidate(cell, row_a[r], R1, R2, R3, P.noise, A.seed2, noise_id,
+                                            row_f1[r][0], row_f1[r][1], row_f1[r][2]);
+                const float s = __fadd_rn(dot, cd.value);
+                if (s > -1e10f) {
+                    key = make_key(s, (unsigned)(e - row_start[r]));
+                    atomicMax(&best[r], key);
+                }
             }
+            __syncthreads();
+            // the pair that holds the atom's maximum so far leaves its direction; a better pair
+            // of a later round overwrites it after that round's barrier
+            if (key != 0ull && best[r] == key) {
+                row_dir[r][0] = cd.ux; row_dir[r][1] = cd.uy; row_dir[r][2] = cd.uz;
+                row_img[r] = cd.img;
+            }
+        }
+        __syncthreads();
+        // ---- one thread per query atom: outputs ----
+        if (tid < rows) {
+            const int64_t i = i0 + tid;
+            const unsigned long long key = best[tid];
+            const int64_t e_win = key == none ? -1 : row_start[tid] + (int64_t)(0xFFFFFFFFu - (unsigned)(key & 0xFFFFFFFFull));
+            const float ux = row_dir[tid][0], uy = row_dir[tid][1], uz = row_dir[tid][2];
             if (axis == 1) {
-                row_f1[tid][0] = cd.ux; row_f1[tid][1] = cd.uy; row_f1[tid][2] = cd.uz;
+                row_f1[tid][0] = ux; row_f1[tid][1] = uy; row_f1[tid][2] = uz;
                 if (A.mode != 2) {
                     float* o = A.frame1 + (i * H + h) * 3;
-                    o[0] = cd.ux; o[1] = cd.uy; o[2] = cd.uz;
+                    o[0] = ux; o[1] = uy; o[2] = uz;
                 }
                 if (A.mode == 1 && A.sel_edge) A.sel_edge[i * H + h] = e_win;
-                if (A.mode == 1 && A.sel_image) A.sel_image[i * H + h] = cd.img;
+                if (A.mode == 1 && A.sel_image) A.sel_image[i * H + h] = row_img[tid];
             } else {
                 float* o2 = A.frame2 + (i * H + h) * 3;
                 if (A.mode == 2) {
-                    o2[0] = cd.ux; o2[1] = cd.uy; o2[2] = cd.uz;
+                    o2[0] = ux; o2[1] = uy; o2[2] = uz;
                     if (A.sel_edge) A.sel_edge[i * H + h] = e_win;
-                    if (A.sel_image) A.sel_image[i * H + h] = cd.img;
+                    if (A.sel_image) A.sel_image[i * H + h] = row_img[tid];
                 } else {
                     // Gram-Schmidt, normalisation with max(norm, 1e-12), cross product
                     const float f1x = row_f1[tid][0], f1y = row_f1[tid][1], f1z = row_f1[tid][2];
-                    const float dot = __fadd_rn(__fadd_rn(__fmul_rn(f1x, cd.ux), __fmul_rn(f1y, cd.uy)), __fmul_rn(f1z, cd.uz));
-                    const float wx = __fsub_rn(cd.ux, __fmul_rn(dot, f1x)), wy = __fsub_rn(cd.uy, __fmul_rn(dot, f1y)),
-                                wz = __fsub_rn(cd.uz, __fmul_rn(dot, f1z));
+                    const float dot = __fadd_rn(__fadd_rn(__fmul_rn(f1x, ux), __fmul_rn(f1y, uy)), __fmul_rn(f1z, uz));
+                    const float wx = __fsub_rn(ux, __fmul_rn(dot, f1x)), wy = __fsub_rn(uy, __fmul_rn(dot, f1y)),
+                                wz = __fsub_rn(uz, __fmul_rn(dot, f1z));
                     float nrm = __fsqrt_rn(__fadd_rn(__fadd_rn(__fmul_rn(wx, wx), __fmul_rn(wy, wy)), __fmul_rn(wz, wz)));
                     nrm = fmaxf(nrm, 1e-12f);
                     const float gx = __fdiv_rn(wx, nrm), gy = __fdiv_rn(wy, nrm), gz = __fdiv_rn(wz, nrm);
@@ -253,8 +284,8 @@ __global__ void __launch_bounds__(kFrThreads, 2) max_frame_kernel(const FrArgs A
 
 int max_frame(const FrArgs& A, const Params& P, cudaStream_t st)
 {
-    if (A.N == 0) return CFB200_OK;
-    const unsigned gx = (unsigned)((A.N + kFrRows - 1) / kFrRows);
+    if (A.N == 0 || A.E == 0) return CFB200_OK;
+    const unsigned gx = (unsigned)((A.E + kFrPairs - 1) / kFrPairs);
     max_frame_kernel<<<dim3(gx, P.H), kFrThreads, 0, st>>>(A, P);
     return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
 }
