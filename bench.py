@@ -8,9 +8,9 @@ with median 8, clipped to 1..64; see crystalframer_b200/synth.py).  The metric i
 second over all GPUs.  Rank 0 prints one JSON line.
 
 ``value``   : batches already resident in HBM; device time of K steps (CUDA events), max over ranks.
-``e2e``     : the same step through the public API with HOST (pinned) buffers: the host-to-device
-              copy of the step's batch and the device-to-host read of the loss are inside the
-              timed region.
+``e2e``     : the same step through the public API with HOST (pinned) buffers: every step copies its
+              batch host-to-device and its loss device-to-host (asynchronously, into pinned memory, as
+              a training loop that logs losses does); the timed region ends when all of it has landed.
 ``roofline``: the dominant kernel call (lattice-sum backward), algorithmic flops / CUDA-event time,
               against the FP32 fused-multiply-add throughput measured on the same device by the
               library's probe kernel; the special-function (ex2) figures sit beside it.
@@ -277,6 +277,7 @@ def run_ours(args, rank, world, local_rank):
         return loss
 
     enqueue_ms = [0.0]
+    loss_host = torch.zeros(64, dtype=torch.float32).pin_memory()      # per-step losses land here asynchronously
 
     def timed(n_steps, from_host):
         """Device time of n_steps back-to-back steps (CUDA events on the launching stream); with
@@ -290,7 +291,7 @@ def run_ours(args, rank, world, local_rank):
             tb = host[i % n_host].to(dev) if from_host else resident[i % n_host]
             loss = train_step(tb)
             if from_host:
-                loss.item()                                       # device-to-host read of the result
+                loss_host[i % len(loss_host)].copy_(loss.detach(), non_blocking=True)   # device-to-host read of the result
         e1.record()
         enqueue_ms[0] = (time.perf_counter() - t0) * 1e3          # host time to enqueue the steps
         torch.cuda.synchronize()

@@ -46,7 +46,9 @@ struct FpArgs {
     float* gW_part;           // (gridDim.x, H, 16, 256) per-block weight gradient (scratch)
 };
 
-constexpr size_t kFpSmemFloats = (size_t)kHd * kFpK + (size_t)kFpSlots * kFpStageStride + (size_t)kFpWarps * 2 * 32 * 4 + 16 * 33;
+constexpr int kWtStride = 20;                          // backward: W stored [k][o] with padded rows (conflict-free 128-bit reads)
+constexpr int kWtPad = kFpK * kWtStride - kHd * kFpK;   // extra floats that layout needs
+constexpr size_t kFpSmemFloats = (size_t)kHd * kFpK + (size_t)kFpSlots * kFpStageStride + (size_t)kFpWarps * 2 * 32 * 4 + 16 * 33 + kWtPad;
 constexpr size_t kFpSmemBytes = kFpSmemFloats * sizeof(float);
 
 // exact float value of a small integer (|n| < 2^22) without a conversion instruction
@@ -59,8 +61,8 @@ template <bool BWD, bool ANG>
 __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj_kernel(const FpArgs A, const Params P)
 {
     extern __shared__ __align__(16) float smem[];
-    float* W_s = smem;                                          // [16][256]
-    float* stage = W_s + kHd * kFpK;                            // [32][260]
+    float* W_s = smem;                                          // fwd: [16][256]; bwd: [256][20] (transposed)
+    float* stage = W_s + kHd * kFpK + kWtPad;                   // [32][260]
     float4* tbuf = reinterpret_cast<float4*>(stage + kFpSlots * kFpStageStride);  // [8][2][32]
     float* side = reinterpret_cast<float*>(tbuf + kFpWarps * 2 * 32);             // fwd: out [16][33]; bwd: gv [32][16]
 
@@ -73,7 +75,13 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (A.W[b] != nullptr)
             v = __ldg(reinterpret_cast<const float4*>(A.W[b] + ((size_t)h * kHd + o) * 64) + d4);
-        reinterpret_cast<float4*>(W_s)[idx] = v;
+        if (!BWD) {
+            reinterpret_cast<float4*>(W_s)[idx] = v;
+        } else {
+            const int k = k4 * 4;
+            W_s[(k + 0) * kWtStride + o] = v.x; W_s[(k + 1) * kWtStride + o] = v.y;
+            W_s[(k + 2) * kWtStride + o] = v.z; W_s[(k + 3) * kWtStride + o] = v.w;
+        }
     }
 
     // per-lane basis constants, pre-scaled so that a Gaussian is ex2(-b*b)
@@ -281,11 +289,16 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
                 }
                 float G[8];
 #pragma unroll
-                for (int j = 0; j < 8; j++) G[j] = 0.f;
+                for (int j = 0; j < 8; j++) {
+                    const float4* wrow = reinterpret_cast<const float4*>(W_s + (j * 32 + lane) * kWtStride);
+                    float acc = 0.f;
 #pragma unroll
-                for (int o = 0; o < kHd; o++)
-#pragma unroll
-                    for (int j = 0; j < 8; j++) G[j] = fmaf(W_s[o * kFpK + j * 32 + lane], gvr[o], G[j]);
+                    for (int o4 = 0; o4 < kHd / 4; o4++) {
+                        const float4 u = wrow[o4];
+                        acc = fmaf(u.x, gvr[4 * o4], fmaf(u.y, gvr[4 * o4 + 1], fmaf(u.z, gvr[4 * o4 + 2], fmaf(u.w, gvr[4 * o4 + 3], acc))));
+                    }
+                    G[j] = acc;
+                }
                 float Ad = fmaf(G[0], qd[0], G[1] * qd[1]), Bd = fmaf(G[0], sd[0], G[1] * sd[1]);
                 float Aa = 0.f, Ba = 0.f;
 #pragma unroll
@@ -338,27 +351,30 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
                 }
             }
         } else {
+            // in this phase lane l owns basis indices 4l..4l+3 and 128+4l..128+4l+3 (128-bit reads)
             for (int slot = 0; slot < kFpSlots; slot++) {
                 const float2 g = *reinterpret_cast<const float2*>(side + slot * kHd + 2 * warp);
-                const float* srow = stage + slot * kFpStageStride + lane;
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    const float s = srow[j * 32];
-                    gacc[0][j] = fmaf(s, g.x, gacc[0][j]);
-                    gacc[1][j] = fmaf(s, g.y, gacc[1][j]);
-                }
+                const float4* srow = reinterpret_cast<const float4*>(stage + slot * kFpStageStride) + lane;
+                const float4 s0 = srow[0], s1 = srow[32];
+                gacc[0][0] = fmaf(s0.x, g.x, gacc[0][0]); gacc[0][1] = fmaf(s0.y, g.x, gacc[0][1]);
+                gacc[0][2] = fmaf(s0.z, g.x, gacc[0][2]); gacc[0][3] = fmaf(s0.w, g.x, gacc[0][3]);
+                gacc[0][4] = fmaf(s1.x, g.x, gacc[0][4]); gacc[0][5] = fmaf(s1.y, g.x, gacc[0][5]);
+                gacc[0][6] = fmaf(s1.z, g.x, gacc[0][6]); gacc[0][7] = fmaf(s1.w, g.x, gacc[0][7]);
+                gacc[1][0] = fmaf(s0.x, g.y, gacc[1][0]); gacc[1][1] = fmaf(s0.y, g.y, gacc[1][1]);
+                gacc[1][2] = fmaf(s0.z, g.y, gacc[1][2]); gacc[1][3] = fmaf(s0.w, g.y, gacc[1][3]);
+                gacc[1][4] = fmaf(s1.x, g.y, gacc[1][4]); gacc[1][5] = fmaf(s1.y, g.y, gacc[1][5]);
+                gacc[1][6] = fmaf(s1.z, g.y, gacc[1][6]); gacc[1][7] = fmaf(s1.w, g.y, gacc[1][7]);
             }
         }
         __syncthreads();
     }
 
     if (BWD) {
-        float* dst = A.gW_part + (((size_t)blockIdx.x * H + h) * kHd + 2 * warp) * kFpK + lane;
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            dst[j * 32] = gacc[0][j];
-            dst[kFpK + j * 32] = gacc[1][j];
-        }
+        float* dst = A.gW_part + (((size_t)blockIdx.x * H + h) * kHd + 2 * warp) * kFpK + 4 * lane;
+        *reinterpret_cast<float4*>(dst) = make_float4(gacc[0][0], gacc[0][1], gacc[0][2], gacc[0][3]);
+        *reinterpret_cast<float4*>(dst + 128) = make_float4(gacc[0][4], gacc[0][5], gacc[0][6], gacc[0][7]);
+        *reinterpret_cast<float4*>(dst + kFpK) = make_float4(gacc[1][0], gacc[1][1], gacc[1][2], gacc[1][3]);
+        *reinterpret_cast<float4*>(dst + kFpK + 128) = make_float4(gacc[1][4], gacc[1][5], gacc[1][6], gacc[1][7]);
     }
 }
 

@@ -45,9 +45,9 @@ def _close_reduction(name, got, want32, want64):
     assert ours <= 3.0 * theirs + ATOL, f"{name}: error vs float64 {ours:.3e}, float32 oracle's {theirs:.3e}"
 
 
-def _configure(noise=0.0, angle_dim=64, c_dist=1.0, c_ang=1.0):
+def _configure(noise=0.0, angle_dim=64, c_dist=1.0, c_ang=1.0, wscale_d=1.0, wscale_a=4.0):
     from crystalframer_b200 import cuda_funcs as F
-    F.compile_kernels(2, 8, 16, 64, angle_dim, 16, True, 0, 1.0, 4.0, c_dist, c_ang, noise)
+    F.compile_kernels(2, 8, 16, 64, angle_dim, 16, True, 0, wscale_d, wscale_a, c_dist, c_ang, noise)
     return F
 
 
@@ -113,12 +113,17 @@ def _frames(P):
     return np.stack([fr["frame1"], fr["frame2"], fr["frame3"]])
 
 
-@pytest.mark.parametrize("workload,nc,angles", [("cfg1", None, True), ("cfg2", 24, True), ("cfg1", None, False)])
-def test_framed_proj_forward_backward(workload, nc, angles):
+@pytest.mark.parametrize("workload,nc,angles,wscales", [
+    ("cfg1", None, True, (1.0, 4.0)), ("cfg2", 24, True, (1.0, 4.0)), ("cfg1", None, False, (1.0, 4.0)),
+    ("cfg1", None, True, (1.5, 3.0)),          # other window widths: 13 distance, 25 angle
+    ("cfg1", None, True, (8.0, 8.0)),          # windows wider than the bases: every Gaussian is evaluated
+])
+def test_framed_proj_forward_backward(workload, nc, angles, wscales):
     dev = _cuda()
     from oracle import oracle as O
-    F = _configure(angle_dim=64 if angles else 0)
+    F = _configure(angle_dim=64 if angles else 0, wscale_d=wscales[0], wscale_a=wscales[1])
     P = make_problem(workload, num_crystals=nc)
+    P["cfg"] = O.Config(wscale_dist=wscales[0], wscale_ang=wscales[1])
     g = _geometry(P, dev)
     frames = _frames(P) if angles else None
     W_a = P["W_a"] if angles else None
@@ -133,8 +138,8 @@ def test_framed_proj_forward_backward(workload, nc, angles):
     else:
         Ws, fs = [None] * 3, [None] * 3
     z, v = F.RealEncodingWithFramedProjFuncCUDA.apply(
-        a, g["pos_ij"], None, g["tvecs"], g["batch"], g["edges"], 64, 14.0, 1.0, Wd, *Ws, *fs, 64, 4.0, 0, 1.0, 1.0,
-        g["rvlen"], -3.5)
+        a, g["pos_ij"], None, g["tvecs"], g["batch"], g["edges"], 64, 14.0, wscales[0], Wd, *Ws, *fs, 64, wscales[1], 0,
+        1.0, 1.0, g["rvlen"], -3.5)
     _close("z", z.detach().cpu().numpy(), z_w)
     _close("values", v.detach().cpu().numpy(), v_w)
     rng = np.random.default_rng(7)
