@@ -38,6 +38,8 @@ SIGNATURES = {
     "cfb200_max_frames": (ctypes.c_int, [vp] * 9 + [i64, i64, f32, u64, u64] + [vp] * 4),
     "cfb200_framed_proj_fwd": (ctypes.c_int, [vp] * 6 + [i64, i64, f32, f32] + [vp] * 10),
     "cfb200_framed_proj_bwd": (ctypes.c_int, [vp] * 7 + [i64, i64, f32, f32] + [vp] * 16 + [i64, vp]),
+    "cfb200_proj_fwd": (ctypes.c_int, [vp] * 6 + [i64, i64, f32, f32] + [vp] * 4),
+    "cfb200_proj_bwd": (ctypes.c_int, [vp] * 7 + [i64, i64, f32, f32] + [vp] * 7 + [i64, vp]),
     "cfb200_framed_proj_bwd_noalloc": (ctypes.c_int, [vp] * 7 + [i64, i64, f32, f32] + [vp] * 15 + [vp]),
     "cfb200_dpa_fwd": (ctypes.c_int, [vp] * 7 + [i64, i64] + [vp] * 4),
     "cfb200_dpa_bwd": (ctypes.c_int, [vp] * 7 + [i64, i64] + [vp] * 9),

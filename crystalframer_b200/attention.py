@@ -21,7 +21,8 @@ from torch.nn.init import constant_, normal_, xavier_uniform_
 from torch.nn.modules.linear import NonDynamicallyQuantizableLinear
 
 from .cuda_funcs import (ComputeFrame1MaximumMethodCUDA, ComputeFrame2MaximumMethodCUDA,
-                         FusedDotProductAttentionCUDA, RealEncodingWithFramedProjFuncCUDA, max_frames_fused)
+                         FusedDotProductAttentionCUDA, RealEncodingWithFramedProjFuncCUDA,
+                         RealPeriodicEncodingWithProjFuncCUDA, max_frames_fused)
 from .latticeformer_params import LatticeformerParams
 
 # use the single-launch frame construction instead of the two Functions plus torch ops
@@ -77,7 +78,11 @@ def compute_real_domain_attn_frame_proj(q, k, v, batch_q, batch_kv, edges, pos, 
                                                    pe_dist_proj, K, dist_max, wscale, "max", this_epoch, *adap)
         W1, W2, W3 = proj_angle1, proj_angle2, proj_angle3
     elif params.frame_method == "no":
-        f1 = f2 = f3 = W1 = W2 = W3 = None
+        # plain Crystalformer: un-windowed distance encoding, no frames, no coefficients
+        # (models/indexed_lattice_multi_head_attention_cuda.py:403-433, :620-624)
+        out = RealPeriodicEncodingWithProjFuncCUDA.apply(alpha, pos, dist2_min, tvecs, batch_q, edges, K, dist_max,
+                                                         wscale, pe_dist_proj, "no", *rv_args)
+        return out[0], (out[1] if len(out) > 1 else None)
     else:
         raise NotImplementedError(f"frame_method={params.frame_method}")
     out = RealEncodingWithFramedProjFuncCUDA.apply(

@@ -49,7 +49,7 @@ float g_prune = 16.0f;
 // (models/cuda_funcs/real_space_framed_proj.py:37-40), and the per-kernel constants
 // (models/kernels/real_enc_frame_proj_fwd_length.cu:130-132, ..._fwd_angle.cu:136-143),
 // evaluated in float where the kernels evaluate them in float.
-int make_params(float dist_max, float cutoff_radius, cfb::Params& P)
+int make_params(float dist_max, float cutoff_radius, cfb::Params& P, bool full_range = false)
 {
     if (!g_configured) return CFB200_E_NOT_CONFIGURED;
     const cfb200_config& c = g_cfg;
@@ -62,6 +62,11 @@ int make_params(float dist_max, float cutoff_radius, cfb::Params& P)
     P.win_dist = (int)ceil(2.0 * (double)c.dist_wscale * c.cut_sigma + 1.0);
     P.windowed_dist = (c.dist_dim - P.win_dist > 8) ? 1 : 0;
     if (!P.windowed_dist) P.win_dist = c.dist_dim;
+    if (full_range) {
+        // plain Crystalformer encoding (real_enc_proj_fwd.cu:127-134): every distance Gaussian, no
+        // coefficient on the values
+        P.windowed_dist = 0; P.win_dist = c.dist_dim; P.c_dist = 1.0f;
+    }
     P.d_interval = dist_max / (float)c.dist_dim;
     P.d_step = 1.0f / (c.dist_wscale * sqrtf(2.0f));
     P.d_cut = (float)c.cut_sigma * (P.d_interval * c.dist_wscale);
@@ -244,6 +249,44 @@ int cfb200_framed_proj_fwd(const float* a_ik, const float* pos_ij, const float* 
     if (values != nullptr && W_dist == nullptr) return CFB200_E_NULL;
     A.z = z; A.values = values;
     return cfb::framed_proj_fwd(A, P, S(stream));
+}
+
+int cfb200_proj_fwd(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                    const int64_t* batch, const int64_t* edges, int64_t N, int64_t E, float dist_max,
+                    float cutoff_radius, const float* W_dist, float* z, float* values, void* stream)
+{
+    cfb::Params P;
+    int rc = make_params(dist_max, cutoff_radius, P, true);
+    if (rc != CFB200_OK) return rc;
+    cfb::FpArgs A;
+    rc = fp_args(A, a_ik, pos_ij, tvecs, rvlen, batch, edges, N, E, cutoff_radius, W_dist, nullptr, nullptr, nullptr,
+                 nullptr, nullptr, nullptr);
+    if (rc != CFB200_OK) return rc;
+    if (E > 0 && z == nullptr) return CFB200_E_NULL;
+    if (values != nullptr && W_dist == nullptr) return CFB200_E_NULL;
+    A.z = z; A.values = values;
+    return cfb::framed_proj_fwd(A, P, S(stream));
+}
+
+int cfb200_proj_bwd(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                    const int64_t* batch, const int64_t* edges, const int64_t* e_start, int64_t N, int64_t E,
+                    float dist_max, float cutoff_radius, const float* W_dist, const float* z, const float* gz,
+                    const float* gvalues, float* ga, float* gW_dist, void* workspace, int64_t workspace_bytes,
+                    void* stream)
+{
+    cfb::Params P;
+    int rc = make_params(dist_max, cutoff_radius, P, true);
+    if (rc != CFB200_OK) return rc;
+    cfb::FpArgs A;
+    rc = fp_args(A, a_ik, pos_ij, tvecs, rvlen, batch, edges, N, E, cutoff_radius, W_dist, nullptr, nullptr, nullptr,
+                 nullptr, nullptr, nullptr);
+    if (rc != CFB200_OK) return rc;
+    if (E > 0 && (!z || !gz || !gvalues || !W_dist || !e_start)) return CFB200_E_NULL;
+    if (N > 0 && (ga == nullptr || e_start == nullptr)) return CFB200_E_NULL;
+    if (gW_dist == nullptr) return CFB200_E_NULL;
+    A.z_in = z; A.gz = gz; A.gv = gvalues;
+    float* gW[4] = {gW_dist, nullptr, nullptr, nullptr};
+    return cfb::framed_proj_bwd(A, P, e_start, ga, gW, workspace, workspace_bytes, S(stream));
 }
 
 int cfb200_framed_proj_bwd(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,

@@ -2,6 +2,7 @@
 ``models/cuda_funcs`` package (models/cuda_funcs/__init__.py:12-47), backed by libcfb200.so."""
 from .kernel_manager import KernelManager, compile_kernels, current_config
 from .framed_proj import RealEncodingWithFramedProjFuncCUDA
+from .enc_proj import RealPeriodicEncodingWithProjFuncCUDA
 from .max_frame import (ComputeFrame1MaximumMethodCUDA, ComputeFrame2MaximumMethodCUDA,
                         max_frame_with_selection, max_frames_fused)
 from .fused_dpa import FusedDotProductAttentionCUDA, attention_probabilities
@@ -15,6 +16,7 @@ CUPY_AVAILABLE = True
 __all__ = [
     "KernelManager", "compile_kernels", "current_config", "FusedDotProductAttentionCUDA",
     "ComputeFrame1MaximumMethodCUDA", "ComputeFrame2MaximumMethodCUDA", "RealEncodingWithFramedProjFuncCUDA",
+    "RealPeriodicEncodingWithProjFuncCUDA",
     "IrregularMeanCUDA", "max_frame_with_selection", "max_frames_fused", "attention_probabilities",
     "csr_offsets", "register_csr", "CUPY_AVAILABLE",
 ]

@@ -131,6 +131,20 @@ int cfb200_framed_proj_bwd(const float* a_ik, const float* pos_ij, const float* 
                            float* gW_ang1, float* gW_ang2, float* gW_ang3, void* workspace,
                            int64_t workspace_bytes, void* stream);
 
+/* Replaces RealPeriodicEncodingWithProjFuncCUDA with frame_method "no"
+ * (models/cuda_funcs/real_space_enc_proj.py:21-213; kernels real_enc_proj_fwd.cu,
+ * real_enc_proj_bwd.cu): the plain Crystalformer encoding -- lattice-sum bias z (E,H) and the
+ * distance value encoding over ALL dist_dim Gaussians (no window, no coefficient, no frames).
+ * The backward needs the same workspace as cfb200_framed_proj_bwd. */
+int cfb200_proj_fwd(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                    const int64_t* batch, const int64_t* edges, int64_t N, int64_t E, float dist_max,
+                    float cutoff_radius, const float* W_dist, float* z, float* values, void* stream);
+int cfb200_proj_bwd(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                    const int64_t* batch, const int64_t* edges, const int64_t* e_start, int64_t N,
+                    int64_t E, float dist_max, float cutoff_radius, const float* W_dist,
+                    const float* z, const float* gz, const float* gvalues, float* ga, float* gW_dist,
+                    void* workspace, int64_t workspace_bytes, void* stream);
+
 /* No counterpart in the reference (whose Functions allocate their temporaries with torch).
  * Same computation, arguments and outputs as cfb200_framed_proj_bwd, for hosts that cannot
  * provide a workspace: a plugin under a runtime that owns the device heap and passes only input

@@ -136,6 +136,28 @@ class RefKernels:
             gWs = gWs.sum(dim=1) * c_ang          # autograd's sum_to_size over the atom axis
         return ga, gW.sum(dim=0), gWs
 
+    # ---- models/cuda_funcs/real_space_enc_proj.py:21-213, frame_method "no" ---------------
+    def proj_fwd(self, a_ik, rpos, tvecs, batch, edges, K, dist_max, wscale, W_k, rvlen, cutoff):
+        N, H = a_ik.shape
+        E = edges.shape[1]
+        kw = dict(device=a_ik.device, dtype=a_ik.dtype)
+        z = torch.empty((E, H), **kw)
+        v = torch.empty((E, H, W_k.shape[-2]), **kw)
+        self.launch("real_enc_proj_fwd", (E * H + H - 1) // H, H, a_ik, rpos, None, tvecs, batch, edges, N, H, E, K,
+                    dist_max, wscale, W_k, 1, rvlen, cutoff, z, v)
+        return z, v
+
+    def proj_bwd(self, a_ik, rpos, tvecs, batch, edges, dist_max, wscale, W_k, rvlen, cutoff, z, gz, gv):
+        N, H = a_ik.shape
+        E = edges.shape[1]
+        kw = dict(device=a_ik.device, dtype=a_ik.dtype)
+        e_start = self.e_start(edges, N)
+        ga = torch.empty((N, H), **kw)
+        gW = torch.empty((N,) + tuple(W_k.shape[-3:]), **kw)
+        self.launch("real_enc_proj_bwd", (N * H + H - 1) // H, H, a_ik, rpos, tvecs, batch, edges, e_start, z,
+                    gz.contiguous(), gv.contiguous(), N, H, E, dist_max, wscale, W_k, 1, rvlen, cutoff, ga, gW)
+        return ga, gW.sum(dim=0)
+
     # ---- models/cuda_funcs/calc_maximum_frame.py:24-170 -----------------------------
     def _edge_scores(self, q, k, edges, value):
         E = edges.shape[1]

@@ -162,6 +162,37 @@ def test_framed_proj_forward_backward(workload, nc, angles, wscales):
     assert _lib.read_status() == 0
 
 
+def test_unwindowed_encoding_forward_backward():
+    """frame_method "no" (plain Crystalformer, the baseline of the large-cell workload): every
+    distance Gaussian, no frames."""
+    dev = _cuda()
+    from oracle import oracle as O
+    F = _configure(angle_dim=0)
+    P = make_problem("cfg1")
+    cfg = O.Config(cut_sigma=32, D_ang=0)
+    g = _geometry(P, dev)
+    geo, b = P["geo"], P["batch"]
+    z_w, v_w = O.framed_proj_fwd(cfg, P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"],
+                                 P["W_d"], None, None)
+    a = _t(P["a"], dev).requires_grad_(True)
+    Wd = _t(P["W_d"][None], dev).requires_grad_(True)
+    z, v, _, _ = F.RealPeriodicEncodingWithProjFuncCUDA.apply(a, g["pos_ij"], None, g["tvecs"], g["batch"], g["edges"], 64,
+                                                              14.0, 1.0, Wd, "no", g["rvlen"], -3.5)
+    _close("z", z.detach().cpu().numpy(), z_w)
+    _close("values", v.detach().cpu().numpy(), v_w)
+    rng = np.random.default_rng(23)
+    gz, gv = rng.normal(size=z_w.shape).astype(np.float32), rng.normal(size=v_w.shape).astype(np.float32)
+    ga_w, gW_w, _ = O.framed_proj_bwd(cfg, P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"],
+                                      geo["e_start"], P["W_d"], None, None, z_w, gz, gv)
+    z64, _ = O.framed_proj_fwd(cfg, P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"], P["W_d"],
+                               None, None, dtype=np.float64)
+    ga_64, gW_64, _ = O.framed_proj_bwd(cfg, P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"],
+                                        geo["e_start"], P["W_d"], None, None, z64, gz, gv, dtype=np.float64)
+    (z * _t(gz, dev)).sum().add((v * _t(gv, dev)).sum()).backward()
+    _close_reduction("ga", a.grad.cpu().numpy(), ga_w, ga_64)
+    _close_reduction("gW", Wd.grad.cpu().numpy()[0], gW_w, gW_64)
+
+
 @pytest.mark.parametrize("workload,nc", [("cfg1", None), ("cfg2", 24)])
 def test_attention_forward_backward(workload, nc):
     dev = _cuda()
@@ -208,3 +239,50 @@ def test_mean_pool():
     _close("mean grad", xt.grad.cpu().numpy(), O.mean_bwd(go, P["batch"].sizes))
     out2 = IrregularMeanCUDA.apply(xt.detach(), g["batch"], None)
     assert torch.equal(out2, out.detach())
+
+
+@pytest.mark.parametrize("layers,frame_method", [(1, "max"), (4, "max"), (2, "no")])
+def test_whole_model_against_cpu_oracle(layers, frame_method):
+    """Forward and backward of the whole model (species embedding, encoder layers, mean pooling,
+    MLP head) on the GPU against the same weights run on the host cores through the oracle:
+    8 crystals of 4-16 atoms, float32, symmetry-breaking noise off."""
+    dev = _cuda()
+    import copy
+    from crystalframer_b200 import data, synth
+    from crystalframer_b200.latticeformer import Latticeformer, ModelParams
+    from oracle import cpu_model
+    torch.manual_seed(0)
+    mp = ModelParams(num_layers=layers, symm_break_noise=0.0, frame_method=frame_method,
+                     value_pe_angle_real=64 if frame_method == "max" else 0)
+    cpu = Latticeformer(mp).train()
+    gpu = copy.deepcopy(cpu).to(dev).train()
+    from crystalframer_b200 import cuda_funcs as F
+    F.compile_kernels(2, 8, 16, 64, 64 if frame_method == "max" else 0, 16, True, 0, 1.0, 4.0, 1.0, 1.0, 0.0)
+    b = synth.make_workload("cfg1")
+    y = np.random.default_rng(0).normal(size=(len(b.sizes), 1)).astype(np.float32)
+    tb = data.host_batch(b, y, pinned=False).to(dev, non_blocking=False)
+    out = gpu(tb)
+    loss = (out - tb.y).abs().mean()
+    loss.backward()
+    if frame_method == "no":
+        # the CPU model driver covers the framed path; the plain-Crystalformer operator has its own
+        # parity test, here the wiring is exercised
+        assert torch.isfinite(out).all()
+        assert all(torch.isfinite(p.grad).all() for p in gpu.parameters() if p.grad is not None)
+        return
+    out_c = cpu_model.forward(cpu, b, backend="port")
+    loss_c = (out_c - torch.from_numpy(y)).abs().mean()
+    loss_c.backward()
+    _close("prediction", out.detach().cpu().numpy(), out_c.detach().numpy(), 1e-4, 1e-5)
+    for l in range(layers):
+        assert torch.allclose(gpu.encoder.layers[l].self_attn.gauss_scale.cpu(), cpu.encoder.layers[l].self_attn.gauss_scale,
+                              rtol=1e-4, atol=1e-6)
+    worst = 0.0
+    for (n, pg), (_, pc) in zip(gpu.named_parameters(), cpu.named_parameters()):
+        if pc.grad is None:
+            assert pg.grad is None or float(pg.grad.abs().max()) == 0.0, n
+            continue
+        g, c = pg.grad.cpu().numpy().astype(np.float64), pc.grad.numpy().astype(np.float64)
+        scale = max(np.abs(c).max(), 1e-8)
+        worst = max(worst, float(np.abs(g - c).max() / scale))
+        assert np.abs(g - c).max() <= 2e-3 * scale + 1e-7, f"{n}: max abs diff {np.abs(g - c).max():.3e} at scale {scale:.3e}"

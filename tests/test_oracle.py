@@ -107,6 +107,31 @@ def test_against_reference_cpu_build(problem_cfg1):
     close("gW_a", gWao, gWa.numpy(), 1e-4, 1e-5 * max(1.0, float(gWa.abs().max())))
 
 
+@pytest.mark.skipif(not R.available("cpu"), reason="oracle/_ref not built (reference tree absent)")
+def test_unwindowed_encoding_against_reference_cpu_build(problem_cfg1):
+    """frame_method "no": the reference's real_enc_proj kernels against the oracle with a window
+    wide enough to cover every Gaussian."""
+    P = problem_cfg1
+    geo, b = P["geo"], P["batch"]
+    cfg = O.Config(cut_sigma=32, D_ang=0)
+    rk = R.RefKernels("cpu")
+    T = lambda x: torch.from_numpy(np.ascontiguousarray(x))
+    a, r, tv, bt, e, rv = T(P["a"]), T(geo["pos_ij"]), T(b.trans_vec), T(geo["batch"]), T(geo["edges"]), T(geo["rvlen"])
+    Wd = T(P["W_d"])[None].contiguous()
+    z, val = rk.proj_fwd(a, r, tv, bt, e, 64, 14.0, 1.0, Wd, rv, -3.5)
+    zo, vo = O.framed_proj_fwd(cfg, P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"], P["W_d"],
+                               None, None)
+    close("z", zo, z.numpy(), 1e-6, 1e-6)
+    close("values", vo, val.numpy(), 1e-5, 1e-6)
+    rng = np.random.default_rng(19)
+    gz, gv = rng.normal(size=zo.shape).astype(np.float32), rng.normal(size=vo.shape).astype(np.float32)
+    ga, gW = rk.proj_bwd(a, r, tv, bt, e, 14.0, 1.0, Wd, rv, -3.5, z, T(gz), T(gv))
+    gao, gWo, _ = O.framed_proj_bwd(cfg, P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"],
+                                    geo["e_start"], P["W_d"], None, None, z.numpy(), gz, gv)
+    close("ga", gao, ga.numpy(), 1e-4, 1e-5 * max(1.0, float(ga.abs().max())))
+    close("gW", gWo, gW.numpy(), 1e-4, 1e-5 * max(1.0, float(gW.abs().max())))
+
+
 def test_finite_differences_float64(problem_cfg1):
     P = problem_cfg1
     geo, b, cfg = P["geo"], P["batch"], P["cfg"]
