@@ -4,8 +4,8 @@
 // models/cuda_funcs/calc_maximum_frame.py and the torch ops of
 // models/indexed_lattice_multi_head_attention_cuda.py:475-481 of the reference).
 //
-// grid = (spans of 256 pairs, heads).  A block owns the query atoms whose first pair falls in its
-// span and walks all pairs of those atoms, one pair per thread -- about 256 pairs per block
+// grid = (spans of 192 pairs, heads).  A block owns the query atoms whose first pair falls in its
+// span and walks all pairs of those atoms, one pair per thread -- about 200 pairs per block
 // whatever the crystal sizes, so small crystals do not leave lanes idle.  Each thread sweeps the
 // lattice translations of its pair, finds the pair's candidate image and score, and folds
 // (score, pair index) into its query atom's slot in shared memory with one 64-bit atomicMax -- an
@@ -14,15 +14,17 @@
 //
 // Every float operation that feeds a comparison is written with explicit round-to-nearest
 // intrinsics in the reference's evaluation order (no fused multiply-add), so the selected pair
-// and image can be reproduced bit for bit on a CPU.  Two exact short-cuts skip work that cannot
-// change the result: the symmetry-breaking noise is only drawn when the image could still win,
-// and the second axis' sqrt / divisions / logf are skipped when the Gaussian part of the score
-// alone is already below the running maximum (the logarithm term is never positive).
+// and image can be reproduced bit for bit on a CPU.  Both searches are written as order-independent
+// arg-min / arg-max with "first translation in the reference's loop order wins" on equal values, which
+// is what the reference's sequential loops compute when the symmetry-breaking noise is off; with
+// noise on, the winner is the arg-max of score + noise (the reference's running comparison adds
+// the noise asymmetrically and therefore depends on the visiting order).
 #include "common.cuh"
 
 namespace cfb {
 
-constexpr int kFrPairs = 256;       // pair-list span whose query atoms one block owns
+constexpr int kFrPairs = 192;       // pair-list span whose query atoms one block owns; with crystals of up to 64
+                                    // atoms all pairs of the block's atoms fit one round of kFrThreads threads
 constexpr int kFrMaxRows = 256;     // at most one atom starts per pair of the span
 constexpr int kFrThreads = 256;
 constexpr int kFrHd = 16;
@@ -54,73 +56,114 @@ __device__ __forceinline__ float noise_term(float amp, uint64_t seed, uint64_t t
     return (float)(((double)hash_uniform(seed, tid, t) - 0.5) * (double)amp);
 }
 
-struct Cand { float value; float ux, uy, uz; int img; };
+struct Cand { float value; float ux, uy, uz; int img; float d2raw; };   // d2raw: smallest d^2 > 1e-5 (first axis only)
 
-// nearest image with d^2 > 1e-5 (compute_maximum_frame_each_edge.cu:81-111)
+// centre-out enumeration of one lattice index: k = 0, 1, 2, 3, 4 ... -> n = 0, -1, 1, -2, 2 ...
+__device__ __forceinline__ int centre_out(int k) { return (k & 1) ? -((k + 1) >> 1) : (k >> 1); }
+
+// Nearest image with d^2 > 1e-5 (compute_maximum_frame_each_edge.cu:81-111): arg-min over the
+// translations of d^2 + noise, the first translation in the reference's loop order on equal values.
+// Pass 1 finds the smallest un-perturbed d^2 and, with noise off, the winner itself; with noise on,
+// pass 2 draws the noise only for translations within the noise amplitude of that minimum (nothing
+// else can win).  The direction is computed once, for the winner.
 __device__ __forceinline__ Cand first_axis_candidate(const Cell& cell, float a, int R1, int R2, int R3, float amp,
                                                      uint64_t seed, uint64_t tid)
 {
     Cand c; c.ux = c.uy = c.uz = 0.f; c.img = -1;
-    float d2_min = 1e10f;
-    const float half = 0.5f * amp;
-    int t = 0;
+    float d2raw = 1e10f;
+    int t = 0, best_t = -1;
     for (int n1 = -R1; n1 <= R1; n1++)
         for (int n2 = -R2; n2 <= R2; n2++)
             for (int n3 = -R3; n3 <= R3; n3++, t++) {
                 float dx, dy, dz, d2;
                 separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
-                if ((double)d2 > 1e-5 && __fadd_rn(d2, -half) < d2_min) {
-                    const float cand = amp == 0.0f ? d2 : __fadd_rn(d2, noise_term(amp, seed, tid, (uint32_t)t));
-                    if (d2_min > cand) {
-                        d2_min = cand;
-                        const float d = __fsqrt_rn(d2);
-                        c.ux = __fdiv_rn(dx, d); c.uy = __fdiv_rn(dy, d); c.uz = __fdiv_rn(dz, d);
-                        c.img = t;
+                if ((double)d2 > 1e-5 && d2 < d2raw) { d2raw = d2; best_t = t; }
+            }
+    float d2_min = d2raw;
+    if (amp != 0.0f && best_t >= 0) {
+        d2_min = 1e10f; best_t = -1;
+        const float limit = __fadd_rn(d2raw, __fmul_rn(amp, 1.001f));
+        t = 0;
+        for (int n1 = -R1; n1 <= R1; n1++)
+            for (int n2 = -R2; n2 <= R2; n2++)
+                for (int n3 = -R3; n3 <= R3; n3++, t++) {
+                    float dx, dy, dz, d2;
+                    separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
+                    if ((double)d2 > 1e-5 && d2 <= limit) {
+                        const float cand = __fadd_rn(d2, noise_term(amp, seed, tid, (uint32_t)t));
+                        if (d2_min > cand) { d2_min = cand; best_t = t; }
                     }
                 }
-            }
+    }
+    if (best_t >= 0) {
+        const int L3 = 2 * R3 + 1, L2 = 2 * R2 + 1;
+        const int q = best_t / L3, n3 = best_t - q * L3 - R3, n1 = q / L2 - R1, n2 = q - (q / L2) * L2 - R2;
+        float dx, dy, dz, d2;
+        separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
+        const float d = __fsqrt_rn(d2);
+        c.ux = __fdiv_rn(dx, d); c.uy = __fdiv_rn(dy, d); c.uz = __fdiv_rn(dz, d);
+        c.img = best_t;
+    } else {
+        d2_min = 1e10f;
+    }
     c.value = __fmul_rn(a, d2_min);
+    c.d2raw = d2raw;
     return c;
 }
 
-// second axis (compute_second_frame_each_edge.cu:81-142)
+// Second axis (compute_second_frame_each_edge.cu:81-142): arg-max over the translations of
+// a (d^2 - d^2_min) + log(max(1 - |cos|, 1e-5)) + noise among images with |cos| < 0.9999, the first
+// translation in the reference's loop order on equal values.  Translations are visited centre-out so
+// that a good candidate is met early; the sqrt, divisions and logarithm are skipped for images whose
+// Gaussian part alone cannot reach the running maximum (the logarithm is never positive).
+// d2min_known >= 0: the smallest non-zero squared distance, already found by the first-axis sweep
+// of the same pair (same operations, same value); otherwise it is searched here.
 __device__ __forceinline__ Cand second_axis_candidate(const Cell& cell, float a, int R1, int R2, int R3, float amp,
-                                                      uint64_t seed, uint64_t tid, float f1x, float f1y, float f1z)
+                                                      uint64_t seed, uint64_t tid, float f1x, float f1y, float f1z,
+                                                      float d2min_known)
 {
-    Cand c; c.ux = c.uy = c.uz = 0.f; c.img = -1; c.value = -1e15f;
-    float d2min = 1e10f;
-    for (int n1 = -R1; n1 <= R1; n1++)
-        for (int n2 = -R2; n2 <= R2; n2++)
-            for (int n3 = -R3; n3 <= R3; n3++) {
-                float dx, dy, dz, d2;
-                separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
-                if ((double)d2 > 1e-5) d2min = fminf(d2min, d2);
-            }
-    float max_val = -1e15f;
+    Cand c; c.ux = c.uy = c.uz = 0.f; c.img = -1; c.value = -1e15f; c.d2raw = 0.f;
+    float d2min = d2min_known >= 0.f ? d2min_known : 1e10f;
+    if (d2min_known < 0.f)
+        for (int n1 = -R1; n1 <= R1; n1++)
+            for (int n2 = -R2; n2 <= R2; n2++)
+                for (int n3 = -R3; n3 <= R3; n3++) {
+                    float dx, dy, dz, d2;
+                    separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
+                    if ((double)d2 > 1e-5) d2min = fminf(d2min, d2);
+                }
+    float best = -1e15f;                 // running maximum of score + noise
     const float half = 0.5f * amp;
-    int t = 0;
-    for (int n1 = -R1; n1 <= R1; n1++)
-        for (int n2 = -R2; n2 <= R2; n2++)
-            for (int n3 = -R3; n3 <= R3; n3++, t++) {
+    const int L2 = 2 * R2 + 1, L3 = 2 * R3 + 1;
+    for (int k1 = 0; k1 <= 2 * R1; k1++) {
+        const int n1 = centre_out(k1);
+        for (int k2 = 0; k2 <= 2 * R2; k2++) {
+            const int n2 = centre_out(k2);
+            for (int k3 = 0; k3 <= 2 * R3; k3++) {
+                const int n3 = centre_out(k3);
                 float dx, dy, dz, d2;
                 separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
                 if (!((double)d2 > 1e-5)) continue;
                 const float gauss = __fmul_rn(a, __fsub_rn(d2, d2min));
-                if (gauss <= __fadd_rn(max_val, -half)) continue;      // score <= gauss cannot exceed the maximum
+                if (__fadd_rn(gauss, half) < best) continue;            // score + noise <= gauss + half
                 const float d = __fsqrt_rn(d2);
                 const float vx = __fdiv_rn(dx, d), vy = __fdiv_rn(dy, d), vz = __fdiv_rn(dz, d);
                 const float cs = __fadd_rn(__fadd_rn(__fmul_rn(vx, f1x), __fmul_rn(vy, f1y)), __fmul_rn(vz, f1z));
+                if (!((double)fabsf(cs) < 0.9999)) continue;
                 const float one_m = __fsub_rn(1.0f, fabsf(cs));
                 const float clipped = ((double)one_m > 1e-5) ? one_m : 1e-5f;
                 const float score = __fadd_rn(gauss, logf(clipped));
-                const float nz = amp == 0.0f ? 0.0f : noise_term(amp, seed, tid, (uint32_t)t);
-                if (score > __fadd_rn(max_val, nz) && (double)fabsf(cs) < 0.9999) {
-                    max_val = __fadd_rn(score, nz);
+                const int t = ((n1 + R1) * L2 + (n2 + R2)) * L3 + (n3 + R3);
+                const float noisy = amp == 0.0f ? score : __fadd_rn(score, noise_term(amp, seed, tid, (uint32_t)t));
+                if (noisy > best || (noisy == best && t < c.img)) {
+                    best = noisy;
                     c.ux = vx; c.uy = vy; c.uz = vz;
                     c.value = __fadd_rn(score, __fmul_rn(a, d2min));
                     c.img = t;
                 }
             }
+        }
+    }
     return c;
 }
 
@@ -183,6 +226,10 @@ __global__ void __launch_bounds__(kFrThreads, 2) max_frame_kernel(const FrArgs A
     __syncthreads();
     const int64_t eb = row_start[0], ee = row_start[rows];
     const unsigned long long none = make_key(-1e10f, 0u);      // a score must exceed -1e10 to be selected
+    // a thread meets the same pair in the same round on both axes, so the nearest non-zero distance
+    // found on the first axis is kept for the second (for up to three rounds)
+    const bool keep_d2 = ee - eb <= 3 * kFrThreads;
+    float d2raw0 = -1.f, d2raw1 = -1.f, d2raw2 = -1.f;
 
     for (int axis = (A.mode == 2 ? 2 : 1); axis <= (A.mode == 1 ? 1 : 2); axis++) {
         if (tid < rows) {
@@ -192,7 +239,8 @@ __global__ void __launch_bounds__(kFrThreads, 2) max_frame_kernel(const FrArgs A
         }
         __syncthreads();
         // ---- every pair of these atoms: candidate image, score, arg-max per query atom ----
-        for (int64_t base = eb; base < ee; base += kFrThreads) {
+        int round = 0;
+        for (int64_t base = eb; base < ee; base += kFrThreads, round++) {
             const int64_t e = base + tid;
             int r = 0;
             unsigned long long key = 0ull;
@@ -222,10 +270,16 @@ __global__ void __launch_bounds__(kFrThreads, 2) max_frame_kernel(const FrArgs A
                 const uint64_t noise_id = (uint64_t)(e * H + h);
                 const int pack = row_R[r];
                 const int R1 = pack & 255, R2 = (pack >> 8) & 255, R3 = (pack >> 16) & 255;
-                cd = axis == 1
-                    ? first_axis_candidate(cell, row_a[r], R1, R2, R3, P.noise, A.seed1, noise_id)
-                    : second_axis_candidate(cell, row_a[r], R1, R2, R3, P.noise, A.seed2, noise_id,
-                                            row_f1[r][0], row_f1[r][1], row_f1[r][2]);
+                if (axis == 1) {
+                    cd = first_axis_candidate(cell, row_a[r], R1, R2, R3, P.noise, A.seed1, noise_id);
+                    if (keep_d2) {
+                        if (round == 0) d2raw0 = cd.d2raw; else if (round == 1) d2raw1 = cd.d2raw; else d2raw2 = cd.d2raw;
+                    }
+                } else {
+                    const float known = round == 0 ? d2raw0 : (round == 1 ? d2raw1 : (round == 2 ? d2raw2 : -1.f));
+                    cd = second_axis_candidate(cell, row_a[r], R1, R2, R3, P.noise, A.seed2, noise_id,
+                                               row_f1[r][0], row_f1[r][1], row_f1[r][2], known);
+                }
                 const float s = __fadd_rn(dot, cd.value);
                 if (s > -1e10f) {
                     key = make_key(s, (unsigned)(e - row_start[r]));

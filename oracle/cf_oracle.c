@@ -476,6 +476,11 @@ void FN(cfo_frame2_edges)(const cfo_config* cfg, const real* a_ik, const real* r
                 SEPARATION(r, T); (void)dx; (void)dy; (void)dz;
                 if ((double)d2 > 1e-5) d2min = R_FMIN(d2min, d2);
             }
+            /* arg-max of score + noise, first translation on equal values.  With the noise off this
+             * is what the reference's running comparison (score > max_val + rand, :130) selects;
+             * with noise on the reference adds the noise asymmetrically (to the running maximum of
+             * the earlier winner and again to the challenger's threshold), which makes its result
+             * depend on the loop order -- that case is unpinned and the symmetric rule is used. */
             real max_val = (real)-1e15, bx = 0, by = 0, bz = 0, bval = (real)-1e15;
             int32_t t = 0, best = -1;
             FOR_TRANSLATIONS(R) {
@@ -487,12 +492,12 @@ void FN(cfo_frame2_edges)(const cfo_config* cfg, const real* a_ik, const real* r
                     real one_m = (real)1 - R_FABS(cs);
                     real clipped = ((double)one_m > 1e-5) ? one_m : (real)1e-5;
                     real score = a * (d2 - d2min) + R_LOG(clipped);
-                    real noise = 0;
+                    real noisy = score;
                     if (cfg->symm_break_noise != 0.0f)
-                        noise = (real)(float)(((double)cfo_uniform(seed, (uint64_t)(e * H + k), (uint32_t)t) - 0.5) *
-                                              (double)cfg->symm_break_noise);
-                    if (score > max_val + noise && (double)R_FABS(cs) < 0.9999) {
-                        max_val = score + noise;
+                        noisy = score + (real)(float)(((double)cfo_uniform(seed, (uint64_t)(e * H + k), (uint32_t)t) - 0.5) *
+                                                      (double)cfg->symm_break_noise);
+                    if (noisy > max_val && (double)R_FABS(cs) < 0.9999) {
+                        max_val = noisy;
                         bx = ux; by = uy; bz = uz;
                         bval = score + a * d2min;
                         best = t;

@@ -106,6 +106,31 @@ def test_max_frames(workload, nc):
     _close("frame3", g3.cpu().numpy()[same], want["frame3"][same], 1e-5, 1e-6)
 
 
+def test_max_frames_with_symmetry_breaking_noise():
+    """Noise on: the library and the oracle share the counter-based noise, so the selected pair and
+    image must still agree (first axis exactly; second axis up to logf near-ties)."""
+    dev = _cuda()
+    from oracle import oracle as O
+    F = _configure(noise=1e-5)
+    P = make_problem("cfg1", noise=1e-5)
+    g = _geometry(P, dev)
+    qs = P["q"] / 4.0
+    q, k, a = _t(qs, dev), _t(P["k"], dev), _t(P["a"], dev)
+    np.random.seed(77)
+    f1, se1, si1 = F.max_frame_with_selection(1, q, k, a, g["pos_ij"], g["tvecs"], g["batch"], g["edges"], g["rvlen"], -3.5)
+    f2, se2, si2 = F.max_frame_with_selection(2, q, k, a, g["pos_ij"], g["tvecs"], g["batch"], g["edges"], g["rvlen"], -3.5, f1)
+    np.random.seed(77)
+    draw = lambda: int(np.random.randint(np.iinfo(np.int64).min, np.iinfo(np.int64).max, dtype=np.int64)) & (2 ** 64 - 1)
+    s1, s2 = draw(), draw()
+    want = O.max_frames(P["cfg"], qs, P["k"], P["a"], P["geo"]["pos_ij"], P["batch"].trans_vec, P["geo"]["rvlen"],
+                        P["geo"]["batch"], P["geo"]["edges"], P["geo"]["e_start"], seed1=s1, seed2=s2)
+    assert np.array_equal(se1.cpu().numpy(), want["sel_edge1"]) and np.array_equal(si1.cpu().numpy(), want["sel_image1"])
+    assert np.array_equal(f1.cpu().numpy(), want["frame1"])
+    same = (se2.cpu().numpy() == want["sel_edge2"]) & (si2.cpu().numpy() == want["sel_image2"])
+    assert same.mean() >= 0.995
+    _configure(noise=0.0)
+
+
 def _frames(P):
     from oracle import oracle as O
     fr = O.max_frames(P["cfg"], P["q"] / 4.0, P["k"], P["a"], P["geo"]["pos_ij"], P["batch"].trans_vec,
