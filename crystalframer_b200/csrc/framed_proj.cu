@@ -223,7 +223,7 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
                                 lo_pack |= lo << (8 * (x + 1));
                             }
                         }
-                        tb[lane] = make_float4(w, xd, xa[0], xa[1]);
+                        tb[lane] = make_float4(arg * kLog2e, xd, xa[0], xa[1]);     // log2 of the weight
                         tb[32 + lane] = make_float4(xa[2], __int_as_float(lo_pack), d2, 0.f);
                     }
                 }
@@ -233,19 +233,19 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
                     const int src = __ffs(mask) - 1;
                     mask &= mask - 1;
                     const float4 r0 = tb[src], r1 = tb[32 + src];
-                    const float w = r0.x, d2 = r1.z;
+                    const float lw = r0.x, d2 = r1.z;          // Gaussian times weight = ex2(lw - b*b)
                     const int lo_pack = __float_as_int(r1.y);
                     {   // distance basis
                         const int lo = (int)__byte_perm((unsigned)lo_pack, 0u, 0x4440);
                         const bool in0 = (unsigned)(lane - lo) < win_d, in1 = (unsigned)(lane + 32 - lo) < win_d;
                         if (!wide_d) {
                             const float b = r0.y + (in1 ? cd_hi : cd_lo);
-                            const float g = ex2_approx(-b * b) * w;
+                            const float g = ex2_approx(fmaf(-b, b, lw));
                             if (in0) { sd[0] += g; if (BWD) qd[0] = fmaf(g, d2, qd[0]); }
                             if (in1) { sd[1] += g; if (BWD) qd[1] = fmaf(g, d2, qd[1]); }
                         } else {
                             const float b0 = r0.y + cd_lo, b1 = r0.y + cd_hi;
-                            const float g0 = ex2_approx(-b0 * b0) * w, g1 = ex2_approx(-b1 * b1) * w;
+                            const float g0 = ex2_approx(fmaf(-b0, b0, lw)), g1 = ex2_approx(fmaf(-b1, b1, lw));
                             if (in0) { sd[0] += g0; if (BWD) qd[0] = fmaf(g0, d2, qd[0]); }
                             if (in1) { sd[1] += g1; if (BWD) qd[1] = fmaf(g1, d2, qd[1]); }
                         }
@@ -256,7 +256,7 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
                         for (int x = 0; x < 3; x++) {
                             const int lo = (int)__byte_perm((unsigned)lo_pack, 0u, 0x4441 + x);
                             const float b0 = xa[x] - ca_lo, b1 = xa[x] - ca_hi;
-                            const float g0 = ex2_approx(-b0 * b0) * w, g1 = ex2_approx(-b1 * b1) * w;
+                            const float g0 = ex2_approx(fmaf(-b0, b0, lw)), g1 = ex2_approx(fmaf(-b1, b1, lw));
                             if ((unsigned)(lane - lo) < win_a) { sa[x][0] += g0; if (BWD) qa[x][0] = fmaf(g0, d2, qa[x][0]); }
                             if ((unsigned)(lane + 32 - lo) < win_a) { sa[x][1] += g1; if (BWD) qa[x][1] = fmaf(g1, d2, qa[x][1]); }
                         }
