@@ -137,9 +137,10 @@ def measure_pipe_peaks(dev):
 
 def lattice_terms(model, tb):
     """Number of (pair, head, translation) terms per layer for this batch and these weights."""
-    from crystalframer_b200 import attention
+    from crystalframer_b200 import attention, encoder
     rec = []
     orig = attention.gaussian_coefficients
+    fused, encoder.FUSED_LAYER = encoder.FUSED_LAYER, False      # the operator path exposes the coefficients
 
     def spy(*a, **k):
         out = orig(*a, **k)
@@ -151,6 +152,7 @@ def lattice_terms(model, tb):
             model(tb)
     finally:
         attention.gaussian_coefficients = orig
+        encoder.FUSED_LAYER = fused
     T = tb.trans_vec
     vcell = torch.linalg.det(T)
     rec_v = torch.stack([torch.linalg.cross(T[:, 1], T[:, 2]), torch.linalg.cross(T[:, 2], T[:, 0]),

@@ -34,6 +34,8 @@ SIGNATURES = {
     "cfb200_framed_proj_bwd_workspace_bytes": (i64, [i64, i64]),
     "cfb200_edge_index": (ctypes.c_int, [vp, i64, i64, i64, vp, vp, vp, vp, vp]),
     "cfb200_csr_offsets": (ctypes.c_int, [vp, i64, i64, vp, vp]),
+    "cfb200_gauss_coef_fwd": (ctypes.c_int, [vp, vp, vp, i64, f32, f32, f32, vp, vp, vp]),
+    "cfb200_gauss_coef_bwd": (ctypes.c_int, [vp, vp, vp, i64, f32, f32, f32, vp, vp, vp, vp, vp]),
     "cfb200_max_frame": (ctypes.c_int, [ctypes.c_int] + [vp] * 9 + [i64, i64, f32, u64] + [vp] * 5),
     "cfb200_max_frames": (ctypes.c_int, [vp] * 9 + [i64, i64, f32, u64, u64] + [vp] * 4),
     "cfb200_framed_proj_fwd": (ctypes.c_int, [vp] * 6 + [i64, i64, f32, f32] + [vp] * 10),

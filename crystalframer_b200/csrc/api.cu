@@ -8,6 +8,7 @@
 #include "frames.cu"
 #include "dpa.cu"
 #include "pool_index.cu"
+#include "coef.cu"
 
 namespace cfb {
 
@@ -354,6 +355,40 @@ int cfb200_dpa_bwd(const float* q_scaled, const float* k, const float* v, const 
     A.out = const_cast<float*>(out); A.lse = const_cast<float*>(lse); A.gout = gout;
     A.gq = gq; A.gk = gk; A.gv = gv; A.gz = gz; A.gb = values ? gvalues : nullptr;
     return cfb::dpa_bwd(A, P, S(stream));
+}
+
+static int coef_args(cfb::CoefArgs& A, const float* q, const float* w, const float* gauss_scale, int64_t N, float lb,
+                     float beta, float scale_real)
+{
+    if (!g_configured) return CFB200_E_NOT_CONFIGURED;
+    if (N < 0 || !(lb < 1.0f) || !(scale_real > 0.0f)) return CFB200_E_SHAPE;
+    if (!q || !w) return N > 0 ? CFB200_E_NULL : CFB200_OK;
+    memset(&A, 0, sizeof(A));
+    A.q = q; A.w = w; A.gauss_scale = gauss_scale; A.N = N; A.H = g_cfg.num_heads;
+    A.lb = lb; A.beta = beta; A.cmul = -0.5f / (scale_real * scale_real); A.qscale = 1.0f / sqrtf((float)g_cfg.head_dim);
+    return CFB200_OK;
+}
+
+int cfb200_gauss_coef_fwd(const float* q, const float* w, const float* gauss_scale, int64_t N, float lb, float beta,
+                          float scale_real, float* a, float* q_scaled, void* stream)
+{
+    cfb::CoefArgs A;
+    int rc = coef_args(A, q, w, gauss_scale, N, lb, beta, scale_real);
+    if (rc != CFB200_OK || N == 0) return rc;
+    if (!a || !q_scaled) return CFB200_E_NULL;
+    A.a = a; A.qs = q_scaled;
+    return cfb::coef_fwd(A, S(stream));
+}
+
+int cfb200_gauss_coef_bwd(const float* q, const float* w, const float* gauss_scale, int64_t N, float lb, float beta,
+                          float scale_real, const float* ga, const float* gq_scaled, float* gq, float* gw, void* stream)
+{
+    cfb::CoefArgs A;
+    int rc = coef_args(A, q, w, gauss_scale, N, lb, beta, scale_real);
+    if (rc != CFB200_OK) return rc;
+    if (!gw || (N > 0 && (!ga || !gq_scaled || !gq))) return CFB200_E_NULL;
+    A.ga = ga; A.gqs = gq_scaled; A.gq = gq; A.gw = gw;
+    return cfb::coef_bwd(A, S(stream));
 }
 
 int cfb200_probe_throughput(int kind, int blocks, int iters, float* sink, void* stream)

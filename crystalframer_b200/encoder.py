@@ -13,9 +13,14 @@ from torch.nn import Dropout, Identity, LayerNorm, Linear, Module, ModuleList
 from torch.nn.init import constant_, xavier_uniform_
 
 from . import _lib
+from . import fused_layer
 from .attention import CrystalformerMultiheadAttentionCUDA
 from .cuda_funcs import compile_kernels, register_csr
 from .latticeformer_params import LatticeformerParams
+
+
+# run default-structure layers as one autograd node (fused_layer.py); off = operator by operator
+FUSED_LAYER = True
 
 
 def build_pair_list(sizes: Tensor, counts=None):
@@ -107,6 +112,7 @@ class CrystalformerEncoderLayerCUDA(Module):
         self.dropout1 = Dropout(dropout) if dropout > 0 else Identity()
         self.dropout2 = Dropout(dropout) if dropout > 0 else Identity()
         self.activation = _activation(activation)
+        self._fused_meta = None
         xavier_uniform_(self.linear1.weight)
         xavier_uniform_(self.linear2.weight)
         constant_(self.linear1.bias, 0)
@@ -120,9 +126,38 @@ class CrystalformerEncoderLayerCUDA(Module):
                       self.self_attn.v_proj_weight):
                 w.mul_(s)
 
+    def _fused_forward(self, x, batch, edges, pos_ij, trans, rvecs):
+        """The whole layer as one autograd node (fused_layer.FusedEncoderLayerFunc), or None when
+        this layer's configuration or state is outside what that path covers."""
+        if not (FUSED_LAYER and x.is_cuda and isinstance(self.norm1, Identity) and isinstance(self.norm2, Identity)
+                and isinstance(self.dropout, Identity) and self.activation is F.relu):
+            return None
+        attn = self.self_attn
+        if not getattr(attn.gauss_scale, "_cf_ready", False):
+            return None          # the first training forward measures the coefficient statistics
+        if self._fused_meta is None:
+            self._fused_meta = fused_layer.layer_meta(attn) or False
+        if self._fused_meta is False:
+            return None
+        geo = getattr(edges, "_cf_geometry", None)
+        if geo is None or geo.pos_ij is not pos_ij:
+            rvlen = torch.norm(rvecs, 2, dim=-1).contiguous() if self._fused_meta["cutoff"] != 0.0 else None
+            geo = fused_layer.LayerGeometry(pos_ij.contiguous(), trans.contiguous(), batch.contiguous(),
+                                            edges.contiguous(), rvlen)
+            edges._cf_geometry = geo
+        return fused_layer.FusedEncoderLayerFunc.apply(
+            x, attn.q_proj_weight, attn.k_proj_weight, attn.v_proj_weight, attn.in_proj_bias, attn.lattice_pos_weights,
+            attn.gauss_scale, attn.out_proj.weight, attn.out_proj.bias, attn.pe_dist_proj, attn.proj_angle1,
+            attn.proj_angle2, attn.proj_angle3, self.linear1.weight, self.linear1.bias, self.linear2.weight,
+            self.linear2.bias, geo, self._fused_meta)
+
     def forward(self, src, batch, edges, pos_ij=None, dist2_min=None, trans=None, kr_base=None, rvecs=None,
                 vcell=None, onehot=None, this_epoch=None):
         x = src
+        if dist2_min is None and pos_ij is not None and rvecs is not None:
+            fused = self._fused_forward(x, batch, edges, pos_ij, trans, rvecs)
+            if fused is not None:
+                return fused
         if self.norm_first:
             x = x + self._sa_block(self.norm1(x), batch, edges, pos_ij, dist2_min, trans, kr_base, rvecs, vcell, onehot, this_epoch)
             x = x + self._ff_block(self.norm2(x))

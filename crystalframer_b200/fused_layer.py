@@ -1,0 +1,139 @@
+"""One autograd Function for a whole encoder layer.
+
+The reference runs an encoder layer as ~35 separately tracked torch operations plus its CuPy
+Functions (models/indexed_latticeformer_encoder.py:848-890 and
+models/indexed_lattice_multi_head_attention_cuda.py:737-996).  At 2-3 k atoms per batch the
+GPU work of most of those operations is a few microseconds, so the step time is set by host-side
+dispatch and autograd bookkeeping.  This Function performs the same arithmetic -- input
+projections, Gaussian coefficients, max frames, lattice-sum bias and value encoding, ragged
+attention, output projection, residuals and the feed-forward block -- with one graph node: the
+dense layers stay on cuBLAS through ``torch.addmm`` / ``torch.mm``, everything specific to the
+periodic attention runs in libcfb200, and the backward pass is written out by hand.
+
+Used by ``CrystalformerEncoderLayerCUDA.forward`` when the layer has the default structure
+(real-space domain, "max" frames, coefficients from q, no dropout, no layer norm, ReLU); any other
+configuration takes the operator-by-operator path.
+"""
+import math
+
+import torch
+
+from . import _lib
+from .cuda_funcs.common import csr_offsets
+from .cuda_funcs.max_frame import _draw_seed
+
+
+class LayerGeometry:
+    """Per-batch tensors shared by all layers."""
+    __slots__ = ("pos_ij", "tvecs", "batch", "edges", "e_start", "rvlen", "N", "E")
+
+    def __init__(self, pos_ij, tvecs, batch, edges, rvlen):
+        self.pos_ij, self.tvecs, self.batch, self.edges, self.rvlen = pos_ij, tvecs, batch, edges, rvlen
+        self.N, self.E = batch.shape[0], edges.shape[1]
+        self.e_start = csr_offsets(edges, self.N)
+
+
+class FusedEncoderLayerFunc(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, Wq, Wk, Wv, b_in, w_lat, gauss_scale, Wo, bo, Wd, W1, W2, W3, Wf1, bf1, Wf2, bf2, geo, meta):
+        H, hd = meta["H"], meta["hd"]
+        N, E, dev = geo.N, geo.E, x.device
+        D = H * hd
+        p, ip = _lib.ptr, _lib.iptr
+        x = x.contiguous()
+        bq, bk, bv = b_in[:D], b_in[D:2 * D], b_in[2 * D:]
+        q = torch.addmm(bq, x, Wq.t())
+        k = torch.addmm(bk, x, Wk.t())
+        v = torch.addmm(bv, x, Wv.t())
+        new = lambda *shape: torch.empty(shape, device=dev, dtype=torch.float32)
+        a, qs = new(N, H), new(N, H, hd)
+        _lib.invoke("cfb200_gauss_coef_fwd", 1, dev, p(q), p(w_lat), p(gauss_scale), N, meta["lb"], meta["beta"],
+                    meta["scale_real"], p(a), p(qs))
+        f = new(3, N, H, 3)
+        s1, s2 = _draw_seed(), _draw_seed()
+        _lib.invoke("cfb200_max_frames", 1, dev, p(qs), p(k), p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
+                    ip(geo.batch), ip(geo.edges), ip(geo.e_start), N, E, meta["cutoff"], s1, s2, p(f[0]), p(f[1]), p(f[2]))
+        z, val = new(E, H), new(E, H, hd)
+        Wd3, W13, W23, W33 = Wd[0], W1[0], W2[0], W3[0]
+        _lib.invoke("cfb200_framed_proj_fwd", 1, dev, p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen), ip(geo.batch),
+                    ip(geo.edges), N, E, meta["dist_max"], meta["cutoff"], p(Wd3), p(W13), p(W23), p(W33),
+                    p(f[0]), p(f[1]), p(f[2]), p(z), p(val))
+        o, lse = new(N, H, hd), new(N, H)
+        _lib.invoke("cfb200_dpa_fwd", 1, dev, p(qs), p(k), p(v), p(z), p(val), ip(geo.edges), ip(geo.e_start), N, E,
+                    p(o), p(lse), None)
+        x1 = torch.addmm(bo, o.view(N, D), Wo.t()).add_(x)
+        h = torch.addmm(bf1, x1, Wf1.t()).relu_()
+        x2 = torch.addmm(bf2, h, Wf2.t()).add_(x1)
+        ctx.save_for_backward(x, Wq, Wk, Wv, w_lat, gauss_scale, Wo, Wd, W1, W2, W3, Wf1, Wf2, q, qs, k, v, a, f, z, val,
+                              o, lse, x1, h)
+        ctx.geo, ctx.meta = geo, meta
+        return x2
+
+    @staticmethod
+    def backward(ctx, g):
+        (x, Wq, Wk, Wv, w_lat, gauss_scale, Wo, Wd, W1, W2, W3, Wf1, Wf2, q, qs, k, v, a, f, z, val, o, lse, x1,
+         h) = ctx.saved_tensors
+        geo, meta = ctx.geo, ctx.meta
+        H, hd = meta["H"], meta["hd"]
+        N, E, dev = geo.N, geo.E, x.device
+        D = H * hd
+        p, ip = _lib.ptr, _lib.iptr
+        new = lambda *shape: torch.empty(shape, device=dev, dtype=torch.float32)
+        g = g.contiguous()
+        # feed-forward block and second residual
+        gWf2 = g.t().mm(h)
+        gbf2 = g.sum(0)
+        gh = torch.ops.aten.threshold_backward(g.mm(Wf2), h, 0)
+        gWf1 = gh.t().mm(x1)
+        gbf1 = gh.sum(0)
+        gx1 = torch.addmm(g, gh, Wf1)
+        # output projection and first residual
+        gWo = gx1.t().mm(o.view(N, D))
+        gbo = gx1.sum(0)
+        go = gx1.mm(Wo)
+        # attention, lattice sums, coefficients
+        gqs, gk, gv, gz, gval = new(N, H, hd), new(N, H, hd), new(N, H, hd), new(E, H), new(E, H, hd)
+        _lib.invoke("cfb200_dpa_bwd", 2, dev, p(qs), p(k), p(v), p(z), p(val), ip(geo.edges), ip(geo.e_start), N, E,
+                    p(o), p(lse), p(go), p(gqs), p(gk), p(gv), p(gz), p(gval))
+        ga = new(N, H)
+        gW = [torch.empty_like(W[0]) for W in (Wd, W1, W2, W3)]
+        lib = _lib.lib()
+        nbytes = int(lib.cfb200_framed_proj_bwd_workspace_bytes(N, E))
+        ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
+        _lib.invoke("cfb200_framed_proj_bwd", 3, dev, p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen), ip(geo.batch),
+                    ip(geo.edges), ip(geo.e_start), N, E, meta["dist_max"], meta["cutoff"], p(Wd[0]), p(W1[0]), p(W2[0]),
+                    p(W3[0]), p(f[0]), p(f[1]), p(f[2]), p(z), p(gz), p(gval), p(ga), p(gW[0]), p(gW[1]), p(gW[2]),
+                    p(gW[3]), ws.data_ptr(), nbytes)
+        gq, gw = new(N, H, hd), torch.empty_like(w_lat)
+        _lib.invoke("cfb200_gauss_coef_bwd", 1, dev, p(q), p(w_lat), p(gauss_scale), N, meta["lb"], meta["beta"],
+                    meta["scale_real"], p(ga), p(gqs), p(gq), p(gw))
+        # input projections
+        gq2, gk2, gv2 = gq.view(N, D), gk.view(N, D), gv.view(N, D)
+        gWq, gWk, gWv = gq2.t().mm(x), gk2.t().mm(x), gv2.t().mm(x)
+        gb_in = torch.cat([gq2.sum(0), gk2.sum(0), gv2.sum(0)])
+        gx = torch.addmm(gx1, gq2, Wq).addmm_(gk2, Wk).addmm_(gv2, Wv)
+        return (gx, gWq, gWk, gWv, gb_in, gw, None, gWo, gbo, gW[0].unsqueeze(0), gW[1].unsqueeze(0), gW[2].unsqueeze(0),
+                gW[3].unsqueeze(0), gWf1, gbf1, gWf2, gbf2, None, None)
+
+
+def layer_meta(attn):
+    """Scalars of the attention module in the form the Function takes; None if the layer's
+    configuration is outside what the fused path covers."""
+    P = attn.params
+    if P.domain != "real" or P.frame_method != "max" or P.gauss_state != "q" or not P.normalize_gauss:
+        return None
+    if attn.in_proj_bias is None or attn.pe_dist_proj is None or attn.proj_angle1 is None or attn.dropout != 0.0:
+        return None
+    if attn.kdim != attn.embed_dim or attn.vdim != attn.embed_dim:
+        return None
+    dist_max = P.value_pe_dist_max
+    if dist_max < 0:
+        dist_max = (-dist_max) * P.scale_real
+    if P.adaptive_cutoff_sigma < 0:
+        cutoff = float(P.adaptive_cutoff_sigma)
+    elif P.adaptive_cutoff_sigma > 0:
+        cutoff = float(P.scale_real * P.gauss_lb_real ** (-0.5) * P.adaptive_cutoff_sigma)
+    else:
+        cutoff = 0.0
+    return dict(H=attn.num_heads, hd=attn.head_dim, lb=float(P.gauss_lb_real), beta=float(P.positive_func_beta),
+                scale_real=float(P.scale_real), dist_max=float(dist_max), cutoff=cutoff)

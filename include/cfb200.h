@@ -82,6 +82,19 @@ int cfb200_edge_index(const int64_t* sizes, int64_t B, int64_t N, int64_t E, int
 /* CSR offsets from a pair list sorted by query atom (models/cuda_funcs/fused_dpa.py:24-26). */
 int cfb200_csr_offsets(const int64_t* edge_i, int64_t E, int64_t N, int64_t* e_start, void* stream);
 
+/* Replaces the torch operations that turn queries into Gaussian coefficients
+ * (models/indexed_lattice_multi_head_attention_cuda.py:896-940, gauss_state "q") and the two
+ * divisions of q by sqrt(head_dim) (:179, :447): a (N,H) = [(1-lb) elu(((q.w) + shift) scale
+ * beta/(1-lb)) + 1] * (-1/(2 scale_real^2)) and q_scaled (N,H,head_dim).  w is lattice_pos_weights
+ * (H*head_dim); gauss_scale points to [scale, shift] on the device (the module's gauss_scale
+ * parameter) or is NULL for no normalisation.  The backward takes the gradients w.r.t. a and
+ * q_scaled and returns those w.r.t. q (N,H,head_dim) and w (H*head_dim, summed in a fixed order). */
+int cfb200_gauss_coef_fwd(const float* q, const float* w, const float* gauss_scale, int64_t N, float lb,
+                          float beta, float scale_real, float* a, float* q_scaled, void* stream);
+int cfb200_gauss_coef_bwd(const float* q, const float* w, const float* gauss_scale, int64_t N, float lb,
+                          float beta, float scale_real, const float* ga, const float* gq_scaled,
+                          float* gq, float* gw, void* stream);
+
 /* Replaces ComputeFrame1MaximumMethodCUDA.forward / ComputeFrame2MaximumMethodCUDA.forward
  * (models/cuda_funcs/calc_maximum_frame.py:24-170) with kernels
  * compute_maximum_frame_each_edge.cu / compute_second_frame_each_edge.cu and the per-atom

@@ -311,3 +311,33 @@ def test_whole_model_against_cpu_oracle(layers, frame_method):
         scale = max(np.abs(c).max(), 1e-8)
         worst = max(worst, float(np.abs(g - c).max() / scale))
         assert np.abs(g - c).max() <= 2e-3 * scale + 1e-7, f"{n}: max abs diff {np.abs(g - c).max():.3e} at scale {scale:.3e}"
+
+
+def test_fused_layer_matches_operator_path():
+    """The one-node encoder layer against the operator-by-operator path: same outputs, same
+    gradients for the input and for every parameter."""
+    dev = _cuda()
+    import copy
+    from crystalframer_b200 import data, encoder, synth
+    from crystalframer_b200.latticeformer import Latticeformer, ModelParams
+    torch.manual_seed(3)
+    model = Latticeformer(ModelParams(num_layers=2, symm_break_noise=0.0)).to(dev).train()
+    b = synth.make_workload("cfg2", num_crystals=16)
+    y = np.random.default_rng(1).normal(size=(len(b.sizes), 1)).astype(np.float32)
+    tb = data.host_batch(b, y, pinned=False).to(dev, non_blocking=False)
+    with torch.no_grad():
+        model(tb)                                   # measures gauss_scale, after which the fused path is eligible
+    results = []
+    for fused in (False, True):
+        encoder.FUSED_LAYER = fused
+        model.zero_grad(set_to_none=True)
+        out = model(tb)
+        (out - tb.y).abs().mean().backward()
+        results.append((out.detach().clone(), {n: p.grad.detach().clone() for n, p in model.named_parameters() if p.grad is not None}))
+    encoder.FUSED_LAYER = True
+    (o0, g0), (o1, g1) = results
+    assert torch.allclose(o0, o1, rtol=1e-5, atol=1e-6)
+    assert set(g0) == set(g1)
+    for n in g0:
+        scale = float(g0[n].abs().max()) + 1e-12
+        assert float((g0[n] - g1[n]).abs().max()) <= 1e-4 * scale + 1e-9, n
