@@ -7,8 +7,8 @@ arguments, same parameter names, shapes and initialisation (so released checkpoi
 data-dependent ``gauss_scale`` state.  Input / output projections and the Gaussian-coefficient
 pipeline stay in PyTorch; everything between them runs in libcfb200.
 
-Only the real-space domain with frame methods "max" (CrystalFramer) and "no" (plain
-Crystalformer distance encoding) is implemented.
+Only the real-space domain is implemented, with frame methods "max" and "weighted_pca"
+(CrystalFramer) and "no" (plain Crystalformer distance encoding).
 """
 import math
 from typing import Optional, Tuple
@@ -22,7 +22,7 @@ from torch.nn.modules.linear import NonDynamicallyQuantizableLinear
 
 from .cuda_funcs import (ComputeFrame1MaximumMethodCUDA, ComputeFrame2MaximumMethodCUDA,
                          FusedDotProductAttentionCUDA, RealEncodingWithFramedProjFuncCUDA,
-                         RealPeriodicEncodingWithProjFuncCUDA, max_frames_fused)
+                         RealPeriodicEncodingWithProjFuncCUDA, max_frames_fused, weighted_pca_frames)
 from .latticeformer_params import LatticeformerParams
 
 # use the single-launch frame construction instead of the two Functions plus torch ops
@@ -76,6 +76,11 @@ def compute_real_domain_attn_frame_proj(q, k, v, batch_q, batch_kv, edges, pos, 
     if params.frame_method == "max":
         f1, f2, f3 = compute_frame_maximum_method_(q, k, None, alpha, pos, dist2_min, tvecs, batch_q, edges,
                                                    pe_dist_proj, K, dist_max, wscale, "max", this_epoch, *adap)
+        W1, W2, W3 = proj_angle1, proj_angle2, proj_angle3
+    elif params.frame_method == "weighted_pca":
+        with torch.no_grad():
+            qs = q / math.sqrt(q.shape[-1])
+            f1, f2, f3 = weighted_pca_frames(qs, k, alpha, pos, tvecs, batch_q, edges, *(rv_args or (None, None)))[:3]
         W1, W2, W3 = proj_angle1, proj_angle2, proj_angle3
     elif params.frame_method == "no":
         # plain Crystalformer: un-windowed distance encoding, no frames, no coefficients

@@ -9,6 +9,7 @@
 #include "dpa.cu"
 #include "pool_index.cu"
 #include "coef.cu"
+#include "sigma.cu"
 
 namespace cfb {
 
@@ -212,6 +213,34 @@ int cfb200_max_frames(const float* q_scaled, const float* k, const float* a_ik, 
     if (N > 0 && (!frame1 || !frame2 || !frame3)) return CFB200_E_NULL;
     return frames_common(3, q_scaled, k, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, N, E, cutoff_radius,
                          seed1, seed2, nullptr, frame1, frame2, frame3, nullptr, nullptr, stream);
+}
+
+int64_t cfb200_sigma_frames_workspace_bytes(int64_t N, int64_t E)
+{
+    if (!g_configured || N < 0 || E < 0) return -1;
+    return (int64_t)((size_t)E * g_cfg.num_heads * 11 * sizeof(float));
+}
+
+int cfb200_sigma_frames(const float* q_scaled, const float* k, const float* a_ik, const float* pos_ij,
+                        const float* tvecs, const float* rvlen, const int64_t* batch, const int64_t* edges,
+                        const int64_t* e_start, int64_t N, int64_t E, float cutoff_radius, uint64_t seed_noise,
+                        uint64_t seed_sign, float* frame1, float* frame2, float* frame3, void* workspace,
+                        int64_t workspace_bytes, void* stream)
+{
+    if (N < 0 || E < 0) return CFB200_E_SHAPE;
+    cfb::Params P;
+    int rc = make_params(1.0f, cutoff_radius, P);
+    if (rc != CFB200_OK) return rc;
+    if (N == 0 || E == 0) return CFB200_OK;
+    if (!q_scaled || !k || !a_ik || !pos_ij || !tvecs || !batch || !edges || !e_start || !frame1 || !frame2 || !frame3)
+        return CFB200_E_NULL;
+    if (cutoff_radius != 0.0f && rvlen == nullptr) return CFB200_E_NULL;
+    if (workspace == nullptr || workspace_bytes < cfb200_sigma_frames_workspace_bytes(N, E)) return CFB200_E_WORKSPACE;
+    cfb::SgArgs A;
+    A.q = q_scaled; A.k = k; A.a_ik = a_ik; A.pos_ij = pos_ij; A.tvecs = tvecs; A.rvlen = rvlen; A.batch = batch;
+    A.edges = edges; A.e_start = e_start; A.N = N; A.E = E; A.seed_noise = seed_noise; A.seed_sign = seed_sign;
+    A.ws = reinterpret_cast<float*>(workspace); A.frame1 = frame1; A.frame2 = frame2; A.frame3 = frame3;
+    return cfb::sigma_frames(A, P, S(stream));
 }
 
 static int fp_args(cfb::FpArgs& A, const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,

@@ -4,7 +4,7 @@ from .kernel_manager import KernelManager, compile_kernels, current_config
 from .framed_proj import RealEncodingWithFramedProjFuncCUDA
 from .enc_proj import RealPeriodicEncodingWithProjFuncCUDA
 from .max_frame import (ComputeFrame1MaximumMethodCUDA, ComputeFrame2MaximumMethodCUDA,
-                        max_frame_with_selection, max_frames_fused)
+                        max_frame_with_selection, max_frames_fused, weighted_pca_frames)
 from .fused_dpa import FusedDotProductAttentionCUDA, attention_probabilities
 from .irregular_mean import IrregularMeanCUDA
 from .common import csr_offsets, register_csr
@@ -17,6 +17,6 @@ __all__ = [
     "KernelManager", "compile_kernels", "current_config", "FusedDotProductAttentionCUDA",
     "ComputeFrame1MaximumMethodCUDA", "ComputeFrame2MaximumMethodCUDA", "RealEncodingWithFramedProjFuncCUDA",
     "RealPeriodicEncodingWithProjFuncCUDA",
-    "IrregularMeanCUDA", "max_frame_with_selection", "max_frames_fused", "attention_probabilities",
+    "IrregularMeanCUDA", "max_frame_with_selection", "max_frames_fused", "weighted_pca_frames", "attention_probabilities",
     "csr_offsets", "register_csr", "CUPY_AVAILABLE",
 ]

@@ -87,3 +87,30 @@ def max_frames_fused(q, k, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_n
                 p(qq), p(kk), p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), ip(e_start), N, E, cutoff, s1, s2,
                 p(f[0]), p(f[1]), p(f[2]))
     return f[0], f[1], f[2]
+
+
+def weighted_pca_frames(q, k, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_n, cutoff_radius):
+    """Weighted-PCA frames (frame1, frame2, frame3), non-differentiable.  ``q`` is q / sqrt(head_dim).
+    Stands for the reference's RealPeriodicEncodingWithProjFuncCUDA(frame_method="weighted_pca"),
+    FusedDotProductAttentionSigmaMatCUDA and the eigen-decomposition block of
+    models/indexed_lattice_multi_head_attention_cuda.py:656-725.  Two seeds are drawn from numpy's
+    global generator (the reference draws two for its kernels); the row signs, which the reference
+    takes from torch.randint, use one more draw from torch's generator."""
+    N, H = a_ik.shape
+    E = edge_ij_e.shape[1]
+    dev = a_ik.device
+    a, qq, kk = f32c(a_ik), f32c(q), f32c(k)
+    pos, tv, rv = f32c(rpos_ij_e), f32c(tvecs_n), f32c(rvlen_n)
+    batch, edges = batch_i.contiguous(), edge_ij_e.contiguous()
+    e_start = csr_offsets(edges, N)
+    cutoff = 0.0 if cutoff_radius is None or rvlen_n is None else float(cutoff_radius)
+    _draw_seed()                                   # select_edges' seed in the reference (its output is never read)
+    seed_noise = _draw_seed()
+    seed_sign = int(torch.randint(0, 2 ** 62, (1,)).item())
+    f = torch.empty((3, N, H, 3), device=dev, dtype=torch.float32)
+    nbytes = int(_lib.lib().cfb200_sigma_frames_workspace_bytes(N, E))
+    ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
+    p, ip = _lib.ptr, _lib.iptr
+    _lib.invoke("cfb200_sigma_frames", 2, dev, p(qq), p(kk), p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges),
+                ip(e_start), N, E, cutoff, seed_noise, seed_sign, p(f[0]), p(f[1]), p(f[2]), ws.data_ptr(), nbytes)
+    return f[0], f[1], f[2], seed_noise, seed_sign

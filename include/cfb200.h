@@ -116,6 +116,24 @@ int cfb200_max_frames(const float* q_scaled, const float* k, const float* a_ik,
                       int64_t N, int64_t E, float cutoff_radius, uint64_t seed1, uint64_t seed2,
                       float* frame1, float* frame2, float* frame3, void* stream);
 
+/* Weighted-PCA frames.  Replaces RealPeriodicEncodingWithProjFuncCUDA with
+ * frame_method "weighted_pca" (models/cuda_funcs/real_space_enc_proj.py:80-125; kernels
+ * select_edges.cu, real_enc_sigma_fwd.cu), FusedDotProductAttentionSigmaMatCUDA
+ * (models/cuda_funcs/fused_dpa_sigmamat.py; kernel fused_dpa_sigmamat_fwd.cu) and the
+ * determinant / eigen-decomposition / sign block of
+ * models/indexed_lattice_multi_head_attention_cuda.py:656-725.  Outputs frame1..3 (N,H,3), a
+ * right-handed orthonormal triad per (atom, head).  The pooling attention uses the lattice-sum
+ * log-weights as its bias (the reference hands it an uninitialised buffer); eigenvector signs are
+ * fixed by "largest component positive", row signs come from seed_sign.  workspace: at least
+ * cfb200_sigma_frames_workspace_bytes(N,E) bytes. */
+int64_t cfb200_sigma_frames_workspace_bytes(int64_t N, int64_t E);
+int cfb200_sigma_frames(const float* q_scaled, const float* k, const float* a_ik, const float* pos_ij,
+                        const float* tvecs, const float* rvlen, const int64_t* batch,
+                        const int64_t* edges, const int64_t* e_start, int64_t N, int64_t E,
+                        float cutoff_radius, uint64_t seed_noise, uint64_t seed_sign, float* frame1,
+                        float* frame2, float* frame3, void* workspace, int64_t workspace_bytes,
+                        void* stream);
+
 /* Replaces RealEncodingWithFramedProjFuncCUDA.forward
  * (models/cuda_funcs/real_space_framed_proj.py:21-120; kernels
  * real_enc_frame_proj_fwd_length.cu, real_enc_frame_proj_fwd_angle.cu).

@@ -513,6 +513,62 @@ void FN(cfo_frame2_edges)(const cfo_config* cfg, const real* a_ik, const real* r
     }
 }
 
+/* --------------------------------------------------------------------------
+ * Weighted-PCA frames, per (pair, head) part: softmax-weighted second moments of the
+ * separation vector over the translations, sigma = sum_n w_n d d^T / sum_n w_n (xx, xy, xz, yy,
+ * yz, zz), models/kernels/real_enc_sigma_fwd.cu:92-165, plus the lattice-sum bias
+ * z = log sum_n exp(a d^2) that the reference's pooling attention is meant to receive (the
+ * reference hands it an uninitialised buffer, models/cuda_funcs/real_space_enc_proj.py:54,97-125).
+ * near_d2 / near_dir: the nearest image with d^2 > 1e-5 (arg-min of d^2 + noise), from which the
+ * per-atom tie-breaking matrix of real_enc_sigma_fwd.cu:150-159 is built.
+ * -------------------------------------------------------------------------- */
+void FN(cfo_sigma_edges)(const cfo_config* cfg, const real* a_ik, const real* rpos, const real* tvecs,
+                         const float* rvlen, const int64_t* batch_i, const int64_t* edges,
+                         int64_t N, int64_t E, uint64_t seed, real* z_ek, real* sigma /* (E,H,6) */,
+                         real* near_d2 /* (E,H) */, real* near_dir /* (E,H,3) */)
+{
+    const int H = cfg->H;
+    (void)N;
+#pragma omp parallel for schedule(dynamic, 64)
+    for (int64_t e = 0; e < E; e++) {
+        const int64_t i = edges[e], c = batch_i[i];
+        const real* r = rpos + 3 * e;
+        const real* T = tvecs + 9 * c;
+        for (int k = 0; k < H; k++) {
+            const real a = a_ik[i * H + k];
+            int R[3];
+            lattice_range(cfg, (float)a, rvlen + 3 * c, R);
+            real d2min = (real)1e10;
+            FOR_TRANSLATIONS(R) { SEPARATION(r, T); (void)dx; (void)dy; (void)dz; d2min = R_FMIN(d2min, d2); }
+            real sum = 0, m[6] = {0, 0, 0, 0, 0, 0}, best = (real)1e8, bd[3] = {0, 0, 0};
+            int32_t t = 0;
+            FOR_TRANSLATIONS(R) {
+                SEPARATION(r, T);
+                real w = R_EXP(a * (d2 - d2min));
+                sum += w;
+                m[0] += dx * dx * w; m[1] += dx * dy * w; m[2] += dx * dz * w;
+                m[3] += dy * dy * w; m[4] += dy * dz * w; m[5] += dz * dz * w;
+                if ((double)d2 > 1e-5) {
+                    real noise = 0;
+                    if (cfg->symm_break_noise != 0.0f)
+                        noise = (real)(float)(((double)cfo_uniform(seed, (uint64_t)(e * H + k), (uint32_t)t) - 0.5) *
+                                              (double)cfg->symm_break_noise);
+                    if (best > d2 + noise) {
+                        best = d2 + noise;
+                        real d = R_SQRT(d2);
+                        bd[0] = dx / d; bd[1] = dy / d; bd[2] = dz / d;
+                    }
+                }
+                t++;
+            }
+            for (int q = 0; q < 6; q++) sigma[(e * H + k) * 6 + q] = m[q] / sum;
+            z_ek[e * H + k] = R_LOG(sum) + d2min * a;
+            near_d2[e * H + k] = best;
+            for (int q = 0; q < 3; q++) near_dir[(e * H + k) * 3 + q] = bd[q];
+        }
+    }
+}
+
 /* Per-(atom, head) selection: q_i.k_j + value, argmax over the atom's pairs
  * (models/cuda_funcs/calc_maximum_frame.py:72-84,146-163).  The reference leaves
  * ties to torch_scatter; here the lowest pair index wins.  The dot product is a

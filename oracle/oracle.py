@@ -297,3 +297,82 @@ def mean_bwd(gout, sizes, dtype=np.float32):
     gx = np.empty((int(sizes.sum()),) + gout.shape[1:], dtype)
     _fn("cfo_mean_bwd", dtype)(_p(gout), _p(start), ctypes.c_int64(len(sizes)), ctypes.c_int64(D), _p(gx))
     return gx
+
+
+# ---------------------------------------------------------------------------------------------
+# Weighted-PCA frames (models/indexed_lattice_multi_head_attention_cuda.py:620-725)
+# ---------------------------------------------------------------------------------------------
+def sigma_edges(cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, seed=0, dtype=np.float32):
+    a = _r(a_ik, dtype)
+    N, H = a.shape
+    E = edges.shape[1]
+    z, sig = np.empty((E, H), dtype), np.empty((E, H, 6), dtype)
+    nd2, ndir = np.empty((E, H), dtype), np.empty((E, H, 3), dtype)
+    c = cfg.c()
+    _fn("cfo_sigma_edges", dtype)(ctypes.byref(c), _p(a), _p(_r(pos_ij, dtype)), _p(_r(tvecs, dtype)), _p(_f32(rvlen)),
+                                  _p(_i64(batch)), _p(_i64(edges)), ctypes.c_int64(N), ctypes.c_int64(E),
+                                  ctypes.c_uint64(seed), _p(z), _p(sig), _p(nd2), _p(ndir))
+    return z, sig, nd2, ndir
+
+
+def hash_uniform(seed, tid, draw):
+    """Python twin of cfo_uniform (the counter-based noise shared with the CUDA library)."""
+    M = (1 << 64) - 1
+    x = (seed ^ ((tid * 0x9E3779B97F4A7C15) & M) ^ ((draw * 0xD1B54A32D192ED03) & M)) & M
+    x ^= x >> 30
+    x = (x * 0xBF58476D1CE4E5B9) & M
+    x ^= x >> 27
+    x = (x * 0x94D049BB133111EB) & M
+    x ^= x >> 31
+    return np.float32(((x >> 40) + 1)) * np.float32(1.0 / 16777216.0)
+
+
+def weighted_pca_frames(cfg, q_scaled, k, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, seed_noise=0,
+                        seed_sign=0):
+    """Per (atom, head): attention-pooled second-moment matrix (softmax over the atom's pairs of
+    q.k + z, the intended bias), optional tie-breaking term sigma_max * det^(1/3) * noise, symmetric
+    eigen-decomposition (ascending eigenvalues; each eigenvector signed so that its largest component
+    is positive), frames = ROWS of the eigenvector matrix (as the reference indexes it, :693-695),
+    hash-drawn row signs, and a final multiplication by the determinant so that the triad is
+    right-handed.  Matrices with determinant <= 1e-5 give the identity.  Returns frames (3,N,H,3),
+    the pooled matrices (N,H,3,3) and their eigenvalues (N,H,3)."""
+    N, H = a_ik.shape
+    z, sig, nd2, ndir = sigma_edges(cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, seed_noise)
+    q_scaled, k = np.asarray(q_scaled, np.float64), np.asarray(k, np.float64)
+    frames = np.zeros((3, N, H, 3), np.float32)
+    mats = np.zeros((N, H, 3, 3), np.float64)
+    evals = np.zeros((N, H, 3), np.float64)
+    idx6 = [(0, 0), (0, 1), (0, 2), (1, 1), (1, 2), (2, 2)]
+    for i in range(N):
+        e0, e1 = int(e_start[i]), int(e_start[i + 1])
+        js = edges[1, e0:e1]
+        for h in range(H):
+            logit = (q_scaled[i, h][None, :] * k[js, h]).sum(-1) + z[e0:e1, h].astype(np.float64)
+            p = np.exp(logit - logit.max())
+            p /= p.sum()
+            s6 = (p[:, None] * sig[e0:e1, h].astype(np.float64)).sum(0)
+            M = np.zeros((3, 3))
+            for v, (r, c) in zip(s6, idx6):
+                M[r, c] = M[c, r] = v
+            M = M.astype(np.float32).astype(np.float64)
+            det = np.linalg.det(M)
+            if cfg.symm_break_noise > 0:
+                jn = int(np.argmin(nd2[e0:e1, h]))
+                u = ndir[e0 + jn, h].astype(np.float64)
+                M = M + np.outer(u, u) * np.cbrt(det) * cfg.symm_break_noise
+            V = np.eye(3)
+            w = np.zeros(3)
+            if det > 1e-5:
+                w, V = np.linalg.eigh(M)
+                for c in range(3):
+                    if V[int(np.argmax(np.abs(V[:, c]))), c] < 0:
+                        V[:, c] = -V[:, c]
+            F = V.copy()                                            # frame r = row r of V
+            for r in range(3):
+                sgn = 1.0 if hash_uniform(seed_sign, i * H + h, r) > 0.5 else -1.0
+                F[r] *= sgn
+            F *= np.sign(np.linalg.det(F.T))
+            mats[i, h], evals[i, h] = M, w
+            for r in range(3):
+                frames[r, i, h] = F[r]
+    return frames, mats, evals

@@ -32,6 +32,7 @@ KERNELS = [
     "fused_dpa_fwd", "fused_dpa_bwd", "fused_dpa_bwd_q",
     "irregular_transpose", "irregular_mean_fwd",
     "real_enc_proj_fwd", "real_enc_proj_bwd",
+    "real_enc_sigma_fwd", "fused_dpa_sigmamat_fwd",
 ]
 
 

@@ -158,6 +158,30 @@ class RefKernels:
                     gz.contiguous(), gv.contiguous(), N, H, E, dist_max, wscale, W_k, 1, rvlen, cutoff, ga, gW)
         return ga, gW.sum(dim=0)
 
+    # ---- weighted PCA: models/cuda_funcs/real_space_enc_proj.py:80-125, fused_dpa_sigmamat.py ----
+    def sigma_fwd(self, a_ik, rpos, tvecs, batch, edges, rvlen, cutoff, seed=0):
+        N, H = a_ik.shape
+        E = edges.shape[1]
+        dev = a_ik.device
+        sigma = torch.zeros(E, H, 6, dtype=torch.float32, device=dev)
+        select = torch.zeros((E, H), dtype=torch.int, device=dev)
+        state = torch.empty(E * H * 48, dtype=torch.uint8, device=dev)
+        sigma_max = torch.zeros((N, H, 6), device=dev)
+        self.launch("real_enc_sigma_fwd", (E * H + H - 1) // H, H, a_ik, rpos, None, tvecs, batch, edges, N, H, E,
+                    64, 14.0, 1.0, 1, rvlen, cutoff, sigma, state, seed, select, sigma_max)
+        return sigma, sigma_max
+
+    def sigma_pool(self, q_scaled, k, z, sigma, edges):
+        N, H, K = q_scaled.shape
+        E = edges.shape[1]
+        e_start = self.e_start(edges, N)
+        v0 = torch.zeros((N, H, 6), device=q_scaled.device)
+        out = torch.empty_like(v0)
+        prob = torch.empty((E, H), dtype=q_scaled.dtype, device=q_scaled.device)
+        self.launch("fused_dpa_sigmamat_fwd", (N * H + H - 1) // H, H, q_scaled, k, v0, z, sigma, edges, e_start, N, H, E,
+                    prob, out)
+        return out
+
     # ---- models/cuda_funcs/calc_maximum_frame.py:24-170 -----------------------------
     def _edge_scores(self, q, k, edges, value):
         E = edges.shape[1]

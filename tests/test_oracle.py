@@ -132,6 +132,36 @@ def test_unwindowed_encoding_against_reference_cpu_build(problem_cfg1):
     close("gW", gWo, gW.numpy(), 1e-4, 1e-5 * max(1.0, float(gW.abs().max())))
 
 
+@pytest.mark.skipif(not R.available("cpu"), reason="oracle/_ref not built (reference tree absent)")
+def test_weighted_pca_moments_against_reference_cpu_build(problem_cfg1):
+    """Second-moment matrices per (pair, head) against real_enc_sigma_fwd, and their attention
+    pooling against fused_dpa_sigmamat_fwd when both receive the same (true) bias z."""
+    P = problem_cfg1
+    geo, b, cfg = P["geo"], P["batch"], P["cfg"]
+    rk = R.RefKernels("cpu")
+    T = lambda x: torch.from_numpy(np.ascontiguousarray(x))
+    a, r, tv, bt, e, rv = T(P["a"]), T(geo["pos_ij"]), T(b.trans_vec), T(geo["batch"]), T(geo["edges"]), T(geo["rvlen"])
+    sigma, sigma_max = rk.sigma_fwd(a, r, tv, bt, e, rv, -3.5)
+    z, sig, nd2, ndir = O.sigma_edges(cfg, P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"])
+    close("sigma", sig, sigma.numpy(), 1e-5, 1e-6)
+    # every pair's thread writes its nearest-image matrix into the same per-atom slot (a race in the
+    # reference): whatever survived must be the matrix of one of the atom's pairs
+    u = ndir
+    cand = np.stack([u[..., 0] * u[..., 0], u[..., 0] * u[..., 1], u[..., 0] * u[..., 2], u[..., 1] * u[..., 1],
+                     u[..., 1] * u[..., 2], u[..., 2] * u[..., 2]], -1)              # (E,H,6)
+    sm = sigma_max.numpy()
+    for i in range(sm.shape[0]):
+        rows = cand[geo["e_start"][i]:geo["e_start"][i + 1]]                         # (n,H,6)
+        err = np.abs(rows - sm[i][None]).max(-1)                                     # (n,H)
+        assert (err.min(0) < 1e-5).all(), i
+    pooled = rk.sigma_pool(T(P["q"] / 4.0), T(P["k"]), T(z), sigma, e)
+    _, mats, _ = O.weighted_pca_frames(cfg, P["q"] / 4.0, P["k"], P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"],
+                                       geo["batch"], geo["edges"], geo["e_start"])
+    idx = [(0, 0), (0, 1), (0, 2), (1, 1), (1, 2), (2, 2)]
+    got = np.stack([mats[:, :, r_, c_] for r_, c_ in idx], -1)
+    close("pooled sigma", got, pooled.numpy(), 1e-4, 1e-5)
+
+
 def test_finite_differences_float64(problem_cfg1):
     P = problem_cfg1
     geo, b, cfg = P["geo"], P["batch"], P["cfg"]
