@@ -66,12 +66,20 @@ def make_optimizer(model, fused):
     return torch.optim.AdamW(groups, lr=5e-4, betas=(0.9, 0.98), fused=fused)
 
 
-def synthetic_batches(n_batches, seed0, num_crystals):
+def synthetic_batches(n_batches, seed0, num_crystals, rank=0, world=1):
+    """Per-step batches.  With several ranks the step's global batch (num_crystals per rank) is
+    drawn identically on every rank and split by pair count, largest crystal first -- the
+    reference's rule for spreading one batch over devices (models/latticeformer.py:224-233) -- so
+    that the ranks' attention work, not just their crystal counts, is equal."""
     from crystalframer_b200 import synth
+    from crystalframer_b200.parallel import partition_by_pair_count
     out = []
     for i in range(n_batches):
-        b = synth.make_workload("cfg3", seed=seed0 + i, num_crystals=num_crystals)
+        b = synth.make_workload("cfg3", seed=seed0 + i, num_crystals=num_crystals * world)
         y = np.random.default_rng(seed0 + i).normal(size=(len(b.sizes), 1)).astype(np.float32)
+        if world > 1:
+            mine = np.sort(partition_by_pair_count(b.sizes, world)[rank])
+            b, y = synth.select(b, mine), y[mine]
         out.append((b, y))
     return out
 
@@ -253,7 +261,7 @@ def run_ours(args, rank, world, local_rank):
     model = make_model(2).to(dev).train()
     opt = make_optimizer(model, fused=True)
     n_host = 4
-    host = [data.host_batch(b, y) for b, y in synthetic_batches(n_host, 2 + 1000 * rank, BATCH)]
+    host = [data.host_batch(b, y) for b, y in synthetic_batches(n_host, 2, BATCH, rank, world)]
     resident = [hb.to(dev, non_blocking=False) for hb in host]
     params = [p for p in model.parameters() if p.requires_grad]
     flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)   # > L2 (126 MB)
@@ -271,9 +279,11 @@ def run_ours(args, rank, world, local_rank):
 
     def train_step(tb):
         opt.zero_grad(set_to_none=True)
-        loss = (model(tb) - tb.y).abs().mean()
+        # L1 loss over the GLOBAL batch: every rank divides by the global crystal count and the
+        # gradients are summed, so ranks holding different numbers of crystals are weighted correctly
+        loss = (model(tb) - tb.y).abs().sum() / float(BATCH * world)
         loss.backward()
-        parallel.allreduce_gradients(params)
+        parallel.allreduce_gradients(params, average=False)
         torch.nn.utils.clip_grad_norm_(params, 1.0)
         opt.step()
         return loss
@@ -300,6 +310,9 @@ def run_ours(args, rank, world, local_rank):
         wall = (time.perf_counter() - t0) * 1e3
         return max(e0.elapsed_time(e1), wall) if from_host else e0.elapsed_time(e1)
 
+    for i in range(3):                      # settle lazy initialisation (library load, cuBLAS, NCCL channels)
+        train_step(resident[i % n_host])
+    barrier()
     for i in range(args.warmup):
         train_step(resident[i % n_host])
     barrier()

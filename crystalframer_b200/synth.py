@@ -92,3 +92,13 @@ def make_workload(name, seed=None, num_crystals=None):
     if num_crystals is not None:
         kw["num_crystals"] = num_crystals
     return make_batch(**kw)
+
+
+def select(b: CrystalBatch, crystal_idx) -> CrystalBatch:
+    """Sub-batch made of the given crystals (in the given order)."""
+    crystal_idx = np.asarray(crystal_idx, dtype=np.int64)
+    start = np.concatenate([[0], np.cumsum(b.sizes)])
+    atoms = np.concatenate([np.arange(start[c], start[c + 1]) for c in crystal_idx]) if len(crystal_idx) else np.zeros(0, np.int64)
+    sizes = b.sizes[crystal_idx]
+    return CrystalBatch(x=b.x[atoms], pos=b.pos[atoms], batch=np.repeat(np.arange(len(sizes), dtype=np.int64), sizes),
+                        trans_vec=b.trans_vec[crystal_idx], sizes=sizes, z=b.z[atoms])
