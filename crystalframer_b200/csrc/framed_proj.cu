@@ -11,10 +11,11 @@
 //           indices l and l+32 of each of the four 64-wide Gaussian bases (distance, three frame
 //           axes) and keeps their running sums in registers, so the data-dependent window offset
 //           becomes a per-lane predicate instead of an indexed shared-memory update.
-//   block = after 4 tasks per warp the 32 basis vectors (32 x 256) sit in shared memory and the
-//           block multiplies them with the head's 16 x 256 projection (forward) or accumulates
-//           the outer product with the upstream gradient (backward) -- the projection weights are
-//           read once per 32 pairs instead of once per pair.
+//   forward: after 4 tasks a warp multiplies its own 4 basis vectors (4 x 256) with the head's
+//           16 x 256 projection from shared memory; warps never wait for one another.
+//   backward: after 4 tasks per warp the block's 32 basis vectors (32 x 256) sit in shared memory
+//           and the block accumulates their outer product with the upstream gradient in registers
+//           -- one weight-gradient partial per block, not per pair.
 //
 // Numerics follow the reference's float expressions for every integer decision (lattice range,
 // window start / end); Gaussians use ex2.approx on pre-scaled arguments.
@@ -24,15 +25,18 @@ namespace cfb {
 
 constexpr int kFpWarps = 8;
 constexpr int kFpThreads = kFpWarps * 32;
-constexpr int kFpTasksPerWarp = 4;
-constexpr int kFpSlots = kFpWarps * kFpTasksPerWarp;   // pairs per chunk (== 32: one lane per pair in the projection)
+// pairs a warp handles between two projections (forward) or between two block barriers (backward:
+// more pairs per barrier shorten the wait for the slowest warp; shared memory has the room at 2 blocks/SM)
+__host__ __device__ constexpr int fp_tasks_per_warp(bool bwd) { return bwd ? 8 : 4; }
+__host__ __device__ constexpr int fp_slots(bool bwd) { return kFpWarps * fp_tasks_per_warp(bwd); }   // staged pairs
 constexpr int kFpK = 256;                              // 4 bases x 64
-constexpr int kFpStageStride = 260;                    // padded row: conflict-free 128-bit reads by 32 lanes
+// staging row stride: the backward reads a row per lane with 128-bit loads (padded, conflict-free); the
+// forward reads rows as half-warp broadcasts and needs no padding
+__host__ __device__ constexpr int fp_stage_stride(bool bwd) { return bwd ? 260 : 256; }
 constexpr int kHd = 16;                                // head dimension of this instance
 // resident blocks per SM the kernels are compiled for (register budget): forward 3, backward 2
 __host__ __device__ constexpr int fp_blocks_per_sm(bool bwd) { return bwd ? 2 : 3; }
 
-static_assert(kFpSlots == 32, "projection maps one lane to one staged pair");
 
 struct FpArgs {
     const float* a_ik; const float* pos_ij; const float* tvecs; const float* rvlen;
@@ -46,10 +50,17 @@ struct FpArgs {
     float* gW_part;           // (gridDim.x, H, 16, 256) per-block weight gradient (scratch)
 };
 
+constexpr int kWfStride = 260;                         // forward: W stored [o][k] with padded rows (conflict-free 128-bit reads by 16 rows)
 constexpr int kWtStride = 20;                          // backward: W stored [k][o] with padded rows (conflict-free 128-bit reads)
-constexpr int kWtPad = kFpK * kWtStride - kHd * kFpK;   // extra floats that layout needs
-constexpr size_t kFpSmemFloats = (size_t)kHd * kFpK + (size_t)kFpSlots * kFpStageStride + (size_t)kFpWarps * 2 * 32 * 4 + 16 * 33 + kWtPad;
-constexpr size_t kFpSmemBytes = kFpSmemFloats * sizeof(float);
+// shared memory: projection weights | staged basis vectors | per-warp translation records (forward 6 floats
+// per record, backward 8) | backward only: upstream gradients of the staged pairs [32][16]
+__host__ __device__ constexpr int fp_w_floats(bool bwd) { return bwd ? kFpK * kWtStride : kHd * kWfStride; }
+__host__ __device__ constexpr int fp_rec_floats(bool bwd) { return bwd ? 8 * 32 : 6 * 32; }
+__host__ __device__ constexpr size_t fp_smem_bytes(bool bwd)
+{
+    return sizeof(float) * ((size_t)fp_w_floats(bwd) + (size_t)fp_slots(bwd) * fp_stage_stride(bwd) +
+                            (size_t)kFpWarps * fp_rec_floats(bwd) + (bwd ? fp_slots(bwd) * kHd : 0));
+}
 
 // exact float value of a small integer (|n| < 2^22) without a conversion instruction
 __device__ __forceinline__ float small_int_to_float(int n)
@@ -61,10 +72,12 @@ template <bool BWD, bool ANG>
 __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj_kernel(const FpArgs A, const Params P)
 {
     extern __shared__ __align__(16) float smem[];
-    float* W_s = smem;                                          // fwd: [16][256]; bwd: [256][20] (transposed)
-    float* stage = W_s + kHd * kFpK + kWtPad;                   // [32][260]
-    float4* tbuf = reinterpret_cast<float4*>(stage + kFpSlots * kFpStageStride);  // [8][2][32]
-    float* side = reinterpret_cast<float*>(tbuf + kFpWarps * 2 * 32);             // fwd: out [16][33]; bwd: gv [32][16]
+    constexpr int kFpStageStride = fp_stage_stride(BWD);
+    constexpr int kFpSlots = fp_slots(BWD), kFpTasksPerWarp = fp_tasks_per_warp(BWD);
+    float* W_s = smem;                                          // fwd: [16][260]; bwd: [256][20] (transposed)
+    float* stage = W_s + fp_w_floats(BWD);                      // [32][stride]
+    float* tbuf = stage + kFpSlots * kFpStageStride;            // per warp: float4[32] then float4[32] (bwd) / float2[32] (fwd)
+    float* side = tbuf + kFpWarps * fp_rec_floats(BWD);         // bwd: gv [32][16]
 
     const int h = blockIdx.y, H = P.H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -76,7 +89,7 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
         if (A.W[b] != nullptr)
             v = __ldg(reinterpret_cast<const float4*>(A.W[b] + ((size_t)h * kHd + o) * 64) + d4);
         if (!BWD) {
-            reinterpret_cast<float4*>(W_s)[idx] = v;
+            reinterpret_cast<float4*>(W_s)[o * (kWfStride / 4) + k4] = v;
         } else {
             const int k = k4 * 4;
             W_s[(k + 0) * kWtStride + o] = v.x; W_s[(k + 1) * kWtStride + o] = v.y;
@@ -100,7 +113,8 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
 #pragma unroll
         for (int j = 0; j < 8; j++) gacc[0][j] = gacc[1][j] = 0.f;
     }
-    float4* tb = tbuf + warp * 64;
+    float4* tb = reinterpret_cast<float4*>(tbuf + warp * fp_rec_floats(BWD));
+    float2* tb2 = reinterpret_cast<float2*>(tb + 32);          // forward's second record half
     __syncthreads();
 
     // Pair assignment: block b takes pairs b, b + G, b + 2G, ... (G = gridDim.x) and stages them 32
@@ -110,19 +124,29 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
     const int64_t G = gridDim.x;
     const int64_t myPairs = A.E > (int64_t)blockIdx.x ? (A.E - blockIdx.x + G - 1) / G : 0;
     const int64_t nChunks = (myPairs + kFpSlots - 1) / kFpSlots;
+    auto slot_of = [&](int tsk) { return BWD ? tsk * kFpWarps + warp : warp * kFpTasksPerWarp + tsk; };
+    // The chain pair -> query atom -> crystal -> cell is three dependent loads; the first two are
+    // issued one task ahead so that a task starts with its atom and crystal already in registers.
+    int i_next = 0, c_next = 0;
+    if (nChunks > 0) {
+        const int64_t e0 = (int64_t)slot_of(0) * G + blockIdx.x;
+        if (e0 < A.E) { i_next = (int)A.edges[e0]; c_next = (int)A.batch[i_next]; }
+    }
     for (int64_t chunk = 0; chunk < nChunks; chunk++) {
         for (int tsk = 0; tsk < kFpTasksPerWarp; tsk++) {
-            const int slot = tsk * kFpWarps + warp;
+            const int slot = slot_of(tsk);
             const int64_t e = (chunk * kFpSlots + slot) * G + blockIdx.x;
             float* srow = stage + slot * kFpStageStride;
-            if (e >= A.E) {
+            if (e >= A.E) {      // a warp's pairs come in increasing order: nothing left to prefetch either
 #pragma unroll
                 for (int j = 0; j < 8; j++) srow[j * 32 + lane] = 0.f;
                 if (BWD && lane < kHd) side[slot * kHd + lane] = 0.f;
                 continue;
             }
-            const int64_t i = A.edges[e];
-            const int64_t c = A.batch[i];
+            const int64_t i = i_next, c = c_next;
+            const bool last_tsk = tsk + 1 == kFpTasksPerWarp;
+            const int64_t e_next = ((chunk + (last_tsk ? 1 : 0)) * kFpSlots + slot_of(last_tsk ? 0 : tsk + 1)) * G + blockIdx.x;
+            if (e_next < A.E) i_next = (int)A.edges[e_next];
             const float rx = __ldg(A.pos_ij + 3 * e), ry = __ldg(A.pos_ij + 3 * e + 1), rz = __ldg(A.pos_ij + 3 * e + 2);
             const float* Tc = A.tvecs + 9 * c;
             const float t1x = __ldg(Tc), t1y = __ldg(Tc + 1), t1z = __ldg(Tc + 2);
@@ -224,7 +248,8 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
                             }
                         }
                         tb[lane] = make_float4(arg * kLog2e, xd, xa[0], xa[1]);     // log2 of the weight
-                        tb[32 + lane] = make_float4(xa[2], __int_as_float(lo_pack), d2, 0.f);
+                        if (BWD) tb[32 + lane] = make_float4(xa[2], __int_as_float(lo_pack), d2, 0.f);
+                        else tb2[lane] = make_float2(xa[2], __int_as_float(lo_pack));
                     }
                 }
                 unsigned mask = __ballot_sync(0xffffffffu, keep);
@@ -232,7 +257,9 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
                 while (mask) {
                     const int src = __ffs(mask) - 1;
                     mask &= mask - 1;
-                    const float4 r0 = tb[src], r1 = tb[32 + src];
+                    const float4 r0 = tb[src];
+                    float4 r1;
+                    if (BWD) { r1 = tb[32 + src]; } else { const float2 t = tb2[src]; r1 = make_float4(t.x, t.y, 0.f, 0.f); }
                     const float lw = r0.x, d2 = r1.z;          // Gaussian times weight = ex2(lw - b*b)
                     const int lo_pack = __float_as_int(r1.y);
                     {   // distance basis
@@ -265,6 +292,8 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
                 __syncwarp();
               }
             }
+
+            if (e_next < A.E) c_next = (int)A.batch[i_next];
 
             if (!BWD) {
                 const float sum = warp_sum(sum_l);
@@ -325,32 +354,31 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
                 if (lane < kHd) side[slot * kHd + lane] = __ldg(A.gv + (e * H + h) * kHd + lane);
             }
         }
-        __syncthreads();
-
         if (!BWD) {
+            // warp-level projection of the warp's own four pairs: lane = (output o, pair half)
+            __syncwarp();
             if (A.values != nullptr) {
-                // lane = staged pair, warp = output pair (2*warp, 2*warp+1)
-                const float4* st = reinterpret_cast<const float4*>(stage + lane * kFpStageStride);
-                const float4* w0 = reinterpret_cast<const float4*>(W_s + (2 * warp) * kFpK);
-                const float4* w1 = w0 + kFpK / 4;
+                const int o = lane & 15, half = lane >> 4;
+                const int slot0 = warp * kFpTasksPerWarp + 2 * half;
+                const float4* wr = reinterpret_cast<const float4*>(W_s + o * kWfStride);
+                const float4* s0 = reinterpret_cast<const float4*>(stage + slot0 * kFpStageStride);
+                const float4* s1 = s0 + kFpStageStride / 4;
                 float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll 8
                 for (int k4 = 0; k4 < kFpK / 4; k4++) {
-                    const float4 s = st[k4], u = w0[k4], v = w1[k4];
+                    const float4 u = wr[k4], s = s0[k4], t = s1[k4];
                     acc0 = fmaf(s.x, u.x, fmaf(s.y, u.y, fmaf(s.z, u.z, fmaf(s.w, u.w, acc0))));
-                    acc1 = fmaf(s.x, v.x, fmaf(s.y, v.y, fmaf(s.z, v.z, fmaf(s.w, v.w, acc1))));
+                    acc1 = fmaf(t.x, u.x, fmaf(t.y, u.y, fmaf(t.z, u.z, fmaf(t.w, u.w, acc1))));
                 }
-                side[(2 * warp) * 33 + lane] = acc0;
-                side[(2 * warp + 1) * 33 + lane] = acc1;
-                __syncthreads();
-                const int p = threadIdx.x >> 3, q = threadIdx.x & 7;
-                const int64_t e = (chunk * kFpSlots + p) * G + blockIdx.x;
-                if (e < A.E) {
-                    float2 v = make_float2(side[(2 * q) * 33 + p], side[(2 * q + 1) * 33 + p]);
-                    *reinterpret_cast<float2*>(A.values + (e * H + h) * kHd + 2 * q) = v;
-                }
+                const int64_t e0 = (chunk * kFpSlots + slot0) * G + blockIdx.x, e1 = e0 + G;
+                if (e0 < A.E) A.values[(e0 * H + h) * kHd + o] = acc0;
+                if (e1 < A.E) A.values[(e1 * H + h) * kHd + o] = acc1;
             }
-        } else {
+            __syncwarp();
+            continue;
+        }
+        __syncthreads();
+        {
             // in this phase lane l owns basis indices 4l..4l+3 and 128+4l..128+4l+3 (128-bit reads)
             for (int slot = 0; slot < kFpSlots; slot++) {
                 const float2 g = *reinterpret_cast<const float2*>(side + slot * kHd + 2 * warp);
@@ -412,7 +440,7 @@ static int grid_x_for(int64_t E, int H, bool bwd)
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int64_t chunks = (E + kFpSlots - 1) / kFpSlots;
+    const int64_t chunks = (E + fp_slots(bwd) - 1) / fp_slots(bwd);
     int64_t want = ((int64_t)sms * fp_blocks_per_sm(bwd)) / H;
     if (want < 1) want = 1;
     if (chunks < want) want = chunks < 1 ? 1 : chunks;
@@ -435,11 +463,11 @@ static int launch_fp(const FpArgs& A, const Params& P, int gx, cudaStream_t st)
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_done[dev & 63]) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFpSmemBytes) != cudaSuccess)
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp_smem_bytes(BWD)) != cudaSuccess)
             return CFB200_E_CUDA;
         attr_done[dev & 63] = true;
     }
-    kern<<<dim3(gx, P.H), kFpThreads, kFpSmemBytes, st>>>(A, P);
+    kern<<<dim3(gx, P.H), kFpThreads, fp_smem_bytes(BWD), st>>>(A, P);
     return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
 }
 
