@@ -167,8 +167,14 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
                     fx[x] = __ldg(f); fy[x] = __ldg(f + 1); fz[x] = __ldg(f + 2);
                 }
             }
-            float zin = 0.f;
-            if (BWD) zin = __ldg(A.z_in + e * H + h);
+            // backward: the pair's upstream gradients are requested now and first used after the lattice
+            // loops (lanes 0..15 hold gv, lane 16 holds gz), so their latency is off the critical path
+            float zin = 0.f, g_up = 0.f;
+            if (BWD) {
+                zin = __ldg(A.z_in + e * H + h);
+                if (lane < kHd) g_up = __ldg(A.gv + (e * H + h) * kHd + lane);
+                else if (lane == kHd) g_up = __ldg(A.gz + e * H + h);
+            }
 
             // Translations are walked slab by slab: lanes own the (n2, n3) offsets of a slab (decoded
             // once), the loop runs over n1.  ---- sweep A (forward only): minimum squared distance ----
@@ -310,10 +316,13 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
                 const float px = warp_sum(px_l);
                 // G = W^T gv restricted to this lane's eight basis indices
                 float gvr[kHd];
-                const float4* gv4 = reinterpret_cast<const float4*>(A.gv + (e * H + h) * kHd);
+                if (lane < kHd) side[slot * kHd + lane] = g_up;
+                const float gz_e = __shfl_sync(0xffffffffu, g_up, kHd);
+                __syncwarp();
+                const float4* gv4 = reinterpret_cast<const float4*>(side + slot * kHd);
 #pragma unroll
                 for (int o4 = 0; o4 < kHd / 4; o4++) {
-                    const float4 v = __ldg(gv4 + o4);
+                    const float4 v = gv4[o4];
                     gvr[4 * o4] = v.x; gvr[4 * o4 + 1] = v.y; gvr[4 * o4 + 2] = v.z; gvr[4 * o4 + 3] = v.w;
                 }
                 float G[8];
@@ -339,7 +348,7 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
                 if (lane == 0) {
                     // the reference scales the whole length-kernel result, gz term included, by the
                     // distance coefficient (models/cuda_funcs/real_space_framed_proj.py:183)
-                    const float g_len = fmaf(px, __ldg(A.gz + e * H + h), Ad - px * Bd);
+                    const float g_len = fmaf(px, gz_e, Ad - px * Bd);
                     const float g_ang = Aa - px * Ba;
                     A.ga_e[e * H + h] = P.c_dist * g_len + P.c_ang * g_ang;
                 }
@@ -351,7 +360,6 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
                     srow[64 + 64 * x + lane] = sa[x][0] * P.c_ang;
                     srow[96 + 64 * x + lane] = sa[x][1] * P.c_ang;
                 }
-                if (lane < kHd) side[slot * kHd + lane] = __ldg(A.gv + (e * H + h) * kHd + lane);
             }
         }
         if (!BWD) {
