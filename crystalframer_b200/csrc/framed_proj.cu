@@ -68,6 +68,13 @@ __device__ __forceinline__ float small_int_to_float(int n)
     return __int_as_float(0x4B400000 + n) - 12582912.0f;
 }
 
+// two fp32 multiply-adds in one instruction (packed fp32 arithmetic of sm_100): the projection loops are
+// bound by instruction issue, not by the FMA pipe
+__device__ __forceinline__ float2 fma2(float a0, float a1, float b0, float b1, float2 c)
+{
+    return __ffma2_rn(make_float2(a0, a1), make_float2(b0, b1), c);
+}
+
 template <bool BWD, bool ANG>
 __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj_kernel(const FpArgs A, const Params P)
 {
@@ -108,10 +115,10 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
     const float xa_scale = P.a_sigma_inv * kSqrtLog2e;
     const bool wide_d = P.win_dist > 32;
 
-    float gacc[2][8];
+    float2 gacc[2][4];
     if (BWD) {
 #pragma unroll
-        for (int j = 0; j < 8; j++) gacc[0][j] = gacc[1][j] = 0.f;
+        for (int j = 0; j < 4; j++) gacc[0][j] = gacc[1][j] = make_float2(0.f, 0.f);
     }
     float4* tb = reinterpret_cast<float4*>(tbuf + warp * fp_rec_floats(BWD));
     float2* tb2 = reinterpret_cast<float2*>(tb + 32);          // forward's second record half
@@ -329,13 +336,14 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
                     const float4* wrow = reinterpret_cast<const float4*>(W_s + (j * 32 + lane) * kWtStride);
-                    float acc = 0.f;
+                    float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
                     for (int o4 = 0; o4 < kHd / 4; o4++) {
                         const float4 u = wrow[o4];
-                        acc = fmaf(u.x, gvr[4 * o4], fmaf(u.y, gvr[4 * o4 + 1], fmaf(u.z, gvr[4 * o4 + 2], fmaf(u.w, gvr[4 * o4 + 3], acc))));
+                        acc = fma2(u.x, u.y, gvr[4 * o4], gvr[4 * o4 + 1], acc);
+                        acc = fma2(u.z, u.w, gvr[4 * o4 + 2], gvr[4 * o4 + 3], acc);
                     }
-                    G[j] = acc;
+                    G[j] = acc.x + acc.y;
                 }
                 float Ad = fmaf(G[0], qd[0], G[1] * qd[1]), Bd = fmaf(G[0], sd[0], G[1] * sd[1]);
                 float Aa = 0.f, Ba = 0.f;
@@ -371,13 +379,14 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
                 const float4* wr = reinterpret_cast<const float4*>(W_s + o * kWfStride);
                 const float4* s0 = reinterpret_cast<const float4*>(stage + slot0 * kFpStageStride);
                 const float4* s1 = s0 + kFpStageStride / 4;
-                float acc0 = 0.f, acc1 = 0.f;
+                float2 a01 = make_float2(0.f, 0.f), a23 = a01, b01 = a01, b23 = a01;
 #pragma unroll 8
                 for (int k4 = 0; k4 < kFpK / 4; k4++) {
                     const float4 u = wr[k4], s = s0[k4], t = s1[k4];
-                    acc0 = fmaf(s.x, u.x, fmaf(s.y, u.y, fmaf(s.z, u.z, fmaf(s.w, u.w, acc0))));
-                    acc1 = fmaf(t.x, u.x, fmaf(t.y, u.y, fmaf(t.z, u.z, fmaf(t.w, u.w, acc1))));
+                    a01 = fma2(s.x, s.y, u.x, u.y, a01); a23 = fma2(s.z, s.w, u.z, u.w, a23);
+                    b01 = fma2(t.x, t.y, u.x, u.y, b01); b23 = fma2(t.z, t.w, u.z, u.w, b23);
                 }
+                const float acc0 = (a01.x + a01.y) + (a23.x + a23.y), acc1 = (b01.x + b01.y) + (b23.x + b23.y);
                 const int64_t e0 = (chunk * kFpSlots + slot0) * G + blockIdx.x, e1 = e0 + G;
                 if (e0 < A.E) A.values[(e0 * H + h) * kHd + o] = acc0;
                 if (e1 < A.E) A.values[(e1 * H + h) * kHd + o] = acc1;
@@ -392,14 +401,10 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
                 const float2 g = *reinterpret_cast<const float2*>(side + slot * kHd + 2 * warp);
                 const float4* srow = reinterpret_cast<const float4*>(stage + slot * kFpStageStride) + lane;
                 const float4 s0 = srow[0], s1 = srow[32];
-                gacc[0][0] = fmaf(s0.x, g.x, gacc[0][0]); gacc[0][1] = fmaf(s0.y, g.x, gacc[0][1]);
-                gacc[0][2] = fmaf(s0.z, g.x, gacc[0][2]); gacc[0][3] = fmaf(s0.w, g.x, gacc[0][3]);
-                gacc[0][4] = fmaf(s1.x, g.x, gacc[0][4]); gacc[0][5] = fmaf(s1.y, g.x, gacc[0][5]);
-                gacc[0][6] = fmaf(s1.z, g.x, gacc[0][6]); gacc[0][7] = fmaf(s1.w, g.x, gacc[0][7]);
-                gacc[1][0] = fmaf(s0.x, g.y, gacc[1][0]); gacc[1][1] = fmaf(s0.y, g.y, gacc[1][1]);
-                gacc[1][2] = fmaf(s0.z, g.y, gacc[1][2]); gacc[1][3] = fmaf(s0.w, g.y, gacc[1][3]);
-                gacc[1][4] = fmaf(s1.x, g.y, gacc[1][4]); gacc[1][5] = fmaf(s1.y, g.y, gacc[1][5]);
-                gacc[1][6] = fmaf(s1.z, g.y, gacc[1][6]); gacc[1][7] = fmaf(s1.w, g.y, gacc[1][7]);
+                gacc[0][0] = fma2(s0.x, s0.y, g.x, g.x, gacc[0][0]); gacc[0][1] = fma2(s0.z, s0.w, g.x, g.x, gacc[0][1]);
+                gacc[0][2] = fma2(s1.x, s1.y, g.x, g.x, gacc[0][2]); gacc[0][3] = fma2(s1.z, s1.w, g.x, g.x, gacc[0][3]);
+                gacc[1][0] = fma2(s0.x, s0.y, g.y, g.y, gacc[1][0]); gacc[1][1] = fma2(s0.z, s0.w, g.y, g.y, gacc[1][1]);
+                gacc[1][2] = fma2(s1.x, s1.y, g.y, g.y, gacc[1][2]); gacc[1][3] = fma2(s1.z, s1.w, g.y, g.y, gacc[1][3]);
             }
         }
         __syncthreads();
@@ -407,10 +412,10 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
 
     if (BWD) {
         float* dst = A.gW_part + (((size_t)blockIdx.x * H + h) * kHd + 2 * warp) * kFpK + 4 * lane;
-        *reinterpret_cast<float4*>(dst) = make_float4(gacc[0][0], gacc[0][1], gacc[0][2], gacc[0][3]);
-        *reinterpret_cast<float4*>(dst + 128) = make_float4(gacc[0][4], gacc[0][5], gacc[0][6], gacc[0][7]);
-        *reinterpret_cast<float4*>(dst + kFpK) = make_float4(gacc[1][0], gacc[1][1], gacc[1][2], gacc[1][3]);
-        *reinterpret_cast<float4*>(dst + kFpK + 128) = make_float4(gacc[1][4], gacc[1][5], gacc[1][6], gacc[1][7]);
+        *reinterpret_cast<float4*>(dst) = make_float4(gacc[0][0].x, gacc[0][0].y, gacc[0][1].x, gacc[0][1].y);
+        *reinterpret_cast<float4*>(dst + 128) = make_float4(gacc[0][2].x, gacc[0][2].y, gacc[0][3].x, gacc[0][3].y);
+        *reinterpret_cast<float4*>(dst + kFpK) = make_float4(gacc[1][0].x, gacc[1][0].y, gacc[1][1].x, gacc[1][1].y);
+        *reinterpret_cast<float4*>(dst + kFpK + 128) = make_float4(gacc[1][2].x, gacc[1][2].y, gacc[1][3].x, gacc[1][3].y);
     }
 }
 

@@ -53,10 +53,18 @@ __device__ __forceinline__ void separation(const Cell& c, float n1, float n2, fl
 
 __device__ __forceinline__ float noise_term(float amp, uint64_t seed, uint64_t tid, uint32_t t)
 {
-    return (float)(((double)hash_uniform(seed, tid, t) - 0.5) * (double)amp);
+    // (u - 0.5) * amp: u is a multiple of 2^-24 in (0, 1], so u - 0.5 is exact and the single rounding of
+    // the float product equals the rounding of the same product formed in double
+    return __fmul_rn(__fsub_rn(hash_uniform(seed, tid, t), 0.5f), amp);
 }
 
 struct Cand { float value; float ux, uy, uz; int img; float d2raw; };   // d2raw: smallest d^2 > 1e-5 (first axis only)
+
+// The reference compares floats with the double literals 1e-5 and 0.9999.  For a float x these are
+// the same decisions as the float comparisons below, because float(1e-5) < 1e-5 and float(0.9999) <
+// 0.9999 with no float in between:  x > 1e-5  <=>  x > kTiny,   x < 0.9999  <=>  x <= kCosMax.
+constexpr float kTiny = 1e-5f;       // 9.99999974737875e-06
+constexpr float kCosMax = 0.9999f;   // 0.99989998340606689453
 
 // centre-out enumeration of one lattice index: k = 0, 1, 2, 3, 4 ... -> n = 0, -1, 1, -2, 2 ...
 __device__ __forceinline__ int centre_out(int k) { return (k & 1) ? -((k + 1) >> 1) : (k >> 1); }
@@ -70,26 +78,33 @@ __device__ __forceinline__ Cand first_axis_candidate(const Cell& cell, float a, 
                                                      uint64_t seed, uint64_t tid)
 {
     Cand c; c.ux = c.uy = c.uz = 0.f; c.img = -1;
-    float d2raw = 1e10f;
+    float d2raw = 1e10f, d2next = 1e10f;      // smallest and second smallest d^2 > 1e-5 (equal values count twice)
     int t = 0, best_t = -1;
     for (int n1 = -R1; n1 <= R1; n1++)
         for (int n2 = -R2; n2 <= R2; n2++)
             for (int n3 = -R3; n3 <= R3; n3++, t++) {
                 float dx, dy, dz, d2;
                 separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
-                if ((double)d2 > 1e-5 && d2 < d2raw) { d2raw = d2; best_t = t; }
+                if (d2 > kTiny) {
+                    if (d2 < d2raw) { d2next = d2raw; d2raw = d2; best_t = t; }
+                    else if (d2 < d2next) d2next = d2;
+                }
             }
     float d2_min = d2raw;
-    if (amp != 0.0f && best_t >= 0) {
+    const float limit = __fadd_rn(d2raw, __fmul_rn(amp, 1.001f));
+    if (amp > 0.0f && best_t >= 0 && !(d2next <= limit)) {
+        // no other translation is within the noise amplitude of the minimum: the winner stands and
+        // only its own noise enters the score
+        d2_min = __fadd_rn(d2raw, noise_term(amp, seed, tid, (uint32_t)best_t));
+    } else if (amp != 0.0f && best_t >= 0) {
         d2_min = 1e10f; best_t = -1;
-        const float limit = __fadd_rn(d2raw, __fmul_rn(amp, 1.001f));
         t = 0;
         for (int n1 = -R1; n1 <= R1; n1++)
             for (int n2 = -R2; n2 <= R2; n2++)
                 for (int n3 = -R3; n3 <= R3; n3++, t++) {
                     float dx, dy, dz, d2;
                     separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
-                    if ((double)d2 > 1e-5 && d2 <= limit) {
+                    if (d2 > kTiny && d2 <= limit) {
                         const float cand = __fadd_rn(d2, noise_term(amp, seed, tid, (uint32_t)t));
                         if (d2_min > cand) { d2_min = cand; best_t = t; }
                     }
@@ -130,7 +145,7 @@ __device__ __forceinline__ Cand second_axis_candidate(const Cell& cell, float a,
                 for (int n3 = -R3; n3 <= R3; n3++) {
                     float dx, dy, dz, d2;
                     separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
-                    if ((double)d2 > 1e-5) d2min = fminf(d2min, d2);
+                    if (d2 > kTiny) d2min = fminf(d2min, d2);
                 }
     float best = -1e15f;                 // running maximum of score + noise
     const float half = 0.5f * amp;
@@ -143,15 +158,15 @@ __device__ __forceinline__ Cand second_axis_candidate(const Cell& cell, float a,
                 const int n3 = centre_out(k3);
                 float dx, dy, dz, d2;
                 separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
-                if (!((double)d2 > 1e-5)) continue;
+                if (!(d2 > kTiny)) continue;
                 const float gauss = __fmul_rn(a, __fsub_rn(d2, d2min));
                 if (__fadd_rn(gauss, half) < best) continue;            // score + noise <= gauss + half
                 const float d = __fsqrt_rn(d2);
                 const float vx = __fdiv_rn(dx, d), vy = __fdiv_rn(dy, d), vz = __fdiv_rn(dz, d);
                 const float cs = __fadd_rn(__fadd_rn(__fmul_rn(vx, f1x), __fmul_rn(vy, f1y)), __fmul_rn(vz, f1z));
-                if (!((double)fabsf(cs) < 0.9999)) continue;
+                if (!(fabsf(cs) <= kCosMax)) continue;
                 const float one_m = __fsub_rn(1.0f, fabsf(cs));
-                const float clipped = ((double)one_m > 1e-5) ? one_m : 1e-5f;
+                const float clipped = one_m > kTiny ? one_m : 1e-5f;
                 const float score = __fadd_rn(gauss, logf(clipped));
                 const int t = ((n1 + R1) * L2 + (n2 + R2)) * L3 + (n3 + R3);
                 const float noisy = amp == 0.0f ? score : __fadd_rn(score, noise_term(amp, seed, tid, (uint32_t)t));
@@ -186,7 +201,7 @@ __device__ __forceinline__ int64_t lower_bound_i64(const int64_t* v, int64_t n, 
     return lo;
 }
 
-__global__ void __launch_bounds__(kFrThreads, 2) max_frame_kernel(const FrArgs A, const Params P)
+__global__ void __launch_bounds__(kFrThreads, 3) max_frame_kernel(const FrArgs A, const Params P)
 {
     __shared__ unsigned long long best[kFrMaxRows];
     __shared__ long long row_start[kFrMaxRows + 1];
