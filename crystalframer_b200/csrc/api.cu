@@ -252,7 +252,8 @@ static int fp_args(cfb::FpArgs& A, const float* a_ik, const float* pos_ij, const
     if (E > 0 && (!a_ik || !pos_ij || !tvecs || !batch || !edges)) return CFB200_E_NULL;
     if (cutoff_radius != 0.0f && E > 0 && rvlen == nullptr) return CFB200_E_NULL;
     const bool ang = W1 || W2 || W3;
-    if (ang && !(W1 && W2 && W3 && f1 && f2 && f3)) return CFB200_E_NULL;
+    if (ang && !(W1 && W2 && W3)) return CFB200_E_NULL;
+    if (ang && E > 0 && !(f1 && f2 && f3)) return CFB200_E_NULL;      // an empty batch has no frames to point at
     if (ang && g_cfg.angle_dim == 0) return CFB200_E_UNSUPPORTED;
     memset(&A, 0, sizeof(A));
     A.a_ik = a_ik; A.pos_ij = pos_ij; A.tvecs = tvecs; A.rvlen = rvlen; A.batch = batch; A.edges = edges;
