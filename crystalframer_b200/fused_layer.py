@@ -23,6 +23,18 @@ from .cuda_funcs.common import csr_offsets
 from .cuda_funcs.max_frame import _draw_seed
 
 
+_side_streams = {}
+
+
+def _side_stream(dev):
+    """Second stream of a device for work that does not sit on the layer's critical path (weight and
+    bias gradients): those GEMMs fill half of the SMs, so they run beside the data-gradient chain."""
+    s = _side_streams.get(dev)
+    if s is None:
+        s = _side_streams[dev] = torch.cuda.Stream(device=dev)
+    return s
+
+
 class LayerGeometry:
     """Per-batch tensors shared by all layers."""
     __slots__ = ("pos_ij", "tvecs", "batch", "edges", "e_start", "rvlen", "N", "E")
@@ -80,17 +92,26 @@ class FusedEncoderLayerFunc(torch.autograd.Function):
         p, ip = _lib.ptr, _lib.iptr
         new = lambda *shape: torch.empty(shape, device=dev, dtype=torch.float32)
         g = g.contiguous()
-        # feed-forward block and second residual
-        gWf2 = g.t().mm(h)
-        gbf2 = g.sum(0)
+        main, side = torch.cuda.current_stream(dev), _side_stream(dev)
+        # Data gradients run on the current stream; weight and bias gradients, which nothing in this
+        # backward pass reads, follow on the side stream as soon as their operands exist.  Every operand
+        # stays referenced until the streams are joined at the end, so no block is recycled early.
+        ev = torch.cuda.Event()
+        ev.record(main)
         gh = torch.ops.aten.threshold_backward(g.mm(Wf2), h, 0)
-        gWf1 = gh.t().mm(x1)
-        gbf1 = gh.sum(0)
         gx1 = torch.addmm(g, gh, Wf1)
-        # output projection and first residual
-        gWo = gx1.t().mm(o.view(N, D))
-        gbo = gx1.sum(0)
+        ev1 = torch.cuda.Event()
+        ev1.record(main)
         go = gx1.mm(Wo)
+        with torch.cuda.stream(side):
+            side.wait_event(ev)
+            gWf2 = g.t().mm(h)
+            gbf2 = g.sum(0)
+            side.wait_event(ev1)
+            gWf1 = gh.t().mm(x1)
+            gbf1 = gh.sum(0)
+            gWo = gx1.t().mm(o.view(N, D))
+            gbo = gx1.sum(0)
         # attention, lattice sums, coefficients
         gqs, gk, gv, gz, gval = new(N, H, hd), new(N, H, hd), new(N, H, hd), new(E, H), new(E, H, hd)
         _lib.invoke("cfb200_dpa_bwd", 2, dev, p(qs), p(k), p(v), p(z), p(val), ip(geo.edges), ip(geo.e_start), N, E,
@@ -109,9 +130,18 @@ class FusedEncoderLayerFunc(torch.autograd.Function):
                     meta["scale_real"], p(ga), p(gqs), p(gq), p(gw))
         # input projections
         gq2, gk2, gv2 = gq.view(N, D), gk.view(N, D), gv.view(N, D)
-        gWq, gWk, gWv = gq2.t().mm(x), gk2.t().mm(x), gv2.t().mm(x)
-        gb_in = torch.cat([gq2.sum(0), gk2.sum(0), gv2.sum(0)])
+        ev2 = torch.cuda.Event()
+        ev2.record(main)
         gx = torch.addmm(gx1, gq2, Wq).addmm_(gk2, Wk).addmm_(gv2, Wv)
+        with torch.cuda.stream(side):
+            side.wait_event(ev2)
+            gWq, gWk, gWv = gq2.t().mm(x), gk2.t().mm(x), gv2.t().mm(x)
+            gb_in = torch.cat([gq2.sum(0), gk2.sum(0), gv2.sum(0)])
+            done = torch.cuda.Event()
+            done.record(side)
+        main.wait_event(done)
+        for t in (gWf2, gbf2, gWf1, gbf1, gWo, gbo, gWq, gWk, gWv, gb_in):
+            t.record_stream(main)               # allocated on the side stream, consumed on the current one
         return (gx, gWq, gWk, gWv, gb_in, gw, None, gWo, gbo, gW[0].unsqueeze(0), gW[1].unsqueeze(0), gW[2].unsqueeze(0),
                 gW[3].unsqueeze(0), gWf1, gbf1, gWf2, gbf2, None, None)
 
