@@ -32,3 +32,4 @@ def host_batch(b: CrystalBatch, targets: np.ndarray, pinned=True) -> TensorBatch
     if pinned and torch.cuda.is_available():
         ts = [t.pin_memory() for t in ts]
     return TensorBatch(*ts, b.num_pairs)
+
