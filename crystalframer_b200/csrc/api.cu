@@ -176,7 +176,7 @@ static int frames_common(int mode, const float* q, const float* k, const float* 
                          const float* tvecs, const float* rvlen, const int64_t* batch, const int64_t* edges,
                          const int64_t* e_start, int64_t N, int64_t E, float cutoff_radius, uint64_t seed1,
                          uint64_t seed2, const float* frame1_in, float* f1, float* f2, float* f3, int64_t* sel_edge,
-                         int32_t* sel_image, void* stream)
+                         int32_t* sel_image, void* stream, const float* pair_cache = nullptr, int cache_range = 0)
 {
     if (N < 0 || E < 0) return CFB200_E_SHAPE;
     cfb::Params P;
@@ -190,6 +190,7 @@ static int frames_common(int mode, const float* q, const float* k, const float* 
     A.batch = batch; A.edges = edges; A.e_start = e_start; A.N = N; A.E = E;
     A.seed1 = seed1; A.seed2 = seed2; A.frame1_in = frame1_in;
     A.frame1 = f1; A.frame2 = f2; A.frame3 = f3; A.sel_edge = sel_edge; A.sel_image = sel_image; A.mode = mode;
+    A.cache = reinterpret_cast<const float4*>(pair_cache); A.cache_range = cache_range;
     return cfb::max_frame(A, P, S(stream));
 }
 
@@ -213,6 +214,28 @@ int cfb200_max_frames(const float* q_scaled, const float* k, const float* a_ik, 
     if (N > 0 && (!frame1 || !frame2 || !frame3)) return CFB200_E_NULL;
     return frames_common(3, q_scaled, k, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, N, E, cutoff_radius,
                          seed1, seed2, nullptr, frame1, frame2, frame3, nullptr, nullptr, stream);
+}
+
+int cfb200_pair_cache(const float* pos_ij, const float* tvecs, const int64_t* batch, const int64_t* edges, int64_t N,
+                      int64_t E, int range, float* pair_cache, void* stream)
+{
+    if (N < 0 || E < 0 || range < 0 || range > CFB200_MAX_RANGE) return CFB200_E_SHAPE;
+    if (E == 0) return CFB200_OK;
+    if (!pos_ij || !tvecs || !batch || !edges || !pair_cache) return CFB200_E_NULL;
+    if ((reinterpret_cast<uintptr_t>(pair_cache) & 15u) != 0) return CFB200_E_SHAPE;
+    return cfb::pair_cache(pos_ij, tvecs, batch, edges, E, range, pair_cache, S(stream));
+}
+
+int cfb200_max_frames_cached(const float* q_scaled, const float* k, const float* a_ik, const float* pos_ij,
+                             const float* tvecs, const float* rvlen, const int64_t* batch, const int64_t* edges,
+                             const int64_t* e_start, int64_t N, int64_t E, float cutoff_radius, uint64_t seed1,
+                             uint64_t seed2, float* frame1, float* frame2, float* frame3, const float* pair_cache,
+                             int cache_range, void* stream)
+{
+    if (N > 0 && (!frame1 || !frame2 || !frame3)) return CFB200_E_NULL;
+    if (pair_cache != nullptr && (reinterpret_cast<uintptr_t>(pair_cache) & 15u) != 0) return CFB200_E_SHAPE;
+    return frames_common(3, q_scaled, k, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, N, E, cutoff_radius,
+                         seed1, seed2, nullptr, frame1, frame2, frame3, nullptr, nullptr, stream, pair_cache, cache_range);
 }
 
 int64_t cfb200_sigma_frames_workspace_bytes(int64_t N, int64_t E)
@@ -279,6 +302,27 @@ int cfb200_framed_proj_fwd(const float* a_ik, const float* pos_ij, const float* 
     if (E > 0 && z == nullptr) return CFB200_E_NULL;
     if (values != nullptr && W_dist == nullptr) return CFB200_E_NULL;
     A.z = z; A.values = values;
+    return cfb::framed_proj_fwd(A, P, S(stream));
+}
+
+int cfb200_framed_proj_fwd_cached(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                                  const int64_t* batch, const int64_t* edges, int64_t N, int64_t E, float dist_max,
+                                  float cutoff_radius, const float* W_dist, const float* W_ang1, const float* W_ang2,
+                                  const float* W_ang3, const float* frame1, const float* frame2, const float* frame3,
+                                  float* z, float* values, const float* pair_cache, int cache_range, void* stream)
+{
+    cfb::Params P;
+    int rc = make_params(dist_max, cutoff_radius, P);
+    if (rc != CFB200_OK) return rc;
+    cfb::FpArgs A;
+    rc = fp_args(A, a_ik, pos_ij, tvecs, rvlen, batch, edges, N, E, cutoff_radius, W_dist, W_ang1, W_ang2, W_ang3,
+                 frame1, frame2, frame3);
+    if (rc != CFB200_OK) return rc;
+    if (E > 0 && z == nullptr) return CFB200_E_NULL;
+    if (values != nullptr && W_dist == nullptr) return CFB200_E_NULL;
+    if (pair_cache != nullptr && (reinterpret_cast<uintptr_t>(pair_cache) & 15u) != 0) return CFB200_E_SHAPE;
+    A.z = z; A.values = values;
+    A.cache = reinterpret_cast<const float4*>(pair_cache); A.cache_range = cache_range;
     return cfb::framed_proj_fwd(A, P, S(stream));
 }
 

@@ -46,6 +46,8 @@ struct FpArgs {
     const float* frame[3];    // each (N,H,3)
     float* z; float* values;                     // forward outputs
     const float* z_in; const float* gz; const float* gv;   // backward inputs
+    const float4* cache;      // optional per-pair geometry (pair_cache_kernel), valid for ranges (cache_range)^3
+    int cache_range;
     float* ga_e;              // (E,H) per-pair coefficient gradient (scratch)
     float* gW_part;           // (gridDim.x, H, 16, 256) per-block weight gradient (scratch)
 };
@@ -186,7 +188,9 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
             // Translations are walked slab by slab: lanes own the (n2, n3) offsets of a slab (decoded
             // once), the loop runs over n1.  ---- sweep A (forward only): minimum squared distance ----
             float d2min = 1e10f;
-            if (!BWD) {
+            if (!BWD && A.cache != nullptr && R1 == A.cache_range && R2 == A.cache_range && R3 == A.cache_range) {
+                d2min = __ldg(&A.cache[e].w);          // head- and layer-independent: computed once per batch
+            } else if (!BWD) {
                 for (int sub = 0; sub < nSub; sub++) {
                     const int idx = sub * 32 + lane;
                     int q2 = (int)(((float)idx + 0.5f) * invL3), r3 = idx - q2 * L3;

@@ -38,6 +38,8 @@ struct FrArgs {
     float* frame1; float* frame2; float* frame3;     // mode 1: frame1 out; mode 2: frame2 out (raw); mode 3: all, completed
     int64_t* sel_edge; int32_t* sel_image;
     int mode;
+    const float4* cache;      // optional per-pair results of pair_cache_kernel, valid for ranges (cache_range)^3
+    int cache_range;
 };
 
 struct Cell { float rx, ry, rz, t1x, t1y, t1z, t2x, t2y, t2z, t3x, t3y, t3z; };
@@ -75,11 +77,15 @@ __device__ __forceinline__ int centre_out(int k) { return (k & 1) ? -((k + 1) >>
 // pass 2 draws the noise only for translations within the noise amplitude of that minimum (nothing
 // else can win).  The direction is computed once, for the winner.
 __device__ __forceinline__ Cand first_axis_candidate(const Cell& cell, float a, int R1, int R2, int R3, float amp,
-                                                     uint64_t seed, uint64_t tid)
+                                                     uint64_t seed, uint64_t tid, const float4* cached)
 {
     Cand c; c.ux = c.uy = c.uz = 0.f; c.img = -1;
     float d2raw = 1e10f, d2next = 1e10f;      // smallest and second smallest d^2 > 1e-5 (equal values count twice)
     int t = 0, best_t = -1;
+    if (cached != nullptr) {                  // pass 1 is pure geometry: the same for every head and layer
+        const float4 g = __ldg(cached);
+        d2raw = g.x; d2next = g.y; best_t = __float_as_int(g.z);
+    } else
     for (int n1 = -R1; n1 <= R1; n1++)
         for (int n2 = -R2; n2 <= R2; n2++)
             for (int n3 = -R3; n3 <= R3; n3++, t++) {
@@ -286,7 +292,9 @@ __global__ void __launch_bounds__(kFrThreads, 3) max_frame_kernel(const FrArgs A
                 const int pack = row_R[r];
                 const int R1 = pack & 255, R2 = (pack >> 8) & 255, R3 = (pack >> 16) & 255;
                 if (axis == 1) {
-                    cd = first_axis_candidate(cell, row_a[r], R1, R2, R3, P.noise, A.seed1, noise_id);
+                    const bool hit = A.cache != nullptr && R1 == A.cache_range && R2 == A.cache_range && R3 == A.cache_range;
+                    cd = first_axis_candidate(cell, row_a[r], R1, R2, R3, P.noise, A.seed1, noise_id,
+                                              hit ? A.cache + e : nullptr);
                     if (keep_d2) {
                         if (round == 0) d2raw0 = cd.d2raw; else if (round == 1) d2raw1 = cd.d2raw; else d2raw2 = cd.d2raw;
                     }
@@ -349,6 +357,53 @@ __global__ void __launch_bounds__(kFrThreads, 3) max_frame_kernel(const FrArgs A
         }
         __syncthreads();
     }
+}
+
+// Per-pair geometry that does not depend on the head or the layer, for lattice ranges (R, R, R):
+//   x, y: smallest and second smallest d^2 > 1e-5 over the translations (equal values count twice), with
+//         the arithmetic of separation() -- what pass 1 of first_axis_candidate() finds;
+//   z:    the linear index of the first translation that attains x (-1 if none), as int bits;
+//   w:    the smallest d^2 over all translations, with the fused arithmetic of the lattice-sum kernel.
+__global__ void __launch_bounds__(256) pair_cache_kernel(const float* __restrict__ pos_ij, const float* __restrict__ tvecs,
+                                                         const int64_t* __restrict__ batch, const int64_t* __restrict__ edges,
+                                                         int64_t E, int R, float4* __restrict__ out)
+{
+    const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= E) return;
+    const int64_t c = batch[edges[e]];
+    Cell cell;
+    const float* Tc = tvecs + 9 * c;
+    cell.t1x = __ldg(Tc); cell.t1y = __ldg(Tc + 1); cell.t1z = __ldg(Tc + 2);
+    cell.t2x = __ldg(Tc + 3); cell.t2y = __ldg(Tc + 4); cell.t2z = __ldg(Tc + 5);
+    cell.t3x = __ldg(Tc + 6); cell.t3y = __ldg(Tc + 7); cell.t3z = __ldg(Tc + 8);
+    cell.rx = __ldg(pos_ij + 3 * e); cell.ry = __ldg(pos_ij + 3 * e + 1); cell.rz = __ldg(pos_ij + 3 * e + 2);
+    float d2raw = 1e10f, d2next = 1e10f, d2all = 1e10f;
+    int t = 0, best_t = -1;
+    for (int n1 = -R; n1 <= R; n1++)
+        for (int n2 = -R; n2 <= R; n2++)
+            for (int n3 = -R; n3 <= R; n3++, t++) {
+                float dx, dy, dz, d2;
+                separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
+                if (d2 > kTiny) {
+                    if (d2 < d2raw) { d2next = d2raw; d2raw = d2; best_t = t; }
+                    else if (d2 < d2next) d2next = d2;
+                }
+                const float f1 = (float)n1, f2 = (float)n2, f3 = (float)n3;
+                const float ox = fmaf(cell.t3x, f3, fmaf(cell.t2x, f2, cell.rx)), oy = fmaf(cell.t3y, f3, fmaf(cell.t2y, f2, cell.ry)),
+                            oz = fmaf(cell.t3z, f3, fmaf(cell.t2z, f2, cell.rz));
+                const float fx = fmaf(cell.t1x, f1, ox), fy = fmaf(cell.t1y, f1, oy), fz = fmaf(cell.t1z, f1, oz);
+                d2all = fminf(d2all, fmaf(fz, fz, fmaf(fy, fy, fx * fx)));
+            }
+    out[e] = make_float4(d2raw, d2next, __int_as_float(best_t), d2all);
+}
+
+int pair_cache(const float* pos_ij, const float* tvecs, const int64_t* batch, const int64_t* edges, int64_t E, int R,
+               float* out, cudaStream_t st)
+{
+    if (E == 0) return CFB200_OK;
+    pair_cache_kernel<<<(unsigned)((E + 255) / 256), 256, 0, st>>>(pos_ij, tvecs, batch, edges, E, R,
+                                                                  reinterpret_cast<float4*>(out));
+    return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
 }
 
 int max_frame(const FrArgs& A, const Params& P, cudaStream_t st)

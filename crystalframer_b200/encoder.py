@@ -143,7 +143,7 @@ class CrystalformerEncoderLayerCUDA(Module):
         if geo is None or geo.pos_ij is not pos_ij:
             rvlen = torch.norm(rvecs, 2, dim=-1).contiguous() if self._fused_meta["cutoff"] != 0.0 else None
             geo = fused_layer.LayerGeometry(pos_ij.contiguous(), trans.contiguous(), batch.contiguous(),
-                                            edges.contiguous(), rvlen)
+                                            edges.contiguous(), rvlen, self._fused_meta["cutoff"])
             edges._cf_geometry = geo
         return fused_layer.FusedEncoderLayerFunc.apply(
             x, attn.q_proj_weight, attn.k_proj_weight, attn.v_proj_weight, attn.in_proj_bias, attn.lattice_pos_weights,

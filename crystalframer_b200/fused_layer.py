@@ -20,6 +20,7 @@ import torch
 
 from . import _lib
 from .cuda_funcs.common import csr_offsets
+from .cuda_funcs.kernel_manager import KernelManager
 from .cuda_funcs.max_frame import _draw_seed
 
 
@@ -36,13 +37,23 @@ def _side_stream(dev):
 
 
 class LayerGeometry:
-    """Per-batch tensors shared by all layers."""
-    __slots__ = ("pos_ij", "tvecs", "batch", "edges", "e_start", "rvlen", "N", "E")
+    """Per-batch tensors shared by all layers, and the per-pair geometry cache (nearest image and
+    smallest squared distance of every pair): pure geometry, the same for every head and layer, so it
+    is computed once per batch for the lattice range nearly all (atom, head) pairs end up with."""
+    __slots__ = ("pos_ij", "tvecs", "batch", "edges", "e_start", "rvlen", "N", "E", "pair_cache", "cache_range")
 
-    def __init__(self, pos_ij, tvecs, batch, edges, rvlen):
+    def __init__(self, pos_ij, tvecs, batch, edges, rvlen, cutoff=0.0):
         self.pos_ij, self.tvecs, self.batch, self.edges, self.rvlen = pos_ij, tvecs, batch, edges, rvlen
         self.N, self.E = batch.shape[0], edges.shape[1]
         self.e_start = csr_offsets(edges, self.N)
+        cfg = KernelManager.config
+        # adaptive ranges are clamped from below by the minimum range, which is what most cells get
+        self.cache_range = int(cfg.lattice_range if cutoff == 0.0 else cfg.minimum_range) if cfg is not None else 0
+        self.pair_cache = None
+        if self.cache_range > 0 and self.E > 0:
+            self.pair_cache = torch.empty((self.E, 4), device=pos_ij.device, dtype=torch.float32)
+            _lib.invoke("cfb200_pair_cache", 1, pos_ij.device, _lib.ptr(pos_ij), _lib.ptr(tvecs), _lib.iptr(batch),
+                        _lib.iptr(edges), self.N, self.E, self.cache_range, _lib.ptr(self.pair_cache))
 
 
 class FusedEncoderLayerFunc(torch.autograd.Function):
@@ -63,13 +74,14 @@ class FusedEncoderLayerFunc(torch.autograd.Function):
                     meta["scale_real"], p(a), p(qs))
         f = new(3, N, H, 3)
         s1, s2 = _draw_seed(), _draw_seed()
-        _lib.invoke("cfb200_max_frames", 1, dev, p(qs), p(k), p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
-                    ip(geo.batch), ip(geo.edges), ip(geo.e_start), N, E, meta["cutoff"], s1, s2, p(f[0]), p(f[1]), p(f[2]))
+        _lib.invoke("cfb200_max_frames_cached", 1, dev, p(qs), p(k), p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
+                    ip(geo.batch), ip(geo.edges), ip(geo.e_start), N, E, meta["cutoff"], s1, s2, p(f[0]), p(f[1]), p(f[2]),
+                    p(geo.pair_cache), geo.cache_range)
         z, val = new(E, H), new(E, H, hd)
         Wd3, W13, W23, W33 = Wd[0], W1[0], W2[0], W3[0]
-        _lib.invoke("cfb200_framed_proj_fwd", 1, dev, p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen), ip(geo.batch),
-                    ip(geo.edges), N, E, meta["dist_max"], meta["cutoff"], p(Wd3), p(W13), p(W23), p(W33),
-                    p(f[0]), p(f[1]), p(f[2]), p(z), p(val))
+        _lib.invoke("cfb200_framed_proj_fwd_cached", 1, dev, p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
+                    ip(geo.batch), ip(geo.edges), N, E, meta["dist_max"], meta["cutoff"], p(Wd3), p(W13), p(W23), p(W33),
+                    p(f[0]), p(f[1]), p(f[2]), p(z), p(val), p(geo.pair_cache), geo.cache_range)
         o, lse = new(N, H, hd), new(N, H)
         _lib.invoke("cfb200_dpa_fwd", 1, dev, p(qs), p(k), p(v), p(z), p(val), ip(geo.edges), ip(geo.e_start), N, E,
                     p(o), p(lse), None)

@@ -300,3 +300,46 @@ def test_properties_at_benchmark_size():
     m.sum().backward()
     inv_n = (1.0 / D["sizes"].double())[D["batch"]].float()
     _close("mean backward", x.grad, inv_n[:, None].expand(N, 32), 1e-6, 1e-7)
+
+
+@pytest.mark.parametrize("noise", [0.0, 1e-5])
+def test_pair_cache_changes_no_bit(noise):
+    """The per-pair geometry cache only spares work: frames, lattice-sum bias and value encoding come
+    out bit-identical with and without it, on a batch that mixes cells at the cached lattice range with
+    small cells whose range is larger (those take the uncached search)."""
+    dev = _cuda()
+    F = _configure(noise)
+    from crystalframer_b200 import _lib
+    D = _device_problem(dev, "cfg2", nc=48)
+    D["tv"][:6] *= 0.45                                    # shrink a few cells: adaptive ranges above the minimum
+    D["pos_ij"][: int((D["b"].sizes[:6] ** 2).sum())] *= 0.45
+    from crystalframer_b200.encoder import det_3x3
+    tv = D["tv"]
+    rvecs = torch.stack([torch.linalg.cross(tv[:, 1], tv[:, 2]), torch.linalg.cross(tv[:, 2], tv[:, 0]),
+                         torch.linalg.cross(tv[:, 0], tv[:, 1])], 1) * (2.0 * np.pi / det_3x3(tv)[:, None, None])
+    rvlen = rvecs.norm(dim=-1).contiguous()
+    N, E, H, hd = D["a"].shape[0], D["edges"].shape[1], 8, 16
+    p, ip = _lib.ptr, _lib.iptr
+    cache = torch.empty(E, 4, device=dev)
+    _lib.invoke("cfb200_pair_cache", 1, dev, p(D["pos_ij"]), p(tv), ip(D["batch"]), ip(D["edges"]), N, E, 2, p(cache))
+    qs = (D["q"] / 4.0).contiguous()
+    outs = []
+    for use in (None, cache):
+        f = torch.empty(3, N, H, 3, device=dev)
+        _lib.invoke("cfb200_max_frames_cached", 1, dev, p(qs), p(D["k"]), p(D["a"]), p(D["pos_ij"]), p(tv), p(rvlen),
+                    ip(D["batch"]), ip(D["edges"]), ip(D["e_start"]), N, E, -3.5, 17, 29, p(f[0]), p(f[1]), p(f[2]),
+                    p(use), 2)
+        z, val = torch.empty(E, H, device=dev), torch.empty(E, H, hd, device=dev)
+        W = [w[0].contiguous() for w in D["W"]]
+        _lib.invoke("cfb200_framed_proj_fwd_cached", 1, dev, p(D["a"]), p(D["pos_ij"]), p(tv), p(rvlen), ip(D["batch"]),
+                    ip(D["edges"]), N, E, 14.0, -3.5, p(W[0]), p(W[1]), p(W[2]), p(W[3]), p(f[0]), p(f[1]), p(f[2]),
+                    p(z), p(val), p(use), 2)
+        outs.append((f, z, val))
+    plain = torch.empty(3, N, H, 3, device=dev)
+    _lib.invoke("cfb200_max_frames", 1, dev, p(qs), p(D["k"]), p(D["a"]), p(D["pos_ij"]), p(tv), p(rvlen), ip(D["batch"]),
+                ip(D["edges"]), ip(D["e_start"]), N, E, -3.5, 17, 29, p(plain[0]), p(plain[1]), p(plain[2]))
+    assert torch.equal(outs[0][0], plain)
+    for a, b, name in zip(outs[0], outs[1], ("frames", "z", "values")):
+        assert torch.equal(a, b), name
+    assert bool(torch.isfinite(outs[1][2]).all())
+    assert _lib.read_status() == 0
