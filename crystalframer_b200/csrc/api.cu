@@ -217,13 +217,13 @@ int cfb200_max_frames(const float* q_scaled, const float* k, const float* a_ik, 
 }
 
 int cfb200_pair_cache(const float* pos_ij, const float* tvecs, const int64_t* batch, const int64_t* edges, int64_t N,
-                      int64_t E, int range, float* pair_cache, void* stream)
+                      int64_t E, int range, float* pair_cache, float* pair_list, void* stream)
 {
     if (N < 0 || E < 0 || range < 0 || range > CFB200_MAX_RANGE) return CFB200_E_SHAPE;
     if (E == 0) return CFB200_OK;
-    if (!pos_ij || !tvecs || !batch || !edges || !pair_cache) return CFB200_E_NULL;
+    if (!pos_ij || !tvecs || !batch || !edges || (!pair_cache && !pair_list)) return CFB200_E_NULL;
     if ((reinterpret_cast<uintptr_t>(pair_cache) & 15u) != 0) return CFB200_E_SHAPE;
-    return cfb::pair_cache(pos_ij, tvecs, batch, edges, E, range, pair_cache, S(stream));
+    return cfb::pair_cache(pos_ij, tvecs, batch, edges, E, range, pair_cache, pair_list, S(stream));
 }
 
 int cfb200_max_frames_cached(const float* q_scaled, const float* k, const float* a_ik, const float* pos_ij,
@@ -309,7 +309,8 @@ int cfb200_framed_proj_fwd_cached(const float* a_ik, const float* pos_ij, const 
                                   const int64_t* batch, const int64_t* edges, int64_t N, int64_t E, float dist_max,
                                   float cutoff_radius, const float* W_dist, const float* W_ang1, const float* W_ang2,
                                   const float* W_ang3, const float* frame1, const float* frame2, const float* frame3,
-                                  float* z, float* values, const float* pair_cache, int cache_range, void* stream)
+                                  float* z, float* values, const float* pair_cache, const float* pair_list,
+                                  int cache_range, void* stream)
 {
     cfb::Params P;
     int rc = make_params(dist_max, cutoff_radius, P);
@@ -322,7 +323,7 @@ int cfb200_framed_proj_fwd_cached(const float* a_ik, const float* pos_ij, const 
     if (values != nullptr && W_dist == nullptr) return CFB200_E_NULL;
     if (pair_cache != nullptr && (reinterpret_cast<uintptr_t>(pair_cache) & 15u) != 0) return CFB200_E_SHAPE;
     A.z = z; A.values = values;
-    A.cache = reinterpret_cast<const float4*>(pair_cache); A.cache_range = cache_range;
+    A.cache = reinterpret_cast<const float4*>(pair_cache); A.list = pair_list; A.cache_range = cache_range;
     return cfb::framed_proj_fwd(A, P, S(stream));
 }
 
@@ -383,6 +384,31 @@ int cfb200_framed_proj_bwd(const float* a_ik, const float* pos_ij, const float* 
     if (N > 0 && (ga == nullptr || e_start == nullptr)) return CFB200_E_NULL;
     if (gW_dist == nullptr) return CFB200_E_NULL;
     A.z_in = z; A.gz = gz; A.gv = gvalues;
+    float* gW[4] = {gW_dist, gW_ang1, gW_ang2, gW_ang3};
+    return cfb::framed_proj_bwd(A, P, e_start, ga, gW, workspace, workspace_bytes, S(stream));
+}
+
+int cfb200_framed_proj_bwd_cached(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                                  const int64_t* batch, const int64_t* edges, const int64_t* e_start, int64_t N,
+                                  int64_t E, float dist_max, float cutoff_radius, const float* W_dist,
+                                  const float* W_ang1, const float* W_ang2, const float* W_ang3, const float* frame1,
+                                  const float* frame2, const float* frame3, const float* z, const float* gz,
+                                  const float* gvalues, float* ga, float* gW_dist, float* gW_ang1, float* gW_ang2,
+                                  float* gW_ang3, void* workspace, int64_t workspace_bytes, const float* pair_list,
+                                  int cache_range, void* stream)
+{
+    cfb::Params P;
+    int rc = make_params(dist_max, cutoff_radius, P);
+    if (rc != CFB200_OK) return rc;
+    cfb::FpArgs A;
+    rc = fp_args(A, a_ik, pos_ij, tvecs, rvlen, batch, edges, N, E, cutoff_radius, W_dist, W_ang1, W_ang2, W_ang3,
+                 frame1, frame2, frame3);
+    if (rc != CFB200_OK) return rc;
+    if (E > 0 && (!z || !gz || !gvalues || !W_dist || !e_start)) return CFB200_E_NULL;
+    if (N > 0 && (ga == nullptr || e_start == nullptr)) return CFB200_E_NULL;
+    if (gW_dist == nullptr) return CFB200_E_NULL;
+    A.z_in = z; A.gz = gz; A.gv = gvalues;
+    A.list = pair_list; A.cache_range = cache_range;
     float* gW[4] = {gW_dist, gW_ang1, gW_ang2, gW_ang3};
     return cfb::framed_proj_bwd(A, P, e_start, ga, gW, workspace, workspace_bytes, S(stream));
 }

@@ -34,6 +34,7 @@ constexpr int kFpK = 256;                              // 4 bases x 64
 // forward reads rows as half-warp broadcasts and needs no padding
 __host__ __device__ constexpr int fp_stage_stride(bool bwd) { return bwd ? 260 : 256; }
 constexpr int kHd = 16;                                // head dimension of this instance
+constexpr int kFpListLen = 128;                        // entries of a per-pair translation list (>= 5^3)
 // resident blocks per SM the kernels are compiled for (register budget): forward 3, backward 2
 __host__ __device__ constexpr int fp_blocks_per_sm(bool bwd) { return bwd ? 2 : 3; }
 
@@ -47,6 +48,7 @@ struct FpArgs {
     float* z; float* values;                     // forward outputs
     const float* z_in; const float* gz; const float* gv;   // backward inputs
     const float4* cache;      // optional per-pair geometry (pair_cache_kernel), valid for ranges (cache_range)^3
+    const float* list;        // optional per-pair translation lists (pair_list_kernel): (E, 4, kFpListLen)
     int cache_range;
     float* ga_e;              // (E,H) per-pair coefficient gradient (scratch)
     float* gW_part;           // (gridDim.x, H, 16, 256) per-block weight gradient (scratch)
@@ -156,15 +158,29 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
             const bool last_tsk = tsk + 1 == kFpTasksPerWarp;
             const int64_t e_next = ((chunk + (last_tsk ? 1 : 0)) * kFpSlots + slot_of(last_tsk ? 0 : tsk + 1)) * G + blockIdx.x;
             if (e_next < A.E) i_next = (int)A.edges[e_next];
-            const float rx = __ldg(A.pos_ij + 3 * e), ry = __ldg(A.pos_ij + 3 * e + 1), rz = __ldg(A.pos_ij + 3 * e + 2);
-            const float* Tc = A.tvecs + 9 * c;
-            const float t1x = __ldg(Tc), t1y = __ldg(Tc + 1), t1z = __ldg(Tc + 2);
-            const float t2x = __ldg(Tc + 3), t2y = __ldg(Tc + 4), t2z = __ldg(Tc + 5);
-            const float t3x = __ldg(Tc + 6), t3y = __ldg(Tc + 7), t3z = __ldg(Tc + 8);
             const float a = __ldg(A.a_ik + i * H + h);
+            // sorted translation list of this pair (prepared once per batch for ranges cache_range^3): four
+            // groups of 32 squared distances and the first group's vectors are requested right away
+            float dl0 = 0.f, dl1 = 0.f, dl2 = 0.f, dl3 = 0.f, lx0 = 0.f, ly0 = 0.f, lz0 = 0.f;
+            if (A.list != nullptr) {
+                const float* Ll = A.list + (size_t)e * (4 * kFpListLen) + lane;
+                dl0 = __ldg(Ll); dl1 = __ldg(Ll + 32); dl2 = __ldg(Ll + 64); dl3 = __ldg(Ll + 96);
+                lx0 = __ldg(Ll + kFpListLen); ly0 = __ldg(Ll + 2 * kFpListLen); lz0 = __ldg(Ll + 3 * kFpListLen);
+            }
             int Rl = 0;
             if (lane < 3) Rl = lattice_range_1d(P, a, P.cutoff_radius != 0.0f ? __ldg(A.rvlen + 3 * c + lane) : 0.0f);
             const int R1 = __shfl_sync(0xffffffffu, Rl, 0), R2 = __shfl_sync(0xffffffffu, Rl, 1), R3 = __shfl_sync(0xffffffffu, Rl, 2);
+            const bool use_list = A.list != nullptr && R1 == A.cache_range && R2 == A.cache_range && R3 == A.cache_range;
+            // separation and cell vectors: only the slab sweeps of pairs without a usable list read them
+            float rx = 0.f, ry = 0.f, rz = 0.f, t1x = 0.f, t1y = 0.f, t1z = 0.f, t2x = 0.f, t2y = 0.f, t2z = 0.f,
+                  t3x = 0.f, t3y = 0.f, t3z = 0.f;
+            if (!use_list) {
+                rx = __ldg(A.pos_ij + 3 * e); ry = __ldg(A.pos_ij + 3 * e + 1); rz = __ldg(A.pos_ij + 3 * e + 2);
+                const float* Tc = A.tvecs + 9 * c;
+                t1x = __ldg(Tc); t1y = __ldg(Tc + 1); t1z = __ldg(Tc + 2);
+                t2x = __ldg(Tc + 3); t2y = __ldg(Tc + 4); t2z = __ldg(Tc + 5);
+                t3x = __ldg(Tc + 6); t3y = __ldg(Tc + 7); t3z = __ldg(Tc + 8);
+            }
             const int L1 = 2 * R1 + 1, L3 = 2 * R3 + 1, L23 = (2 * R2 + 1) * L3;
             const int nSub = (L23 + 31) >> 5;                 // 32-lane pieces of one (n2, n3) slab
             const float invL3 = 1.0f / (float)L3;
@@ -188,7 +204,9 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
             // Translations are walked slab by slab: lanes own the (n2, n3) offsets of a slab (decoded
             // once), the loop runs over n1.  ---- sweep A (forward only): minimum squared distance ----
             float d2min = 1e10f;
-            if (!BWD && A.cache != nullptr && R1 == A.cache_range && R2 == A.cache_range && R3 == A.cache_range) {
+            if (!BWD && use_list) {
+                d2min = __shfl_sync(0xffffffffu, dl0, 0);               // the sorted list starts with the smallest
+            } else if (!BWD && A.cache != nullptr && R1 == A.cache_range && R2 == A.cache_range && R3 == A.cache_range) {
                 d2min = __ldg(&A.cache[e].w);          // head- and layer-independent: computed once per batch
             } else if (!BWD) {
                 for (int sub = 0; sub < nSub; sub++) {
@@ -213,26 +231,22 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
             float sd[2] = {0.f, 0.f}, sa[3][2] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
             float qd[2] = {0.f, 0.f}, qa[3][2] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};   // backward: sums of g*p*d2
             float sum_l = 0.f, px_l = 0.f;
-            for (int sub = 0; sub < nSub; sub++) {
-              const int idx = sub * 32 + lane;
-              int q2 = (int)(((float)idx + 0.5f) * invL3), r3 = idx - q2 * L3;
-              if (r3 < 0) { q2--; r3 += L3; } else if (r3 >= L3) { q2++; r3 -= L3; }
-              const float n2 = small_int_to_float(q2 - R2), n3 = small_int_to_float(r3 - R3);
-              const float ox = fmaf(t3x, n3, fmaf(t2x, n2, rx)), oy = fmaf(t3y, n3, fmaf(t2y, n2, ry)),
-                          oz = fmaf(t3z, n3, fmaf(t2z, n2, rz));
-              const bool valid = idx < L23;
-              for (int k1 = 0; k1 < L1; k1++) {
-                bool keep = false;
-                if (valid) {
-                    const float n1 = small_int_to_float(k1 - R1);
-                    const float dx = fmaf(t1x, n1, ox), dy = fmaf(t1y, n1, oy), dz = fmaf(t1z, n1, oz);
-                    const float d2 = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
-                    const float arg = BWD ? fmaf(a, d2, -zin) : a * (d2 - d2min);
-                    const float w = ex2_approx(arg * kLog2e);
-                    sum_l += w;
-                    if (BWD) px_l = fmaf(w, d2, px_l);
-                    keep = arg > -P.prune;
+            // One group = up to 32 translations, one per lane.  ``expand`` builds the window records of the
+            // lanes whose translation passes the pruning threshold and walks these survivors; ``xyz`` yields
+            // a lane's separation vector and is only called by lanes that keep their translation.
+            // log of a translation's weight; its contribution to the normaliser (and, backward, to sum p d^2)
+            auto weigh = [&](const float d2) {
+                const float arg = BWD ? fmaf(a, d2, -zin) : a * (d2 - d2min);
+                const float w = ex2_approx(arg * kLog2e);
+                sum_l += w;
+                if (BWD) px_l = fmaf(w, d2, px_l);
+                return arg;
+            };
+            auto expand = [&](const bool keep, const float arg, const float d2, auto xyz) {
+                {
                     if (keep) {
+                        float dx, dy, dz;
+                        xyz(dx, dy, dz);
                         // d and 1/d from one reciprocal square root plus a Newton step; quotients by
                         // the basis spacings become products with their reciprocals.  These differ
                         // from the reference's IEEE sqrt / divisions in the last bit only.
@@ -307,7 +321,44 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
                     }
                 }
                 __syncwarp();
-              }
+            };
+
+            if (use_list) {
+                // weights of all listed translations (the normaliser keeps every term), then the groups that
+                // hold survivors: the list is sorted, so they come first and the loop stops at the first
+                // group without any
+                const float a0 = weigh(dl0), a1 = weigh(dl1), a2 = weigh(dl2), a3 = weigh(dl3);
+                for (int g = 0; g < kFpListLen / 32; g++) {
+                    const float d2 = g == 0 ? dl0 : (g == 1 ? dl1 : (g == 2 ? dl2 : dl3));
+                    const float arg = g == 0 ? a0 : (g == 1 ? a1 : (g == 2 ? a2 : a3));
+                    const bool keep = arg > -P.prune;
+                    if (!__any_sync(0xffffffffu, keep)) break;
+                    expand(keep, arg, d2, [&](float& dx, float& dy, float& dz) {
+                        if (g == 0) { dx = lx0; dy = ly0; dz = lz0; }
+                        else {
+                            const float* Lg = A.list + (size_t)e * (4 * kFpListLen) + g * 32 + lane;
+                            dx = __ldg(Lg + kFpListLen); dy = __ldg(Lg + 2 * kFpListLen); dz = __ldg(Lg + 3 * kFpListLen);
+                        }
+                    });
+                }
+            } else {
+                for (int sub = 0; sub < nSub; sub++) {
+                    const int idx = sub * 32 + lane;
+                    int q2 = (int)(((float)idx + 0.5f) * invL3), r3 = idx - q2 * L3;
+                    if (r3 < 0) { q2--; r3 += L3; } else if (r3 >= L3) { q2++; r3 -= L3; }
+                    const float n2 = small_int_to_float(q2 - R2), n3 = small_int_to_float(r3 - R3);
+                    const float ox = fmaf(t3x, n3, fmaf(t2x, n2, rx)), oy = fmaf(t3y, n3, fmaf(t2y, n2, ry)),
+                                oz = fmaf(t3z, n3, fmaf(t2z, n2, rz));
+                    const bool valid = idx < L23;
+                    for (int k1 = 0; k1 < L1; k1++) {
+                        const float n1 = small_int_to_float(k1 - R1);
+                        const float dx0 = fmaf(t1x, n1, ox), dy0 = fmaf(t1y, n1, oy), dz0 = fmaf(t1z, n1, oz);
+                        const float d2 = fmaf(dz0, dz0, fmaf(dy0, dy0, dx0 * dx0));
+                        float arg = -1e30f;
+                        if (valid) arg = weigh(d2);
+                        expand(arg > -P.prune, arg, d2, [&](float& dx, float& dy, float& dz) { dx = dx0; dy = dy0; dz = dz0; });
+                    }
+                }
             }
 
             if (e_next < A.E) c_next = (int)A.batch[i_next];

@@ -397,12 +397,57 @@ __global__ void __launch_bounds__(256) pair_cache_kernel(const float* __restrict
     out[e] = make_float4(d2raw, d2next, __int_as_float(best_t), d2all);
 }
 
+// Per-pair translation list for lattice ranges (R, R, R) with (2R+1)^3 <= kListLen: the separations of all
+// translations of a pair sorted by squared distance (equal distances in index order), as four planes of
+// kListLen floats -- d^2, x, y, z -- with the fused arithmetic of the lattice-sum kernel.  Unused entries
+// hold d^2 = 1e30.  Because the weight exp(a (d^2 - d^2_min)) falls with the distance, the translations a
+// lattice-sum task has to expand are a prefix of this list, whatever the head or the layer.
+constexpr int kListLen = 128;
+
+__global__ void __launch_bounds__(kListLen) pair_list_kernel(const float* __restrict__ pos_ij, const float* __restrict__ tvecs,
+                                                             const int64_t* __restrict__ batch, const int64_t* __restrict__ edges,
+                                                             int64_t E, int R, float* __restrict__ out)
+{
+    __shared__ float sd2[kListLen];
+    const int64_t e = blockIdx.x;
+    const int t = threadIdx.x;
+    const int L = 2 * R + 1, nT = L * L * L;
+    const int64_t c = batch[edges[e]];
+    const float* Tc = tvecs + 9 * c;
+    float dx = 0.f, dy = 0.f, dz = 0.f, d2 = 1e30f;
+    if (t < nT) {
+        const int q = t / L;
+        const float n1 = (float)(q / L - R), n2 = (float)(q % L - R), n3 = (float)(t % L - R);
+        const float rx = __ldg(pos_ij + 3 * e), ry = __ldg(pos_ij + 3 * e + 1), rz = __ldg(pos_ij + 3 * e + 2);
+        const float ox = fmaf(__ldg(Tc + 6), n3, fmaf(__ldg(Tc + 3), n2, rx)), oy = fmaf(__ldg(Tc + 7), n3, fmaf(__ldg(Tc + 4), n2, ry)),
+                    oz = fmaf(__ldg(Tc + 8), n3, fmaf(__ldg(Tc + 5), n2, rz));
+        dx = fmaf(__ldg(Tc), n1, ox); dy = fmaf(__ldg(Tc + 1), n1, oy); dz = fmaf(__ldg(Tc + 2), n1, oz);
+        d2 = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
+    }
+    sd2[t] = d2;
+    __syncthreads();
+    int rank = 0;
+#pragma unroll 8
+    for (int j = 0; j < kListLen; j++) {
+        const float dj = sd2[j];
+        rank += (dj < d2 || (dj == d2 && j < t)) ? 1 : 0;
+    }
+    float* o = out + (size_t)e * (4 * kListLen);
+    o[rank] = d2; o[kListLen + rank] = dx; o[2 * kListLen + rank] = dy; o[3 * kListLen + rank] = dz;
+}
+
 int pair_cache(const float* pos_ij, const float* tvecs, const int64_t* batch, const int64_t* edges, int64_t E, int R,
-               float* out, cudaStream_t st)
+               float* out, float* list, cudaStream_t st)
 {
     if (E == 0) return CFB200_OK;
-    pair_cache_kernel<<<(unsigned)((E + 255) / 256), 256, 0, st>>>(pos_ij, tvecs, batch, edges, E, R,
-                                                                  reinterpret_cast<float4*>(out));
+    if (out != nullptr)
+        pair_cache_kernel<<<(unsigned)((E + 255) / 256), 256, 0, st>>>(pos_ij, tvecs, batch, edges, E, R,
+                                                                      reinterpret_cast<float4*>(out));
+    if (list != nullptr) {
+        if ((2 * R + 1) * (2 * R + 1) * (2 * R + 1) > kListLen) return CFB200_E_UNSUPPORTED;
+        if (E > 0x7fffffff) return CFB200_E_TOO_LARGE;
+        pair_list_kernel<<<(unsigned)E, kListLen, 0, st>>>(pos_ij, tvecs, batch, edges, E, R, list);
+    }
     return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
 }
 

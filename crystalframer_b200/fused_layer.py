@@ -40,7 +40,8 @@ class LayerGeometry:
     """Per-batch tensors shared by all layers, and the per-pair geometry cache (nearest image and
     smallest squared distance of every pair): pure geometry, the same for every head and layer, so it
     is computed once per batch for the lattice range nearly all (atom, head) pairs end up with."""
-    __slots__ = ("pos_ij", "tvecs", "batch", "edges", "e_start", "rvlen", "N", "E", "pair_cache", "cache_range")
+    __slots__ = ("pos_ij", "tvecs", "batch", "edges", "e_start", "rvlen", "N", "E", "pair_cache", "pair_list",
+                 "cache_range")
 
     def __init__(self, pos_ij, tvecs, batch, edges, rvlen, cutoff=0.0):
         self.pos_ij, self.tvecs, self.batch, self.edges, self.rvlen = pos_ij, tvecs, batch, edges, rvlen
@@ -49,11 +50,15 @@ class LayerGeometry:
         cfg = KernelManager.config
         # adaptive ranges are clamped from below by the minimum range, which is what most cells get
         self.cache_range = int(cfg.lattice_range if cutoff == 0.0 else cfg.minimum_range) if cfg is not None else 0
-        self.pair_cache = None
+        self.pair_cache = self.pair_list = None
         if self.cache_range > 0 and self.E > 0:
-            self.pair_cache = torch.empty((self.E, 4), device=pos_ij.device, dtype=torch.float32)
-            _lib.invoke("cfb200_pair_cache", 1, pos_ij.device, _lib.ptr(pos_ij), _lib.ptr(tvecs), _lib.iptr(batch),
-                        _lib.iptr(edges), self.N, self.E, self.cache_range, _lib.ptr(self.pair_cache))
+            dev = pos_ij.device
+            self.pair_cache = torch.empty((self.E, 4), device=dev, dtype=torch.float32)
+            if (2 * self.cache_range + 1) ** 3 <= 128:       # sorted translation lists: 2 KB per pair
+                self.pair_list = torch.empty((self.E, 4, 128), device=dev, dtype=torch.float32)
+            _lib.invoke("cfb200_pair_cache", 2, dev, _lib.ptr(pos_ij), _lib.ptr(tvecs), _lib.iptr(batch),
+                        _lib.iptr(edges), self.N, self.E, self.cache_range, _lib.ptr(self.pair_cache),
+                        _lib.ptr(self.pair_list))
 
 
 class FusedEncoderLayerFunc(torch.autograd.Function):
@@ -81,7 +86,7 @@ class FusedEncoderLayerFunc(torch.autograd.Function):
         Wd3, W13, W23, W33 = Wd[0], W1[0], W2[0], W3[0]
         _lib.invoke("cfb200_framed_proj_fwd_cached", 1, dev, p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
                     ip(geo.batch), ip(geo.edges), N, E, meta["dist_max"], meta["cutoff"], p(Wd3), p(W13), p(W23), p(W33),
-                    p(f[0]), p(f[1]), p(f[2]), p(z), p(val), p(geo.pair_cache), geo.cache_range)
+                    p(f[0]), p(f[1]), p(f[2]), p(z), p(val), p(geo.pair_cache), p(geo.pair_list), geo.cache_range)
         o, lse = new(N, H, hd), new(N, H)
         _lib.invoke("cfb200_dpa_fwd", 1, dev, p(qs), p(k), p(v), p(z), p(val), ip(geo.edges), ip(geo.e_start), N, E,
                     p(o), p(lse), None)
@@ -133,10 +138,10 @@ class FusedEncoderLayerFunc(torch.autograd.Function):
         lib = _lib.lib()
         nbytes = int(lib.cfb200_framed_proj_bwd_workspace_bytes(N, E))
         ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
-        _lib.invoke("cfb200_framed_proj_bwd", 3, dev, p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen), ip(geo.batch),
-                    ip(geo.edges), ip(geo.e_start), N, E, meta["dist_max"], meta["cutoff"], p(Wd[0]), p(W1[0]), p(W2[0]),
-                    p(W3[0]), p(f[0]), p(f[1]), p(f[2]), p(z), p(gz), p(gval), p(ga), p(gW[0]), p(gW[1]), p(gW[2]),
-                    p(gW[3]), ws.data_ptr(), nbytes)
+        _lib.invoke("cfb200_framed_proj_bwd_cached", 3, dev, p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
+                    ip(geo.batch), ip(geo.edges), ip(geo.e_start), N, E, meta["dist_max"], meta["cutoff"], p(Wd[0]),
+                    p(W1[0]), p(W2[0]), p(W3[0]), p(f[0]), p(f[1]), p(f[2]), p(z), p(gz), p(gval), p(ga), p(gW[0]),
+                    p(gW[1]), p(gW[2]), p(gW[3]), ws.data_ptr(), nbytes, p(geo.pair_list), geo.cache_range)
         gq, gw = new(N, H, hd), torch.empty_like(w_lat)
         _lib.invoke("cfb200_gauss_coef_bwd", 1, dev, p(q), p(w_lat), p(gauss_scale), N, meta["lb"], meta["beta"],
                     meta["scale_real"], p(ga), p(gqs), p(gq), p(gw))

@@ -199,19 +199,25 @@ int cfb200_framed_proj_bwd_noalloc(const float* a_ik, const float* pos_ij, const
                                    const float* gz, const float* gvalues, float* ga, float* gW_dist,
                                    float* gW_ang1, float* gW_ang2, float* gW_ang3, void* stream);
 
-/* Per-pair geometry cache.  No counterpart in the reference, whose kernels redo this work in every
- * layer and for every head: the nearest image of a pair and its smallest squared distance depend
- * only on the pair's separation and the cell, not on the head or the layer.  cfb200_pair_cache
- * fills pair_cache (E,4) float, 16-byte aligned, for the lattice ranges (range, range, range):
- *   [0], [1]  smallest and second smallest d^2 > 1e-5 over the translations,
- *   [2]       linear index of the first translation attaining [0] (int32 bits, -1 if none),
- *   [3]       smallest d^2 over all translations.
- * The *_cached entry points below compute exactly what their plain namesakes compute (same bits)
- * and read the cache for every (atom, head) whose three lattice ranges equal cache_range; other
- * ranges are searched as usual.  pair_cache may be NULL (then they are the plain entry points). */
+/* Per-pair geometry shared by all heads and layers.  No counterpart in the reference, whose kernels
+ * redo this work in every layer and for every head: which lattice translations of a pair are near,
+ * and how near, depends only on the pair's separation and the cell.  For the lattice ranges
+ * (range, range, range) cfb200_pair_cache fills either or both of
+ *   pair_cache (E,4) float, 16-byte aligned:
+ *     [0], [1]  smallest and second smallest d^2 > 1e-5 over the translations,
+ *     [2]       linear index of the first translation attaining [0] (int32 bits, -1 if none),
+ *     [3]       smallest d^2 over all translations;
+ *   pair_list (E,4,128) float, only for (2 range + 1)^3 <= 128 (CFB200_E_UNSUPPORTED otherwise):
+ *     the separation vectors of all translations sorted by squared distance -- planes d^2, x, y, z;
+ *     unused entries have d^2 = 1e30.
+ * The *_cached entry points compute what their plain namesakes compute and use the cache for every
+ * (atom, head) whose three lattice ranges equal cache_range; other ranges are searched as usual.
+ * With pair_cache the results are bit-identical to the plain entry points; with pair_list the
+ * lattice sums are accumulated nearest-first instead of in index order (differences of a few ulp).
+ * Either pointer may be NULL. */
 int cfb200_pair_cache(const float* pos_ij, const float* tvecs, const int64_t* batch,
                       const int64_t* edges, int64_t N, int64_t E, int range, float* pair_cache,
-                      void* stream);
+                      float* pair_list, void* stream);
 int cfb200_max_frames_cached(const float* q_scaled, const float* k, const float* a_ik,
                              const float* pos_ij, const float* tvecs, const float* rvlen,
                              const int64_t* batch, const int64_t* edges, const int64_t* e_start,
@@ -224,7 +230,18 @@ int cfb200_framed_proj_fwd_cached(const float* a_ik, const float* pos_ij, const 
                                   const float* W_dist, const float* W_ang1, const float* W_ang2,
                                   const float* W_ang3, const float* frame1, const float* frame2,
                                   const float* frame3, float* z, float* values,
-                                  const float* pair_cache, int cache_range, void* stream);
+                                  const float* pair_cache, const float* pair_list, int cache_range,
+                                  void* stream);
+int cfb200_framed_proj_bwd_cached(const float* a_ik, const float* pos_ij, const float* tvecs,
+                                  const float* rvlen, const int64_t* batch, const int64_t* edges,
+                                  const int64_t* e_start, int64_t N, int64_t E, float dist_max,
+                                  float cutoff_radius, const float* W_dist, const float* W_ang1,
+                                  const float* W_ang2, const float* W_ang3, const float* frame1,
+                                  const float* frame2, const float* frame3, const float* z,
+                                  const float* gz, const float* gvalues, float* ga, float* gW_dist,
+                                  float* gW_ang1, float* gW_ang2, float* gW_ang3, void* workspace,
+                                  int64_t workspace_bytes, const float* pair_list, int cache_range,
+                                  void* stream);
 
 /* Replaces FusedDotProductAttentionCUDA.forward (models/cuda_funcs/fused_dpa.py:17-64;
  * kernel fused_dpa_fwd.cu).  q_scaled, k, v (N,H,head_dim); z (E,H) or NULL; values

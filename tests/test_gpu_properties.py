@@ -321,7 +321,9 @@ def test_pair_cache_changes_no_bit(noise):
     N, E, H, hd = D["a"].shape[0], D["edges"].shape[1], 8, 16
     p, ip = _lib.ptr, _lib.iptr
     cache = torch.empty(E, 4, device=dev)
-    _lib.invoke("cfb200_pair_cache", 1, dev, p(D["pos_ij"]), p(tv), ip(D["batch"]), ip(D["edges"]), N, E, 2, p(cache))
+    plist = torch.empty(E, 4, 128, device=dev)
+    _lib.invoke("cfb200_pair_cache", 2, dev, p(D["pos_ij"]), p(tv), ip(D["batch"]), ip(D["edges"]), N, E, 2, p(cache),
+                p(plist))
     qs = (D["q"] / 4.0).contiguous()
     outs = []
     for use in (None, cache):
@@ -333,7 +335,7 @@ def test_pair_cache_changes_no_bit(noise):
         W = [w[0].contiguous() for w in D["W"]]
         _lib.invoke("cfb200_framed_proj_fwd_cached", 1, dev, p(D["a"]), p(D["pos_ij"]), p(tv), p(rvlen), ip(D["batch"]),
                     ip(D["edges"]), N, E, 14.0, -3.5, p(W[0]), p(W[1]), p(W[2]), p(W[3]), p(f[0]), p(f[1]), p(f[2]),
-                    p(z), p(val), p(use), 2)
+                    p(z), p(val), p(use), None, 2)
         outs.append((f, z, val))
     plain = torch.empty(3, N, H, 3, device=dev)
     _lib.invoke("cfb200_max_frames", 1, dev, p(qs), p(D["k"]), p(D["a"]), p(D["pos_ij"]), p(tv), p(rvlen), ip(D["batch"]),
@@ -342,4 +344,37 @@ def test_pair_cache_changes_no_bit(noise):
     for a, b, name in zip(outs[0], outs[1], ("frames", "z", "values")):
         assert torch.equal(a, b), name
     assert bool(torch.isfinite(outs[1][2]).all())
+
+    # sorted translation lists: ascending d^2, consistent vectors, 125 real entries; the lattice sums
+    # accumulated nearest-first agree with the index-order sums to a few ulp, forward and backward
+    d2l = plist[:, 0]
+    assert bool((d2l[:, 1:] >= d2l[:, :-1]).all())
+    assert bool((d2l[:, 125:] == 1e30).all()) and bool((d2l[:, :125] < 1e30).all())
+    vec2 = (plist[:, 1:, :125] ** 2).sum(1)
+    assert float(((vec2 - d2l[:, :125]).abs() / (d2l[:, :125] + 1e-6)).max()) < 1e-5
+    assert torch.equal(d2l[:, 0], cache[:, 3])
+    f, z0, v0 = outs[0]
+    W = [w[0].contiguous() for w in D["W"]]
+    z1, v1 = torch.empty(E, H, device=dev), torch.empty(E, H, hd, device=dev)
+    _lib.invoke("cfb200_framed_proj_fwd_cached", 1, dev, p(D["a"]), p(D["pos_ij"]), p(tv), p(rvlen), ip(D["batch"]),
+                ip(D["edges"]), N, E, 14.0, -3.5, p(W[0]), p(W[1]), p(W[2]), p(W[3]), p(f[0]), p(f[1]), p(f[2]),
+                p(z1), p(v1), p(cache), p(plist), 2)
+    _close("z with lists", z1, z0, 1e-6, 1e-6)
+    _close("values with lists", v1, v0, 1e-5, 1e-6)
+    g = torch.Generator(device="cpu").manual_seed(5)
+    gz, gv = torch.randn(E, H, generator=g).to(dev), torch.randn(E, H, hd, generator=g).to(dev)
+    nbytes = int(_lib.lib().cfb200_framed_proj_bwd_workspace_bytes(N, E))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    res = []
+    for use in (None, plist):
+        ga = torch.empty(N, H, device=dev)
+        gW = [torch.empty(H, hd, 64, device=dev) for _ in range(4)]
+        _lib.invoke("cfb200_framed_proj_bwd_cached", 3, dev, p(D["a"]), p(D["pos_ij"]), p(tv), p(rvlen), ip(D["batch"]),
+                    ip(D["edges"]), ip(D["e_start"]), N, E, 14.0, -3.5, p(W[0]), p(W[1]), p(W[2]), p(W[3]), p(f[0]),
+                    p(f[1]), p(f[2]), p(z0), p(gz), p(gv), p(ga), p(gW[0]), p(gW[1]), p(gW[2]), p(gW[3]), ws.data_ptr(),
+                    nbytes, p(use), 2)
+        res.append([ga] + gW)
+    for x, y, name in zip(res[0], res[1], ("ga", "gW_dist", "gW_ang1", "gW_ang2", "gW_ang3")):
+        scale = max(1.0, float(x.abs().max()))
+        _close(name + " with lists", y, x, 1e-4, 1e-5 * scale)
     assert _lib.read_status() == 0
