@@ -176,7 +176,8 @@ static int frames_common(int mode, const float* q, const float* k, const float* 
                          const float* tvecs, const float* rvlen, const int64_t* batch, const int64_t* edges,
                          const int64_t* e_start, int64_t N, int64_t E, float cutoff_radius, uint64_t seed1,
                          uint64_t seed2, const float* frame1_in, float* f1, float* f2, float* f3, int64_t* sel_edge,
-                         int32_t* sel_image, void* stream, const float* pair_cache = nullptr, int cache_range = 0)
+                         int32_t* sel_image, void* stream, const float* pair_cache = nullptr,
+                         const float* pair_list = nullptr, int cache_range = 0)
 {
     if (N < 0 || E < 0) return CFB200_E_SHAPE;
     cfb::Params P;
@@ -190,7 +191,7 @@ static int frames_common(int mode, const float* q, const float* k, const float* 
     A.batch = batch; A.edges = edges; A.e_start = e_start; A.N = N; A.E = E;
     A.seed1 = seed1; A.seed2 = seed2; A.frame1_in = frame1_in;
     A.frame1 = f1; A.frame2 = f2; A.frame3 = f3; A.sel_edge = sel_edge; A.sel_image = sel_image; A.mode = mode;
-    A.cache = reinterpret_cast<const float4*>(pair_cache); A.cache_range = cache_range;
+    A.cache = reinterpret_cast<const float4*>(pair_cache); A.list = pair_list; A.cache_range = cache_range;
     return cfb::max_frame(A, P, S(stream));
 }
 
@@ -230,12 +231,13 @@ int cfb200_max_frames_cached(const float* q_scaled, const float* k, const float*
                              const float* tvecs, const float* rvlen, const int64_t* batch, const int64_t* edges,
                              const int64_t* e_start, int64_t N, int64_t E, float cutoff_radius, uint64_t seed1,
                              uint64_t seed2, float* frame1, float* frame2, float* frame3, const float* pair_cache,
-                             int cache_range, void* stream)
+                             const float* pair_list, int cache_range, void* stream)
 {
     if (N > 0 && (!frame1 || !frame2 || !frame3)) return CFB200_E_NULL;
     if (pair_cache != nullptr && (reinterpret_cast<uintptr_t>(pair_cache) & 15u) != 0) return CFB200_E_SHAPE;
     return frames_common(3, q_scaled, k, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, N, E, cutoff_radius,
-                         seed1, seed2, nullptr, frame1, frame2, frame3, nullptr, nullptr, stream, pair_cache, cache_range);
+                         seed1, seed2, nullptr, frame1, frame2, frame3, nullptr, nullptr, stream, pair_cache, pair_list,
+                         cache_range);
 }
 
 int64_t cfb200_sigma_frames_workspace_bytes(int64_t N, int64_t E)

@@ -71,6 +71,13 @@ __host__ __device__ __forceinline__ float hash_uniform(uint64_t seed, uint64_t t
     return (float)((uint32_t)(x >> 40) + 1u) * (1.0f / 16777216.0f);
 }
 
+// Per-pair translation list (pair_list_kernel): kListPlanes planes of kListLen entries per pair, sorted by
+// squared distance -- d^2, x, y, z (fused arithmetic of the lattice-sum kernel) and the packed translation
+// (n1 + R) | (n2 + R) << 8 | (n3 + R) << 16 | linear index << 24.  Unused entries hold d^2 = 1e30.
+constexpr int kListLen = 128;
+constexpr int kListPlanes = 5;
+constexpr int kListStride = kListLen * kListPlanes;
+
 // Lattice range along one reciprocal axis for Gaussian coefficient a (< 0):
 // models/kernels/real_enc_frame_proj_fwd_length.cu:59-86.  (cutoff + 0.01f) * rvl is a float
 // product, the division by 2.0 * CUDART_PI_F and the ceil are double, as in the reference.

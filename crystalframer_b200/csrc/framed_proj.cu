@@ -34,7 +34,6 @@ constexpr int kFpK = 256;                              // 4 bases x 64
 // forward reads rows as half-warp broadcasts and needs no padding
 __host__ __device__ constexpr int fp_stage_stride(bool bwd) { return bwd ? 260 : 256; }
 constexpr int kHd = 16;                                // head dimension of this instance
-constexpr int kFpListLen = 128;                        // entries of a per-pair translation list (>= 5^3)
 // resident blocks per SM the kernels are compiled for (register budget): forward 3, backward 2
 __host__ __device__ constexpr int fp_blocks_per_sm(bool bwd) { return bwd ? 2 : 3; }
 
@@ -48,7 +47,7 @@ struct FpArgs {
     float* z; float* values;                     // forward outputs
     const float* z_in; const float* gz; const float* gv;   // backward inputs
     const float4* cache;      // optional per-pair geometry (pair_cache_kernel), valid for ranges (cache_range)^3
-    const float* list;        // optional per-pair translation lists (pair_list_kernel): (E, 4, kFpListLen)
+    const float* list;        // optional per-pair translation lists (pair_list_kernel): (E, kListPlanes, kListLen)
     int cache_range;
     float* ga_e;              // (E,H) per-pair coefficient gradient (scratch)
     float* gW_part;           // (gridDim.x, H, 16, 256) per-block weight gradient (scratch)
@@ -163,9 +162,9 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
             // groups of 32 squared distances and the first group's vectors are requested right away
             float dl0 = 0.f, dl1 = 0.f, dl2 = 0.f, dl3 = 0.f, lx0 = 0.f, ly0 = 0.f, lz0 = 0.f;
             if (A.list != nullptr) {
-                const float* Ll = A.list + (size_t)e * (4 * kFpListLen) + lane;
+                const float* Ll = A.list + (size_t)e * kListStride + lane;
                 dl0 = __ldg(Ll); dl1 = __ldg(Ll + 32); dl2 = __ldg(Ll + 64); dl3 = __ldg(Ll + 96);
-                lx0 = __ldg(Ll + kFpListLen); ly0 = __ldg(Ll + 2 * kFpListLen); lz0 = __ldg(Ll + 3 * kFpListLen);
+                lx0 = __ldg(Ll + kListLen); ly0 = __ldg(Ll + 2 * kListLen); lz0 = __ldg(Ll + 3 * kListLen);
             }
             int Rl = 0;
             if (lane < 3) Rl = lattice_range_1d(P, a, P.cutoff_radius != 0.0f ? __ldg(A.rvlen + 3 * c + lane) : 0.0f);
@@ -328,7 +327,7 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
                 // hold survivors: the list is sorted, so they come first and the loop stops at the first
                 // group without any
                 const float a0 = weigh(dl0), a1 = weigh(dl1), a2 = weigh(dl2), a3 = weigh(dl3);
-                for (int g = 0; g < kFpListLen / 32; g++) {
+                for (int g = 0; g < kListLen / 32; g++) {
                     const float d2 = g == 0 ? dl0 : (g == 1 ? dl1 : (g == 2 ? dl2 : dl3));
                     const float arg = g == 0 ? a0 : (g == 1 ? a1 : (g == 2 ? a2 : a3));
                     const bool keep = arg > -P.prune;
@@ -336,8 +335,8 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
                     expand(keep, arg, d2, [&](float& dx, float& dy, float& dz) {
                         if (g == 0) { dx = lx0; dy = ly0; dz = lz0; }
                         else {
-                            const float* Lg = A.list + (size_t)e * (4 * kFpListLen) + g * 32 + lane;
-                            dx = __ldg(Lg + kFpListLen); dy = __ldg(Lg + 2 * kFpListLen); dz = __ldg(Lg + 3 * kFpListLen);
+                            const float* Lg = A.list + (size_t)e * kListStride + g * 32 + lane;
+                            dx = __ldg(Lg + kListLen); dy = __ldg(Lg + 2 * kListLen); dz = __ldg(Lg + 3 * kListLen);
                         }
                     });
                 }

@@ -39,6 +39,7 @@ struct FrArgs {
     int64_t* sel_edge; int32_t* sel_image;
     int mode;
     const float4* cache;      // optional per-pair results of pair_cache_kernel, valid for ranges (cache_range)^3
+    const float* list;        // optional per-pair sorted translation lists (pair_list_kernel)
     int cache_range;
 };
 
@@ -141,7 +142,7 @@ __device__ __forceinline__ Cand first_axis_candidate(const Cell& cell, float a, 
 // of the same pair (same operations, same value); otherwise it is searched here.
 __device__ __forceinline__ Cand second_axis_candidate(const Cell& cell, float a, int R1, int R2, int R3, float amp,
                                                       uint64_t seed, uint64_t tid, float f1x, float f1y, float f1z,
-                                                      float d2min_known)
+                                                      float d2min_known, const float* list)
 {
     Cand c; c.ux = c.uy = c.uz = 0.f; c.img = -1; c.value = -1e15f; c.d2raw = 0.f;
     float d2min = d2min_known >= 0.f ? d2min_known : 1e10f;
@@ -156,34 +157,47 @@ __device__ __forceinline__ Cand second_axis_candidate(const Cell& cell, float a,
     float best = -1e15f;                 // running maximum of score + noise
     const float half = 0.5f * amp;
     const int L2 = 2 * R2 + 1, L3 = 2 * R3 + 1;
-    for (int k1 = 0; k1 <= 2 * R1; k1++) {
-        const int n1 = centre_out(k1);
-        for (int k2 = 0; k2 <= 2 * R2; k2++) {
-            const int n2 = centre_out(k2);
-            for (int k3 = 0; k3 <= 2 * R3; k3++) {
-                const int n3 = centre_out(k3);
-                float dx, dy, dz, d2;
-                separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
-                if (!(d2 > kTiny)) continue;
-                const float gauss = __fmul_rn(a, __fsub_rn(d2, d2min));
-                if (__fadd_rn(gauss, half) < best) continue;            // score + noise <= gauss + half
-                const float d = __fsqrt_rn(d2);
-                const float vx = __fdiv_rn(dx, d), vy = __fdiv_rn(dy, d), vz = __fdiv_rn(dz, d);
-                const float cs = __fadd_rn(__fadd_rn(__fmul_rn(vx, f1x), __fmul_rn(vy, f1y)), __fmul_rn(vz, f1z));
-                if (!(fabsf(cs) <= kCosMax)) continue;
-                const float one_m = __fsub_rn(1.0f, fabsf(cs));
-                const float clipped = one_m > kTiny ? one_m : 1e-5f;
-                const float score = __fadd_rn(gauss, logf(clipped));
-                const int t = ((n1 + R1) * L2 + (n2 + R2)) * L3 + (n3 + R3);
-                const float noisy = amp == 0.0f ? score : __fadd_rn(score, noise_term(amp, seed, tid, (uint32_t)t));
-                if (noisy > best || (noisy == best && t < c.img)) {
-                    best = noisy;
-                    c.ux = vx; c.uy = vy; c.uz = vz;
-                    c.value = __fadd_rn(score, __fmul_rn(a, d2min));
-                    c.img = t;
-                }
-            }
+    // one candidate: exactly the reference's arithmetic, whatever the visiting order
+    auto score_candidate = [&](const int n1, const int n2, const int n3) {
+        float dx, dy, dz, d2;
+        separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
+        if (!(d2 > kTiny)) return;
+        const float gauss = __fmul_rn(a, __fsub_rn(d2, d2min));
+        if (__fadd_rn(gauss, half) < best) return;              // score + noise <= gauss + half
+        const float d = __fsqrt_rn(d2);
+        const float vx = __fdiv_rn(dx, d), vy = __fdiv_rn(dy, d), vz = __fdiv_rn(dz, d);
+        const float cs = __fadd_rn(__fadd_rn(__fmul_rn(vx, f1x), __fmul_rn(vy, f1y)), __fmul_rn(vz, f1z));
+        if (!(fabsf(cs) <= kCosMax)) return;
+        const float one_m = __fsub_rn(1.0f, fabsf(cs));
+        const float clipped = one_m > kTiny ? one_m : 1e-5f;
+        const float score = __fadd_rn(gauss, logf(clipped));
+        const int t = ((n1 + R1) * L2 + (n2 + R2)) * L3 + (n3 + R3);
+        const float noisy = amp == 0.0f ? score : __fadd_rn(score, noise_term(amp, seed, tid, (uint32_t)t));
+        if (noisy > best || (noisy == best && t < c.img)) {
+            best = noisy;
+            c.ux = vx; c.uy = vy; c.uz = vz;
+            c.value = __fadd_rn(score, __fmul_rn(a, d2min));
+            c.img = t;
         }
+    };
+    if (list != nullptr) {
+        // Candidates nearest-first from the pair's sorted list.  The Gaussian part of the score only falls
+        // along the list and the other part is never positive, so the search ends at the first entry whose
+        // Gaussian part -- with a margin for the few ulp between the list's fused arithmetic and the
+        // arithmetic above -- cannot reach the running maximum: nothing behind it can win or tie.
+        for (int s = 0; s < kListLen; s++) {
+            const float d2l = __ldg(list + s);
+            if (!(d2l < 1e29f)) break;                                   // end of the real entries
+            const float g_est = a * (d2l - d2min);
+            const float slack = fabsf(a) * d2l * 4e-6f + fabsf(g_est) * 2e-6f + 1e-12f;
+            if (g_est + slack + half < best) break;
+            const int code = __float_as_int(__ldg(list + 4 * kListLen + s));
+            score_candidate((code & 255) - R1, ((code >> 8) & 255) - R2, ((code >> 16) & 255) - R3);
+        }
+    } else {
+        for (int k1 = 0; k1 <= 2 * R1; k1++)
+            for (int k2 = 0; k2 <= 2 * R2; k2++)
+                for (int k3 = 0; k3 <= 2 * R3; k3++) score_candidate(centre_out(k1), centre_out(k2), centre_out(k3));
     }
     return c;
 }
@@ -300,8 +314,10 @@ __global__ void __launch_bounds__(kFrThreads, 3) max_frame_kernel(const FrArgs A
                     }
                 } else {
                     const float known = round == 0 ? d2raw0 : (round == 1 ? d2raw1 : (round == 2 ? d2raw2 : -1.f));
+                    const bool hit = A.list != nullptr && R1 == A.cache_range && R2 == A.cache_range && R3 == A.cache_range;
                     cd = second_axis_candidate(cell, row_a[r], R1, R2, R3, P.noise, A.seed2, noise_id,
-                                               row_f1[r][0], row_f1[r][1], row_f1[r][2], known);
+                                               row_f1[r][0], row_f1[r][1], row_f1[r][2], known,
+                                               hit ? A.list + (size_t)e * kListStride : nullptr);
                 }
                 const float s = __fadd_rn(dot, cd.value);
                 if (s > -1e10f) {
@@ -397,12 +413,10 @@ __global__ void __launch_bounds__(256) pair_cache_kernel(const float* __restrict
     out[e] = make_float4(d2raw, d2next, __int_as_float(best_t), d2all);
 }
 
-// Per-pair translation list for lattice ranges (R, R, R) with (2R+1)^3 <= kListLen: the separations of all
-// translations of a pair sorted by squared distance (equal distances in index order), as four planes of
-// kListLen floats -- d^2, x, y, z -- with the fused arithmetic of the lattice-sum kernel.  Unused entries
-// hold d^2 = 1e30.  Because the weight exp(a (d^2 - d^2_min)) falls with the distance, the translations a
-// lattice-sum task has to expand are a prefix of this list, whatever the head or the layer.
-constexpr int kListLen = 128;
+// Per-pair translation list for lattice ranges (R, R, R) with (2R+1)^3 <= kListLen: all translations of a
+// pair sorted by squared distance (equal distances in index order).  Because the weight
+// exp(a (d^2 - d^2_min)) falls with the distance, the translations a lattice-sum task has to expand, and the
+// candidates a second-axis search has to score, are a prefix of this list, whatever the head or the layer.
 
 __global__ void __launch_bounds__(kListLen) pair_list_kernel(const float* __restrict__ pos_ij, const float* __restrict__ tvecs,
                                                              const int64_t* __restrict__ batch, const int64_t* __restrict__ edges,
@@ -432,8 +446,11 @@ __global__ void __launch_bounds__(kListLen) pair_list_kernel(const float* __rest
         const float dj = sd2[j];
         rank += (dj < d2 || (dj == d2 && j < t)) ? 1 : 0;
     }
-    float* o = out + (size_t)e * (4 * kListLen);
+    float* o = out + (size_t)e * kListStride;
     o[rank] = d2; o[kListLen + rank] = dx; o[2 * kListLen + rank] = dy; o[3 * kListLen + rank] = dz;
+    int code = -1;
+    if (t < nT) { const int q = t / L; code = (q / L) | ((q % L) << 8) | ((t % L) << 16) | (t << 24); }
+    o[4 * kListLen + rank] = __int_as_float(code);
 }
 
 int pair_cache(const float* pos_ij, const float* tvecs, const int64_t* batch, const int64_t* edges, int64_t E, int R,

@@ -54,8 +54,8 @@ class LayerGeometry:
         if self.cache_range > 0 and self.E > 0:
             dev = pos_ij.device
             self.pair_cache = torch.empty((self.E, 4), device=dev, dtype=torch.float32)
-            if (2 * self.cache_range + 1) ** 3 <= 128:       # sorted translation lists: 2 KB per pair
-                self.pair_list = torch.empty((self.E, 4, 128), device=dev, dtype=torch.float32)
+            if (2 * self.cache_range + 1) ** 3 <= 128:       # sorted translation lists: 2.5 KB per pair
+                self.pair_list = torch.empty((self.E, 5, 128), device=dev, dtype=torch.float32)
             _lib.invoke("cfb200_pair_cache", 2, dev, _lib.ptr(pos_ij), _lib.ptr(tvecs), _lib.iptr(batch),
                         _lib.iptr(edges), self.N, self.E, self.cache_range, _lib.ptr(self.pair_cache),
                         _lib.ptr(self.pair_list))
@@ -81,7 +81,7 @@ class FusedEncoderLayerFunc(torch.autograd.Function):
         s1, s2 = _draw_seed(), _draw_seed()
         _lib.invoke("cfb200_max_frames_cached", 1, dev, p(qs), p(k), p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
                     ip(geo.batch), ip(geo.edges), ip(geo.e_start), N, E, meta["cutoff"], s1, s2, p(f[0]), p(f[1]), p(f[2]),
-                    p(geo.pair_cache), geo.cache_range)
+                    p(geo.pair_cache), p(geo.pair_list), geo.cache_range)
         z, val = new(E, H), new(E, H, hd)
         Wd3, W13, W23, W33 = Wd[0], W1[0], W2[0], W3[0]
         _lib.invoke("cfb200_framed_proj_fwd_cached", 1, dev, p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),

@@ -207,13 +207,14 @@ int cfb200_framed_proj_bwd_noalloc(const float* a_ik, const float* pos_ij, const
  *     [0], [1]  smallest and second smallest d^2 > 1e-5 over the translations,
  *     [2]       linear index of the first translation attaining [0] (int32 bits, -1 if none),
  *     [3]       smallest d^2 over all translations;
- *   pair_list (E,4,128) float, only for (2 range + 1)^3 <= 128 (CFB200_E_UNSUPPORTED otherwise):
- *     the separation vectors of all translations sorted by squared distance -- planes d^2, x, y, z;
- *     unused entries have d^2 = 1e30.
+ *   pair_list (E,5,128) float, only for (2 range + 1)^3 <= 128 (CFB200_E_UNSUPPORTED otherwise):
+ *     all translations sorted by squared distance -- planes d^2, x, y, z of the separation vector and
+ *     the packed translation (n1+range) | (n2+range) << 8 | (n3+range) << 16 | index << 24 (int32
+ *     bits); unused entries have d^2 = 1e30.
  * The *_cached entry points compute what their plain namesakes compute and use the cache for every
  * (atom, head) whose three lattice ranges equal cache_range; other ranges are searched as usual.
- * With pair_cache the results are bit-identical to the plain entry points; with pair_list the
- * lattice sums are accumulated nearest-first instead of in index order (differences of a few ulp).
+ * Frames are bit-identical to the plain entry point with either cache; with pair_list the lattice
+ * sums are accumulated nearest-first instead of in index order (differences of a few ulp).
  * Either pointer may be NULL. */
 int cfb200_pair_cache(const float* pos_ij, const float* tvecs, const int64_t* batch,
                       const int64_t* edges, int64_t N, int64_t E, int range, float* pair_cache,
@@ -223,7 +224,8 @@ int cfb200_max_frames_cached(const float* q_scaled, const float* k, const float*
                              const int64_t* batch, const int64_t* edges, const int64_t* e_start,
                              int64_t N, int64_t E, float cutoff_radius, uint64_t seed1,
                              uint64_t seed2, float* frame1, float* frame2, float* frame3,
-                             const float* pair_cache, int cache_range, void* stream);
+                             const float* pair_cache, const float* pair_list, int cache_range,
+                             void* stream);
 int cfb200_framed_proj_fwd_cached(const float* a_ik, const float* pos_ij, const float* tvecs,
                                   const float* rvlen, const int64_t* batch, const int64_t* edges,
                                   int64_t N, int64_t E, float dist_max, float cutoff_radius,

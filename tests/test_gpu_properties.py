@@ -321,7 +321,7 @@ def test_pair_cache_changes_no_bit(noise):
     N, E, H, hd = D["a"].shape[0], D["edges"].shape[1], 8, 16
     p, ip = _lib.ptr, _lib.iptr
     cache = torch.empty(E, 4, device=dev)
-    plist = torch.empty(E, 4, 128, device=dev)
+    plist = torch.empty(E, 5, 128, device=dev)
     _lib.invoke("cfb200_pair_cache", 2, dev, p(D["pos_ij"]), p(tv), ip(D["batch"]), ip(D["edges"]), N, E, 2, p(cache),
                 p(plist))
     qs = (D["q"] / 4.0).contiguous()
@@ -330,7 +330,7 @@ def test_pair_cache_changes_no_bit(noise):
         f = torch.empty(3, N, H, 3, device=dev)
         _lib.invoke("cfb200_max_frames_cached", 1, dev, p(qs), p(D["k"]), p(D["a"]), p(D["pos_ij"]), p(tv), p(rvlen),
                     ip(D["batch"]), ip(D["edges"]), ip(D["e_start"]), N, E, -3.5, 17, 29, p(f[0]), p(f[1]), p(f[2]),
-                    p(use), 2)
+                    p(use), None, 2)
         z, val = torch.empty(E, H, device=dev), torch.empty(E, H, hd, device=dev)
         W = [w[0].contiguous() for w in D["W"]]
         _lib.invoke("cfb200_framed_proj_fwd_cached", 1, dev, p(D["a"]), p(D["pos_ij"]), p(tv), p(rvlen), ip(D["batch"]),
@@ -350,7 +350,15 @@ def test_pair_cache_changes_no_bit(noise):
     d2l = plist[:, 0]
     assert bool((d2l[:, 1:] >= d2l[:, :-1]).all())
     assert bool((d2l[:, 125:] == 1e30).all()) and bool((d2l[:, :125] < 1e30).all())
-    vec2 = (plist[:, 1:, :125] ** 2).sum(1)
+    vec2 = (plist[:, 1:4, :125] ** 2).sum(1)
+    codes = plist[:, 4, :125].contiguous().view(torch.int32)
+    assert bool((codes >> 24 == ((codes & 255) * 5 + ((codes >> 8) & 255)) * 5 + ((codes >> 16) & 255)).all())
+    assert bool((codes.sort(dim=1).values >> 24 == torch.arange(125, device=dev, dtype=torch.int32)[None]).all())
+    flist = torch.empty(3, N, H, 3, device=dev)
+    _lib.invoke("cfb200_max_frames_cached", 1, dev, p(qs), p(D["k"]), p(D["a"]), p(D["pos_ij"]), p(tv), p(rvlen),
+                ip(D["batch"]), ip(D["edges"]), ip(D["e_start"]), N, E, -3.5, 17, 29, p(flist[0]), p(flist[1]),
+                p(flist[2]), p(cache), p(plist), 2)
+    assert torch.equal(flist, outs[0][0]), "frames searched nearest-first differ from the exhaustive search"
     assert float(((vec2 - d2l[:, :125]).abs() / (d2l[:, :125] + 1e-6)).max()) < 1e-5
     assert torch.equal(d2l[:, 0], cache[:, 3])
     f, z0, v0 = outs[0]
