@@ -418,39 +418,79 @@ __global__ void __launch_bounds__(256) pair_cache_kernel(const float* __restrict
 // exp(a (d^2 - d^2_min)) falls with the distance, the translations a lattice-sum task has to expand, and the
 // candidates a second-axis search has to score, are a prefix of this list, whatever the head or the layer.
 
-__global__ void __launch_bounds__(kListLen) pair_list_kernel(const float* __restrict__ pos_ij, const float* __restrict__ tvecs,
-                                                             const int64_t* __restrict__ batch, const int64_t* __restrict__ edges,
-                                                             int64_t E, int R, float* __restrict__ out)
+// warp = one pair; lane l holds list positions l, l+32, l+64, l+96.  Keys are (bits of d^2) << 32 | index:
+// d^2 >= 0, so the unsigned order of the bits is the order of the values, and equal distances fall in
+// index order.  A bitonic network sorts the 128 keys: strides below 32 exchange between lanes, strides 32
+// and 64 between a lane's own registers.
+__global__ void __launch_bounds__(128) pair_list_kernel(const float* __restrict__ pos_ij, const float* __restrict__ tvecs,
+                                                        const int64_t* __restrict__ batch, const int64_t* __restrict__ edges,
+                                                        int64_t E, int R, float* __restrict__ out)
 {
-    __shared__ float sd2[kListLen];
-    const int64_t e = blockIdx.x;
-    const int t = threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int64_t e = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (e >= E) return;
     const int L = 2 * R + 1, nT = L * L * L;
     const int64_t c = batch[edges[e]];
     const float* Tc = tvecs + 9 * c;
-    float dx = 0.f, dy = 0.f, dz = 0.f, d2 = 1e30f;
-    if (t < nT) {
-        const int q = t / L;
-        const float n1 = (float)(q / L - R), n2 = (float)(q % L - R), n3 = (float)(t % L - R);
-        const float rx = __ldg(pos_ij + 3 * e), ry = __ldg(pos_ij + 3 * e + 1), rz = __ldg(pos_ij + 3 * e + 2);
-        const float ox = fmaf(__ldg(Tc + 6), n3, fmaf(__ldg(Tc + 3), n2, rx)), oy = fmaf(__ldg(Tc + 7), n3, fmaf(__ldg(Tc + 4), n2, ry)),
-                    oz = fmaf(__ldg(Tc + 8), n3, fmaf(__ldg(Tc + 5), n2, rz));
-        dx = fmaf(__ldg(Tc), n1, ox); dy = fmaf(__ldg(Tc + 1), n1, oy); dz = fmaf(__ldg(Tc + 2), n1, oz);
+    const float t1x = __ldg(Tc), t1y = __ldg(Tc + 1), t1z = __ldg(Tc + 2);
+    const float t2x = __ldg(Tc + 3), t2y = __ldg(Tc + 4), t2z = __ldg(Tc + 5);
+    const float t3x = __ldg(Tc + 6), t3y = __ldg(Tc + 7), t3z = __ldg(Tc + 8);
+    const float rx = __ldg(pos_ij + 3 * e), ry = __ldg(pos_ij + 3 * e + 1), rz = __ldg(pos_ij + 3 * e + 2);
+    auto separation_fused = [&](const int t, float& dx, float& dy, float& dz, float& d2, int& code) {
+        const int q = t / L, k1 = q / L, k2 = q - k1 * L, k3 = t - q * L;
+        const float n1 = (float)(k1 - R), n2 = (float)(k2 - R), n3 = (float)(k3 - R);
+        const float ox = fmaf(t3x, n3, fmaf(t2x, n2, rx)), oy = fmaf(t3y, n3, fmaf(t2y, n2, ry)), oz = fmaf(t3z, n3, fmaf(t2z, n2, rz));
+        dx = fmaf(t1x, n1, ox); dy = fmaf(t1y, n1, oy); dz = fmaf(t1z, n1, oz);
         d2 = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
+        code = k1 | (k2 << 8) | (k3 << 16) | (t << 24);
+    };
+    unsigned long long key[4];
+#pragma unroll
+    for (int r = 0; r < 4; r++) {
+        const int t = r * 32 + lane;
+        float dx, dy, dz, d2 = 1e30f;
+        int code;
+        if (t < nT) separation_fused(t, dx, dy, dz, d2, code);
+        key[r] = ((unsigned long long)__float_as_uint(d2) << 32) | (unsigned)t;
     }
-    sd2[t] = d2;
-    __syncthreads();
-    int rank = 0;
-#pragma unroll 8
-    for (int j = 0; j < kListLen; j++) {
-        const float dj = sd2[j];
-        rank += (dj < d2 || (dj == d2 && j < t)) ? 1 : 0;
+#pragma unroll
+    for (int k = 2; k <= kListLen; k <<= 1) {
+#pragma unroll
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            if (j >= 32) {
+                const int dr = j >> 5;
+#pragma unroll
+                for (int r = 0; r < 4; r++) {
+                    if ((r & dr) == 0) {
+                        const bool up = (((r * 32 + lane) & k) == 0);
+                        const unsigned long long lo = key[r] < key[r | dr] ? key[r] : key[r | dr];
+                        const unsigned long long hi = key[r] < key[r | dr] ? key[r | dr] : key[r];
+                        key[r] = up ? lo : hi;
+                        key[r | dr] = up ? hi : lo;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < 4; r++) {
+                    const unsigned long long other = __shfl_xor_sync(0xffffffffu, key[r], j);
+                    const bool up = (((r * 32 + lane) & k) == 0);
+                    const bool take_min = ((lane & j) == 0) == up;
+                    const bool less = key[r] < other;
+                    key[r] = (less == take_min) ? key[r] : other;
+                }
+            }
+        }
     }
-    float* o = out + (size_t)e * kListStride;
-    o[rank] = d2; o[kListLen + rank] = dx; o[2 * kListLen + rank] = dy; o[3 * kListLen + rank] = dz;
-    int code = -1;
-    if (t < nT) { const int q = t / L; code = (q / L) | ((q % L) << 8) | ((t % L) << 16) | (t << 24); }
-    o[4 * kListLen + rank] = __int_as_float(code);
+    float* o = out + (size_t)e * kListStride + lane;
+#pragma unroll
+    for (int r = 0; r < 4; r++) {
+        const int t = (int)(unsigned)(key[r] & 0xffffffffull);
+        float dx = 0.f, dy = 0.f, dz = 0.f, d2 = 1e30f;
+        int code = -1;
+        if (t < nT) separation_fused(t, dx, dy, dz, d2, code);
+        o[r * 32] = d2; o[kListLen + r * 32] = dx; o[2 * kListLen + r * 32] = dy; o[3 * kListLen + r * 32] = dz;
+        o[4 * kListLen + r * 32] = __int_as_float(code);
+    }
 }
 
 int pair_cache(const float* pos_ij, const float* tvecs, const int64_t* batch, const int64_t* edges, int64_t E, int R,
@@ -462,8 +502,7 @@ int pair_cache(const float* pos_ij, const float* tvecs, const int64_t* batch, co
                                                                       reinterpret_cast<float4*>(out));
     if (list != nullptr) {
         if ((2 * R + 1) * (2 * R + 1) * (2 * R + 1) > kListLen) return CFB200_E_UNSUPPORTED;
-        if (E > 0x7fffffff) return CFB200_E_TOO_LARGE;
-        pair_list_kernel<<<(unsigned)E, kListLen, 0, st>>>(pos_ij, tvecs, batch, edges, E, R, list);
+        pair_list_kernel<<<(unsigned)((E + 3) / 4), 128, 0, st>>>(pos_ij, tvecs, batch, edges, E, R, list);
     }
     return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
 }
