@@ -35,3 +35,42 @@ def register_csr(edge_ij_e, N, e_start):
 
 def f32c(t):
     return None if t is None else t.detach().contiguous().float()
+
+
+_pair_cache = {}
+PAIR_LIST_MAX_PAIRS = 4_000_000      # 2.5 KB of translation list per pair: at most 10 GB
+
+
+def pair_geometry(rpos_ij_e, tvecs_n, batch_i, edge_ij_e, cutoff):
+    """(pair_cache, pair_list, cache_range): which lattice translations of every pair are near, and how
+    near -- the nearest non-zero image, the smallest squared distance, all translations sorted by distance.
+    Pure geometry, identical for every head and layer, so it is computed on the first call that sees a
+    batch's relative positions and kept while that tensor is alive and unmodified; the reference redoes
+    this search inside every kernel launch.  Returns (None, None, 0) when no range can be fixed up front."""
+    from .kernel_manager import KernelManager
+    cfg = KernelManager.config
+    if cfg is None or rpos_ij_e is None or edge_ij_e.shape[1] == 0:
+        return None, None, 0
+    rng = int(cfg.lattice_range if cutoff == 0.0 else cfg.minimum_range)
+    if rng <= 0:
+        return None, None, 0
+    key = id(rpos_ij_e)
+    sig = (rpos_ij_e._version, rpos_ij_e.data_ptr(), tvecs_n.data_ptr(), tvecs_n._version, edge_ij_e.data_ptr(), rng)
+    hit = _pair_cache.get(key)
+    if hit is not None and hit[0]() is rpos_ij_e and hit[1] == sig:
+        return hit[2], hit[3], rng
+    _pair_cache.pop(key, None)
+    dev = rpos_ij_e.device
+    pos, tv = f32c(rpos_ij_e), f32c(tvecs_n)
+    batch, edges = batch_i.contiguous(), edge_ij_e.contiguous()
+    N, E = batch.shape[0], edges.shape[1]
+    cache = torch.empty((E, 4), device=dev, dtype=torch.float32)
+    plist = None
+    if (2 * rng + 1) ** 3 <= 128 and E <= PAIR_LIST_MAX_PAIRS:
+        plist = torch.empty((E, 5, 128), device=dev, dtype=torch.float32)
+    _lib.invoke("cfb200_pair_cache", 2, dev, _lib.ptr(pos), _lib.ptr(tv), _lib.iptr(batch), _lib.iptr(edges), N, E, rng,
+                _lib.ptr(cache), _lib.ptr(plist))
+    for k in [k for k, v in _pair_cache.items() if v[0]() is None]:      # lists are large: drop dead batches at once
+        del _pair_cache[k]
+    _pair_cache[key] = (weakref.ref(rpos_ij_e), sig, cache, plist)
+    return cache, plist, rng

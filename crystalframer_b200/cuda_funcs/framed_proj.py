@@ -2,7 +2,7 @@
 import torch
 
 from .. import _lib
-from .common import csr_offsets, f32c
+from .common import csr_offsets, f32c, pair_geometry
 from .kernel_manager import current_config
 
 
@@ -55,10 +55,12 @@ class RealEncodingWithFramedProjFuncCUDA(torch.autograd.Function):
         z = torch.empty((E, H), device=dev, dtype=torch.float32)
         v = torch.empty((E, H, Wd.shape[-2]), device=dev, dtype=torch.float32) if want_v else None
         p, ip = _lib.ptr, _lib.iptr
-        _lib.invoke("cfb200_framed_proj_fwd", 1, dev,
+        pcache, plist, prange = pair_geometry(rpos_ij_e, tvecs_n, batch_i, edge_ij_e, cutoff)
+        _lib.invoke("cfb200_framed_proj_fwd_cached", 1, dev,
                     p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), N, E, float(dist_max), cutoff,
-                    p(Wd), p(W1), p(W2), p(W3), p(f1), p(f2), p(f3), p(z), p(v))
+                    p(Wd), p(W1), p(W2), p(W3), p(f1), p(f2), p(f3), p(z), p(v), p(pcache), p(plist), prange)
         ctx.save_for_backward(a, pos, tv, batch, edges, rv, Wd, W1, W2, W3, f1, f2, f3, z)
+        ctx.pair_list = (plist, prange)
         ctx.meta = (float(dist_max), cutoff, rvlen_n is not None,
                     None if W_k is None else tuple(W_k.shape), None if W_k1 is None else tuple(W_k1.shape))
         if not want_v:
@@ -88,10 +90,11 @@ class RealEncodingWithFramedProjFuncCUDA(torch.autograd.Function):
         nbytes = lib.cfb200_framed_proj_bwd_workspace_bytes(N, E)
         ws = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=dev)
         p, ip = _lib.ptr, _lib.iptr
-        _lib.invoke("cfb200_framed_proj_bwd", 3, dev,
+        plist, prange = ctx.pair_list
+        _lib.invoke("cfb200_framed_proj_bwd_cached", 3, dev,
                     p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), ip(e_start), N, E, dist_max, cutoff,
                     p(Wd), p(W1), p(W2), p(W3), p(f1), p(f2), p(f3), p(z), p(gz), p(gv), p(ga),
-                    p(gWd), p(gW1), p(gW2), p(gW3), ws.data_ptr(), int(nbytes))
+                    p(gWd), p(gW1), p(gW2), p(gW3), ws.data_ptr(), int(nbytes), p(plist), prange)
         out[0] = ga
         out[9] = gWd.reshape(shape_d)
         if gW1 is not None:

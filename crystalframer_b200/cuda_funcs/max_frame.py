@@ -3,7 +3,7 @@ import numpy as np
 import torch
 
 from .. import _lib
-from .common import csr_offsets, f32c
+from .common import csr_offsets, f32c, pair_geometry
 
 
 def _draw_seed():
@@ -83,9 +83,10 @@ def max_frames_fused(q, k, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_n
     s1, s2 = _draw_seed(), _draw_seed()
     f = torch.empty((3, N, H, 3), device=dev, dtype=torch.float32)
     p, ip = _lib.ptr, _lib.iptr
-    _lib.invoke("cfb200_max_frames", 1, dev,
+    pcache, plist, prange = pair_geometry(rpos_ij_e, tvecs_n, batch_i, edge_ij_e, cutoff)
+    _lib.invoke("cfb200_max_frames_cached", 1, dev,
                 p(qq), p(kk), p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), ip(e_start), N, E, cutoff, s1, s2,
-                p(f[0]), p(f[1]), p(f[2]))
+                p(f[0]), p(f[1]), p(f[2]), p(pcache), p(plist), prange)
     return f[0], f[1], f[2]
 
 

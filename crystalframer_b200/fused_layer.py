@@ -19,8 +19,7 @@ import math
 import torch
 
 from . import _lib
-from .cuda_funcs.common import csr_offsets
-from .cuda_funcs.kernel_manager import KernelManager
+from .cuda_funcs.common import csr_offsets, pair_geometry
 from .cuda_funcs.max_frame import _draw_seed
 
 
@@ -47,18 +46,7 @@ class LayerGeometry:
         self.pos_ij, self.tvecs, self.batch, self.edges, self.rvlen = pos_ij, tvecs, batch, edges, rvlen
         self.N, self.E = batch.shape[0], edges.shape[1]
         self.e_start = csr_offsets(edges, self.N)
-        cfg = KernelManager.config
-        # adaptive ranges are clamped from below by the minimum range, which is what most cells get
-        self.cache_range = int(cfg.lattice_range if cutoff == 0.0 else cfg.minimum_range) if cfg is not None else 0
-        self.pair_cache = self.pair_list = None
-        if self.cache_range > 0 and self.E > 0:
-            dev = pos_ij.device
-            self.pair_cache = torch.empty((self.E, 4), device=dev, dtype=torch.float32)
-            if (2 * self.cache_range + 1) ** 3 <= 128:       # sorted translation lists: 2.5 KB per pair
-                self.pair_list = torch.empty((self.E, 5, 128), device=dev, dtype=torch.float32)
-            _lib.invoke("cfb200_pair_cache", 2, dev, _lib.ptr(pos_ij), _lib.ptr(tvecs), _lib.iptr(batch),
-                        _lib.iptr(edges), self.N, self.E, self.cache_range, _lib.ptr(self.pair_cache),
-                        _lib.ptr(self.pair_list))
+        self.pair_cache, self.pair_list, self.cache_range = pair_geometry(pos_ij, tvecs, batch, edges, cutoff)
 
 
 class FusedEncoderLayerFunc(torch.autograd.Function):
