@@ -3,10 +3,11 @@
 // fused_dpa_bwd_q.cu and the four irregular_transpose launches of the reference).
 //
 // These kernels are bound by HBM traffic: every pair contributes 4 B of logit bias and 64 B of
-// value bias per head and almost no arithmetic.  One warp owns one atom; lane = (jj, h) with
-// h = lane % H the head and jj = lane / H a stride over the atom's pairs, so one warp iteration
-// reads 32/H consecutive pairs x H heads -- contiguous runs of (32/H)*H*4 B of z and
-// (32/H)*H*64 B of the value bias.  The softmax is computed online (running max / sum); the
+// value bias per head and almost no arithmetic.  A warp owns one atom and Hs of its H heads (the
+// heads are split over several warps so that more pairs are in flight per atom: with a handful of
+// atoms per crystal the loops are short chains of dependent loads); lane = (jj, h) with
+// h = lane % Hs the head within the warp's share and jj = lane / Hs a stride over the atom's pairs,
+// so one warp iteration reads 32/Hs consecutive pairs x Hs heads.  The softmax is computed online (running max / sum); the
 // log-sum-exp per (atom, head) is kept for the backward pass, which recomputes probabilities
 // instead of transposing stored ones:
 //   pass 1 (rows, warp = query atom): gz, gvalues, gq
@@ -51,12 +52,14 @@ __device__ __forceinline__ float dot16(const float* a, const float* b)
     return s;
 }
 
-__global__ void __launch_bounds__(kDpWarps * 32) dpa_fwd_kernel(const DpArgs A, int H)
+__global__ void __launch_bounds__(kDpWarps * 32) dpa_fwd_kernel(const DpArgs A, int H, int Hs)
 {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t i = (int64_t)blockIdx.x * kDpWarps + warp;
+    const int S = H / Hs;                                   // warps per atom
+    const int64_t gw = (int64_t)blockIdx.x * kDpWarps + warp;
+    const int64_t i = gw / S;
     if (i >= A.N) return;
-    const int h = lane % H, jj = lane / H, G = 32 / H;
+    const int h = (int)(gw - i * S) * Hs + lane % Hs, jj = lane / Hs, G = 32 / Hs;
     const int64_t e0 = A.e_start[i], e1 = A.e_start[i + 1];
     float qv[kDpHd], acc[kDpHd];
     load16(A.q + (i * H + h) * kDpHd, qv);
@@ -86,7 +89,7 @@ __global__ void __launch_bounds__(kDpWarps * 32) dpa_fwd_kernel(const DpArgs A, 
         m = mn;
     }
     // merge the 32/H partial softmax states of each head
-    for (int o = H; o < 32; o <<= 1) {
+    for (int o = Hs; o < 32; o <<= 1) {
         const float m2 = __shfl_xor_sync(0xffffffffu, m, o), l2 = __shfl_xor_sync(0xffffffffu, l, o);
         const float mn = fmaxf(m, m2);
         const float s1 = (m == -INFINITY) ? 0.f : __expf(m - mn), s2 = (m2 == -INFINITY) ? 0.f : __expf(m2 - mn);
@@ -109,12 +112,14 @@ __global__ void __launch_bounds__(kDpWarps * 32) dpa_fwd_kernel(const DpArgs A, 
 
 // pass 1: rows.  gvalues_ij = p_ij * gout_i ; gz_ij = p_ij * (gout_i . (v_j + b_ij) - gout_i . out_i)
 //         gq_i = sum_j gz_ij * k_j           (fused_dpa_bwd.cu:52-124, fused_dpa_bwd_q.cu:27-52)
-__global__ void __launch_bounds__(kDpWarps * 32) dpa_bwd_rows_kernel(const DpArgs A, int H)
+__global__ void __launch_bounds__(kDpWarps * 32) dpa_bwd_rows_kernel(const DpArgs A, int H, int Hs)
 {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t i = (int64_t)blockIdx.x * kDpWarps + warp;
+    const int S = H / Hs;                                   // warps per atom
+    const int64_t gw = (int64_t)blockIdx.x * kDpWarps + warp;
+    const int64_t i = gw / S;
     if (i >= A.N) return;
-    const int h = lane % H, jj = lane / H, G = 32 / H;
+    const int h = (int)(gw - i * S) * Hs + lane % Hs, jj = lane / Hs, G = 32 / Hs;
     const int64_t e0 = A.e_start[i], e1 = A.e_start[i + 1];
     float qv[kDpHd], go[kDpHd], gq[kDpHd];
     load16(A.q + (i * H + h) * kDpHd, qv);
@@ -153,7 +158,7 @@ __global__ void __launch_bounds__(kDpWarps * 32) dpa_bwd_rows_kernel(const DpArg
 #pragma unroll
         for (int d = 0; d < kDpHd; d++) gq[d] = fmaf(gs, kv[d], gq[d]);
     }
-    for (int o = H; o < 32; o <<= 1)
+    for (int o = Hs; o < 32; o <<= 1)
 #pragma unroll
         for (int d = 0; d < kDpHd; d++) gq[d] += __shfl_xor_sync(0xffffffffu, gq[d], o);
     if (jj == 0) store16(A.gq + (i * H + h) * kDpHd, gq);
@@ -161,12 +166,14 @@ __global__ void __launch_bounds__(kDpWarps * 32) dpa_bwd_rows_kernel(const DpArg
 
 // pass 2: columns.  For key atom j of a crystal whose first atom is a0 and size n, the pair
 // (i, j) has index e_start[i] + (j - a0).  gk_j = sum_i gz_ij q_i ; gv_j = sum_i p_ij gout_i.
-__global__ void __launch_bounds__(kDpWarps * 32) dpa_bwd_cols_kernel(const DpArgs A, int H)
+__global__ void __launch_bounds__(kDpWarps * 32) dpa_bwd_cols_kernel(const DpArgs A, int H, int Hs)
 {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t j = (int64_t)blockIdx.x * kDpWarps + warp;
+    const int S = H / Hs;
+    const int64_t gw = (int64_t)blockIdx.x * kDpWarps + warp;
+    const int64_t j = gw / S;
     if (j >= A.N) return;
-    const int h = lane % H, ii = lane / H, G = 32 / H;
+    const int h = (int)(gw - j * S) * Hs + lane % Hs, ii = lane / Hs, G = 32 / Hs;
     const int64_t ej0 = A.e_start[j];
     const int64_t n = A.e_start[j + 1] - ej0;
     const int64_t a0 = A.edges[A.E + ej0];
@@ -191,7 +198,7 @@ __global__ void __launch_bounds__(kDpWarps * 32) dpa_bwd_cols_kernel(const DpArg
             gv[d] = fmaf(p, go[d], gv[d]);
         }
     }
-    for (int o = H; o < 32; o <<= 1)
+    for (int o = Hs; o < 32; o <<= 1)
 #pragma unroll
         for (int d = 0; d < kDpHd; d++) {
             gk[d] += __shfl_xor_sync(0xffffffffu, gk[d], o);
@@ -205,11 +212,19 @@ __global__ void __launch_bounds__(kDpWarps * 32) dpa_bwd_cols_kernel(const DpArg
 
 static bool heads_ok(int H) { return H >= 1 && H <= 32 && (32 % H) == 0; }
 
+// heads per warp: half of them when that still divides a warp evenly (two warps per atom)
+static int heads_per_warp(int H)
+{
+    return (H % 2 == 0 && 32 % (H / 2) == 0) ? H / 2 : H;
+}
+
 int dpa_fwd(const DpArgs& A, const Params& P, cudaStream_t st)
 {
     if (!heads_ok(P.H)) return CFB200_E_UNSUPPORTED;
     if (A.N == 0) return CFB200_OK;
-    dpa_fwd_kernel<<<(unsigned)((A.N + kDpWarps - 1) / kDpWarps), kDpWarps * 32, 0, st>>>(A, P.H);
+    const int Hs = heads_per_warp(P.H);
+    const int64_t warps = A.N * (P.H / Hs);
+    dpa_fwd_kernel<<<(unsigned)((warps + kDpWarps - 1) / kDpWarps), kDpWarps * 32, 0, st>>>(A, P.H, Hs);
     return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
 }
 
@@ -217,9 +232,11 @@ int dpa_bwd(const DpArgs& A, const Params& P, cudaStream_t st)
 {
     if (!heads_ok(P.H)) return CFB200_E_UNSUPPORTED;
     if (A.N == 0) return CFB200_OK;
-    const unsigned grid = (unsigned)((A.N + kDpWarps - 1) / kDpWarps);
-    dpa_bwd_rows_kernel<<<grid, kDpWarps * 32, 0, st>>>(A, P.H);
-    dpa_bwd_cols_kernel<<<grid, kDpWarps * 32, 0, st>>>(A, P.H);
+    const int Hs = heads_per_warp(P.H);
+    const int64_t warps = A.N * (P.H / Hs);
+    const unsigned grid = (unsigned)((warps + kDpWarps - 1) / kDpWarps);
+    dpa_bwd_rows_kernel<<<grid, kDpWarps * 32, 0, st>>>(A, P.H, Hs);
+    dpa_bwd_cols_kernel<<<grid, kDpWarps * 32, 0, st>>>(A, P.H, Hs);
     return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
 }
 
