@@ -407,9 +407,26 @@ def run_ours(args, rank, world, local_rank):
                 "peak_source": "FP32 FMA throughput measured on this device by cfb200_probe_throughput",
                 "algorithmic_flop_per_launch": flops_bwd, "terms_per_launch": avg_terms, "ms_per_launch": bwd_ms,
                 "sfu_achieved_tops": avg_terms * SFU_TERM / (bwd_ms * 1e-3) / 1e12, "sfu_peak_tops": peaks["sfu_tops"],
-                "traffic": None,
+                # DRAM bytes of one launch: 59.97 MB for 306 560 (pair, head) tasks in the profiler capture of
+                # the operator-level case (profiles/framed_proj_kernel_cfg2_opbench.md), scaled by the task count
+                "traffic": 59.97e6 / 306560.0 * pairs_heads, "traffic_unit": "bytes per launch (DRAM read + write)",
                 "forward": {"ms_per_launch": fwd_ms, "achieved": flops_fwd / (fwd_ms * 1e-3) / 1e12,
                             "frac": flops_fwd / (fwd_ms * 1e-3) / 1e12 / peaks["fp32_tflops"]}}
+    # the HBM-bound kernels of the path (ragged attention): algorithmic bytes over CUDA-event time against the
+    # copy bandwidth measured on this pool (MEASURED_PEAKS.json beside this file; 6650 GB/s if it is absent)
+    hbm_peak, hbm_src = 6650.0, "fallback"
+    peaks_file = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_file):
+        with open(peaks_file) as f:
+            hbm_peak, hbm_src = float(json.load(f)["hbm_gbs"]), "measured"
+    attention_hbm = {}
+    for name, bytes_per_pair_head in (("cfb200_dpa_fwd", 72.0), ("cfb200_dpa_bwd", 72.0 + 8.0 + 68.0)):
+        if name in ktimes:
+            t_ms = ktimes[name][1] / ktimes[name][0]
+            gbs = pairs_heads * bytes_per_pair_head / (t_ms * 1e-3) / 1e9
+            attention_hbm[name] = {"ms_per_launch": t_ms, "achieved": gbs, "peak": hbm_peak, "unit": "GB/s",
+                                   "frac": gbs / hbm_peak, "peak_source": hbm_src,
+                                   "bytes_per_pair_head": bytes_per_pair_head}
     pair_sums = avg_terms * 2 * len(terms) * args.steps * world / (ms * 1e-3)   # one fwd + one bwd sweep per layer, all ranks
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -421,7 +438,8 @@ def run_ours(args, rank, world, local_rank):
                        "e2e_pass_ms_per_step": [round(x / args.steps, 3) for x in passes_e2e]},
             "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": host[0].nbytes(), "d2h_bytes_per_step": 4},
-            "gpu_launches": launches, "pair_sums_per_s": pair_sums, "roofline": roofline, "kernels": kern,
+            "gpu_launches": launches, "pair_sums_per_s": pair_sums, "roofline": roofline,
+            "attention_hbm": attention_hbm, "kernels": kern,
             "host_enqueue_ms_per_step": host_ms / args.steps,
             "ms_per_step_with_kernel_events": ms_instrumented / args.steps, "clocks": clocks, "device_status": status}
     if world == 1 and not args.no_cpu_baseline:
