@@ -42,6 +42,7 @@ BATCH = int(os.environ.get("CF_BENCH_BATCH", 256))   # 256 is the benchmark; oth
 # algorithmic work per unit: one (pair, head, translation) term and one (pair, head) projection
 FLOP_TERM_FWD, FLOP_TERM_BWD, SFU_TERM = 516.0, 738.0, 110.0
 FLOP_PROJ_FWD, FLOP_PROJ_BWD = 8192.0, 16384.0
+FLOP_ATT_FWD, FLOP_ATT_BWD = 70.0, 170.0          # ragged attention per (pair, head)
 
 
 def parse():
@@ -395,21 +396,24 @@ def run_ours(args, rank, world, local_rank):
     kern = {}
     for name, (calls, total) in ktimes.items():
         kern[name] = {"calls": calls, "ms_total": round(total, 3), "ms_avg": round(total / max(calls, 1), 4)}
-    bwd_name = "cfb200_framed_proj_bwd_cached" if "cfb200_framed_proj_bwd_cached" in ktimes else "cfb200_framed_proj_bwd"
+    # the dominant call: the fused lattice-sum + attention backward (or, on the operator path, the
+    # lattice-sum backward); the backward entry point includes the column pass of the attention
+    def first_of(*names):
+        return next(n for n in names if n in ktimes)
+    bwd_name = first_of("cfb200_attn_fused_bwd", "cfb200_framed_proj_bwd_cached", "cfb200_framed_proj_bwd")
+    fwd_name = first_of("cfb200_attn_fused_fwd", "cfb200_framed_proj_fwd_cached", "cfb200_framed_proj_fwd")
     bwd_ms = ktimes[bwd_name][1] / ktimes[bwd_name][0]
-    fwd_name = "cfb200_framed_proj_fwd_cached" if "cfb200_framed_proj_fwd_cached" in ktimes else "cfb200_framed_proj_fwd"
     fwd_ms = ktimes[fwd_name][1] / ktimes[fwd_name][0]
-    flops_bwd = avg_terms * FLOP_TERM_BWD + pairs_heads * FLOP_PROJ_BWD
-    flops_fwd = avg_terms * FLOP_TERM_FWD + pairs_heads * FLOP_PROJ_FWD
+    fused = bwd_name == "cfb200_attn_fused_bwd"
+    flops_bwd = avg_terms * FLOP_TERM_BWD + pairs_heads * (FLOP_PROJ_BWD + (FLOP_ATT_BWD if fused else 0.0))
+    flops_fwd = avg_terms * FLOP_TERM_FWD + pairs_heads * (FLOP_PROJ_FWD + (FLOP_ATT_FWD if fused else 0.0))
     ach = flops_bwd / (bwd_ms * 1e-3) / 1e12
-    roofline = {"kernel": "framed_proj_kernel<backward> (cfb200_framed_proj_bwd)", "bound": "fp32+sfu",
+    roofline = {"kernel": bwd_name, "bound": "fp32+sfu",
                 "achieved": ach, "peak": peaks["fp32_tflops"], "unit": "TFLOP/s", "frac": ach / peaks["fp32_tflops"],
                 "peak_source": "FP32 FMA throughput measured on this device by cfb200_probe_throughput",
                 "algorithmic_flop_per_launch": flops_bwd, "terms_per_launch": avg_terms, "ms_per_launch": bwd_ms,
                 "sfu_achieved_tops": avg_terms * SFU_TERM / (bwd_ms * 1e-3) / 1e12, "sfu_peak_tops": peaks["sfu_tops"],
-                # DRAM bytes of one launch: 59.97 MB for 306 560 (pair, head) tasks in the profiler capture of
-                # the operator-level case (profiles/framed_proj_kernel_cfg2_opbench.md), scaled by the task count
-                "traffic": 59.97e6 / 306560.0 * pairs_heads, "traffic_unit": "bytes per launch (DRAM read + write)",
+                "traffic": None,
                 "forward": {"ms_per_launch": fwd_ms, "achieved": flops_fwd / (fwd_ms * 1e-3) / 1e12,
                             "frac": flops_fwd / (fwd_ms * 1e-3) / 1e12 / peaks["fp32_tflops"]}}
     # the HBM-bound kernels of the path (ragged attention): algorithmic bytes over CUDA-event time against the

@@ -10,6 +10,7 @@
 #include "pool_index.cu"
 #include "coef.cu"
 #include "sigma.cu"
+#include "attn_fused.cu"
 
 namespace cfb {
 
@@ -413,6 +414,82 @@ int cfb200_framed_proj_bwd_cached(const float* a_ik, const float* pos_ij, const 
     A.list = pair_list; A.cache_range = cache_range;
     float* gW[4] = {gW_dist, gW_ang1, gW_ang2, gW_ang3};
     return cfb::framed_proj_bwd(A, P, e_start, ga, gW, workspace, workspace_bytes, S(stream));
+}
+
+static int at_args(cfb::AtArgs& A, const float* q_scaled, const float* k, const float* v, const float* a_ik,
+                   const float* pos_ij, const float* tvecs, const float* rvlen, const int64_t* batch,
+                   const int64_t* edges, const int64_t* e_start, const int32_t* order, int32_t* counters, int64_t N,
+                   int64_t E, float cutoff_radius, const float* W_dist, const float* W1, const float* W2,
+                   const float* W3, const float* f1, const float* f2, const float* f3, const float* pair_list,
+                   int cache_range)
+{
+    if (N < 0 || E < 0) return CFB200_E_SHAPE;
+    if (g_cfg.head_dim != 16 || g_cfg.dist_dim != 64) return CFB200_E_UNSUPPORTED;
+    if (N > 0 && (!q_scaled || !k || !v || !a_ik || !pos_ij || !tvecs || !batch || !edges || !e_start || !W_dist ||
+                  !counters))
+        return CFB200_E_NULL;
+    if (N > 0x7fffffff) return CFB200_E_TOO_LARGE;
+    if (cutoff_radius != 0.0f && N > 0 && rvlen == nullptr) return CFB200_E_NULL;
+    const bool ang = W1 || W2 || W3;
+    if (ang && !(W1 && W2 && W3)) return CFB200_E_NULL;
+    if (ang && N > 0 && !(f1 && f2 && f3)) return CFB200_E_NULL;
+    if (ang && g_cfg.angle_dim == 0) return CFB200_E_UNSUPPORTED;
+    memset(&A, 0, sizeof(A));
+    A.qs = q_scaled; A.k = k; A.v = v; A.a_ik = a_ik; A.pos_ij = pos_ij; A.tvecs = tvecs; A.rvlen = rvlen;
+    A.batch = batch; A.edges = edges; A.e_start = e_start; A.order = order; A.counters = counters; A.N = N; A.E = E;
+    A.W[0] = W_dist; A.W[1] = W1; A.W[2] = W2; A.W[3] = W3;
+    A.frame[0] = f1; A.frame[1] = f2; A.frame[2] = f3;
+    A.list = pair_list; A.cache_range = cache_range;
+    return CFB200_OK;
+}
+
+int cfb200_attn_fused_fwd(const float* q_scaled, const float* k, const float* v, const float* a_ik,
+                          const float* pos_ij, const float* tvecs, const float* rvlen, const int64_t* batch,
+                          const int64_t* edges, const int64_t* e_start, const int32_t* order, int32_t* counters,
+                          int64_t N, int64_t E, float dist_max, float cutoff_radius, const float* W_dist, const float* W_ang1,
+                          const float* W_ang2, const float* W_ang3, const float* frame1, const float* frame2,
+                          const float* frame3, const float* pair_list, int cache_range, float* out, float* z,
+                          float* lse, float* spool, void* stream)
+{
+    cfb::Params P;
+    int rc = make_params(dist_max, cutoff_radius, P);
+    if (rc != CFB200_OK) return rc;
+    cfb::AtArgs A;
+    rc = at_args(A, q_scaled, k, v, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, order, counters, N, E, cutoff_radius,
+                 W_dist, W_ang1, W_ang2, W_ang3, frame1, frame2, frame3, pair_list, cache_range);
+    if (rc != CFB200_OK) return rc;
+    if (N > 0 && (!out || !z || !lse || !spool)) return CFB200_E_NULL;
+    A.out = out; A.z = z; A.lse = lse; A.spool = spool;
+    return cfb::attn_fused_fwd(A, P, S(stream));
+}
+
+int cfb200_attn_fused_bwd(const float* q_scaled, const float* k, const float* v, const float* a_ik,
+                          const float* pos_ij, const float* tvecs, const float* rvlen, const int64_t* batch,
+                          const int64_t* edges, const int64_t* e_start, const int32_t* order, int32_t* counters,
+                          int64_t N, int64_t E, float dist_max, float cutoff_radius, const float* W_dist, const float* W_ang1,
+                          const float* W_ang2, const float* W_ang3, const float* frame1, const float* frame2,
+                          const float* frame3, const float* pair_list, int cache_range, const float* out,
+                          const float* z, const float* lse, const float* gout, float* gq_scaled, float* gk, float* gv,
+                          float* ga, float* gz, void* stream)
+{
+    cfb::Params P;
+    int rc = make_params(dist_max, cutoff_radius, P);
+    if (rc != CFB200_OK) return rc;
+    cfb::AtArgs A;
+    rc = at_args(A, q_scaled, k, v, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, order, counters, N, E, cutoff_radius,
+                 W_dist, W_ang1, W_ang2, W_ang3, frame1, frame2, frame3, pair_list, cache_range);
+    if (rc != CFB200_OK) return rc;
+    if (N > 0 && (!out || !z || !lse || !gout || !gq_scaled || !gk || !gv || !ga || !gz)) return CFB200_E_NULL;
+    A.out = const_cast<float*>(out); A.lse = const_cast<float*>(lse); A.z_in = z; A.gout = gout;
+    A.gq = gq_scaled; A.ga = ga; A.gz = gz;
+    rc = cfb::attn_fused_bwd(A, P, S(stream));
+    if (rc != CFB200_OK || N == 0) return rc;
+    // column pass: gk_j = sum_i gz_ij q_i, gv_j = sum_i p_ij gout_i
+    cfb::DpArgs D;
+    memset(&D, 0, sizeof(D));
+    D.q = q_scaled; D.k = k; D.v = v; D.z = z; D.edges = edges; D.e_start = e_start; D.N = N; D.E = E;
+    D.lse = const_cast<float*>(lse); D.gout = gout; D.gz = gz; D.gk = gk; D.gv = gv;
+    return cfb::dpa_bwd_cols(D, P, S(stream));
 }
 
 static int dp_args(cfb::DpArgs& A, const float* q, const float* k, const float* v, const float* z, const float* b,

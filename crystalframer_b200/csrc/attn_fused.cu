@@ -1,0 +1,343 @@
+// Periodic attention of one encoder layer as two kernels: lattice-sum bias, frame-projected value
+// encoding and ragged softmax attention together, forward and backward (what
+// RealEncodingWithFramedProjFuncCUDA followed by FusedDotProductAttentionCUDA compute in the reference,
+// models/indexed_lattice_multi_head_attention_cuda.py:944-985).
+//
+// The value encoding is linear in the 256 basis sums of a pair, values_ij = W s_ij, so the attention
+// output  out_i = sum_j p_ij (v_j + W s_ij) = sum_j p_ij v_j + W (sum_j p_ij s_ij)  needs the 16 x 256
+// projection once per (atom, head) instead of once per (pair, head), and the (E,H,16) value encoding and
+// its gradient never exist in memory.  Backward likewise: W^T gout_i is formed once per (atom, head), the
+// weight gradient is  sum_i gout_i (x) S_i  with the pooled basis S_i = sum_j p_ij s_ij saved by the
+// forward (a small GEMM left to the caller), and the coefficient gradient of an atom is accumulated by
+// the warp that walks its pairs -- no scratch, no second-stage reductions.
+//
+// Work decomposition: grid = (resident blocks, heads); warp = one (atom, head) at a time, walking the
+// atom's pairs with an online softmax.  The cost of an atom varies a hundredfold (1 to 64+ pairs, a few
+// to a hundred surviving translations each), so warps draw atoms from a per-head queue in the order given
+// by ``order`` (most expensive first).  Which warp computes an atom does not affect any result: nothing is
+// accumulated across atoms, so every sum stays deterministic.  The per-pair lattice arithmetic is LatticeLane
+// (lattice_lane.cuh).  Outputs of the forward: out (N,H,16), z (E,H), lse (N,H), spool (N,H,256) with the
+// distance part unscaled and the angle parts times the angle coefficient (the scaling the reference's
+// weight gradients carry).  The backward leaves gz (E,H) for the column pass that forms gk and gv
+// (dpa_bwd_cols_kernel), gq (N,H,16) with respect to the scaled query, and ga (N,H).
+#include "lattice_lane.cuh"
+
+namespace cfb {
+
+constexpr int kAtWarps = 8;
+constexpr int kAtThreads = kAtWarps * 32;
+constexpr int kAtHd = 16;
+constexpr int kAtK = 256;
+constexpr int kAtWfStride = 260;      // forward: W [16][260], conflict-free 128-bit reads by 16 rows
+constexpr int kAtWtStride = 20;       // backward: W transposed [256][20]
+constexpr int kAtFwdBlocks = 3, kAtBwdBlocks = 3;   // resident blocks per SM the kernels are compiled for
+
+struct AtArgs {
+    const float* qs; const float* k; const float* v; const float* a_ik;
+    const float* pos_ij; const float* tvecs; const float* rvlen;
+    const int64_t* batch; const int64_t* edges; const int64_t* e_start; const int32_t* order;
+    int* counters;            // (H) work-queue heads, zeroed before the launch
+    int64_t N, E;
+    const float* W[4]; const float* frame[3];
+    const float* list; int cache_range;
+    float* z; float* out; float* lse; float* spool;                    // forward outputs
+    const float* gout; const float* z_in;                             // backward inputs (plus out, lse above)
+    float* gz; float* gq; float* ga;                                   // backward outputs
+};
+
+__host__ __device__ constexpr size_t at_smem_bytes(bool bwd)
+{
+    // projection weights | per-warp translation records | per-warp row (forward: pooled basis, backward: gout)
+    return sizeof(float) * ((bwd ? kAtK * kAtWtStride : kAtHd * kAtWfStride) + kAtWarps * (bwd ? 8 * 32 : 6 * 32) +
+                            kAtWarps * (bwd ? 32 : kAtK));
+}
+
+// per-(atom, head) inputs shared by both directions
+struct AtomTask {
+    int64_t i, c, e0, e1;
+    int R1, R2, R3;
+    bool use_list;
+};
+
+template <bool BWD, bool ANG>
+__device__ __forceinline__ AtomTask load_atom(const AtArgs& A, const Params& P, LatticeLane<BWD, ANG>& L, const int64_t i,
+                                              const int h, const int lane)
+{
+    AtomTask T;
+    const int H = P.H;
+    T.i = i; T.c = A.batch[i];
+    T.e0 = A.e_start[i]; T.e1 = A.e_start[i + 1];
+    L.a = __ldg(A.a_ik + i * H + h);
+    if (ANG) {
+#pragma unroll
+        for (int x = 0; x < 3; x++) {
+            const float* f = A.frame[x] + (i * H + h) * 3;
+            L.fx[x] = __ldg(f); L.fy[x] = __ldg(f + 1); L.fz[x] = __ldg(f + 2);
+        }
+    }
+    int Rl = 0;
+    if (lane < 3) Rl = lattice_range_1d(P, L.a, P.cutoff_radius != 0.0f ? __ldg(A.rvlen + 3 * T.c + lane) : 0.0f);
+    T.R1 = __shfl_sync(0xffffffffu, Rl, 0); T.R2 = __shfl_sync(0xffffffffu, Rl, 1); T.R3 = __shfl_sync(0xffffffffu, Rl, 2);
+    T.use_list = A.list != nullptr && T.R1 == A.cache_range && T.R2 == A.cache_range && T.R3 == A.cache_range;
+    return T;
+}
+
+template <bool BWD, bool ANG>
+__device__ __forceinline__ void run_pair(const AtArgs& A, const Params& P, LatticeLane<BWD, ANG>& L, const AtomTask& T,
+                                         const int64_t e)
+{
+    L.reset();
+    if (T.use_list) {
+        L.run_list(P, A.list + (size_t)e * kListStride);
+    } else {
+        L.run_slabs(P, T.R1, T.R2, T.R3, __ldg(A.pos_ij + 3 * e), __ldg(A.pos_ij + 3 * e + 1), __ldg(A.pos_ij + 3 * e + 2),
+                    A.tvecs + 9 * T.c);
+    }
+}
+
+// next atom of this head's work queue (one atomic per task; the whole warp gets the same answer)
+__device__ __forceinline__ int64_t next_task(int* counter, const int lane)
+{
+    int t = 0;
+    if (lane == 0) t = atomicAdd(counter, 1);
+    return (int64_t)__shfl_sync(0xffffffffu, t, 0);
+}
+
+template <bool ANG>
+__global__ void __launch_bounds__(kAtThreads, kAtFwdBlocks) attn_fwd_kernel(const AtArgs A, const Params P)
+{
+    extern __shared__ __align__(16) float smem[];
+    float* W_s = smem;                                      // [16][260]
+    float* tbuf = W_s + kAtHd * kAtWfStride;                // per warp 6 x 32
+    float* rows = tbuf + kAtWarps * 6 * 32;                 // per warp 256: pooled basis, forward scaling
+    const int h = blockIdx.y, H = P.H;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int idx = threadIdx.x; idx < kAtHd * kAtK / 4; idx += kAtThreads) {
+        const int o = idx >> 6, k4 = idx & 63, b = k4 >> 4, d4 = k4 & 15;
+        float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (A.W[b] != nullptr) w = __ldg(reinterpret_cast<const float4*>(A.W[b] + ((size_t)h * kAtHd + o) * 64) + d4);
+        reinterpret_cast<float4*>(W_s)[o * (kAtWfStride / 4) + k4] = w;
+    }
+    LatticeLane<false, ANG> L;
+    L.init(P, lane, tbuf + warp * 6 * 32);
+    float* srow = rows + warp * kAtK;
+    __syncthreads();
+
+    for (;;) {
+        const int64_t t = next_task(A.counters + h, lane);
+        if (t >= A.N) break;
+        const int64_t i = A.order != nullptr ? (int64_t)A.order[t] : t;
+        const AtomTask T = load_atom<false, ANG>(A, P, L, i, h, lane);
+        const float qd = lane < kAtHd ? __ldg(A.qs + (i * H + h) * kAtHd + lane) : 0.f;
+        float m = -INFINITY, l = 0.f, V = 0.f;
+        float S[8];
+#pragma unroll
+        for (int r = 0; r < 8; r++) S[r] = 0.f;
+        // the pairs of an atom run over the atoms of its crystal in order: key atom = first atom + offset
+        const int64_t j0 = A.edges[A.E + T.e0];
+        for (int64_t e = T.e0; e < T.e1; e++) {
+            const int64_t j = j0 + (e - T.e0);
+            float kd = 0.f, vd = 0.f;
+            if (lane < kAtHd) { kd = __ldg(A.k + (j * H + h) * kAtHd + lane); vd = __ldg(A.v + (j * H + h) * kAtHd + lane); }
+            run_pair<false, ANG>(A, P, L, T, e);
+            const float sum = warp_sum(L.sum_l);
+            const float qk = warp_sum(qd * kd);
+            const float zv = logf(sum) + L.ref * L.a;
+            if (lane == 0) A.z[e * H + h] = zv;
+            const float s = qk + zv;
+            const float mn = fmaxf(m, s);
+            const float sc = __expf(m - mn), p = __expf(s - mn);
+            const float f = p / sum;
+            l = fmaf(l, sc, p);
+            V = fmaf(V, sc, p * vd);
+            S[0] = fmaf(S[0], sc, f * L.sd[0]); S[1] = fmaf(S[1], sc, f * L.sd[1]);
+#pragma unroll
+            for (int x = 0; x < 3; x++) {
+                S[2 + 2 * x] = fmaf(S[2 + 2 * x], sc, f * L.sa[x][0]);
+                S[3 + 2 * x] = fmaf(S[3 + 2 * x], sc, f * L.sa[x][1]);
+            }
+            m = mn;
+        }
+        const float inv_l = T.e1 > T.e0 ? 1.0f / l : 0.f;
+        if (lane == 0) A.lse[i * H + h] = m + logf(l);
+        // pooled basis: to memory with the scaling of the weight gradients, to shared memory with the
+        // scaling of the values
+        float* sp = A.spool + (i * H + h) * kAtK;
+        {
+            const float d0 = S[0] * inv_l, d1 = S[1] * inv_l;
+            sp[lane] = d0; sp[32 + lane] = d1;
+            srow[lane] = d0 * P.c_dist; srow[32 + lane] = d1 * P.c_dist;
+#pragma unroll
+            for (int x = 0; x < 3; x++) {
+                const float a0 = S[2 + 2 * x] * inv_l * P.c_ang, a1 = S[3 + 2 * x] * inv_l * P.c_ang;
+                sp[64 + 64 * x + lane] = a0; sp[96 + 64 * x + lane] = a1;
+                srow[64 + 64 * x + lane] = a0; srow[96 + 64 * x + lane] = a1;
+            }
+        }
+        __syncwarp();
+        // out_d = sum_j p_ij v_jd + W_d . S: lane = (output d, half of the 256 basis indices)
+        {
+            const int d = lane & 15, half = lane >> 4;
+            const float4* wr = reinterpret_cast<const float4*>(W_s + d * kAtWfStride) + half * 32;
+            const float4* sr = reinterpret_cast<const float4*>(srow) + half * 32;
+            float acc = 0.f;
+#pragma unroll 8
+            for (int k4 = 0; k4 < 32; k4++) {
+                const float4 u = wr[k4], s4 = sr[k4];
+                acc = fmaf(s4.x, u.x, fmaf(s4.y, u.y, fmaf(s4.z, u.z, fmaf(s4.w, u.w, acc))));
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+            if (lane < kAtHd) A.out[(i * H + h) * kAtHd + lane] = fmaf(V, inv_l, acc);
+        }
+        __syncwarp();
+    }
+}
+
+template <bool ANG>
+__global__ void __launch_bounds__(kAtThreads, kAtBwdBlocks) attn_bwd_kernel(const AtArgs A, const Params P)
+{
+    extern __shared__ __align__(16) float smem[];
+    float* W_s = smem;                                      // [256][20]: W transposed
+    float* tbuf = W_s + kAtK * kAtWtStride;                 // per warp 8 x 32
+    float* rows = tbuf + kAtWarps * 8 * 32;                 // per warp 32: gout of the atom
+    const int h = blockIdx.y, H = P.H;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int idx = threadIdx.x; idx < kAtHd * kAtK / 4; idx += kAtThreads) {
+        const int o = idx >> 6, k4 = idx & 63, b = k4 >> 4, d4 = k4 & 15;
+        float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (A.W[b] != nullptr) w = __ldg(reinterpret_cast<const float4*>(A.W[b] + ((size_t)h * kAtHd + o) * 64) + d4);
+        const int k = k4 * 4;
+        W_s[(k + 0) * kAtWtStride + o] = w.x; W_s[(k + 1) * kAtWtStride + o] = w.y;
+        W_s[(k + 2) * kAtWtStride + o] = w.z; W_s[(k + 3) * kAtWtStride + o] = w.w;
+    }
+    LatticeLane<true, ANG> L;
+    L.init(P, lane, tbuf + warp * 8 * 32);
+    float* grow = rows + warp * 32;
+    __syncthreads();
+
+    for (;;) {
+        const int64_t t = next_task(A.counters + h, lane);
+        if (t >= A.N) break;
+        const int64_t i = A.order != nullptr ? (int64_t)A.order[t] : t;
+        const AtomTask T = load_atom<true, ANG>(A, P, L, i, h, lane);
+        float qd = 0.f, god = 0.f, od = 0.f;
+        if (lane < kAtHd) {
+            qd = __ldg(A.qs + (i * H + h) * kAtHd + lane);
+            god = __ldg(A.gout + (i * H + h) * kAtHd + lane);
+            od = __ldg(A.out + (i * H + h) * kAtHd + lane);
+        }
+        const float D = warp_sum(god * od);
+        const float lse = __ldg(A.lse + i * H + h);
+        // G = W^T gout restricted to this lane's eight basis indices
+        grow[lane] = god;
+        __syncwarp();
+        float G[8];
+        {
+            float gvr[kAtHd];
+            const float4* g4 = reinterpret_cast<const float4*>(grow);
+#pragma unroll
+            for (int o4 = 0; o4 < kAtHd / 4; o4++) {
+                const float4 u = g4[o4];
+                gvr[4 * o4] = u.x; gvr[4 * o4 + 1] = u.y; gvr[4 * o4 + 2] = u.z; gvr[4 * o4 + 3] = u.w;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const float4* wrow = reinterpret_cast<const float4*>(W_s + (j * 32 + lane) * kAtWtStride);
+                float acc = 0.f;
+#pragma unroll
+                for (int o4 = 0; o4 < kAtHd / 4; o4++) {
+                    const float4 u = wrow[o4];
+                    acc = fmaf(u.x, gvr[4 * o4], fmaf(u.y, gvr[4 * o4 + 1], fmaf(u.z, gvr[4 * o4 + 2], fmaf(u.w, gvr[4 * o4 + 3], acc))));
+                }
+                G[j] = acc;
+            }
+        }
+        __syncwarp();
+        float gq = 0.f, ga_acc = 0.f;
+        const int64_t j0 = A.edges[A.E + T.e0];
+        float z_next = __ldg(A.z_in + T.e0 * H + h);
+        for (int64_t e = T.e0; e < T.e1; e++) {
+            const int64_t j = j0 + (e - T.e0);
+            float kd = 0.f, vd = 0.f;
+            if (lane < kAtHd) { kd = __ldg(A.k + (j * H + h) * kAtHd + lane); vd = __ldg(A.v + (j * H + h) * kAtHd + lane); }
+            const float zin = z_next;
+            if (e + 1 < T.e1) z_next = __ldg(A.z_in + (e + 1) * H + h);      // requested one pair ahead
+            L.ref = zin;
+            run_pair<true, ANG>(A, P, L, T, e);
+            // one butterfly for the seven warp-wide sums of this pair
+            float r0 = qd * kd, r1 = god * vd, r2 = L.px_l;
+            float r3 = fmaf(G[0], L.qd[0], G[1] * L.qd[1]), r4 = fmaf(G[0], L.sd[0], G[1] * L.sd[1]);
+            float r5 = 0.f, r6 = 0.f;
+#pragma unroll
+            for (int x = 0; x < 3; x++) {
+                r5 = fmaf(G[2 + 2 * x], L.qa[x][0], fmaf(G[3 + 2 * x], L.qa[x][1], r5));
+                r6 = fmaf(G[2 + 2 * x], L.sa[x][0], fmaf(G[3 + 2 * x], L.sa[x][1], r6));
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                r0 += __shfl_xor_sync(0xffffffffu, r0, o); r1 += __shfl_xor_sync(0xffffffffu, r1, o);
+                r2 += __shfl_xor_sync(0xffffffffu, r2, o); r3 += __shfl_xor_sync(0xffffffffu, r3, o);
+                r4 += __shfl_xor_sync(0xffffffffu, r4, o); r5 += __shfl_xor_sync(0xffffffffu, r5, o);
+                r6 += __shfl_xor_sync(0xffffffffu, r6, o);
+            }
+            const float qk = r0, gov = r1, px = r2, Ad = r3, Bd = r4, Aa = r5, Ba = r6;
+            const float p_att = __expf(qk + zin - lse);
+            // gradient with respect to the logit bias: p (gout . (v_j + values_ij) - gout . out_i)
+            const float gzv = p_att * (gov + P.c_dist * Bd + P.c_ang * Ba - D);
+            if (lane == 0) A.gz[e * H + h] = gzv;
+            // coefficient gradient; the upstream gradient of the pair's values is p gout, so its W^T image is p G.
+            // The reference scales the whole length-kernel result, gz term included, by the distance coefficient
+            // (models/cuda_funcs/real_space_framed_proj.py:183).
+            const float g_len = fmaf(px, gzv, p_att * (Ad - px * Bd));
+            const float g_ang = p_att * (Aa - px * Ba);
+            ga_acc += P.c_dist * g_len + P.c_ang * g_ang;
+            gq = fmaf(gzv, kd, gq);
+        }
+        if (lane == 0) A.ga[i * H + h] = ga_acc;
+        if (lane < kAtHd) A.gq[(i * H + h) * kAtHd + lane] = gq;
+    }
+}
+
+static int at_grid_x(int64_t N, int H, bool bwd)
+{
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int64_t want = ((int64_t)sms * (bwd ? kAtBwdBlocks : kAtFwdBlocks)) / H;
+    if (want < 1) want = 1;
+    const int64_t need = (N + kAtWarps - 1) / kAtWarps;
+    if (need < want) want = need < 1 ? 1 : need;
+    return (int)want;
+}
+
+template <bool BWD, bool ANG>
+static int launch_at(const AtArgs& A, const Params& P, cudaStream_t st)
+{
+    auto kern = BWD ? (void (*)(const AtArgs, const Params))attn_bwd_kernel<ANG> : (void (*)(const AtArgs, const Params))attn_fwd_kernel<ANG>;
+    static bool attr_done[64] = {false};   // per instantiation and device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_done[dev & 63]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)at_smem_bytes(BWD)) != cudaSuccess)
+            return CFB200_E_CUDA;
+        attr_done[dev & 63] = true;
+    }
+    kern<<<dim3(at_grid_x(A.N, P.H, BWD), P.H), kAtThreads, at_smem_bytes(BWD), st>>>(A, P);
+    return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
+}
+
+int attn_fused_fwd(const AtArgs& A, const Params& P, cudaStream_t st)
+{
+    if (A.N == 0) return CFB200_OK;
+    if (cudaMemsetAsync(A.counters, 0, sizeof(int) * P.H, st) != cudaSuccess) return CFB200_E_CUDA;
+    return A.W[1] != nullptr ? launch_at<false, true>(A, P, st) : launch_at<false, false>(A, P, st);
+}
+
+int attn_fused_bwd(const AtArgs& A, const Params& P, cudaStream_t st)
+{
+    if (A.N == 0) return CFB200_OK;
+    if (cudaMemsetAsync(A.counters, 0, sizeof(int) * P.H, st) != cudaSuccess) return CFB200_E_CUDA;
+    return A.W[1] != nullptr ? launch_at<true, true>(A, P, st) : launch_at<true, false>(A, P, st);
+}
+
+}  // namespace cfb

@@ -240,4 +240,15 @@ int dpa_bwd(const DpArgs& A, const Params& P, cudaStream_t st)
     return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
 }
 
+// the column pass alone, for callers that produced gz themselves
+int dpa_bwd_cols(const DpArgs& A, const Params& P, cudaStream_t st)
+{
+    if (!heads_ok(P.H)) return CFB200_E_UNSUPPORTED;
+    if (A.N == 0) return CFB200_OK;
+    const int Hs = heads_per_warp(P.H);
+    const int64_t warps = A.N * (P.H / Hs);
+    dpa_bwd_cols_kernel<<<(unsigned)((warps + kDpWarps - 1) / kDpWarps), kDpWarps * 32, 0, st>>>(A, P.H, Hs);
+    return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
+}
+
 }  // namespace cfb

@@ -23,6 +23,8 @@ from .cuda_funcs.common import csr_offsets, pair_geometry
 from .cuda_funcs.max_frame import _draw_seed
 
 
+FUSED_ATTENTION = True      # lattice sums + attention as one kernel per direction; False: separate entry points
+
 _side_streams = {}
 
 
@@ -40,13 +42,21 @@ class LayerGeometry:
     smallest squared distance of every pair): pure geometry, the same for every head and layer, so it
     is computed once per batch for the lattice range nearly all (atom, head) pairs end up with."""
     __slots__ = ("pos_ij", "tvecs", "batch", "edges", "e_start", "rvlen", "N", "E", "pair_cache", "pair_list",
-                 "cache_range")
+                 "cache_range", "order", "counters")
 
     def __init__(self, pos_ij, tvecs, batch, edges, rvlen, cutoff=0.0):
         self.pos_ij, self.tvecs, self.batch, self.edges, self.rvlen = pos_ij, tvecs, batch, edges, rvlen
         self.N, self.E = batch.shape[0], edges.shape[1]
         self.e_start = csr_offsets(edges, self.N)
         self.pair_cache, self.pair_list, self.cache_range = pair_geometry(pos_ij, tvecs, batch, edges, cutoff)
+        # The order in which the per-atom attention kernels hand out work: most expensive atoms first.  An
+        # atom costs about (a constant + its surviving translations) per pair, and the translations within
+        # reach of a Gaussian of typical width number about (a sphere of radius 8 A) / (cell volume).
+        pairs_per_atom = (self.e_start[1:] - self.e_start[:-1]).float()
+        vcell = (tvecs[:, 0] * torch.linalg.cross(tvecs[:, 1], tvecs[:, 2])).sum(1).abs().clamp_min(1e-6)
+        survivors = (2145.0 / vcell).clamp(1.0, 125.0)[batch]
+        self.order = torch.argsort(pairs_per_atom * (7.0 + survivors), descending=True, stable=True).to(torch.int32)
+        self.counters = torch.zeros(64, dtype=torch.int32, device=pos_ij.device)
 
 
 class FusedEncoderLayerFunc(torch.autograd.Function):
@@ -70,26 +80,37 @@ class FusedEncoderLayerFunc(torch.autograd.Function):
         _lib.invoke("cfb200_max_frames_cached", 1, dev, p(qs), p(k), p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
                     ip(geo.batch), ip(geo.edges), ip(geo.e_start), N, E, meta["cutoff"], s1, s2, p(f[0]), p(f[1]), p(f[2]),
                     p(geo.pair_cache), p(geo.pair_list), geo.cache_range)
-        z, val = new(E, H), new(E, H, hd)
         Wd3, W13, W23, W33 = Wd[0], W1[0], W2[0], W3[0]
-        _lib.invoke("cfb200_framed_proj_fwd_cached", 1, dev, p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
-                    ip(geo.batch), ip(geo.edges), N, E, meta["dist_max"], meta["cutoff"], p(Wd3), p(W13), p(W23), p(W33),
-                    p(f[0]), p(f[1]), p(f[2]), p(z), p(val), p(geo.pair_cache), p(geo.pair_list), geo.cache_range)
         o, lse = new(N, H, hd), new(N, H)
-        _lib.invoke("cfb200_dpa_fwd", 1, dev, p(qs), p(k), p(v), p(z), p(val), ip(geo.edges), ip(geo.e_start), N, E,
-                    p(o), p(lse), None)
+        if FUSED_ATTENTION:
+            # lattice sums, value encoding and attention in one kernel: the basis sums are pooled with the
+            # attention weights and projected once per (atom, head)
+            z, val, spool = new(E, H), None, new(N, H, 4 * 64)
+            _lib.invoke("cfb200_attn_fused_fwd", 1, dev, p(qs), p(k), p(v), p(a), p(geo.pos_ij), p(geo.tvecs),
+                        p(geo.rvlen), ip(geo.batch), ip(geo.edges), ip(geo.e_start), p(geo.order, torch.int32),
+                        p(geo.counters, torch.int32), N, E,
+                        meta["dist_max"], meta["cutoff"], p(Wd3), p(W13), p(W23), p(W33), p(f[0]), p(f[1]), p(f[2]),
+                        p(geo.pair_list), geo.cache_range, p(o), p(z), p(lse), p(spool))
+        else:
+            z, val, spool = new(E, H), new(E, H, hd), None
+            _lib.invoke("cfb200_framed_proj_fwd_cached", 1, dev, p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
+                        ip(geo.batch), ip(geo.edges), N, E, meta["dist_max"], meta["cutoff"], p(Wd3), p(W13), p(W23),
+                        p(W33), p(f[0]), p(f[1]), p(f[2]), p(z), p(val), p(geo.pair_cache), p(geo.pair_list),
+                        geo.cache_range)
+            _lib.invoke("cfb200_dpa_fwd", 1, dev, p(qs), p(k), p(v), p(z), p(val), ip(geo.edges), ip(geo.e_start), N, E,
+                        p(o), p(lse), None)
         x1 = torch.addmm(bo, o.view(N, D), Wo.t()).add_(x)
         h = torch.addmm(bf1, x1, Wf1.t()).relu_()
         x2 = torch.addmm(bf2, h, Wf2.t()).add_(x1)
-        ctx.save_for_backward(x, Wq, Wk, Wv, w_lat, gauss_scale, Wo, Wd, W1, W2, W3, Wf1, Wf2, q, qs, k, v, a, f, z, val,
-                              o, lse, x1, h)
-        ctx.geo, ctx.meta = geo, meta
+        ctx.save_for_backward(x, Wq, Wk, Wv, w_lat, gauss_scale, Wo, Wd, W1, W2, W3, Wf1, Wf2, q, qs, k, v, a, f, z,
+                              val if val is not None else spool, o, lse, x1, h)
+        ctx.geo, ctx.meta, ctx.fused_attention = geo, meta, val is None
         return x2
 
     @staticmethod
     def backward(ctx, g):
         (x, Wq, Wk, Wv, w_lat, gauss_scale, Wo, Wd, W1, W2, W3, Wf1, Wf2, q, qs, k, v, a, f, z, val, o, lse, x1,
-         h) = ctx.saved_tensors
+         h) = ctx.saved_tensors                  # val: the value encoding, or the pooled basis sums (fused attention)
         geo, meta = ctx.geo, ctx.meta
         H, hd = meta["H"], meta["hd"]
         N, E, dev = geo.N, geo.E, x.device
@@ -118,18 +139,36 @@ class FusedEncoderLayerFunc(torch.autograd.Function):
             gWo = gx1.t().mm(o.view(N, D))
             gbo = gx1.sum(0)
         # attention, lattice sums, coefficients
-        gqs, gk, gv, gz, gval = new(N, H, hd), new(N, H, hd), new(N, H, hd), new(E, H), new(E, H, hd)
-        _lib.invoke("cfb200_dpa_bwd", 2, dev, p(qs), p(k), p(v), p(z), p(val), ip(geo.edges), ip(geo.e_start), N, E,
-                    p(o), p(lse), p(go), p(gqs), p(gk), p(gv), p(gz), p(gval))
         ga = new(N, H)
-        gW = [torch.empty_like(W[0]) for W in (Wd, W1, W2, W3)]
-        lib = _lib.lib()
-        nbytes = int(lib.cfb200_framed_proj_bwd_workspace_bytes(N, E))
-        ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
-        _lib.invoke("cfb200_framed_proj_bwd_cached", 3, dev, p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
-                    ip(geo.batch), ip(geo.edges), ip(geo.e_start), N, E, meta["dist_max"], meta["cutoff"], p(Wd[0]),
-                    p(W1[0]), p(W2[0]), p(W3[0]), p(f[0]), p(f[1]), p(f[2]), p(z), p(gz), p(gval), p(ga), p(gW[0]),
-                    p(gW[1]), p(gW[2]), p(gW[3]), ws.data_ptr(), nbytes, p(geo.pair_list), geo.cache_range)
+        if ctx.fused_attention:
+            spool = val
+            gqs, gk, gv, gz = new(N, H, hd), new(N, H, hd), new(N, H, hd), new(E, H)
+            go = go.view(N, H, hd)
+            _lib.invoke("cfb200_attn_fused_bwd", 2, dev, p(qs), p(k), p(v), p(a), p(geo.pos_ij), p(geo.tvecs),
+                        p(geo.rvlen), ip(geo.batch), ip(geo.edges), ip(geo.e_start), p(geo.order, torch.int32),
+                        p(geo.counters, torch.int32), N, E,
+                        meta["dist_max"], meta["cutoff"], p(Wd[0]), p(W1[0]), p(W2[0]), p(W3[0]), p(f[0]), p(f[1]),
+                        p(f[2]), p(geo.pair_list), geo.cache_range, p(o), p(z), p(lse), p(go), p(gqs), p(gk), p(gv),
+                        p(ga), p(gz))
+            ev3 = torch.cuda.Event()
+            ev3.record(main)
+            with torch.cuda.stream(side):
+                # weight gradients of the value encoding: gW[h] (16 x 256) = sum_i gout[i,h,:]^T spool[i,h,:]
+                side.wait_event(ev3)
+                gW_all = torch.bmm(go.permute(1, 2, 0), spool.permute(1, 0, 2))
+                gW = [gW_all[:, :, 64 * b:64 * (b + 1)].contiguous() for b in range(4)]
+        else:
+            gqs, gk, gv, gz, gval = new(N, H, hd), new(N, H, hd), new(N, H, hd), new(E, H), new(E, H, hd)
+            _lib.invoke("cfb200_dpa_bwd", 2, dev, p(qs), p(k), p(v), p(z), p(val), ip(geo.edges), ip(geo.e_start), N, E,
+                        p(o), p(lse), p(go), p(gqs), p(gk), p(gv), p(gz), p(gval))
+            gW = [torch.empty_like(W[0]) for W in (Wd, W1, W2, W3)]
+            lib = _lib.lib()
+            nbytes = int(lib.cfb200_framed_proj_bwd_workspace_bytes(N, E))
+            ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
+            _lib.invoke("cfb200_framed_proj_bwd_cached", 3, dev, p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
+                        ip(geo.batch), ip(geo.edges), ip(geo.e_start), N, E, meta["dist_max"], meta["cutoff"], p(Wd[0]),
+                        p(W1[0]), p(W2[0]), p(W3[0]), p(f[0]), p(f[1]), p(f[2]), p(z), p(gz), p(gval), p(ga), p(gW[0]),
+                        p(gW[1]), p(gW[2]), p(gW[3]), ws.data_ptr(), nbytes, p(geo.pair_list), geo.cache_range)
         gq, gw = new(N, H, hd), torch.empty_like(w_lat)
         _lib.invoke("cfb200_gauss_coef_bwd", 1, dev, p(q), p(w_lat), p(gauss_scale), N, meta["lb"], meta["beta"],
                     meta["scale_real"], p(ga), p(gqs), p(gq), p(gw))
@@ -145,7 +184,7 @@ class FusedEncoderLayerFunc(torch.autograd.Function):
             done = torch.cuda.Event()
             done.record(side)
         main.wait_event(done)
-        for t in (gWf2, gbf2, gWf1, gbf1, gWo, gbo, gWq, gWk, gWv, gb_in):
+        for t in (gWf2, gbf2, gWf1, gbf1, gWo, gbo, gWq, gWk, gWv, gb_in) + (tuple(gW) if ctx.fused_attention else ()):
             t.record_stream(main)               # allocated on the side stream, consumed on the current one
         return (gx, gWq, gWk, gWv, gb_in, gw, None, gWo, gbo, gW[0].unsqueeze(0), gW[1].unsqueeze(0), gW[2].unsqueeze(0),
                 gW[3].unsqueeze(0), gWf1, gbf1, gWf2, gbf2, None, None)

@@ -245,6 +245,40 @@ int cfb200_framed_proj_bwd_cached(const float* a_ik, const float* pos_ij, const 
                                   int64_t workspace_bytes, const float* pair_list, int cache_range,
                                   void* stream);
 
+/* Lattice-sum bias, frame-projected value encoding and ragged attention of one layer in one pass:
+ * what RealEncodingWithFramedProjFuncCUDA.forward followed by FusedDotProductAttentionCUDA.forward
+ * compute (models/indexed_lattice_multi_head_attention_cuda.py:944-985), without ever forming the
+ * (E,H,head_dim) value encoding: it is linear in the 256 basis sums of a pair, so the sums are pooled
+ * with the attention weights first and projected once per (atom, head).  For head_dim 16 and 64 distance
+ * Gaussians.  order (N) int32 or NULL: the sequence in which atoms are handed to the warps (most
+ * expensive first balances best); counters: num_heads int32 of scratch (work-queue heads; the call
+ * clears them).  pair_list / cache_range as in cfb200_pair_cache (NULL: every pair is
+ * swept).  Outputs: out (N,H,16); z (E,H); lse (N,H) log-sum-exp of the logits; spool (N,H,256) the
+ * attention-pooled basis sums [distance 64 | axis 1..3 64 each], distance part unscaled, angle parts times
+ * the angle coefficient -- the weight gradients are  gW[h] (16 x 256) = sum_i gout[i,h,:]^T spool[i,h,:],
+ * a GEMM left to the caller.
+ * The backward takes the forward's out, z, lse and the upstream gout (N,H,16) and returns gq_scaled, gk,
+ * gv (N,H,16), ga (N,H) and gz (E,H) (scratch the column pass reads; also the gradient of the logit bias). */
+int cfb200_attn_fused_fwd(const float* q_scaled, const float* k, const float* v, const float* a_ik,
+                          const float* pos_ij, const float* tvecs, const float* rvlen,
+                          const int64_t* batch, const int64_t* edges, const int64_t* e_start,
+                          const int32_t* order, int32_t* counters, int64_t N, int64_t E, float dist_max,
+                          float cutoff_radius, const float* W_dist, const float* W_ang1,
+                          const float* W_ang2, const float* W_ang3, const float* frame1,
+                          const float* frame2, const float* frame3, const float* pair_list,
+                          int cache_range, float* out, float* z, float* lse, float* spool,
+                          void* stream);
+int cfb200_attn_fused_bwd(const float* q_scaled, const float* k, const float* v, const float* a_ik,
+                          const float* pos_ij, const float* tvecs, const float* rvlen,
+                          const int64_t* batch, const int64_t* edges, const int64_t* e_start,
+                          const int32_t* order, int32_t* counters, int64_t N, int64_t E, float dist_max,
+                          float cutoff_radius, const float* W_dist, const float* W_ang1,
+                          const float* W_ang2, const float* W_ang3, const float* frame1,
+                          const float* frame2, const float* frame3, const float* pair_list,
+                          int cache_range, const float* out, const float* z, const float* lse,
+                          const float* gout, float* gq_scaled, float* gk, float* gv, float* ga,
+                          float* gz, void* stream);
+
 /* Replaces FusedDotProductAttentionCUDA.forward (models/cuda_funcs/fused_dpa.py:17-64;
  * kernel fused_dpa_fwd.cu).  q_scaled, k, v (N,H,head_dim); z (E,H) or NULL; values
  * (E,H,head_dim) or NULL.  Outputs out (N,H,head_dim), lse (N,H) = log-sum-exp of the logits
