@@ -30,7 +30,7 @@ constexpr int kAtHd = 16;
 constexpr int kAtK = 256;
 constexpr int kAtWfStride = 260;      // forward: W [16][260], conflict-free 128-bit reads by 16 rows
 constexpr int kAtWtStride = 20;       // backward: W transposed [256][20]
-constexpr int kAtFwdBlocks = 3, kAtBwdBlocks = 3;   // resident blocks per SM the kernels are compiled for
+constexpr int kAtFwdBlocks = 2, kAtBwdBlocks = 2;   // resident blocks per SM the kernels are compiled for
 
 struct AtArgs {
     const float* qs; const float* k; const float* v; const float* a_ik;

@@ -381,3 +381,64 @@ def test_fused_layer_matches_operator_path():
     for n in g0:
         scale = float(g0[n].abs().max()) + 1e-12
         assert float((g0[n] - g1[n]).abs().max()) <= 1e-4 * scale + 1e-9, n
+
+
+@pytest.mark.parametrize("workload,nc,use_list", [("cfg1", None, True), ("cfg2", 24, True), ("cfg2", 24, False)])
+def test_fused_attention_entry_points(workload, nc, use_list):
+    """cfb200_attn_fused_fwd / _bwd (lattice sums + value encoding + attention in one pass, the value
+    encoding never materialised) against the CPU oracle's chain of the separate operators."""
+    dev = _cuda()
+    from oracle import oracle as O
+    from crystalframer_b200 import _lib
+    _configure()
+    P = make_problem(workload, num_crystals=nc)
+    g = _geometry(P, dev)
+    geo, b, cfg = P["geo"], P["batch"], P["cfg"]
+    frames = _frames(P)
+    qs = (P["q"] / 4.0).astype(np.float32)
+    z_w, v_w = O.framed_proj_fwd(cfg, P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"],
+                                 P["W_d"], P["W_a"], frames)
+    out_w, prob_w = O.dpa_fwd(cfg, qs, P["k"], P["v"], z_w, v_w, geo["edges"], geo["e_start"])
+    rng = np.random.default_rng(11)
+    go = rng.normal(size=out_w.shape).astype(np.float32)
+    gq_w, gk_w, gv_w, gz_w, gval_w = O.dpa_bwd(cfg, qs, P["k"], P["v"], v_w, geo["edges"], geo["e_start"], prob_w, out_w, go)
+    ga_w, gWd_w, gWa_w = O.framed_proj_bwd(cfg, P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"],
+                                           geo["edges"], geo["e_start"], P["W_d"], P["W_a"], frames, z_w, gz_w, gval_w)
+    z64, v64 = O.framed_proj_fwd(cfg, P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"],
+                                 P["W_d"], P["W_a"], frames, dtype=np.float64)
+    ga_64, gWd_64, gWa_64 = O.framed_proj_bwd(cfg, P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"],
+                                              geo["edges"], geo["e_start"], P["W_d"], P["W_a"], frames, z64, gz_w, gval_w,
+                                              dtype=np.float64)
+    N, E, H, hd = P["a"].shape[0], geo["edges"].shape[1], 8, 16
+    p, ip = _lib.ptr, _lib.iptr
+    t = lambda x: _t(x, dev)
+    q_, k_, v_, a_ = t(qs), t(P["k"]), t(P["v"]), t(P["a"])
+    e_start = t(geo["e_start"])
+    W = [t(P["W_d"])] + [t(P["W_a"][x]) for x in range(3)]
+    f = [t(frames[x]) for x in range(3)]
+    plist = None
+    if use_list:
+        plist = torch.empty(E, 5, 128, device=dev)
+        _lib.invoke("cfb200_pair_cache", 2, dev, p(g["pos_ij"]), p(g["tvecs"]), ip(g["batch"]), ip(g["edges"]), N, E, 2,
+                    None, p(plist))
+    order = torch.argsort(e_start[1:] - e_start[:-1], descending=True, stable=True).to(torch.int32)
+    counters = torch.zeros(8, dtype=torch.int32, device=dev)
+    out, z, lse, spool = (torch.empty(s, device=dev) for s in ((N, H, hd), (E, H), (N, H), (N, H, 256)))
+    common = (p(q_), p(k_), p(v_), p(a_), p(g["pos_ij"]), p(g["tvecs"]), p(g["rvlen"]), ip(g["batch"]), ip(g["edges"]),
+              ip(e_start), p(order, torch.int32), p(counters, torch.int32), N, E, 14.0, -3.5, p(W[0]), p(W[1]), p(W[2]),
+              p(W[3]), p(f[0]), p(f[1]), p(f[2]), p(plist), 2)
+    _lib.invoke("cfb200_attn_fused_fwd", 1, dev, *common, p(out), p(z), p(lse), p(spool))
+    _close("z", z.cpu().numpy(), z_w)
+    _close("out", out.cpu().numpy(), out_w)
+    gq, gk, gv, ga, gz = (torch.empty(s, device=dev) for s in ((N, H, hd), (N, H, hd), (N, H, hd), (N, H), (E, H)))
+    _lib.invoke("cfb200_attn_fused_bwd", 2, dev, *common, p(out), p(z), p(lse), p(t(go)), p(gq), p(gk), p(gv), p(ga), p(gz))
+    _close("gq", gq.cpu().numpy(), gq_w)
+    _close("gk", gk.cpu().numpy(), gk_w)
+    _close("gv", gv.cpu().numpy(), gv_w)
+    _close("gz", gz.cpu().numpy(), gz_w)
+    _close_reduction("ga", ga.cpu().numpy(), ga_w, ga_64)
+    gW = torch.bmm(t(go).permute(1, 2, 0), spool.permute(1, 0, 2)).cpu().numpy()       # (H,16,256)
+    _close_reduction("gW_dist", gW[:, :, :64], gWd_w, gWd_64)
+    for x in range(3):
+        _close_reduction(f"gW_ang{x + 1}", gW[:, :, 64 * (x + 1):64 * (x + 2)], gWa_w[x], gWa_64[x])
+    assert _lib.read_status() == 0
