@@ -1,7 +1,7 @@
 """Operator-level benchmark: the isolated attention path, forward + backward, on one synthetic
 batch (256 crystals, log-normal sizes, q/k/v ~ N(0,1), upstream gradient ~ N(0,1)).
 
-    python -m crystalframer_b200.opbench [--workload cfg2] [--crystals 256] [--iters 20] [--noise 1e-5]
+    python -m crystalframer_b200.opbench [--workload cfg2] [--crystals 256] [--iters 20] [--noise 1e-5] [--fused]
 
 Prints one JSON line with the CUDA-event time of every entry point.  Also the small, fixed
 workload used for single-kernel profiler captures (few iterations, < 1 GB on the device).
@@ -56,6 +56,37 @@ def run_once(I):
     return out
 
 
+def run_once_fused(I):
+    """The same work through the fused entry points (lattice sums + value encoding + attention in one
+    kernel per direction, as the one-node encoder layer calls them)."""
+    from .cuda_funcs.common import pair_geometry
+    dev = I["q"].device
+    p, ip = _lib.ptr, _lib.iptr
+    q, k, v, a = I["q"], I["k"], I["v"], I["a"]
+    N, H, hd = q.shape
+    E = I["edges"].shape[1]
+    qs = q / 4.0
+    f1, f2, f3 = F.max_frames_fused(qs, k, a, I["pos_ij"], I["tv"], I["batch"], I["edges"], I["rvlen"], -3.5)
+    _, plist, prange = pair_geometry(I["pos_ij"], I["tv"], I["batch"], I["edges"], -3.5)
+    if "order" not in I:
+        n_i = (I["e_start"][1:] - I["e_start"][:-1]).float()
+        vcell = (I["tv"][:, 0] * torch.linalg.cross(I["tv"][:, 1], I["tv"][:, 2])).sum(1).abs()
+        I["order"] = torch.argsort(n_i * (7.0 + (2145.0 / vcell).clamp(1.0, 125.0)[I["batch"]]), descending=True,
+                                   stable=True).to(torch.int32)
+        I["counters"] = torch.zeros(H, dtype=torch.int32, device=dev)
+    W = [w[0] for w in I["W"]]
+    out, z, lse, spool = (torch.empty(s, device=dev) for s in ((N, H, hd), (E, H), (N, H), (N, H, 256)))
+    common = (p(qs), p(k), p(v), p(a), p(I["pos_ij"]), p(I["tv"]), p(I["rvlen"]), ip(I["batch"]), ip(I["edges"]),
+              ip(I["e_start"]), p(I["order"], torch.int32), p(I["counters"], torch.int32), N, E, 14.0, -3.5, p(W[0]),
+              p(W[1]), p(W[2]), p(W[3]), p(f1), p(f2), p(f3), p(plist), prange)
+    _lib.invoke("cfb200_attn_fused_fwd", 1, dev, *common, p(out), p(z), p(lse), p(spool))
+    gq, gk, gv, ga, gz = (torch.empty(s, device=dev) for s in ((N, H, hd), (N, H, hd), (N, H, hd), (N, H), (E, H)))
+    _lib.invoke("cfb200_attn_fused_bwd", 2, dev, *common, p(out), p(z), p(lse), p(I["go"]), p(gq), p(gk), p(gv), p(ga),
+                p(gz))
+    gW = torch.bmm(I["go"].permute(1, 2, 0), spool.permute(1, 0, 2))
+    return out, gW
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="cfg2")
@@ -63,18 +94,20 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--noise", type=float, default=1e-5)
+    ap.add_argument("--fused", action="store_true", help="time the fused attention entry points")
     args = ap.parse_args()
     dev = torch.device("cuda:0")
     F.compile_kernels(2, 8, 16, 64, 64, 16, True, 0, 1.0, 4.0, 1.0, 1.0, args.noise)
     I = make_inputs(args.workload, args.crystals, dev)
+    step = run_once_fused if args.fused else run_once
     for _ in range(args.warmup):
-        run_once(I)
+        step(I)
     torch.cuda.synchronize()
     with _lib.KernelTimer() as kt:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(args.iters):
-            run_once(I)
+            step(I)
         e1.record()
         times = kt.summary()
     b = I["batch_obj"]
