@@ -24,8 +24,9 @@
 
 namespace cfb {
 
-constexpr int kAtWarps = 8;
-constexpr int kAtThreads = kAtWarps * 32;
+// warps per block (two blocks per SM either way): the forward runs best with 10 (96 registers), the backward,
+// which holds more state per lane, with 8 (no spills)
+__host__ __device__ constexpr int at_warps(bool bwd) { return bwd ? 8 : 10; }
 constexpr int kAtHd = 16;
 constexpr int kAtK = 256;
 constexpr int kAtWfStride = 260;      // forward: W [16][260], conflict-free 128-bit reads by 16 rows
@@ -48,8 +49,8 @@ struct AtArgs {
 __host__ __device__ constexpr size_t at_smem_bytes(bool bwd)
 {
     // projection weights | per-warp translation records | per-warp row (forward: pooled basis, backward: gout)
-    return sizeof(float) * ((bwd ? kAtK * kAtWtStride : kAtHd * kAtWfStride) + kAtWarps * (bwd ? 8 * 32 : 6 * 32) +
-                            kAtWarps * (bwd ? 32 : kAtK));
+    return sizeof(float) * ((bwd ? kAtK * kAtWtStride : kAtHd * kAtWfStride) + at_warps(bwd) * (bwd ? 8 * 32 : 6 * 32) +
+                            at_warps(bwd) * (bwd ? 32 : kAtK));
 }
 
 // per-(atom, head) inputs shared by both directions
@@ -104,15 +105,15 @@ __device__ __forceinline__ int64_t next_task(int* counter, const int lane)
 }
 
 template <bool ANG>
-__global__ void __launch_bounds__(kAtThreads, kAtFwdBlocks) attn_fwd_kernel(const AtArgs A, const Params P)
+__global__ void __launch_bounds__(at_warps(false) * 32, kAtFwdBlocks) attn_fwd_kernel(const AtArgs A, const Params P)
 {
     extern __shared__ __align__(16) float smem[];
     float* W_s = smem;                                      // [16][260]
     float* tbuf = W_s + kAtHd * kAtWfStride;                // per warp 6 x 32
-    float* rows = tbuf + kAtWarps * 6 * 32;                 // per warp 256: pooled basis, forward scaling
+    float* rows = tbuf + at_warps(false) * 6 * 32;          // per warp 256: pooled basis, forward scaling
     const int h = blockIdx.y, H = P.H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int idx = threadIdx.x; idx < kAtHd * kAtK / 4; idx += kAtThreads) {
+    for (int idx = threadIdx.x; idx < kAtHd * kAtK / 4; idx += at_warps(false) * 32) {
         const int o = idx >> 6, k4 = idx & 63, b = k4 >> 4, d4 = k4 & 15;
         float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
         if (A.W[b] != nullptr) w = __ldg(reinterpret_cast<const float4*>(A.W[b] + ((size_t)h * kAtHd + o) * 64) + d4);
@@ -194,15 +195,15 @@ __global__ void __launch_bounds__(kAtThreads, kAtFwdBlocks) attn_fwd_kernel(cons
 }
 
 template <bool ANG>
-__global__ void __launch_bounds__(kAtThreads, kAtBwdBlocks) attn_bwd_kernel(const AtArgs A, const Params P)
+__global__ void __launch_bounds__(at_warps(true) * 32, kAtBwdBlocks) attn_bwd_kernel(const AtArgs A, const Params P)
 {
     extern __shared__ __align__(16) float smem[];
     float* W_s = smem;                                      // [256][20]: W transposed
     float* tbuf = W_s + kAtK * kAtWtStride;                 // per warp 8 x 32
-    float* rows = tbuf + kAtWarps * 8 * 32;                 // per warp 32: gout of the atom
+    float* rows = tbuf + at_warps(true) * 8 * 32;           // per warp 32: gout of the atom
     const int h = blockIdx.y, H = P.H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int idx = threadIdx.x; idx < kAtHd * kAtK / 4; idx += kAtThreads) {
+    for (int idx = threadIdx.x; idx < kAtHd * kAtK / 4; idx += at_warps(true) * 32) {
         const int o = idx >> 6, k4 = idx & 63, b = k4 >> 4, d4 = k4 & 15;
         float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
         if (A.W[b] != nullptr) w = __ldg(reinterpret_cast<const float4*>(A.W[b] + ((size_t)h * kAtHd + o) * 64) + d4);
@@ -305,7 +306,7 @@ static int at_grid_x(int64_t N, int H, bool bwd)
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     int64_t want = ((int64_t)sms * (bwd ? kAtBwdBlocks : kAtFwdBlocks)) / H;
     if (want < 1) want = 1;
-    const int64_t need = (N + kAtWarps - 1) / kAtWarps;
+    const int64_t need = (N + at_warps(bwd) - 1) / at_warps(bwd);
     if (need < want) want = need < 1 ? 1 : need;
     return (int)want;
 }
@@ -322,7 +323,7 @@ static int launch_at(const AtArgs& A, const Params& P, cudaStream_t st)
             return CFB200_E_CUDA;
         attr_done[dev & 63] = true;
     }
-    kern<<<dim3(at_grid_x(A.N, P.H, BWD), P.H), kAtThreads, at_smem_bytes(BWD), st>>>(A, P);
+    kern<<<dim3(at_grid_x(A.N, P.H, BWD), P.H), at_warps(BWD) * 32, at_smem_bytes(BWD), st>>>(A, P);
     return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
 }
 
