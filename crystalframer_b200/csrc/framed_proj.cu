@@ -4,22 +4,23 @@
 // Work decomposition
 //   grid  = (resident blocks, heads); a block owns one head and a strided subset of the pairs,
 //           which it stages 32 at a time.
-//   warp  = one (pair, head) task at a time.  Lanes first evaluate 32 lattice translations in
-//           parallel (separation, weight w = exp(a (d^2 - d^2_min)), window positions), drop
-//           translations whose weight is below exp(-P.prune) of the largest, and leave one record per surviving
+//   warp  = one (pair, head) task at a time (LatticeLane, lattice_lane.cuh).  Lanes first evaluate 32
+//           lattice translations in parallel -- from the pair's sorted list where one exists, else by
+//           slab sweeps -- (weight w = exp(a (d^2 - d^2_min)), window positions), drop translations
+//           whose weight is below exp(-P.prune) of the largest, and leave one record per surviving
 //           translation in shared memory.  Then the warp walks the survivors: lane l owns basis
 //           indices l and l+32 of each of the four 64-wide Gaussian bases (distance, three frame
 //           axes) and keeps their running sums in registers, so the data-dependent window offset
 //           becomes a per-lane predicate instead of an indexed shared-memory update.
 //   forward: after 4 tasks a warp multiplies its own 4 basis vectors (4 x 256) with the head's
 //           16 x 256 projection from shared memory; warps never wait for one another.
-//   backward: after 4 tasks per warp the block's 32 basis vectors (32 x 256) sit in shared memory
+//   backward: after 8 tasks per warp the block's 64 basis vectors (64 x 256) sit in shared memory
 //           and the block accumulates their outer product with the upstream gradient in registers
 //           -- one weight-gradient partial per block, not per pair.
 //
 // Numerics follow the reference's float expressions for every integer decision (lattice range,
 // window start / end); Gaussians use ex2.approx on pre-scaled arguments.
-#include "common.cuh"
+#include "lattice_lane.cuh"
 
 namespace cfb {
 
@@ -65,12 +66,6 @@ __host__ __device__ constexpr size_t fp_smem_bytes(bool bwd)
                             (size_t)kFpWarps * fp_rec_floats(bwd) + (bwd ? fp_slots(bwd) * kHd : 0));
 }
 
-// exact float value of a small integer (|n| < 2^22) without a conversion instruction
-__device__ __forceinline__ float small_int_to_float(int n)
-{
-    return __int_as_float(0x4B400000 + n) - 12582912.0f;
-}
-
 // two fp32 multiply-adds in one instruction (packed fp32 arithmetic of sm_100): the projection loops are
 // bound by instruction issue, not by the FMA pipe
 __device__ __forceinline__ float2 fma2(float a0, float a1, float b0, float b1, float2 c)
@@ -107,24 +102,13 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
         }
     }
 
-    // per-lane basis constants, pre-scaled so that a Gaussian is ex2(-b*b)
-    const float dstep = P.d_step * kSqrtLog2e, astep = P.a_step * kSqrtLog2e;
-    const float cd_lo = (float)(lane + 1) * dstep, cd_hi = (float)(lane + 33) * dstep;
-    const float ca_lo = (float)(63 - lane) * astep, ca_hi = (float)(31 - lane) * astep;
-    const unsigned win_d = (unsigned)P.win_dist, win_a = (unsigned)P.win_ang;
-    const float inv_d_interval = 1.0f / P.d_interval, d_cut_scaled = P.d_cut / P.d_interval;
-    const float xd_scale = dstep / P.d_interval;
-    const float inv_a_interval = P.angle_dim > 1 ? 1.0f / P.a_interval : 0.0f;
-    const float xa_scale = P.a_sigma_inv * kSqrtLog2e;
-    const bool wide_d = P.win_dist > 32;
-
     float2 gacc[2][4];
     if (BWD) {
 #pragma unroll
         for (int j = 0; j < 4; j++) gacc[0][j] = gacc[1][j] = make_float2(0.f, 0.f);
     }
-    float4* tb = reinterpret_cast<float4*>(tbuf + warp * fp_rec_floats(BWD));
-    float2* tb2 = reinterpret_cast<float2*>(tb + 32);          // forward's second record half
+    LatticeLane<BWD, ANG> L;
+    L.init(P, lane, tbuf + warp * fp_rec_floats(BWD));
     __syncthreads();
 
     // Pair assignment: block b takes pairs b, b + G, b + 2G, ... (G = gridDim.x) and stages them 32
@@ -157,208 +141,41 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
             const bool last_tsk = tsk + 1 == kFpTasksPerWarp;
             const int64_t e_next = ((chunk + (last_tsk ? 1 : 0)) * kFpSlots + slot_of(last_tsk ? 0 : tsk + 1)) * G + blockIdx.x;
             if (e_next < A.E) i_next = (int)A.edges[e_next];
-            const float a = __ldg(A.a_ik + i * H + h);
-            // sorted translation list of this pair (prepared once per batch for ranges cache_range^3): four
-            // groups of 32 squared distances and the first group's vectors are requested right away
-            float dl0 = 0.f, dl1 = 0.f, dl2 = 0.f, dl3 = 0.f, lx0 = 0.f, ly0 = 0.f, lz0 = 0.f;
-            if (A.list != nullptr) {
-                const float* Ll = A.list + (size_t)e * kListStride + lane;
-                dl0 = __ldg(Ll); dl1 = __ldg(Ll + 32); dl2 = __ldg(Ll + 64); dl3 = __ldg(Ll + 96);
-                lx0 = __ldg(Ll + kListLen); ly0 = __ldg(Ll + 2 * kListLen); lz0 = __ldg(Ll + 3 * kListLen);
-            }
-            int Rl = 0;
-            if (lane < 3) Rl = lattice_range_1d(P, a, P.cutoff_radius != 0.0f ? __ldg(A.rvlen + 3 * c + lane) : 0.0f);
-            const int R1 = __shfl_sync(0xffffffffu, Rl, 0), R2 = __shfl_sync(0xffffffffu, Rl, 1), R3 = __shfl_sync(0xffffffffu, Rl, 2);
-            const bool use_list = A.list != nullptr && R1 == A.cache_range && R2 == A.cache_range && R3 == A.cache_range;
-            // separation and cell vectors: only the slab sweeps of pairs without a usable list read them
-            float rx = 0.f, ry = 0.f, rz = 0.f, t1x = 0.f, t1y = 0.f, t1z = 0.f, t2x = 0.f, t2y = 0.f, t2z = 0.f,
-                  t3x = 0.f, t3y = 0.f, t3z = 0.f;
-            if (!use_list) {
-                rx = __ldg(A.pos_ij + 3 * e); ry = __ldg(A.pos_ij + 3 * e + 1); rz = __ldg(A.pos_ij + 3 * e + 2);
-                const float* Tc = A.tvecs + 9 * c;
-                t1x = __ldg(Tc); t1y = __ldg(Tc + 1); t1z = __ldg(Tc + 2);
-                t2x = __ldg(Tc + 3); t2y = __ldg(Tc + 4); t2z = __ldg(Tc + 5);
-                t3x = __ldg(Tc + 6); t3y = __ldg(Tc + 7); t3z = __ldg(Tc + 8);
-            }
-            const int L1 = 2 * R1 + 1, L3 = 2 * R3 + 1, L23 = (2 * R2 + 1) * L3;
-            const int nSub = (L23 + 31) >> 5;                 // 32-lane pieces of one (n2, n3) slab
-            const float invL3 = 1.0f / (float)L3;
-            float fx[3], fy[3], fz[3];
+            // per-pair lattice arithmetic: LatticeLane (lattice_lane.cuh)
+            L.a = __ldg(A.a_ik + i * H + h);
             if (ANG) {
 #pragma unroll
                 for (int x = 0; x < 3; x++) {
                     const float* f = A.frame[x] + (i * H + h) * 3;
-                    fx[x] = __ldg(f); fy[x] = __ldg(f + 1); fz[x] = __ldg(f + 2);
+                    L.fx[x] = __ldg(f); L.fy[x] = __ldg(f + 1); L.fz[x] = __ldg(f + 2);
                 }
             }
             // backward: the pair's upstream gradients are requested now and first used after the lattice
             // loops (lanes 0..15 hold gv, lane 16 holds gz), so their latency is off the critical path
-            float zin = 0.f, g_up = 0.f;
+            float g_up = 0.f;
             if (BWD) {
-                zin = __ldg(A.z_in + e * H + h);
+                L.ref = __ldg(A.z_in + e * H + h);
                 if (lane < kHd) g_up = __ldg(A.gv + (e * H + h) * kHd + lane);
                 else if (lane == kHd) g_up = __ldg(A.gz + e * H + h);
             }
-
-            // Translations are walked slab by slab: lanes own the (n2, n3) offsets of a slab (decoded
-            // once), the loop runs over n1.  ---- sweep A (forward only): minimum squared distance ----
-            float d2min = 1e10f;
-            if (!BWD && use_list) {
-                d2min = __shfl_sync(0xffffffffu, dl0, 0);               // the sorted list starts with the smallest
-            } else if (!BWD && A.cache != nullptr && R1 == A.cache_range && R2 == A.cache_range && R3 == A.cache_range) {
-                d2min = __ldg(&A.cache[e].w);          // head- and layer-independent: computed once per batch
-            } else if (!BWD) {
-                for (int sub = 0; sub < nSub; sub++) {
-                    const int idx = sub * 32 + lane;
-                    int q2 = (int)(((float)idx + 0.5f) * invL3), r3 = idx - q2 * L3;
-                    if (r3 < 0) { q2--; r3 += L3; } else if (r3 >= L3) { q2++; r3 -= L3; }
-                    const float n2 = small_int_to_float(q2 - R2), n3 = small_int_to_float(r3 - R3);
-                    const float ox = fmaf(t3x, n3, fmaf(t2x, n2, rx)), oy = fmaf(t3y, n3, fmaf(t2y, n2, ry)),
-                                oz = fmaf(t3z, n3, fmaf(t2z, n2, rz));
-                    if (idx < L23) {
-                        for (int k1 = 0; k1 < L1; k1++) {
-                            const float n1 = small_int_to_float(k1 - R1);
-                            const float dx = fmaf(t1x, n1, ox), dy = fmaf(t1y, n1, oy), dz = fmaf(t1z, n1, oz);
-                            d2min = fminf(d2min, fmaf(dz, dz, fmaf(dy, dy, dx * dx)));
-                        }
-                    }
-                }
-                d2min = warp_min(d2min);
-            }
-
-            // ---- sweep B: weights, window records, basis accumulation ----
-            float sd[2] = {0.f, 0.f}, sa[3][2] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
-            float qd[2] = {0.f, 0.f}, qa[3][2] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};   // backward: sums of g*p*d2
-            float sum_l = 0.f, px_l = 0.f;
-            // One group = up to 32 translations, one per lane.  ``expand`` builds the window records of the
-            // lanes whose translation passes the pruning threshold and walks these survivors; ``xyz`` yields
-            // a lane's separation vector and is only called by lanes that keep their translation.
-            // log of a translation's weight; its contribution to the normaliser (and, backward, to sum p d^2)
-            auto weigh = [&](const float d2) {
-                const float arg = BWD ? fmaf(a, d2, -zin) : a * (d2 - d2min);
-                const float w = ex2_approx(arg * kLog2e);
-                sum_l += w;
-                if (BWD) px_l = fmaf(w, d2, px_l);
-                return arg;
-            };
-            auto expand = [&](const bool keep, const float arg, const float d2, auto xyz) {
-                {
-                    if (keep) {
-                        float dx, dy, dz;
-                        xyz(dx, dy, dz);
-                        // d and 1/d from one reciprocal square root plus a Newton step; quotients by
-                        // the basis spacings become products with their reciprocals.  These differ
-                        // from the reference's IEEE sqrt / divisions in the last bit only.
-                        float rinv = rsqrtf(fmaxf(d2, 1e-30f));
-                        rinv = rinv * fmaf(-0.5f * d2 * rinv, rinv, 1.5f);
-                        const float d = d2 * rinv;
-                        int lo_d = 0;
-                        if (P.windowed_dist) {
-                            lo_d = (int)(fmaf(d, inv_d_interval, -d_cut_scaled) - 1.0f);
-                            lo_d = min(max(lo_d, 0), 64 - P.win_dist);
-                        }
-                        const float xd = -d * xd_scale;
-                        float xa[3] = {0.f, 0.f, 0.f};
-                        int lo_pack = lo_d;
-                        if (ANG) {
-#pragma unroll
-                            for (int x = 0; x < 3; x++) {
-                                float cosv = 1e3f;
-                                if (d2 > 1e-5f) cosv = fmaf(dz, fz[x], fmaf(dy, fy[x], dx * fx[x])) * rinv;
-                                if (P.cos_abs) cosv = fabsf(cosv);
-                                int lo = 0;
-                                if (P.windowed_ang) {
-                                    const float en = fmaf(cosv + 1.0f + P.a_cut, inv_a_interval, 1.0f);
-                                    int end = (int)fminf(en, 64.0f);
-                                    end = max(end, P.win_ang);
-                                    lo = end - P.win_ang;
-                                }
-                                xa[x] = (1.0f - cosv) * xa_scale;
-                                lo_pack |= lo << (8 * (x + 1));
-                            }
-                        }
-                        tb[lane] = make_float4(arg * kLog2e, xd, xa[0], xa[1]);     // log2 of the weight
-                        if (BWD) tb[32 + lane] = make_float4(xa[2], __int_as_float(lo_pack), d2, 0.f);
-                        else tb2[lane] = make_float2(xa[2], __int_as_float(lo_pack));
-                    }
-                }
-                unsigned mask = __ballot_sync(0xffffffffu, keep);
-                __syncwarp();
-                while (mask) {
-                    const int src = __ffs(mask) - 1;
-                    mask &= mask - 1;
-                    const float4 r0 = tb[src];
-                    float4 r1;
-                    if (BWD) { r1 = tb[32 + src]; } else { const float2 t = tb2[src]; r1 = make_float4(t.x, t.y, 0.f, 0.f); }
-                    const float lw = r0.x, d2 = r1.z;          // Gaussian times weight = ex2(lw - b*b)
-                    const int lo_pack = __float_as_int(r1.y);
-                    {   // distance basis
-                        const int lo = (int)__byte_perm((unsigned)lo_pack, 0u, 0x4440);
-                        const bool in0 = (unsigned)(lane - lo) < win_d, in1 = (unsigned)(lane + 32 - lo) < win_d;
-                        if (!wide_d) {
-                            const float b = r0.y + (in1 ? cd_hi : cd_lo);
-                            const float g = ex2_approx(fmaf(-b, b, lw));
-                            if (in0) { sd[0] += g; if (BWD) qd[0] = fmaf(g, d2, qd[0]); }
-                            if (in1) { sd[1] += g; if (BWD) qd[1] = fmaf(g, d2, qd[1]); }
-                        } else {
-                            const float b0 = r0.y + cd_lo, b1 = r0.y + cd_hi;
-                            const float g0 = ex2_approx(fmaf(-b0, b0, lw)), g1 = ex2_approx(fmaf(-b1, b1, lw));
-                            if (in0) { sd[0] += g0; if (BWD) qd[0] = fmaf(g0, d2, qd[0]); }
-                            if (in1) { sd[1] += g1; if (BWD) qd[1] = fmaf(g1, d2, qd[1]); }
-                        }
-                    }
-                    if (ANG) {
-                        const float xa[3] = {r0.z, r0.w, r1.x};
-#pragma unroll
-                        for (int x = 0; x < 3; x++) {
-                            const int lo = (int)__byte_perm((unsigned)lo_pack, 0u, 0x4441 + x);
-                            const float b0 = xa[x] - ca_lo, b1 = xa[x] - ca_hi;
-                            const float g0 = ex2_approx(fmaf(-b0, b0, lw)), g1 = ex2_approx(fmaf(-b1, b1, lw));
-                            if ((unsigned)(lane - lo) < win_a) { sa[x][0] += g0; if (BWD) qa[x][0] = fmaf(g0, d2, qa[x][0]); }
-                            if ((unsigned)(lane + 32 - lo) < win_a) { sa[x][1] += g1; if (BWD) qa[x][1] = fmaf(g1, d2, qa[x][1]); }
-                        }
-                    }
-                }
-                __syncwarp();
-            };
-
-            if (use_list) {
-                // weights of all listed translations (the normaliser keeps every term), then the groups that
-                // hold survivors: the list is sorted, so they come first and the loop stops at the first
-                // group without any
-                const float a0 = weigh(dl0), a1 = weigh(dl1), a2 = weigh(dl2), a3 = weigh(dl3);
-                for (int g = 0; g < kListLen / 32; g++) {
-                    const float d2 = g == 0 ? dl0 : (g == 1 ? dl1 : (g == 2 ? dl2 : dl3));
-                    const float arg = g == 0 ? a0 : (g == 1 ? a1 : (g == 2 ? a2 : a3));
-                    const bool keep = arg > -P.prune;
-                    if (!__any_sync(0xffffffffu, keep)) break;
-                    expand(keep, arg, d2, [&](float& dx, float& dy, float& dz) {
-                        if (g == 0) { dx = lx0; dy = ly0; dz = lz0; }
-                        else {
-                            const float* Lg = A.list + (size_t)e * kListStride + g * 32 + lane;
-                            dx = __ldg(Lg + kListLen); dy = __ldg(Lg + 2 * kListLen); dz = __ldg(Lg + 3 * kListLen);
-                        }
-                    });
-                }
+            int Rl = 0;
+            if (lane < 3) Rl = lattice_range_1d(P, L.a, P.cutoff_radius != 0.0f ? __ldg(A.rvlen + 3 * c + lane) : 0.0f);
+            const int R1 = __shfl_sync(0xffffffffu, Rl, 0), R2 = __shfl_sync(0xffffffffu, Rl, 1), R3 = __shfl_sync(0xffffffffu, Rl, 2);
+            L.reset();
+            if (A.list != nullptr && R1 == A.cache_range && R2 == A.cache_range && R3 == A.cache_range) {
+                // the pair's translations sorted by distance, prepared once per batch: a prefix is expanded
+                L.run_list(P, A.list + (size_t)e * kListStride);
             } else {
-                for (int sub = 0; sub < nSub; sub++) {
-                    const int idx = sub * 32 + lane;
-                    int q2 = (int)(((float)idx + 0.5f) * invL3), r3 = idx - q2 * L3;
-                    if (r3 < 0) { q2--; r3 += L3; } else if (r3 >= L3) { q2++; r3 -= L3; }
-                    const float n2 = small_int_to_float(q2 - R2), n3 = small_int_to_float(r3 - R3);
-                    const float ox = fmaf(t3x, n3, fmaf(t2x, n2, rx)), oy = fmaf(t3y, n3, fmaf(t2y, n2, ry)),
-                                oz = fmaf(t3z, n3, fmaf(t2z, n2, rz));
-                    const bool valid = idx < L23;
-                    for (int k1 = 0; k1 < L1; k1++) {
-                        const float n1 = small_int_to_float(k1 - R1);
-                        const float dx0 = fmaf(t1x, n1, ox), dy0 = fmaf(t1y, n1, oy), dz0 = fmaf(t1z, n1, oz);
-                        const float d2 = fmaf(dz0, dz0, fmaf(dy0, dy0, dx0 * dx0));
-                        float arg = -1e30f;
-                        if (valid) arg = weigh(d2);
-                        expand(arg > -P.prune, arg, d2, [&](float& dx, float& dy, float& dz) { dx = dx0; dy = dy0; dz = dz0; });
-                    }
-                }
+                // slab sweeps over (n1; n2, n3) for lattice ranges the lists do not cover
+                L.run_slabs(P, R1, R2, R3, __ldg(A.pos_ij + 3 * e), __ldg(A.pos_ij + 3 * e + 1), __ldg(A.pos_ij + 3 * e + 2),
+                            A.tvecs + 9 * c);
             }
+            const float a = L.a, d2min = L.ref;
+            const float sum_l = L.sum_l, px_l = L.px_l;
+            const float (&sd)[2] = L.sd;
+            const float (&sa)[3][2] = L.sa;
+            const float (&qd)[2] = L.qd;
+            const float (&qa)[3][2] = L.qa;
 
             if (e_next < A.E) c_next = (int)A.batch[i_next];
 
