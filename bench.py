@@ -413,7 +413,11 @@ def run_ours(args, rank, world, local_rank):
                 "peak_source": "FP32 FMA throughput measured on this device by cfb200_probe_throughput",
                 "algorithmic_flop_per_launch": flops_bwd, "terms_per_launch": avg_terms, "ms_per_launch": bwd_ms,
                 "sfu_achieved_tops": avg_terms * SFU_TERM / (bwd_ms * 1e-3) / 1e12, "sfu_peak_tops": peaks["sfu_tops"],
-                "traffic": None,
+                # DRAM bytes of one launch: 43.9 MB (backward) for 306 560 (pair, head) sub-tasks in the profiler
+                # capture of the operator-level case (profiles/attn_fused_kernels_cfg2_opbench.md), scaled by
+                # the (pair, head) count -- mostly the first touch of the per-pair translation lists
+                "traffic": (43.9e6 / 306560.0 * pairs_heads) if fused else None,
+                "traffic_unit": "bytes per launch (DRAM read + write)",
                 "forward": {"ms_per_launch": fwd_ms, "achieved": flops_fwd / (fwd_ms * 1e-3) / 1e12,
                             "frac": flops_fwd / (fwd_ms * 1e-3) / 1e12 / peaks["fp32_tflops"]}}
     # the HBM-bound kernels of the path (ragged attention): algorithmic bytes over CUDA-event time against the
