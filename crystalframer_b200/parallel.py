@@ -7,16 +7,25 @@ import torch
 import torch.distributed as dist
 
 
-def partition_by_pair_count(sizes, n_parts):
-    """Greedy split of crystals into ``n_parts`` groups of nearly equal sum of squared sizes (the
-    attention cost), largest first -- the rule of models/latticeformer.py:224-233.  Returns a
-    list of index arrays."""
-    size2 = np.asarray(sizes, dtype=np.int64) ** 2
-    totals = np.zeros(n_parts, np.int64)
+def attention_cost(sizes, cells):
+    """Estimated attention cost of each crystal: pairs x (a constant + the lattice translations within reach
+    of a Gaussian of typical width, about a sphere of radius 8 A over the cell volume, between 1 and 125) --
+    the same estimate that orders the work queue of the fused attention kernels."""
+    vol = np.abs(np.linalg.det(np.asarray(cells, dtype=np.float64)))
+    survivors = np.clip(2145.0 / np.maximum(vol, 1e-6), 1.0, 125.0)
+    return np.asarray(sizes, dtype=np.float64) ** 2 * (7.0 + survivors)
+
+
+def partition_by_pair_count(sizes, n_parts, cost=None):
+    """Greedy split of crystals into ``n_parts`` groups of nearly equal cost, largest first -- the rule of
+    models/latticeformer.py:224-233, whose cost is the squared size (the pair count).  ``cost`` replaces the
+    squared sizes by a better estimate (``attention_cost``).  Returns a list of index arrays."""
+    weight = np.asarray(sizes, dtype=np.float64) ** 2 if cost is None else np.asarray(cost, dtype=np.float64)
+    totals = np.zeros(n_parts, np.float64)
     groups = [[] for _ in range(n_parts)]
-    for item in np.argsort(-size2, kind="stable"):
+    for item in np.argsort(-weight, kind="stable"):
         g = int(np.argmin(totals))
-        totals[g] += size2[item]
+        totals[g] += weight[item]
         groups[g].append(int(item))
     return [np.asarray(g, np.int64) for g in groups]
 

@@ -47,6 +47,15 @@ def test_partition_by_pair_count_balances():
     assert sorted(np.concatenate(parts).tolist()) == list(range(len(sizes)))
     loads = np.array([(sizes[p] ** 2).sum() for p in parts])
     assert loads.max() - loads.min() <= (sizes ** 2).max()
+    # with the attention-cost estimate (pairs x translations in reach) the same rule balances that cost
+    from crystalframer_b200.parallel import attention_cost
+    b = synth.make_workload("cfg2")
+    cost = attention_cost(b.sizes, b.trans_vec)
+    assert cost.shape == b.sizes.shape and (cost >= 8.0 * b.sizes ** 2).all() and (cost <= 132.0 * b.sizes ** 2).all()
+    parts = partition_by_pair_count(b.sizes, 8, cost)
+    assert sorted(np.concatenate(parts).tolist()) == list(range(len(b.sizes)))
+    loads = np.array([cost[p].sum() for p in parts])
+    assert loads.max() - loads.min() <= cost.max()
 
 
 def _worker(rank, world, port, q):
