@@ -53,5 +53,4 @@ def allreduce_gradients(params, average=True):
     dist.all_reduce(flat)
     if average:
         flat.div_(dist.get_world_size())
-    for g, r in zip(grads, torch._utils._unflatten_dense_tensors(flat, grads)):
-        g.copy_(r)
+    torch._foreach_copy_(grads, list(torch._utils._unflatten_dense_tensors(flat, grads)))   # one launch, not one per tensor
