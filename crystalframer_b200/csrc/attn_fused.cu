@@ -265,33 +265,34 @@ __global__ void __launch_bounds__(at_warps(true) * 32, kAtBwdBlocks) attn_bwd_ke
             if (e + 1 < T.e1) z_next = __ldg(A.z_in + (e + 1) * H + h);      // requested one pair ahead
             L.ref = zin;
             run_pair<true, ANG>(A, P, L, T, e);
-            // one butterfly for the seven warp-wide sums of this pair
+            // one butterfly for the five warp-wide sums of this pair; the four dot products of G with the
+            // basis sums enter the results only through two combinations
             float r0 = qd * kd, r1 = god * vd, r2 = L.px_l;
-            float r3 = fmaf(G[0], L.qd[0], G[1] * L.qd[1]), r4 = fmaf(G[0], L.sd[0], G[1] * L.sd[1]);
-            float r5 = 0.f, r6 = 0.f;
+            float Ad = fmaf(G[0], L.qd[0], G[1] * L.qd[1]), Bd = fmaf(G[0], L.sd[0], G[1] * L.sd[1]);
+            float Aa = 0.f, Ba = 0.f;
 #pragma unroll
             for (int x = 0; x < 3; x++) {
-                r5 = fmaf(G[2 + 2 * x], L.qa[x][0], fmaf(G[3 + 2 * x], L.qa[x][1], r5));
-                r6 = fmaf(G[2 + 2 * x], L.sa[x][0], fmaf(G[3 + 2 * x], L.sa[x][1], r6));
+                Aa = fmaf(G[2 + 2 * x], L.qa[x][0], fmaf(G[3 + 2 * x], L.qa[x][1], Aa));
+                Ba = fmaf(G[2 + 2 * x], L.sa[x][0], fmaf(G[3 + 2 * x], L.sa[x][1], Ba));
             }
+            float r3 = fmaf(P.c_dist, Ad, P.c_ang * Aa), r4 = fmaf(P.c_dist, Bd, P.c_ang * Ba);
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
                 r0 += __shfl_xor_sync(0xffffffffu, r0, o); r1 += __shfl_xor_sync(0xffffffffu, r1, o);
                 r2 += __shfl_xor_sync(0xffffffffu, r2, o); r3 += __shfl_xor_sync(0xffffffffu, r3, o);
-                r4 += __shfl_xor_sync(0xffffffffu, r4, o); r5 += __shfl_xor_sync(0xffffffffu, r5, o);
-                r6 += __shfl_xor_sync(0xffffffffu, r6, o);
+                r4 += __shfl_xor_sync(0xffffffffu, r4, o);
             }
-            const float qk = r0, gov = r1, px = r2, Ad = r3, Bd = r4, Aa = r5, Ba = r6;
+            const float qk = r0, gov = r1, px = r2, cA = r3, cB = r4;
             const float p_att = __expf(qk + zin - lse);
-            // gradient with respect to the logit bias: p (gout . (v_j + values_ij) - gout . out_i)
-            const float gzv = p_att * (gov + P.c_dist * Bd + P.c_ang * Ba - D);
+            // gradient with respect to the logit bias: p (gout . (v_j + values_ij) - gout . out_i), where
+            // gout . values_ij = c_dist G_d . s_d + c_ang G_a . s_a = cB
+            const float gzv = p_att * (gov + cB - D);
             if (lane == 0) A.gz[e * H + h] = gzv;
-            // coefficient gradient; the upstream gradient of the pair's values is p gout, so its W^T image is p G.
+            // coefficient gradient; the upstream gradient of the pair's values is p gout, so its W^T image is p G:
+            //   c_dist [px gz + p (Ad - px Bd)] + c_ang [p (Aa - px Ba)] = c_dist px gz + p (cA - px cB).
             // The reference scales the whole length-kernel result, gz term included, by the distance coefficient
             // (models/cuda_funcs/real_space_framed_proj.py:183).
-            const float g_len = fmaf(px, gzv, p_att * (Ad - px * Bd));
-            const float g_ang = p_att * (Aa - px * Ba);
-            ga_acc += P.c_dist * g_len + P.c_ang * g_ang;
+            ga_acc += fmaf(P.c_dist * px, gzv, p_att * (cA - px * cB));
             gq = fmaf(gzv, kd, gq);
         }
         if (lane == 0) A.ga[i * H + h] = ga_acc;
