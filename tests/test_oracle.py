@@ -258,3 +258,55 @@ def test_values_linear_in_weights(problem_cfg1):
     _, v2 = O.framed_proj_fwd(*args, W2, None, None)
     _, v12 = O.framed_proj_fwd(*args, P["W_d"] + W2, None, None)
     close("linearity", v12, v1 + v2, 1e-4, 1e-6)
+
+
+def test_pooling_identity_behind_the_fused_attention(problem_cfg1):
+    """The fused attention kernels never form the value encoding: they pool the 256 basis sums of an atom's
+    pairs with the attention weights and project once per (atom, head).  The algebra, on the oracle in
+    float64: with s_ij the basis sums of a pair (read off the oracle through one-hot projection weights),
+      out_i = sum_j p_ij v_j + W (sum_j p_ij s_ij)          and          gW = sum_i gout_i (x) S_i,
+    where S_i is the pooled basis (distance part unscaled, angle parts times the angle coefficient)."""
+    P = problem_cfg1
+    geo, b, cfg = P["geo"], P["batch"], P["cfg"]
+    fr = O.max_frames(cfg, P["q"] / 4.0, P["k"], P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"],
+                      geo["edges"], geo["e_start"])
+    frames = np.stack([fr["frame1"], fr["frame2"], fr["frame3"]])
+    args = (cfg, P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"])
+    E, H, hd = geo["edges"].shape[1], 8, 16
+    f64 = np.float64
+    # basis sums (E,H,4,64): values with W = 16 one-hot rows at a time, distance then the three axes
+    basis = np.zeros((E, H, 4, 64), f64)
+    for blk in range(4):
+        sel = np.zeros((H, hd, 64), f64)
+        for o in range(hd):
+            sel[:, o, blk * hd + o] = 1.0
+        zero_a = np.zeros((3, H, hd, 64), f64)
+        _, vd = O.framed_proj_fwd(*args, sel, zero_a, frames, dtype=f64)
+        basis[:, :, 0, blk * hd:(blk + 1) * hd] = vd / cfg.c_dist
+        for x in range(3):
+            Wa = zero_a.copy()
+            Wa[x] = sel
+            _, va = O.framed_proj_fwd(*args, np.zeros((H, hd, 64), f64), Wa, frames, dtype=f64)
+            basis[:, :, 1 + x, blk * hd:(blk + 1) * hd] = va
+    Wd, Wa = P["W_d"].astype(f64), P["W_a"].astype(f64)
+    z, values = O.framed_proj_fwd(*args, Wd, Wa, frames, dtype=f64)
+    W_all = np.concatenate([Wd[:, :, None, :], np.moveaxis(Wa, 0, 2)], 2)                   # (H,16,4,64)
+    close("values = W s", np.einsum("hobk,ehbk->eho", W_all, basis), values, 1e-9, 1e-10)
+    qs, k, v = (P["q"] / 4.0).astype(f64), P["k"].astype(f64), P["v"].astype(f64)
+    out, prob = O.dpa_fwd(cfg, qs, k, v, z, values, geo["edges"], geo["e_start"], dtype=f64)
+    i_of, j_of = geo["edges"][0], geo["edges"][1]
+    N = qs.shape[0]
+    pooled_v = np.zeros((N, H, hd), f64)
+    pooled_s = np.zeros((N, H, 4, 64), f64)
+    np.add.at(pooled_v, i_of, prob[:, :, None] * v[j_of])
+    np.add.at(pooled_s, i_of, prob[:, :, None, None] * basis)
+    close("out = sum p v + W S", pooled_v + np.einsum("hobk,nhbk->nho", W_all, pooled_s), out, 1e-9, 1e-10)
+    # weight gradients from the pooled basis
+    rng = np.random.default_rng(9)
+    go = rng.normal(size=out.shape)
+    _, _, _, gz, gval = O.dpa_bwd(cfg, qs, k, v, values, geo["edges"], geo["e_start"], prob, out, go, dtype=f64)
+    _, gWd, gWa = O.framed_proj_bwd(*args, geo["e_start"], Wd, Wa, frames, z, gz, gval, dtype=f64)
+    gW_all = np.einsum("nho,nhbk->hobk", go, pooled_s)
+    close("gW_dist = sum gout (x) S", gW_all[:, :, 0], gWd, 1e-8, 1e-10)
+    for x in range(3):
+        close(f"gW_ang{x + 1}", gW_all[:, :, 1 + x], gWa[x], 1e-8, 1e-10)
