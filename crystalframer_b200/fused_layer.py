@@ -11,7 +11,7 @@ dense layers stay on cuBLAS through ``torch.addmm`` / ``torch.mm``, everything s
 periodic attention runs in libcfb200, and the backward pass is written out by hand.
 
 Used by ``CrystalformerEncoderLayerCUDA.forward`` when the layer has the default structure
-(real-space domain, "max" frames, coefficients from q, no dropout, no layer norm, ReLU); any other
+(real-space domain, "max" or weighted-PCA frames, coefficients from q, no dropout, no layer norm, ReLU); any other
 configuration takes the operator-by-operator path.
 """
 import math
@@ -76,10 +76,21 @@ class FusedEncoderLayerFunc(torch.autograd.Function):
         _lib.invoke("cfb200_gauss_coef_fwd", 1, dev, p(q), p(w_lat), p(gauss_scale), N, meta["lb"], meta["beta"],
                     meta["scale_real"], p(a), p(qs))
         f = new(3, N, H, 3)
-        s1, s2 = _draw_seed(), _draw_seed()
-        _lib.invoke("cfb200_max_frames_cached", 1, dev, p(qs), p(k), p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
-                    ip(geo.batch), ip(geo.edges), ip(geo.e_start), N, E, meta["cutoff"], s1, s2, p(f[0]), p(f[1]), p(f[2]),
-                    p(geo.pair_cache), p(geo.pair_list), geo.cache_range)
+        if meta["frame_method"] == "max":
+            s1, s2 = _draw_seed(), _draw_seed()
+            _lib.invoke("cfb200_max_frames_cached", 1, dev, p(qs), p(k), p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
+                        ip(geo.batch), ip(geo.edges), ip(geo.e_start), N, E, meta["cutoff"], s1, s2, p(f[0]), p(f[1]),
+                        p(f[2]), p(geo.pair_cache), p(geo.pair_list), geo.cache_range)
+        else:
+            # weighted-PCA frames; the same draws from the generators as cuda_funcs.weighted_pca_frames
+            _draw_seed()
+            seed_noise = _draw_seed()
+            seed_sign = int(torch.randint(0, 2 ** 62, (1,)).item())
+            nbytes = int(_lib.lib().cfb200_sigma_frames_workspace_bytes(N, E))
+            ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
+            _lib.invoke("cfb200_sigma_frames", 2, dev, p(qs), p(k), p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
+                        ip(geo.batch), ip(geo.edges), ip(geo.e_start), N, E, meta["cutoff"], seed_noise, seed_sign,
+                        p(f[0]), p(f[1]), p(f[2]), ws.data_ptr(), nbytes)
         Wd3, W13, W23, W33 = Wd[0], W1[0], W2[0], W3[0]
         o, lse = new(N, H, hd), new(N, H)
         if FUSED_ATTENTION:
@@ -194,7 +205,8 @@ def layer_meta(attn):
     """Scalars of the attention module in the form the Function takes; None if the layer's
     configuration is outside what the fused path covers."""
     P = attn.params
-    if P.domain != "real" or P.frame_method != "max" or P.gauss_state != "q" or not P.normalize_gauss:
+    if P.domain != "real" or P.frame_method not in ("max", "weighted_pca") or P.gauss_state != "q" or \
+            not P.normalize_gauss:
         return None
     if attn.in_proj_bias is None or attn.pe_dist_proj is None or attn.proj_angle1 is None or attn.dropout != 0.0:
         return None
@@ -209,5 +221,5 @@ def layer_meta(attn):
         cutoff = float(P.scale_real * P.gauss_lb_real ** (-0.5) * P.adaptive_cutoff_sigma)
     else:
         cutoff = 0.0
-    return dict(H=attn.num_heads, hd=attn.head_dim, lb=float(P.gauss_lb_real), beta=float(P.positive_func_beta),
-                scale_real=float(P.scale_real), dist_max=float(dist_max), cutoff=cutoff)
+    return dict(frame_method=P.frame_method, H=attn.num_heads, hd=attn.head_dim, lb=float(P.gauss_lb_real),
+                beta=float(P.positive_func_beta), scale_real=float(P.scale_real), dist_max=float(dist_max), cutoff=cutoff)
