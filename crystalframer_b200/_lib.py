@@ -49,8 +49,10 @@ SIGNATURES = {
     "cfb200_proj_fwd": (ctypes.c_int, [vp] * 6 + [i64, i64, f32, f32] + [vp] * 4),
     "cfb200_proj_bwd": (ctypes.c_int, [vp] * 7 + [i64, i64, f32, f32] + [vp] * 7 + [i64, vp]),
     "cfb200_framed_proj_bwd_noalloc": (ctypes.c_int, [vp] * 7 + [i64, i64, f32, f32] + [vp] * 15 + [vp]),
-    "cfb200_attn_fused_fwd": (ctypes.c_int, [vp] * 12 + [i64, i64, f32, f32] + [vp] * 8 + [ctypes.c_int] + [vp] * 5),
-    "cfb200_attn_fused_bwd": (ctypes.c_int, [vp] * 12 + [i64, i64, f32, f32] + [vp] * 8 + [ctypes.c_int] + [vp] * 10),
+    "cfb200_attn_fused_fwd": (ctypes.c_int, [vp] * 12 + [i64, i64, f32, f32] + [vp] * 8 + [ctypes.c_int] + [vp] * 4
+                              + [ctypes.c_int, vp]),
+    "cfb200_attn_fused_bwd": (ctypes.c_int, [vp] * 12 + [i64, i64, f32, f32] + [vp] * 8 + [ctypes.c_int] + [vp] * 9
+                              + [ctypes.c_int, vp]),
     "cfb200_dpa_fwd": (ctypes.c_int, [vp] * 7 + [i64, i64] + [vp] * 4),
     "cfb200_dpa_bwd": (ctypes.c_int, [vp] * 7 + [i64, i64] + [vp] * 9),
     "cfb200_segment_mean_fwd": (ctypes.c_int, [vp, vp, i64, i64, vp, vp]),

@@ -449,10 +449,11 @@ int cfb200_attn_fused_fwd(const float* q_scaled, const float* k, const float* v,
                           int64_t N, int64_t E, float dist_max, float cutoff_radius, const float* W_dist, const float* W_ang1,
                           const float* W_ang2, const float* W_ang3, const float* frame1, const float* frame2,
                           const float* frame3, const float* pair_list, int cache_range, float* out, float* z,
-                          float* lse, float* spool, void* stream)
+                          float* lse, float* spool, int unwindowed, void* stream)
 {
     cfb::Params P;
-    int rc = make_params(dist_max, cutoff_radius, P);
+    int rc = make_params(dist_max, cutoff_radius, P, unwindowed != 0);
+    if (unwindowed != 0 && (W_ang1 || W_ang2 || W_ang3)) return CFB200_E_UNSUPPORTED;
     if (rc != CFB200_OK) return rc;
     cfb::AtArgs A;
     rc = at_args(A, q_scaled, k, v, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, order, counters, N, E, cutoff_radius,
@@ -470,10 +471,11 @@ int cfb200_attn_fused_bwd(const float* q_scaled, const float* k, const float* v,
                           const float* W_ang2, const float* W_ang3, const float* frame1, const float* frame2,
                           const float* frame3, const float* pair_list, int cache_range, const float* out,
                           const float* z, const float* lse, const float* gout, float* gq_scaled, float* gk, float* gv,
-                          float* ga, float* gz, void* stream)
+                          float* ga, float* gz, int unwindowed, void* stream)
 {
     cfb::Params P;
-    int rc = make_params(dist_max, cutoff_radius, P);
+    int rc = make_params(dist_max, cutoff_radius, P, unwindowed != 0);
+    if (unwindowed != 0 && (W_ang1 || W_ang2 || W_ang3)) return CFB200_E_UNSUPPORTED;
     if (rc != CFB200_OK) return rc;
     cfb::AtArgs A;
     rc = at_args(A, q_scaled, k, v, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, order, counters, N, E, cutoff_radius,

@@ -11,7 +11,7 @@ dense layers stay on cuBLAS through ``torch.addmm`` / ``torch.mm``, everything s
 periodic attention runs in libcfb200, and the backward pass is written out by hand.
 
 Used by ``CrystalformerEncoderLayerCUDA.forward`` when the layer has the default structure
-(real-space domain, "max" or weighted-PCA frames, coefficients from q, no dropout, no layer norm, ReLU); any other
+(real-space domain, "max" or weighted-PCA frames or none, coefficients from q, no dropout, no layer norm, ReLU); any other
 configuration takes the operator-by-operator path.
 """
 import math
@@ -75,8 +75,12 @@ class FusedEncoderLayerFunc(torch.autograd.Function):
         a, qs = new(N, H), new(N, H, hd)
         _lib.invoke("cfb200_gauss_coef_fwd", 1, dev, p(q), p(w_lat), p(gauss_scale), N, meta["lb"], meta["beta"],
                     meta["scale_real"], p(a), p(qs))
-        f = new(3, N, H, 3)
-        if meta["frame_method"] == "max":
+        plain = meta["frame_method"] == "no"           # plain Crystalformer: un-windowed distance encoding, no frames
+        f = None if plain else new(3, N, H, 3)
+        fr = (None, None, None) if plain else (f[0], f[1], f[2])
+        if plain:
+            pass
+        elif meta["frame_method"] == "max":
             s1, s2 = _draw_seed(), _draw_seed()
             _lib.invoke("cfb200_max_frames_cached", 1, dev, p(qs), p(k), p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
                         ip(geo.batch), ip(geo.edges), ip(geo.e_start), N, E, meta["cutoff"], s1, s2, p(f[0]), p(f[1]),
@@ -91,17 +95,18 @@ class FusedEncoderLayerFunc(torch.autograd.Function):
             _lib.invoke("cfb200_sigma_frames", 2, dev, p(qs), p(k), p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
                         ip(geo.batch), ip(geo.edges), ip(geo.e_start), N, E, meta["cutoff"], seed_noise, seed_sign,
                         p(f[0]), p(f[1]), p(f[2]), ws.data_ptr(), nbytes)
-        Wd3, W13, W23, W33 = Wd[0], W1[0], W2[0], W3[0]
+        Wd3 = Wd[0]
+        W13, W23, W33 = (None, None, None) if plain else (W1[0], W2[0], W3[0])
         o, lse = new(N, H, hd), new(N, H)
-        if FUSED_ATTENTION:
+        if FUSED_ATTENTION or plain:
             # lattice sums, value encoding and attention in one kernel: the basis sums are pooled with the
             # attention weights and projected once per (atom, head)
             z, val, spool = new(E, H), None, new(N, H, 4 * 64)
             _lib.invoke("cfb200_attn_fused_fwd", 1, dev, p(qs), p(k), p(v), p(a), p(geo.pos_ij), p(geo.tvecs),
                         p(geo.rvlen), ip(geo.batch), ip(geo.edges), ip(geo.e_start), p(geo.order, torch.int32),
                         p(geo.counters, torch.int32), N, E,
-                        meta["dist_max"], meta["cutoff"], p(Wd3), p(W13), p(W23), p(W33), p(f[0]), p(f[1]), p(f[2]),
-                        p(geo.pair_list), geo.cache_range, p(o), p(z), p(lse), p(spool))
+                        meta["dist_max"], meta["cutoff"], p(Wd3), p(W13), p(W23), p(W33), p(fr[0]), p(fr[1]), p(fr[2]),
+                        p(geo.pair_list), geo.cache_range, p(o), p(z), p(lse), p(spool), 1 if plain else 0)
         else:
             z, val, spool = new(E, H), new(E, H, hd), None
             _lib.invoke("cfb200_framed_proj_fwd_cached", 1, dev, p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
@@ -126,6 +131,7 @@ class FusedEncoderLayerFunc(torch.autograd.Function):
         H, hd = meta["H"], meta["hd"]
         N, E, dev = geo.N, geo.E, x.device
         D = H * hd
+        plain = meta["frame_method"] == "no"
         p, ip = _lib.ptr, _lib.iptr
         new = lambda *shape: torch.empty(shape, device=dev, dtype=torch.float32)
         g = g.contiguous()
@@ -158,16 +164,17 @@ class FusedEncoderLayerFunc(torch.autograd.Function):
             _lib.invoke("cfb200_attn_fused_bwd", 2, dev, p(qs), p(k), p(v), p(a), p(geo.pos_ij), p(geo.tvecs),
                         p(geo.rvlen), ip(geo.batch), ip(geo.edges), ip(geo.e_start), p(geo.order, torch.int32),
                         p(geo.counters, torch.int32), N, E,
-                        meta["dist_max"], meta["cutoff"], p(Wd[0]), p(W1[0]), p(W2[0]), p(W3[0]), p(f[0]), p(f[1]),
-                        p(f[2]), p(geo.pair_list), geo.cache_range, p(o), p(z), p(lse), p(go), p(gqs), p(gk), p(gv),
-                        p(ga), p(gz))
+                        meta["dist_max"], meta["cutoff"], p(Wd[0]), *((None,) * 6 if plain else
+                                                                      (p(W1[0]), p(W2[0]), p(W3[0]), p(f[0]), p(f[1]), p(f[2]))),
+                        p(geo.pair_list), geo.cache_range, p(o), p(z), p(lse), p(go), p(gqs), p(gk), p(gv),
+                        p(ga), p(gz), 1 if plain else 0)
             ev3 = torch.cuda.Event()
             ev3.record(main)
             with torch.cuda.stream(side):
                 # weight gradients of the value encoding: gW[h] (16 x 256) = sum_i gout[i,h,:]^T spool[i,h,:]
                 side.wait_event(ev3)
                 gW_all = torch.bmm(go.permute(1, 2, 0), spool.permute(1, 0, 2))
-                gW = [gW_all[:, :, 64 * b:64 * (b + 1)].contiguous() for b in range(4)]
+                gW = [gW_all[:, :, 64 * b:64 * (b + 1)].contiguous() for b in range(1 if plain else 4)]
         else:
             gqs, gk, gv, gz, gval = new(N, H, hd), new(N, H, hd), new(N, H, hd), new(E, H), new(E, H, hd)
             _lib.invoke("cfb200_dpa_bwd", 2, dev, p(qs), p(k), p(v), p(z), p(val), ip(geo.edges), ip(geo.e_start), N, E,
@@ -197,19 +204,21 @@ class FusedEncoderLayerFunc(torch.autograd.Function):
         main.wait_event(done)
         for t in (gWf2, gbf2, gWf1, gbf1, gWo, gbo, gWq, gWk, gWv, gb_in) + (tuple(gW) if ctx.fused_attention else ()):
             t.record_stream(main)               # allocated on the side stream, consumed on the current one
-        return (gx, gWq, gWk, gWv, gb_in, gw, None, gWo, gbo, gW[0].unsqueeze(0), gW[1].unsqueeze(0), gW[2].unsqueeze(0),
-                gW[3].unsqueeze(0), gWf1, gbf1, gWf2, gbf2, None, None)
+        gWa = (None, None, None) if plain else (gW[1].unsqueeze(0), gW[2].unsqueeze(0), gW[3].unsqueeze(0))
+        return (gx, gWq, gWk, gWv, gb_in, gw, None, gWo, gbo, gW[0].unsqueeze(0), *gWa, gWf1, gbf1, gWf2, gbf2, None, None)
 
 
 def layer_meta(attn):
     """Scalars of the attention module in the form the Function takes; None if the layer's
     configuration is outside what the fused path covers."""
     P = attn.params
-    if P.domain != "real" or P.frame_method not in ("max", "weighted_pca") or P.gauss_state != "q" or \
+    if P.domain != "real" or P.frame_method not in ("max", "weighted_pca", "no") or P.gauss_state != "q" or \
             not P.normalize_gauss:
         return None
-    if attn.in_proj_bias is None or attn.pe_dist_proj is None or attn.proj_angle1 is None or attn.dropout != 0.0:
+    if attn.in_proj_bias is None or attn.pe_dist_proj is None or attn.dropout != 0.0:
         return None
+    if (attn.proj_angle1 is None) != (P.frame_method == "no"):
+        return None                      # angle weights exactly when there are frames
     if attn.kdim != attn.embed_dim or attn.vdim != attn.embed_dim:
         return None
     dist_max = P.value_pe_dist_max

@@ -79,10 +79,10 @@ def run_once_fused(I):
     common = (p(qs), p(k), p(v), p(a), p(I["pos_ij"]), p(I["tv"]), p(I["rvlen"]), ip(I["batch"]), ip(I["edges"]),
               ip(I["e_start"]), p(I["order"], torch.int32), p(I["counters"], torch.int32), N, E, 14.0, -3.5, p(W[0]),
               p(W[1]), p(W[2]), p(W[3]), p(f1), p(f2), p(f3), p(plist), prange)
-    _lib.invoke("cfb200_attn_fused_fwd", 1, dev, *common, p(out), p(z), p(lse), p(spool))
+    _lib.invoke("cfb200_attn_fused_fwd", 1, dev, *common, p(out), p(z), p(lse), p(spool), 0)
     gq, gk, gv, ga, gz = (torch.empty(s, device=dev) for s in ((N, H, hd), (N, H, hd), (N, H, hd), (N, H), (E, H)))
     _lib.invoke("cfb200_attn_fused_bwd", 2, dev, *common, p(out), p(z), p(lse), p(I["go"]), p(gq), p(gk), p(gv), p(ga),
-                p(gz))
+                p(gz), 0)
     gW = torch.bmm(I["go"].permute(1, 2, 0), spool.permute(1, 0, 2))
     return out, gW
 

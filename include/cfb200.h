@@ -253,7 +253,8 @@ int cfb200_framed_proj_bwd_cached(const float* a_ik, const float* pos_ij, const 
  * Gaussians.  order (N) int32 or NULL: the sequence in which atoms are handed to the warps (most
  * expensive first balances best); counters: num_heads int32 of scratch (work-queue heads; the call
  * clears them).  pair_list / cache_range as in cfb200_pair_cache (NULL: every pair is
- * swept).  Outputs: out (N,H,16); z (E,H); lse (N,H) log-sum-exp of the logits; spool (N,H,256) the
+ * swept).  unwindowed != 0 selects the plain Crystalformer encoding of cfb200_proj_fwd (every distance
+ * Gaussian, no coefficient, no angle weights).  Outputs: out (N,H,16); z (E,H); lse (N,H) log-sum-exp of the logits; spool (N,H,256) the
  * attention-pooled basis sums [distance 64 | axis 1..3 64 each], distance part unscaled, angle parts times
  * the angle coefficient -- the weight gradients are  gW[h] (16 x 256) = sum_i gout[i,h,:]^T spool[i,h,:],
  * a GEMM left to the caller.
@@ -267,7 +268,7 @@ int cfb200_attn_fused_fwd(const float* q_scaled, const float* k, const float* v,
                           const float* W_ang2, const float* W_ang3, const float* frame1,
                           const float* frame2, const float* frame3, const float* pair_list,
                           int cache_range, float* out, float* z, float* lse, float* spool,
-                          void* stream);
+                          int unwindowed, void* stream);
 int cfb200_attn_fused_bwd(const float* q_scaled, const float* k, const float* v, const float* a_ik,
                           const float* pos_ij, const float* tvecs, const float* rvlen,
                           const int64_t* batch, const int64_t* edges, const int64_t* e_start,
@@ -277,7 +278,7 @@ int cfb200_attn_fused_bwd(const float* q_scaled, const float* k, const float* v,
                           const float* frame2, const float* frame3, const float* pair_list,
                           int cache_range, const float* out, const float* z, const float* lse,
                           const float* gout, float* gq_scaled, float* gk, float* gv, float* ga,
-                          float* gz, void* stream);
+                          float* gz, int unwindowed, void* stream);
 
 /* Replaces FusedDotProductAttentionCUDA.forward (models/cuda_funcs/fused_dpa.py:17-64;
  * kernel fused_dpa_fwd.cu).  q_scaled, k, v (N,H,head_dim); z (E,H) or NULL; values
