@@ -126,21 +126,34 @@ class KernelTimer:
         return {name: (len(ev), sum(a.elapsed_time(b) for a, b in ev)) for name, ev in self.records.items()}
 
 
+def _device_index(device):
+    if isinstance(device, int):
+        return device
+    idx = torch.device(device).index
+    return torch.cuda.current_device() if idx is None else idx
+
+
 def invoke(name, n_kernels, device, *args):
-    """Calls entry point ``name`` with ``args`` followed by the current stream of ``device``."""
+    """Calls entry point ``name`` with ``args`` followed by the current stream of ``device``.  The device is
+    made current for the call only when it is not already (the usual case costs no device switch)."""
     global launch_count
     fn = getattr(lib(), name)
-    with torch.cuda.device(device):
-        st = torch.cuda.current_stream(device)
-        if _timer is not None:
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(st)
-            rc = fn(*args, st.cuda_stream)
-            e1.record(st)
-            _timer.records.setdefault(name, []).append((e0, e1))
-        else:
-            rc = fn(*args, st.cuda_stream)
-    check(rc, name)
+    idx = _device_index(device)
+    if _timer is None and idx == torch.cuda.current_device():
+        rc = fn(*args, torch._C._cuda_getCurrentRawStream(idx))
+    else:
+        with torch.cuda.device(idx):
+            st = torch.cuda.current_stream(idx)
+            if _timer is not None:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(st)
+                rc = fn(*args, st.cuda_stream)
+                e1.record(st)
+                _timer.records.setdefault(name, []).append((e0, e1))
+            else:
+                rc = fn(*args, st.cuda_stream)
+    if rc != 0:
+        check(rc, name)
     launch_count += n_kernels
 
 
