@@ -63,10 +63,15 @@ def make_model(seed):
 
 
 def make_optimizer(model, fused):
+    """AdamW lr 5e-4, betas (0.9, 0.98), weight decay 1e-5 on the weights only; clip-norm 1.0.  ``fused``: the
+    library's flat-buffer optimiser (clip + update in two launches); otherwise torch.optim.AdamW (CPU arm)."""
     decay = [p for n, p in model.named_parameters() if p.requires_grad and not n.endswith("bias")]
     no_decay = [p for n, p in model.named_parameters() if p.requires_grad and n.endswith("bias")]
+    if fused:
+        from crystalframer_b200.optim import FlatAdamW
+        return FlatAdamW(decay, no_decay, lr=5e-4, betas=(0.9, 0.98), eps=1e-8, weight_decay=1e-5, max_norm=1.0)
     groups = [{"params": decay, "weight_decay": 1e-5}, {"params": no_decay, "weight_decay": 0.0}]
-    return torch.optim.AdamW(groups, lr=5e-4, betas=(0.9, 0.98), fused=fused)
+    return torch.optim.AdamW(groups, lr=5e-4, betas=(0.9, 0.98))
 
 
 def synthetic_batches(n_batches, seed0, num_crystals, rank=0, world=1):
@@ -298,9 +303,7 @@ def run_ours(args, rank, world, local_rank):
         # gradients are summed, so ranks holding different numbers of crystals are weighted correctly
         loss = (model(tb) - tb.y).abs().sum() / float(BATCH * world)
         loss.backward()
-        parallel.allreduce_gradients(params, average=False)
-        torch.nn.utils.clip_grad_norm_(params, 1.0)
-        opt.step()
+        opt.step(world_sum=True)            # gradient all-reduce (sum), clip-norm 1.0 and AdamW in one call
         return loss
 
     enqueue_ms = [0.0]

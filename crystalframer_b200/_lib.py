@@ -57,6 +57,7 @@ SIGNATURES = {
     "cfb200_dpa_bwd": (ctypes.c_int, [vp] * 7 + [i64, i64] + [vp] * 9),
     "cfb200_segment_mean_fwd": (ctypes.c_int, [vp, vp, i64, i64, vp, vp]),
     "cfb200_segment_mean_bwd": (ctypes.c_int, [vp, vp, i64, i64, vp, vp]),
+    "cfb200_adamw_clip_step": (ctypes.c_int, [vp] * 4 + [i64, i64] + [f32] * 6 + [ctypes.c_double, ctypes.c_double, vp, vp, vp]),
     "cfb200_probe_throughput": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, vp, vp]),
 }
 

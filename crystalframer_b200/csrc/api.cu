@@ -11,6 +11,7 @@
 #include "coef.cu"
 #include "sigma.cu"
 #include "attn_fused.cu"
+#include "optim.cu"
 
 namespace cfb {
 
@@ -592,6 +593,23 @@ int cfb200_segment_mean_bwd(const float* gout, const int64_t* start, int64_t B, 
     if (B < 0 || D < 0) return CFB200_E_SHAPE;
     if (B * D > 0 && (!gout || !start || !gx)) return CFB200_E_NULL;
     return cfb::segment_mean(true, gout, start, B, D, gx, S(stream));
+}
+
+int cfb200_adamw_clip_step(float* params, const float* grads, float* exp_avg, float* exp_avg_sq, int64_t n,
+                           int64_t decay_end, float lr, float beta1, float beta2, float eps, float weight_decay,
+                           float max_norm, double bias_correction1, double bias_correction2, float* scratch,
+                           float* grad_norm, void* stream)
+{
+    if (n < 0 || decay_end < 0 || decay_end > n) return CFB200_E_SHAPE;
+    if (n == 0) return CFB200_OK;
+    if (!params || !grads || !exp_avg || !exp_avg_sq || !scratch) return CFB200_E_NULL;
+    if (!(bias_correction1 > 0.0) || !(bias_correction2 > 0.0)) return CFB200_E_SHAPE;
+    cfb::AdamArgs A;
+    A.p = params; A.g = grads; A.m = exp_avg; A.v = exp_avg_sq; A.n = n; A.decay_end = decay_end;
+    A.lr = lr; A.beta1 = beta1; A.beta2 = beta2; A.eps = eps; A.weight_decay = weight_decay; A.max_norm = max_norm;
+    A.inv_bc1 = (float)(1.0 / bias_correction1); A.inv_sqrt_bc2 = (float)(1.0 / sqrt(bias_correction2));
+    A.partial = scratch; A.norm_out = grad_norm;
+    return cfb::adamw_clip_step(A, scratch, S(stream));
 }
 
 }  // extern "C"

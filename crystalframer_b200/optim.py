@@ -1,0 +1,72 @@
+"""AdamW with gradient clipping on flat buffers: one library call per training step.
+
+The reference trains with torch's AdamW and Lightning's ``gradient_clip_val`` (train.py, params "adamw" /
+"clip_norm"), i.e. a per-tensor norm, a per-tensor scale and a multi-tensor update for the 60 parameter
+tensors of the 4-layer model -- about a millisecond of host work and a dozen launches per step.  Here the
+parameters are views into one flat buffer, the gradients are gathered into another with one copy, and
+``cfb200_adamw_clip_step`` does norm, clip and update in two launches.  With several ranks the gradient
+buffer is what is all-reduced, so nothing is flattened or copied back."""
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+
+class FlatAdamW:
+    """``FlatAdamW(decay_params, no_decay_params, lr, betas, eps, weight_decay, max_norm)``; ``step()`` takes
+    the parameters' ``.grad``.  Same arithmetic as ``clip_grad_norm_(params, max_norm)`` followed by
+    ``torch.optim.AdamW.step()`` with ``weight_decay`` on ``decay_params`` only."""
+
+    def __init__(self, decay_params, no_decay_params=(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2,
+                 max_norm=0.0):
+        self.params = [p for p in list(decay_params) + list(no_decay_params) if p.requires_grad]
+        if not self.params or not all(p.is_cuda and p.dtype == torch.float32 for p in self.params):
+            raise RuntimeError("FlatAdamW needs fp32 CUDA parameters (there is no CPU path)")
+        dev = self.params[0].device
+        self.decay_end = sum(p.numel() for p in decay_params if p.requires_grad)
+        self.n = sum(p.numel() for p in self.params)
+        self.flat = torch.empty(self.n, device=dev, dtype=torch.float32)
+        off = 0
+        for p in self.params:                       # parameters become views of the flat buffer
+            k = p.numel()
+            self.flat[off:off + k].copy_(p.data.reshape(-1))
+            p.data = self.flat[off:off + k].view(p.shape)
+            off += k
+        self.grad = torch.zeros(self.n, device=dev, dtype=torch.float32)
+        self.exp_avg = torch.zeros_like(self.flat)
+        self.exp_avg_sq = torch.zeros_like(self.flat)
+        self.scratch = torch.zeros(256, device=dev, dtype=torch.float32)
+        self.grad_norm = torch.zeros(1, device=dev, dtype=torch.float32)
+        self.lr, self.betas, self.eps, self.weight_decay, self.max_norm = lr, betas, eps, weight_decay, max_norm
+        self.steps = 0
+
+    def zero_grad(self, set_to_none=True):
+        for p in self.params:
+            p.grad = None
+
+    def gather_grads(self):
+        """Copies every parameter's gradient into the flat gradient buffer (zeros where there is none)."""
+        views = [p.grad.reshape(-1) if p.grad is not None else torch.zeros(p.numel(), device=self.flat.device)
+                 for p in self.params]
+        torch.cat(views, out=self.grad)
+        return self.grad
+
+    def step(self, world_sum=False):
+        """One update.  ``world_sum``: sum the gradient buffer over the ranks first (one all-reduce)."""
+        g = self.gather_grads()
+        if world_sum and dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(g)
+        self.steps += 1
+        b1, b2 = self.betas
+        p = _lib.ptr
+        _lib.invoke("cfb200_adamw_clip_step", 2, self.flat.device, p(self.flat), p(g), p(self.exp_avg), p(self.exp_avg_sq),
+                    self.n, self.decay_end, self.lr, b1, b2, self.eps, self.weight_decay, self.max_norm,
+                    1.0 - b1 ** self.steps, 1.0 - b2 ** self.steps, p(self.scratch), p(self.grad_norm))
+
+    def state_dict(self):
+        return {"steps": self.steps, "exp_avg": self.exp_avg.clone(), "exp_avg_sq": self.exp_avg_sq.clone()}
+
+    def load_state_dict(self, state):
+        self.steps = int(state["steps"])
+        self.exp_avg.copy_(state["exp_avg"])
+        self.exp_avg_sq.copy_(state["exp_avg_sq"])

@@ -303,6 +303,16 @@ int cfb200_segment_mean_fwd(const float* x, const int64_t* start, int64_t B, int
 int cfb200_segment_mean_bwd(const float* gout, const int64_t* start, int64_t B, int64_t D,
                             float* gx, void* stream);
 
+/* Gradient clipping by global norm and the AdamW update on flat fp32 buffers, in two launches (what
+ * torch.nn.utils.clip_grad_norm_ + torch.optim.AdamW.step do tensor by tensor for the reference's
+ * trainer).  params, grads, exp_avg, exp_avg_sq: n floats each; weight decay applies to the first
+ * decay_end elements only; max_norm <= 0 disables clipping; bias_correction{1,2} = 1 - beta{1,2}^step;
+ * scratch: 256 floats; grad_norm (1 float, optional): the norm before clipping. */
+int cfb200_adamw_clip_step(float* params, const float* grads, float* exp_avg, float* exp_avg_sq,
+                           int64_t n, int64_t decay_end, float lr, float beta1, float beta2, float eps,
+                           float weight_decay, float max_norm, double bias_correction1,
+                           double bias_correction2, float* scratch, float* grad_norm, void* stream);
+
 /* Measurement aid with no counterpart in the reference: every thread of `blocks` x 256 threads
  * runs `iters` rounds of 8 independent chains of fused multiply-adds (kind 0) or ex2.approx
  * (kind 1) and writes one float to sink (blocks*256 floats).  Timed by the caller, it gives the

@@ -386,3 +386,38 @@ def test_pair_cache_changes_no_bit(noise):
         scale = max(1.0, float(x.abs().max()))
         _close(name + " with lists", y, x, 1e-4, 1e-5 * scale)
     assert _lib.read_status() == 0
+
+
+def test_flat_adamw_matches_torch():
+    """cfb200_adamw_clip_step (clip by global norm + AdamW on flat buffers) against
+    torch.nn.utils.clip_grad_norm_ + torch.optim.AdamW over several steps, with and without clipping active."""
+    dev = _cuda()
+    from crystalframer_b200.optim import FlatAdamW
+
+    def make():
+        torch.manual_seed(5)
+        return torch.nn.Sequential(torch.nn.Linear(37, 64), torch.nn.ReLU(), torch.nn.Linear(64, 3)).to(dev)
+
+    ref, ours = make(), make()
+    split = lambda m: ([p for n, p in m.named_parameters() if not n.endswith("bias")],
+                       [p for n, p in m.named_parameters() if n.endswith("bias")])
+    d, nd = split(ref)
+    opt_ref = torch.optim.AdamW([{"params": d, "weight_decay": 1e-2}, {"params": nd, "weight_decay": 0.0}], lr=3e-3,
+                                betas=(0.9, 0.98))
+    d2, nd2 = split(ours)
+    opt = FlatAdamW(d2, nd2, lr=3e-3, betas=(0.9, 0.98), eps=1e-8, weight_decay=1e-2, max_norm=0.5)
+    g = torch.Generator(device="cpu").manual_seed(1)
+    for step in range(6):
+        x = torch.randn(50, 37, generator=g).to(dev) * (10.0 if step % 2 == 0 else 0.01)   # large and tiny gradients
+        for m, o in ((ref, opt_ref), (ours, opt)):
+            o.zero_grad(set_to_none=True)
+            m(x).square().mean().backward()
+        norm_ref = torch.nn.utils.clip_grad_norm_(list(ref.parameters()), 0.5)
+        opt_ref.step()
+        opt.step()
+        assert abs(float(opt.grad_norm) - float(norm_ref)) <= 1e-5 * max(1.0, float(norm_ref))
+        for (n, a), b in zip(ref.named_parameters(), ours.parameters()):
+            _close(f"step {step} {n}", b, a, 1e-5, 1e-7)
+    # parameters stay views of the flat buffer, so state_dict round trips keep working
+    ours.load_state_dict({k: v.clone() for k, v in ref.state_dict().items()})
+    assert all(p.data_ptr() >= opt.flat.data_ptr() and p.data_ptr() < opt.flat.data_ptr() + 4 * opt.n for p in ours.parameters())
