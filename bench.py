@@ -16,6 +16,12 @@ second over all GPUs.  Rank 0 prints one JSON line.
               library's probe kernel; the special-function (ex2) figures sit beside it.
 ``cpu_baseline`` / ``--impl reference``: the reference's own kernels compiled for the host cores
               (oracle/_ref; else the C restatement) under the same model, on a bounded sample.
+``gpu_reference``: the reference's own CUDA kernels (compiled from their sources for sm_100a into oracle/_ref)
+              on this GPU in the same run -- the isolated attention operator on the 256-crystal operator
+              batch, and whole training steps of the same model on the benchmark's batches -- with this
+              library's times beside them.
+``cpu_baseline_pure``: the reference's pure-PyTorch model on the host cores; needs the reference's Python
+              tree (environment variable CF_REFERENCE_ROOT), reported as unavailable elsewhere.
 """
 import argparse
 import copy
@@ -43,6 +49,9 @@ BATCH = int(os.environ.get("CF_BENCH_BATCH", 256))   # 256 is the benchmark; oth
 FLOP_TERM_FWD, FLOP_TERM_BWD, SFU_TERM = 516.0, 738.0, 110.0
 FLOP_PROJ_FWD, FLOP_PROJ_BWD = 8192.0, 16384.0
 FLOP_ATT_FWD, FLOP_ATT_BWD = 70.0, 170.0          # ragged attention per (pair, head)
+# DRAM bytes (read + write) of one launch of the fused attention kernels on batch 0 of this benchmark, as the
+# profiler counted them (dram__bytes_read.sum + dram__bytes_write.sum; one kernel, two launches captured)
+NCU_TRAFFIC_BYTES = {}
 
 
 def parse():
@@ -53,13 +62,23 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-crystals", type=int, default=16, help="crystals per CPU-baseline step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-gpu-reference", action="store_true")
     return ap.parse_args()
 
 
-def make_model(seed):
+def make_model(seed, cpu_container=False):
+    """The 4-layer max-frame model.  ``cpu_container``: the instance only holds parameters for the CPU legs
+    (oracle/cpu_model.py runs them); the hyper-parameter binding is then left pending so that this process
+    does not load libcfb200.so."""
+    from crystalframer_b200.cuda_funcs import kernel_manager
     from crystalframer_b200.latticeformer import Latticeformer, ModelParams
     torch.manual_seed(seed)
-    return Latticeformer(ModelParams())
+    if cpu_container:
+        kernel_manager.DEFER_BINDING = True
+    try:
+        return Latticeformer(ModelParams())
+    finally:
+        kernel_manager.DEFER_BINDING = False
 
 
 def make_optimizer(model, fused):
@@ -204,17 +223,12 @@ def run_reference(args, rank, world):
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
     os.environ.setdefault("OMP_NUM_THREADS", str(threads))
-    model = make_model(2).train()
+    model = make_model(2, cpu_container=True).train()
     opt = make_optimizer(model, fused=False)
     backend = "reference" if R.available("cpu") else "port"
-    # size the per-step sample so that K + W steps take about two minutes on these cores
-    probe_b, _ = synthetic_batches(1, 1999, 4)[0]
-    t0 = time.perf_counter()
-    cpu_model.forward(model, probe_b, backend=backend).abs().mean().backward()
-    rate = 4.0 / (time.perf_counter() - t0)
-    for l in model.encoder.layers:
-        l.self_attn.gauss_scale.data.zero_()
-    nc = int(max(2, min(args.cpu_crystals, rate * 120.0 / max(1, args.steps + args.warmup))))
+    # a fixed sample: steps of --cpu-crystals crystals (16) of the benchmark's distribution; at about 3 crystals
+    # per second on 16 cores the default K + W = 25 steps take a few minutes
+    nc = args.cpu_crystals
     batches = synthetic_batches(max(2, min(args.steps, 4)), 2000, nc)
 
     def step(i):
@@ -238,7 +252,8 @@ def run_reference(args, rank, world):
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "crystals_per_step": nc, "device": "host cores"},
+            "config": {"workload": WORKLOAD, "crystals_per_step": nc, "device": "host cores",
+                       "sample": "the same model, optimiser and crystal distribution; steps of %d crystals instead of 256" % nc},
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": backend, "sample": sample},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
@@ -248,7 +263,7 @@ def cpu_baseline(nc, budget_s=20.0):
     from oracle import cpu_model, reference as R
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    model = make_model(2).train()
+    model = make_model(2, cpu_container=True).train()
     opt = make_optimizer(model, fused=False)
     backend = "reference" if R.available("cpu") else "port"
     batches = synthetic_batches(2, 2000, nc)
@@ -258,6 +273,7 @@ def cpu_baseline(nc, budget_s=20.0):
         opt.zero_grad(set_to_none=True)
         loss = (cpu_model.forward(model, b, backend=backend) - torch.from_numpy(y)).abs().mean()
         loss.backward()
+        torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
         opt.step()
         n += 1
         if n == 1:
@@ -268,6 +284,77 @@ def cpu_baseline(nc, budget_s=20.0):
     steps = n - 1
     return {"value": nc * steps / dt, "unit": UNIT, "cores": threads, "kind": backend,
             "sample": f"{steps} training steps of {nc} crystals each (same distribution and model) after 1 warm-up step"}
+
+
+def gpu_reference(dev, model, host_batches, ours_ms_per_step):
+    """The reference's own CUDA kernels, compiled from their sources for sm_100a (oracle/_ref/libcfref_gpu.so), on
+    this GPU: (i) the isolated attention operator, forward + backward, on the 256-crystal operator batch, with this
+    library's fused entry points (per-pair geometry included) beside it; (ii) whole training steps of the same
+    4-layer model on the benchmark's own batches (the reference's launch sequence and host glue, torch AdamW and
+    clip_grad_norm_), with this library's step time beside it."""
+    from oracle import reference as R
+    if not R.available("cuda"):
+        return {"unavailable": "oracle/_ref/libcfref_gpu.so is not built on this machine"}
+    from crystalframer_b200 import _lib, opbench, synth
+    from crystalframer_b200 import cuda_funcs as F
+    from crystalframer_b200.cuda_funcs import common as FC
+    from oracle import cpu_model, gpu_reference_bench as G
+    out = {}
+    # (i) operator level
+    I = opbench.make_inputs("cfg2", None, dev)
+    ref_ms = G.reference_operator_ms(I, iters=3)
+    ours = []
+    for it in range(8):
+        FC._pair_cache.clear()                       # the per-pair geometry is part of the operator's cost
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        opbench.run_once_fused(I)
+        e1.record()
+        torch.cuda.synchronize()
+        ours.append(e0.elapsed_time(e1))
+    b = I["batch_obj"]
+    out["operator"] = {"workload": "cfg2: 256 crystals, %d atoms, %d pairs; frames + forward + backward" % (b.num_atoms, b.num_pairs),
+                       "reference_ms": {k: round(v, 3) for k, v in ref_ms.items()}, "reference_ms_total": round(sum(ref_ms.values()), 3),
+                       "ours_ms_total": round(float(np.median(ours[2:])), 4),
+                       "speedup": sum(ref_ms.values()) / float(np.median(ours[2:]))}
+    # (ii) step level: the same weights, the benchmark's batches, the reference kernels under the reference's glue
+    ref_model = copy.deepcopy(model)
+    for p in ref_model.parameters():
+        p.data = p.data.clone()                      # detach from the flat optimiser buffers of the timed model
+    opt = make_optimizer(ref_model, fused=False)
+    batches = synthetic_batches(2, 2, BATCH)
+    times = []
+    for i in range(3):
+        b, y = batches[i % 2]
+        yt = torch.from_numpy(y).to(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        opt.zero_grad(set_to_none=True)
+        loss = (cpu_model.forward(ref_model, b, backend="reference_cuda") - yt).abs().mean()
+        loss.backward()
+        torch.nn.utils.clip_grad_norm_(ref_model.parameters(), 1.0)
+        opt.step()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    ref_step = float(np.min(times[1:]))
+    out["step"] = {"workload": WORKLOAD, "reference_ms_per_step": round(ref_step, 2), "ours_ms_per_step": round(ours_ms_per_step, 4),
+                   "reference_crystals_per_s": BATCH / (ref_step * 1e-3), "speedup": ref_step / ours_ms_per_step,
+                   "note": "reference kernels built with SYMM_BREAK_NOISE 0; pair list and geometry prepared on the host (untimed would "
+                           "favour the reference, so they are inside its time, as in its own training loop)"}
+    return out
+
+
+def cpu_baseline_pure(budget_s=20.0):
+    """The reference's pure-PyTorch model (models/indexed_lattice_multi_head_attention.py of the reference, plain
+    Crystalformer without frames) on the host cores, 1 layer, 8 crystals of 4-16 atoms (the CPU-runnable
+    configuration).  Needs the reference's Python tree, named by CF_REFERENCE_ROOT; elsewhere it is reported as
+    unavailable -- the measured figure of the development machine is kept in the profiles folder."""
+    root = os.environ.get("CF_REFERENCE_ROOT")
+    if not root or not os.path.isdir(root):
+        return {"unavailable": "the reference's Python tree is not on this machine (CF_REFERENCE_ROOT)"}
+    from oracle import pure_baseline
+    return pure_baseline.measure(root, budget_s)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -343,13 +430,14 @@ def run_ours(args, rank, world, local_rank):
         while sampler.thread is not None and not sampler.samples and time.perf_counter() - t_wait < 8.0:
             time.sleep(0.05)
     barrier()
-    # pass 1: the K steps with every library call bracketed by CUDA events (per-kernel durations for
-    # the roofline); pass 2: the same K steps without those events -- this is ``value``
-    with _lib.KernelTimer() as kt:
+    # pass 1: the K steps with every library call, and every stage inside the one-call entry points, bracketed by
+    # CUDA events (per-kernel durations for the roofline); the later passes run without those events
+    with _lib.KernelTimer() as kt, _lib.StageTimer() as stg:
         barrier()
         ms_instrumented = timed(args.steps, from_host=False)
         barrier()
         ktimes = kt.summary()
+        stages = stg.summary()
     # Each arm times exactly K steps, REPEATS times over; the fastest pass is reported and all pass
     # times are listed (a slow pass is host interference on the shared machine, not the code).
     # The cost of a step depends on the model's state (the learned Gaussian widths set how many lattice
@@ -380,48 +468,58 @@ def run_ours(args, rank, world, local_rank):
     ms = min(passes)
     ms_e2e = min(passes_e2e)
     clocks = sampler.stop() if rank == 0 else None
-    t = torch.tensor([ms, ms_e2e, ms_instrumented], device=dev, dtype=torch.float64)
+    t = torch.tensor([ms, ms_e2e, ms_instrumented, float(np.median(passes)), float(np.median(passes_e2e))], device=dev,
+                     dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, ms_e2e, ms_instrumented = t.tolist()
+    ms, ms_e2e, ms_instrumented, ms_median, ms_e2e_median = t.tolist()
     status = _lib.read_status(dev)
+    # every rank's fused attention kernels (milliseconds per launch) and the work it was dealt
+    terms = lattice_terms(model, resident[0])
+    per_launch = lambda name: stages[name][1] / max(stages[name][0], 1) if name in stages else 0.0
+    mine = torch.tensor([per_launch("attn_fwd_kernel"), per_launch("attn_bwd_kernel"), sum(terms) / len(terms),
+                         float(np.mean([hb.num_pairs for hb in host])), enqueue_ms[0] / args.steps], device=dev,
+                        dtype=torch.float64)
+    ranks = [torch.zeros_like(mine) for _ in range(world)]
+    if world > 1:
+        dist.all_gather(ranks, mine)
+    else:
+        ranks = [mine]
+    ranks = torch.stack(ranks).cpu().numpy()
     if rank != 0:
         return
     value = BATCH * world * args.steps / (ms * 1e-3)
     e2e = BATCH * world * args.steps / (ms_e2e * 1e-3)
+    per_rank = {"attn_fwd_kernel_ms": [round(float(x), 4) for x in ranks[:, 0]],
+                "attn_bwd_kernel_ms": [round(float(x), 4) for x in ranks[:, 1]],
+                "terms_per_launch": [float(x) for x in ranks[:, 2]], "pairs_per_batch": [float(x) for x in ranks[:, 3]]}
 
-    # ---- roofline of the dominant kernel call ----
+    # ---- roofline of the dominant kernel ----
     peaks = measure_pipe_peaks(dev)
-    terms = lattice_terms(model, resident[0])
     avg_terms = sum(terms) / len(terms)
     pairs_heads = float(np.mean([hb.num_pairs for hb in host])) * 8
     kern = {}
-    for name, (calls, total) in ktimes.items():
+    for name, (calls, total) in list(ktimes.items()) + list(stages.items()):
         kern[name] = {"calls": calls, "ms_total": round(total, 3), "ms_avg": round(total / max(calls, 1), 4)}
-    # the dominant call: the fused lattice-sum + attention backward (or, on the operator path, the
-    # lattice-sum backward); the backward entry point includes the column pass of the attention
-    def first_of(*names):
-        return next(n for n in names if n in ktimes)
-    bwd_name = first_of("cfb200_attn_fused_bwd", "cfb200_framed_proj_bwd_cached", "cfb200_framed_proj_bwd")
-    fwd_name = first_of("cfb200_attn_fused_fwd", "cfb200_framed_proj_fwd_cached", "cfb200_framed_proj_fwd")
-    bwd_ms = ktimes[bwd_name][1] / ktimes[bwd_name][0]
-    fwd_ms = ktimes[fwd_name][1] / ktimes[fwd_name][0]
-    fused = bwd_name == "cfb200_attn_fused_bwd"
-    flops_bwd = avg_terms * FLOP_TERM_BWD + pairs_heads * (FLOP_PROJ_BWD + (FLOP_ATT_BWD if fused else 0.0))
-    flops_fwd = avg_terms * FLOP_TERM_FWD + pairs_heads * (FLOP_PROJ_FWD + (FLOP_ATT_FWD if fused else 0.0))
+    # the dominant kernel: the backward of the fused lattice-sum attention (attn_bwd_kernel), timed by CUDA events
+    # around its launch inside cfb200_encoder_layer_bwd
+    bwd_name, fwd_name = "attn_bwd_kernel", "attn_fwd_kernel"
+    bwd_ms, fwd_ms = per_launch(bwd_name), per_launch(fwd_name)
+    flops_bwd = avg_terms * FLOP_TERM_BWD + pairs_heads * (FLOP_PROJ_BWD + FLOP_ATT_BWD)
+    flops_fwd = avg_terms * FLOP_TERM_FWD + pairs_heads * (FLOP_PROJ_FWD + FLOP_ATT_FWD)
     ach = flops_bwd / (bwd_ms * 1e-3) / 1e12
     roofline = {"kernel": bwd_name, "bound": "fp32+sfu",
                 "achieved": ach, "peak": peaks["fp32_tflops"], "unit": "TFLOP/s", "frac": ach / peaks["fp32_tflops"],
                 "peak_source": "FP32 FMA throughput measured on this device by cfb200_probe_throughput",
                 "algorithmic_flop_per_launch": flops_bwd, "terms_per_launch": avg_terms, "ms_per_launch": bwd_ms,
                 "sfu_achieved_tops": avg_terms * SFU_TERM / (bwd_ms * 1e-3) / 1e12, "sfu_peak_tops": peaks["sfu_tops"],
-                # DRAM bytes of one launch: 43.9 MB (backward) for 306 560 (pair, head) sub-tasks in the profiler
-                # capture of the operator-level case (profiles/attn_fused_kernels_cfg2_opbench.md), scaled by
-                # the (pair, head) count -- mostly the first touch of the per-pair translation lists
-                "traffic": (43.9e6 / 306560.0 * pairs_heads) if fused else None,
+                # DRAM read + write bytes of ONE launch of this kernel on this workload's first batch, from a profiler
+                # capture of this command (one kernel, two launches); None until such a capture has been taken
+                "traffic": NCU_TRAFFIC_BYTES.get(bwd_name),
                 "traffic_unit": "bytes per launch (DRAM read + write)",
-                "forward": {"ms_per_launch": fwd_ms, "achieved": flops_fwd / (fwd_ms * 1e-3) / 1e12,
-                            "frac": flops_fwd / (fwd_ms * 1e-3) / 1e12 / peaks["fp32_tflops"]}}
+                "forward": {"kernel": fwd_name, "ms_per_launch": fwd_ms, "achieved": flops_fwd / (fwd_ms * 1e-3) / 1e12,
+                            "frac": flops_fwd / (fwd_ms * 1e-3) / 1e12 / peaks["fp32_tflops"],
+                            "traffic": NCU_TRAFFIC_BYTES.get(fwd_name)}}
     # the HBM-bound kernels of the path (ragged attention): algorithmic bytes over CUDA-event time against the
     # copy bandwidth measured on this pool (MEASURED_PEAKS.json beside this file; 6650 GB/s if it is absent)
     hbm_peak, hbm_src = 6650.0, "fallback"
@@ -443,17 +541,23 @@ def run_ours(args, rank, world, local_rank):
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "global_batch": BATCH * world, "parallelism": f"dp{world}",
                        "l2": "256 MB buffer written between timed steps", "optimizer": "AdamW lr 5e-4, clip 1.0, L1 loss",
-                       "timing": f"fastest of {REPEATS} passes of K steps per arm",
+                       "timing": f"fastest of {REPEATS} passes of K steps per arm; medians beside it",
                        "pass_ms_per_step": [round(x / args.steps, 3) for x in passes],
                        "e2e_pass_ms_per_step": [round(x / args.steps, 3) for x in passes_e2e]},
+            "pass_median_ms_per_step": ms_median / args.steps,
             "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
+                    "pass_median_ms_per_step": ms_e2e_median / args.steps,
                     "h2d_bytes_per_step": host[0].nbytes(), "d2h_bytes_per_step": 4},
+            "per_rank": per_rank,
             "gpu_launches": launches, "pair_sums_per_s": pair_sums, "roofline": roofline,
             "attention_hbm": attention_hbm, "kernels": kern,
             "host_enqueue_ms_per_step": host_ms / args.steps,
             "ms_per_step_with_kernel_events": ms_instrumented / args.steps, "clocks": clocks, "device_status": status}
+    if world == 1 and not args.no_gpu_reference:
+        line["gpu_reference"] = gpu_reference(dev, model, host, ms / args.steps)
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(args.cpu_crystals)
+        line["cpu_baseline_pure"] = cpu_baseline_pure()
     print(json.dumps(line), flush=True)
 
 

@@ -24,6 +24,31 @@ class Config(ctypes.Structure):
                 ("symm_break_noise", f32)]
 
 
+class LayerWeights(ctypes.Structure):          # cfb200_layer_weights
+    _fields_ = [(n, vp) for n in ("q_proj", "k_proj", "v_proj", "in_bias", "lattice_pos", "gauss_scale", "out_proj",
+                                  "out_bias", "pe_dist", "pe_ang1", "pe_ang2", "pe_ang3", "ff1", "ff1_bias", "ff2",
+                                  "ff2_bias")]
+
+
+class LayerGrads(ctypes.Structure):            # cfb200_layer_grads
+    _fields_ = [(n, vp) for n in ("q_proj", "k_proj", "v_proj", "in_bias", "lattice_pos", "out_proj", "out_bias",
+                                  "pe_dist", "pe_ang1", "pe_ang2", "pe_ang3", "ff1", "ff1_bias", "ff2", "ff2_bias")]
+
+
+class Geometry(ctypes.Structure):              # cfb200_geometry
+    _fields_ = [(n, vp) for n in ("pos_ij", "tvecs", "rvlen", "batch", "edges", "e_start", "order", "counters",
+                                  "pair_cache", "pair_list")] + [("N", i64), ("E", i64), ("cache_range", i32)]
+
+
+class LayerState(ctypes.Structure):            # cfb200_layer_state
+    _fields_ = [(n, vp) for n in ("q", "q_scaled", "k", "v", "a", "frames", "z", "spool", "attn", "lse", "x1", "h")]
+
+
+class LayerDesc(ctypes.Structure):             # cfb200_layer_desc
+    _fields_ = [("d_model", i32), ("ff_dim", i32), ("frame_method", i32), ("gauss_lb", f32), ("beta", f32),
+                ("scale_real", f32), ("dist_max", f32), ("cutoff_radius", f32), ("seed1", u64), ("seed2", u64)]
+
+
 # name -> (restype, argtypes); one entry per declaration of include/cfb200.h
 SIGNATURES = {
     "cfb200_configure": (ctypes.c_int, [ctypes.POINTER(Config)]),
@@ -58,8 +83,27 @@ SIGNATURES = {
     "cfb200_segment_mean_fwd": (ctypes.c_int, [vp, vp, i64, i64, vp, vp]),
     "cfb200_segment_mean_bwd": (ctypes.c_int, [vp, vp, i64, i64, vp, vp]),
     "cfb200_adamw_clip_step": (ctypes.c_int, [vp] * 4 + [i64, i64] + [f32] * 6 + [ctypes.c_double, ctypes.c_double, vp, vp, vp]),
+    "cfb200_batch_geometry_workspace_bytes": (i64, [i64]),
+    "cfb200_batch_geometry": (ctypes.c_int, [vp, vp, vp, i64, i64, i64, ctypes.c_int] + [vp] * 11 + [vp, i64, vp]),
+    "cfb200_encoder_layer_workspace_bytes": (i64, [i64, i64, ctypes.c_int, ctypes.c_int, ctypes.c_int]),
+    "cfb200_encoder_layer_fwd": (ctypes.c_int, [vp, vp, vp, vp, vp, vp, vp, i64, vp]),
+    "cfb200_encoder_layer_bwd": (ctypes.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, ctypes.c_int, vp, i64, vp]),
+    "cfb200_timing_begin": (ctypes.c_int, []),
+    "cfb200_timing_end": (ctypes.c_int, [vp, vp]),
     "cfb200_probe_throughput": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, vp, vp]),
 }
+
+
+_pending = []
+
+
+def loaded():
+    return _lib is not None
+
+
+def on_load(fn):
+    """Runs ``fn(handle)`` when the shared library is first loaded (only the latest registration is kept)."""
+    _pending[:] = [fn]
 
 
 def lib():
@@ -75,6 +119,9 @@ def lib():
             fn.restype = res
             fn.argtypes = args
         _lib = handle
+        for fn in _pending:
+            fn(handle)
+        _pending.clear()
     return _lib
 
 
@@ -125,6 +172,28 @@ class KernelTimer:
     def summary(self):
         torch.cuda.synchronize()
         return {name: (len(ev), sum(a.elapsed_time(b) for a, b in ev)) for name, ev in self.records.items()}
+
+
+TIMING_STAGES = ("batch_geometry", "linear_fwd", "coef", "frames", "attn_fwd_kernel", "linear_bwd", "attn_bwd_kernel",
+                 "attn_bwd_cols_kernel", "wgrad")
+
+
+class StageTimer:
+    """Per-stage CUDA-event times of the one-call entry points (cfb200_timing_begin / _end): ``summary()``
+    waits for the events and returns {stage: (brackets, total milliseconds)}."""
+
+    def __enter__(self):
+        check(lib().cfb200_timing_begin(), "cfb200_timing_begin")
+        return self
+
+    def __exit__(self, *exc):
+        pass
+
+    def summary(self):
+        ms = (f32 * len(TIMING_STAGES))()
+        n = (i32 * len(TIMING_STAGES))()
+        check(lib().cfb200_timing_end(ms, n), "cfb200_timing_end")
+        return {name: (int(n[i]), float(ms[i])) for i, name in enumerate(TIMING_STAGES) if n[i] > 0}
 
 
 def _device_index(device):

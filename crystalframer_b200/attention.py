@@ -82,6 +82,9 @@ def compute_real_domain_attn_frame_proj(q, k, v, batch_q, batch_kv, edges, pos, 
             qs = q / math.sqrt(q.shape[-1])
             f1, f2, f3 = weighted_pca_frames(qs, k, alpha, pos, tvecs, batch_q, edges, *(rv_args or (None, None)))[:3]
         W1, W2, W3 = proj_angle1, proj_angle2, proj_angle3
+        from . import fused_layer
+        if fused_layer.FRAME_TAP is not None:
+            fused_layer.FRAME_TAP.append(torch.stack([f1, f2, f3]).clone())
     elif params.frame_method == "no":
         # plain Crystalformer: un-windowed distance encoding, no frames, no coefficients
         # (models/indexed_lattice_multi_head_attention_cuda.py:403-433, :620-624)
@@ -97,6 +100,29 @@ def compute_real_domain_attn_frame_proj(q, k, v, batch_q, batch_kv, edges, pos, 
     return out[0], (out[1] if len(out) > 1 else None)
 
 
+def gauss_scale_ready(gauss_scale):
+    """True once the coefficient statistics in ``gauss_scale`` are known to be set.  ``gauss_scale[0] > 0`` is a
+    device-side fact; reading it every call would stall the host once per layer, so a positive answer is
+    remembered on the tensor object TOGETHER with the tensor's version counter: any in-place write
+    (load_state_dict, zero_, re-calibration) invalidates it and the value is read again."""
+    if getattr(gauss_scale, "_cf_ready", None) == gauss_scale._version:
+        return True
+    if bool(gauss_scale[0] > 0):
+        gauss_scale._cf_ready = gauss_scale._version
+        return True
+    return False
+
+
+def reset_gauss_scale(module):
+    """Forgets the measured coefficient statistics of every attention module below ``module``; the next training
+    forward measures them again (as the reference does when gauss_scale is zero)."""
+    for m in module.modules():
+        gs = getattr(m, "gauss_scale", None)
+        if gs is not None:
+            with torch.no_grad():
+                gs.zero_()
+
+
 def gaussian_coefficients(q, lattice_pos_weights, gauss_scale, params, training):
     """models/indexed_lattice_multi_head_attention_cuda.py:896-940: per (atom, head) coefficient
     a < 0 of exp(a d^2), from q and the learned per-head direction, normalised with statistics
@@ -106,13 +132,7 @@ def gaussian_coefficients(q, lattice_pos_weights, gauss_scale, params, training)
         raise NotImplementedError(f"gauss_state={params.gauss_state}")
     alpha = (q.reshape(N, H, 1, hd) @ lattice_pos_weights.reshape(H, hd, 1)).view(N, H)
     if params.normalize_gauss:
-        # ``gauss_scale[0] > 0`` is a device-side fact; reading it every call would stall the host
-        # once per layer, so a positive answer is remembered on the tensor object.
-        ready = getattr(gauss_scale, "_cf_ready", False)
-        if not ready and bool(gauss_scale[0] > 0):
-            ready = True
-            gauss_scale._cf_ready = True
-        if ready:
+        if gauss_scale_ready(gauss_scale):
             scale, shift = gauss_scale[0], gauss_scale[1]
         else:
             scale = torch.reciprocal(alpha.detach().std())
@@ -121,7 +141,7 @@ def gaussian_coefficients(q, lattice_pos_weights, gauss_scale, params, training)
                 with torch.no_grad():
                     gauss_scale[0] = scale
                     gauss_scale[1] = shift
-                gauss_scale._cf_ready = True
+                gauss_scale._cf_ready = gauss_scale._version
         alpha = (alpha + shift) * scale
     lb, beta = params.gauss_lb_real, params.positive_func_beta
     pos = (1.0 - lb) * F.elu(alpha * (beta / (1.0 - lb))) + 1.0

@@ -12,6 +12,7 @@
 #include "sigma.cu"
 #include "attn_fused.cu"
 #include "optim.cu"
+#include "linear.cu"
 
 namespace cfb {
 
@@ -615,3 +616,4 @@ int cfb200_adamw_clip_step(float* params, const float* grads, float* exp_avg, fl
 }  // extern "C"
 
 #include "framed_proj_noalloc.cu"
+#include "layer.cu"

@@ -6,6 +6,11 @@ import ctypes
 from .. import _lib
 
 
+# When True, compile_kernels only records the hyper-parameters; they are bound when the library is first
+# loaded.  For processes that build the model classes as parameter containers without ever running them.
+DEFER_BINDING = False
+
+
 class KernelManager:
     """Limits of the reference kept for callers that read them (kernel_manager.py:59-62).
     The kernels of this package have no atom-count limit."""
@@ -29,8 +34,11 @@ def compile_kernels(lattice_range: int, head_num: int, key_head_dim: int, value_
                       cut_sigma=4, dist_wscale=value_pe_dist_wscale, angle_wscale=value_pe_angle_wscale,
                       dist_coef=value_pe_dist_coef, angle_coef=value_pe_angle_coef,
                       symm_break_noise=symm_break_noise)
-    _lib.check(_lib.lib().cfb200_configure(ctypes.byref(cfg)), "cfb200_configure")
     KernelManager.config = cfg
+    if DEFER_BINDING and not _lib.loaded():
+        _lib.on_load(lambda handle: _lib.check(handle.cfb200_configure(ctypes.byref(cfg)), "cfb200_configure"))
+        return cfg
+    _lib.check(_lib.lib().cfb200_configure(ctypes.byref(cfg)), "cfb200_configure")
     return cfg
 
 

@@ -14,7 +14,7 @@ from torch.nn.init import constant_, xavier_uniform_
 
 from . import _lib
 from . import fused_layer
-from .attention import CrystalformerMultiheadAttentionCUDA
+from .attention import CrystalformerMultiheadAttentionCUDA, gauss_scale_ready
 from .cuda_funcs import compile_kernels, register_csr
 from .latticeformer_params import LatticeformerParams
 
@@ -126,30 +126,33 @@ class CrystalformerEncoderLayerCUDA(Module):
                       self.self_attn.v_proj_weight):
                 w.mul_(s)
 
-    def _fused_forward(self, x, batch, edges, pos_ij, trans, rvecs):
-        """The whole layer as one autograd node (fused_layer.FusedEncoderLayerFunc), or None when
-        this layer's configuration or state is outside what that path covers."""
+    def fused_meta(self, x):
+        """Scalars for the one-call layer (fused_layer), or None when this layer's configuration or state
+        is outside what that path covers."""
         if not (FUSED_LAYER and x.is_cuda and isinstance(self.norm1, Identity) and isinstance(self.norm2, Identity)
                 and isinstance(self.dropout, Identity) and self.activation is F.relu):
             return None
-        attn = self.self_attn
-        if not getattr(attn.gauss_scale, "_cf_ready", False):
+        if not gauss_scale_ready(self.self_attn.gauss_scale):
             return None          # the first training forward measures the coefficient statistics
         if self._fused_meta is None:
-            self._fused_meta = fused_layer.layer_meta(attn) or False
-        if self._fused_meta is False:
+            self._fused_meta = fused_layer.layer_meta(self) or False
+        return self._fused_meta or None
+
+    def fused_apply(self, x, geo, meta):
+        return fused_layer.FusedEncoderLayerFunc.apply(x, *fused_layer.layer_parameters(self), geo, meta)
+
+    def _fused_forward(self, x, batch, edges, pos_ij, trans, rvecs):
+        """The whole layer as one autograd node for callers that hand over the reference's tensors."""
+        meta = self.fused_meta(x)
+        if meta is None:
             return None
         geo = getattr(edges, "_cf_geometry", None)
         if geo is None or geo.pos_ij is not pos_ij:
-            rvlen = torch.norm(rvecs, 2, dim=-1).contiguous() if self._fused_meta["cutoff"] != 0.0 else None
-            geo = fused_layer.LayerGeometry(pos_ij.contiguous(), trans.contiguous(), batch.contiguous(),
-                                            edges.contiguous(), rvlen, self._fused_meta["cutoff"])
+            rvlen = torch.norm(rvecs, 2, dim=-1).contiguous() if meta["cutoff"] != 0.0 else None
+            geo = fused_layer.LayerGeometry.from_tensors(pos_ij.contiguous(), trans.contiguous(), batch.contiguous(),
+                                                         edges.contiguous(), rvlen, meta["cutoff"])
             edges._cf_geometry = geo
-        return fused_layer.FusedEncoderLayerFunc.apply(
-            x, attn.q_proj_weight, attn.k_proj_weight, attn.v_proj_weight, attn.in_proj_bias, attn.lattice_pos_weights,
-            attn.gauss_scale, attn.out_proj.weight, attn.out_proj.bias, attn.pe_dist_proj, attn.proj_angle1,
-            attn.proj_angle2, attn.proj_angle3, self.linear1.weight, self.linear1.bias, self.linear2.weight,
-            self.linear2.bias, geo, self._fused_meta)
+        return self.fused_apply(x, geo, meta)
 
     def forward(self, src, batch, edges, pos_ij=None, dist2_min=None, trans=None, kr_base=None, rvecs=None,
                 vcell=None, onehot=None, this_epoch=None):
@@ -203,12 +206,23 @@ class CrystalformerEncoderCUDA(Module):
                         P.value_pe_angle_coef, P.symm_break_noise)
 
     def forward(self, src, pos, batch, trans, sizes, onehot=None, this_epoch=None, num_pairs=None):
+        if src.size(-1) != self.d_model:
+            raise RuntimeError("the feature number of src must be equal to d_model")
+        # Fast path: every layer runs as one library call and the batch is prepared by one
+        # (fused_layer.LayerGeometry.from_raw); needs the pair count, which the batch objects of this package carry.
+        if num_pairs is not None and torch.is_tensor(sizes) and sizes.is_cuda and sizes.dtype == torch.int64:
+            metas = [layer.fused_meta(src) for layer in self.layers]
+            if all(m is not None for m in metas) and pos.dtype == torch.float32 and trans.dtype == torch.float32:
+                geo = fused_layer.LayerGeometry.from_raw(pos.contiguous(), trans.contiguous(), sizes.contiguous(),
+                                                         pos.shape[0], int(num_pairs), metas[0]["cutoff"])
+                out = src
+                for layer, meta in zip(self.layers, metas):
+                    out = layer.fused_apply(out, geo, meta)
+                return out if self.norm is None else self.norm(out)
         batch = batch - batch[0]
         pos_ij, dist2_min, kr_base, rvecs, vcell, edges = compute_lattice_distances_for_cuda(
             pos, batch, trans, sizes, self.lattice_params.lattice_range, -1, output_real=True, output_reci=False,
             num_pairs=num_pairs)
-        if src.size(-1) != self.d_model:
-            raise RuntimeError("the feature number of src must be equal to d_model")
         out = src
         for layer in self.layers:
             out = layer(out, batch, edges, pos_ij, dist2_min, trans, kr_base, rvecs, vcell, onehot, this_epoch)

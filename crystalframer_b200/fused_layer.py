@@ -1,225 +1,237 @@
-"""One autograd Function for a whole encoder layer.
+"""One autograd node and ONE library call per encoder layer and direction.
 
 The reference runs an encoder layer as ~35 separately tracked torch operations plus its CuPy
 Functions (models/indexed_latticeformer_encoder.py:848-890 and
-models/indexed_lattice_multi_head_attention_cuda.py:737-996).  At 2-3 k atoms per batch the
-GPU work of most of those operations is a few microseconds, so the step time is set by host-side
-dispatch and autograd bookkeeping.  This Function performs the same arithmetic -- input
-projections, Gaussian coefficients, max frames, lattice-sum bias and value encoding, ragged
-attention, output projection, residuals and the feed-forward block -- with one graph node: the
-dense layers stay on cuBLAS through ``torch.addmm`` / ``torch.mm``, everything specific to the
-periodic attention runs in libcfb200, and the backward pass is written out by hand.
+models/indexed_lattice_multi_head_attention_cuda.py:737-996) and prepares a batch with ~60 more
+(models/indexed_latticeformer_encoder.py:15-32, :175-245).  At 2-3 k atoms per batch the GPU work of
+most of those operations is a few microseconds, so the step time is set by host-side dispatch and
+autograd bookkeeping.  Here ``cfb200_batch_geometry`` prepares a batch and
+``cfb200_encoder_layer_fwd`` / ``_bwd`` run a whole layer -- input projections, Gaussian
+coefficients, frames, lattice-sum attention, output projection, residuals, feed-forward block, and in
+the backward all data, weight and bias gradients -- with every kernel enqueued from C.
 
-Used by ``CrystalformerEncoderLayerCUDA.forward`` when the layer has the default structure
-(real-space domain, "max" or weighted-PCA frames or none, coefficients from q, no dropout, no layer norm, ReLU); any other
-configuration takes the operator-by-operator path.
+Used by ``CrystalformerEncoderCUDA.forward`` when the layers have the default structure (real-space
+domain, "max" or weighted-PCA frames or none, coefficients from q, no dropout, no layer norm, ReLU);
+any other configuration takes the operator-by-operator path.
+
+Gradient sink: when a parameter carries ``_cf_grad_sink`` (a tensor of its shape, set by
+``optim.FlatAdamW``) the backward ADDS the parameter's gradient into that tensor and reports no
+gradient to autograd, so a training step neither allocates per-parameter gradients nor gathers them.
 """
+import ctypes
 import math
 
 import torch
 
 from . import _lib
-from .cuda_funcs.common import csr_offsets, pair_geometry
 from .cuda_funcs.max_frame import _draw_seed
 
+# entry points whose presence in a trace shows that a layer ran through this module
+FUSED_FORWARD_CALLS = ("cfb200_encoder_layer_fwd",)
+# test hook: a list here receives a copy of every layer's frames (3,N,H,3) as the forward computes them
+FRAME_TAP = None
 
-FUSED_ATTENTION = True      # lattice sums + attention as one kernel per direction; False: separate entry points
+FRAME_METHODS = {"no": 0, "max": 1, "weighted_pca": 2}
+WEIGHT_FIELDS = ("q_proj", "k_proj", "v_proj", "in_bias", "lattice_pos", "gauss_scale", "out_proj", "out_bias",
+                 "pe_dist", "pe_ang1", "pe_ang2", "pe_ang3", "ff1", "ff1_bias", "ff2", "ff2_bias")
+GRAD_FIELDS = tuple(f for f in WEIGHT_FIELDS if f != "gauss_scale")
 
-_side_streams = {}
 
-
-def _side_stream(dev):
-    """Second stream of a device for work that does not sit on the layer's critical path (weight and
-    bias gradients): those GEMMs fill half of the SMs, so they run beside the data-gradient chain."""
-    s = _side_streams.get(dev)
-    if s is None:
-        s = _side_streams[dev] = torch.cuda.Stream(device=dev)
-    return s
+def _align(n, a=64):
+    return (n + a - 1) // a * a
 
 
 class LayerGeometry:
-    """Per-batch tensors shared by all layers, and the per-pair geometry cache (nearest image and
-    smallest squared distance of every pair): pure geometry, the same for every head and layer, so it
-    is computed once per batch for the lattice range nearly all (atom, head) pairs end up with."""
-    __slots__ = ("pos_ij", "tvecs", "batch", "edges", "e_start", "rvlen", "N", "E", "pair_cache", "pair_list",
-                 "cache_range", "order", "counters")
+    """Per-batch tensors shared by all layers: pair list, relative positions, reciprocal-vector lengths, the
+    per-pair geometry cache (nearest image, smallest squared distance, translations sorted by distance:
+    pure geometry, identical for every head and layer), the work-queue order of the attention kernels and
+    a scratch buffer that all layers of the batch reuse (their kernels run on one stream, in order)."""
 
-    def __init__(self, pos_ij, tvecs, batch, edges, rvlen, cutoff=0.0):
-        self.pos_ij, self.tvecs, self.batch, self.edges, self.rvlen = pos_ij, tvecs, batch, edges, rvlen
-        self.N, self.E = batch.shape[0], edges.shape[1]
-        self.e_start = csr_offsets(edges, self.N)
-        self.pair_cache, self.pair_list, self.cache_range = pair_geometry(pos_ij, tvecs, batch, edges, cutoff)
-        # The order in which the per-atom attention kernels hand out work: most expensive atoms first.  An
-        # atom costs about (a constant + its surviving translations) per pair, and the translations within
-        # reach of a Gaussian of typical width number about (a sphere of radius 8 A) / (cell volume).
-        pairs_per_atom = (self.e_start[1:] - self.e_start[:-1]).float()
+    def __init__(self):
+        self.c = _lib.Geometry()
+        self.N = self.E = self.B = 0
+        self.cache_range = 0
+        self._keep = []
+        self._ws = None
+
+    @classmethod
+    def from_raw(cls, pos, trans, sizes, N, E, cutoff):
+        """One call of cfb200_batch_geometry on raw positions (N,3), lattice vectors (B,3,3), sizes (B)."""
+        from .cuda_funcs.common import PAIR_LIST_MAX_PAIRS
+        from .cuda_funcs.kernel_manager import KernelManager
+        g = cls()
+        dev = pos.device
+        B = trans.shape[0]
+        cfg = KernelManager.config
+        rng = int(cfg.lattice_range if cutoff == 0.0 else cfg.minimum_range)
+        want_list = rng > 0 and (2 * rng + 1) ** 3 <= 128 and E <= PAIR_LIST_MAX_PAIRS
+        # int64 block: edges (2E) | e_start (N+1) | batch (N) | crystal_start (B+1)
+        o_es = 2 * E
+        o_b = o_es + N + 1
+        o_cs = o_b + N
+        ibuf = torch.empty(o_cs + B + 1, dtype=torch.int64, device=dev)
+        # float32 block: pos_ij (3E) | rvlen (3B) | pair_cache (4E) | order (N, int32) | counters (64, int32) | call scratch
+        ws_bytes = int(_lib.lib().cfb200_batch_geometry_workspace_bytes(B))
+        o_rv = _align(3 * E)
+        o_pc = _align(o_rv + 3 * B)
+        o_or = _align(o_pc + 4 * E)
+        o_ct = _align(o_or + N)
+        o_ws = _align(o_ct + 64)
+        fbuf = torch.empty(o_ws + ws_bytes // 4, dtype=torch.float32, device=dev)
+        plist = torch.empty((E, 5, 128), dtype=torch.float32, device=dev) if want_list else None
+        ip, fp = ibuf.data_ptr(), fbuf.data_ptr()
+        _lib.invoke("cfb200_batch_geometry", 7, dev, _lib.ptr(pos), _lib.ptr(trans), _lib.iptr(sizes), B, N, E, rng,
+                    ip, ip + 8 * o_es, ip + 8 * o_b, ip + 8 * o_cs, fp, None, fp + 4 * o_rv, None,
+                    fp + 4 * o_pc if rng > 0 else None, _lib.ptr(plist), fp + 4 * o_or, fp + 4 * o_ws, ws_bytes)
+        g.N, g.E, g.B, g.cache_range = N, E, B, rng
+        g._keep = [ibuf, fbuf, plist, pos, trans, sizes]
+        g.edges = ibuf[:2 * E].view(2, E)
+        g.e_start = ibuf[o_es:o_es + N + 1]
+        g.batch = ibuf[o_b:o_b + N]
+        g.pos_ij = fbuf[:3 * E].view(E, 3)
+        g.rvlen = fbuf[o_rv:o_rv + 3 * B].view(B, 3)
+        g.tvecs = trans
+        c = g.c
+        c.pos_ij, c.tvecs, c.rvlen = fp, trans.data_ptr(), fp + 4 * o_rv
+        c.batch, c.edges, c.e_start = ip + 8 * o_b, ip, ip + 8 * o_es
+        c.order, c.counters = fp + 4 * o_or, fp + 4 * o_ct
+        c.pair_cache = fp + 4 * o_pc if rng > 0 else None
+        c.pair_list = plist.data_ptr() if plist is not None else None
+        c.N, c.E, c.cache_range = N, E, g.cache_range
+        return g
+
+    @classmethod
+    def from_tensors(cls, pos_ij, tvecs, batch, edges, rvlen, cutoff=0.0):
+        """From the tensors the reference's callers hand to a layer (pair list and relative positions already
+        built): adds CSR offsets, the per-pair geometry cache and the work-queue order."""
+        from .cuda_funcs.common import csr_offsets, pair_geometry
+        g = cls()
+        g.N, g.E, g.B = batch.shape[0], edges.shape[1], tvecs.shape[0]
+        g.pos_ij, g.tvecs, g.batch, g.edges, g.rvlen = pos_ij, tvecs, batch, edges, rvlen
+        g.e_start = csr_offsets(edges, g.N)
+        pair_cache, pair_list, g.cache_range = pair_geometry(pos_ij, tvecs, batch, edges, cutoff)
+        pairs_per_atom = (g.e_start[1:] - g.e_start[:-1]).float()
         vcell = (tvecs[:, 0] * torch.linalg.cross(tvecs[:, 1], tvecs[:, 2])).sum(1).abs().clamp_min(1e-6)
         survivors = (2145.0 / vcell).clamp(1.0, 125.0)[batch]
-        self.order = torch.argsort(pairs_per_atom * (7.0 + survivors), descending=True, stable=True).to(torch.int32)
-        self.counters = torch.zeros(64, dtype=torch.int32, device=pos_ij.device)
+        order = torch.argsort(pairs_per_atom * (7.0 + survivors), descending=True, stable=True).to(torch.int32)
+        counters = torch.zeros(64, dtype=torch.int32, device=pos_ij.device)
+        g._keep = [pair_cache, pair_list, order, counters]
+        c = g.c
+        c.pos_ij, c.tvecs, c.rvlen = _lib.ptr(pos_ij), _lib.ptr(tvecs), _lib.ptr(rvlen)
+        c.batch, c.edges, c.e_start = _lib.iptr(batch), _lib.iptr(edges), _lib.iptr(g.e_start)
+        c.order, c.counters = order.data_ptr(), counters.data_ptr()
+        c.pair_cache, c.pair_list = _lib.ptr(pair_cache), _lib.ptr(pair_list)
+        c.N, c.E, c.cache_range = g.N, g.E, g.cache_range
+        return g
+
+    def workspace(self, nbytes, device):
+        if self._ws is None or self._ws.numel() < nbytes:
+            self._ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+        return self._ws
+
+
+def _state_layout(N, E, H, D, F, frames):
+    """Offsets (floats) of the activations a layer's forward leaves for its backward, in one buffer."""
+    sizes = (("q", N * D), ("q_scaled", N * D), ("k", N * D), ("v", N * D), ("a", N * H),
+             ("frames", 9 * N * H if frames else 0), ("z", E * H), ("spool", N * H * 256), ("attn", N * D),
+             ("lse", N * H), ("x1", N * D), ("h", N * F))
+    off, total = {}, 0
+    for name, n in sizes:
+        off[name] = total if n else None
+        total += _align(n)
+    return off, total
 
 
 class FusedEncoderLayerFunc(torch.autograd.Function):
+    """forward(x, q_proj, k_proj, v_proj, in_bias, lattice_pos, gauss_scale, out_proj, out_bias, pe_dist, pe_ang1,
+    pe_ang2, pe_ang3, ff1, ff1_bias, ff2, ff2_bias, geometry, meta) -> x_out"""
+
     @staticmethod
-    def forward(ctx, x, Wq, Wk, Wv, b_in, w_lat, gauss_scale, Wo, bo, Wd, W1, W2, W3, Wf1, bf1, Wf2, bf2, geo, meta):
-        H, hd = meta["H"], meta["hd"]
+    def forward(ctx, x, *args):
+        params, geo, meta = args[:16], args[16], args[17]
+        H, hd, F = meta["H"], meta["hd"], meta["F"]
         N, E, dev = geo.N, geo.E, x.device
         D = H * hd
-        p, ip = _lib.ptr, _lib.iptr
         x = x.contiguous()
-        bq, bk, bv = b_in[:D], b_in[D:2 * D], b_in[2 * D:]
-        q = torch.addmm(bq, x, Wq.t())
-        k = torch.addmm(bk, x, Wk.t())
-        v = torch.addmm(bv, x, Wv.t())
-        new = lambda *shape: torch.empty(shape, device=dev, dtype=torch.float32)
-        a, qs = new(N, H), new(N, H, hd)
-        _lib.invoke("cfb200_gauss_coef_fwd", 1, dev, p(q), p(w_lat), p(gauss_scale), N, meta["lb"], meta["beta"],
-                    meta["scale_real"], p(a), p(qs))
-        plain = meta["frame_method"] == "no"           # plain Crystalformer: un-windowed distance encoding, no frames
-        f = None if plain else new(3, N, H, 3)
-        fr = (None, None, None) if plain else (f[0], f[1], f[2])
-        if plain:
-            pass
-        elif meta["frame_method"] == "max":
-            s1, s2 = _draw_seed(), _draw_seed()
-            _lib.invoke("cfb200_max_frames_cached", 1, dev, p(qs), p(k), p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
-                        ip(geo.batch), ip(geo.edges), ip(geo.e_start), N, E, meta["cutoff"], s1, s2, p(f[0]), p(f[1]),
-                        p(f[2]), p(geo.pair_cache), p(geo.pair_list), geo.cache_range)
-        else:
-            # weighted-PCA frames; the same draws from the generators as cuda_funcs.weighted_pca_frames
+        method = FRAME_METHODS[meta["frame_method"]]
+        if method == 2:
+            # weighted-PCA frames: the same draws from the generators as cuda_funcs.weighted_pca_frames
             _draw_seed()
-            seed_noise = _draw_seed()
-            seed_sign = int(torch.randint(0, 2 ** 62, (1,)).item())
-            nbytes = int(_lib.lib().cfb200_sigma_frames_workspace_bytes(N, E))
-            ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
-            _lib.invoke("cfb200_sigma_frames", 2, dev, p(qs), p(k), p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
-                        ip(geo.batch), ip(geo.edges), ip(geo.e_start), N, E, meta["cutoff"], seed_noise, seed_sign,
-                        p(f[0]), p(f[1]), p(f[2]), ws.data_ptr(), nbytes)
-        Wd3 = Wd[0]
-        W13, W23, W33 = (None, None, None) if plain else (W1[0], W2[0], W3[0])
-        o, lse = new(N, H, hd), new(N, H)
-        if FUSED_ATTENTION or plain:
-            # lattice sums, value encoding and attention in one kernel: the basis sums are pooled with the
-            # attention weights and projected once per (atom, head)
-            z, val, spool = new(E, H), None, new(N, H, 4 * 64)
-            _lib.invoke("cfb200_attn_fused_fwd", 1, dev, p(qs), p(k), p(v), p(a), p(geo.pos_ij), p(geo.tvecs),
-                        p(geo.rvlen), ip(geo.batch), ip(geo.edges), ip(geo.e_start), p(geo.order, torch.int32),
-                        p(geo.counters, torch.int32), N, E,
-                        meta["dist_max"], meta["cutoff"], p(Wd3), p(W13), p(W23), p(W33), p(fr[0]), p(fr[1]), p(fr[2]),
-                        p(geo.pair_list), geo.cache_range, p(o), p(z), p(lse), p(spool), 1 if plain else 0)
+            seed1 = _draw_seed()
+            seed2 = int(torch.randint(0, 2 ** 62, (1,)).item())
+        elif method == 1:
+            seed1, seed2 = _draw_seed(), _draw_seed()
         else:
-            z, val, spool = new(E, H), new(E, H, hd), None
-            _lib.invoke("cfb200_framed_proj_fwd_cached", 1, dev, p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
-                        ip(geo.batch), ip(geo.edges), N, E, meta["dist_max"], meta["cutoff"], p(Wd3), p(W13), p(W23),
-                        p(W33), p(f[0]), p(f[1]), p(f[2]), p(z), p(val), p(geo.pair_cache), p(geo.pair_list),
-                        geo.cache_range)
-            _lib.invoke("cfb200_dpa_fwd", 1, dev, p(qs), p(k), p(v), p(z), p(val), ip(geo.edges), ip(geo.e_start), N, E,
-                        p(o), p(lse), None)
-        x1 = torch.addmm(bo, o.view(N, D), Wo.t()).add_(x)
-        h = torch.addmm(bf1, x1, Wf1.t()).relu_()
-        x2 = torch.addmm(bf2, h, Wf2.t()).add_(x1)
-        ctx.save_for_backward(x, Wq, Wk, Wv, w_lat, gauss_scale, Wo, Wd, W1, W2, W3, Wf1, Wf2, q, qs, k, v, a, f, z,
-                              val if val is not None else spool, o, lse, x1, h)
-        ctx.geo, ctx.meta, ctx.fused_attention = geo, meta, val is None
-        return x2
+            seed1 = seed2 = 0
+        desc = _lib.LayerDesc(D, F, method, meta["lb"], meta["beta"], meta["scale_real"], meta["dist_max"], meta["cutoff"],
+                              seed1, seed2)
+        W = _lib.LayerWeights(*[None if p is None else _lib.ptr(p) for p in params])
+        off, total = _state_layout(N, E, H, D, F, method != 0)
+        state = torch.empty(total, dtype=torch.float32, device=dev)
+        base = state.data_ptr()
+        St = _lib.LayerState(*[None if off[f] is None else base + 4 * off[f] for f, _ in _lib.LayerState._fields_])
+        out = torch.empty_like(x)
+        nbytes = int(_lib.lib().cfb200_encoder_layer_workspace_bytes(N, E, D, F, method))
+        ws = geo.workspace(nbytes, dev)
+        _lib.invoke("cfb200_encoder_layer_fwd", 8 + (method == 1) + 2 * (method == 2), dev, ctypes.byref(desc),
+                    ctypes.byref(W), ctypes.byref(geo.c), x.data_ptr(), ctypes.byref(St), out.data_ptr(), ws.data_ptr(),
+                    ws.numel())
+        if FRAME_TAP is not None and method != 0:
+            FRAME_TAP.append(state[off["frames"]:off["frames"] + 9 * N * H].view(3, N, H, 3).clone())
+        ctx.save_for_backward(x, state, *params)
+        ctx.geo, ctx.desc, ctx.St, ctx.W = geo, desc, St, W
+        ctx.sinks = tuple(getattr(p, "_cf_grad_sink", None) if p is not None else None for p in params)
+        return out
 
     @staticmethod
     def backward(ctx, g):
-        (x, Wq, Wk, Wv, w_lat, gauss_scale, Wo, Wd, W1, W2, W3, Wf1, Wf2, q, qs, k, v, a, f, z, val, o, lse, x1,
-         h) = ctx.saved_tensors                  # val: the value encoding, or the pooled basis sums (fused attention)
-        geo, meta = ctx.geo, ctx.meta
-        H, hd = meta["H"], meta["hd"]
+        x, state = ctx.saved_tensors[:2]
+        params = ctx.saved_tensors[2:]
+        geo, desc = ctx.geo, ctx.desc
         N, E, dev = geo.N, geo.E, x.device
-        D = H * hd
-        plain = meta["frame_method"] == "no"
-        p, ip = _lib.ptr, _lib.iptr
-        new = lambda *shape: torch.empty(shape, device=dev, dtype=torch.float32)
         g = g.contiguous()
-        main, side = torch.cuda.current_stream(dev), _side_stream(dev)
-        # Data gradients run on the current stream; weight and bias gradients, which nothing in this
-        # backward pass reads, follow on the side stream as soon as their operands exist.  Every operand
-        # stays referenced until the streams are joined at the end, so no block is recycled early.
-        ev = torch.cuda.Event()
-        ev.record(main)
-        gh = torch.ops.aten.threshold_backward(g.mm(Wf2), h, 0)
-        gx1 = torch.addmm(g, gh, Wf1)
-        ev1 = torch.cuda.Event()
-        ev1.record(main)
-        go = gx1.mm(Wo)
-        with torch.cuda.stream(side):
-            side.wait_event(ev)
-            gWf2 = g.t().mm(h)
-            gbf2 = g.sum(0)
-            side.wait_event(ev1)
-            gWf1 = gh.t().mm(x1)
-            gbf1 = gh.sum(0)
-            gWo = gx1.t().mm(o.view(N, D))
-            gbo = gx1.sum(0)
-        # attention, lattice sums, coefficients
-        ga = new(N, H)
-        if ctx.fused_attention:
-            spool = val
-            gqs, gk, gv, gz = new(N, H, hd), new(N, H, hd), new(N, H, hd), new(E, H)
-            go = go.view(N, H, hd)
-            _lib.invoke("cfb200_attn_fused_bwd", 2, dev, p(qs), p(k), p(v), p(a), p(geo.pos_ij), p(geo.tvecs),
-                        p(geo.rvlen), ip(geo.batch), ip(geo.edges), ip(geo.e_start), p(geo.order, torch.int32),
-                        p(geo.counters, torch.int32), N, E,
-                        meta["dist_max"], meta["cutoff"], p(Wd[0]), *((None,) * 6 if plain else
-                                                                      (p(W1[0]), p(W2[0]), p(W3[0]), p(f[0]), p(f[1]), p(f[2]))),
-                        p(geo.pair_list), geo.cache_range, p(o), p(z), p(lse), p(go), p(gqs), p(gk), p(gv),
-                        p(ga), p(gz), 1 if plain else 0)
-            ev3 = torch.cuda.Event()
-            ev3.record(main)
-            with torch.cuda.stream(side):
-                # weight gradients of the value encoding: gW[h] (16 x 256) = sum_i gout[i,h,:]^T spool[i,h,:]
-                side.wait_event(ev3)
-                gW_all = torch.bmm(go.permute(1, 2, 0), spool.permute(1, 0, 2))
-                gW = [gW_all[:, :, 64 * b:64 * (b + 1)].contiguous() for b in range(1 if plain else 4)]
+        gx = torch.empty_like(x)
+        named = dict(zip(WEIGHT_FIELDS, params))
+        sinks = dict(zip(WEIGHT_FIELDS, ctx.sinks))
+        trainable = [f for f in GRAD_FIELDS if named[f] is not None]
+        use_sink = all(sinks[f] is not None for f in trainable)
+        if use_sink:
+            dest = {f: sinks[f] for f in trainable}
         else:
-            gqs, gk, gv, gz, gval = new(N, H, hd), new(N, H, hd), new(N, H, hd), new(E, H), new(E, H, hd)
-            _lib.invoke("cfb200_dpa_bwd", 2, dev, p(qs), p(k), p(v), p(z), p(val), ip(geo.edges), ip(geo.e_start), N, E,
-                        p(o), p(lse), p(go), p(gqs), p(gk), p(gv), p(gz), p(gval))
-            gW = [torch.empty_like(W[0]) for W in (Wd, W1, W2, W3)]
-            lib = _lib.lib()
-            nbytes = int(lib.cfb200_framed_proj_bwd_workspace_bytes(N, E))
-            ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
-            _lib.invoke("cfb200_framed_proj_bwd_cached", 3, dev, p(a), p(geo.pos_ij), p(geo.tvecs), p(geo.rvlen),
-                        ip(geo.batch), ip(geo.edges), ip(geo.e_start), N, E, meta["dist_max"], meta["cutoff"], p(Wd[0]),
-                        p(W1[0]), p(W2[0]), p(W3[0]), p(f[0]), p(f[1]), p(f[2]), p(z), p(gz), p(gval), p(ga), p(gW[0]),
-                        p(gW[1]), p(gW[2]), p(gW[3]), ws.data_ptr(), nbytes, p(geo.pair_list), geo.cache_range)
-        gq, gw = new(N, H, hd), torch.empty_like(w_lat)
-        _lib.invoke("cfb200_gauss_coef_bwd", 1, dev, p(q), p(w_lat), p(gauss_scale), N, meta["lb"], meta["beta"],
-                    meta["scale_real"], p(ga), p(gqs), p(gq), p(gw))
-        # input projections
-        gq2, gk2, gv2 = gq.view(N, D), gk.view(N, D), gv.view(N, D)
-        ev2 = torch.cuda.Event()
-        ev2.record(main)
-        gx = torch.addmm(gx1, gq2, Wq).addmm_(gk2, Wk).addmm_(gv2, Wv)
-        with torch.cuda.stream(side):
-            side.wait_event(ev2)
-            gWq, gWk, gWv = gq2.t().mm(x), gk2.t().mm(x), gv2.t().mm(x)
-            gb_in = torch.cat([gq2.sum(0), gk2.sum(0), gv2.sum(0)])
-            done = torch.cuda.Event()
-            done.record(side)
-        main.wait_event(done)
-        for t in (gWf2, gbf2, gWf1, gbf1, gWo, gbo, gWq, gWk, gWv, gb_in) + (tuple(gW) if ctx.fused_attention else ()):
-            t.record_stream(main)               # allocated on the side stream, consumed on the current one
-        gWa = (None, None, None) if plain else (gW[1].unsqueeze(0), gW[2].unsqueeze(0), gW[3].unsqueeze(0))
-        return (gx, gWq, gWk, gWv, gb_in, gw, None, gWo, gbo, gW[0].unsqueeze(0), *gWa, gWf1, gbf1, gWf2, gbf2, None, None)
+            # one buffer for all gradients of the layer, handed to autograd as views
+            offs, total = {}, 0
+            for f in trainable:
+                offs[f] = total
+                total += _align(named[f].numel())
+            flat = torch.empty(total, dtype=torch.float32, device=dev)
+            dest = {f: flat[offs[f]:offs[f] + named[f].numel()].view(named[f].shape) for f in trainable}
+        Gr = _lib.LayerGrads(*[dest[f].data_ptr() if f in dest else None for f in GRAD_FIELDS])
+        nbytes = int(_lib.lib().cfb200_encoder_layer_workspace_bytes(N, E, desc.d_model, desc.ff_dim, desc.frame_method))
+        ws = geo.workspace(nbytes, dev)
+        _lib.invoke("cfb200_encoder_layer_bwd", 9 + (1 if use_sink else 0), dev, ctypes.byref(desc), ctypes.byref(ctx.W),
+                    ctypes.byref(geo.c), x.data_ptr(), ctypes.byref(ctx.St), g.data_ptr(), gx.data_ptr(),
+                    ctypes.byref(Gr), 1 if use_sink else 0, ws.data_ptr(), ws.numel())
+        if use_sink:
+            grads = [None] * 16
+        else:
+            grads = [dest.get(f) for f in WEIGHT_FIELDS]
+        return (gx, *grads, None, None)
 
 
-def layer_meta(attn):
-    """Scalars of the attention module in the form the Function takes; None if the layer's
-    configuration is outside what the fused path covers."""
+def layer_meta(layer):
+    """Scalars of an encoder layer in the form the Function takes; None if the layer's configuration is
+    outside what the fused path covers."""
+    attn = layer.self_attn
     P = attn.params
-    if P.domain != "real" or P.frame_method not in ("max", "weighted_pca", "no") or P.gauss_state != "q" or \
-            not P.normalize_gauss:
+    if P.domain != "real" or P.frame_method not in FRAME_METHODS or P.gauss_state != "q" or not P.normalize_gauss:
         return None
     if attn.in_proj_bias is None or attn.pe_dist_proj is None or attn.dropout != 0.0:
         return None
     if (attn.proj_angle1 is None) != (P.frame_method == "no"):
         return None                      # angle weights exactly when there are frames
     if attn.kdim != attn.embed_dim or attn.vdim != attn.embed_dim:
+        return None
+    if layer.linear1.bias is None or layer.linear2.bias is None or layer.linear1.out_features % 4:
         return None
     dist_max = P.value_pe_dist_max
     if dist_max < 0:
@@ -230,5 +242,16 @@ def layer_meta(attn):
         cutoff = float(P.scale_real * P.gauss_lb_real ** (-0.5) * P.adaptive_cutoff_sigma)
     else:
         cutoff = 0.0
-    return dict(frame_method=P.frame_method, H=attn.num_heads, hd=attn.head_dim, lb=float(P.gauss_lb_real),
-                beta=float(P.positive_func_beta), scale_real=float(P.scale_real), dist_max=float(dist_max), cutoff=cutoff)
+    return dict(frame_method=P.frame_method, H=attn.num_heads, hd=attn.head_dim, F=layer.linear1.out_features,
+                lb=float(P.gauss_lb_real), beta=float(P.positive_func_beta), scale_real=float(P.scale_real),
+                dist_max=float(dist_max), cutoff=cutoff)
+
+
+def layer_parameters(layer):
+    """The layer's parameters in the Function's order (WEIGHT_FIELDS)."""
+    attn = layer.self_attn
+    pe = lambda p: None if p is None else p
+    return (attn.q_proj_weight, attn.k_proj_weight, attn.v_proj_weight, attn.in_proj_bias, attn.lattice_pos_weights,
+            attn.gauss_scale, attn.out_proj.weight, attn.out_proj.bias, pe(attn.pe_dist_proj), pe(attn.proj_angle1),
+            pe(attn.proj_angle2), pe(attn.proj_angle3), layer.linear1.weight, layer.linear1.bias, layer.linear2.weight,
+            layer.linear2.bias)

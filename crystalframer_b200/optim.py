@@ -3,36 +3,55 @@
 The reference trains with torch's AdamW and Lightning's ``gradient_clip_val`` (train.py, params "adamw" /
 "clip_norm"), i.e. a per-tensor norm, a per-tensor scale and a multi-tensor update for the 60 parameter
 tensors of the 4-layer model -- about a millisecond of host work and a dozen launches per step.  Here the
-parameters are views into one flat buffer, the gradients are gathered into another with one copy, and
-``cfb200_adamw_clip_step`` does norm, clip and update in two launches.  With several ranks the gradient
-buffer is what is all-reduced, so nothing is flattened or copied back."""
+parameters are views into one flat buffer, every parameter owns a slice of one flat gradient buffer (its
+"gradient sink"), and ``cfb200_adamw_clip_step`` does norm, clip and update in two launches.  The one-call
+encoder layers add their weight gradients straight into the sinks (fused_layer.py); gradients that autograd
+delivers in ``p.grad`` (embedding, output head) are added with one multi-tensor call.  With several ranks the
+flat gradient buffer is what is all-reduced, so nothing is flattened or copied back."""
 import torch
 import torch.distributed as dist
 
 from . import _lib
 
+ALIGN = 64          # floats; every parameter starts on a 256-byte boundary of the flat buffers
+
 
 class FlatAdamW:
     """``FlatAdamW(decay_params, no_decay_params, lr, betas, eps, weight_decay, max_norm)``; ``step()`` takes
-    the parameters' ``.grad``.  Same arithmetic as ``clip_grad_norm_(params, max_norm)`` followed by
-    ``torch.optim.AdamW.step()`` with ``weight_decay`` on ``decay_params`` only."""
+    the gradient sinks plus the parameters' ``.grad``.  Same arithmetic as ``clip_grad_norm_(params, max_norm)``
+    followed by ``torch.optim.AdamW.step()`` with ``weight_decay`` on ``decay_params`` only.  Both arguments may
+    be any iterables (generators included); a parameter may appear only once."""
 
     def __init__(self, decay_params, no_decay_params=(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2,
-                 max_norm=0.0):
-        self.params = [p for p in list(decay_params) + list(no_decay_params) if p.requires_grad]
+                 max_norm=0.0, grad_sink=True):
+        decay = [p for p in decay_params if p.requires_grad]
+        no_decay = [p for p in no_decay_params if p.requires_grad]
+        self.params = decay + no_decay
+        if len({id(p) for p in self.params}) != len(self.params):
+            raise ValueError("FlatAdamW: a parameter appears more than once (tied weights or overlapping groups)")
         if not self.params or not all(p.is_cuda and p.dtype == torch.float32 for p in self.params):
             raise RuntimeError("FlatAdamW needs fp32 CUDA parameters (there is no CPU path)")
         dev = self.params[0].device
-        self.decay_end = sum(p.numel() for p in decay_params if p.requires_grad)
-        self.n = sum(p.numel() for p in self.params)
-        self.flat = torch.empty(self.n, device=dev, dtype=torch.float32)
-        off = 0
-        for p in self.params:                       # parameters become views of the flat buffer
-            k = p.numel()
-            self.flat[off:off + k].copy_(p.data.reshape(-1))
-            p.data = self.flat[off:off + k].view(p.shape)
-            off += k
+        offsets, off = [], 0
+        for i, p in enumerate(self.params):
+            if i == len(decay):
+                self.decay_end = off                 # padding between parameters holds zeros and stays zero
+            offsets.append(off)
+            off += (p.numel() + ALIGN - 1) // ALIGN * ALIGN
+        if len(no_decay) == 0:
+            self.decay_end = off
+        self.n = off
+        self.flat = torch.zeros(self.n, device=dev, dtype=torch.float32)
         self.grad = torch.zeros(self.n, device=dev, dtype=torch.float32)
+        self.sinks = []
+        for p, o in zip(self.params, offsets):       # parameters become views of the flat buffer
+            k = p.numel()
+            self.flat[o:o + k].copy_(p.data.reshape(-1))
+            p.data = self.flat[o:o + k].view(p.shape)
+            sink = self.grad[o:o + k].view(p.shape)
+            self.sinks.append(sink)
+            if grad_sink:
+                p._cf_grad_sink = sink
         self.exp_avg = torch.zeros_like(self.flat)
         self.exp_avg_sq = torch.zeros_like(self.flat)
         self.scratch = torch.zeros(256, device=dev, dtype=torch.float32)
@@ -41,14 +60,22 @@ class FlatAdamW:
         self.steps = 0
 
     def zero_grad(self, set_to_none=True):
+        """Clears the flat gradient buffer (one launch) and drops the parameters' ``.grad``."""
+        self.grad.zero_()
         for p in self.params:
             p.grad = None
 
     def gather_grads(self):
-        """Copies every parameter's gradient into the flat gradient buffer (zeros where there is none)."""
-        views = [p.grad.reshape(-1) if p.grad is not None else torch.zeros(p.numel(), device=self.flat.device)
-                 for p in self.params]
-        torch.cat(views, out=self.grad)
+        """Adds every gradient that autograd left in ``p.grad`` to the parameter's slice of the flat buffer (one
+        multi-tensor call) and drops it; returns the flat gradient buffer."""
+        dst, src = [], []
+        for p, s in zip(self.params, self.sinks):
+            if p.grad is not None:
+                dst.append(s)
+                src.append(p.grad)
+                p.grad = None
+        if dst:
+            torch._foreach_add_(dst, src)
         return self.grad
 
     def step(self, world_sum=False):

@@ -313,6 +313,103 @@ int cfb200_adamw_clip_step(float* params, const float* grads, float* exp_avg, fl
                            float weight_decay, float max_norm, double bias_correction1,
                            double bias_correction2, float* scratch, float* grad_norm, void* stream);
 
+/* ---- one host call per batch and per encoder layer -------------------------------------------
+ *
+ * Replaces get_edge_index and compute_lattice_distances_for_cuda
+ * (models/indexed_latticeformer_encoder.py:15-32, :175-245) and the reciprocal-vector lengths of
+ * models/indexed_lattice_multi_head_attention_cuda.py:539 with one call: from raw positions pos (N,3),
+ * lattice vectors tvecs (B,3,3) and sizes (B) it produces the pair list (edges (2,E), e_start (N+1),
+ * batch (N), crystal_start (B+1)), pos_ij (E,3), rvecs (B,3,3) (optional), rvlen (B,3), vcell (B)
+ * (optional), the per-pair geometry of cfb200_pair_cache for lattice ranges (range)^3 (pair_cache (E,4),
+ * pair_list (E,5,128); either may be NULL, range 0 skips both) and `order` (N) int32, the work-queue order
+ * of cfb200_attn_fused_*: atoms of the crystals with the most attention work first.  workspace: at least
+ * cfb200_batch_geometry_workspace_bytes(B) bytes. */
+int64_t cfb200_batch_geometry_workspace_bytes(int64_t B);
+int cfb200_batch_geometry(const float* pos, const float* tvecs, const int64_t* sizes, int64_t B, int64_t N,
+                          int64_t E, int range, int64_t* edges, int64_t* e_start, int64_t* batch,
+                          int64_t* crystal_start, float* pos_ij, float* rvecs, float* rvlen, float* vcell,
+                          float* pair_cache, float* pair_list, int32_t* order, void* workspace,
+                          int64_t workspace_bytes, void* stream);
+
+/* Parameters of one encoder layer, laid out as the reference module stores them
+ * (models/indexed_lattice_multi_head_attention_cuda.py:1078-1160, models/indexed_latticeformer_encoder.py:783-790):
+ * q/k/v_proj (D,D), in_bias (3D), lattice_pos (D), gauss_scale (2) or NULL, out_proj (D,D), out_bias (D),
+ * pe_dist and pe_ang1..3 (H,16,64) (pe_ang*: NULL without frames), ff1 (F,D), ff1_bias (F), ff2 (D,F),
+ * ff2_bias (D).  Every pointer must be 16-byte aligned. */
+typedef struct cfb200_layer_weights {
+    const float *q_proj, *k_proj, *v_proj, *in_bias, *lattice_pos, *gauss_scale, *out_proj, *out_bias;
+    const float *pe_dist, *pe_ang1, *pe_ang2, *pe_ang3, *ff1, *ff1_bias, *ff2, *ff2_bias;
+} cfb200_layer_weights;
+
+/* Destinations of the gradients, same shapes (no gauss_scale: it is not trained). */
+typedef struct cfb200_layer_grads {
+    float *q_proj, *k_proj, *v_proj, *in_bias, *lattice_pos, *out_proj, *out_bias;
+    float *pe_dist, *pe_ang1, *pe_ang2, *pe_ang3, *ff1, *ff1_bias, *ff2, *ff2_bias;
+} cfb200_layer_grads;
+
+/* Batch tensors shared by all layers (outputs of cfb200_batch_geometry); counters: 64 int32 of scratch. */
+typedef struct cfb200_geometry {
+    const float *pos_ij, *tvecs, *rvlen;
+    const int64_t *batch, *edges, *e_start;
+    const int32_t* order;
+    int32_t* counters;
+    const float *pair_cache, *pair_list;
+    int64_t N, E;
+    int32_t cache_range;
+} cfb200_geometry;
+
+/* Activations a layer's forward leaves for its backward (caller-allocated): q, q_scaled, k, v, attn, x1
+ * (N,D); a, lse (N,H); frames (3,N,H,3) (NULL for frame_method 0); z (E,H); spool (N,H,256); h (N,F). */
+typedef struct cfb200_layer_state {
+    float *q, *q_scaled, *k, *v, *a, *frames, *z, *spool, *attn, *lse, *x1, *h;
+} cfb200_layer_state;
+
+/* frame_method: 0 = none (plain Crystalformer encoding), 1 = max frames, 2 = weighted-PCA frames.
+ * seed1, seed2: noise seeds of the two max-frame axes, or noise seed and sign seed of the weighted-PCA frames. */
+typedef struct cfb200_layer_desc {
+    int32_t d_model, ff_dim, frame_method;
+    float gauss_lb, beta, scale_real, dist_max, cutoff_radius;
+    uint64_t seed1, seed2;
+} cfb200_layer_desc;
+
+/* One encoder layer (no layer norm, no dropout, ReLU; the structure of the reference's default
+ * configuration), forward and backward, every kernel enqueued by one call.  Replaces
+ * CrystalformerEncoderLayerCUDA.forward (models/indexed_latticeformer_encoder.py:848-890) with
+ * crystalformer_multi_head_attention_forward_cuda inside it
+ * (models/indexed_lattice_multi_head_attention_cuda.py:737-996) and the autograd graph behind them:
+ *   q,k,v = x W^T + b;  a, q_scaled = coefficients(q);  frames;  attn = fused lattice-sum attention;
+ *   x1 = x + attn Wo^T + bo;  h = relu(x1 Wf1^T + bf1);  x_out = x1 + h Wf2^T + bf2.
+ * x, x_out, g_out, g_x: (N,D).  The backward writes every gradient of `grads` (adds to it when
+ * accumulate != 0; sums run in a fixed order).  workspace: cfb200_encoder_layer_workspace_bytes bytes. */
+int64_t cfb200_encoder_layer_workspace_bytes(int64_t N, int64_t E, int d_model, int ff_dim, int frame_method);
+int cfb200_encoder_layer_fwd(const cfb200_layer_desc* desc /* host */, const cfb200_layer_weights* weights /* host */,
+                             const cfb200_geometry* geometry /* host */, const float* x,
+                             cfb200_layer_state* state /* host */, float* x_out, void* workspace,
+                             int64_t workspace_bytes, void* stream);
+int cfb200_encoder_layer_bwd(const cfb200_layer_desc* desc /* host */, const cfb200_layer_weights* weights /* host */,
+                             const cfb200_geometry* geometry /* host */, const float* x,
+                             const cfb200_layer_state* state /* host */, const float* g_out, float* g_x,
+                             const cfb200_layer_grads* grads /* host */, int accumulate, void* workspace,
+                             int64_t workspace_bytes, void* stream);
+
+/* Measurement aid with no counterpart in the reference: between cfb200_timing_begin() and
+ * cfb200_timing_end() every stage of cfb200_batch_geometry and cfb200_encoder_layer_fwd / _bwd is bracketed by
+ * CUDA events on the stream it runs on.  cfb200_timing_end waits for them and returns, per stage
+ * CFB200_TM_*, the summed milliseconds and the number of brackets (arrays of CFB200_TM_STAGES entries, host).
+ * For one host thread; off by default, and then no events are created. */
+#define CFB200_TM_GEOMETRY 0       /* cfb200_batch_geometry                                          */
+#define CFB200_TM_LINEAR_FWD 1     /* input projections; output projection + feed-forward block      */
+#define CFB200_TM_COEF 2           /* Gaussian coefficients, forward and backward                    */
+#define CFB200_TM_FRAMES 3         /* max or weighted-PCA frames                                     */
+#define CFB200_TM_ATTN_FWD 4       /* fused lattice-sum attention, forward kernel                    */
+#define CFB200_TM_LINEAR_BWD 5     /* data gradients of the dense layers                             */
+#define CFB200_TM_ATTN_BWD 6       /* fused lattice-sum attention, backward kernel                   */
+#define CFB200_TM_ATTN_BWD_COLS 7  /* column pass of the attention backward (gk, gv)                 */
+#define CFB200_TM_WGRAD 8          /* weight and bias gradients of the layer                         */
+#define CFB200_TM_STAGES 9
+int cfb200_timing_begin(void);
+int cfb200_timing_end(float* ms_by_stage /* host */, int32_t* calls_by_stage /* host */);
+
 /* Measurement aid with no counterpart in the reference: every thread of `blocks` x 256 threads
  * runs `iters` rounds of 8 independent chains of fused multiply-adds (kind 0) or ex2.approx
  * (kind 1) and writes one float to sink (blocks*256 floats).  Timed by the caller, it gives the

@@ -21,8 +21,12 @@ from . import oracle as O
 def oracle_config(model):
     p = model.encoder.lattice_params
     attn = model.encoder.layers[0].self_attn
+    plain = p.frame_method == "no"
+    # plain Crystalformer encoding (models/kernels/real_enc_proj_fwd.cu:127-134): every distance Gaussian
+    # is evaluated (a window wider than the basis) and there is no angle basis
     return O.Config(H=attn.num_heads, head_dim=attn.head_dim, D_dist=p.value_pe_dist_real,
-                    D_ang=p.value_pe_angle_real, lattice_range=p.lattice_range,
+                    D_ang=0 if plain else p.value_pe_angle_real, cut_sigma=32 if plain else 4,
+                    lattice_range=p.lattice_range,
                     minimum_range=p.lattice_range if p.minimum_range else 0, cos_abs=p.cos_abs,
                     dist_max=(-p.value_pe_dist_max) * attn.params.scale_real if p.value_pe_dist_max < 0 else p.value_pe_dist_max,
                     wscale_dist=p.value_pe_dist_wscale, wscale_ang=p.value_pe_angle_wscale,
@@ -50,7 +54,21 @@ def coefficients(attn, q):
     return ((1.0 - lb) * F.elu(alpha * (beta / (1.0 - lb))) + 1.0) * (-0.5 * P.scale_real ** -2)
 
 
-def attention_layer(attn, x, geo, cfg):
+def draw_frame_seeds(frame_method):
+    """The draws the library's frame construction takes from the global generators, in its order
+    (crystalframer_b200/cuda_funcs/max_frame.py): numpy for the noise seeds, torch for the row signs."""
+    draw = lambda: int(np.random.randint(np.iinfo(np.int64).min, np.iinfo(np.int64).max, dtype=np.int64)) & (2 ** 64 - 1)
+    if frame_method == "weighted_pca":
+        draw()
+        seed_noise = draw()
+        return seed_noise, int(torch.randint(0, 2 ** 62, (1,)).item())
+    return draw(), draw()
+
+
+def attention_layer(attn, x, geo, cfg, frames=None):
+    """One attention block.  ``frames``: (3,N,H,3) tensor to use instead of constructing the frames here
+    (for comparisons downstream of identical frames, e.g. weighted-PCA frames, whose eigenvectors are
+    not comparable across implementations where eigenvalues nearly coincide)."""
     N = x.shape[0]
     H, hd = attn.num_heads, attn.head_dim
     bq, bk, bv = attn.in_proj_bias.split([attn.kdim, attn.kdim, attn.vdim])
@@ -60,9 +78,25 @@ def attention_layer(attn, x, geo, cfg):
     a = coefficients(attn, q)
     cutoff = attn.params.adaptive_cutoff_sigma
     qs = q / math.sqrt(hd)
-    with torch.no_grad():
-        f1, f2, f3 = OF.max_frames(qs.detach().contiguous(), k.detach().contiguous(), a.detach().contiguous(),
-                                   geo["pos_ij"], geo["tvecs"], geo["batch"], geo["edges"], geo["rvlen"], cutoff)
+    method = attn.params.frame_method
+    if method == "no":
+        f1 = f2 = f3 = None
+    elif frames is not None:
+        f1, f2, f3 = frames[0], frames[1], frames[2]
+    elif method == "max":
+        with torch.no_grad():
+            f1, f2, f3 = OF.max_frames(qs.detach().contiguous(), k.detach().contiguous(), a.detach().contiguous(),
+                                       geo["pos_ij"], geo["tvecs"], geo["batch"], geo["edges"], geo["rvlen"], cutoff)
+    elif method == "weighted_pca":
+        seed_noise, seed_sign = draw_frame_seeds(method)
+        npy = lambda t: t.detach().contiguous().numpy()
+        e_start = OF._e_start(geo["edges"], N)
+        fr, _, _ = O.weighted_pca_frames(cfg, npy(qs), npy(k), npy(a), npy(geo["pos_ij"]), npy(geo["tvecs"]),
+                                         npy(geo["rvlen"]), npy(geo["batch"]), npy(geo["edges"]), npy(e_start),
+                                         seed_noise, seed_sign)
+        f1, f2, f3 = (torch.from_numpy(fr[x]) for x in range(3))
+    else:
+        raise NotImplementedError(method)
     z, val = OF.FramedProj.apply(a, geo["pos_ij"], geo["tvecs"], geo["batch"], geo["edges"], geo["rvlen"], cutoff,
                                  cfg.dist_max, attn.pe_dist_proj, attn.proj_angle1, attn.proj_angle2,
                                  attn.proj_angle3, f1, f2, f3)
@@ -70,18 +104,22 @@ def attention_layer(attn, x, geo, cfg):
     return F.linear(out.reshape(N, H * hd), attn.out_proj.weight, attn.out_proj.bias)
 
 
-def forward(model, batch, backend=None):
-    """``batch``: crystalframer_b200.synth.CrystalBatch (numpy).  Returns the (B, 1) prediction."""
+def forward(model, batch, backend=None, frames=None):
+    """``batch``: crystalframer_b200.synth.CrystalBatch (numpy).  Returns the (B, 1) prediction.
+    ``frames``: optional list with one (3,N,H,3) tensor per layer to use instead of constructing them.
+    With ``backend="reference_cuda"`` the model's parameters must live on the GPU; the reference's own CUDA
+    kernels then run there, with the reference's host glue between them."""
     cfg = oracle_config(model)
     OF.configure(cfg, backend)
     g = O.lattice_geometry(batch.pos, batch.trans_vec, batch.sizes)
-    t = lambda arr: torch.from_numpy(np.ascontiguousarray(arr))
+    dev = next(model.parameters()).device
+    t = lambda arr: torch.from_numpy(np.ascontiguousarray(arr)).to(dev)
     geo = dict(pos_ij=t(g["pos_ij"]), tvecs=t(batch.trans_vec), batch=t(g["batch"]), edges=t(g["edges"]),
                rvlen=t(g["rvlen"]))
     sizes = t(batch.sizes)
     x = model.input_embeddings(t(batch.x))
-    for layer in model.encoder.layers:
-        x = layer.norm1(x + attention_layer(layer.self_attn, x, geo, cfg))
+    for li, layer in enumerate(model.encoder.layers):
+        x = layer.norm1(x + attention_layer(layer.self_attn, x, geo, cfg, None if frames is None else frames[li]))
         x = layer.norm2(x + layer.linear2(layer.activation(layer.linear1(x))))
     if model.encoder.norm is not None:
         x = model.encoder.norm(x)

@@ -16,11 +16,19 @@ _state = {"backend": None, "rk": None, "cfg": O.Config()}
 
 
 def configure(cfg: O.Config, backend=None):
+    """``backend``: "port" (C restatement, CPU), "reference" (the reference's kernels built for the CPU) or
+    "reference_cuda" (the reference's kernels built with nvcc, tensors on the current GPU: the
+    reference-on-the-same-GPU baseline)."""
     if backend is None:
         backend = "reference" if R.available("cpu") else "port"
-    _state["backend"] = backend
     _state["cfg"] = cfg
-    _state["rk"] = R.RefKernels("cpu") if backend == "reference" else None
+    _state["rk"] = None
+    if backend == "reference":
+        _state["rk"] = R.RefKernels("cpu")
+    elif backend == "reference_cuda":
+        _state["rk"] = R.RefKernels("cuda")
+        backend = "reference"            # same host glue; only the device of the tensors differs
+    _state["backend"] = backend
     if backend == "reference":
         c = _state["rk"].consts
         assert (c["HEAD_NUM"], c["VPE_DIM"], c["ANGLE_ENC_DIM"], c["LATTICE_RANGE"]) == \
@@ -124,7 +132,14 @@ class Attention(torch.autograd.Function):
 class Mean(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, sizes):
-        if _state["backend"] == "reference":
+        if x.is_cuda:
+            # the reference's pooling kernel has no nvcc build (it calls an unqualified host template);
+            # the same per-crystal mean with torch operations
+            batch = torch.repeat_interleave(torch.arange(len(sizes), device=x.device), sizes)
+            out = torch.zeros((len(sizes),) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+            out.index_add_(0, batch, x.detach())
+            out = out / sizes[:, None].to(x.dtype)
+        elif _state["backend"] == "reference":
             out = _state["rk"].mean_fwd(x.detach().contiguous(), sizes)
         else:
             out = torch.from_numpy(O.mean_fwd(_np(x), _np(sizes)))
@@ -134,5 +149,5 @@ class Mean(torch.autograd.Function):
     @staticmethod
     def backward(ctx, go):
         sizes, = ctx.saved_tensors
-        batch = torch.repeat_interleave(torch.arange(len(sizes)), sizes)
+        batch = torch.repeat_interleave(torch.arange(len(sizes), device=sizes.device), sizes)
         return (go / sizes[:, None].float())[batch], None

@@ -30,6 +30,30 @@ def timed(fn, iters):
     return e0.elapsed_time(e1) / iters, out
 
 
+def reference_operator_ms(I, iters=3):
+    """CUDA-event milliseconds of the reference kernels' launch sequence for one forward + backward of the
+    isolated attention operator on the inputs ``I`` (crystalframer_b200.opbench.make_inputs): first and second
+    frame axis, lattice sums + value encoding forward, attention forward, attention backward, lattice sums backward."""
+    rk = R.RefKernels("cuda")
+    a, pos, tv, batch, edges, rv = I["a"], I["pos_ij"], I["tv"], I["batch"], I["edges"], I["rvlen"]
+    qs, k, v = (I["q"] / 4.0).contiguous(), I["k"], I["v"]
+    Wd = I["W"][0].contiguous()
+    Ws = torch.stack(I["W"][1:]).contiguous()
+    asig = R.angle_sigma(4.0, 64)
+    res = {}
+    res["frame1"], (f1, _) = timed(lambda: rk.frame1(qs, k, a, pos, tv, batch, edges, rv, -3.5), iters)
+    res["frame2"], (f2m, _) = timed(lambda: rk.frame2(qs, k, a, pos, tv, batch, edges, rv, -3.5, f1), iters)
+    f2, f3 = rk.complete(f1, f2m)
+    frames = torch.stack([f1, f2, f3]).contiguous()
+    res["framed_proj_fwd"], (z, val) = timed(lambda: rk.framed_proj_fwd(a, pos, tv, batch, edges, 14.0, 1.0, Wd, Ws, frames,
+                                                                        asig, 1.0, 1.0, rv, -3.5), iters)
+    res["dpa_fwd"], (out, prob, es) = timed(lambda: rk.dpa_fwd(qs, k, v, z, val, edges), iters)
+    res["dpa_bwd"], (gq, gk, gv, gz, gb) = timed(lambda: rk.dpa_bwd(qs, k, v, z, val, batch, edges, es, prob, out, I["go"]), iters)
+    res["framed_proj_bwd"], _ = timed(lambda: rk.framed_proj_bwd(a, pos, tv, batch, edges, 14.0, 1.0, Wd, Ws, frames, asig, 1.0,
+                                                                 1.0, rv, -3.5, z, gz, gb), iters)
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="cfg2")

@@ -1,0 +1,222 @@
+"""The one-call batch preparation and encoder layer (cfb200_batch_geometry, cfb200_encoder_layer_fwd / _bwd)
+and the flat optimiser with gradient sinks.
+
+* batch geometry: integer outputs bit-exact against the oracle's restatement of the reference host code,
+  floats to float32 rounding, work-queue order against the stable sort it stands for;
+* the layer: outputs and every gradient against the operator-by-operator path of the same module
+  (reference-signature Functions + torch linear layers), for the three frame methods, at odd sizes;
+  the comparison with the CPU oracle at model level is tests/test_gpu_parity.py::test_whole_model_against_cpu_oracle;
+* gradient sinks: a training step through FlatAdamW equals clip_grad_norm_ + torch AdamW on autograd's gradients;
+  a batch split over two shards and summed equals the whole batch.
+"""
+import copy
+
+import numpy as np
+import pytest
+import torch
+
+from parity_util import close, cuda, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+def test_batch_geometry_against_oracle():
+    dev = cuda()
+    from crystalframer_b200 import cuda_funcs as F, fused_layer, synth
+    from oracle import oracle as O
+    F.compile_kernels(2, 8, 16, 64, 64, 16, True, 0, 1.0, 4.0, 1.0, 1.0, 0.0)
+    for workload, nc in (("cfg1", None), ("cfg2", 64), ("cfg4", 2)):
+        b = synth.make_workload(workload, num_crystals=nc)
+        want = O.lattice_geometry(b.pos, b.trans_vec, b.sizes)
+        pos, tv, sizes = to_dev(b.pos, dev), to_dev(b.trans_vec, dev), to_dev(b.sizes, dev)
+        g = fused_layer.LayerGeometry.from_raw(pos, tv, sizes, b.num_atoms, b.num_pairs, -3.5)
+        assert torch.equal(g.edges.cpu(), torch.from_numpy(want["edges"]))
+        assert torch.equal(g.e_start.cpu(), torch.from_numpy(want["e_start"]))
+        assert torch.equal(g.batch.cpu(), torch.from_numpy(want["batch"]))
+        # pos_ij is one float subtraction per component: identical on any IEEE machine
+        assert np.array_equal(g.pos_ij.cpu().numpy(), want["pos_ij"])
+        close("rvlen", g.rvlen.cpu().numpy(), want["rvlen"], 4e-7, 0.0)
+        # work-queue order: stable descending sort of the atoms by their crystal's key
+        vol = np.abs(np.linalg.det(b.trans_vec.astype(np.float64)))
+        key = (b.sizes * (7.0 + np.clip(2145.0 / np.maximum(vol, 1e-6), 1.0, 125.0))).astype(np.float32)
+        N = b.num_atoms
+        from crystalframer_b200 import _lib
+        # the library's order lives inside the geometry's float buffer; locate it through its pointer
+        fbuf = g._keep[1]
+        off = (g.c.order - fbuf.data_ptr()) // 4
+        got = fbuf[off:off + N].view(torch.int32).cpu().numpy()
+        assert sorted(got.tolist()) == list(range(N))
+        k_atom = key[want["batch"]]
+        assert (np.diff(k_atom[got]) <= 1e-3 * k_atom.max()).all()           # non-increasing up to float rounding of the key
+        same_key = np.diff(k_atom[got]) == 0
+        assert (np.diff(got)[same_key] > 0).all()                             # stable within equal keys
+        # per-pair geometry equals what cfb200_pair_cache gives on the same inputs
+        cache = torch.empty(b.num_pairs, 4, device=dev)
+        plist = torch.empty(b.num_pairs, 5, 128, device=dev)
+        _lib.invoke("cfb200_pair_cache", 2, dev, _lib.ptr(g.pos_ij.contiguous()), _lib.ptr(tv), _lib.iptr(g.batch.contiguous()),
+                    _lib.iptr(g.edges.contiguous()), N, b.num_pairs, 2, _lib.ptr(cache), _lib.ptr(plist))
+        off_pc = (g.c.pair_cache - fbuf.data_ptr()) // 4
+        assert torch.equal(fbuf[off_pc:off_pc + 4 * b.num_pairs].view(-1, 4).view(torch.int32), cache.view(torch.int32))
+        assert torch.equal(g._keep[2].view(torch.int32), plist.view(torch.int32))
+        assert _lib.read_status(dev) == 0
+
+
+@pytest.mark.parametrize("frame_method,workload,nc", [("max", "cfg2", 16), ("max", "cfg1", None), ("no", "cfg2", 16),
+                                                      ("weighted_pca", "cfg1", None)])
+def test_one_call_layer_matches_operator_path(frame_method, workload, nc):
+    """Same model, same batch: operator by operator (reference-signature Functions, torch linear layers, autograd)
+    against one library call per layer with hand-written backward."""
+    dev = cuda()
+    from crystalframer_b200 import _lib, data, encoder, fused_layer, synth
+    from crystalframer_b200.latticeformer import Latticeformer, ModelParams
+    torch.manual_seed(3)
+    mp = ModelParams(num_layers=2, symm_break_noise=0.0, frame_method=frame_method,
+                     value_pe_angle_real=0 if frame_method == "no" else 64)
+    model = Latticeformer(mp).to(dev).train()
+    b = synth.make_workload(workload, num_crystals=nc)
+    y = np.random.default_rng(1).normal(size=(len(b.sizes), 1)).astype(np.float32)
+    tb = data.host_batch(b, y, pinned=False).to(dev, non_blocking=False)
+    with torch.no_grad():
+        model(tb)                                   # measures gauss_scale, after which the one-call path is eligible
+    results = []
+    for fused in (False, True):
+        encoder.FUSED_LAYER = fused
+        model.zero_grad(set_to_none=True)
+        np.random.seed(11)
+        torch.manual_seed(11)                       # frame seeds are drawn from the global generators
+        calls = []
+        orig = _lib.invoke
+        _lib.invoke = lambda name, *a, **k: (calls.append(name), orig(name, *a, **k))[1]
+        try:
+            out = model(tb)
+            (out - tb.y).abs().mean().backward()
+        finally:
+            _lib.invoke = orig
+        assert ("cfb200_encoder_layer_fwd" in calls) == fused and ("cfb200_encoder_layer_bwd" in calls) == fused
+        results.append((out.detach().clone(), {n: p.grad.detach().clone() for n, p in model.named_parameters() if p.grad is not None}))
+    encoder.FUSED_LAYER = True
+    (o0, g0), (o1, g1) = results
+    assert torch.allclose(o0, o1, rtol=1e-5, atol=1e-6), float((o0 - o1).abs().max())
+    assert set(g0) == set(g1)
+    for n in g0:
+        scale = float(g0[n].abs().max()) + 1e-12
+        assert float((g0[n] - g1[n]).abs().max()) <= 1e-4 * scale + 1e-9, (n, float((g0[n] - g1[n]).abs().max()), scale)
+    assert _lib.read_status(dev) == 0
+
+
+def _step_models(dev, sink):
+    from crystalframer_b200 import data, synth
+    from crystalframer_b200.latticeformer import Latticeformer, ModelParams
+    from crystalframer_b200.optim import FlatAdamW
+    torch.manual_seed(4)
+    ref = Latticeformer(ModelParams(num_layers=2, symm_break_noise=0.0)).to(dev).train()
+    ours = copy.deepcopy(ref)
+    b = synth.make_workload("cfg2", num_crystals=24)
+    y = np.random.default_rng(2).normal(size=(len(b.sizes), 1)).astype(np.float32)
+    tb = data.host_batch(b, y, pinned=False).to(dev, non_blocking=False)
+    with torch.no_grad():
+        ref(tb)
+    for lr, lo in zip(ref.encoder.layers, ours.encoder.layers):
+        with torch.no_grad():
+            lo.self_attn.gauss_scale.copy_(lr.self_attn.gauss_scale)
+    split = lambda m: ([p for n, p in m.named_parameters() if p.requires_grad and not n.endswith("bias")],
+                       [p for n, p in m.named_parameters() if p.requires_grad and n.endswith("bias")])
+    d, nd = split(ref)
+    opt_ref = torch.optim.AdamW([{"params": d, "weight_decay": 1e-2}, {"params": nd, "weight_decay": 0.0}], lr=5e-4,
+                                betas=(0.9, 0.98))
+    d2, nd2 = split(ours)
+    opt = FlatAdamW(iter(d2), iter(nd2), lr=5e-4, betas=(0.9, 0.98), eps=1e-8, weight_decay=1e-2, max_norm=1.0, grad_sink=sink)
+    return ref, ours, opt_ref, opt, b, y, tb
+
+
+@pytest.mark.parametrize("sink", [True, False])
+def test_training_step_with_gradient_sinks(sink):
+    """Three training steps: autograd gradients + clip_grad_norm_ + torch AdamW against the one-call layers adding
+    their weight gradients into FlatAdamW's flat buffer.  The parameter groups are passed as iterators."""
+    dev = cuda()
+    from crystalframer_b200 import encoder
+    ref, ours, opt_ref, opt, b, y, tb = _step_models(dev, sink)
+    for step in range(3):
+        np.random.seed(20 + step)
+        encoder.FUSED_LAYER = False
+        opt_ref.zero_grad(set_to_none=True)
+        (ref(tb) - tb.y).abs().mean().backward()
+        norm_ref = torch.nn.utils.clip_grad_norm_(list(ref.parameters()), 1.0)
+        opt_ref.step()
+        np.random.seed(20 + step)
+        encoder.FUSED_LAYER = True
+        opt.zero_grad()
+        (ours(tb) - tb.y).abs().mean().backward()
+        if sink:
+            layer_w = ours.encoder.layers[0].linear1.weight
+            assert layer_w.grad is None and float(layer_w._cf_grad_sink.abs().max()) > 0.0
+        # gradients first: the flat buffer against autograd's gradients of the operator path
+        opt.gather_grads()
+        by_param = {id(p): s_ for p, s_ in zip(opt.params, opt.sinks)}
+        for (n, a), c in zip(ref.named_parameters(), ours.parameters()):
+            if a.grad is None:
+                continue
+            scale = float(a.grad.abs().max()) + 1e-12
+            err = float((by_param[id(c)] - a.grad).abs().max())
+            assert err <= 1e-4 * scale + 1e-9, (step, n, err, scale)
+        opt.step()
+        assert abs(float(opt.grad_norm) - float(norm_ref)) <= 1e-4 * max(1.0, float(norm_ref))
+        # Adam divides by the root of the squared gradient: an entry whose gradient is at rounding level may move
+        # by up to the learning rate in either implementation, so a few entries may differ by that much
+        for (n, a), c in zip(ref.named_parameters(), ours.parameters()):
+            close(f"step {step} {n}", c.detach().cpu().numpy(), a.detach().cpu().numpy(), 1e-4, 2e-6, frac_ok=2e-3)
+            assert float((c - a).abs().max()) <= 2.5 * 5e-4 * (step + 1)
+        with torch.no_grad():                       # continue from identical weights
+            for a, c in zip(ref.parameters(), ours.parameters()):
+                c.copy_(a)
+
+
+def test_weight_decay_applies_with_iterator_groups():
+    """With zero gradients AdamW only shrinks the decayed parameters; groups given as generators must not
+    silently lose their weight decay."""
+    dev = cuda()
+    from crystalframer_b200.optim import FlatAdamW
+    torch.manual_seed(0)
+    m = torch.nn.Linear(16, 8).to(dev)
+    w0, b0 = m.weight.detach().clone(), m.bias.detach().clone()
+    opt = FlatAdamW((p for n, p in m.named_parameters() if n == "weight"), (p for n, p in m.named_parameters() if n == "bias"),
+                    lr=1e-1, weight_decay=0.5)
+    opt.zero_grad()
+    opt.step()
+    assert torch.allclose(m.weight, w0 * (1 - 1e-1 * 0.5), rtol=1e-6, atol=1e-8)
+    assert torch.equal(m.bias, b0)
+    with pytest.raises(ValueError):
+        FlatAdamW([m.weight, m.weight], [])
+
+
+def test_sharded_step_equals_whole_batch():
+    """One global batch dealt into two shards by attention cost, each shard's loss divided by the GLOBAL crystal
+    count, gradient buffers added: the same gradients and the same update as one pass over the whole batch
+    (what the multi-GPU benchmark does with an all-reduce in place of the addition)."""
+    dev = cuda()
+    from crystalframer_b200 import data, synth
+    from crystalframer_b200.parallel import attention_cost, partition_by_pair_count
+    ref, ours, _, opt, b, y, tb = _step_models(dev, True)
+    from crystalframer_b200.optim import FlatAdamW
+    split = lambda m: ([p for n, p in m.named_parameters() if p.requires_grad and not n.endswith("bias")],
+                       [p for n, p in m.named_parameters() if p.requires_grad and n.endswith("bias")])
+    opt_whole = FlatAdamW(*split(ref), lr=5e-4, betas=(0.9, 0.98), eps=1e-8, weight_decay=1e-2, max_norm=1.0)
+    B = len(b.sizes)
+    np.random.seed(5)
+    opt_whole.zero_grad()
+    ((ref(tb) - tb.y).abs().sum() / B).backward()
+    g_whole = opt_whole.gather_grads().clone()
+    parts = partition_by_pair_count(b.sizes, 2, attention_cost(b.sizes, b.trans_vec))
+    assert sorted(np.concatenate(parts).tolist()) == list(range(B))
+    opt.zero_grad()
+    for idx in parts:
+        idx = np.sort(idx)
+        sb = data.host_batch(synth.select(b, idx), y[idx], pinned=False).to(dev, non_blocking=False)
+        np.random.seed(5)
+        ((ours(sb) - sb.y).abs().sum() / B).backward()        # sinks and .grad accumulate over the shards
+    g_sum = opt.gather_grads()
+    scale = float(g_whole.abs().max())
+    assert float((g_sum - g_whole).abs().max()) <= 1e-4 * scale
+    opt_whole.step()
+    opt.step()
+    assert float((opt.flat - opt_whole.flat).abs().max()) <= 2e-6

@@ -306,14 +306,22 @@ def test_mean_pool():
     assert torch.equal(out2, out.detach())
 
 
+@pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("layers,frame_method", [(1, "max"), (4, "max"), (2, "no"), (2, "weighted_pca")])
-def test_whole_model_against_cpu_oracle(layers, frame_method):
+def test_whole_model_against_cpu_oracle(layers, frame_method, fused):
     """Forward and backward of the whole model (species embedding, encoder layers, mean pooling,
     MLP head) on the GPU against the same weights run on the host cores through the oracle:
-    8 crystals of 4-16 atoms, float32, symmetry-breaking noise off."""
+    8 crystals of 4-16 atoms, float32, symmetry-breaking noise off.
+
+    ``fused=False``: the first training forward, which measures the coefficient statistics and runs
+    operator by operator.  ``fused=True``: the statistics are in place, so every layer runs as the
+    one-node fused layer -- the path the benchmark times; the test checks that it was taken.
+    Weighted-PCA frames are compared in their own tests (eigenvectors are not comparable where
+    eigenvalues nearly coincide); here the CPU model receives the frames the GPU constructed, so
+    everything downstream of the frames is compared."""
     dev = _cuda()
     import copy
-    from crystalframer_b200 import data, synth
+    from crystalframer_b200 import _lib, data, encoder, fused_layer, synth
     from crystalframer_b200.latticeformer import Latticeformer, ModelParams
     from oracle import cpu_model
     torch.manual_seed(0)
@@ -326,61 +334,57 @@ def test_whole_model_against_cpu_oracle(layers, frame_method):
     b = synth.make_workload("cfg1")
     y = np.random.default_rng(0).normal(size=(len(b.sizes), 1)).astype(np.float32)
     tb = data.host_batch(b, y, pinned=False).to(dev, non_blocking=False)
-    out = gpu(tb)
-    loss = (out - tb.y).abs().mean()
-    loss.backward()
-    if frame_method != "max":
-        # the CPU model driver covers the max-frame path; the other operators have their own parity
-        # tests, here the wiring is exercised
-        assert torch.isfinite(out).all()
-        assert all(torch.isfinite(p.grad).all() for p in gpu.parameters() if p.grad is not None)
-        return
-    out_c = cpu_model.forward(cpu, b, backend="port")
+    if fused:
+        with torch.no_grad():
+            gpu(tb)                                   # measures gauss_scale; the next forward takes the fused layers
+        for lg, lc in zip(gpu.encoder.layers, cpu.encoder.layers):
+            with torch.no_grad():
+                lc.self_attn.gauss_scale.copy_(lg.self_attn.gauss_scale.cpu())
+    calls = []
+    orig_invoke = _lib.invoke
+    _lib.invoke = lambda name, *a, **k: (calls.append(name), orig_invoke(name, *a, **k))[1]
+    fused_layer.FRAME_TAP = tap = []
+    try:
+        out = gpu(tb)
+        loss = (out - tb.y).abs().mean()
+        loss.backward()
+    finally:
+        _lib.invoke = orig_invoke
+        fused_layer.FRAME_TAP = None
+    n_fused = sum(1 for c in calls if c in fused_layer.FUSED_FORWARD_CALLS)
+    assert n_fused == (layers if fused else 0), (n_fused, sorted(set(calls)))
+    frames = None
+    if frame_method == "weighted_pca":
+        assert len(tap) == layers
+        frames = [f.cpu() for f in tap]
+    out_c = cpu_model.forward(cpu, b, backend="port", frames=frames)
     loss_c = (out_c - torch.from_numpy(y)).abs().mean()
     loss_c.backward()
     _close("prediction", out.detach().cpu().numpy(), out_c.detach().numpy(), 1e-4, 1e-5)
     for l in range(layers):
         assert torch.allclose(gpu.encoder.layers[l].self_attn.gauss_scale.cpu(), cpu.encoder.layers[l].self_attn.gauss_scale,
                               rtol=1e-4, atol=1e-6)
-    worst = 0.0
     for (n, pg), (_, pc) in zip(gpu.named_parameters(), cpu.named_parameters()):
         if pc.grad is None:
             assert pg.grad is None or float(pg.grad.abs().max()) == 0.0, n
             continue
+        assert pg.grad is not None, n
         g, c = pg.grad.cpu().numpy().astype(np.float64), pc.grad.numpy().astype(np.float64)
         scale = max(np.abs(c).max(), 1e-8)
-        worst = max(worst, float(np.abs(g - c).max() / scale))
-        assert np.abs(g - c).max() <= 2e-3 * scale + 1e-7, f"{n}: max abs diff {np.abs(g - c).max():.3e} at scale {scale:.3e}"
-
-
-def test_fused_layer_matches_operator_path():
-    """The one-node encoder layer against the operator-by-operator path: same outputs, same
-    gradients for the input and for every parameter."""
-    dev = _cuda()
-    import copy
-    from crystalframer_b200 import data, encoder, synth
-    from crystalframer_b200.latticeformer import Latticeformer, ModelParams
-    torch.manual_seed(3)
-    model = Latticeformer(ModelParams(num_layers=2, symm_break_noise=0.0)).to(dev).train()
-    b = synth.make_workload("cfg2", num_crystals=16)
-    y = np.random.default_rng(1).normal(size=(len(b.sizes), 1)).astype(np.float32)
-    tb = data.host_batch(b, y, pinned=False).to(dev, non_blocking=False)
-    with torch.no_grad():
-        model(tb)                                   # measures gauss_scale, after which the fused path is eligible
-    results = []
-    for fused in (False, True):
-        encoder.FUSED_LAYER = fused
-        model.zero_grad(set_to_none=True)
-        out = model(tb)
-        (out - tb.y).abs().mean().backward()
-        results.append((out.detach().clone(), {n: p.grad.detach().clone() for n, p in model.named_parameters() if p.grad is not None}))
-    encoder.FUSED_LAYER = True
-    (o0, g0), (o1, g1) = results
-    assert torch.allclose(o0, o1, rtol=1e-5, atol=1e-6)
-    assert set(g0) == set(g1)
-    for n in g0:
-        scale = float(g0[n].abs().max()) + 1e-12
-        assert float((g0[n] - g1[n]).abs().max()) <= 1e-4 * scale + 1e-9, n
+        bad = np.abs(g - c) > 2e-3 * scale + 1e-7
+        # A ReLU unit whose pre-activation is within rounding of zero for some atom may be switched on in one
+        # implementation and off in the other (the activations themselves agree: the unit's output is ~0 either
+        # way).  That moves one atom's contribution in that unit's row of the feed-forward input weights and
+        # bias -- about 1/atoms of the row's gradient.  Up to two such rows per layer are tolerated there, and
+        # only there; everything else must agree entry by entry.
+        if n.endswith("linear1.weight"):
+            rows = bad.any(axis=1)
+            assert rows.sum() <= 2 and np.abs(g - c).max() <= 5e-2 * scale, \
+                f"{n}: {rows.sum()} rows differ, max abs diff {np.abs(g - c).max():.3e} at scale {scale:.3e}"
+        elif n.endswith("linear1.bias"):
+            assert bad.sum() <= 2 and np.abs(g - c).max() <= 5e-2 * scale, f"{n}: {bad.sum()} entries differ"
+        else:
+            assert not bad.any(), f"{n}: max abs diff {np.abs(g - c).max():.3e} at scale {scale:.3e}"
 
 
 @pytest.mark.parametrize("workload,nc,use_list", [("cfg1", None, True), ("cfg2", 24, True), ("cfg2", 24, False)])
