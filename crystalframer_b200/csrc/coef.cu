@@ -15,7 +15,10 @@ struct CoefArgs {
     float lb, beta, cmul, qscale;
     float* a; float* qs;
     const float* ga; const float* gqs; float* gq; float* gw;
+    float* partial;          // optional scratch of kCoSplits * H * 16 floats: the backward then runs kCoSplits blocks per head
 };
+
+constexpr int kCoSplits = 32;
 
 __device__ __forceinline__ float coef_from_dot(const CoefArgs& A, float dot, float scale, float shift, float& dadot)
 {
@@ -47,17 +50,20 @@ __global__ void __launch_bounds__(256) coef_fwd_kernel(const CoefArgs A)
     A.a[t] = coef_from_dot(A, dot, scale, shift, dadot);
 }
 
-// One block per head: gq = gqs * qscale + (ga da/ddot) w ; gw[h] = sum_i (ga da/ddot) q_i, summed in a
-// fixed order (thread-strided partials, then a tree over the block).
+// One block per head (and per slice of the atoms when scratch is given): gq = gqs * qscale + (ga da/ddot) w ;
+// gw[h] = sum_i (ga da/ddot) q_i, summed in a fixed order (thread-strided partials, a tree over the block, then the
+// slices in order by coef_bwd_reduce_kernel).
 __global__ void __launch_bounds__(256) coef_bwd_kernel(const CoefArgs A)
 {
     __shared__ float part[256][kCoHd + 1];
     const int h = blockIdx.x, tid = threadIdx.x;
+    const int64_t chunk = (A.N + gridDim.y - 1) / gridDim.y;
+    const int64_t i_begin = (int64_t)blockIdx.y * chunk, i_end = min(A.N, i_begin + chunk);
     const float scale = A.gauss_scale ? __ldg(A.gauss_scale) : 1.0f, shift = A.gauss_scale ? __ldg(A.gauss_scale + 1) : 0.0f;
     float wv[kCoHd], acc[kCoHd];
 #pragma unroll
     for (int d = 0; d < kCoHd; d++) { wv[d] = __ldg(A.w + h * kCoHd + d); acc[d] = 0.f; }
-    for (int64_t i = tid; i < A.N; i += 256) {
+    for (int64_t i = i_begin + tid; i < i_end; i += 256) {
         const int64_t t = i * A.H + h;
         const float4* q4 = reinterpret_cast<const float4*>(A.q + t * kCoHd);
         const float4* g4 = reinterpret_cast<const float4*>(A.gqs + t * kCoHd);
@@ -91,7 +97,19 @@ __global__ void __launch_bounds__(256) coef_bwd_kernel(const CoefArgs A)
             for (int d = 0; d < kCoHd; d++) part[tid][d] += part[tid + s][d];
         __syncthreads();
     }
-    if (tid < kCoHd) A.gw[h * kCoHd + tid] = part[0][tid];
+    if (tid < kCoHd) {
+        if (gridDim.y == 1) A.gw[h * kCoHd + tid] = part[0][tid];
+        else A.partial[((size_t)blockIdx.y * A.H + h) * kCoHd + tid] = part[0][tid];
+    }
+}
+
+__global__ void coef_bwd_reduce_kernel(const CoefArgs A, int splits)
+{
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= A.H * kCoHd) return;
+    float s = 0.f;
+    for (int y = 0; y < splits; y++) s += A.partial[(size_t)y * A.H * kCoHd + t];
+    A.gw[t] = s;
 }
 
 int coef_fwd(const CoefArgs& A, cudaStream_t st)
@@ -104,7 +122,12 @@ int coef_fwd(const CoefArgs& A, cudaStream_t st)
 
 int coef_bwd(const CoefArgs& A, cudaStream_t st)
 {
-    coef_bwd_kernel<<<A.H, 256, 0, st>>>(A);
+    if (A.partial != nullptr && A.N > 1024) {
+        coef_bwd_kernel<<<dim3(A.H, kCoSplits), 256, 0, st>>>(A);
+        coef_bwd_reduce_kernel<<<(A.H * kCoHd + 127) / 128, 128, 0, st>>>(A, kCoSplits);
+    } else {
+        coef_bwd_kernel<<<dim3(A.H, 1), 256, 0, st>>>(A);
+    }
     return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
 }
 

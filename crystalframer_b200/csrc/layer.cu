@@ -175,6 +175,7 @@ int64_t layer_bwd_workspace_bytes(int64_t N, int64_t E, int D, int F, int H, boo
     b += pad256(N * H * 4) + pad256(E * H * 4);   // ga, gz
     b += pad256(cfb::wgrad_workspace_floats(N, layer_grad_outputs(D, F, H, angles)) * 4);
     b += pad256(D * 4);                           // gradient of lattice_pos before it is added to its destination
+    b += pad256((int64_t)cfb::kCoSplits * D * 4);  // its partial sums over slices of the atoms
     return b;
 }
 
@@ -281,15 +282,19 @@ int cfb200_encoder_layer_fwd(const cfb200_layer_desc* L, const cfb200_layer_weig
     if (rc != CFB200_OK) return rc;
     cudaStream_t st = S(stream);
 
-    // input projections: q, k, v = x W^T + b
-    const float* Wqkv[3] = {W->q_proj, W->k_proj, W->v_proj};
-    float* qkv[3] = {St->q, St->k, St->v};
-    for (int i = 0; i < 3; i++) {
+    // input projections: q, k, v = x W^T + b, one launch
+    {
         TmScope tm(CFB200_TM_LINEAR_FWD, st);
-        cfb::GemmArgs g;
-        memset(&g, 0, sizeof(g));
-        g.seg[0] = {x, Wqkv[i], D, D, D}; g.nseg = 1; g.M = (int)N; g.N = D; g.C = qkv[i]; g.ldc = D; g.bias = W->in_bias + i * D;
-        if ((rc = cfb::gemm(g, false, st)) != CFB200_OK) return rc;
+        const float* Wqkv[3] = {W->q_proj, W->k_proj, W->v_proj};
+        float* qkv[3] = {St->q, St->k, St->v};
+        cfb::GemmBatch gb;
+        memset(&gb, 0, sizeof(gb));
+        gb.n = 3;
+        for (int i = 0; i < 3; i++) {
+            cfb::GemmArgs& g = gb.g[i];
+            g.seg[0] = {x, Wqkv[i], D, D, D}; g.nseg = 1; g.M = (int)N; g.N = D; g.C = qkv[i]; g.ldc = D; g.bias = W->in_bias + i * D;
+        }
+        if ((rc = cfb::gemm_batch(gb, false, st)) != CFB200_OK) return rc;
     }
     // Gaussian coefficients and the scaled query
     {
@@ -370,6 +375,7 @@ int cfb200_encoder_layer_bwd(const cfb200_layer_desc* L, const cfb200_layer_weig
     const int64_t wg_floats = cfb::wgrad_workspace_floats(N, layer_grad_outputs(D, F, H, ang));
     float* wg = ws.take<float>(wg_floats);
     float* gw_tmp = ws.take<float>(D);
+    float* coef_part = ws.take<float>((int64_t)cfb::kCoSplits * D);
     if (!ws.ok) return CFB200_E_WORKSPACE;
 
     cfb::GemmArgs g;
@@ -410,7 +416,7 @@ int cfb200_encoder_layer_bwd(const cfb200_layer_desc* L, const cfb200_layer_weig
         TmScope tm(CFB200_TM_COEF, st);
         cfb::CoefArgs C;
         if ((rc = coef_args(C, St->q, W->lattice_pos, W->gauss_scale, N, L->gauss_lb, L->beta, L->scale_real)) != CFB200_OK) return rc;
-        C.ga = ga; C.gqs = gqs; C.gq = gq; C.gw = gw_lat;
+        C.ga = ga; C.gqs = gqs; C.gq = gq; C.gw = gw_lat; C.partial = coef_part;
         if ((rc = cfb::coef_bwd(C, st)) != CFB200_OK) return rc;
     }
     // g_x = gx1 + gq Wq + gk Wk + gv Wv

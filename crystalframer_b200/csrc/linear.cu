@@ -34,9 +34,13 @@ struct GemmArgs {
     int relu;
 };
 
+// up to three products of equal shape in one launch (blockIdx.z picks one): the q, k and v projections
+struct GemmBatch { GemmArgs g[3]; int n; };
+
 template <bool B_KN, int TM>
-__global__ void __launch_bounds__(kGmThreads) gemm_kernel(const GemmArgs G)
+__global__ void __launch_bounds__(kGmThreads) gemm_kernel(const GemmBatch Gb)
 {
+    const GemmArgs& G = Gb.g[blockIdx.z];
     constexpr int BM = 16 * TM;
     __shared__ __align__(16) float As[2][kGmBK][kGmLd];
     __shared__ __align__(16) float Bs[2][kGmBK][kGmLd];
@@ -54,14 +58,17 @@ __global__ void __launch_bounds__(kGmThreads) gemm_kernel(const GemmArgs G)
     int steps[3], total = 0;
     for (int s = 0; s < G.nseg; s++) { steps[s] = (G.seg[s].K + kGmBK - 1) / kGmBK; total += steps[s]; }
 
-    float4 ra = make_float4(0.f, 0.f, 0.f, 0.f), rb = ra;
-    auto fetch = [&](int step) {
+    // Tiles travel global memory -> registers -> shared memory.  Two register sets are in flight, so a tile is
+    // requested two steps (about 600 cycles of arithmetic) before it is needed: one step does not cover the latency
+    // of L2 at this tile size.
+    auto fetch = [&](int step, float4& ra, float4& rb) {
+        ra = make_float4(0.f, 0.f, 0.f, 0.f);
+        rb = ra;
+        if (step >= total) return;
         int s = 0;
         while (step >= steps[s]) { step -= steps[s]; s++; }
         const GemmSeg& S = G.seg[s];
         const int k0 = step * kGmBK;
-        ra = make_float4(0.f, 0.f, 0.f, 0.f);
-        rb = ra;
         if (a_row < BM && m0 + a_row < G.M && k0 + a_k < S.K)
             ra = __ldg(reinterpret_cast<const float4*>(S.A + (size_t)(m0 + a_row) * S.lda + k0 + a_k));
         if (B_KN) {
@@ -72,7 +79,7 @@ __global__ void __launch_bounds__(kGmThreads) gemm_kernel(const GemmArgs G)
                 rb = __ldg(reinterpret_cast<const float4*>(S.B + (size_t)(n0 + b_row) * S.ldb + k0 + b_col));
         }
     };
-    auto stash = [&](int buf) {
+    auto stash = [&](int buf, const float4& ra, const float4& rb) {
         if (a_row < BM) {
             As[buf][a_k + 0][a_row] = ra.x; As[buf][a_k + 1][a_row] = ra.y;
             As[buf][a_k + 2][a_row] = ra.z; As[buf][a_k + 3][a_row] = ra.w;
@@ -84,13 +91,7 @@ __global__ void __launch_bounds__(kGmThreads) gemm_kernel(const GemmArgs G)
             Bs[buf][b_col + 2][b_row] = rb.z; Bs[buf][b_col + 3][b_row] = rb.w;
         }
     };
-
-    fetch(0);
-    stash(0);
-    __syncthreads();
-    for (int step = 0; step < total; step++) {
-        const int buf = step & 1;
-        if (step + 1 < total) fetch(step + 1);
+    auto compute = [&](int buf) {
 #pragma unroll
         for (int kk = 0; kk < kGmBK; kk++) {
             float a[TM];
@@ -108,10 +109,22 @@ __global__ void __launch_bounds__(kGmThreads) gemm_kernel(const GemmArgs G)
                 acc[i][2] = fmaf(a[i], b.z, acc[i][2]); acc[i][3] = fmaf(a[i], b.w, acc[i][3]);
             }
         }
-        if (step + 1 < total) {
-            stash(buf ^ 1);            // the other buffer was last read before the previous barrier
-            __syncthreads();
-        }
+    };
+
+    float4 ra0, rb0, ra1, rb1;
+    fetch(0, ra0, rb0);
+    stash(0, ra0, rb0);
+    fetch(1, ra0, rb0);
+    fetch(2, ra1, rb1);
+    __syncthreads();
+    for (int step = 0; step < total; step += 2) {
+        compute(0);
+        if (step + 1 < total) { stash(1, ra0, rb0); fetch(step + 3, ra0, rb0); }
+        __syncthreads();
+        if (step + 1 >= total) break;
+        compute(1);
+        if (step + 2 < total) { stash(0, ra1, rb1); fetch(step + 4, ra1, rb1); }
+        __syncthreads();
     }
 
     const int n = n0 + tx * 4;
@@ -138,30 +151,49 @@ __global__ void __launch_bounds__(kGmThreads) gemm_kernel(const GemmArgs G)
 
 static inline bool gm_aligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Launches one product.  Every leading dimension, K and N must be multiples of 4 floats and every pointer
-// 16-byte aligned (float4 accesses).
-static int gemm(const GemmArgs& G, bool b_kn, cudaStream_t st)
+static int gemm_check(const GemmArgs& G)
 {
-    if (G.M <= 0 || G.N <= 0) return CFB200_OK;
     if ((G.N & 3) || (G.ldc & 3) || !gm_aligned(G.C) || !gm_aligned(G.bias) || !gm_aligned(G.resid) || !gm_aligned(G.mask) ||
         (G.resid && (G.ldr & 3)) || (G.mask && (G.ldm & 3)))
         return CFB200_E_SHAPE;
     for (int s = 0; s < G.nseg; s++)
         if ((G.seg[s].K & 3) || (G.seg[s].lda & 3) || (G.seg[s].ldb & 3) || !gm_aligned(G.seg[s].A) || !gm_aligned(G.seg[s].B))
             return CFB200_E_SHAPE;
+    return CFB200_OK;
+}
+
+// Launches up to three products of the same shape (M, N).  Every leading dimension, K and N must be multiples of
+// 4 floats and every pointer 16-byte aligned (float4 accesses).
+static int gemm_batch(const GemmBatch& Gb, bool b_kn, cudaStream_t st)
+{
+    const GemmArgs& G = Gb.g[0];
+    if (G.M <= 0 || G.N <= 0 || Gb.n <= 0) return CFB200_OK;
+    for (int i = 0; i < Gb.n; i++) {
+        if (Gb.g[i].M != G.M || Gb.g[i].N != G.N) return CFB200_E_SHAPE;
+        const int rc = gemm_check(Gb.g[i]);
+        if (rc != CFB200_OK) return rc;
+    }
     const int gy = (G.N + kGmBN - 1) / kGmBN;
     // the 64-row tile when it already gives every SM a block, else the 32-row tile (twice the blocks)
-    const bool tall = (int64_t)((G.M + 63) / 64) * gy >= 148;
+    const bool tall = (int64_t)((G.M + 63) / 64) * gy * Gb.n >= 148;
     if (tall) {
-        const dim3 grid((G.M + 63) / 64, gy);
-        if (b_kn) gemm_kernel<true, 4><<<grid, kGmThreads, 0, st>>>(G);
-        else gemm_kernel<false, 4><<<grid, kGmThreads, 0, st>>>(G);
+        const dim3 grid((G.M + 63) / 64, gy, Gb.n);
+        if (b_kn) gemm_kernel<true, 4><<<grid, kGmThreads, 0, st>>>(Gb);
+        else gemm_kernel<false, 4><<<grid, kGmThreads, 0, st>>>(Gb);
     } else {
-        const dim3 grid((G.M + 31) / 32, gy);
-        if (b_kn) gemm_kernel<true, 2><<<grid, kGmThreads, 0, st>>>(G);
-        else gemm_kernel<false, 2><<<grid, kGmThreads, 0, st>>>(G);
+        const dim3 grid((G.M + 31) / 32, gy, Gb.n);
+        if (b_kn) gemm_kernel<true, 2><<<grid, kGmThreads, 0, st>>>(Gb);
+        else gemm_kernel<false, 2><<<grid, kGmThreads, 0, st>>>(Gb);
     }
     return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
+}
+
+static int gemm(const GemmArgs& G, bool b_kn, cudaStream_t st)
+{
+    GemmBatch Gb;
+    Gb.g[0] = G;
+    Gb.n = 1;
+    return gemm_batch(Gb, b_kn, st);
 }
 
 // ---- weight and bias gradients ------------------------------------------------------------------------
@@ -211,27 +243,20 @@ __global__ void __launch_bounds__(kGmThreads) wgrad_kernel(const WgArgs W)
     const bool want_bias = Pb.bias_out != nullptr && q0 == 0 && b == 0;
     const int l_row = tid >> 4, l_col = (tid & 15) * 4;          // 16 rows x 64 columns, one float4 per thread and operand
     float4 ra = make_float4(0.f, 0.f, 0.f, 0.f), rb = ra;
-    auto fetch = [&](int r) {
-        ra = make_float4(0.f, 0.f, 0.f, 0.f);
-        rb = ra;
+    float4 ra1 = make_float4(0.f, 0.f, 0.f, 0.f), rb1 = ra1;
+    auto fetch2 = [&](int r, float4& xa, float4& xb) {
+        xa = make_float4(0.f, 0.f, 0.f, 0.f);
+        xb = xa;
         if (r + l_row < r1) {
-            if (p0 + l_col < Pb.P) ra = __ldg(reinterpret_cast<const float4*>(A + (size_t)(r + l_row) * Pb.lda + p0 + l_col));
-            if (q0 + l_col < Pb.Q) rb = __ldg(reinterpret_cast<const float4*>(B + (size_t)(r + l_row) * Pb.ldb + q0 + l_col));
+            if (p0 + l_col < Pb.P) xa = __ldg(reinterpret_cast<const float4*>(A + (size_t)(r + l_row) * Pb.lda + p0 + l_col));
+            if (q0 + l_col < Pb.Q) xb = __ldg(reinterpret_cast<const float4*>(B + (size_t)(r + l_row) * Pb.ldb + q0 + l_col));
         }
     };
-    auto stash = [&](int buf) {
-        *reinterpret_cast<float4*>(&As[buf][l_row][l_col]) = ra;
-        *reinterpret_cast<float4*>(&Bs[buf][l_row][l_col]) = rb;
+    auto stash2 = [&](int buf, const float4& xa, const float4& xb) {
+        *reinterpret_cast<float4*>(&As[buf][l_row][l_col]) = xa;
+        *reinterpret_cast<float4*>(&Bs[buf][l_row][l_col]) = xb;
     };
-    if (r0 < r1) {
-        fetch(r0);
-        stash(0);
-    }
-    __syncthreads();
-    int buf = 0;
-    for (int r = r0; r < r1; r += kGmBK, buf ^= 1) {
-        const bool more = r + kGmBK < r1;
-        if (more) fetch(r + kGmBK);
+    auto compute = [&](int buf) {
 #pragma unroll
         for (int kk = 0; kk < kGmBK; kk++) {
             const float4 a = *reinterpret_cast<const float4*>(&As[buf][kk][ty * 4]);
@@ -247,10 +272,21 @@ __global__ void __launch_bounds__(kGmThreads) wgrad_kernel(const WgArgs W)
 #pragma unroll
             for (int kk = 0; kk < kGmBK; kk++) colsum += As[buf][kk][tid];
         }
-        if (more) {
-            stash(buf ^ 1);
-            __syncthreads();
-        }
+    };
+    // two register sets in flight, as in gemm_kernel: rows beyond r1 read as zeros
+    fetch2(r0, ra, rb);
+    stash2(0, ra, rb);
+    fetch2(r0 + kGmBK, ra, rb);
+    fetch2(r0 + 2 * kGmBK, ra1, rb1);
+    __syncthreads();
+    for (int r = r0; r < r1; r += 2 * kGmBK) {
+        compute(0);
+        if (r + kGmBK < r1) { stash2(1, ra, rb); fetch2(r + 3 * kGmBK, ra, rb); }
+        __syncthreads();
+        if (r + kGmBK >= r1) break;
+        compute(1);
+        if (r + 2 * kGmBK < r1) { stash2(0, ra1, rb1); fetch2(r + 4 * kGmBK, ra1, rb1); }
+        __syncthreads();
     }
     // partial tile -> scratch [split][batch][P][Q]
     float* ws = W.ws + Pb.ws_off + ((size_t)split * Pb.nb + b) * Pb.P * Pb.Q;

@@ -219,4 +219,7 @@ def test_sharded_step_equals_whole_batch():
     assert float((g_sum - g_whole).abs().max()) <= 1e-4 * scale
     opt_whole.step()
     opt.step()
-    assert float((opt.flat - opt_whole.flat).abs().max()) <= 2e-6
+    # Adam divides by the root of the squared gradient: entries whose gradient is at rounding level may move by up
+    # to the learning rate in either run, so a few entries may differ by that much
+    diff = (opt.flat - opt_whole.flat).abs()
+    assert float((diff > 2e-6).float().mean()) <= 1e-3 and float(diff.max()) <= 2.5 * 5e-4
