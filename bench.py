@@ -350,8 +350,9 @@ def cpu_baseline_pure(budget_s=20.0):
     Crystalformer without frames) on the host cores, 1 layer, 8 crystals of 4-16 atoms (the CPU-runnable
     configuration).  Needs the reference's Python tree, named by CF_REFERENCE_ROOT; elsewhere it is reported as
     unavailable -- the measured figure of the development machine is kept in the profiles folder."""
-    root = os.environ.get("CF_REFERENCE_ROOT")
-    if not root or not os.path.isdir(root):
+    from oracle import build_oracle
+    root = build_oracle.reference_root()
+    if root is None:
         return {"unavailable": "the reference's Python tree is not on this machine (CF_REFERENCE_ROOT)"}
     from oracle import pure_baseline
     return pure_baseline.measure(root, budget_s)

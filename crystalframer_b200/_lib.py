@@ -62,11 +62,15 @@ SIGNATURES = {
     "cfb200_gauss_coef_fwd": (ctypes.c_int, [vp, vp, vp, i64, f32, f32, f32, vp, vp, vp]),
     "cfb200_gauss_coef_bwd": (ctypes.c_int, [vp, vp, vp, i64, f32, f32, f32, vp, vp, vp, vp, vp]),
     "cfb200_max_frame": (ctypes.c_int, [ctypes.c_int] + [vp] * 9 + [i64, i64, f32, u64] + [vp] * 5),
+    "cfb200_max_frame_static": (ctypes.c_int, [ctypes.c_int] + [vp] * 7 + [i64, i64, f32, u64] + [vp] * 5),
+    "cfb200_max_frames_static": (ctypes.c_int, [vp] * 7 + [i64, i64, f32, u64, u64] + [vp] * 4 + [ctypes.c_int, vp]),
+    "cfb200_lattice_frames": (ctypes.c_int, [vp] * 6 + [i64, i64, f32, u64, u64, u64] + [vp] * 4),
     "cfb200_max_frames": (ctypes.c_int, [vp] * 9 + [i64, i64, f32, u64, u64] + [vp] * 4),
     "cfb200_pair_cache": (ctypes.c_int, [vp] * 4 + [i64, i64, ctypes.c_int, vp, vp, vp]),
     "cfb200_max_frames_cached": (ctypes.c_int, [vp] * 9 + [i64, i64, f32, u64, u64] + [vp] * 5 + [ctypes.c_int, vp]),
     "cfb200_framed_proj_fwd_cached": (ctypes.c_int, [vp] * 6 + [i64, i64, f32, f32] + [vp] * 11 + [ctypes.c_int, vp]),
     "cfb200_framed_proj_bwd_cached": (ctypes.c_int, [vp] * 7 + [i64, i64, f32, f32] + [vp] * 16 + [i64, vp, ctypes.c_int, vp]),
+    "cfb200_sigma_edges": (ctypes.c_int, [vp] * 6 + [i64, i64, f32, u64, vp, vp]),
     "cfb200_sigma_frames_workspace_bytes": (i64, [i64, i64]),
     "cfb200_sigma_frames": (ctypes.c_int, [vp] * 9 + [i64, i64, f32, u64, u64] + [vp] * 4 + [i64, vp]),
     "cfb200_framed_proj_fwd": (ctypes.c_int, [vp] * 6 + [i64, i64, f32, f32] + [vp] * 10),
@@ -88,6 +92,7 @@ SIGNATURES = {
     "cfb200_encoder_layer_workspace_bytes": (i64, [i64, i64, ctypes.c_int, ctypes.c_int, ctypes.c_int]),
     "cfb200_encoder_layer_fwd": (ctypes.c_int, [vp, vp, vp, vp, vp, vp, vp, i64, vp]),
     "cfb200_encoder_layer_bwd": (ctypes.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, ctypes.c_int, vp, i64, vp]),
+    "cfb200_linear": (ctypes.c_int, [vp, vp, vp, vp, i64, i64, i64, ctypes.c_int, ctypes.c_int, vp, vp]),
     "cfb200_timing_begin": (ctypes.c_int, []),
     "cfb200_timing_end": (ctypes.c_int, [vp, vp]),
     "cfb200_probe_throughput": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, vp, vp]),

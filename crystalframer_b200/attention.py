@@ -7,8 +7,8 @@ arguments, same parameter names, shapes and initialisation (so released checkpoi
 data-dependent ``gauss_scale`` state.  Input / output projections and the Gaussian-coefficient
 pipeline stay in PyTorch; everything between them runs in libcfb200.
 
-Only the real-space domain is implemented, with frame methods "max" and "weighted_pca"
-(CrystalFramer) and "no" (plain Crystalformer distance encoding).
+Only the real-space domain is implemented, with frame methods "max", "max_static", "lattice" and
+"weighted_pca" (CrystalFramer) and "no" (plain Crystalformer distance encoding).
 """
 import math
 from typing import Optional, Tuple
@@ -20,9 +20,11 @@ from torch.nn import Module, Parameter
 from torch.nn.init import constant_, normal_, xavier_uniform_
 from torch.nn.modules.linear import NonDynamicallyQuantizableLinear
 
-from .cuda_funcs import (ComputeFrame1MaximumMethodCUDA, ComputeFrame2MaximumMethodCUDA,
+from .cuda_funcs import (ComputeFrame1MaximumMethodCUDA, ComputeFrame1MaximumStaticMethodCUDA,
+                         ComputeFrame2MaximumMethodCUDA, ComputeFrame2MaximumStaticMethodCUDA, ComputeLatticeFrameCUDA,
                          FusedDotProductAttentionCUDA, RealEncodingWithFramedProjFuncCUDA,
-                         RealPeriodicEncodingWithProjFuncCUDA, max_frames_fused, weighted_pca_frames)
+                         RealPeriodicEncodingWithProjFuncCUDA, max_frames_fused, max_static_frames_fused,
+                         weighted_pca_frames)
 from .latticeformer_params import LatticeformerParams
 
 # use the single-launch frame construction instead of the two Functions plus torch ops
@@ -39,19 +41,21 @@ def _scaled_dot_product_attention(q, k, v, batch, batch_kv, edges, attn_weights=
 
 def compute_frame_maximum_method_(q, k, v, alpha, pos, dist2_min, tvecs, batch, edges, proj, K, dist_max, wscale,
                                   frame_method, this_epoch=None, rvecs=None, cutoff=None):
-    """models/indexed_lattice_multi_head_attention_cuda.py:435-493 for frame_method == "max"."""
-    if frame_method != "max":
+    """models/indexed_lattice_multi_head_attention_cuda.py:435-493 for frame_method "max" and "max_static"."""
+    if frame_method not in ("max", "max_static"):
         raise NotImplementedError(f"frame_method={frame_method}")
     rvlen = torch.norm(rvecs, 2, dim=-1) if cutoff is not None else None
     qs = q / math.sqrt(q.shape[-1])
     if FUSED_FRAMES:
         with torch.no_grad():
+            if frame_method == "max_static":
+                return max_static_frames_fused(alpha, pos, tvecs, batch, edges, rvlen, cutoff)
             return max_frames_fused(qs, k, alpha, pos, tvecs, batch, edges, rvlen, cutoff)
     extra = (rvlen, cutoff) if cutoff is not None else ()
-    f1 = ComputeFrame1MaximumMethodCUDA.apply(qs, k, v, alpha, pos, dist2_min, tvecs, batch, edges, K, dist_max,
-                                              wscale, *extra)
-    f2m = ComputeFrame2MaximumMethodCUDA.apply(qs, k, v, alpha, pos, dist2_min, tvecs, batch, edges, K, dist_max,
-                                               wscale, f1, *extra)
+    F1, F2 = (ComputeFrame1MaximumMethodCUDA, ComputeFrame2MaximumMethodCUDA) if frame_method == "max" else \
+        (ComputeFrame1MaximumStaticMethodCUDA, ComputeFrame2MaximumStaticMethodCUDA)
+    f1 = F1.apply(qs, k, v, alpha, pos, dist2_min, tvecs, batch, edges, K, dist_max, wscale, *extra)
+    f2m = F2.apply(qs, k, v, alpha, pos, dist2_min, tvecs, batch, edges, K, dist_max, wscale, f1, *extra)
     dot = (f1 * f2m).sum(dim=-1, keepdim=True)
     f2 = F.normalize(f2m - dot * f1, dim=2)
     return f1, f2, torch.linalg.cross(f1, f2)
@@ -73,9 +77,15 @@ def compute_real_domain_attn_frame_proj(q, k, v, batch_q, batch_kv, edges, pos, 
     elif params.adaptive_cutoff_sigma > 0:
         adap = (rvecs, params.scale_real * params.gauss_lb_real ** (-0.5) * params.adaptive_cutoff_sigma)
     rv_args = (torch.norm(adap[0], 2, dim=-1), adap[1]) if adap else ()
-    if params.frame_method == "max":
+    if params.frame_method in ("max", "max_static"):
         f1, f2, f3 = compute_frame_maximum_method_(q, k, None, alpha, pos, dist2_min, tvecs, batch_q, edges,
-                                                   pe_dist_proj, K, dist_max, wscale, "max", this_epoch, *adap)
+                                                   pe_dist_proj, K, dist_max, wscale, params.frame_method, this_epoch, *adap)
+        W1, W2, W3 = proj_angle1, proj_angle2, proj_angle3
+    elif params.frame_method == "lattice":
+        # models/indexed_lattice_multi_head_attention_cuda.py:496-520
+        with torch.no_grad():
+            f1, f2, f3 = ComputeLatticeFrameCUDA.apply(q / math.sqrt(q.shape[-1]), k, None, alpha, pos, dist2_min, tvecs,
+                                                       batch_q, edges, K, dist_max, wscale, *rv_args)
         W1, W2, W3 = proj_angle1, proj_angle2, proj_angle3
     elif params.frame_method == "weighted_pca":
         with torch.no_grad():

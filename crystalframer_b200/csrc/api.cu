@@ -13,6 +13,7 @@
 #include "attn_fused.cu"
 #include "optim.cu"
 #include "linear.cu"
+#include "tc_linear.cu"
 
 namespace cfb {
 
@@ -180,7 +181,7 @@ static int frames_common(int mode, const float* q, const float* k, const float* 
                          const int64_t* e_start, int64_t N, int64_t E, float cutoff_radius, uint64_t seed1,
                          uint64_t seed2, const float* frame1_in, float* f1, float* f2, float* f3, int64_t* sel_edge,
                          int32_t* sel_image, void* stream, const float* pair_cache = nullptr,
-                         const float* pair_list = nullptr, int cache_range = 0)
+                         const float* pair_list = nullptr, int cache_range = 0, int is_static = 0)
 {
     if (N < 0 || E < 0) return CFB200_E_SHAPE;
     cfb::Params P;
@@ -195,6 +196,7 @@ static int frames_common(int mode, const float* q, const float* k, const float* 
     A.seed1 = seed1; A.seed2 = seed2; A.frame1_in = frame1_in;
     A.frame1 = f1; A.frame2 = f2; A.frame3 = f3; A.sel_edge = sel_edge; A.sel_image = sel_image; A.mode = mode;
     A.cache = reinterpret_cast<const float4*>(pair_cache); A.list = pair_list; A.cache_range = cache_range;
+    A.is_static = is_static;
     return cfb::max_frame(A, P, S(stream));
 }
 
@@ -208,6 +210,46 @@ int cfb200_max_frame(int axis, const float* q_scaled, const float* k, const floa
     return frames_common(axis, q_scaled, k, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, N, E, cutoff_radius,
                          seed, seed, frame1, axis == 1 ? frame : nullptr, axis == 2 ? frame : nullptr, nullptr,
                          sel_edge, sel_image, stream);
+}
+
+int cfb200_max_frame_static(int axis, const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                            const int64_t* batch, const int64_t* edges, const int64_t* e_start, int64_t N, int64_t E,
+                            float cutoff_radius, uint64_t seed, const float* frame1, float* frame, int64_t* sel_edge,
+                            int32_t* sel_image, void* stream)
+{
+    if (axis != 1 && axis != 2) return CFB200_E_SHAPE;
+    if (N > 0 && (frame == nullptr || (axis == 2 && frame1 == nullptr))) return CFB200_E_NULL;
+    // queries and keys are not read in the static mode; any non-NULL pointer satisfies the common checks
+    return frames_common(axis, a_ik, a_ik, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, N, E, cutoff_radius, seed, seed,
+                         frame1, axis == 1 ? frame : nullptr, axis == 2 ? frame : nullptr, nullptr, sel_edge, sel_image, stream,
+                         nullptr, nullptr, 0, 1);
+}
+
+int cfb200_max_frames_static(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                             const int64_t* batch, const int64_t* edges, const int64_t* e_start, int64_t N, int64_t E,
+                             float cutoff_radius, uint64_t seed1, uint64_t seed2, float* frame1, float* frame2, float* frame3,
+                             const float* pair_cache, int cache_range, void* stream)
+{
+    if (N > 0 && (!frame1 || !frame2 || !frame3)) return CFB200_E_NULL;
+    if (pair_cache != nullptr && (reinterpret_cast<uintptr_t>(pair_cache) & 15u) != 0) return CFB200_E_SHAPE;
+    return frames_common(3, a_ik, a_ik, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, N, E, cutoff_radius, seed1, seed2,
+                         nullptr, frame1, frame2, frame3, nullptr, nullptr, stream, pair_cache, nullptr, cache_range, 1);
+}
+
+int cfb200_lattice_frames(const float* a_ik, const float* tvecs, const float* rvlen, const int64_t* batch,
+                          const int64_t* edges, const int64_t* e_start, int64_t N, int64_t E, float cutoff_radius,
+                          uint64_t seed1, uint64_t seed2, uint64_t seed3, float* frame1, float* frame2, float* frame3,
+                          void* stream)
+{
+    if (N < 0 || E < 0) return CFB200_E_SHAPE;
+    cfb::Params P;
+    int rc = make_params(1.0f, cutoff_radius, P);
+    if (rc != CFB200_OK) return rc;
+    if (N == 0) return CFB200_OK;
+    if (!a_ik || !tvecs || !batch || !edges || !e_start || !frame1 || !frame2 || !frame3) return CFB200_E_NULL;
+    if (cutoff_radius != 0.0f && rvlen == nullptr) return CFB200_E_NULL;
+    return cfb::lattice_frames(a_ik, tvecs, rvlen, batch, e_start, edges, N, E, seed1, seed2, seed3, frame1, frame2, frame3, P,
+                               S(stream));
 }
 
 int cfb200_max_frames(const float* q_scaled, const float* k, const float* a_ik, const float* pos_ij,
@@ -269,6 +311,24 @@ int cfb200_sigma_frames(const float* q_scaled, const float* k, const float* a_ik
     A.edges = edges; A.e_start = e_start; A.N = N; A.E = E; A.seed_noise = seed_noise; A.seed_sign = seed_sign;
     A.ws = reinterpret_cast<float*>(workspace); A.frame1 = frame1; A.frame2 = frame2; A.frame3 = frame3;
     return cfb::sigma_frames(A, P, S(stream));
+}
+
+int cfb200_sigma_edges(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen, const int64_t* batch,
+                       const int64_t* edges, int64_t N, int64_t E, float cutoff_radius, uint64_t seed_noise, float* records,
+                       void* stream)
+{
+    if (N < 0 || E < 0) return CFB200_E_SHAPE;
+    cfb::Params P;
+    int rc = make_params(1.0f, cutoff_radius, P);
+    if (rc != CFB200_OK) return rc;
+    if (N == 0 || E == 0) return CFB200_OK;
+    if (!a_ik || !pos_ij || !tvecs || !batch || !edges || !records) return CFB200_E_NULL;
+    if (cutoff_radius != 0.0f && rvlen == nullptr) return CFB200_E_NULL;
+    cfb::SgArgs A;
+    memset(&A, 0, sizeof(A));
+    A.a_ik = a_ik; A.pos_ij = pos_ij; A.tvecs = tvecs; A.rvlen = rvlen; A.batch = batch; A.edges = edges; A.N = N; A.E = E;
+    A.seed_noise = seed_noise; A.ws = records;
+    return cfb::sigma_edges(A, P, S(stream));
 }
 
 static int fp_args(cfb::FpArgs& A, const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,

@@ -41,6 +41,8 @@ struct FrArgs {
     const float4* cache;      // optional per-pair results of pair_cache_kernel, valid for ranges (cache_range)^3
     const float* list;        // optional per-pair sorted translation lists (pair_list_kernel)
     int cache_range;
+    int is_static;            // "max_static": queries and keys do not enter the selection and the second axis' score
+                              // carries no Gaussian coefficient (compute_second_frame_static_each_edge.cu:126,135)
 };
 
 struct Cell { float rx, ry, rz, t1x, t1y, t1z, t2x, t2y, t2z, t3x, t3y, t3z; };
@@ -142,7 +144,7 @@ __device__ __forceinline__ Cand first_axis_candidate(const Cell& cell, float a, 
 // of the same pair (same operations, same value); otherwise it is searched here.
 __device__ __forceinline__ Cand second_axis_candidate(const Cell& cell, float a, int R1, int R2, int R3, float amp,
                                                       uint64_t seed, uint64_t tid, float f1x, float f1y, float f1z,
-                                                      float d2min_known, const float* list)
+                                                      float d2min_known, const float* list, const bool is_static = false)
 {
     Cand c; c.ux = c.uy = c.uz = 0.f; c.img = -1; c.value = -1e15f; c.d2raw = 0.f;
     float d2min = d2min_known >= 0.f ? d2min_known : 1e10f;
@@ -162,7 +164,8 @@ __device__ __forceinline__ Cand second_axis_candidate(const Cell& cell, float a,
         float dx, dy, dz, d2;
         separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
         if (!(d2 > kTiny)) return;
-        const float gauss = __fmul_rn(a, __fsub_rn(d2, d2min));
+        // the static variant's score is (d^2 - d^2_min) + log(...): it grows with the distance
+        const float gauss = is_static ? __fsub_rn(d2, d2min) : __fmul_rn(a, __fsub_rn(d2, d2min));
         if (__fadd_rn(gauss, half) < best) return;              // score + noise <= gauss + half
         const float d = __fsqrt_rn(d2);
         const float vx = __fdiv_rn(dx, d), vy = __fdiv_rn(dy, d), vz = __fdiv_rn(dz, d);
@@ -176,7 +179,7 @@ __device__ __forceinline__ Cand second_axis_candidate(const Cell& cell, float a,
         if (noisy > best || (noisy == best && t < c.img)) {
             best = noisy;
             c.ux = vx; c.uy = vy; c.uz = vz;
-            c.value = __fadd_rn(score, __fmul_rn(a, d2min));
+            c.value = __fadd_rn(score, is_static ? d2min : __fmul_rn(a, d2min));
             c.img = t;
         }
     };
@@ -296,6 +299,7 @@ __global__ void __launch_bounds__(kFrThreads, 3) max_frame_kernel(const FrArgs A
                 float dot = 0.f;
                 const float4* q4 = reinterpret_cast<const float4*>(A.q + (i * H + h) * kFrHd);
                 const float4* k4 = reinterpret_cast<const float4*>(A.k + (j * H + h) * kFrHd);
+                if (!A.is_static)
 #pragma unroll
                 for (int d4 = 0; d4 < kFrHd / 4; d4++) {
                     const float4 u = __ldg(q4 + d4), v = __ldg(k4 + d4);
@@ -314,10 +318,11 @@ __global__ void __launch_bounds__(kFrThreads, 3) max_frame_kernel(const FrArgs A
                     }
                 } else {
                     const float known = round == 0 ? d2raw0 : (round == 1 ? d2raw1 : (round == 2 ? d2raw2 : -1.f));
-                    const bool hit = A.list != nullptr && R1 == A.cache_range && R2 == A.cache_range && R3 == A.cache_range;
+                    // the sorted list serves the search only where the score falls with the distance
+                    const bool hit = A.list != nullptr && !A.is_static && R1 == A.cache_range && R2 == A.cache_range && R3 == A.cache_range;
                     cd = second_axis_candidate(cell, row_a[r], R1, R2, R3, P.noise, A.seed2, noise_id,
                                                row_f1[r][0], row_f1[r][1], row_f1[r][2], known,
-                                               hit ? A.list + (size_t)e * kListStride : nullptr);
+                                               hit ? A.list + (size_t)e * kListStride : nullptr, A.is_static != 0);
                 }
                 const float s = __fadd_rn(dot, cd.value);
                 if (s > -1e10f) {
@@ -372,6 +377,96 @@ __global__ void __launch_bounds__(kFrThreads, 3) max_frame_kernel(const FrArgs A
             }
         }
         __syncthreads();
+    }
+}
+
+// "lattice" frames: thread = (atom, head); the directions of the three shortest lattice vectors of the atom's cell
+// within its lattice ranges (replaces compute_lattice_first_frame.cu, compute_lattice_second_frame.cu,
+// compute_lattice_third_frame.cu and the host glue of models/cuda_funcs/calc_lattice_frame.py:22-150).  Only an atom's
+// self pair takes part in the reference (separation zero), so no pair data is read.  Three greedy searches with a
+// running minimum (strict comparison: the first translation in the reference's loop order wins on equal lengths):
+// axis 1 the shortest translation; axis 2 the shortest one not collinear with it, on its side; axis 3 the shortest
+// one out of their plane, on the side of axis 1; all three negated when axis 3 points against axis 1 x axis 2.
+// Outputs are zero where nothing qualifies (the reference leaves them uninitialised).  Unfused IEEE operations in the
+// reference's order, so a CPU reproduces the frames bit for bit.  self_pair (N): pair index of (i, i), which names
+// the noise stream.
+__global__ void __launch_bounds__(128) lattice_frame_kernel(const float* __restrict__ a_ik, const float* __restrict__ tvecs,
+                                                            const float* __restrict__ rvlen, const int64_t* __restrict__ batch,
+                                                            const int64_t* __restrict__ e_start, const int64_t* __restrict__ edges,
+                                                            int64_t N, int64_t E, uint64_t seed1, uint64_t seed2, uint64_t seed3,
+                                                            float* __restrict__ f1, float* __restrict__ f2, float* __restrict__ f3,
+                                                            const Params P)
+{
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int H = P.H;
+    if (tid >= N * H) return;
+    const int64_t i = tid / H;
+    const int h = (int)(tid - i * H);
+    const int64_t c = batch[i];
+    Cell cell;
+    const float* Tc = tvecs + 9 * c;
+    cell.t1x = __ldg(Tc); cell.t1y = __ldg(Tc + 1); cell.t1z = __ldg(Tc + 2);
+    cell.t2x = __ldg(Tc + 3); cell.t2y = __ldg(Tc + 4); cell.t2z = __ldg(Tc + 5);
+    cell.t3x = __ldg(Tc + 6); cell.t3y = __ldg(Tc + 7); cell.t3z = __ldg(Tc + 8);
+    cell.rx = cell.ry = cell.rz = 0.f;
+    const float a = __ldg(a_ik + i * H + h);
+    int R[3];
+    for (int d = 0; d < 3; d++) R[d] = lattice_range_1d(P, a, P.cutoff_radius != 0.0f ? __ldg(rvlen + 3 * c + d) : 0.0f);
+    uint64_t noise_id = 0;
+    if (P.noise != 0.0f) {
+        // the atom's pairs run over its crystal's atoms in order: the self pair is at offset (i - first key atom)
+        const int64_t e0 = e_start[i];
+        noise_id = (uint64_t)((e0 + (i - edges[E + e0])) * H + h);
+    }
+    float o1[3] = {0.f, 0.f, 0.f}, o2[3] = {0.f, 0.f, 0.f}, o3[3] = {0.f, 0.f, 0.f};
+    float cx = 0.f, cy = 0.f, cz = 0.f;
+    for (int axis = 0; axis < 3; axis++) {
+        if (axis == 2) {
+            cx = __fsub_rn(__fmul_rn(o1[1], o2[2]), __fmul_rn(o1[2], o2[1]));
+            cy = __fsub_rn(__fmul_rn(o1[2], o2[0]), __fmul_rn(o1[0], o2[2]));
+            cz = __fsub_rn(__fmul_rn(o1[0], o2[1]), __fmul_rn(o1[1], o2[0]));
+            const float cn = __fsqrt_rn(__fadd_rn(__fadd_rn(__fmul_rn(cx, cx), __fmul_rn(cy, cy)), __fmul_rn(cz, cz)));
+            cx = __fdiv_rn(cx, cn); cy = __fdiv_rn(cy, cn); cz = __fdiv_rn(cz, cn);
+        }
+        const uint64_t seed = axis == 0 ? seed1 : (axis == 1 ? seed2 : seed3);
+        float d2_min = 1e10f;
+        int t = 0;
+        for (int n1 = -R[0]; n1 <= R[0]; n1++)
+            for (int n2 = -R[1]; n2 <= R[1]; n2++)
+                for (int n3 = -R[2]; n3 <= R[2]; n3++, t++) {
+                    float dx, dy, dz, d2;
+                    separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
+                    const float cand = P.noise != 0.0f ? __fadd_rn(d2, noise_term(P.noise, seed, noise_id, (uint32_t)t)) : d2;
+                    if (!(d2_min > cand && d2 > kTiny)) continue;
+                    const float d = __fsqrt_rn(d2);
+                    const float ux = __fdiv_rn(dx, d), uy = __fdiv_rn(dy, d), uz = __fdiv_rn(dz, d);
+                    if (axis == 0) {
+                        d2_min = cand;
+                        o1[0] = ux; o1[1] = uy; o1[2] = uz;
+                    } else if (axis == 1) {
+                        const float cs = __fadd_rn(__fadd_rn(__fmul_rn(ux, o1[0]), __fmul_rn(uy, o1[1])), __fmul_rn(uz, o1[2]));
+                        if (__fsub_rn(1.0f, fabsf(cs)) > kTiny) {
+                            const float sg = cs < 0.f ? -1.0f : 1.0f;
+                            o2[0] = sg * ux; o2[1] = sg * uy; o2[2] = sg * uz;
+                            d2_min = cand;
+                        }
+                    } else {
+                        const float cc = __fadd_rn(__fadd_rn(__fmul_rn(ux, cx), __fmul_rn(uy, cy)), __fmul_rn(uz, cz));
+                        const float c1 = __fadd_rn(__fadd_rn(__fmul_rn(ux, o1[0]), __fmul_rn(uy, o1[1])), __fmul_rn(uz, o1[2]));
+                        if (fabsf(cc) > kTiny) {
+                            const float sg = c1 < 0.f ? -1.0f : 1.0f;
+                            o3[0] = sg * ux; o3[1] = sg * uy; o3[2] = sg * uz;
+                            d2_min = cand;
+                        }
+                    }
+                }
+    }
+    const float cc = __fadd_rn(__fadd_rn(__fmul_rn(o3[0], cx), __fmul_rn(o3[1], cy)), __fmul_rn(o3[2], cz));
+    const float flip = cc < 0.f ? -1.0f : 1.0f;
+    for (int d = 0; d < 3; d++) {
+        f1[(i * H + h) * 3 + d] = flip * o1[d];
+        f2[(i * H + h) * 3 + d] = flip * o2[d];
+        f3[(i * H + h) * 3 + d] = flip * o3[d];
     }
 }
 
@@ -504,6 +599,17 @@ int pair_cache(const float* pos_ij, const float* tvecs, const int64_t* batch, co
         if ((2 * R + 1) * (2 * R + 1) * (2 * R + 1) > kListLen) return CFB200_E_UNSUPPORTED;
         pair_list_kernel<<<(unsigned)((E + 3) / 4), 128, 0, st>>>(pos_ij, tvecs, batch, edges, E, R, list);
     }
+    return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
+}
+
+int lattice_frames(const float* a_ik, const float* tvecs, const float* rvlen, const int64_t* batch, const int64_t* e_start,
+                   const int64_t* edges, int64_t N, int64_t E, uint64_t seed1, uint64_t seed2, uint64_t seed3, float* f1, float* f2,
+                   float* f3, const Params& P, cudaStream_t st)
+{
+    if (N == 0) return CFB200_OK;
+    const int64_t n = N * P.H;
+    lattice_frame_kernel<<<(unsigned)((n + 127) / 128), 128, 0, st>>>(a_ik, tvecs, rvlen, batch, e_start, edges, N, E, seed1, seed2,
+                                                                    seed3, f1, f2, f3, P);
     return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
 }
 

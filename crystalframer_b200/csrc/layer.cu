@@ -233,7 +233,7 @@ static int layer_check(const cfb200_layer_desc* L, const cfb200_layer_weights* W
     const int H = g_cfg.num_heads;
     if (L->d_model != H * g_cfg.head_dim || g_cfg.head_dim != 16 || g_cfg.dist_dim != 64 || L->ff_dim <= 0 || (L->ff_dim & 3))
         return CFB200_E_UNSUPPORTED;
-    if (L->frame_method < 0 || L->frame_method > 2) return CFB200_E_UNSUPPORTED;
+    if (L->frame_method < 0 || L->frame_method > 4) return CFB200_E_UNSUPPORTED;
     if (L->frame_method != 0 && g_cfg.angle_dim == 0) return CFB200_E_UNSUPPORTED;
     if (G->N < 0 || G->E < 0) return CFB200_E_SHAPE;
     if (G->N > 0x7fffffff) return CFB200_E_TOO_LARGE;
@@ -311,6 +311,15 @@ int cfb200_encoder_layer_fwd(const cfb200_layer_desc* L, const cfb200_layer_weig
         rc = frames_common(3, St->q_scaled, St->k, St->a, G->pos_ij, G->tvecs, G->rvlen, G->batch, G->edges, G->e_start, N, E,
                            L->cutoff_radius, L->seed1, L->seed2, nullptr, St->frames, St->frames + fr, St->frames + 2 * fr,
                            nullptr, nullptr, stream, G->pair_cache, G->pair_list, G->cache_range);
+    } else if (L->frame_method == 3) {
+        TmScope tm(CFB200_TM_FRAMES, st);
+        rc = frames_common(3, St->q_scaled, St->k, St->a, G->pos_ij, G->tvecs, G->rvlen, G->batch, G->edges, G->e_start, N, E,
+                           L->cutoff_radius, L->seed1, L->seed2, nullptr, St->frames, St->frames + fr, St->frames + 2 * fr,
+                           nullptr, nullptr, stream, G->pair_cache, nullptr, G->cache_range, 1);
+    } else if (L->frame_method == 4) {
+        TmScope tm(CFB200_TM_FRAMES, st);
+        rc = cfb200_lattice_frames(St->a, G->tvecs, G->rvlen, G->batch, G->edges, G->e_start, N, E, L->cutoff_radius, L->seed1,
+                                   L->seed2, L->seed1 ^ L->seed2, St->frames, St->frames + fr, St->frames + 2 * fr, stream);
     } else if (L->frame_method == 2) {
         TmScope tm(CFB200_TM_FRAMES, st);
         rc = cfb200_sigma_frames(St->q_scaled, St->k, St->a, G->pos_ij, G->tvecs, G->rvlen, G->batch, G->edges, G->e_start, N, E,
@@ -456,6 +465,19 @@ int cfb200_encoder_layer_bwd(const cfb200_layer_desc* L, const cfb200_layer_weig
         if (cudaGetLastError() != cudaSuccess) return CFB200_E_CUDA;
     }
     return CFB200_OK;
+}
+
+int cfb200_linear(const float* x, const float* weight, const float* bias, const float* residual, int64_t M, int64_t N,
+                  int64_t K, int relu, int weight_is_kn, float* y, void* stream)
+{
+    if (M < 0 || N <= 0 || K <= 0 || M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) return CFB200_E_SHAPE;
+    if (M == 0) return CFB200_OK;
+    if (!x || !weight || !y) return CFB200_E_NULL;
+    cfb::GemmArgs g;
+    memset(&g, 0, sizeof(g));
+    g.seg[0] = {x, weight, (int)K, weight_is_kn ? (int)N : (int)K, (int)K};
+    g.nseg = 1; g.M = (int)M; g.N = (int)N; g.C = y; g.ldc = (int)N; g.bias = bias; g.resid = residual; g.ldr = (int)N; g.relu = relu;
+    return cfb::gemm(g, weight_is_kn != 0, S(stream));
 }
 
 int cfb200_timing_begin(void)

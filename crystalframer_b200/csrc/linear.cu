@@ -16,6 +16,7 @@
 // wgrad_kernel:  out[P,Q] = A[M,P]^T B[M,Q] for a table of problems (optionally batched over heads), the
 //   M rows split over gridDim.y; every block writes its partial tile and partial column sums of A (the bias
 //   gradient) to scratch, and wgrad_reduce_kernel adds the partials in a fixed order (bit-reproducible).
+#include <stdlib.h>
 #include "common.cuh"
 
 namespace cfb {
@@ -151,6 +152,19 @@ __global__ void __launch_bounds__(kGmThreads) gemm_kernel(const GemmBatch Gb)
 
 static inline bool gm_aligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+struct WgArgs;
+static int tc_gemm_batch(const GemmBatch& Gb, bool b_kn, cudaStream_t st);
+static bool tc_gemm_covers(const GemmBatch& Gb);
+static int tc_wgrad_launch(const WgArgs& W, int tiles, cudaStream_t st);
+
+// CFB200_TC=0 keeps the dense layers on the FP32 pipe (gemm_kernel); default: tensor cores where the shapes allow
+static bool use_tensor_cores()
+{
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("CFB200_TC"); v = e ? atoi(e) : 0; }
+    return v != 0;
+}
+
 static int gemm_check(const GemmArgs& G)
 {
     if ((G.N & 3) || (G.ldc & 3) || !gm_aligned(G.C) || !gm_aligned(G.bias) || !gm_aligned(G.resid) || !gm_aligned(G.mask) ||
@@ -173,6 +187,7 @@ static int gemm_batch(const GemmBatch& Gb, bool b_kn, cudaStream_t st)
         const int rc = gemm_check(Gb.g[i]);
         if (rc != CFB200_OK) return rc;
     }
+    if (use_tensor_cores() && tc_gemm_covers(Gb)) return tc_gemm_batch(Gb, b_kn, st);
     const int gy = (G.N + kGmBN - 1) / kGmBN;
     // the 64-row tile when it already gives every SM a block, else the 32-row tile (twice the blocks)
     const bool tall = (int64_t)((G.M + 63) / 64) * gy * Gb.n >= 148;
@@ -351,22 +366,19 @@ static int64_t wgrad_workspace_floats(int64_t M, int64_t outputs)
     return (int64_t)S * outputs;
 }
 
-// Fills tile counts and scratch offsets, then launches the grouped product and the reduction.
+// Fills tile counts and scratch offsets, then launches the grouped products and the reduction.  Problems whose
+// output is a whole number of 128 x 128 tiles go to the tensor-core kernel (tc_linear.cu), the others (the per-head
+// value-encoding weights, 16 rows) to wgrad_kernel; both leave their partials in the same scratch layout.
 static int wgrad(WgArgs& W, int64_t ws_floats, cudaStream_t st)
 {
     if (W.M <= 0 || W.nprob == 0) return CFB200_OK;
     wgrad_splits(W.M, W.S, W.rows);
-    int tiles = 0;
     int64_t off = 0, largest = 0;
     for (int i = 0; i < W.nprob; i++) {
         WgProblem& Pb = W.prob[i];
         if ((Pb.lda & 3) || (Pb.ldb & 3) || (Pb.P & 3) || (Pb.Q & 3) || (Pb.sA & 3) || (Pb.sB & 3) || !gm_aligned(Pb.A) ||
             !gm_aligned(Pb.B))
             return CFB200_E_SHAPE;
-        Pb.tiles_p = (Pb.P + kWgTile - 1) / kWgTile;
-        Pb.tiles_q = (Pb.Q + kWgTile - 1) / kWgTile;
-        Pb.tile0 = tiles;
-        tiles += Pb.nb * Pb.tiles_p * Pb.tiles_q;
         Pb.ws_off = off;
         const int64_t n = (int64_t)Pb.nb * Pb.P * Pb.Q + (Pb.bias_out ? Pb.P : 0);
         off += (int64_t)W.S * n;
@@ -374,7 +386,27 @@ static int wgrad(WgArgs& W, int64_t ws_floats, cudaStream_t st)
         if (n > largest) largest = n;
     }
     if (W.ws == nullptr || off > ws_floats) return CFB200_E_WORKSPACE;
-    wgrad_kernel<<<dim3(tiles, W.S), kGmThreads, 0, st>>>(W);
+    WgArgs tc = W, fp = W;
+    tc.nprob = fp.nprob = 0;
+    int tc_tiles = 0, fp_tiles = 0;
+    for (int i = 0; i < W.nprob; i++) {
+        const WgProblem& Pb = W.prob[i];
+        const bool on_tc = use_tensor_cores() && Pb.nb == 1 && Pb.P % 128 == 0 && Pb.Q % 128 == 0;
+        WgArgs& dst = on_tc ? tc : fp;
+        WgProblem& q = dst.prob[dst.nprob++];
+        q = Pb;
+        const int tile = on_tc ? 128 : kWgTile;
+        q.tiles_p = (Pb.P + tile - 1) / tile;
+        q.tiles_q = (Pb.Q + tile - 1) / tile;
+        int& tiles = on_tc ? tc_tiles : fp_tiles;
+        q.tile0 = tiles;
+        tiles += Pb.nb * q.tiles_p * q.tiles_q;
+    }
+    if (tc.nprob > 0) {
+        const int rc = tc_wgrad_launch(tc, tc_tiles, st);
+        if (rc != CFB200_OK) return rc;
+    }
+    if (fp.nprob > 0) wgrad_kernel<<<dim3(fp_tiles, W.S), kGmThreads, 0, st>>>(fp);
     int gx = (int)((largest + 255) / 256);
     if (gx > 148) gx = 148;
     wgrad_reduce_kernel<<<dim3(gx, W.nprob), 256, 0, st>>>(W);

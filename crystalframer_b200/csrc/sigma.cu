@@ -210,6 +210,15 @@ __global__ void __launch_bounds__(128) sigma_frames_kernel(const SgArgs A, const
     for (int c = 0; c < 3; c++) { o1[c] = Fm[0][c] * flip; o2[c] = Fm[1][c] * flip; o3[c] = Fm[2][c] * flip; }
 }
 
+// the per-pair records alone (what the reference's real_enc_sigma_fwd.cu leaves, plus the logit it omits)
+int sigma_edges(const SgArgs& A, const Params& P, cudaStream_t st)
+{
+    if (A.N == 0 || A.E == 0) return CFB200_OK;
+    const int64_t n1 = A.E * P.H;
+    sigma_edges_kernel<<<(unsigned)((n1 + 255) / 256), 256, 0, st>>>(A, P);
+    return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
+}
+
 int sigma_frames(const SgArgs& A, const Params& P, cudaStream_t st)
 {
     if (A.N == 0 || A.E == 0) return CFB200_OK;

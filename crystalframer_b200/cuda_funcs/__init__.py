@@ -3,9 +3,10 @@
 from .kernel_manager import KernelManager, compile_kernels, current_config
 from .framed_proj import RealEncodingWithFramedProjFuncCUDA
 from .enc_proj import RealPeriodicEncodingWithProjFuncCUDA
-from .max_frame import (ComputeFrame1MaximumMethodCUDA, ComputeFrame2MaximumMethodCUDA,
-                        max_frame_with_selection, max_frames_fused, weighted_pca_frames)
-from .fused_dpa import FusedDotProductAttentionCUDA, attention_probabilities
+from .max_frame import (ComputeFrame1MaximumMethodCUDA, ComputeFrame1MaximumStaticMethodCUDA, ComputeFrame2MaximumMethodCUDA,
+                        ComputeFrame2MaximumStaticMethodCUDA, ComputeLatticeFrameCUDA, max_frame_with_selection,
+                        max_frames_fused, max_static_frame_with_selection, max_static_frames_fused, weighted_pca_frames)
+from .fused_dpa import FusedDotProductAttentionCUDA, FusedDotProductAttentionSigmaMatCUDA, attention_probabilities
 from .irregular_mean import IrregularMeanCUDA
 from .common import csr_offsets, register_csr
 
@@ -15,7 +16,10 @@ CUPY_AVAILABLE = True
 
 __all__ = [
     "KernelManager", "compile_kernels", "current_config", "FusedDotProductAttentionCUDA",
+    "FusedDotProductAttentionSigmaMatCUDA",
     "ComputeFrame1MaximumMethodCUDA", "ComputeFrame2MaximumMethodCUDA", "RealEncodingWithFramedProjFuncCUDA",
+    "ComputeFrame1MaximumStaticMethodCUDA", "ComputeFrame2MaximumStaticMethodCUDA", "ComputeLatticeFrameCUDA",
+    "max_static_frame_with_selection", "max_static_frames_fused",
     "RealPeriodicEncodingWithProjFuncCUDA",
     "IrregularMeanCUDA", "max_frame_with_selection", "max_frames_fused", "weighted_pca_frames", "attention_probabilities",
     "csr_offsets", "register_csr", "CUPY_AVAILABLE",

@@ -115,3 +115,101 @@ def weighted_pca_frames(q, k, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvle
     _lib.invoke("cfb200_sigma_frames", 2, dev, p(qq), p(kk), p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges),
                 ip(e_start), N, E, cutoff, seed_noise, seed_sign, p(f[0]), p(f[1]), p(f[2]), ws.data_ptr(), nbytes)
     return f[0], f[1], f[2], seed_noise, seed_sign
+
+
+def _static_call(axis, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_n, cutoff_radius, frame1, want_selection=False):
+    N, H = a_ik.shape
+    E = edge_ij_e.shape[1]
+    dev = a_ik.device
+    a, pos, tv, rv = f32c(a_ik), f32c(rpos_ij_e), f32c(tvecs_n), f32c(rvlen_n)
+    batch, edges = batch_i.contiguous(), edge_ij_e.contiguous()
+    e_start = csr_offsets(edges, N)
+    cutoff = 0.0 if cutoff_radius is None or rvlen_n is None else float(cutoff_radius)
+    seed = _draw_seed()
+    out = torch.empty((N, H, 3), device=dev, dtype=torch.float32)
+    sel_e = torch.empty((N, H), device=dev, dtype=torch.int64) if want_selection else None
+    sel_i = torch.empty((N, H), device=dev, dtype=torch.int32) if want_selection else None
+    p, ip = _lib.ptr, _lib.iptr
+    _lib.invoke("cfb200_max_frame_static", 1, dev, axis, p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), ip(e_start), N, E,
+                cutoff, seed, p(f32c(frame1)), p(out), ip(sel_e), _lib.ptr(sel_i, torch.int32))
+    return (out, sel_e, sel_i) if want_selection else out
+
+
+class ComputeFrame1MaximumStaticMethodCUDA(torch.autograd.Function):
+    """Drop-in for models/cuda_funcs/calc_maximum_static_frame.py:24-91: first axis (N,H,3) of the "max_static"
+    frames -- the unit vector to the nearest periodic image of the pair that maximises a d^2_min; queries and
+    keys are accepted and ignored, as in the reference."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, a_ik, rpos_ij_e, dist2_min_e, tvecs_n, batch_i, edge_ij_e, K, dist_max, wscale,
+                rvlen_n=None, cutoff_radius=None):
+        return _static_call(1, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_n, cutoff_radius, None)
+
+    @staticmethod
+    def backward(ctx, gframevec):
+        return (None,) * 14
+
+
+class ComputeFrame2MaximumStaticMethodCUDA(torch.autograd.Function):
+    """Drop-in for models/cuda_funcs/calc_maximum_static_frame.py:95-170: second axis (N,H,3), not yet
+    orthogonalised; its score is (d^2 - d^2_min) + log(max(1 - |cos|, 1e-5)) without the Gaussian coefficient."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, a_ik, rpos_ij_e, dist2_min_e, tvecs_n, batch_i, edge_ij_e, K, dist_max, wscale,
+                frame1, rvlen_n=None, cutoff_radius=None):
+        return _static_call(2, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_n, cutoff_radius, frame1)
+
+    @staticmethod
+    def backward(ctx, gframevec):
+        return (None,) * 15
+
+
+def max_static_frame_with_selection(axis, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_n, cutoff_radius, frame1=None):
+    """Static frame axis plus the integer selection behind it (frame, pair index (N,H), translation index (N,H))."""
+    return _static_call(axis, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_n, cutoff_radius, frame1, want_selection=True)
+
+
+def max_static_frames_fused(a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_n, cutoff_radius):
+    """Both static axes and the Gram-Schmidt completion in one launch; draws two seeds like the two Functions."""
+    N, H = a_ik.shape
+    E = edge_ij_e.shape[1]
+    dev = a_ik.device
+    a, pos, tv, rv = f32c(a_ik), f32c(rpos_ij_e), f32c(tvecs_n), f32c(rvlen_n)
+    batch, edges = batch_i.contiguous(), edge_ij_e.contiguous()
+    e_start = csr_offsets(edges, N)
+    cutoff = 0.0 if cutoff_radius is None or rvlen_n is None else float(cutoff_radius)
+    s1, s2 = _draw_seed(), _draw_seed()
+    f = torch.empty((3, N, H, 3), device=dev, dtype=torch.float32)
+    pcache, _, prange = pair_geometry(rpos_ij_e, tvecs_n, batch_i, edge_ij_e, cutoff)
+    p, ip = _lib.ptr, _lib.iptr
+    _lib.invoke("cfb200_max_frames_static", 1, dev, p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), ip(e_start), N, E, cutoff,
+                s1, s2, p(f[0]), p(f[1]), p(f[2]), p(pcache), prange)
+    return f[0], f[1], f[2]
+
+
+class ComputeLatticeFrameCUDA(torch.autograd.Function):
+    """Drop-in for models/cuda_funcs/calc_lattice_frame.py:22-150: (frame_first, frame_second, frame_third), each
+    (N,H,3): the directions of the three shortest lattice vectors of each atom's cell.  Three seeds are drawn from
+    numpy's global generator, as the reference does."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, a_ik, rpos_ij_e, dist2_min_e, tvecs_n, batch_i, edge_ij_e, K, dist_max, wscale,
+                rvlen_n=None, cutoff_radius=None):
+        N, H = a_ik.shape
+        E = edge_ij_e.shape[1]
+        dev = a_ik.device
+        a, tv, rv = f32c(a_ik), f32c(tvecs_n), f32c(rvlen_n)
+        batch, edges = batch_i.contiguous(), edge_ij_e.contiguous()
+        e_start = csr_offsets(edges, N)
+        cutoff = 0.0 if cutoff_radius is None or rvlen_n is None else float(cutoff_radius)
+        s1, s2, s3 = _draw_seed(), _draw_seed(), _draw_seed()
+        f = torch.empty((3, N, H, 3), device=dev, dtype=torch.float32)
+        p, ip = _lib.ptr, _lib.iptr
+        _lib.invoke("cfb200_lattice_frames", 1, dev, p(a), p(tv), p(rv), ip(batch), ip(edges), ip(e_start), N, E, cutoff, s1, s2,
+                    s3, p(f[0]), p(f[1]), p(f[2]))
+        ctx.mark_non_differentiable(f)
+        return f[0], f[1], f[2]
+
+    @staticmethod
+    def backward(ctx, g1, g2, g3):
+        return (None,) * 14

@@ -39,6 +39,7 @@ extern "C" {
 #define CFB200_ST_BAD_COEF 1       /* a Gaussian coefficient a_ik was not negative             */
 #define CFB200_ST_RANGE_CLAMPED 2  /* a lattice range exceeded CFB200_MAX_RANGE and was clamped */
 #define CFB200_ST_SIZE_MISMATCH 4 /* sizes do not sum to the N and E passed to cfb200_edge_index */
+#define CFB200_ST_TC_TIMEOUT 8    /* a tensor-core kernel gave up waiting for its own instructions   */
 #define CFB200_MAX_RANGE 48
 
 typedef struct cfb200_config {
@@ -108,6 +109,33 @@ int cfb200_max_frame(int axis, const float* q_scaled, const float* k, const floa
                      const float* frame1, float* frame, int64_t* sel_edge, int32_t* sel_image,
                      void* stream);
 
+/* The "max_static" frame method: replaces ComputeFrame1MaximumStaticMethodCUDA / ComputeFrame2MaximumStaticMethodCUDA
+ * (models/cuda_funcs/calc_maximum_static_frame.py:24-170; kernels compute_maximum_frame_each_edge.cu,
+ * compute_second_frame_static_each_edge.cu).  As cfb200_max_frame, but queries and keys do not enter the per-atom
+ * arg-max and the second axis' score is (d^2 - d^2_min) + log(max(1 - |cos|, 1e-5)) without the Gaussian
+ * coefficient.  cfb200_max_frames_static: both axes and the Gram-Schmidt completion in one launch (pair_cache
+ * optional, as in cfb200_max_frames_cached). */
+int cfb200_max_frame_static(int axis, const float* a_ik, const float* pos_ij, const float* tvecs,
+                            const float* rvlen, const int64_t* batch, const int64_t* edges,
+                            const int64_t* e_start, int64_t N, int64_t E, float cutoff_radius, uint64_t seed,
+                            const float* frame1, float* frame, int64_t* sel_edge, int32_t* sel_image,
+                            void* stream);
+int cfb200_max_frames_static(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                             const int64_t* batch, const int64_t* edges, const int64_t* e_start, int64_t N,
+                             int64_t E, float cutoff_radius, uint64_t seed1, uint64_t seed2, float* frame1,
+                             float* frame2, float* frame3, const float* pair_cache, int cache_range,
+                             void* stream);
+
+/* The "lattice" frame method: replaces ComputeLatticeFrameCUDA (models/cuda_funcs/calc_lattice_frame.py:22-150;
+ * kernels compute_lattice_first_frame.cu, compute_lattice_second_frame.cu, compute_lattice_third_frame.cu).
+ * Per (atom, head) the directions of the three shortest lattice vectors of the atom's cell within its lattice
+ * ranges: shortest; shortest not collinear with it; shortest out of their plane; signs fixed as in the reference.
+ * frame1..3 (N,H,3); zero where nothing qualifies.  seed1..3: noise seeds of the three searches. */
+int cfb200_lattice_frames(const float* a_ik, const float* tvecs, const float* rvlen, const int64_t* batch,
+                          const int64_t* edges, const int64_t* e_start, int64_t N, int64_t E,
+                          float cutoff_radius, uint64_t seed1, uint64_t seed2, uint64_t seed3, float* frame1,
+                          float* frame2, float* frame3, void* stream);
+
 /* Both axes plus the Gram-Schmidt completion
  * (models/indexed_lattice_multi_head_attention_cuda.py:435-493) in one launch. */
 int cfb200_max_frames(const float* q_scaled, const float* k, const float* a_ik,
@@ -115,6 +143,16 @@ int cfb200_max_frames(const float* q_scaled, const float* k, const float* a_ik,
                       const int64_t* batch, const int64_t* edges, const int64_t* e_start,
                       int64_t N, int64_t E, float cutoff_radius, uint64_t seed1, uint64_t seed2,
                       float* frame1, float* frame2, float* frame3, void* stream);
+
+/* The per-pair part of the weighted-PCA frames alone: replaces the weighted_pca branch of
+ * RealPeriodicEncodingWithProjFuncCUDA.forward (models/cuda_funcs/real_space_enc_proj.py:80-125; kernels
+ * select_edges.cu, real_enc_sigma_fwd.cu).  records (E,H,11) per (pair, head): [0] the lattice-sum logit
+ * z = log sum_n exp(a d_n^2) (the reference returns an uninitialised buffer in its place), [1..6] the
+ * weight-averaged second moments xx, xy, xz, yy, yz, zz of the pair's images (the reference's sigma_mat),
+ * [7] the smallest d^2 > 1e-5 (plus tie-breaking noise), [8..10] the unit vector to that image. */
+int cfb200_sigma_edges(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                       const int64_t* batch, const int64_t* edges, int64_t N, int64_t E, float cutoff_radius,
+                       uint64_t seed_noise, float* records, void* stream);
 
 /* Weighted-PCA frames.  Replaces RealPeriodicEncodingWithProjFuncCUDA with
  * frame_method "weighted_pca" (models/cuda_funcs/real_space_enc_proj.py:80-125; kernels
@@ -331,6 +369,15 @@ int cfb200_batch_geometry(const float* pos, const float* tvecs, const int64_t* s
                           float* pair_cache, float* pair_list, int32_t* order, void* workspace,
                           int64_t workspace_bytes, void* stream);
 
+/* A dense layer, y (M,N) = x (M,K) op(W) (+ bias (N)) (+ residual (M,N)), then ReLU if relu != 0 -- what the
+ * reference computes with torch.nn.functional.linear (models/indexed_lattice_multi_head_attention_cuda.py:869,
+ * :987-988; models/indexed_latticeformer_encoder.py:888-890).  weight_is_kn = 0: W is (N,K) as torch stores a
+ * Linear weight (y = x W^T); 1: W is (K,N) (y = x W, the data gradient of the same layer).  K and N must be
+ * multiples of 4 and all pointers 16-byte aligned.  Runs on the tensor cores (tcgen05, three-product TF32
+ * split with FP32 accumulation) when N is a multiple of 128 and K of 32, else on the FP32 pipe. */
+int cfb200_linear(const float* x, const float* weight, const float* bias, const float* residual, int64_t M,
+                  int64_t N, int64_t K, int relu, int weight_is_kn, float* y, void* stream);
+
 /* Parameters of one encoder layer, laid out as the reference module stores them
  * (models/indexed_lattice_multi_head_attention_cuda.py:1078-1160, models/indexed_latticeformer_encoder.py:783-790):
  * q/k/v_proj (D,D), in_bias (3D), lattice_pos (D), gauss_scale (2) or NULL, out_proj (D,D), out_bias (D),
@@ -364,8 +411,9 @@ typedef struct cfb200_layer_state {
     float *q, *q_scaled, *k, *v, *a, *frames, *z, *spool, *attn, *lse, *x1, *h;
 } cfb200_layer_state;
 
-/* frame_method: 0 = none (plain Crystalformer encoding), 1 = max frames, 2 = weighted-PCA frames.
- * seed1, seed2: noise seeds of the two max-frame axes, or noise seed and sign seed of the weighted-PCA frames. */
+/* frame_method: 0 = none (plain Crystalformer encoding), 1 = max frames, 2 = weighted-PCA frames, 3 = static max
+ * frames, 4 = lattice frames.  seed1, seed2: noise seeds of the two max-frame axes (lattice frames: of the first two
+ * searches, the third uses seed1 ^ seed2), or noise seed and sign seed of the weighted-PCA frames. */
 typedef struct cfb200_layer_desc {
     int32_t d_model, ff_dim, frame_method;
     float gauss_lb, beta, scale_real, dist_max, cutoff_radius;

@@ -17,6 +17,16 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(HERE, "libcforacle.so")
 
 
+def reference_root():
+    """Root of the reference project's tree on this machine, or None: the environment variable CF_REFERENCE_ROOT,
+    else a directory named ``reference`` beside this repository."""
+    env = os.environ.get("CF_REFERENCE_ROOT")
+    if env:
+        return env if os.path.isdir(env) else None
+    sibling = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return sibling if os.path.isdir(os.path.join(sibling, "models", "kernels")) else None
+
+
 def _newer(target, sources):
     if not os.path.exists(target):
         return False
@@ -38,13 +48,14 @@ def build_restatement(force=False):
     return LIB
 
 
-def build_all(force=False, reference_root="/root/reference"):
+def build_all(force=False, root=None):
     build_restatement(force)
-    if os.path.isdir(os.path.join(reference_root, "models", "kernels")):
+    root = root or reference_root()
+    if root and os.path.isdir(os.path.join(root, "models", "kernels")):
         sys.path.insert(0, os.path.join(HERE, "ref_shim"))
         try:
             import gen_ref
-            gen_ref.build(reference_root, force=force)
+            gen_ref.build(root, force=force)
         finally:
             sys.path.pop(0)
 

@@ -454,10 +454,13 @@ void FN(cfo_frame1_edges)(const cfo_config* cfg, const real* a_ik, const real* r
     }
 }
 
-void FN(cfo_frame2_edges)(const cfo_config* cfg, const real* a_ik, const real* rpos, const real* tvecs,
-                          const float* rvlen, const int64_t* batch_i, const int64_t* edges,
-                          int64_t N, int64_t E, uint64_t seed, const real* frame1 /* (N,H,3) */,
-                          real* dir, real* value, int32_t* sel_image)
+/* is_static: the "max_static" variant (models/kernels/compute_second_frame_static_each_edge.cu:126,135), whose
+ * score is (d^2 - d^2_min) + log(...) and whose value is score + d^2_min -- the Gaussian coefficient does not
+ * enter, so the score GROWS with the distance. */
+static void FN(frame2_edges_impl)(const cfo_config* cfg, int is_static, const real* a_ik, const real* rpos, const real* tvecs,
+                                  const float* rvlen, const int64_t* batch_i, const int64_t* edges,
+                                  int64_t N, int64_t E, uint64_t seed, const real* frame1 /* (N,H,3) */,
+                                  real* dir, real* value, int32_t* sel_image)
 {
     const int H = cfg->H;
     (void)N;
@@ -491,7 +494,7 @@ void FN(cfo_frame2_edges)(const cfo_config* cfg, const real* a_ik, const real* r
                     real cs = ux * f1[0] + uy * f1[1] + uz * f1[2];
                     real one_m = (real)1 - R_FABS(cs);
                     real clipped = ((double)one_m > 1e-5) ? one_m : (real)1e-5;
-                    real score = a * (d2 - d2min) + R_LOG(clipped);
+                    real score = (is_static ? (d2 - d2min) : a * (d2 - d2min)) + R_LOG(clipped);
                     real noisy = score;
                     if (cfg->symm_break_noise != 0.0f)
                         noisy = score + (real)(float)(((double)cfo_uniform(seed, (uint64_t)(e * H + k), (uint32_t)t) - 0.5) *
@@ -499,7 +502,7 @@ void FN(cfo_frame2_edges)(const cfo_config* cfg, const real* a_ik, const real* r
                     if (noisy > max_val && (double)R_FABS(cs) < 0.9999) {
                         max_val = noisy;
                         bx = ux; by = uy; bz = uz;
-                        bval = score + a * d2min;
+                        bval = score + (is_static ? d2min : a * d2min);
                         best = t;
                     }
                 }
@@ -509,6 +512,101 @@ void FN(cfo_frame2_edges)(const cfo_config* cfg, const real* a_ik, const real* r
             o[0] = bx; o[1] = by; o[2] = bz;
             value[e * H + k] = bval;
             sel_image[e * H + k] = best;
+        }
+    }
+}
+
+void FN(cfo_frame2_edges)(const cfo_config* cfg, const real* a_ik, const real* rpos, const real* tvecs,
+                          const float* rvlen, const int64_t* batch_i, const int64_t* edges,
+                          int64_t N, int64_t E, uint64_t seed, const real* frame1, real* dir, real* value, int32_t* sel_image)
+{
+    FN(frame2_edges_impl)(cfg, 0, a_ik, rpos, tvecs, rvlen, batch_i, edges, N, E, seed, frame1, dir, value, sel_image);
+}
+
+void FN(cfo_frame2_static_edges)(const cfo_config* cfg, const real* a_ik, const real* rpos, const real* tvecs,
+                                 const float* rvlen, const int64_t* batch_i, const int64_t* edges,
+                                 int64_t N, int64_t E, uint64_t seed, const real* frame1, real* dir, real* value,
+                                 int32_t* sel_image)
+{
+    FN(frame2_edges_impl)(cfg, 1, a_ik, rpos, tvecs, rvlen, batch_i, edges, N, E, seed, frame1, dir, value, sel_image);
+}
+
+/* --------------------------------------------------------------------------
+ * Lattice frames: the three shortest lattice vectors of the atom's cell, per (atom, head)
+ * (models/kernels/compute_lattice_first_frame.cu:86-110, compute_lattice_second_frame.cu:95-130,
+ * compute_lattice_third_frame.cu:96-170; host glue models/cuda_funcs/calc_lattice_frame.py:22-150).
+ * Only the self pair (i == j, separation 0) takes part, so the frames depend on the cell and, through
+ * the lattice ranges, on the Gaussian coefficient.  Axis 1: the shortest translation; axis 2: the shortest
+ * translation not collinear with axis 1 (1 - |cos| > 1e-5), flipped to the side of axis 1; axis 3: the
+ * shortest translation out of their plane (|cos to the normalised cross product| > 1e-5), flipped to the side
+ * of axis 1; finally all three are negated when axis 3 points against the cross product.  Running minimum with
+ * strict comparison: the first translation in loop order wins on equal lengths.  Outputs are zero where no
+ * translation qualifies (the reference leaves them uninitialised).  seeds: one per axis.
+ * -------------------------------------------------------------------------- */
+void FN(cfo_lattice_frames)(const cfo_config* cfg, const real* a_ik, const real* tvecs, const float* rvlen,
+                            const int64_t* batch_i, int64_t N, const uint64_t* seeds, const int64_t* self_pair /* (N) */,
+                            real* f1 /* (N,H,3) */, real* f2, real* f3)
+{
+    const int H = cfg->H;
+    const real zero3[3] = {0, 0, 0};
+#pragma omp parallel for schedule(dynamic, 16)
+    for (int64_t i = 0; i < N; i++) {
+        const int64_t c = batch_i[i];
+        const real* T = tvecs + 9 * c;
+        const real* r = zero3;
+        for (int k = 0; k < H; k++) {
+            const real a = a_ik[i * H + k];
+            int R[3];
+            lattice_range(cfg, (float)a, rvlen + 3 * c, R);
+            const uint64_t tid = (uint64_t)(self_pair[i] * H + k);
+            real* o1 = f1 + (i * H + k) * 3; real* o2 = f2 + (i * H + k) * 3; real* o3 = f3 + (i * H + k) * 3;
+            for (int d = 0; d < 3; d++) o1[d] = o2[d] = o3[d] = 0;
+            for (int axis = 0; axis < 3; axis++) {
+                real d2_min = (real)1e10;
+                real cx = 0, cy = 0, cz = 0;
+                if (axis == 2) {
+                    cx = o1[1] * o2[2] - o1[2] * o2[1];
+                    cy = o1[2] * o2[0] - o1[0] * o2[2];
+                    cz = o1[0] * o2[1] - o1[1] * o2[0];
+                    real cn = R_SQRT(cx * cx + cy * cy + cz * cz);
+                    cx = cx / cn; cy = cy / cn; cz = cz / cn;
+                }
+                int32_t t = 0;
+                FOR_TRANSLATIONS(R) {
+                    SEPARATION(r, T);
+                    real d = R_SQRT(d2);
+                    real noise = 0;
+                    if (cfg->symm_break_noise != 0.0f)
+                        noise = (real)(float)(((double)cfo_uniform(seeds[axis], tid, (uint32_t)t) - 0.5) * (double)cfg->symm_break_noise);
+                    if (d2_min > d2 + noise && (double)d2 > 1e-5) {
+                        real ux = dx / d, uy = dy / d, uz = dz / d;
+                        if (axis == 0) {
+                            d2_min = d2 + noise;
+                            o1[0] = ux; o1[1] = uy; o1[2] = uz;
+                        } else if (axis == 1) {
+                            real cs = ux * o1[0] + uy * o1[1] + uz * o1[2];
+                            if ((double)((real)1 - R_FABS(cs)) > 1e-5) {
+                                real sg = cs < 0 ? (real)-1 : (real)1;
+                                o2[0] = sg * ux; o2[1] = sg * uy; o2[2] = sg * uz;
+                                d2_min = d2 + noise;
+                            }
+                        } else {
+                            real cc = ux * cx + uy * cy + uz * cz;
+                            real c1 = ux * o1[0] + uy * o1[1] + uz * o1[2];
+                            if ((double)R_FABS(cc) > 1e-5) {
+                                real sg = c1 < 0 ? (real)-1 : (real)1;
+                                o3[0] = sg * ux; o3[1] = sg * uy; o3[2] = sg * uz;
+                                d2_min = d2 + noise;
+                            }
+                        }
+                    }
+                    t++;
+                }
+                if (axis == 2) {
+                    real cc = o3[0] * cx + o3[1] * cy + o3[2] * cz;
+                    if (cc < 0) for (int d = 0; d < 3; d++) { o1[d] = -o1[d]; o2[d] = -o2[d]; o3[d] = -o3[d]; }
+                }
+            }
         }
     }
 }

@@ -87,6 +87,16 @@ def attention_layer(attn, x, geo, cfg, frames=None):
         with torch.no_grad():
             f1, f2, f3 = OF.max_frames(qs.detach().contiguous(), k.detach().contiguous(), a.detach().contiguous(),
                                        geo["pos_ij"], geo["tvecs"], geo["batch"], geo["edges"], geo["rvlen"], cutoff)
+    elif method in ("max_static", "lattice"):
+        npy = lambda t: t.detach().contiguous().numpy()
+        e_start = OF._e_start(geo["edges"], N)
+        if method == "max_static":
+            fr = O.max_static_frames(cfg, npy(a), npy(geo["pos_ij"]), npy(geo["tvecs"]), npy(geo["rvlen"]), npy(geo["batch"]),
+                                     npy(geo["edges"]), npy(e_start))
+            f1, f2, f3 = (torch.from_numpy(fr[n]) for n in ("frame1", "frame2", "frame3"))
+        else:
+            f1, f2, f3 = (torch.from_numpy(x) for x in O.lattice_frames(cfg, npy(a), npy(geo["tvecs"]), npy(geo["rvlen"]),
+                                                                        npy(geo["batch"]), npy(geo["edges"]), npy(e_start)))
     elif method == "weighted_pca":
         seed_noise, seed_sign = draw_frame_seeds(method)
         npy = lambda t: t.detach().contiguous().numpy()

@@ -210,6 +210,10 @@ def frame2_edges(cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, frame1, seed=0, 
     return _frame_edges("cfo_frame2_edges", cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, seed, frame1, dtype)
 
 
+def frame2_static_edges(cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, frame1, seed=0, dtype=np.float32):
+    return _frame_edges("cfo_frame2_static_edges", cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, seed, frame1, dtype)
+
+
 def frame_select(cfg, q, k, edges, e_start, direction, value, dtype=np.float32):
     q = _r(q, dtype)
     N, H = q.shape[:2]
@@ -247,6 +251,41 @@ def max_frames(cfg, q_scaled, k, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_sta
     hh = np.arange(H)[None, :]
     return dict(frame1=f1, frame2_max=f2max, frame2=f2, frame3=f3, sel_edge1=sel1, sel_edge2=sel2,
                 sel_image1=img1[sel1, hh], sel_image2=img2[sel2, hh])
+
+
+def max_static_frames(cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, seed1=0, seed2=0, dtype=np.float32):
+    """The "max_static" frame method (models/cuda_funcs/calc_maximum_static_frame.py:24-170 with
+    models/indexed_lattice_multi_head_attention_cuda.py:463-481): as "max", but queries and keys do not enter
+    the selection and the second axis' score carries no Gaussian coefficient."""
+    N, H = a_ik.shape
+    zeros = np.zeros((N, H, cfg.head_dim), dtype)
+    d1, v1, img1 = frame1_edges(cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, seed1, dtype)
+    f1, sel1 = frame_select(cfg, zeros, zeros, edges, e_start, d1, v1, dtype)
+    d2, v2, img2 = frame2_static_edges(cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, f1, seed2, dtype)
+    f2max, sel2 = frame_select(cfg, zeros, zeros, edges, e_start, d2, v2, dtype)
+    f2, f3 = frame_complete(f1, f2max, dtype)
+    hh = np.arange(cfg.H)[None, :]
+    return dict(frame1=f1, frame2_max=f2max, frame2=f2, frame3=f3, sel_edge1=sel1, sel_edge2=sel2,
+                sel_image1=img1[sel1, hh], sel_image2=img2[sel2, hh])
+
+
+def lattice_frames(cfg, a_ik, tvecs, rvlen, batch, edges, e_start, seeds=(0, 0, 0), dtype=np.float32):
+    """The "lattice" frame method: per (atom, head) the directions of the three shortest lattice vectors
+    (models/cuda_funcs/calc_lattice_frame.py:22-150).  Returns (frame1, frame2, frame3), each (N,H,3)."""
+    a = _r(a_ik, dtype)
+    N, H = a.shape
+    # pair index of every atom's self pair (the reference's kernels run over all pairs and act on i == j only;
+    # the noise stream is indexed by that pair)
+    self_pair = np.empty(N, np.int64)
+    for i in range(N):
+        js = edges[1, e_start[i]:e_start[i + 1]]
+        self_pair[i] = e_start[i] + int(np.nonzero(js == i)[0][0])
+    f = [np.empty((N, H, 3), dtype) for _ in range(3)]
+    sd = (ctypes.c_uint64 * 3)(*[int(x) & (2 ** 64 - 1) for x in seeds])
+    c = cfg.c()
+    _fn("cfo_lattice_frames", dtype)(ctypes.byref(c), _p(a), _p(_r(tvecs, dtype)), _p(_f32(rvlen)), _p(_i64(batch)),
+                                     ctypes.c_int64(N), sd, _p(self_pair), _p(f[0]), _p(f[1]), _p(f[2]))
+    return f[0], f[1], f[2]
 
 
 def dpa_fwd(cfg, q, k, v, aij, bij, edges, e_start, dtype=np.float32):

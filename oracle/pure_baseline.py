@@ -109,7 +109,8 @@ if __name__ == "__main__":
     ap.add_argument("--seconds", type=float, default=20.0)
     ap.add_argument("--crystals", type=int, default=None)
     args = ap.parse_args()
-    root = os.environ.get("CF_REFERENCE_ROOT")
-    if not root or not os.path.isdir(root):
+    from oracle import build_oracle
+    root = build_oracle.reference_root()
+    if root is None:
         raise SystemExit("set CF_REFERENCE_ROOT to the reference project's root")
     print(json.dumps(measure(root, args.seconds, args.layers, args.crystals)))

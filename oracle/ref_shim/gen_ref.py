@@ -33,6 +33,8 @@ KERNELS = [
     "irregular_transpose", "irregular_mean_fwd",
     "real_enc_proj_fwd", "real_enc_proj_bwd",
     "real_enc_sigma_fwd", "fused_dpa_sigmamat_fwd",
+    "compute_second_frame_static_each_edge",
+    "compute_lattice_first_frame", "compute_lattice_second_frame", "compute_lattice_third_frame",
 ]
 
 
@@ -164,4 +166,9 @@ def build(reference_root, force=False, consts=None, tag=""):
 
 if __name__ == "__main__":
     import sys
-    build(os.environ.get("CF_REFERENCE_ROOT", "/root/reference"), force="--force" in sys.argv)
+    sys.path.insert(0, os.path.dirname(HERE))
+    import build_oracle
+    root = build_oracle.reference_root()
+    if root is None:
+        raise SystemExit("reference tree not found: set CF_REFERENCE_ROOT")
+    build(root, force="--force" in sys.argv)

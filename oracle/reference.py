@@ -216,6 +216,47 @@ class RefKernels:
         hh = torch.arange(H, device=a_ik.device)[None, :].expand(N, H)
         return torch.stack([dx[arg, hh], dy[arg, hh], dz[arg, hh]], dim=-1), arg
 
+    # ---- models/cuda_funcs/calc_maximum_static_frame.py:24-170: as frame1 / frame2 without q.k, static second kernel ----
+    def frame1_static(self, a_ik, rpos, tvecs, batch, edges, rvlen, cutoff, seed=0):
+        N, H = a_ik.shape
+        E = edges.shape[1]
+        kw = dict(device=a_ik.device, dtype=a_ik.dtype)
+        state = torch.empty(E * H * 48, dtype=torch.uint8, device=a_ik.device)
+        dx, dy, dz = (torch.zeros(E, H, **kw) for _ in range(3))
+        val = torch.ones((E, H), **kw) * 1e10
+        self.launch("compute_maximum_frame_each_edge", (E * H + 31) // 32, 32,
+                    a_ik, rpos, None, tvecs, batch, edges, N, H, E, rvlen, cutoff, state, seed, dx, dy, dz, val)
+        arg = segment_argmax(val, edges[0], N)
+        hh = torch.arange(H, device=a_ik.device)[None, :].expand(N, H)
+        return torch.stack([dx[arg, hh], dy[arg, hh], dz[arg, hh]], dim=-1), arg
+
+    def frame2_static(self, a_ik, rpos, tvecs, batch, edges, rvlen, cutoff, frame1, seed=0):
+        N, H = a_ik.shape
+        E = edges.shape[1]
+        kw = dict(device=a_ik.device, dtype=a_ik.dtype)
+        state = torch.empty(E * H * 48, dtype=torch.uint8, device=a_ik.device)
+        f1 = [frame1[:, :, d].contiguous() for d in range(3)]
+        dx, dy, dz, val = (torch.zeros(E, H, **kw) for _ in range(4))
+        self.launch("compute_second_frame_static_each_edge", (E * H + 31) // 32, 32,
+                    a_ik, rpos, None, tvecs, batch, edges, N, H, E, rvlen, cutoff, state, seed,
+                    f1[0], f1[1], f1[2], dx, dy, dz, val)
+        arg = segment_argmax(val, edges[0], N)
+        hh = torch.arange(H, device=a_ik.device)[None, :].expand(N, H)
+        return torch.stack([dx[arg, hh], dy[arg, hh], dz[arg, hh]], dim=-1), arg
+
+    # ---- models/cuda_funcs/calc_lattice_frame.py:22-150 -------------------------------------
+    def lattice_frames(self, a_ik, rpos, tvecs, batch, edges, rvlen, cutoff, seeds=(0, 0, 0)):
+        N, H = a_ik.shape
+        E = edges.shape[1]
+        kw = dict(device=a_ik.device, dtype=a_ik.dtype)
+        f = [[torch.zeros(N, H, **kw) for _ in range(3)] for _ in range(3)]
+        common = (a_ik, rpos, None, tvecs, batch, edges, N, H, E, 64, 14.0, 1.0, rvlen, cutoff)
+        state = torch.empty(E * H * 48, dtype=torch.uint8, device=a_ik.device)
+        self.launch("compute_lattice_first_frame", E, H, *common, state, seeds[0], *f[0])
+        self.launch("compute_lattice_second_frame", E, H, *common, state, seeds[1], *f[0], *f[1])
+        self.launch("compute_lattice_third_frame", E, H, *common, state, seeds[2], *f[0], *f[1], *f[2])
+        return tuple(torch.stack(f[x], dim=-1) for x in range(3))
+
     @staticmethod
     def complete(frame1, frame2_max):
         """models/indexed_lattice_multi_head_attention_cuda.py:475-481"""

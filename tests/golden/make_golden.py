@@ -118,7 +118,10 @@ def pure_fixture(path, ref_root):
 
 
 if __name__ == "__main__":
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("CF_REFERENCE_ROOT", "/root/reference")
+    from oracle import build_oracle
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else build_oracle.reference_root()
+    if ref_root is None:
+        raise SystemExit("reference tree not found: pass its root or set CF_REFERENCE_ROOT")
     kernels_fixture(os.path.join(HERE, "ref_kernels_small.npz"))
     pure_fixture(os.path.join(HERE, "ref_pure_small.npz"), ref_root)
     print("fixtures written")

@@ -54,7 +54,7 @@ def geometry(P, dev):
                 e_start=to_dev(g["e_start"], dev))
 
 
-def second_axis_score64(P, R, frame1, i, h, e, image):
+def second_axis_score64(P, R, frame1, i, h, e, image, static=False):
     """float64 score of candidate (pair e, translation ``image``) for the second axis of (atom i,
     head h): q.k + a d^2 + log(max(1 - |cos(d, frame1)|, 1e-5))
     (models/kernels/compute_second_frame_each_edge.cu:100-135 plus the selection of
@@ -72,12 +72,14 @@ def second_axis_score64(P, R, frame1, i, h, e, image):
     cosv = abs(float(d @ frame1[i, h].astype(np.float64)) / np.sqrt(d2))
     if cosv >= 0.9999:
         return None
+    if static:          # no query-key term, no Gaussian coefficient (compute_second_frame_static_each_edge.cu:126,135)
+        return d2 + np.log(max(1.0 - cosv, 1e-5))
     j = geo["edges"][1, e]
     qk = float((P["q"][i, h].astype(np.float64) / 4.0) @ P["k"][j, h].astype(np.float64))
     return qk + float(P["a"][i, h]) * d2 + np.log(max(1.0 - cosv, 1e-5))
 
 
-def adjudicate_second_axis(P, frame1, sel_e, sel_i, want_e, want_i, max_reported=5):
+def adjudicate_second_axis(P, frame1, sel_e, sel_i, want_e, want_i, static=False):
     """Every (atom, head) whose second-axis selection differs from the oracle's must be a tie at
     float32 resolution.  Returns the number of differing selections."""
     from oracle import oracle as O
@@ -86,8 +88,8 @@ def adjudicate_second_axis(P, frame1, sel_e, sel_i, want_e, want_i, max_reported
         return 0
     R = O.lattice_range(P["cfg"], P["a"], P["geo"]["rvlen"], P["geo"]["batch"])
     for i, h in diff:
-        s_got = second_axis_score64(P, R, frame1, i, h, int(sel_e[i, h]), int(sel_i[i, h]))
-        s_want = second_axis_score64(P, R, frame1, i, h, int(want_e[i, h]), int(want_i[i, h]))
+        s_got = second_axis_score64(P, R, frame1, i, h, int(sel_e[i, h]), int(sel_i[i, h]), static)
+        s_want = second_axis_score64(P, R, frame1, i, h, int(want_e[i, h]), int(want_i[i, h]), static)
         assert s_got is not None and s_want is not None, f"atom {i} head {h}: inadmissible candidate selected"
         # float32 resolution of a score of this size, times the handful of roundings in its evaluation
         tol = 16 * np.finfo(np.float32).eps * max(1.0, abs(s_want))

@@ -309,3 +309,45 @@ def test_gauss_coefficient_kernels_against_oracle():
                 p(gw_out))
     close("gq", gq_out.cpu().numpy(), q64.grad.numpy())
     close("gw", gw_out.cpu().numpy(), w64.grad.numpy(), RTOL, ATOL * max(1.0, float(w64.grad.abs().max())))
+
+
+@pytest.mark.parametrize("workload,nc", [("cfg1", None), ("cfg2", 24)])
+def test_static_and_lattice_frames(workload, nc):
+    """Frame methods "max_static" and "lattice" against the oracle (which tests/test_oracle.py holds to the
+    reference's own kernels): selections and first axes bit for bit; a differing static second-axis selection must be
+    a tie at float32 resolution; lattice frames, which involve no transcendental function, bit for bit."""
+    dev = cuda()
+    from oracle import oracle as O
+    F = _configure()
+    P = make_problem(workload, num_crystals=nc)
+    g = geometry(P, dev)
+    geo, b, cfg = P["geo"], P["batch"], P["cfg"]
+    a = to_dev(P["a"], dev)
+    want = O.max_static_frames(cfg, P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"], geo["e_start"])
+    f1, se1, si1 = F.max_static_frame_with_selection(1, a, g["pos_ij"], g["tvecs"], g["batch"], g["edges"], g["rvlen"], -3.5)
+    assert np.array_equal(se1.cpu().numpy(), want["sel_edge1"]) and np.array_equal(si1.cpu().numpy(), want["sel_image1"])
+    assert np.array_equal(f1.cpu().numpy(), want["frame1"])
+    f2, se2, si2 = F.max_static_frame_with_selection(2, a, g["pos_ij"], g["tvecs"], g["batch"], g["edges"], g["rvlen"], -3.5, f1)
+    n_diff = adjudicate_second_axis(P, want["frame1"], se2.cpu().numpy(), si2.cpu().numpy(), want["sel_edge2"], want["sel_image2"],
+                                    static=True)
+    assert n_diff <= max(2, se2.numel() // 500)
+    same = (se2.cpu().numpy() == want["sel_edge2"]) & (si2.cpu().numpy() == want["sel_image2"])
+    close("static frame2_max", f2.cpu().numpy()[same], want["frame2_max"][same], 1e-6, 1e-6)
+    g1, g2, g3 = F.max_static_frames_fused(a, g["pos_ij"], g["tvecs"], g["batch"], g["edges"], g["rvlen"], -3.5)
+    assert np.array_equal(g1.cpu().numpy(), want["frame1"])
+    close("static frame2", g2.cpu().numpy()[same], want["frame2"][same], 1e-5, 1e-6)
+    close("static frame3", g3.cpu().numpy()[same], want["frame3"][same], 1e-5, 1e-6)
+    # the drop-in Functions give the same axes
+    q = to_dev(P["q"] / 4.0, dev)
+    k = to_dev(P["k"], dev)
+    h1 = F.ComputeFrame1MaximumStaticMethodCUDA.apply(q, k, None, a, g["pos_ij"], None, g["tvecs"], g["batch"], g["edges"], 64, 14.0,
+                                                      1.0, g["rvlen"], -3.5)
+    assert torch.equal(h1, f1)
+    # lattice frames
+    l_want = O.lattice_frames(cfg, P["a"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"], geo["e_start"])
+    l_got = F.ComputeLatticeFrameCUDA.apply(q, k, None, a, g["pos_ij"], None, g["tvecs"], g["batch"], g["edges"], 64, 14.0, 1.0,
+                                            g["rvlen"], -3.5)
+    for x in range(3):
+        assert np.array_equal(l_got[x].cpu().numpy(), l_want[x]), f"lattice frame {x + 1}"
+    from crystalframer_b200 import _lib
+    assert _lib.read_status(dev) == 0

@@ -62,7 +62,8 @@ def test_batch_geometry_against_oracle():
 
 
 @pytest.mark.parametrize("frame_method,workload,nc", [("max", "cfg2", 16), ("max", "cfg1", None), ("no", "cfg2", 16),
-                                                      ("weighted_pca", "cfg1", None)])
+                                                      ("weighted_pca", "cfg1", None), ("max_static", "cfg1", None),
+                                                      ("lattice", "cfg2", 16)])
 def test_one_call_layer_matches_operator_path(frame_method, workload, nc):
     """Same model, same batch: operator by operator (reference-signature Functions, torch linear layers, autograd)
     against one library call per layer with hand-written backward."""
@@ -223,3 +224,27 @@ def test_sharded_step_equals_whole_batch():
     # to the learning rate in either run, so a few entries may differ by that much
     diff = (opt.flat - opt_whole.flat).abs()
     assert float((diff > 2e-6).float().mean()) <= 1e-3 and float(diff.max()) <= 2.5 * 5e-4
+
+
+@pytest.mark.parametrize("M,N,K,kn", [(300, 128, 128, 0), (2661, 512, 128, 0), (1000, 128, 512, 0), (517, 128, 128, 1),
+                                      (129, 512, 128, 1), (64, 96, 36, 0)])
+def test_dense_layer_kernels(M, N, K, kn):
+    """cfb200_linear (the kernels behind the layer's dense parts) against float64 matmul: plain, with bias +
+    residual + ReLU, for torch-layout and transposed weights, at sizes with ragged last tiles.  The last case has a
+    shape the tensor-core kernel does not cover and runs on the FP32 pipe."""
+    dev = cuda()
+    from crystalframer_b200 import _lib, cuda_funcs as F
+    F.compile_kernels(2, 8, 16, 64, 64, 16, True, 0, 1.0, 4.0, 1.0, 1.0, 0.0)
+    g = torch.Generator(device="cpu").manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g)
+    w = torch.randn((K, N) if kn else (N, K), generator=g) * K ** -0.5
+    b, r = torch.randn(N, generator=g), torch.randn(M, N, generator=g)
+    ref = x.double() @ (w.double() if kn else w.double().t())
+    xd, wd, bd, rd = x.to(dev), w.to(dev), b.to(dev), r.to(dev)
+    y = torch.empty(M, N, device=dev)
+    p = _lib.ptr
+    _lib.invoke("cfb200_linear", 1, dev, p(xd), p(wd), None, None, M, N, K, 0, kn, p(y))
+    close("x W", y.cpu().numpy(), ref.numpy(), 1e-5, 2e-5)
+    _lib.invoke("cfb200_linear", 1, dev, p(xd), p(wd), p(bd), p(rd), M, N, K, 1, kn, p(y))
+    close("relu(x W + b + r)", y.cpu().numpy(), torch.relu(ref + b.double() + r.double()).numpy(), 1e-5, 2e-5)
+    assert _lib.read_status(dev) == 0

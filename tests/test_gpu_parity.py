@@ -95,9 +95,12 @@ def test_max_frames(workload, nc):
     assert np.array_equal(f1.cpu().numpy(), want["frame1"])          # bit-exact: same IEEE operations
     f2, se2, si2 = F.max_frame_with_selection(2, q, k, a, g["pos_ij"], g["tvecs"], g["batch"], g["edges"], g["rvlen"], -3.5, f1)
     same = (se2.cpu().numpy() == want["sel_edge2"]) & (si2.cpu().numpy() == want["sel_image2"])
-    # the second axis' score contains logf, whose last bit differs between CUDA and glibc; a
-    # differing selection is only acceptable as a near-tie and must be very rare
-    assert same.mean() >= 0.999, f"second-axis selection differs on {(~same).sum()} of {same.size}"
+    # the second axis' score contains logf, whose last bit differs between CUDA and glibc: a differing selection
+    # must be a tie at float32 resolution (both candidates' float64 scores within rounding), and rare
+    from parity_util import adjudicate_second_axis
+    n_diff = adjudicate_second_axis(P, want["frame1"], se2.cpu().numpy(), si2.cpu().numpy(), want["sel_edge2"],
+                                    want["sel_image2"])
+    assert n_diff <= max(1, same.size // 1000), f"second-axis selection differs on {n_diff} of {same.size}"
     _close("frame2_max", f2.cpu().numpy()[same], want["frame2_max"][same], 1e-6, 1e-6)
     # fused launch: all three completed axes
     g1, g2, g3 = F.max_frames_fused(q, k, a, g["pos_ij"], g["tvecs"], g["batch"], g["edges"], g["rvlen"], -3.5)
@@ -307,7 +310,8 @@ def test_mean_pool():
 
 
 @pytest.mark.parametrize("fused", [False, True])
-@pytest.mark.parametrize("layers,frame_method", [(1, "max"), (4, "max"), (2, "no"), (2, "weighted_pca")])
+@pytest.mark.parametrize("layers,frame_method", [(1, "max"), (4, "max"), (2, "no"), (2, "weighted_pca"), (2, "max_static"),
+                                                 (2, "lattice")])
 def test_whole_model_against_cpu_oracle(layers, frame_method, fused):
     """Forward and backward of the whole model (species embedding, encoder layers, mean pooling,
     MLP head) on the GPU against the same weights run on the host cores through the oracle:

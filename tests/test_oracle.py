@@ -310,3 +310,32 @@ def test_pooling_identity_behind_the_fused_attention(problem_cfg1):
     close("gW_dist = sum gout (x) S", gW_all[:, :, 0], gWd, 1e-8, 1e-10)
     for x in range(3):
         close(f"gW_ang{x + 1}", gW_all[:, :, 1 + x], gWa[x], 1e-8, 1e-10)
+
+
+def test_static_and_lattice_frames_against_reference_kernels():
+    """Frame methods "max_static" and "lattice": the restatement against the reference's own kernels compiled for the
+    CPU (compute_second_frame_static_each_edge.cu, compute_lattice_{first,second,third}_frame.cu) with the reference's
+    host logic: selections and frames bit for bit (symmetry-breaking noise off)."""
+    from oracle import reference as R
+    if not R.available("cpu"):
+        pytest.skip("oracle/_ref is not built on this machine")
+    import json
+    sigs = json.load(open(os.path.join(R.REF_DIR, "signatures.json")))
+    if "compute_lattice_third_frame" not in sigs:
+        pytest.skip("oracle/_ref was built before the lattice kernels were added: rebuild it")
+    from conftest import make_problem
+    for workload, nc in (("cfg1", None), ("cfg2", 12)):
+        P = make_problem(workload, num_crystals=nc)
+        geo, b, cfg = P["geo"], P["batch"], P["cfg"]
+        T = lambda x: torch.from_numpy(np.ascontiguousarray(x))
+        rk = R.RefKernels("cpu")
+        a, r, tv, bt, e, rv = T(P["a"]), T(geo["pos_ij"]), T(b.trans_vec), T(geo["batch"]), T(geo["edges"]), T(geo["rvlen"])
+        f1r, s1r = rk.frame1_static(a, r, tv, bt, e, rv, -3.5)
+        f2r, s2r = rk.frame2_static(a, r, tv, bt, e, rv, -3.5, f1r)
+        w = O.max_static_frames(cfg, P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"], geo["e_start"])
+        assert np.array_equal(s1r.numpy(), w["sel_edge1"]) and np.array_equal(f1r.numpy(), w["frame1"])
+        assert np.array_equal(s2r.numpy(), w["sel_edge2"]) and np.array_equal(f2r.numpy(), w["frame2_max"])
+        got = rk.lattice_frames(a, r, tv, bt, e, rv, -3.5)
+        want = O.lattice_frames(cfg, P["a"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"], geo["e_start"])
+        for x in range(3):
+            assert np.array_equal(got[x].numpy(), want[x]), (workload, x)
