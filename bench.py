@@ -95,17 +95,18 @@ def make_optimizer(model, fused):
 
 def synthetic_batches(n_batches, seed0, num_crystals, rank=0, world=1):
     """Per-step batches.  With several ranks the step's global batch (num_crystals per rank) is
-    drawn identically on every rank and split by estimated attention cost, most expensive crystal
-    first -- the reference's rule for spreading one batch over devices (models/latticeformer.py:224-233,
-    there by pair count) -- so that the ranks' attention work, not just their crystal counts, is equal."""
+    drawn identically on every rank and split by attention cost (counted surviving lattice translations per pair),
+    most expensive crystal first -- the reference's rule for spreading one batch over devices
+    (models/latticeformer.py:224-233, there by pair count) -- so that the ranks' attention work, not just their
+    crystal counts, is equal."""
     from crystalframer_b200 import synth
-    from crystalframer_b200.parallel import attention_cost, partition_by_pair_count
+    from crystalframer_b200.parallel import attention_cost_counted, partition_by_pair_count
     out = []
     for i in range(n_batches):
         b = synth.make_workload("cfg3", seed=seed0 + i, num_crystals=num_crystals * world)
         y = np.random.default_rng(seed0 + i).normal(size=(len(b.sizes), 1)).astype(np.float32)
         if world > 1:
-            mine = np.sort(partition_by_pair_count(b.sizes, world, attention_cost(b.sizes, b.trans_vec))[rank])
+            mine = np.sort(partition_by_pair_count(b.sizes, world, attention_cost_counted(b.pos, b.trans_vec, b.sizes))[rank])
             b, y = synth.select(b, mine), y[mine]
         out.append((b, y))
     return out

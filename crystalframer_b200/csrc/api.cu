@@ -3,6 +3,8 @@
 #include <math.h>
 #include <stdlib.h>
 #include <string.h>
+#include <atomic>
+#include <mutex>
 #include "common.cuh"
 #include "framed_proj.cu"
 #include "frames.cu"
@@ -44,11 +46,23 @@ __global__ void __launch_bounds__(256) probe_kernel(int kind, int iters, float* 
 
 namespace {
 
-cfb200_config g_cfg;
-bool g_configured = false;
+// Hyper-parameters bound by cfb200_configure.  Entry points may be called from several host threads (the reference
+// launches one Python thread per device, models/latticeformer.py:256-262): every read takes a copy under the lock.
+std::mutex g_cfg_mutex;
+cfb200_config g_cfg_storage;
+bool g_configured_storage = false;
 // Weight threshold of the basis accumulation (see framed_proj.cu).  CFB200_PRUNE overrides it for
 // accuracy studies.
-float g_prune = 16.0f;
+float g_prune_storage = 16.0f;
+
+struct CfgSnapshot { cfb200_config c; bool configured; float prune; };
+CfgSnapshot cfg_snapshot()
+{
+    std::lock_guard<std::mutex> lk(g_cfg_mutex);
+    return CfgSnapshot{g_cfg_storage, g_configured_storage, g_prune_storage};
+}
+#define g_cfg (cfg_snapshot().c)
+#define g_configured (cfg_snapshot().configured)
 
 // Same formulas as the reference host code: LENGTH_RANGE / ANGLE_RANGE
 // (models/cuda_funcs/kernel_manager.py:148-149), angle sigma
@@ -57,14 +71,15 @@ float g_prune = 16.0f;
 // evaluated in float where the kernels evaluate them in float.
 int make_params(float dist_max, float cutoff_radius, cfb::Params& P, bool full_range = false)
 {
-    if (!g_configured) return CFB200_E_NOT_CONFIGURED;
-    const cfb200_config& c = g_cfg;
+    const CfgSnapshot snap = cfg_snapshot();
+    if (!snap.configured) return CFB200_E_NOT_CONFIGURED;
+    const cfb200_config& c = snap.c;
     memset(&P, 0, sizeof(P));
     P.H = c.num_heads; P.head_dim = c.head_dim; P.dist_dim = c.dist_dim; P.angle_dim = c.angle_dim;
     P.lattice_range = c.lattice_range; P.minimum_range = c.minimum_range; P.cos_abs = c.cos_abs;
     P.cutoff_radius = cutoff_radius;
     P.c_dist = c.dist_coef; P.c_ang = c.angle_coef; P.noise = c.symm_break_noise;
-    P.prune = g_prune;
+    P.prune = snap.prune;
     P.win_dist = (int)ceil(2.0 * (double)c.dist_wscale * c.cut_sigma + 1.0);
     P.windowed_dist = (c.dist_dim - P.win_dist > 8) ? 1 : 0;
     if (!P.windowed_dist) P.win_dist = c.dist_dim;
@@ -125,17 +140,19 @@ int cfb200_configure(const cfb200_config* cfg)
     if (c.cut_sigma < 1 || !(c.dist_wscale > 0.f) || (c.angle_dim > 0 && !(c.angle_wscale > 0.f))) return CFB200_E_UNSUPPORTED;
     if (ceil(2.0 * c.dist_wscale * c.cut_sigma + 1.0) > 64.0 && c.dist_dim - ceil(2.0 * c.dist_wscale * c.cut_sigma + 1.0) > 8)
         return CFB200_E_UNSUPPORTED;
-    g_cfg = c;
-    g_configured = true;
-    if (const char* e = getenv("CFB200_PRUNE")) { const float v = (float)atof(e); if (v > 1.0f) g_prune = v; }
+    std::lock_guard<std::mutex> lk(g_cfg_mutex);
+    g_cfg_storage = c;
+    g_configured_storage = true;
+    if (const char* e = getenv("CFB200_PRUNE")) { const float v = (float)atof(e); if (v > 1.0f) g_prune_storage = v; }
     return CFB200_OK;
 }
 
 int cfb200_get_config(cfb200_config* out)
 {
     if (out == nullptr) return CFB200_E_NULL;
-    if (!g_configured) return CFB200_E_NOT_CONFIGURED;
-    *out = g_cfg;
+    const CfgSnapshot snap = cfg_snapshot();
+    if (!snap.configured) return CFB200_E_NOT_CONFIGURED;
+    *out = snap.c;
     return CFB200_OK;
 }
 

@@ -20,6 +20,7 @@
 // distance part unscaled and the angle parts times the angle coefficient (the scaling the reference's
 // weight gradients carry).  The backward leaves gz (E,H) for the column pass that forms gk and gv
 // (dpa_bwd_cols_kernel), gq (N,H,16) with respect to the scaled query, and ga (N,H).
+#include <atomic>
 #include "lattice_lane.cuh"
 
 namespace cfb {
@@ -138,6 +139,7 @@ __global__ void __launch_bounds__(at_warps(false) * 32, kAtFwdBlocks) attn_fwd_k
         const int64_t j0 = A.edges[A.E + T.e0];
         for (int64_t e = T.e0; e < T.e1; e++) {
             const int64_t j = j0 + (e - T.e0);
+            if (lane == 0 && __ldg(A.edges + A.E + e) != j) atomicOr(&g_status, CFB200_ST_PAIR_LAYOUT);   // not the dense layout
             float kd = 0.f, vd = 0.f;
             if (lane < kAtHd) { kd = __ldg(A.k + (j * H + h) * kAtHd + lane); vd = __ldg(A.v + (j * H + h) * kAtHd + lane); }
             run_pair<false, ANG>(A, P, L, T, e);
@@ -316,7 +318,7 @@ template <bool BWD, bool ANG>
 static int launch_at(const AtArgs& A, const Params& P, cudaStream_t st)
 {
     auto kern = BWD ? (void (*)(const AtArgs, const Params))attn_bwd_kernel<ANG> : (void (*)(const AtArgs, const Params))attn_fwd_kernel<ANG>;
-    static bool attr_done[64] = {false};   // per instantiation and device
+    static std::atomic<bool> attr_done[64];   // per instantiation and device
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_done[dev & 63]) {

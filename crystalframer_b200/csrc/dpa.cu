@@ -66,8 +66,11 @@ __global__ void __launch_bounds__(kDpWarps * 32) dpa_fwd_kernel(const DpArgs A, 
 #pragma unroll
     for (int d = 0; d < kDpHd; d++) acc[d] = 0.f;
     float m = -INFINITY, l = 0.f;
+    const int64_t j_first = e1 > e0 ? A.edges[A.E + e0] : 0;
     for (int64_t e = e0 + jj; e < e1; e += G) {
         const int64_t j = A.edges[A.E + e];
+        // the backward's column pass locates pairs by the dense layout: report a list that breaks it
+        if (j != j_first + (e - e0)) atomicOr(&g_status, CFB200_ST_PAIR_LAYOUT);
         float kv[kDpHd];
         load16(A.k + (j * H + h) * kDpHd, kv);
         float s = dot16(qv, kv);

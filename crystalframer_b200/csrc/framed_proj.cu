@@ -20,6 +20,7 @@
 //
 // Numerics follow the reference's float expressions for every integer decision (lattice range,
 // window start / end); Gaussians use ex2.approx on pre-scaled arguments.
+#include <atomic>
 #include "lattice_lane.cuh"
 
 namespace cfb {
@@ -343,7 +344,7 @@ template <bool BWD, bool ANG>
 static int launch_fp(const FpArgs& A, const Params& P, int gx, cudaStream_t st)
 {
     auto kern = framed_proj_kernel<BWD, ANG>;
-    static bool attr_done[64] = {false};   // per instantiation and device
+    static std::atomic<bool> attr_done[64];   // per instantiation and device
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_done[dev & 63]) {

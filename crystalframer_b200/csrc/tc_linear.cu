@@ -18,6 +18,7 @@
 // tensor memory and returns.
 //
 // No TMA: the operands need the hi / lo split on the way to shared memory, so they pass through registers anyway.
+#include <atomic>
 #include "common.cuh"
 
 namespace cfb {
@@ -309,7 +310,7 @@ static bool tc_gemm_covers(const GemmBatch& Gb)
 static int tc_gemm_batch(const GemmBatch& Gb, bool b_kn, cudaStream_t st)
 {
     const GemmArgs& G = Gb.g[0];
-    static bool attr_done[2][64] = {{false}};
+    static std::atomic<bool> attr_done[2][64];
     int dev = 0;
     cudaGetDevice(&dev);
     auto kern = b_kn ? tc_gemm_kernel<true> : tc_gemm_kernel<false>;
@@ -393,7 +394,7 @@ __global__ void __launch_bounds__(256) wgrad_colsum_kernel(const WgArgs W)
 
 static int tc_wgrad_launch(const WgArgs& W, int tiles, cudaStream_t st)
 {
-    static bool attr_done[64] = {false};
+    static std::atomic<bool> attr_done[64];
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_done[dev & 63]) {

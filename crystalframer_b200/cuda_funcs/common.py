@@ -38,7 +38,18 @@ def f32c(t):
 
 
 _pair_cache = {}
-PAIR_LIST_MAX_PAIRS = 4_000_000      # 2.5 KB of translation list per pair: at most 10 GB
+PAIR_LIST_BYTES_PER_PAIR = 5 * 128 * 4   # five planes of 128 floats: 2.5 KB of translation list per pair
+PAIR_LIST_MAX_PAIRS = 4_000_000          # hard cap (10 GB); below it the list also has to fit a quarter of the free memory
+
+
+def pair_list_fits(num_pairs, device):
+    """Whether the per-pair translation lists of a batch may be built: the batch's lists (2.5 KB per pair, e.g. 133 MB
+    for 52 k pairs, 3.6 GB for the 1.4 M pairs of a large-cell batch) must stay under a quarter of the device memory
+    that is free right now and under the hard cap; otherwise the kernels sweep the translations instead."""
+    if num_pairs > PAIR_LIST_MAX_PAIRS:
+        return False
+    free, _ = torch.cuda.mem_get_info(device)
+    return num_pairs * PAIR_LIST_BYTES_PER_PAIR <= free // 4
 
 
 def pair_geometry(rpos_ij_e, tvecs_n, batch_i, edge_ij_e, cutoff):
@@ -66,7 +77,7 @@ def pair_geometry(rpos_ij_e, tvecs_n, batch_i, edge_ij_e, cutoff):
     N, E = batch.shape[0], edges.shape[1]
     cache = torch.empty((E, 4), device=dev, dtype=torch.float32)
     plist = None
-    if (2 * rng + 1) ** 3 <= 128 and E <= PAIR_LIST_MAX_PAIRS:
+    if (2 * rng + 1) ** 3 <= 128 and pair_list_fits(E, dev):
         plist = torch.empty((E, 5, 128), device=dev, dtype=torch.float32)
     _lib.invoke("cfb200_pair_cache", 2, dev, _lib.ptr(pos), _lib.ptr(tv), _lib.iptr(batch), _lib.iptr(edges), N, E, rng,
                 _lib.ptr(cache), _lib.ptr(plist))

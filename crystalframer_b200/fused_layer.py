@@ -57,14 +57,14 @@ class LayerGeometry:
     @classmethod
     def from_raw(cls, pos, trans, sizes, N, E, cutoff):
         """One call of cfb200_batch_geometry on raw positions (N,3), lattice vectors (B,3,3), sizes (B)."""
-        from .cuda_funcs.common import PAIR_LIST_MAX_PAIRS
+        from .cuda_funcs.common import pair_list_fits
         from .cuda_funcs.kernel_manager import KernelManager
         g = cls()
         dev = pos.device
         B = trans.shape[0]
         cfg = KernelManager.config
         rng = int(cfg.lattice_range if cutoff == 0.0 else cfg.minimum_range)
-        want_list = rng > 0 and (2 * rng + 1) ** 3 <= 128 and E <= PAIR_LIST_MAX_PAIRS
+        want_list = rng > 0 and (2 * rng + 1) ** 3 <= 128 and pair_list_fits(E, dev)
         # int64 block: edges (2E) | e_start (N+1) | batch (N) | crystal_start (B+1)
         o_es = 2 * E
         o_b = o_es + N + 1

@@ -14,6 +14,12 @@
  *   - hyper-parameters the reference bakes into its kernel text (compile_kernels,
  *     kernel_manager.py:116-167) are bound once per process with cfb200_configure().
  *
+ * Pair lists: every entry point that takes `edges` together with `e_start` expects the reference's
+ * dense layout (get_edge_index, models/indexed_latticeformer_encoder.py:15-32): pairs sorted by query
+ * atom, and the pairs of an atom running over the atoms of its crystal in order, so that the key atom of
+ * pair e of atom i is edges[1][e_start[i]] + (e - e_start[i]).  The attention kernels use that identity in
+ * their backward passes; a list that breaks it sets CFB200_ST_PAIR_LAYOUT in the status word.
+ *
  * Each entry point names the reference interface it replaces by file:line (paths relative
  * to the reference project root).
  */
@@ -40,6 +46,7 @@ extern "C" {
 #define CFB200_ST_RANGE_CLAMPED 2  /* a lattice range exceeded CFB200_MAX_RANGE and was clamped */
 #define CFB200_ST_SIZE_MISMATCH 4 /* sizes do not sum to the N and E passed to cfb200_edge_index */
 #define CFB200_ST_TC_TIMEOUT 8    /* a tensor-core kernel gave up waiting for its own instructions   */
+#define CFB200_ST_PAIR_LAYOUT 16  /* the pair list is not the dense n x n block of every crystal       */
 #define CFB200_MAX_RANGE 48
 
 typedef struct cfb200_config {

@@ -7,8 +7,8 @@ here on small seeded inputs and the inputs and outputs are committed:
 
 * ``ref_kernels_small.npz`` -- the reference's CUDA kernel sources compiled for the CPU
   (oracle/_ref, built by oracle/ref_shim/gen_ref.py) driven with the reference's host logic:
-  max frames, lattice-sum bias z, value encoding, their gradients, ragged attention forward and
-  backward, mean pooling.  Crystals: 1 atom, 3 atoms in a small cell (lattice range 3 and 4 occur),
+  max frames, static max frames, lattice frames, lattice-sum bias z, value encoding, their gradients,
+  ragged attention forward and backward, mean pooling.  Crystals: 1 atom, 3 atoms in a small cell (lattice range 3 and 4 occur),
   5 atoms, 2 atoms in a large cell.
 * ``ref_pure_small.npz`` -- the reference's pure-PyTorch twin
   (models/indexed_lattice_multi_head_attention.py: LogSumExpXYFunc, AverageGaussiansBySoftmaxXYFunc_,
@@ -78,13 +78,20 @@ def kernels_fixture(path):
     gq, gk, gvv, gaij, gbij = rk.dpa_bwd(q, k, v, z, val, b, e, es, prob, out, go)
     x = T(rng.normal(size=(a.shape[0], 32)).astype(np.float32))
     mean = rk.mean_fwd(x, T(P["sizes"]))
+    # frame methods "max_static" and "lattice"
+    fs1, ssel1 = rk.frame1_static(a, r, tv, b, e, rv, -3.5)
+    fs2m, ssel2 = rk.frame2_static(a, r, tv, b, e, rv, -3.5, fs1)
+    lat = rk.lattice_frames(a, r, tv, b, e, rv, -3.5)
     R_eh = O.lattice_range(O.Config(), P["a"], g["rvlen"], g["batch"])
     np.savez_compressed(
         path, **{k_: v_ for k_, v_ in P.items()}, edges=g["edges"], e_start=g["e_start"], R_ah=R_eh,
         frame1=f1.numpy(), frame2_max=f2m.numpy(), frame2=f2.numpy(), frame3=f3.numpy(), sel_edge1=sel1.numpy(),
         sel_edge2=sel2.numpy(), z=z.numpy(), values=val.numpy(), gz=gz.numpy(), gv=gv.numpy(), ga=ga.numpy(),
         gW_d=gWd.numpy(), gW_a=gWa.numpy(), dpa_out=out.numpy(), dpa_prob=prob.numpy(), go=go.numpy(), gq=gq.numpy(),
-        gk=gk.numpy(), gvv=gvv.numpy(), gaij=gaij.numpy(), gbij=gbij.numpy(), mean_x=x.numpy(), mean=mean.numpy())
+        gk=gk.numpy(), gvv=gvv.numpy(), gaij=gaij.numpy(), gbij=gbij.numpy(), mean_x=x.numpy(), mean=mean.numpy(),
+        static_frame1=fs1.numpy(), static_frame2_max=fs2m.numpy(), static_sel_edge1=ssel1.numpy(),
+        static_sel_edge2=ssel2.numpy(), lattice_frame1=lat[0].numpy(), lattice_frame2=lat[1].numpy(),
+        lattice_frame3=lat[2].numpy())
 
 
 def pure_fixture(path, ref_root):

@@ -76,3 +76,37 @@ def test_operators_fail_loudly_without_cuda():
     with pytest.raises((ValueError, RuntimeError)):
         F.FusedDotProductAttentionCUDA.apply(x, x, x, None, None, torch.zeros(4, dtype=torch.long),
                                              torch.zeros(2, 16, dtype=torch.long))
+
+
+def test_configuration_is_thread_safe(lib):
+    """Several host threads configure and read the bound hyper-parameters at once (the reference runs one Python
+    thread per device over process-global kernel state): every read must return one of the written configurations
+    whole, never a mixture."""
+    import threading
+    L = lib.lib()
+    base = dict(num_heads=8, head_dim=16, dist_dim=64, lattice_range=2, minimum_range=2, cos_abs=0, cut_sigma=4,
+                dist_wscale=1.0, angle_wscale=4.0, dist_coef=1.0, angle_coef=1.0)
+    variants = [lib.Config(angle_dim=64, symm_break_noise=1e-5, **base), lib.Config(angle_dim=0, symm_break_noise=0.0, **base)]
+    torn, stop = [], threading.Event()
+
+    def writer(i):
+        while not stop.is_set():
+            assert L.cfb200_configure(ctypes.byref(variants[i])) == 0
+
+    def reader():
+        out = lib.Config()
+        for _ in range(3000):
+            assert L.cfb200_get_config(ctypes.byref(out)) == 0
+            pair = (out.angle_dim, round(out.symm_break_noise, 9))
+            if pair not in ((64, round(1e-5, 9)), (0, 0.0)):
+                torn.append(pair)
+            assert L.cfb200_framed_proj_bwd_workspace_bytes(10, 100) > 0
+        stop.set()
+
+    threads = [threading.Thread(target=writer, args=(i,)) for i in range(2)] + [threading.Thread(target=reader)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(60)
+    assert not torn, torn[:3]
+    assert L.cfb200_configure(ctypes.byref(variants[0])) == 0

@@ -1,0 +1,147 @@
+"""The drop-in contract, checked against the reference's own source where its tree is present.
+
+The reference's attention module does ``from .cuda_funcs import *`` and calls the autograd Functions positionally.
+Swapping this package's ``cuda_funcs`` in for ``models.cuda_funcs`` therefore needs (i) the reference module to
+import with the swapped package, (ii) every Function name it uses on the supported branches to resolve to this
+package's class, and (iii) each ``forward`` to take the reference's parameters (same names, same order, same
+defaults) and each ``backward`` to return one slot per forward input.  Running the reference module end to end needs
+a GPU *and* the reference tree, which do not meet on one machine here; numerical equivalence of the callers is
+covered by this package's own mirror of that module (tests/test_gpu_parity.py).  Skipped where the reference tree
+is absent.
+"""
+import ast
+import inspect
+import os
+import sys
+import types
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from oracle import build_oracle  # noqa: E402
+
+REF = build_oracle.reference_root()
+pytestmark = pytest.mark.skipif(REF is None, reason="reference tree not present (CF_REFERENCE_ROOT)")
+
+# reference file -> Function classes it defines that this package offers as drop-ins
+FUNCTIONS = {
+    "real_space_framed_proj.py": ["RealEncodingWithFramedProjFuncCUDA"],
+    "real_space_enc_proj.py": ["RealPeriodicEncodingWithProjFuncCUDA"],
+    "calc_maximum_frame.py": ["ComputeFrame1MaximumMethodCUDA", "ComputeFrame2MaximumMethodCUDA"],
+    "calc_maximum_static_frame.py": ["ComputeFrame1MaximumStaticMethodCUDA", "ComputeFrame2MaximumStaticMethodCUDA"],
+    "calc_lattice_frame.py": ["ComputeLatticeFrameCUDA"],
+    "fused_dpa.py": ["FusedDotProductAttentionCUDA"],
+    "fused_dpa_sigmamat.py": ["FusedDotProductAttentionSigmaMatCUDA"],
+    "irregular_mean.py": ["IrregularMeanCUDA"],
+}
+
+
+def _reference_forward_params(path, cls_name):
+    """(parameter names without ctx, number of defaults, slots returned by backward) of a reference Function."""
+    tree = ast.parse(open(path).read())
+    for node in tree.body:
+        if isinstance(node, ast.ClassDef) and node.name == cls_name:
+            out = {}
+            for fn in node.body:
+                if isinstance(fn, ast.FunctionDef) and fn.name in ("forward", "backward"):
+                    out[fn.name] = fn
+            fwd = out["forward"]
+            names = [a.arg for a in fwd.args.args][1:]
+            n_def = len(fwd.args.defaults)
+            slots = None
+            for stmt in ast.walk(out["backward"]):
+                if isinstance(stmt, ast.Return) and isinstance(stmt.value, ast.Tuple):
+                    slots = max(slots or 0, len(stmt.value.elts))
+            return names, n_def, slots
+    raise AssertionError(f"{cls_name} not found in {path}")
+
+
+def test_function_signatures_match_the_reference():
+    from crystalframer_b200 import cuda_funcs as ours
+    for fname, classes in FUNCTIONS.items():
+        path = os.path.join(REF, "models", "cuda_funcs", fname)
+        for cls_name in classes:
+            names, n_def, slots = _reference_forward_params(path, cls_name)
+            cls = getattr(ours, cls_name)
+            sig = inspect.signature(cls.forward)
+            mine = list(sig.parameters)[1:]
+            assert mine == names, (cls_name, mine, names)
+            my_defaults = [p for p in list(sig.parameters.values())[1:] if p.default is not inspect.Parameter.empty]
+            assert len(my_defaults) == n_def, (cls_name, len(my_defaults), n_def)
+            assert all(p.default is None for p in my_defaults), cls_name        # the reference's defaults are all None
+
+
+def test_compile_kernels_signature_matches_the_reference():
+    from crystalframer_b200.cuda_funcs import compile_kernels
+    tree = ast.parse(open(os.path.join(REF, "models", "cuda_funcs", "kernel_manager.py")).read())
+    fn = next(n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name == "compile_kernels")
+    assert [a.arg for a in fn.args.args] == list(inspect.signature(compile_kernels).parameters)
+
+
+def test_reference_attention_module_imports_with_this_package_swapped_in():
+    """``models.cuda_funcs`` replaced by this package's ``cuda_funcs``: the reference's attention module must import
+    and every Function it names on the supported branches must be this package's class."""
+    import crystalframer_b200.cuda_funcs as ours
+    saved = {k: sys.modules.get(k) for k in list(sys.modules) if k == "models" or k.startswith("models.")}
+    for k in saved:
+        del sys.modules[k]
+    pkg = types.ModuleType("models")
+    pkg.__path__ = [os.path.join(REF, "models")]
+    sys.modules["models"] = pkg
+    sys.modules["models.cuda_funcs"] = ours
+    try:
+        import importlib
+        mod = importlib.import_module("models.indexed_lattice_multi_head_attention_cuda")
+        for classes in FUNCTIONS.values():
+            for cls_name in classes:
+                if cls_name == "IrregularMeanCUDA":
+                    continue                          # used by models/pooling.py, not by the attention module
+                assert getattr(mod, cls_name) is getattr(ours, cls_name), cls_name
+        assert mod.CUPY_AVAILABLE is True
+        # the module class the encoder instantiates, with the constructor this package mirrors
+        ref_init = list(inspect.signature(mod.CrystalformerMultiheadAttentionCUDA.__init__).parameters)
+        from crystalframer_b200.attention import CrystalformerMultiheadAttentionCUDA
+        assert list(inspect.signature(CrystalformerMultiheadAttentionCUDA.__init__).parameters) == ref_init
+        ref_fwd = list(inspect.signature(mod.CrystalformerMultiheadAttentionCUDA.forward).parameters)
+        assert list(inspect.signature(CrystalformerMultiheadAttentionCUDA.forward).parameters) == ref_fwd
+    finally:
+        for k in [k for k in sys.modules if k == "models" or k.startswith("models.")]:
+            del sys.modules[k]
+        sys.modules.update({k: v for k, v in saved.items() if v is not None})
+
+
+def test_parameter_names_and_shapes_match_the_reference_module():
+    """state_dict keys and shapes of the attention module: reference checkpoints must load."""
+    import torch
+    import crystalframer_b200.cuda_funcs as ours
+    from crystalframer_b200.attention import CrystalformerMultiheadAttentionCUDA
+    from crystalframer_b200.latticeformer_params import LatticeformerParams
+    saved = {k: sys.modules.get(k) for k in list(sys.modules) if k == "models" or k.startswith("models.")}
+    for k in saved:
+        del sys.modules[k]
+    pkg = types.ModuleType("models")
+    pkg.__path__ = [os.path.join(REF, "models")]
+    sys.modules["models"] = pkg
+    sys.modules["models.cuda_funcs"] = ours
+    try:
+        import importlib
+        mod = importlib.import_module("models.indexed_lattice_multi_head_attention_cuda")
+        ref_params = importlib.import_module("models.latticeformer_params").LatticeformerParams()
+        mine_params = LatticeformerParams()
+        for P in (ref_params, mine_params):
+            P.domain, P.frame_method = "real", "max"
+            P.value_pe_dist_real, P.value_pe_angle_real = 64, 64
+        torch.manual_seed(0)
+        ref = mod.CrystalformerMultiheadAttentionCUDA(128, 8, params=ref_params)
+        mine = CrystalformerMultiheadAttentionCUDA(128, 8, params=mine_params)
+        a, b = ref.state_dict(), mine.state_dict()
+        assert list(a) == list(b)
+        assert all(a[k].shape == b[k].shape for k in a)
+        mine.load_state_dict(a)
+    finally:
+        for k in [k for k in sys.modules if k == "models" or k.startswith("models.")]:
+            del sys.modules[k]
+        sys.modules.update({k: v for k, v in saved.items() if v is not None})

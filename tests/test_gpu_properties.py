@@ -115,6 +115,15 @@ def test_golden_fixture_of_the_reference_kernels():
         _close(n, t.grad, G[n])
     m = F.IrregularMeanCUDA.apply(_t(G["mean_x"], dev), batch, sizes)
     _close("mean", m, G["mean"])
+    # frame methods "max_static" and "lattice": outputs of the reference's kernels, bit for bit
+    s1, se1, _ = F.max_static_frame_with_selection(1, a, pos_ij, tv, batch, edges, rvlen, -3.5)
+    assert np.array_equal(se1.cpu().numpy(), G["static_sel_edge1"]) and np.array_equal(s1.cpu().numpy(), G["static_frame1"])
+    s2, se2, _ = F.max_static_frame_with_selection(2, a, pos_ij, tv, batch, edges, rvlen, -3.5, s1)
+    assert np.array_equal(se2.cpu().numpy(), G["static_sel_edge2"])
+    _close("static frame2_max", s2, G["static_frame2_max"], 1e-6, 1e-6)
+    lat = F.ComputeLatticeFrameCUDA.apply(q / 4.0, k, None, a, pos_ij, None, tv, batch, edges, 64, 14.0, 1.0, rvlen, -3.5)
+    for x in range(3):
+        assert np.array_equal(lat[x].cpu().numpy(), G[f"lattice_frame{x + 1}"])
 
 
 def test_empty_batch_and_single_atoms():
@@ -224,6 +233,29 @@ def test_status_word_reports_bad_coefficients():
     assert st & 1, st                   # CFB200_STATUS_BAD_COEF
     _encode(F, D, D["a"], D["W"], fr)
     assert _lib.read_status() == 0      # reading clears the word
+
+
+def test_status_word_reports_a_pair_list_that_is_not_dense():
+    """The kernels read keys and per-pair rows of one atom as consecutive; a pair list whose columns are permuted
+    inside an atom's block (still valid indices) is reported, not silently mis-summed."""
+    dev = _cuda()
+    F = _configure()
+    from crystalframer_b200 import _lib
+    D = _device_problem(dev, "cfg1")
+    N, H = D["a"].shape
+    gen = torch.Generator(device="cpu").manual_seed(0)
+    q, k, v = (torch.randn(N, H, 16, generator=gen).to(dev) for _ in range(3))
+    E = D["edges"].shape[1]
+    z, val = torch.zeros(E, H, device=dev), torch.zeros(E, H, 16, device=dev)
+    _lib.read_status()
+    F.FusedDotProductAttentionCUDA.apply(q, k, v, z, val, D["batch"], D["edges"])
+    assert _lib.read_status() == 0
+    edges = D["edges"].clone()
+    same = (edges[0, 1:] == edges[0, :-1]).nonzero()      # two consecutive pairs of one atom: swap their keys
+    e = int(same[0])
+    edges[1, e], edges[1, e + 1] = D["edges"][1, e + 1], D["edges"][1, e]
+    F.FusedDotProductAttentionCUDA.apply(q, k, v, z, val, D["batch"], edges)
+    assert _lib.read_status() & 16                        # CFB200_ST_PAIR_LAYOUT
 
 
 def test_properties_at_benchmark_size():

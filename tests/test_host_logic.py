@@ -56,6 +56,15 @@ def test_partition_by_pair_count_balances():
     assert sorted(np.concatenate(parts).tolist()) == list(range(len(b.sizes)))
     loads = np.array([cost[p].sum() for p in parts])
     assert loads.max() - loads.min() <= cost.max()
+    # the counted cost: per pair, the translations of the 5x5x5 block above the pruning threshold
+    from crystalframer_b200.parallel import attention_cost_counted
+    small = synth.make_workload("cfg2", num_crystals=32)
+    counted = attention_cost_counted(small.pos, small.trans_vec, small.sizes)
+    n2 = small.sizes.astype(np.float64) ** 2
+    assert counted.shape == small.sizes.shape
+    assert (counted >= (350.0 + 70.0) * n2).all() and (counted <= (350.0 + 70.0 * 125) * n2).all()
+    one = attention_cost_counted(small.pos[:small.sizes[0]], small.trans_vec[:1], small.sizes[:1])
+    assert one[0] == counted[0]
 
 
 def _worker(rank, world, port, q):

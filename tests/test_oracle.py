@@ -57,6 +57,12 @@ def test_golden_reference_kernels():
     for n, x in zip(("gq", "gk", "gvv", "gaij", "gbij"), res):
         close(n, x, G[n])
     close("mean", O.mean_fwd(G["mean_x"], G["sizes"]), G["mean"])
+    st = O.max_static_frames(cfg, G["a"], g["pos_ij"], G["cells"], g["rvlen"], g["batch"], g["edges"], g["e_start"])
+    assert np.array_equal(st["sel_edge1"], G["static_sel_edge1"]) and np.array_equal(st["sel_edge2"], G["static_sel_edge2"])
+    assert np.array_equal(st["frame1"], G["static_frame1"]) and np.array_equal(st["frame2_max"], G["static_frame2_max"])
+    lat = O.lattice_frames(cfg, G["a"], G["cells"], g["rvlen"], g["batch"], g["edges"], g["e_start"])
+    for x in range(3):
+        assert np.array_equal(lat[x], G[f"lattice_frame{x + 1}"])
 
 
 def test_golden_pure_pytorch_twin():
