@@ -37,11 +37,11 @@ class LayerGrads(ctypes.Structure):            # cfb200_layer_grads
 
 class Geometry(ctypes.Structure):              # cfb200_geometry
     _fields_ = [(n, vp) for n in ("pos_ij", "tvecs", "rvlen", "batch", "edges", "e_start", "order", "counters",
-                                  "pair_cache", "pair_list")] + [("N", i64), ("E", i64), ("cache_range", i32)]
+                                  "pair_cache", "pair_list")] + [("N", i64), ("E", i64), ("cache_range", i32), ("split", vp)]
 
 
 class LayerState(ctypes.Structure):            # cfb200_layer_state
-    _fields_ = [(n, vp) for n in ("q", "q_scaled", "k", "v", "a", "frames", "z", "spool", "attn", "lse", "x1", "h")]
+    _fields_ = [(n, vp) for n in ("q", "q_scaled", "k", "v", "a", "frames", "z", "spool", "attn", "lse", "x1", "h", "tasks")]
 
 
 class LayerDesc(ctypes.Structure):             # cfb200_layer_desc
@@ -88,7 +88,10 @@ SIGNATURES = {
     "cfb200_segment_mean_bwd": (ctypes.c_int, [vp, vp, i64, i64, vp, vp]),
     "cfb200_adamw_clip_step": (ctypes.c_int, [vp] * 4 + [i64, i64] + [f32] * 6 + [ctypes.c_double, ctypes.c_double, vp, vp, vp]),
     "cfb200_batch_geometry_workspace_bytes": (i64, [i64]),
-    "cfb200_batch_geometry": (ctypes.c_int, [vp, vp, vp, i64, i64, i64, ctypes.c_int] + [vp] * 11 + [vp, i64, vp]),
+    "cfb200_queue_entries": (i64, [i64]),
+    "cfb200_split_ints": (i64, [i64]),
+    "cfb200_attn_tasks_bytes": (i64, [i64]),
+    "cfb200_batch_geometry": (ctypes.c_int, [vp, vp, vp, i64, i64, i64, ctypes.c_int] + [vp] * 12 + [vp, i64, vp]),
     "cfb200_encoder_layer_workspace_bytes": (i64, [i64, i64, ctypes.c_int, ctypes.c_int, ctypes.c_int]),
     "cfb200_encoder_layer_fwd": (ctypes.c_int, [vp, vp, vp, vp, vp, vp, vp, i64, vp]),
     "cfb200_encoder_layer_bwd": (ctypes.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, ctypes.c_int, vp, i64, vp]),

@@ -20,6 +20,14 @@
 // distance part unscaled and the angle parts times the angle coefficient (the scaling the reference's
 // weight gradients carry).  The backward leaves gz (E,H) for the column pass that forms gk and gv
 // (dpa_bwd_cols_kernel), gq (N,H,16) with respect to the scaled query, and ga (N,H).
+//
+// Chunked queue (kernels instantiated with TASKS): one warp walks the pairs of an (atom, head) one after the other, so an
+// atom of a dense 64-atom cell with a wide Gaussian can take several times a warp's average load and the launch
+// would end with that warp alone.  attn_plan_kernel turns the batch's work queue (atom_order_kernel) and the layer's
+// coefficients into a table of tasks per head: an atom whole, or one chunk of its pairs.  A chunk is computed exactly
+// like an atom with fewer pairs and leaves its result in a partial row; attn_merge_fwd / _bwd_kernel combine the
+// rows of an atom in chunk order (softmax-weighted by the chunks' log-sum-exp; plain sums backward), so results do
+// not depend on which warp ran what.
 #include <atomic>
 #include "lattice_lane.cuh"
 
@@ -39,6 +47,11 @@ struct AtArgs {
     const float* pos_ij; const float* tvecs; const float* rvlen;
     const int64_t* batch; const int64_t* edges; const int64_t* e_start; const int32_t* order;
     int* counters;            // (H) work-queue heads, zeroed before the launch
+    // task table of the chunked queue (attn_plan_kernel), or NULL: then ``order`` (or the atom index) is the queue
+    const int4* tasks; int64_t n_entries;
+    int* chunk_count;         // (H) chunk entries in use per head: they sit at the end of the chunk region
+    float* part_out; float* part_lse; float* part_spool;               // forward results of chunks (kSplitSlots rows)
+    float* part_gq; float* part_ga;                                    // backward results of chunks
     int64_t N, E;
     const float* W[4]; const float* frame[3];
     const float* list; int cache_range;
@@ -105,7 +118,7 @@ __device__ __forceinline__ int64_t next_task(int* counter, const int lane)
     return (int64_t)__shfl_sync(0xffffffffu, t, 0);
 }
 
-template <bool ANG>
+template <bool ANG, bool TASKS>
 __global__ void __launch_bounds__(at_warps(false) * 32, kAtFwdBlocks) attn_fwd_kernel(const AtArgs A, const Params P)
 {
     extern __shared__ __align__(16) float smem[];
@@ -124,12 +137,26 @@ __global__ void __launch_bounds__(at_warps(false) * 32, kAtFwdBlocks) attn_fwd_k
     L.init(P, lane, tbuf + warp * 6 * 32);
     float* srow = rows + warp * kAtK;
     __syncthreads();
+    // the queue of this head begins where its chunk entries begin
+    const int first = TASKS ? kSplitSlots - __ldg(A.chunk_count + h) : 0;
 
     for (;;) {
-        const int64_t t = next_task(A.counters + h, lane);
-        if (t >= A.N) break;
-        const int64_t i = A.order != nullptr ? (int64_t)A.order[t] : t;
-        const AtomTask T = load_atom<false, ANG>(A, P, L, i, h, lane);
+        const int64_t t = next_task(A.counters + h, lane) + first;
+        if (t >= (TASKS ? A.n_entries : A.N)) break;
+        int64_t i, row;
+        AtomTask T;
+        if (TASKS) {
+            const int4 d = __ldg(A.tasks + (size_t)h * A.n_entries + t);
+            const int cnt = d.w & 0xFFFFFF;
+            if (cnt == 0) continue;                         // an entry this head does not use
+            i = d.x; row = d.y;
+            T = load_atom<false, ANG>(A, P, L, i, h, lane);
+            T.e0 += d.z; T.e1 = T.e0 + cnt;
+        } else {
+            i = A.order != nullptr ? (int64_t)A.order[t] : t;
+            row = i;
+            T = load_atom<false, ANG>(A, P, L, i, h, lane);
+        }
         const float qd = lane < kAtHd ? __ldg(A.qs + (i * H + h) * kAtHd + lane) : 0.f;
         float m = -INFINITY, l = 0.f, V = 0.f;
         float S[8];
@@ -162,10 +189,13 @@ __global__ void __launch_bounds__(at_warps(false) * 32, kAtFwdBlocks) attn_fwd_k
             m = mn;
         }
         const float inv_l = T.e1 > T.e0 ? 1.0f / l : 0.f;
-        if (lane == 0) A.lse[i * H + h] = m + logf(l);
+        // an atom's results go to its row, a chunk's to a partial row (numbered from N)
+        const bool partial = TASKS && row >= A.N;
+        if (partial) row -= A.N;
+        if (lane == 0) (partial ? A.part_lse : A.lse)[row * H + h] = m + logf(l);
         // pooled basis: to memory with the scaling of the weight gradients, to shared memory with the
         // scaling of the values
-        float* sp = A.spool + (i * H + h) * kAtK;
+        float* sp = (partial ? A.part_spool : A.spool) + (row * H + h) * kAtK;
         {
             const float d0 = S[0] * inv_l, d1 = S[1] * inv_l;
             sp[lane] = d0; sp[32 + lane] = d1;
@@ -190,13 +220,13 @@ __global__ void __launch_bounds__(at_warps(false) * 32, kAtFwdBlocks) attn_fwd_k
                 acc = fmaf(s4.x, u.x, fmaf(s4.y, u.y, fmaf(s4.z, u.z, fmaf(s4.w, u.w, acc))));
             }
             acc += __shfl_xor_sync(0xffffffffu, acc, 16);
-            if (lane < kAtHd) A.out[(i * H + h) * kAtHd + lane] = fmaf(V, inv_l, acc);
+            if (lane < kAtHd) (partial ? A.part_out : A.out)[(row * H + h) * kAtHd + lane] = fmaf(V, inv_l, acc);
         }
         __syncwarp();
     }
 }
 
-template <bool ANG>
+template <bool ANG, bool TASKS>
 __global__ void __launch_bounds__(at_warps(true) * 32, kAtBwdBlocks) attn_bwd_kernel(const AtArgs A, const Params P)
 {
     extern __shared__ __align__(16) float smem[];
@@ -217,12 +247,25 @@ __global__ void __launch_bounds__(at_warps(true) * 32, kAtBwdBlocks) attn_bwd_ke
     L.init(P, lane, tbuf + warp * 8 * 32);
     float* grow = rows + warp * 32;
     __syncthreads();
+    const int first = TASKS ? kSplitSlots - __ldg(A.chunk_count + h) : 0;
 
     for (;;) {
-        const int64_t t = next_task(A.counters + h, lane);
-        if (t >= A.N) break;
-        const int64_t i = A.order != nullptr ? (int64_t)A.order[t] : t;
-        const AtomTask T = load_atom<true, ANG>(A, P, L, i, h, lane);
+        const int64_t t = next_task(A.counters + h, lane) + first;
+        if (t >= (TASKS ? A.n_entries : A.N)) break;
+        int64_t i, row;
+        AtomTask T;
+        if (TASKS) {
+            const int4 d = __ldg(A.tasks + (size_t)h * A.n_entries + t);
+            const int cnt = d.w & 0xFFFFFF;
+            if (cnt == 0) continue;
+            i = d.x; row = d.y;
+            T = load_atom<true, ANG>(A, P, L, i, h, lane);
+            T.e0 += d.z; T.e1 = T.e0 + cnt;
+        } else {
+            i = A.order != nullptr ? (int64_t)A.order[t] : t;
+            row = i;
+            T = load_atom<true, ANG>(A, P, L, i, h, lane);
+        }
         float qd = 0.f, god = 0.f, od = 0.f;
         if (lane < kAtHd) {
             qd = __ldg(A.qs + (i * H + h) * kAtHd + lane);
@@ -297,8 +340,10 @@ __global__ void __launch_bounds__(at_warps(true) * 32, kAtBwdBlocks) attn_bwd_ke
             ga_acc += fmaf(P.c_dist * px, gzv, p_att * (cA - px * cB));
             gq = fmaf(gzv, kd, gq);
         }
-        if (lane == 0) A.ga[i * H + h] = ga_acc;
-        if (lane < kAtHd) A.gq[(i * H + h) * kAtHd + lane] = gq;
+        const bool partial = TASKS && row >= A.N;
+        if (partial) row -= A.N;
+        if (lane == 0) (partial ? A.part_ga : A.ga)[row * H + h] = ga_acc;
+        if (lane < kAtHd) (partial ? A.part_gq : A.gq)[(row * H + h) * kAtHd + lane] = gq;
     }
 }
 
@@ -314,10 +359,103 @@ static int at_grid_x(int64_t N, int H, bool bwd)
     return (int)want;
 }
 
-template <bool BWD, bool ANG>
+// thread = (queue entry, head): the task table.  Entry (x, y, z, w) = atom, result row (the atom, or N + partial row of
+// a chunk), offset of the first pair within the atom's pairs, pairs | chunks in use << 24 | (chunk == 1) << 28;
+// w = 0: nothing to do.  split: the chunked queue of atom_order_kernel (chunks 1.. in the first kSplitSlots entries,
+// then the atoms).
+__global__ void __launch_bounds__(256) attn_plan_kernel(const int32_t* __restrict__ order, const int32_t* __restrict__ split,
+                                                        const float* __restrict__ a_ik, const int64_t* __restrict__ e_start,
+                                                        int64_t N, int64_t n_entries, int H, int* __restrict__ chunk_count,
+                                                        int4* __restrict__ tasks)
+{
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int h = blockIdx.y;
+    if (t >= n_entries) return;
+    int4 d = make_int4(0, 0, 0, 0);
+    const int info = __ldg(split + 4 + 2 * t);
+    if (info != 0) {
+        const int i = __ldg(order + t);
+        const int chunks = (info >> 4) & 15, index = info & 15;
+        const int pairs = (int)(e_start[i + 1] - e_start[i]);
+        int active = 1;
+        if (chunks > 1)
+            active = split_active_chunks(__ldg(a_ik + (int64_t)i * H + h), pairs, __int_as_float(__ldg(split + 4 + 2 * t + 1)),
+                                         __int_as_float(__ldg(split + 1)), chunks);
+        if (index < active && pairs > 0) {
+            const int lo = pairs * index / active, hi = pairs * (index + 1) / active;
+            d.x = i;
+            d.y = active > 1 ? (int)N + (info >> 8) + index : i;
+            d.z = lo;
+            d.w = (hi - lo) | (active << 24) | ((index == 1 ? 1 : 0) << 28);
+        }
+    }
+    if (t >= kSplitSlots) {
+        tasks[(size_t)h * n_entries + t] = d;                    // an atom's entry keeps its place
+    } else if (d.w != 0) {
+        // chunk entries in use gather at the end of the chunk region, in any order (they are all about one target long)
+        const int pos = atomicAdd(chunk_count + h, 1);
+        tasks[(size_t)h * n_entries + (kSplitSlots - 1 - pos)] = d;
+    }
+}
+
+// warp = (entry of the queue's chunk region, head): where the entry is chunk 1 of a task (so the task was cut), the
+// chunks' results are combined in chunk order.  Forward: chunk c holds the attention output, pooled basis and
+// log-sum-exp over its own pairs; the whole is their average weighted by exp(lse_c - lse).
+__global__ void __launch_bounds__(256) attn_merge_fwd_kernel(const AtArgs A, const int H)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int h = blockIdx.y;
+    if (t >= kSplitSlots || t < kSplitSlots - __ldg(A.chunk_count + h)) return;
+    const int4 d = __ldg(A.tasks + (size_t)h * A.n_entries + t);
+    const int active = (d.w >> 24) & 15;
+    if (!((d.w >> 28) & 1)) return;
+    const int64_t i = d.x, r0 = d.y - A.N - 1;
+    float m = -INFINITY;
+    for (int c = 0; c < active; c++) m = fmaxf(m, __ldg(A.part_lse + (r0 + c) * H + h));
+    float wsum = 0.f;
+    for (int c = 0; c < active; c++) wsum += __expf(__ldg(A.part_lse + (r0 + c) * H + h) - m);
+    float o = 0.f, s[8];
+#pragma unroll
+    for (int r = 0; r < 8; r++) s[r] = 0.f;
+    for (int c = 0; c < active; c++) {
+        const float w = __expf(__ldg(A.part_lse + (r0 + c) * H + h) - m) / wsum;
+        if (lane < kAtHd) o = fmaf(w, __ldg(A.part_out + ((r0 + c) * H + h) * kAtHd + lane), o);
+        const float* sp = A.part_spool + ((r0 + c) * H + h) * kAtK;
+#pragma unroll
+        for (int r = 0; r < 8; r++) s[r] = fmaf(w, __ldg(sp + r * 32 + lane), s[r]);
+    }
+    if (lane == 0) A.lse[i * H + h] = m + logf(wsum);
+    if (lane < kAtHd) A.out[(i * H + h) * kAtHd + lane] = o;
+#pragma unroll
+    for (int r = 0; r < 8; r++) A.spool[(i * H + h) * kAtK + r * 32 + lane] = s[r];
+}
+
+// Backward: the chunks' parts of the query gradient and of the coefficient gradient are summed in chunk order.
+__global__ void __launch_bounds__(256) attn_merge_bwd_kernel(const AtArgs A, const int H)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int h = blockIdx.y;
+    if (t >= kSplitSlots || t < kSplitSlots - __ldg(A.chunk_count + h)) return;
+    const int4 d = __ldg(A.tasks + (size_t)h * A.n_entries + t);
+    const int active = (d.w >> 24) & 15;
+    if (!((d.w >> 28) & 1)) return;
+    const int64_t i = d.x, r0 = d.y - A.N - 1;
+    float gq = 0.f, ga = 0.f;
+    for (int c = 0; c < active; c++) {
+        if (lane < kAtHd) gq += __ldg(A.part_gq + ((r0 + c) * H + h) * kAtHd + lane);
+        ga += __ldg(A.part_ga + (r0 + c) * H + h);
+    }
+    if (lane == 0) A.ga[i * H + h] = ga;
+    if (lane < kAtHd) A.gq[(i * H + h) * kAtHd + lane] = gq;
+}
+
+template <bool BWD, bool ANG, bool TASKS>
 static int launch_at(const AtArgs& A, const Params& P, cudaStream_t st)
 {
-    auto kern = BWD ? (void (*)(const AtArgs, const Params))attn_bwd_kernel<ANG> : (void (*)(const AtArgs, const Params))attn_fwd_kernel<ANG>;
+    auto kern = BWD ? (void (*)(const AtArgs, const Params))attn_bwd_kernel<ANG, TASKS>
+                    : (void (*)(const AtArgs, const Params))attn_fwd_kernel<ANG, TASKS>;
     static std::atomic<bool> attr_done[64];   // per instantiation and device
     int dev = 0;
     cudaGetDevice(&dev);
@@ -327,6 +465,22 @@ static int launch_at(const AtArgs& A, const Params& P, cudaStream_t st)
         attr_done[dev & 63] = true;
     }
     kern<<<dim3(at_grid_x(A.N, P.H, BWD), P.H), at_warps(BWD) * 32, at_smem_bytes(BWD), st>>>(A, P);
+    if (TASKS) {
+        const dim3 grid(kSplitSlots / 8, P.H);
+        if (BWD) attn_merge_bwd_kernel<<<grid, 256, 0, st>>>(A, P.H);
+        else attn_merge_fwd_kernel<<<grid, 256, 0, st>>>(A, P.H);
+    }
+    return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
+}
+
+// the task table of one layer (both directions use it)
+int attn_plan(const int32_t* order, const int32_t* split, const float* a_ik, const int64_t* e_start, int64_t N,
+              int64_t n_entries, int H, int* chunk_count, int4* tasks, cudaStream_t st)
+{
+    if (n_entries <= 0) return CFB200_OK;
+    if (cudaMemsetAsync(chunk_count, 0, sizeof(int) * H, st) != cudaSuccess) return CFB200_E_CUDA;
+    attn_plan_kernel<<<dim3((unsigned)((n_entries + 255) / 256), H), 256, 0, st>>>(order, split, a_ik, e_start, N, n_entries, H,
+                                                                                  chunk_count, tasks);
     return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
 }
 
@@ -334,14 +488,16 @@ int attn_fused_fwd(const AtArgs& A, const Params& P, cudaStream_t st)
 {
     if (A.N == 0) return CFB200_OK;
     if (cudaMemsetAsync(A.counters, 0, sizeof(int) * P.H, st) != cudaSuccess) return CFB200_E_CUDA;
-    return A.W[1] != nullptr ? launch_at<false, true>(A, P, st) : launch_at<false, false>(A, P, st);
+    if (A.tasks != nullptr) return A.W[1] != nullptr ? launch_at<false, true, true>(A, P, st) : launch_at<false, false, true>(A, P, st);
+    return A.W[1] != nullptr ? launch_at<false, true, false>(A, P, st) : launch_at<false, false, false>(A, P, st);
 }
 
 int attn_fused_bwd(const AtArgs& A, const Params& P, cudaStream_t st)
 {
     if (A.N == 0) return CFB200_OK;
     if (cudaMemsetAsync(A.counters, 0, sizeof(int) * P.H, st) != cudaSuccess) return CFB200_E_CUDA;
-    return A.W[1] != nullptr ? launch_at<true, true>(A, P, st) : launch_at<true, false>(A, P, st);
+    if (A.tasks != nullptr) return A.W[1] != nullptr ? launch_at<true, true, true>(A, P, st) : launch_at<true, false, true>(A, P, st);
+    return A.W[1] != nullptr ? launch_at<true, true, false>(A, P, st) : launch_at<true, false, false>(A, P, st);
 }
 
 }  // namespace cfb

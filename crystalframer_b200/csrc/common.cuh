@@ -78,6 +78,31 @@ constexpr int kListLen = 128;
 constexpr int kListPlanes = 5;
 constexpr int kListStride = kListLen * kListPlanes;
 
+// Work estimate of the fused attention kernels, in warp instructions: one pair of an (atom, head) task costs about
+// kAtPairCost plus kAtTermCost per translation that survives the pruning.
+constexpr float kAtPairCost = 350.0f, kAtTermCost = 70.0f;
+// Long tasks are cut into chunks of consecutive pairs whose partial results a small kernel merges afterwards
+// (see atom_order_kernel and attn_fused.cu): at most kSplitMaxChunks chunks of at least kSplitMinPairs pairs,
+// kSplitSlots partial rows per head, no task below kSplitMinTarget instructions is cut.  kSplitWideSphere: volume of
+// the pruning sphere (radius^2 = 16 / |a|) of a Gaussian two standard deviations wider than typical (|a| = 0.051).
+constexpr int kSplitSlots = CFB200_SPLIT_SLOTS, kSplitMaxChunks = 8, kSplitMinPairs = 4;
+constexpr float kSplitMinTarget = 20000.0f, kSplitWideSphere = 23200.0f, kSplitWideCap = 1500.0f;
+constexpr int kSplitPartFwd = 288, kSplitPartBwd = 32;       // floats per partial row and head (273 and 17 used)
+
+// Chunks an (atom, head) task with `pairs` pairs really uses, of the `chunks` its crystal was given: its own
+// instruction estimate (translations within the pruning radius of its coefficient a) over the target.  Every warp
+// that draws a chunk of the task computes the same number.
+__device__ __forceinline__ int split_active_chunks(const float a, const int pairs, const float inv_vol, const float target,
+                                                   const int chunks)
+{
+    const float aa = fmaxf(fabsf(a), 1e-6f);
+    const float sphere = 268.08f / (aa * sqrtf(aa)) * inv_vol;          // 4/3 pi (16 / |a|)^(3/2) / volume
+    const float terms = fminf(kSplitWideCap, fmaxf(sphere, 1.0f));
+    const float est = (float)pairs * (kAtPairCost + kAtTermCost * terms);
+    const float want = ceilf(est / target);
+    return want >= (float)chunks ? chunks : max((int)want, 1);
+}
+
 // Lattice range along one reciprocal axis for Gaussian coefficient a (< 0):
 // models/kernels/real_enc_frame_proj_fwd_length.cu:59-86.  (cutoff + 0.01f) * rvl is a float
 // product, the division by 2.0 * CUDART_PI_F and the ceil are double, as in the reference.

@@ -13,12 +13,14 @@ namespace cfb {
 
 // ---- per-crystal cell quantities ------------------------------------------------------------------------
 // thread = crystal: reciprocal vectors 2 pi (b x c, c x a, a x b) / det, their lengths, the cell volume, and
-// the work-queue key of the crystal's atoms: size x (7 + translations in reach of a Gaussian of typical width,
+// the work-queue key of the crystal's atoms, an instruction estimate of one (atom, head) task of the attention
+// kernels: size x (cost of a pair + cost of a translation x translations in reach of a Gaussian of typical width,
 // about a sphere of radius 8 A over the cell volume, between 1 and 125).
 // (models/indexed_latticeformer_encoder.py:205-222, models/indexed_lattice_multi_head_attention_cuda.py:539.)
 __global__ void __launch_bounds__(128) cell_kernel(const float* __restrict__ tvecs, const int64_t* __restrict__ sizes, int64_t B,
                                                    float* __restrict__ rvecs, float* __restrict__ rvlen,
-                                                   float* __restrict__ vcell, float* __restrict__ key)
+                                                   float* __restrict__ vcell, float* __restrict__ key,
+                                                   float* __restrict__ inv_vol)
 {
     const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= B) return;
@@ -47,7 +49,8 @@ __global__ void __launch_bounds__(128) cell_kernel(const float* __restrict__ tve
     if (vcell != nullptr) vcell[c] = det;
     const float vol = fmaxf(fabsf(det), 1e-6f);
     const float survivors = fminf(fmaxf(2145.0f / vol, 1.0f), 125.0f);
-    key[c] = (float)sizes[c] * (7.0f + survivors);
+    key[c] = (float)sizes[c] * (kAtPairCost + kAtTermCost * survivors);
+    if (inv_vol != nullptr) inv_vol[c] = 1.0f / vol;
 }
 
 // thread = pair: separation of the pair's atoms in the home cell
@@ -61,17 +64,54 @@ __global__ void __launch_bounds__(256) pos_ij_kernel(const float* __restrict__ p
     for (int d = 0; d < 3; d++) pos_ij[3 * e + d] = __fsub_rn(__ldg(pos + 3 * j + d), __ldg(pos + 3 * i + d));
 }
 
-// One block: the order in which the attention kernels' work queue hands out atoms -- crystals by
-// decreasing key (equal keys in index order), the atoms of a crystal in their own order.  This is the
-// stable descending sort of the atoms by their crystal's key.  rank by counting, then a scan of the
-// sizes in rank order.  ``rank_of`` (B ints) and ``start_of`` (B ints) are scratch.
-__global__ void __launch_bounds__(1024) atom_order_kernel(const float* __restrict__ key, const int64_t* __restrict__ sizes,
-                                                          const int64_t* __restrict__ crystal_start, int64_t B,
-                                                          int32_t* __restrict__ by_rank, int32_t* __restrict__ start_of,
-                                                          int32_t* __restrict__ order)
+// exclusive scan of v over the block's threads (blockDim.x a multiple of 32, at most 1024); returns the value
+// before this thread's and leaves the block's total in *total (shared).  tmp: 32 shared ints.
+__device__ __forceinline__ int block_scan_exclusive(const int v, int* tmp, int* total)
 {
-    __shared__ int warp_tot[32];
-    __shared__ int carry;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int s = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, s, o); if (lane >= o) s += t; }
+    if (lane == 31) tmp[warp] = s;
+    __syncthreads();
+    if (warp == 0) {
+        int w = lane < (int)(blockDim.x >> 5) ? tmp[lane] : 0;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, w, o); if (lane >= o) w += t; }
+        tmp[lane] = w;
+    }
+    __syncthreads();
+    const int out = (warp ? tmp[warp - 1] : 0) + s - v;
+    if (threadIdx.x == blockDim.x - 1) *total = out + v;
+    __syncthreads();
+    return out;
+}
+
+// One block: the work queue of the attention kernels -- crystals by decreasing key (equal keys in index
+// order, ranked by counting), the atoms of a crystal in their own order.
+//
+// Without ``split``, ``order`` holds the N atoms.  With it the queue also cuts long tasks into chunks (see
+// attn_fused.cu): a crystal whose atoms may be expensive (cost of an atom for a Gaussian two standard deviations
+// wider than typical, against ``target`` = half the average load per warp at typical width) gets ``want`` chunks
+// per atom and want partial rows per atom.  Queue layout: kSplitSlots entries for the chunks 1 .. want-1 (heaviest
+// crystal first; the unused rest empty), then the N atoms, whose entries stand for chunk 0 or for the whole task.
+// How many chunks an (atom, head) really uses is decided per layer from its own coefficient (attn_plan_kernel).
+// split (int32): [0] chunk entries in use, [1] bits of target, [2] partial rows in use, [3] 0; then
+// (info, bits of 1/volume) per queue entry, info = chunk | chunks << 4 | first partial row << 8 (0: empty entry).
+__global__ void __launch_bounds__(1024) atom_order_kernel(const float* __restrict__ key, const float* __restrict__ inv_vol,
+                                                          const int64_t* __restrict__ sizes,
+                                                          const int64_t* __restrict__ crystal_start, int64_t B, int64_t N,
+                                                          int workers, int32_t* __restrict__ by_rank,
+                                                          int32_t* __restrict__ start_of, int32_t* __restrict__ want_of,
+                                                          int32_t* __restrict__ slot_of, int32_t* __restrict__ order,
+                                                          int32_t* __restrict__ split)
+{
+    __shared__ int tmp[32];
+    __shared__ int total;
+    __shared__ float red[32];
+    __shared__ float target_s;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float load = 0.f;                                           // sum over atoms of their key
     for (int64_t c = threadIdx.x; c < B; c += blockDim.x) {
         const float kc = key[c];
         int rank = 0;
@@ -80,35 +120,93 @@ __global__ void __launch_bounds__(1024) atom_order_kernel(const float* __restric
             rank += (ko > kc || (ko == kc && o < c)) ? 1 : 0;
         }
         by_rank[rank] = (int32_t)c;
+        load += kc * (float)sizes[c];
     }
-    if (threadIdx.x == 0) carry = 0;
+    load = warp_sum(load);
+    if (lane == 0) red[warp] = load;
     __syncthreads();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int w = 0; w < (int)(blockDim.x >> 5); w++) t += red[w];          // fixed order
+        target_s = fmaxf(0.5f * t / (float)max(workers, 1), kSplitMinTarget);
+    }
+    __syncthreads();
+    const float target = target_s;
+    const int base_atoms = split != nullptr ? kSplitSlots : 0;  // where the atoms' entries begin
+    // chunks wanted per crystal and its partial rows, in rank order; crystals that find no rows left stay whole
+    int carry = 0, used = 0;
+    for (int64_t base = 0; base < B; base += blockDim.x) {
+        const int64_t r = base + threadIdx.x;
+        int want = 1, n = 0;
+        if (r < B && split != nullptr) {
+            const int c = by_rank[r];
+            n = (int)sizes[c];
+            const float wide = fminf(kSplitWideSphere * __ldg(inv_vol + c), kSplitWideCap);
+            const float heavy = (float)n * (kAtPairCost + kAtTermCost * fmaxf(wide, 1.0f));
+            want = (int)ceilf(heavy / target);
+            want = max(1, min(want, min(kSplitMaxChunks, n / kSplitMinPairs)));
+        }
+        const int cnt = want > 1 ? n * want : 0;
+        const int off = carry + block_scan_exclusive(cnt, tmp, &total);
+        if (r < B) {
+            const bool fits = off + cnt <= kSplitSlots;
+            want_of[r] = fits ? want : 1;
+            slot_of[r] = fits ? off : 0;
+            if (fits && cnt > 0) used = max(used, off + cnt);
+        }
+        carry += total;
+        __syncthreads();
+    }
+    if (split != nullptr) {                                     // partial rows in use: the largest end
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) used = max(used, __shfl_xor_sync(0xffffffffu, used, o));
+        if (lane == 0) tmp[warp] = used;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int u = 0;
+            for (int w = 0; w < (int)(blockDim.x >> 5); w++) u = max(u, tmp[w]);
+            split[1] = __float_as_int(target); split[2] = u; split[3] = 0;
+        }
+        __syncthreads();
+    }
+    // queue positions: every crystal's atoms once, and size x (chunks - 1) entries in the chunk region
+    int carry_atoms = 0, carry_chunks = 0;
     for (int64_t base = 0; base < B; base += blockDim.x) {
         const int64_t r = base + threadIdx.x;
         const int n = r < B ? (int)sizes[by_rank[r]] : 0;
-        int s = n;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, s, o); if (lane >= o) s += t; }
-        if (lane == 31) warp_tot[warp] = s;
+        const int extra = r < B ? n * (want_of[r] - 1) : 0;
+        const int off = carry_atoms + block_scan_exclusive(n, tmp, &total);
+        carry_atoms += total;
         __syncthreads();
-        if (warp == 0) {
-            int w = warp_tot[lane];
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, w, o); if (lane >= o) w += t; }
-            warp_tot[lane] = w;
-        }
+        const int off2 = carry_chunks + block_scan_exclusive(extra, tmp, &total);
+        carry_chunks += total;
         __syncthreads();
-        const int off = carry + (warp ? warp_tot[warp - 1] : 0);
-        if (r < B) start_of[r] = off + s - n;
-        __syncthreads();
-        if (threadIdx.x == blockDim.x - 1) carry = off + s;
-        __syncthreads();
+        if (r < B) { start_of[r] = off; want_of[r] |= off2 << 4; }      // chunk-region offset above the count
     }
-    for (int64_t r = warp; r < B; r += blockDim.x >> 5) {          // warp = crystal, lanes = its atoms
+    if (split != nullptr) {
+        if (threadIdx.x == 0) split[0] = carry_chunks;
+        for (int x = carry_chunks + threadIdx.x; x < kSplitSlots; x += blockDim.x) {     // the unused chunk entries
+            order[x] = 0; split[4 + 2 * x] = 0; split[4 + 2 * x + 1] = 0;
+        }
+    }
+    for (int64_t r = warp; r < B; r += blockDim.x >> 5) {          // warp = crystal, lanes = its entries
         const int c = by_rank[r];
-        const int n = (int)sizes[c], a0 = (int)crystal_start[c], o0 = start_of[r];
-        for (int t = lane; t < n; t += 32) order[o0 + t] = a0 + t;
+        const int n = (int)sizes[c], a0 = (int)crystal_start[c], o0 = base_atoms + start_of[r];
+        const int want = want_of[r] & 15, c0 = want_of[r] >> 4, s0 = slot_of[r];
+        const int vbits = split != nullptr ? __float_as_int(__ldg(inv_vol + c)) : 0;
+        for (int t = lane; t < n; t += 32) {
+            order[o0 + t] = a0 + t;
+            if (split != nullptr) {
+                split[4 + 2 * (o0 + t)] = (want << 4) | ((want > 1 ? s0 + t * want : 0) << 8);
+                split[4 + 2 * (o0 + t) + 1] = vbits;
+            }
+        }
+        for (int x = lane; x < n * (want - 1); x += 32) {          // chunks 1 .. want-1, chunk-major
+            const int k = 1 + x / n, t = x - (k - 1) * n;
+            order[c0 + x] = a0 + t;
+            split[4 + 2 * (c0 + x)] = k | (want << 4) | ((s0 + t * want) << 8);
+            split[4 + 2 * (c0 + x) + 1] = vbits;
+        }
     }
 }
 
@@ -176,6 +274,7 @@ int64_t layer_bwd_workspace_bytes(int64_t N, int64_t E, int D, int F, int H, boo
     b += pad256(cfb::wgrad_workspace_floats(N, layer_grad_outputs(D, F, H, angles)) * 4);
     b += pad256(D * 4);                           // gradient of lattice_pos before it is added to its destination
     b += pad256((int64_t)cfb::kCoSplits * D * 4);  // its partial sums over slices of the atoms
+    b += pad256((int64_t)cfb::kSplitSlots * H * cfb::kSplitPartBwd * 4);   // partial results of chunked attention tasks
     return b;
 }
 
@@ -183,12 +282,22 @@ int64_t layer_bwd_workspace_bytes(int64_t N, int64_t E, int D, int F, int H, boo
 
 extern "C" {
 
-int64_t cfb200_batch_geometry_workspace_bytes(int64_t B) { return B < 0 ? -1 : pad256(B * 4) * 3; }
+int64_t cfb200_batch_geometry_workspace_bytes(int64_t B) { return B < 0 ? -1 : pad256(B * 4) * 6; }
+
+int64_t cfb200_queue_entries(int64_t N) { return N < 0 ? -1 : N + cfb::kSplitSlots; }
+
+int64_t cfb200_split_ints(int64_t N) { return N < 0 ? -1 : 4 + 2 * (N + cfb::kSplitSlots); }
+
+int64_t cfb200_attn_tasks_bytes(int64_t N)
+{
+    if (!g_configured || N < 0) return -1;
+    return (N + cfb::kSplitSlots) * 16 * (int64_t)g_cfg.num_heads + 256;
+}
 
 int cfb200_batch_geometry(const float* pos, const float* tvecs, const int64_t* sizes, int64_t B, int64_t N, int64_t E,
                           int range, int64_t* edges, int64_t* e_start, int64_t* batch, int64_t* crystal_start,
                           float* pos_ij, float* rvecs, float* rvlen, float* vcell, float* pair_cache, float* pair_list,
-                          int32_t* order, void* workspace, int64_t workspace_bytes, void* stream)
+                          int32_t* order, int32_t* split, void* workspace, int64_t workspace_bytes, void* stream)
 {
     if (B < 0 || N < 0 || E < 0 || range < 0 || range > CFB200_MAX_RANGE) return CFB200_E_SHAPE;
     if (N > 0x7fffffff) return CFB200_E_TOO_LARGE;
@@ -200,14 +309,23 @@ int cfb200_batch_geometry(const float* pos, const float* tvecs, const int64_t* s
     float* key = ws.take<float>(B);
     int32_t* by_rank = ws.take<int32_t>(B);
     int32_t* start_of = ws.take<int32_t>(B);
+    int32_t* want_of = ws.take<int32_t>(B);
+    int32_t* slot_of = ws.take<int32_t>(B);
+    float* inv_vol = ws.take<float>(B);
     if (!ws.ok) return CFB200_E_WORKSPACE;
+    if (split != nullptr && !g_configured) return CFB200_E_NOT_CONFIGURED;
+    if (split != nullptr && B > 0x7ffffff) return CFB200_E_TOO_LARGE;
     cudaStream_t st = S(stream);
     TmScope tm(CFB200_TM_GEOMETRY, st);
     int rc = cfb::edge_index(sizes, B, N, E, edges, e_start, batch, crystal_start, st);
     if (rc != CFB200_OK) return rc;
-    cfb::cell_kernel<<<(unsigned)((B + 127) / 128), 128, 0, st>>>(tvecs, sizes, B, rvecs, rvlen, vcell, key);
+    cfb::cell_kernel<<<(unsigned)((B + 127) / 128), 128, 0, st>>>(tvecs, sizes, B, rvecs, rvlen, vcell, key, inv_vol);
     if (E > 0) cfb::pos_ij_kernel<<<(unsigned)((E + 255) / 256), 256, 0, st>>>(pos, edges, E, pos_ij);
-    cfb::atom_order_kernel<<<1, 1024, 0, st>>>(key, sizes, crystal_start, B, by_rank, start_of, order);
+    // warps that serve one head's queue in the attention kernels (the backward launch, which has the fewer)
+    const int heads = split != nullptr ? g_cfg.num_heads : 1;
+    const int workers = cfb::at_grid_x(N, heads, true) * cfb::at_warps(true);
+    cfb::atom_order_kernel<<<1, 1024, 0, st>>>(key, inv_vol, sizes, crystal_start, B, N, workers, by_rank, start_of, want_of,
+                                               slot_of, order, split);
     if (cudaGetLastError() != cudaSuccess) return CFB200_E_CUDA;
     if (E > 0 && range > 0 && (pair_cache != nullptr || pair_list != nullptr)) {
         float* list = pair_list;
@@ -222,6 +340,9 @@ int64_t cfb200_encoder_layer_workspace_bytes(int64_t N, int64_t E, int d_model, 
     if (!g_configured || N < 0 || E < 0 || d_model <= 0 || ff_dim <= 0) return -1;
     const int H = g_cfg.num_heads;
     int64_t fwd = frame_method == 2 ? pad256(cfb200_sigma_frames_workspace_bytes(N, E)) : 0;
+    // partial results of chunked attention tasks (the frames' scratch is free again by then)
+    const int64_t parts = pad256((int64_t)cfb::kSplitSlots * H * cfb::kSplitPartFwd * 4);
+    if (parts > fwd) fwd = parts;
     int64_t bwd = layer_bwd_workspace_bytes(N, E, d_model, ff_dim, H, frame_method != 0);
     return fwd > bwd ? fwd : bwd;
 }
@@ -254,6 +375,12 @@ static void layer_attn_args(cfb::AtArgs& A, const cfb200_layer_desc* L, const cf
     const int64_t fr = G->N * g_cfg.num_heads * 3;
     A.qs = St->q_scaled; A.k = St->k; A.v = St->v; A.a_ik = St->a; A.pos_ij = G->pos_ij; A.tvecs = G->tvecs; A.rvlen = G->rvlen;
     A.batch = G->batch; A.edges = G->edges; A.e_start = G->e_start; A.order = G->order; A.counters = G->counters;
+    if (G->split != nullptr && St->tasks != nullptr) {
+        // the table's last 256 bytes hold the per-head counts of chunk entries in use
+        A.tasks = reinterpret_cast<const int4*>(St->tasks);
+        A.n_entries = G->N + cfb::kSplitSlots;
+        A.chunk_count = reinterpret_cast<int*>(reinterpret_cast<char*>(St->tasks) + A.n_entries * 16 * g_cfg.num_heads);
+    }
     A.N = G->N; A.E = G->E;
     A.W[0] = W->pe_dist;
     if (ang) {
@@ -333,6 +460,18 @@ int cfb200_encoder_layer_fwd(const cfb200_layer_desc* L, const cfb200_layer_weig
         cfb::AtArgs A;
         layer_attn_args(A, L, W, G, St);
         A.out = St->attn; A.z = St->z; A.lse = St->lse; A.spool = St->spool;
+        if (A.tasks != nullptr) {
+            const int64_t rows = (int64_t)cfb::kSplitSlots * H;
+            if (workspace == nullptr || workspace_bytes < rows * cfb::kSplitPartFwd * 4) return CFB200_E_WORKSPACE;
+            if ((reinterpret_cast<uintptr_t>(St->tasks) & 15u) != 0) return CFB200_E_SHAPE;
+            A.part_spool = reinterpret_cast<float*>(workspace);
+            A.part_out = A.part_spool + rows * 256;
+            A.part_lse = A.part_out + rows * 16;
+            // this layer's task table: which entries of the queue this layer's coefficients leave whole, cut or unused
+            if ((rc = cfb::attn_plan(G->order, G->split, St->a, G->e_start, N, A.n_entries, H, A.chunk_count,
+                                     reinterpret_cast<int4*>(St->tasks), st)) != CFB200_OK)
+                return rc;
+        }
         if ((rc = cfb::attn_fused_fwd(A, P, st)) != CFB200_OK) return rc;
     }
     // x1 = attn Wo^T + bo + x ; h = relu(x1 Wf1^T + bf1) ; x_out = h Wf2^T + bf2 + x1
@@ -385,6 +524,7 @@ int cfb200_encoder_layer_bwd(const cfb200_layer_desc* L, const cfb200_layer_weig
     float* wg = ws.take<float>(wg_floats);
     float* gw_tmp = ws.take<float>(D);
     float* coef_part = ws.take<float>((int64_t)cfb::kCoSplits * D);
+    float* split_part = ws.take<float>((int64_t)cfb::kSplitSlots * H * cfb::kSplitPartBwd);
     if (!ws.ok) return CFB200_E_WORKSPACE;
 
     cfb::GemmArgs g;
@@ -408,6 +548,7 @@ int cfb200_encoder_layer_bwd(const cfb200_layer_desc* L, const cfb200_layer_weig
         cfb::AtArgs A;
         layer_attn_args(A, L, W, G, const_cast<cfb200_layer_state*>(St));
         A.out = St->attn; A.lse = St->lse; A.z_in = St->z; A.gout = go; A.gq = gqs; A.ga = ga; A.gz = gz;
+        A.part_gq = split_part; A.part_ga = split_part + (int64_t)cfb::kSplitSlots * H * 16;
         {
             TmScope tm(CFB200_TM_ATTN_BWD, st);
             if ((rc = cfb::attn_fused_bwd(A, P, st)) != CFB200_OK) return rc;

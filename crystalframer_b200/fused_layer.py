@@ -28,6 +28,9 @@ from .cuda_funcs.max_frame import _draw_seed
 
 # entry points whose presence in a trace shows that a layer ran through this module
 FUSED_FORWARD_CALLS = ("cfb200_encoder_layer_fwd",)
+# cut the longest (atom, head) tasks of the attention kernels into chunks (see cfb200_batch_geometry); a switch for
+# tests and measurements
+SPLIT_TASKS = True
 # test hook: a list here receives a copy of every layer's frames (3,N,H,3) as the forward computes them
 FRAME_TAP = None
 
@@ -70,19 +73,23 @@ class LayerGeometry:
         o_b = o_es + N + 1
         o_cs = o_b + N
         ibuf = torch.empty(o_cs + B + 1, dtype=torch.int64, device=dev)
-        # float32 block: pos_ij (3E) | rvlen (3B) | pair_cache (4E) | order (N, int32) | counters (64, int32) | call scratch
+        # float32 block: pos_ij (3E) | rvlen (3B) | pair_cache (4E) | order (queue entries, int32) | counters (64, int32)
+        # | chunk records and arrival counters of the queue (int32) | call scratch
         ws_bytes = int(_lib.lib().cfb200_batch_geometry_workspace_bytes(B))
+        n_queue, n_split = int(_lib.lib().cfb200_queue_entries(N)), int(_lib.lib().cfb200_split_ints(N))
         o_rv = _align(3 * E)
         o_pc = _align(o_rv + 3 * B)
         o_or = _align(o_pc + 4 * E)
-        o_ct = _align(o_or + N)
-        o_ws = _align(o_ct + 64)
+        o_ct = _align(o_or + n_queue)
+        o_sp = _align(o_ct + 64)
+        o_ws = _align(o_sp + n_split)
         fbuf = torch.empty(o_ws + ws_bytes // 4, dtype=torch.float32, device=dev)
         plist = torch.empty((E, 5, 128), dtype=torch.float32, device=dev) if want_list else None
         ip, fp = ibuf.data_ptr(), fbuf.data_ptr()
         _lib.invoke("cfb200_batch_geometry", 7, dev, _lib.ptr(pos), _lib.ptr(trans), _lib.iptr(sizes), B, N, E, rng,
                     ip, ip + 8 * o_es, ip + 8 * o_b, ip + 8 * o_cs, fp, None, fp + 4 * o_rv, None,
-                    fp + 4 * o_pc if rng > 0 else None, _lib.ptr(plist), fp + 4 * o_or, fp + 4 * o_ws, ws_bytes)
+                    fp + 4 * o_pc if rng > 0 else None, _lib.ptr(plist), fp + 4 * o_or, fp + 4 * o_sp if SPLIT_TASKS else None,
+                    fp + 4 * o_ws, ws_bytes)
         g.N, g.E, g.B, g.cache_range = N, E, B, rng
         g._keep = [ibuf, fbuf, plist, pos, trans, sizes]
         g.edges = ibuf[:2 * E].view(2, E)
@@ -95,6 +102,8 @@ class LayerGeometry:
         c.pos_ij, c.tvecs, c.rvlen = fp, trans.data_ptr(), fp + 4 * o_rv
         c.batch, c.edges, c.e_start = ip + 8 * o_b, ip, ip + 8 * o_es
         c.order, c.counters = fp + 4 * o_or, fp + 4 * o_ct
+        c.split = fp + 4 * o_sp if SPLIT_TASKS else None
+        g.split = fbuf[o_sp:o_sp + n_split].view(torch.int32) if SPLIT_TASKS else None
         c.pair_cache = fp + 4 * o_pc if rng > 0 else None
         c.pair_list = plist.data_ptr() if plist is not None else None
         c.N, c.E, c.cache_range = N, E, g.cache_range
@@ -122,6 +131,7 @@ class LayerGeometry:
         c.order, c.counters = order.data_ptr(), counters.data_ptr()
         c.pair_cache, c.pair_list = _lib.ptr(pair_cache), _lib.ptr(pair_list)
         c.N, c.E, c.cache_range = g.N, g.E, g.cache_range
+        c.split = None
         return g
 
     def workspace(self, nbytes, device):
@@ -130,11 +140,11 @@ class LayerGeometry:
         return self._ws
 
 
-def _state_layout(N, E, H, D, F, frames):
+def _state_layout(N, E, H, D, F, frames, tasks_bytes=0):
     """Offsets (floats) of the activations a layer's forward leaves for its backward, in one buffer."""
     sizes = (("q", N * D), ("q_scaled", N * D), ("k", N * D), ("v", N * D), ("a", N * H),
              ("frames", 9 * N * H if frames else 0), ("z", E * H), ("spool", N * H * 256), ("attn", N * D),
-             ("lse", N * H), ("x1", N * D), ("h", N * F))
+             ("lse", N * H), ("x1", N * D), ("h", N * F), ("tasks", tasks_bytes // 4))
     off, total = {}, 0
     for name, n in sizes:
         off[name] = total if n else None
@@ -169,7 +179,8 @@ class FusedEncoderLayerFunc(torch.autograd.Function):
         desc = _lib.LayerDesc(D, F, method, meta["lb"], meta["beta"], meta["scale_real"], meta["dist_max"], meta["cutoff"],
                               seed1, seed2)
         W = _lib.LayerWeights(*[None if p is None else _lib.ptr(p) for p in params])
-        off, total = _state_layout(N, E, H, D, F, method != 0)
+        tasks_bytes = int(_lib.lib().cfb200_attn_tasks_bytes(N)) if geo.c.split else 0
+        off, total = _state_layout(N, E, H, D, F, method != 0, tasks_bytes)
         state = torch.empty(total, dtype=torch.float32, device=dev)
         base = state.data_ptr()
         St = _lib.LayerState(*[None if off[f] is None else base + 4 * off[f] for f, _ in _lib.LayerState._fields_])

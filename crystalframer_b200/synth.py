@@ -102,3 +102,12 @@ def select(b: CrystalBatch, crystal_idx) -> CrystalBatch:
     sizes = b.sizes[crystal_idx]
     return CrystalBatch(x=b.x[atoms], pos=b.pos[atoms], batch=np.repeat(np.arange(len(sizes), dtype=np.int64), sizes),
                         trans_vec=b.trans_vec[crystal_idx], sizes=sizes, z=b.z[atoms])
+
+
+def concat(batches) -> CrystalBatch:
+    """One batch holding the crystals of several, in order."""
+    sizes = np.concatenate([b.sizes for b in batches])
+    return CrystalBatch(x=np.concatenate([b.x for b in batches]), pos=np.concatenate([b.pos for b in batches]),
+                        batch=np.repeat(np.arange(len(sizes), dtype=np.int64), sizes),
+                        trans_vec=np.concatenate([b.trans_vec for b in batches]), sizes=sizes,
+                        z=np.concatenate([b.z for b in batches]))

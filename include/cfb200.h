@@ -48,6 +48,7 @@ extern "C" {
 #define CFB200_ST_TC_TIMEOUT 8    /* a tensor-core kernel gave up waiting for its own instructions   */
 #define CFB200_ST_PAIR_LAYOUT 16  /* the pair list is not the dense n x n block of every crystal       */
 #define CFB200_MAX_RANGE 48
+#define CFB200_SPLIT_SLOTS 4096    /* partial results of chunked attention tasks a batch may hold per head */
 
 typedef struct cfb200_config {
     int32_t num_heads;        /* HEAD_NUM / THREAD_NUM                                  */
@@ -366,14 +367,23 @@ int cfb200_adamw_clip_step(float* params, const float* grads, float* exp_avg, fl
  * lattice vectors tvecs (B,3,3) and sizes (B) it produces the pair list (edges (2,E), e_start (N+1),
  * batch (N), crystal_start (B+1)), pos_ij (E,3), rvecs (B,3,3) (optional), rvlen (B,3), vcell (B)
  * (optional), the per-pair geometry of cfb200_pair_cache for lattice ranges (range)^3 (pair_cache (E,4),
- * pair_list (E,5,128); either may be NULL, range 0 skips both) and `order` (N) int32, the work-queue order
- * of cfb200_attn_fused_*: atoms of the crystals with the most attention work first.  workspace: at least
- * cfb200_batch_geometry_workspace_bytes(B) bytes. */
+ * pair_list (E,5,128); either may be NULL, range 0 skips both) and `order`, int32, the work queue of the fused
+ * attention kernels: atoms of the crystals with the most attention work first.
+ * split == NULL: `order` holds the N atoms.  Otherwise `order` has room for cfb200_queue_entries(N) entries and
+ * `split` for cfb200_split_ints(N) int32, and the queue can cut the longest tasks into chunks: one warp walks the
+ * pairs of an (atom, head) one after the other, so an atom of a dense cell with many atoms can take several times
+ * a warp's average load and the launch would end with that warp alone; such an atom gets an entry per chunk of
+ * its pairs, every layer decides from its coefficients which (atom, head) tasks it really cuts, the chunks leave
+ * partial results and a small kernel merges them in chunk order (results do not depend on the scheduling).  Hand
+ * `split` to the layer calls through cfb200_geometry and give each layer's state a task table.  workspace: at least cfb200_batch_geometry_workspace_bytes(B) bytes. */
 int64_t cfb200_batch_geometry_workspace_bytes(int64_t B);
+int64_t cfb200_queue_entries(int64_t N);
+int64_t cfb200_split_ints(int64_t N);
+int64_t cfb200_attn_tasks_bytes(int64_t N);
 int cfb200_batch_geometry(const float* pos, const float* tvecs, const int64_t* sizes, int64_t B, int64_t N,
                           int64_t E, int range, int64_t* edges, int64_t* e_start, int64_t* batch,
                           int64_t* crystal_start, float* pos_ij, float* rvecs, float* rvlen, float* vcell,
-                          float* pair_cache, float* pair_list, int32_t* order, void* workspace,
+                          float* pair_cache, float* pair_list, int32_t* order, int32_t* split, void* workspace,
                           int64_t workspace_bytes, void* stream);
 
 /* A dense layer, y (M,N) = x (M,K) op(W) (+ bias (N)) (+ residual (M,N)), then ReLU if relu != 0 -- what the
@@ -410,12 +420,16 @@ typedef struct cfb200_geometry {
     const float *pair_cache, *pair_list;
     int64_t N, E;
     int32_t cache_range;
+    int32_t* split;   /* chunked work queue of cfb200_batch_geometry, or NULL: `order` then holds N atoms */
 } cfb200_geometry;
 
 /* Activations a layer's forward leaves for its backward (caller-allocated): q, q_scaled, k, v, attn, x1
- * (N,D); a, lse (N,H); frames (3,N,H,3) (NULL for frame_method 0); z (E,H); spool (N,H,256); h (N,F). */
+ * (N,D); a, lse (N,H); frames (3,N,H,3) (NULL for frame_method 0); z (E,H); spool (N,H,256); h (N,F); tasks:
+ * cfb200_attn_tasks_bytes(N) bytes, 16-byte aligned, the layer's task table when the geometry carries a chunked
+ * queue (NULL otherwise, or to run the layer on the plain queue). */
 typedef struct cfb200_layer_state {
     float *q, *q_scaled, *k, *v, *a, *frames, *z, *spool, *attn, *lse, *x1, *h;
+    void* tasks;
 } cfb200_layer_state;
 
 /* frame_method: 0 = none (plain Crystalformer encoding), 1 = max frames, 2 = weighted-PCA frames, 3 = static max

@@ -36,20 +36,45 @@ def test_batch_geometry_against_oracle():
         # pos_ij is one float subtraction per component: identical on any IEEE machine
         assert np.array_equal(g.pos_ij.cpu().numpy(), want["pos_ij"])
         close("rvlen", g.rvlen.cpu().numpy(), want["rvlen"], 4e-7, 0.0)
-        # work-queue order: stable descending sort of the atoms by their crystal's key
+        # work queue: stable descending sort of the atoms by their crystal's key; a crystal cut into chunks appears once
+        # per chunk, its atoms in their order each time, with disjoint slots for the partial results
         vol = np.abs(np.linalg.det(b.trans_vec.astype(np.float64)))
-        key = (b.sizes * (7.0 + np.clip(2145.0 / np.maximum(vol, 1e-6), 1.0, 125.0))).astype(np.float32)
+        key = (b.sizes * (350.0 + 70.0 * np.clip(2145.0 / np.maximum(vol, 1e-6), 1.0, 125.0))).astype(np.float32)
         N = b.num_atoms
         from crystalframer_b200 import _lib
         # the library's order lives inside the geometry's float buffer; locate it through its pointer
         fbuf = g._keep[1]
         off = (g.c.order - fbuf.data_ptr()) // 4
-        got = fbuf[off:off + N].view(torch.int32).cpu().numpy()
-        assert sorted(got.tolist()) == list(range(N))
+        split = g.split.cpu().numpy()
+        S, SLOTS = int(split[0]), 4096                       # chunk entries in use; the atoms' entries follow the region
+        assert 0 <= S <= SLOTS
+        queue = fbuf[off:off + SLOTS + N].view(torch.int32).cpu().numpy()
+        info_all = split[4:4 + 2 * (SLOTS + N):2]
+        assert (info_all[S:SLOTS] == 0).all() and (info_all[:S] != 0).all() and (info_all[SLOTS:] != 0).all()
+        first = queue[SLOTS:]
+        assert sorted(first.tolist()) == list(range(N))
         k_atom = key[want["batch"]]
-        assert (np.diff(k_atom[got]) <= 1e-3 * k_atom.max()).all()           # non-increasing up to float rounding of the key
-        same_key = np.diff(k_atom[got]) == 0
-        assert (np.diff(got)[same_key] > 0).all()                             # stable within equal keys
+        assert (np.diff(k_atom[first]) <= 1e-3 * k_atom.max()).all()         # non-increasing up to float rounding of the key
+        same_key = np.diff(k_atom[first]) == 0
+        assert (np.diff(first)[same_key] > 0).all()                           # stable within equal keys
+        got = np.concatenate([queue[:S], first])
+        info = np.concatenate([info_all[:S], info_all[SLOTS:]])
+        chunk, chunks, slot = info & 15, (info >> 4) & 15, info >> 8
+        assert (chunk[S:] == 0).all() and (chunk[:S] >= 1).all()
+        counts = np.bincount(got, minlength=N)
+        per_atom_chunks = np.zeros(N, np.int64)
+        per_atom_chunks[got] = chunks
+        assert np.array_equal(counts, per_atom_chunks)                        # every chunk of every atom queued once
+        assert (chunks >= 1).all() and (chunks <= 8).all() and (chunk < chunks).all()
+        assert (chunks <= np.maximum(b.sizes[want["batch"]][got] // 4, 1)).all()
+        taken = np.zeros(SLOTS, np.int64)
+        for a in np.unique(got[chunks > 1]):
+            rows = slot[got == a]
+            assert (rows == rows[0]).all() and sorted(chunk[got == a].tolist()) == list(range(chunks[got == a][0]))
+            taken[rows[0]:rows[0] + chunks[got == a][0]] += 1
+        assert taken.max() <= 1 and int(split[2]) == (np.nonzero(taken)[0].max() + 1 if taken.any() else 0)
+        inv_vol = np.concatenate([split[5:5 + 2 * S:2], split[5 + 2 * SLOTS:5 + 2 * (SLOTS + N):2]]).view(np.float32)
+        assert np.allclose(inv_vol, 1.0 / np.maximum(vol, 1e-6)[want["batch"]][got], rtol=1e-5)
         # per-pair geometry equals what cfb200_pair_cache gives on the same inputs
         cache = torch.empty(b.num_pairs, 4, device=dev)
         plist = torch.empty(b.num_pairs, 5, 128, device=dev)
@@ -102,6 +127,55 @@ def test_one_call_layer_matches_operator_path(frame_method, workload, nc):
     for n in g0:
         scale = float(g0[n].abs().max()) + 1e-12
         assert float((g0[n] - g1[n]).abs().max()) <= 1e-4 * scale + 1e-9, (n, float((g0[n] - g1[n]).abs().max()), scale)
+    assert _lib.read_status(dev) == 0
+
+
+def test_chunked_tasks_change_nothing_but_rounding():
+    """A batch with dense 48-64 atom cells among small crystals: the work queue cuts their atoms' tasks into chunks
+    (partial results merged in chunk order).  Outputs and gradients equal the uncut run to rounding, and two cut runs
+    are bit-identical however the chunks were scheduled."""
+    dev = cuda()
+    from crystalframer_b200 import _lib, data, encoder, fused_layer, synth
+    from crystalframer_b200.latticeformer import Latticeformer, ModelParams
+    torch.manual_seed(5)
+    model = Latticeformer(ModelParams(num_layers=2, symm_break_noise=0.0)).to(dev).train()
+    dense = synth.make_batch(3, 21, size_dist="uniform", size_lo=48, size_hi=64, len_lo=3.0, len_hi=5.0)
+    small = synth.make_batch(61, 22, size_dist="uniform", size_lo=1, size_hi=6, len_lo=6.0, len_hi=15.0)
+    b = synth.concat([small, dense])
+    y = np.random.default_rng(1).normal(size=(len(b.sizes), 1)).astype(np.float32)
+    tb = data.host_batch(b, y, pinned=False).to(dev, non_blocking=False)
+    with torch.no_grad():
+        model(tb)
+    seen = []
+    orig = fused_layer.LayerGeometry.from_raw.__func__
+
+    def spy(cls, *a, **k):
+        g = orig(cls, *a, **k)
+        seen.append(g)
+        return g
+    fused_layer.LayerGeometry.from_raw = classmethod(spy)
+    results = []
+    try:
+        for split in (False, True, True):
+            fused_layer.SPLIT_TASKS = split
+            model.zero_grad(set_to_none=True)
+            np.random.seed(11)
+            torch.manual_seed(11)
+            out = model(tb)
+            (out - tb.y).abs().mean().backward()
+            results.append((out.detach().clone(), {n: p.grad.detach().clone() for n, p in model.named_parameters() if p.grad is not None}))
+    finally:
+        fused_layer.SPLIT_TASKS = True
+        fused_layer.LayerGeometry.from_raw = classmethod(orig)
+    assert len(seen) == 3 and seen[0].split is None
+    header = seen[1].split[:4].cpu().numpy()
+    assert header[0] > 0 and header[2] > 0                            # the dense cells got chunk entries and partial rows
+    (o0, g0), (o1, g1), (o2, g2) = results
+    assert torch.allclose(o0, o1, rtol=1e-5, atol=1e-6), float((o0 - o1).abs().max())
+    for n in g0:
+        scale = float(g0[n].abs().max()) + 1e-12
+        assert float((g0[n] - g1[n]).abs().max()) <= 1e-4 * scale + 1e-9, (n, float((g0[n] - g1[n]).abs().max()), scale)
+    assert torch.equal(o1, o2) and all(torch.equal(g1[n], g2[n]) for n in g1)
     assert _lib.read_status(dev) == 0
 
 
