@@ -289,6 +289,20 @@ int cfb200_pair_cache(const float* pos_ij, const float* tvecs, const int64_t* ba
     return cfb::pair_cache(pos_ij, tvecs, batch, edges, E, range, pair_cache, pair_list, S(stream));
 }
 
+int cfb200_max_frame_cached(int axis, const float* q_scaled, const float* k, const float* a_ik, const float* pos_ij,
+                            const float* tvecs, const float* rvlen, const int64_t* batch, const int64_t* edges,
+                            const int64_t* e_start, int64_t N, int64_t E, float cutoff_radius, uint64_t seed,
+                            const float* frame1, float* frame, int64_t* sel_edge, int32_t* sel_image,
+                            const float* pair_cache, const float* pair_list, int cache_range, void* stream)
+{
+    if (axis != 1 && axis != 2) return CFB200_E_SHAPE;
+    if (N > 0 && (frame == nullptr || (axis == 2 && frame1 == nullptr))) return CFB200_E_NULL;
+    if (pair_cache != nullptr && (reinterpret_cast<uintptr_t>(pair_cache) & 15u) != 0) return CFB200_E_SHAPE;
+    return frames_common(axis, q_scaled, k, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, N, E, cutoff_radius,
+                         seed, seed, frame1, axis == 1 ? frame : nullptr, axis == 2 ? frame : nullptr, nullptr,
+                         sel_edge, sel_image, stream, pair_cache, pair_list, cache_range);
+}
+
 int cfb200_max_frames_cached(const float* q_scaled, const float* k, const float* a_ik, const float* pos_ij,
                              const float* tvecs, const float* rvlen, const int64_t* batch, const int64_t* edges,
                              const int64_t* e_start, int64_t N, int64_t E, float cutoff_radius, uint64_t seed1,

@@ -23,10 +23,15 @@
 
 namespace cfb {
 
-constexpr int kFrPairs = 192;       // pair-list span whose query atoms one block owns; with crystals of up to 64
-                                    // atoms all pairs of the block's atoms fit one round of kFrThreads threads
-constexpr int kFrMaxRows = 256;     // at most one atom starts per pair of the span
-constexpr int kFrThreads = 256;
+#ifndef CFB_FR_THREADS
+#define CFB_FR_THREADS 256
+#define CFB_FR_PAIRS 192
+#define CFB_FR_BLOCKS 3
+#endif
+constexpr int kFrPairs = CFB_FR_PAIRS;     // pair-list span whose query atoms one block owns; with crystals of up to 64
+                                           // atoms all pairs of the block's atoms fit one round of kFrThreads threads
+constexpr int kFrThreads = CFB_FR_THREADS;
+constexpr int kFrMaxRows = kFrThreads;     // at most one atom starts per pair of the span (kFrPairs <= kFrThreads)
 constexpr int kFrHd = 16;
 
 struct FrArgs {
@@ -80,7 +85,8 @@ __device__ __forceinline__ int centre_out(int k) { return (k & 1) ? -((k + 1) >>
 // pass 2 draws the noise only for translations within the noise amplitude of that minimum (nothing
 // else can win).  The direction is computed once, for the winner.
 __device__ __forceinline__ Cand first_axis_candidate(const Cell& cell, float a, int R1, int R2, int R3, float amp,
-                                                     uint64_t seed, uint64_t tid, const float4* cached)
+                                                     uint64_t seed, uint64_t tid, const float4* cached, const int cache_range,
+                                                     const float* list = nullptr, const float reach2 = 1e38f)
 {
     Cand c; c.ux = c.uy = c.uz = 0.f; c.img = -1;
     float d2raw = 1e10f, d2next = 1e10f;      // smallest and second smallest d^2 > 1e-5 (equal values count twice)
@@ -88,6 +94,12 @@ __device__ __forceinline__ Cand first_axis_candidate(const Cell& cell, float a, 
     if (cached != nullptr) {                  // pass 1 is pure geometry: the same for every head and layer
         const float4 g = __ldg(cached);
         d2raw = g.x; d2next = g.y; best_t = __float_as_int(g.z);
+        if (best_t >= 0 && (R1 != cache_range || R2 != cache_range || R3 != cache_range)) {
+            // the cached index counts the translations of the cached box; here the box is larger
+            const int Lc = 2 * cache_range + 1;
+            const int q = best_t / Lc, k3 = best_t - q * Lc, k1 = q / Lc, k2 = q - k1 * Lc;
+            best_t = ((k1 - cache_range + R1) * (2 * R2 + 1) + (k2 - cache_range + R2)) * (2 * R3 + 1) + (k3 - cache_range + R3);
+        }
     } else
     for (int n1 = -R1; n1 <= R1; n1++)
         for (int n2 = -R2; n2 <= R2; n2++)
@@ -105,6 +117,26 @@ __device__ __forceinline__ Cand first_axis_candidate(const Cell& cell, float a, 
         // no other translation is within the noise amplitude of the minimum: the winner stands and
         // only its own noise enters the score
         d2_min = __fadd_rn(d2raw, noise_term(amp, seed, tid, (uint32_t)best_t));
+    } else if (amp != 0.0f && best_t >= 0 && list != nullptr && limit < reach2) {
+        // The translations within the noise amplitude of the minimum are the first few of the pair's sorted list
+        // (the list's distances differ from the ones compared here by a few ulp, hence the margin; everything
+        // outside the listed box is farther than reach2).  Same arg-min as the sweep below, written without
+        // reference to the visiting order: smallest d^2 + noise, lowest translation index on equal values.
+        d2_min = 1e10f; best_t = -1;
+        const float stop = limit + fabsf(limit) * 8e-6f + 1e-12f;
+        const int L2 = 2 * R2 + 1, L3 = 2 * R3 + 1;
+        for (int s = 0; s < kListLen; s++) {
+            if (!(__ldg(list + s) <= stop)) break;
+            const int code = __float_as_int(__ldg(list + 4 * kListLen + s));
+            const int n1 = (code & 255) - cache_range, n2 = ((code >> 8) & 255) - cache_range, n3 = ((code >> 16) & 255) - cache_range;
+            float dx, dy, dz, d2;
+            separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
+            if (d2 > kTiny && d2 <= limit) {
+                const int tt = ((n1 + R1) * L2 + (n2 + R2)) * L3 + (n3 + R3);
+                const float cand = __fadd_rn(d2, noise_term(amp, seed, tid, (uint32_t)tt));
+                if (cand < d2_min || (cand == d2_min && tt < best_t)) { d2_min = cand; best_t = tt; }
+            }
+        }
     } else if (amp != 0.0f && best_t >= 0) {
         d2_min = 1e10f; best_t = -1;
         t = 0;
@@ -144,7 +176,8 @@ __device__ __forceinline__ Cand first_axis_candidate(const Cell& cell, float a, 
 // of the same pair (same operations, same value); otherwise it is searched here.
 __device__ __forceinline__ Cand second_axis_candidate(const Cell& cell, float a, int R1, int R2, int R3, float amp,
                                                       uint64_t seed, uint64_t tid, float f1x, float f1y, float f1z,
-                                                      float d2min_known, const float* list, const bool is_static = false)
+                                                      float d2min_known, const float* list, const bool is_static = false,
+                                                      const int list_range = 0, const float reach2 = 1e38f)
 {
     Cand c; c.ux = c.uy = c.uz = 0.f; c.img = -1; c.value = -1e15f; c.d2raw = 0.f;
     float d2min = d2min_known >= 0.f ? d2min_known : 1e10f;
@@ -183,26 +216,58 @@ __device__ __forceinline__ Cand second_axis_candidate(const Cell& cell, float a,
             c.img = t;
         }
     };
+    bool sweep = list == nullptr;
     if (list != nullptr) {
         // Candidates nearest-first from the pair's sorted list.  The Gaussian part of the score only falls
         // along the list and the other part is never positive, so the search ends at the first entry whose
         // Gaussian part -- with a margin for the few ulp between the list's fused arithmetic and the
         // arithmetic above -- cannot reach the running maximum: nothing behind it can win or tie.
+        // The list holds the translations of the box (list_range)^3.  Where the task's box is larger, every
+        // translation outside the listed box is at least sqrt(reach2) away (see box_reach2): the list serves as long
+        // as the search ends before that distance, else the whole box is swept.
+        // (entries are requested two ahead of their use: the search is a chain of dependent loads otherwise)
+        const bool complete = R1 == list_range && R2 == list_range && R3 == list_range;
+        float d2_a = __ldg(list), d2_b = __ldg(list + 1);
+        int code_a = __float_as_int(__ldg(list + 4 * kListLen)), code_b = __float_as_int(__ldg(list + 4 * kListLen + 1));
         for (int s = 0; s < kListLen; s++) {
-            const float d2l = __ldg(list + s);
-            if (!(d2l < 1e29f)) break;                                   // end of the real entries
+            const float d2l = d2_a;
+            const int code = code_a;
+            d2_a = d2_b; code_a = code_b;
+            if (s + 2 < kListLen) { d2_b = __ldg(list + s + 2); code_b = __float_as_int(__ldg(list + 4 * kListLen + s + 2)); }
+            if (!(d2l < 1e29f)) { sweep = !complete; break; }           // end of the real entries
+            if (!complete && !(d2l < reach2)) { sweep = true; break; }
             const float g_est = a * (d2l - d2min);
             const float slack = fabsf(a) * d2l * 4e-6f + fabsf(g_est) * 2e-6f + 1e-12f;
             if (g_est + slack + half < best) break;
-            const int code = __float_as_int(__ldg(list + 4 * kListLen + s));
-            score_candidate((code & 255) - R1, ((code >> 8) & 255) - R2, ((code >> 16) & 255) - R3);
+            score_candidate((code & 255) - list_range, ((code >> 8) & 255) - list_range, ((code >> 16) & 255) - list_range);
+            if (s == kListLen - 1) sweep = !complete;
         }
-    } else {
+    }
+    if (sweep) {
         for (int k1 = 0; k1 <= 2 * R1; k1++)
             for (int k2 = 0; k2 <= 2 * R2; k2++)
                 for (int k3 = 0; k3 <= 2 * R3; k3++) score_candidate(centre_out(k1), centre_out(k2), centre_out(k3));
     }
     return c;
+}
+
+// Squared distance below which every translation of the pair lies inside the box (C)^3: a translation with |n_d| > C on
+// axis d is at least (C + 1 - |f_d|) plane spacings of that axis away, f the pair's separation in fractional
+// coordinates.  Shrunk by 1e-3 against rounding; 0 if the separation is not within C cells.
+__device__ __forceinline__ float box_reach2(const Cell& c, const int C)
+{
+    const float ax = c.t2y * c.t3z - c.t2z * c.t3y, ay = c.t2z * c.t3x - c.t2x * c.t3z, az = c.t2x * c.t3y - c.t2y * c.t3x;
+    const float bx = c.t3y * c.t1z - c.t3z * c.t1y, by = c.t3z * c.t1x - c.t3x * c.t1z, bz = c.t3x * c.t1y - c.t3y * c.t1x;
+    const float gx = c.t1y * c.t2z - c.t1z * c.t2y, gy = c.t1z * c.t2x - c.t1x * c.t2z, gz = c.t1x * c.t2y - c.t1y * c.t2x;
+    const float vol = c.t1x * ax + c.t1y * ay + c.t1z * az;
+    if (!(fabsf(vol) > 1e-12f)) return 0.f;
+    const float la = sqrtf(ax * ax + ay * ay + az * az), lb = sqrtf(bx * bx + by * by + bz * bz), lg = sqrtf(gx * gx + gy * gy + gz * gz);
+    // (C + 1 - |f_d|) spacing_d = ((C + 1) |vol| - |r . normal_d|) / |normal_d|
+    const float r1 = ((float)(C + 1) * fabsf(vol) - fabsf(c.rx * ax + c.ry * ay + c.rz * az)) / la;
+    const float r2 = ((float)(C + 1) * fabsf(vol) - fabsf(c.rx * bx + c.ry * by + c.rz * bz)) / lb;
+    const float r3 = ((float)(C + 1) * fabsf(vol) - fabsf(c.rx * gx + c.ry * gy + c.rz * gz)) / lg;
+    const float r = fminf(r1, fminf(r2, r3));
+    return r > 0.f ? r * r * 0.999f : 0.f;
 }
 
 // (score, pair) -> 64-bit key whose unsigned order is (score ascending, pair index descending)
@@ -224,7 +289,7 @@ __device__ __forceinline__ int64_t lower_bound_i64(const int64_t* v, int64_t n, 
     return lo;
 }
 
-__global__ void __launch_bounds__(kFrThreads, 3) max_frame_kernel(const FrArgs A, const Params P)
+__global__ void __launch_bounds__(kFrThreads, CFB_FR_BLOCKS) max_frame_kernel(const FrArgs A, const Params P)
 {
     __shared__ unsigned long long best[kFrMaxRows];
     __shared__ long long row_start[kFrMaxRows + 1];
@@ -309,20 +374,31 @@ __global__ void __launch_bounds__(kFrThreads, 3) max_frame_kernel(const FrArgs A
                 const uint64_t noise_id = (uint64_t)(e * H + h);
                 const int pack = row_R[r];
                 const int R1 = pack & 255, R2 = (pack >> 8) & 255, R3 = (pack >> 16) & 255;
+                // the per-pair cache and list cover the box (cache_range)^3; a task with a larger box can use them where
+                // everything outside the cached box is provably farther than what decides the search
+                const int C = A.cache_range;
+                const bool same_box = R1 == C && R2 == C && R3 == C;
+                const bool wider = !same_box && R1 >= C && R2 >= C && R3 >= C && (A.cache != nullptr || A.list != nullptr);
+                const float reach2 = wider ? box_reach2(cell, C) : 1e38f;
                 if (axis == 1) {
-                    const bool hit = A.cache != nullptr && R1 == A.cache_range && R2 == A.cache_range && R3 == A.cache_range;
+                    // the two nearest images inside the cached box are the two nearest of the larger box
+                    const bool hit = A.cache != nullptr && (same_box || (wider && __ldg(&A.cache[e].y) < reach2));
                     cd = first_axis_candidate(cell, row_a[r], R1, R2, R3, P.noise, A.seed1, noise_id,
-                                              hit ? A.cache + e : nullptr);
+                                              hit ? A.cache + e : nullptr, C,
+                                              hit && A.list != nullptr ? A.list + (size_t)e * kListStride : nullptr, reach2);
                     if (keep_d2) {
                         if (round == 0) d2raw0 = cd.d2raw; else if (round == 1) d2raw1 = cd.d2raw; else d2raw2 = cd.d2raw;
                     }
                 } else {
-                    const float known = round == 0 ? d2raw0 : (round == 1 ? d2raw1 : (round == 2 ? d2raw2 : -1.f));
+                    float known = round == 0 ? d2raw0 : (round == 1 ? d2raw1 : (round == 2 ? d2raw2 : -1.f));
+                    // the smallest non-zero squared distance is cached pair geometry (second axis on its own)
+                    if (known < 0.f && A.cache != nullptr && (same_box || (wider && __ldg(&A.cache[e].y) < reach2)))
+                        known = __ldg(&A.cache[e].x);
                     // the sorted list serves the search only where the score falls with the distance
-                    const bool hit = A.list != nullptr && !A.is_static && R1 == A.cache_range && R2 == A.cache_range && R3 == A.cache_range;
+                    const bool hit = A.list != nullptr && !A.is_static && (same_box || (wider && reach2 > 0.f));
                     cd = second_axis_candidate(cell, row_a[r], R1, R2, R3, P.noise, A.seed2, noise_id,
                                                row_f1[r][0], row_f1[r][1], row_f1[r][2], known,
-                                               hit ? A.list + (size_t)e * kListStride : nullptr, A.is_static != 0);
+                                               hit ? A.list + (size_t)e * kListStride : nullptr, A.is_static != 0, C, reach2);
                 }
                 const float s = __fadd_rn(dot, cd.value);
                 if (s > -1e10f) {

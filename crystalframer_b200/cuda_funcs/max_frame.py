@@ -27,9 +27,11 @@ def _frame_call(axis, q, k, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_
     sel_e = torch.empty((N, H), device=dev, dtype=torch.int64) if want_selection else None
     sel_i = torch.empty((N, H), device=dev, dtype=torch.int32) if want_selection else None
     p, ip = _lib.ptr, _lib.iptr
-    _lib.invoke("cfb200_max_frame", 1, dev,
+    # per-pair geometry shared by the heads, the two axes and the layers of a batch (kept on the input tensor)
+    pcache, plist, prange = pair_geometry(rpos_ij_e, tvecs_n, batch_i, edge_ij_e, cutoff)
+    _lib.invoke("cfb200_max_frame_cached", 1, dev,
                 axis, p(qq), p(kk), p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), ip(e_start), N, E, cutoff, seed,
-                p(f32c(frame1)), p(out), ip(sel_e), _lib.ptr(sel_i, torch.int32))
+                p(f32c(frame1)), p(out), ip(sel_e), _lib.ptr(sel_i, torch.int32), p(pcache), p(plist), prange)
     return (out, sel_e, sel_i) if want_selection else out
 
 

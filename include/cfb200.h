@@ -258,7 +258,9 @@ int cfb200_framed_proj_bwd_noalloc(const float* a_ik, const float* pos_ij, const
  *     the packed translation (n1+range) | (n2+range) << 8 | (n3+range) << 16 | index << 24 (int32
  *     bits); unused entries have d^2 = 1e30.
  * The *_cached entry points compute what their plain namesakes compute and use the cache for every
- * (atom, head) whose three lattice ranges equal cache_range; other ranges are searched as usual.
+ * (atom, head) whose three lattice ranges equal cache_range -- the frame searches also for larger ranges,
+ * wherever every translation outside the cached box is provably farther than what decides the search;
+ * other tasks are searched as usual.
  * Frames are bit-identical to the plain entry point with either cache; with pair_list the lattice
  * sums are accumulated nearest-first instead of in index order (differences of a few ulp).
  * Either pointer may be NULL. */
@@ -272,6 +274,13 @@ int cfb200_max_frames_cached(const float* q_scaled, const float* k, const float*
                              uint64_t seed2, float* frame1, float* frame2, float* frame3,
                              const float* pair_cache, const float* pair_list, int cache_range,
                              void* stream);
+int cfb200_max_frame_cached(int axis, const float* q_scaled, const float* k, const float* a_ik,
+                            const float* pos_ij, const float* tvecs, const float* rvlen,
+                            const int64_t* batch, const int64_t* edges, const int64_t* e_start,
+                            int64_t N, int64_t E, float cutoff_radius, uint64_t seed,
+                            const float* frame1, float* frame, int64_t* sel_edge, int32_t* sel_image,
+                            const float* pair_cache, const float* pair_list, int cache_range,
+                            void* stream);
 int cfb200_framed_proj_fwd_cached(const float* a_ik, const float* pos_ij, const float* tvecs,
                                   const float* rvlen, const int64_t* batch, const int64_t* edges,
                                   int64_t N, int64_t E, float dist_max, float cutoff_radius,
