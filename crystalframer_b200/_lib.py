@@ -41,7 +41,7 @@ class Geometry(ctypes.Structure):              # cfb200_geometry
 
 
 class LayerState(ctypes.Structure):            # cfb200_layer_state
-    _fields_ = [(n, vp) for n in ("q", "q_scaled", "k", "v", "a", "frames", "z", "spool", "attn", "lse", "x1", "h", "tasks")]
+    _fields_ = [(n, vp) for n in ("q", "q_scaled", "k", "v", "a", "frames", "z", "spool", "attn", "lse", "x1", "h", "tasks", "val", "px", "upool")]
 
 
 class LayerDesc(ctypes.Structure):             # cfb200_layer_desc
@@ -79,9 +79,9 @@ SIGNATURES = {
     "cfb200_proj_fwd": (ctypes.c_int, [vp] * 6 + [i64, i64, f32, f32] + [vp] * 4),
     "cfb200_proj_bwd": (ctypes.c_int, [vp] * 7 + [i64, i64, f32, f32] + [vp] * 7 + [i64, vp]),
     "cfb200_framed_proj_bwd_noalloc": (ctypes.c_int, [vp] * 7 + [i64, i64, f32, f32] + [vp] * 15 + [vp]),
-    "cfb200_attn_fused_fwd": (ctypes.c_int, [vp] * 12 + [i64, i64, f32, f32] + [vp] * 8 + [ctypes.c_int] + [vp] * 4
+    "cfb200_attn_fused_fwd": (ctypes.c_int, [vp] * 12 + [i64, i64, f32, f32] + [vp] * 8 + [ctypes.c_int] + [vp] * 7
                               + [ctypes.c_int, vp]),
-    "cfb200_attn_fused_bwd": (ctypes.c_int, [vp] * 12 + [i64, i64, f32, f32] + [vp] * 8 + [ctypes.c_int] + [vp] * 9
+    "cfb200_attn_fused_bwd": (ctypes.c_int, [vp] * 12 + [i64, i64, f32, f32] + [vp] * 8 + [ctypes.c_int] + [vp] * 12
                               + [ctypes.c_int, vp]),
     "cfb200_dpa_fwd": (ctypes.c_int, [vp] * 7 + [i64, i64] + [vp] * 4),
     "cfb200_dpa_bwd": (ctypes.c_int, [vp] * 7 + [i64, i64] + [vp] * 9),

@@ -542,7 +542,7 @@ int cfb200_attn_fused_fwd(const float* q_scaled, const float* k, const float* v,
                           int64_t N, int64_t E, float dist_max, float cutoff_radius, const float* W_dist, const float* W_ang1,
                           const float* W_ang2, const float* W_ang3, const float* frame1, const float* frame2,
                           const float* frame3, const float* pair_list, int cache_range, float* out, float* z,
-                          float* lse, float* spool, int unwindowed, void* stream)
+                          float* lse, float* spool, float* val, float* px, float* upool, int unwindowed, void* stream)
 {
     cfb::Params P;
     int rc = make_params(dist_max, cutoff_radius, P, unwindowed != 0);
@@ -553,7 +553,8 @@ int cfb200_attn_fused_fwd(const float* q_scaled, const float* k, const float* v,
                  W_dist, W_ang1, W_ang2, W_ang3, frame1, frame2, frame3, pair_list, cache_range);
     if (rc != CFB200_OK) return rc;
     if (N > 0 && (!out || !z || !lse || !spool)) return CFB200_E_NULL;
-    A.out = out; A.z = z; A.lse = lse; A.spool = spool;
+    if ((val != nullptr) != (px != nullptr) || (val != nullptr) != (upool != nullptr)) return CFB200_E_NULL;
+    A.out = out; A.z = z; A.lse = lse; A.spool = spool; A.val = val; A.px = px; A.upool = upool;
     return cfb::attn_fused_fwd(A, P, S(stream));
 }
 
@@ -564,7 +565,8 @@ int cfb200_attn_fused_bwd(const float* q_scaled, const float* k, const float* v,
                           const float* W_ang2, const float* W_ang3, const float* frame1, const float* frame2,
                           const float* frame3, const float* pair_list, int cache_range, const float* out,
                           const float* z, const float* lse, const float* gout, float* gq_scaled, float* gk, float* gv,
-                          float* ga, float* gz, int unwindowed, void* stream)
+                          float* ga, float* gz, const float* val, const float* px, const float* upool, int unwindowed,
+                          void* stream)
 {
     cfb::Params P;
     int rc = make_params(dist_max, cutoff_radius, P, unwindowed != 0);
@@ -577,6 +579,8 @@ int cfb200_attn_fused_bwd(const float* q_scaled, const float* k, const float* v,
     if (N > 0 && (!out || !z || !lse || !gout || !gq_scaled || !gk || !gv || !ga || !gz)) return CFB200_E_NULL;
     A.out = const_cast<float*>(out); A.lse = const_cast<float*>(lse); A.z_in = z; A.gout = gout;
     A.gq = gq_scaled; A.ga = ga; A.gz = gz;
+    if ((val != nullptr) != (px != nullptr) || (val != nullptr) != (upool != nullptr)) return CFB200_E_NULL;
+    A.val = const_cast<float*>(val); A.px = const_cast<float*>(px); A.upool = const_cast<float*>(upool);
     rc = cfb::attn_fused_bwd(A, P, S(stream));
     if (rc != CFB200_OK || N == 0) return rc;
     // column pass: gk_j = sum_i gz_ij q_i, gv_j = sum_i p_ij gout_i

@@ -58,6 +58,10 @@ struct AtArgs {
     float* z; float* out; float* lse; float* spool;                    // forward outputs
     const float* gout; const float* z_in;                             // backward inputs (plus out, lse above)
     float* gz; float* gq; float* ga;                                   // backward outputs
+    // what a training forward leaves for a backward pass without a second lattice sum: per pair its value encoding
+    // (E,H,16) and sum p d^2 (E,H); per atom the projection of the attention-pooled d^2-weighted basis sums (N,H,16)
+    float* val; float* px; float* upool;
+    float* part_upool;                                                  // its chunk results (kSplitSlots rows)
 };
 
 __host__ __device__ constexpr size_t at_smem_bytes(bool bwd)
@@ -74,8 +78,8 @@ struct AtomTask {
     bool use_list;
 };
 
-template <bool BWD, bool ANG>
-__device__ __forceinline__ AtomTask load_atom(const AtArgs& A, const Params& P, LatticeLane<BWD, ANG>& L, const int64_t i,
+template <int MODE, bool ANG>
+__device__ __forceinline__ AtomTask load_atom(const AtArgs& A, const Params& P, LatticeLane<MODE, ANG>& L, const int64_t i,
                                               const int h, const int lane)
 {
     AtomTask T;
@@ -97,8 +101,8 @@ __device__ __forceinline__ AtomTask load_atom(const AtArgs& A, const Params& P, 
     return T;
 }
 
-template <bool BWD, bool ANG>
-__device__ __forceinline__ void run_pair(const AtArgs& A, const Params& P, LatticeLane<BWD, ANG>& L, const AtomTask& T,
+template <int MODE, bool ANG>
+__device__ __forceinline__ void run_pair(const AtArgs& A, const Params& P, LatticeLane<MODE, ANG>& L, const AtomTask& T,
                                          const int64_t e)
 {
     L.reset();
@@ -133,7 +137,7 @@ __global__ void __launch_bounds__(at_warps(false) * 32, kAtFwdBlocks) attn_fwd_k
         if (A.W[b] != nullptr) w = __ldg(reinterpret_cast<const float4*>(A.W[b] + ((size_t)h * kAtHd + o) * 64) + d4);
         reinterpret_cast<float4*>(W_s)[o * (kAtWfStride / 4) + k4] = w;
     }
-    LatticeLane<false, ANG> L;
+    LatticeLane<0, ANG> L;
     L.init(P, lane, tbuf + warp * 6 * 32);
     float* srow = rows + warp * kAtK;
     __syncthreads();
@@ -150,12 +154,12 @@ __global__ void __launch_bounds__(at_warps(false) * 32, kAtFwdBlocks) attn_fwd_k
             const int cnt = d.w & 0xFFFFFF;
             if (cnt == 0) continue;                         // an entry this head does not use
             i = d.x; row = d.y;
-            T = load_atom<false, ANG>(A, P, L, i, h, lane);
+            T = load_atom<0, ANG>(A, P, L, i, h, lane);
             T.e0 += d.z; T.e1 = T.e0 + cnt;
         } else {
             i = A.order != nullptr ? (int64_t)A.order[t] : t;
             row = i;
-            T = load_atom<false, ANG>(A, P, L, i, h, lane);
+            T = load_atom<0, ANG>(A, P, L, i, h, lane);
         }
         const float qd = lane < kAtHd ? __ldg(A.qs + (i * H + h) * kAtHd + lane) : 0.f;
         float m = -INFINITY, l = 0.f, V = 0.f;
@@ -169,7 +173,7 @@ __global__ void __launch_bounds__(at_warps(false) * 32, kAtFwdBlocks) attn_fwd_k
             if (lane == 0 && __ldg(A.edges + A.E + e) != j) atomicOr(&g_status, CFB200_ST_PAIR_LAYOUT);   // not the dense layout
             float kd = 0.f, vd = 0.f;
             if (lane < kAtHd) { kd = __ldg(A.k + (j * H + h) * kAtHd + lane); vd = __ldg(A.v + (j * H + h) * kAtHd + lane); }
-            run_pair<false, ANG>(A, P, L, T, e);
+            run_pair<0, ANG>(A, P, L, T, e);
             const float sum = warp_sum(L.sum_l);
             const float qk = warp_sum(qd * kd);
             const float zv = logf(sum) + L.ref * L.a;
@@ -226,6 +230,214 @@ __global__ void __launch_bounds__(at_warps(false) * 32, kAtFwdBlocks) attn_fwd_k
     }
 }
 
+// ---- training forward: also leaves what the backward pass needs of every pair ------------------------------
+// With s_ij the basis sums of a pair, t_ij the same sums weighted with d^2 and x_ij = sum p d^2, the backward pass is
+//   gz_ij = p_ij (gout_i . (v_j + W s_ij) - gout_i . out_i)
+//   ga_i  = sum_j c_dist x_ij gz_ij + p_ij gout_i . W (t_ij - x_ij s_ij)
+//         = gout_i . W (sum_j p_ij t_ij) + sum_j (c_dist x_ij gz_ij - p_ij x_ij gout_i . W s_ij)
+// so it needs the lattice sums only through the pair's value encoding W s_ij (16 numbers), x_ij, and the projection
+// of the attention-pooled t of the atom (16 numbers per atom).  None of these depends on gout: the training forward
+// projects W s_ij per pair (one 16 x 256 product), pools t beside s, and stores 68 bytes per (pair, head); the
+// backward pass (attn_bwd_saved_kernel) is then a plain ragged attention backward: no second lattice sum.  The
+// attention output sums the stored value encodings directly; the pooled s is still kept for the weight gradients.
+constexpr int kAtTrainWarps = 8;
+constexpr size_t kAtTrainSmem = sizeof(float) * (kAtHd * kAtWfStride + kAtTrainWarps * 8 * 32 + kAtTrainWarps * kAtK);
+
+// out_d = W_d . row: lane = (output d, half of the 256 basis indices); every lane returns the full sum of its d
+__device__ __forceinline__ float project_row(const float* W_s, const float* row, const int lane)
+{
+    const int d = lane & 15, half = lane >> 4;
+    const float4* wr = reinterpret_cast<const float4*>(W_s + d * kAtWfStride) + half * 32;
+    const float4* sr = reinterpret_cast<const float4*>(row) + half * 32;
+    float acc = 0.f;
+#pragma unroll 8
+    for (int k4 = 0; k4 < 32; k4++) {
+        const float4 w4 = wr[k4], s4 = sr[k4];
+        acc = fmaf(s4.x, w4.x, fmaf(s4.y, w4.y, fmaf(s4.z, w4.z, fmaf(s4.w, w4.w, acc))));
+    }
+    return acc + __shfl_xor_sync(0xffffffffu, acc, 16);
+}
+
+template <bool ANG, bool TASKS>
+__global__ void __launch_bounds__(kAtTrainWarps * 32, 2) attn_fwd_train_kernel(const AtArgs A, const Params P)
+{
+    extern __shared__ __align__(16) float smem[];
+    float* W_s = smem;                                      // [16][260]
+    float* tbuf = W_s + kAtHd * kAtWfStride;                // per warp 8 x 32
+    float* rows = tbuf + kAtTrainWarps * 8 * 32;            // per warp 256: the basis vector being projected
+    const int h = blockIdx.y, H = P.H;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int idx = threadIdx.x; idx < kAtHd * kAtK / 4; idx += kAtTrainWarps * 32) {
+        const int o = idx >> 6, k4 = idx & 63, b = k4 >> 4, d4 = k4 & 15;
+        float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (A.W[b] != nullptr) w = __ldg(reinterpret_cast<const float4*>(A.W[b] + ((size_t)h * kAtHd + o) * 64) + d4);
+        reinterpret_cast<float4*>(W_s)[o * (kAtWfStride / 4) + k4] = w;
+    }
+    LatticeLane<2, ANG> L;
+    L.init(P, lane, tbuf + warp * 8 * 32);
+    float* srow = rows + warp * kAtK;
+    __syncthreads();
+    const int first = TASKS ? kSplitSlots - __ldg(A.chunk_count + h) : 0;
+
+    for (;;) {
+        const int64_t t = next_task(A.counters + h, lane) + first;
+        if (t >= (TASKS ? A.n_entries : A.N)) break;
+        int64_t i, row;
+        AtomTask T;
+        if (TASKS) {
+            const int4 d = __ldg(A.tasks + (size_t)h * A.n_entries + t);
+            const int cnt = d.w & 0xFFFFFF;
+            if (cnt == 0) continue;
+            i = d.x; row = d.y;
+            T = load_atom<2, ANG>(A, P, L, i, h, lane);
+            T.e0 += d.z; T.e1 = T.e0 + cnt;
+        } else {
+            i = A.order != nullptr ? (int64_t)A.order[t] : t;
+            row = i;
+            T = load_atom<2, ANG>(A, P, L, i, h, lane);
+        }
+        const float qd = lane < kAtHd ? __ldg(A.qs + (i * H + h) * kAtHd + lane) : 0.f;
+        float m = -INFINITY, l = 0.f, V = 0.f;
+        float S[8], Tp[8];                                  // attention-pooled basis sums, plain and d^2-weighted
+#pragma unroll
+        for (int r = 0; r < 8; r++) S[r] = Tp[r] = 0.f;
+        const int64_t j0 = A.edges[A.E + T.e0];
+        for (int64_t e = T.e0; e < T.e1; e++) {
+            const int64_t j = j0 + (e - T.e0);
+            if (lane == 0 && __ldg(A.edges + A.E + e) != j) atomicOr(&g_status, CFB200_ST_PAIR_LAYOUT);   // not the dense layout
+            float kd = 0.f, vd = 0.f;
+            if (lane < kAtHd) { kd = __ldg(A.k + (j * H + h) * kAtHd + lane); vd = __ldg(A.v + (j * H + h) * kAtHd + lane); }
+            run_pair<2, ANG>(A, P, L, T, e);
+            float r0 = L.sum_l, r1 = L.px_l, r2 = qd * kd;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                r0 += __shfl_xor_sync(0xffffffffu, r0, o); r1 += __shfl_xor_sync(0xffffffffu, r1, o);
+                r2 += __shfl_xor_sync(0xffffffffu, r2, o);
+            }
+            const float sum = r0, qk = r2;
+            const float inv = 1.0f / sum;
+            const float zv = logf(sum) + L.ref * L.a;
+            if (lane == 0) { A.z[e * H + h] = zv; A.px[e * H + h] = r1 * inv; }
+            // the pair's value encoding: its normalised basis sums, with the scaling of the values, times W
+            {
+                const float cd = inv * P.c_dist, ca = inv * P.c_ang;
+                srow[lane] = L.sd[0] * cd; srow[32 + lane] = L.sd[1] * cd;
+#pragma unroll
+                for (int x = 0; x < 3; x++) { srow[64 + 64 * x + lane] = L.sa[x][0] * ca; srow[96 + 64 * x + lane] = L.sa[x][1] * ca; }
+            }
+            __syncwarp();
+            const float val_d = project_row(W_s, srow, lane);
+            if (lane < kAtHd) A.val[(e * H + h) * kAtHd + lane] = val_d;
+            __syncwarp();
+            const float s = qk + zv;
+            const float mn = fmaxf(m, s);
+            const float sc = __expf(m - mn), p = __expf(s - mn);
+            const float f = p * inv;
+            l = fmaf(l, sc, p);
+            V = fmaf(V, sc, p * (vd + val_d));
+            S[0] = fmaf(S[0], sc, f * L.sd[0]); S[1] = fmaf(S[1], sc, f * L.sd[1]);
+            Tp[0] = fmaf(Tp[0], sc, f * L.qd[0]); Tp[1] = fmaf(Tp[1], sc, f * L.qd[1]);
+#pragma unroll
+            for (int x = 0; x < 3; x++) {
+                S[2 + 2 * x] = fmaf(S[2 + 2 * x], sc, f * L.sa[x][0]); S[3 + 2 * x] = fmaf(S[3 + 2 * x], sc, f * L.sa[x][1]);
+                Tp[2 + 2 * x] = fmaf(Tp[2 + 2 * x], sc, f * L.qa[x][0]); Tp[3 + 2 * x] = fmaf(Tp[3 + 2 * x], sc, f * L.qa[x][1]);
+            }
+            m = mn;
+        }
+        const float inv_l = T.e1 > T.e0 ? 1.0f / l : 0.f;
+        const bool partial = TASKS && row >= A.N;
+        if (partial) row -= A.N;
+        if (lane == 0) (partial ? A.part_lse : A.lse)[row * H + h] = m + logf(l);
+        float* sp = (partial ? A.part_spool : A.spool) + (row * H + h) * kAtK;
+        sp[lane] = S[0] * inv_l; sp[32 + lane] = S[1] * inv_l;
+        srow[lane] = Tp[0] * inv_l * P.c_dist; srow[32 + lane] = Tp[1] * inv_l * P.c_dist;
+#pragma unroll
+        for (int x = 0; x < 3; x++) {
+            sp[64 + 64 * x + lane] = S[2 + 2 * x] * inv_l * P.c_ang; sp[96 + 64 * x + lane] = S[3 + 2 * x] * inv_l * P.c_ang;
+            srow[64 + 64 * x + lane] = Tp[2 + 2 * x] * inv_l * P.c_ang; srow[96 + 64 * x + lane] = Tp[3 + 2 * x] * inv_l * P.c_ang;
+        }
+        __syncwarp();
+        const float up_d = project_row(W_s, srow, lane);     // W (pooled d^2-weighted sums)
+        if (lane < kAtHd) {
+            (partial ? A.part_out : A.out)[(row * H + h) * kAtHd + lane] = V * inv_l;
+            (partial ? A.part_upool : A.upool)[(row * H + h) * kAtHd + lane] = up_d;
+        }
+        __syncwarp();
+    }
+}
+
+// Backward pass from the results of the training forward: warp = (atom, head), lane = pair (32 at a time).  Per pair
+//   p = exp(q.k + z - lse),  gz = p (gout . (v_j + values_ij) - gout . out_i),
+//   ga += c_dist x gz - p x gout . values_ij,  gq += gz k_j;   and ga += gout . upool once per atom
+// (the coefficient gradient of attn_bwd_kernel, reference quirk included).  The 16-component dot products run inside
+// the lanes; the 17 per-atom sums are reduced over the lanes once at the end, in a fixed order.
+__global__ void __launch_bounds__(256) attn_bwd_saved_kernel(const AtArgs A, const Params P)
+{
+    const int lane = threadIdx.x & 31, H = P.H;
+    const int64_t task = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (task >= A.N * H) return;
+    const int64_t i = task / H;
+    const int h = (int)(task - i * H);
+    float q[kAtHd], g[kAtHd], gq[kAtHd];
+    float D = 0.f, gup = 0.f;
+    {
+        const float4* q4 = reinterpret_cast<const float4*>(A.qs + (i * H + h) * kAtHd);
+        const float4* g4 = reinterpret_cast<const float4*>(A.gout + (i * H + h) * kAtHd);
+        const float4* o4 = reinterpret_cast<const float4*>(A.out + (i * H + h) * kAtHd);
+        const float4* u4 = reinterpret_cast<const float4*>(A.upool + (i * H + h) * kAtHd);
+#pragma unroll
+        for (int c = 0; c < kAtHd / 4; c++) {
+            const float4 a = __ldg(q4 + c), b = __ldg(g4 + c), o = __ldg(o4 + c), u = __ldg(u4 + c);
+            q[4 * c] = a.x; q[4 * c + 1] = a.y; q[4 * c + 2] = a.z; q[4 * c + 3] = a.w;
+            g[4 * c] = b.x; g[4 * c + 1] = b.y; g[4 * c + 2] = b.z; g[4 * c + 3] = b.w;
+            D = fmaf(b.x, o.x, fmaf(b.y, o.y, fmaf(b.z, o.z, fmaf(b.w, o.w, D))));
+            gup = fmaf(b.x, u.x, fmaf(b.y, u.y, fmaf(b.z, u.z, fmaf(b.w, u.w, gup))));
+        }
+#pragma unroll
+        for (int c = 0; c < kAtHd; c++) gq[c] = 0.f;
+    }
+    const float lse = __ldg(A.lse + i * H + h);
+    const int64_t e0 = A.e_start[i], e1 = A.e_start[i + 1];
+    const int64_t j0 = e1 > e0 ? A.edges[A.E + e0] : 0;
+    float ga = 0.f;
+    for (int64_t e = e0 + lane; e < e1; e += 32) {
+        const int64_t j = j0 + (e - e0);
+        const float4* k4 = reinterpret_cast<const float4*>(A.k + (j * H + h) * kAtHd);
+        const float4* v4 = reinterpret_cast<const float4*>(A.v + (j * H + h) * kAtHd);
+        const float4* x4 = reinterpret_cast<const float4*>(A.val + (e * H + h) * kAtHd);
+        const float zin = __ldg(A.z_in + e * H + h), px = __ldg(A.px + e * H + h);
+        float kk[kAtHd];
+        float qk = 0.f, gov = 0.f, cB = 0.f;
+#pragma unroll
+        for (int c = 0; c < kAtHd / 4; c++) {
+            const float4 a = __ldg(k4 + c), b = __ldg(v4 + c), x = __ldg(x4 + c);
+            kk[4 * c] = a.x; kk[4 * c + 1] = a.y; kk[4 * c + 2] = a.z; kk[4 * c + 3] = a.w;
+            qk = fmaf(q[4 * c], a.x, fmaf(q[4 * c + 1], a.y, fmaf(q[4 * c + 2], a.z, fmaf(q[4 * c + 3], a.w, qk))));
+            gov = fmaf(g[4 * c], b.x, fmaf(g[4 * c + 1], b.y, fmaf(g[4 * c + 2], b.z, fmaf(g[4 * c + 3], b.w, gov))));
+            cB = fmaf(g[4 * c], x.x, fmaf(g[4 * c + 1], x.y, fmaf(g[4 * c + 2], x.z, fmaf(g[4 * c + 3], x.w, cB))));
+        }
+        const float p_att = __expf(qk + zin - lse);
+        const float gzv = p_att * (gov + cB - D);
+        A.gz[e * H + h] = gzv;
+        ga += px * fmaf(P.c_dist, gzv, -p_att * cB);
+#pragma unroll
+        for (int c = 0; c < kAtHd; c++) gq[c] = fmaf(gzv, kk[c], gq[c]);
+    }
+    // the lanes' sums, one butterfly per value (fixed order)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ga += __shfl_xor_sync(0xffffffffu, ga, o);
+#pragma unroll
+        for (int c = 0; c < kAtHd; c++) gq[c] += __shfl_xor_sync(0xffffffffu, gq[c], o);
+    }
+    if (lane == 0) A.ga[i * H + h] = ga + gup;
+    if (lane == 0) {
+        float4* o4 = reinterpret_cast<float4*>(A.gq + (i * H + h) * kAtHd);
+#pragma unroll
+        for (int c = 0; c < kAtHd / 4; c++) o4[c] = make_float4(gq[4 * c], gq[4 * c + 1], gq[4 * c + 2], gq[4 * c + 3]);
+    }
+}
+
 template <bool ANG, bool TASKS>
 __global__ void __launch_bounds__(at_warps(true) * 32, kAtBwdBlocks) attn_bwd_kernel(const AtArgs A, const Params P)
 {
@@ -243,7 +455,7 @@ __global__ void __launch_bounds__(at_warps(true) * 32, kAtBwdBlocks) attn_bwd_ke
         W_s[(k + 0) * kAtWtStride + o] = w.x; W_s[(k + 1) * kAtWtStride + o] = w.y;
         W_s[(k + 2) * kAtWtStride + o] = w.z; W_s[(k + 3) * kAtWtStride + o] = w.w;
     }
-    LatticeLane<true, ANG> L;
+    LatticeLane<1, ANG> L;
     L.init(P, lane, tbuf + warp * 8 * 32);
     float* grow = rows + warp * 32;
     __syncthreads();
@@ -259,12 +471,12 @@ __global__ void __launch_bounds__(at_warps(true) * 32, kAtBwdBlocks) attn_bwd_ke
             const int cnt = d.w & 0xFFFFFF;
             if (cnt == 0) continue;
             i = d.x; row = d.y;
-            T = load_atom<true, ANG>(A, P, L, i, h, lane);
+            T = load_atom<1, ANG>(A, P, L, i, h, lane);
             T.e0 += d.z; T.e1 = T.e0 + cnt;
         } else {
             i = A.order != nullptr ? (int64_t)A.order[t] : t;
             row = i;
-            T = load_atom<true, ANG>(A, P, L, i, h, lane);
+            T = load_atom<1, ANG>(A, P, L, i, h, lane);
         }
         float qd = 0.f, god = 0.f, od = 0.f;
         if (lane < kAtHd) {
@@ -309,7 +521,7 @@ __global__ void __launch_bounds__(at_warps(true) * 32, kAtBwdBlocks) attn_bwd_ke
             const float zin = z_next;
             if (e + 1 < T.e1) z_next = __ldg(A.z_in + (e + 1) * H + h);      // requested one pair ahead
             L.ref = zin;
-            run_pair<true, ANG>(A, P, L, T, e);
+            run_pair<1, ANG>(A, P, L, T, e);
             // one butterfly for the five warp-wide sums of this pair; the four dot products of G with the
             // basis sums enter the results only through two combinations
             float r0 = qd * kd, r1 = god * vd, r2 = L.px_l;
@@ -427,6 +639,12 @@ __global__ void __launch_bounds__(256) attn_merge_fwd_kernel(const AtArgs A, con
     }
     if (lane == 0) A.lse[i * H + h] = m + logf(wsum);
     if (lane < kAtHd) A.out[(i * H + h) * kAtHd + lane] = o;
+    if (A.upool != nullptr && lane < kAtHd) {
+        float u = 0.f;
+        for (int c = 0; c < active; c++)
+            u = fmaf(__expf(__ldg(A.part_lse + (r0 + c) * H + h) - m) / wsum, __ldg(A.part_upool + ((r0 + c) * H + h) * kAtHd + lane), u);
+        A.upool[(i * H + h) * kAtHd + lane] = u;
+    }
 #pragma unroll
     for (int r = 0; r < 8; r++) A.spool[(i * H + h) * kAtK + r * 32 + lane] = s[r];
 }
@@ -484,20 +702,49 @@ int attn_plan(const int32_t* order, const int32_t* split, const float* a_ik, con
     return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
 }
 
+template <bool ANG, bool TASKS>
+static int launch_train(const AtArgs& A, const Params& P, cudaStream_t st)
+{
+    auto kern = attn_fwd_train_kernel<ANG, TASKS>;
+    static std::atomic<bool> attr_done[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_done[dev & 63]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAtTrainSmem) != cudaSuccess) return CFB200_E_CUDA;
+        attr_done[dev & 63] = true;
+    }
+    kern<<<dim3(at_grid_x(A.N, P.H, true), P.H), kAtTrainWarps * 32, kAtTrainSmem, st>>>(A, P);
+    if (TASKS) attn_merge_fwd_kernel<<<dim3(kSplitSlots / 8, P.H), 256, 0, st>>>(A, P.H);
+    return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
+}
+
+// A.val set: the training forward (per-pair results for attn_fused_bwd).
 int attn_fused_fwd(const AtArgs& A, const Params& P, cudaStream_t st)
 {
     if (A.N == 0) return CFB200_OK;
     if (cudaMemsetAsync(A.counters, 0, sizeof(int) * P.H, st) != cudaSuccess) return CFB200_E_CUDA;
-    if (A.tasks != nullptr) return A.W[1] != nullptr ? launch_at<false, true, true>(A, P, st) : launch_at<false, false, true>(A, P, st);
-    return A.W[1] != nullptr ? launch_at<false, true, false>(A, P, st) : launch_at<false, false, false>(A, P, st);
+    const bool ang = A.W[1] != nullptr;
+    if (A.val != nullptr) {
+        if (A.tasks != nullptr) return ang ? launch_train<true, true>(A, P, st) : launch_train<false, true>(A, P, st);
+        return ang ? launch_train<true, false>(A, P, st) : launch_train<false, false>(A, P, st);
+    }
+    if (A.tasks != nullptr) return ang ? launch_at<false, true, true>(A, P, st) : launch_at<false, false, true>(A, P, st);
+    return ang ? launch_at<false, true, false>(A, P, st) : launch_at<false, false, false>(A, P, st);
 }
 
+// A.val set: from the per-pair results of the training forward; else by recomputing the lattice sums.
 int attn_fused_bwd(const AtArgs& A, const Params& P, cudaStream_t st)
 {
     if (A.N == 0) return CFB200_OK;
+    if (A.val != nullptr) {
+        const int64_t tasks = A.N * P.H;
+        attn_bwd_saved_kernel<<<(unsigned)((tasks + 7) / 8), 256, 0, st>>>(A, P);
+        return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
+    }
     if (cudaMemsetAsync(A.counters, 0, sizeof(int) * P.H, st) != cudaSuccess) return CFB200_E_CUDA;
-    if (A.tasks != nullptr) return A.W[1] != nullptr ? launch_at<true, true, true>(A, P, st) : launch_at<true, false, true>(A, P, st);
-    return A.W[1] != nullptr ? launch_at<true, true, false>(A, P, st) : launch_at<true, false, false>(A, P, st);
+    const bool ang = A.W[1] != nullptr;
+    if (A.tasks != nullptr) return ang ? launch_at<true, true, true>(A, P, st) : launch_at<true, false, true>(A, P, st);
+    return ang ? launch_at<true, true, false>(A, P, st) : launch_at<true, false, false>(A, P, st);
 }
 
 }  // namespace cfb

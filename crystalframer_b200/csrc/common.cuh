@@ -87,7 +87,7 @@ constexpr float kAtPairCost = 350.0f, kAtTermCost = 70.0f;
 // the pruning sphere (radius^2 = 16 / |a|) of a Gaussian two standard deviations wider than typical (|a| = 0.051).
 constexpr int kSplitSlots = CFB200_SPLIT_SLOTS, kSplitMaxChunks = 8, kSplitMinPairs = 4;
 constexpr float kSplitMinTarget = 20000.0f, kSplitWideSphere = 23200.0f, kSplitWideCap = 1500.0f;
-constexpr int kSplitPartFwd = 288, kSplitPartBwd = 32;       // floats per partial row and head (273 and 17 used)
+constexpr int kSplitPartFwd = 304, kSplitPartBwd = 32;       // floats per partial row and head (289 and 17 used)
 
 // Chunks an (atom, head) task with `pairs` pairs really uses, of the `chunks` its crystal was given: its own
 // instruction estimate (translations within the pruning radius of its coefficient a) over the target.  Every warp

@@ -16,8 +16,13 @@ __device__ __forceinline__ float ll_int_to_float(int n)
     return __int_as_float(0x4B400000 + n) - 12582912.0f;
 }
 
-template <bool BWD, bool ANG>
+// MODE 0: forward, basis sums only.  MODE 1: backward by recomputation: weights relative to the pair's z, plus the
+// sums weighted with d^2 that the coefficient gradient needs.  MODE 2: forward that also forms those d^2-weighted sums
+// (weights relative to d^2_min, as in mode 0), so that the backward pass needs no second lattice sum.
+template <int MODE, bool ANG>
 struct LatticeLane {
+    static constexpr bool BWD = MODE != 0;        // d^2-weighted sums and sum p d^2 are formed
+    static constexpr bool REFZ = MODE == 1;       // ref is the pair's z (else d^2_min, found here)
     // per-lane basis constants, pre-scaled so that a Gaussian is ex2(-b*b)
     float cd_lo, cd_hi, ca_lo, ca_hi;
     float inv_d_interval, d_cut_scaled, xd_scale, inv_a_interval, xa_scale;
@@ -27,7 +32,7 @@ struct LatticeLane {
     float4* tb;       // per-warp records: [32] first halves, then [32] second halves (float4 backward, float2 forward)
     // per-pair state
     float sd[2], sa[3][2];      // basis sums
-    float qd[2], qa[3][2];      // backward: sums of g * p * d^2
+    float qd[2], qa[3][2];      // modes 1, 2: sums of g * p * d^2
     float sum_l, px_l;          // per-lane parts of sum w and (backward) sum w d^2
     float a, ref;               // Gaussian coefficient; forward: d^2_min, backward: z of the pair
     float fx[3], fy[3], fz[3];  // frame axes of the query atom
@@ -58,7 +63,7 @@ struct LatticeLane {
     // log of a translation's weight; adds its contribution to the normaliser (and, backward, to sum p d^2)
     __device__ __forceinline__ float weigh(const float d2)
     {
-        const float arg = BWD ? fmaf(a, d2, -ref) : a * (d2 - ref);
+        const float arg = REFZ ? fmaf(a, d2, -ref) : a * (d2 - ref);
         const float w = ex2_approx(arg * kLlLog2e);
         sum_l += w;
         if (BWD) px_l = fmaf(w, d2, px_l);
@@ -154,7 +159,7 @@ struct LatticeLane {
         const float* Ll = list + lane;
         const float dl0 = __ldg(Ll), dl1 = __ldg(Ll + 32), dl2 = __ldg(Ll + 64), dl3 = __ldg(Ll + 96);
         const float lx0 = __ldg(Ll + kListLen), ly0 = __ldg(Ll + 2 * kListLen), lz0 = __ldg(Ll + 3 * kListLen);
-        if (!BWD) ref = __shfl_sync(0xffffffffu, dl0, 0);
+        if (!REFZ) ref = __shfl_sync(0xffffffffu, dl0, 0);
         const float a0 = weigh(dl0), a1 = weigh(dl1), a2 = weigh(dl2), a3 = weigh(dl3);
         for (int g = 0; g < kListLen / 32; g++) {
             const float d2 = g == 0 ? dl0 : (g == 1 ? dl1 : (g == 2 ? dl2 : dl3));
@@ -181,7 +186,7 @@ struct LatticeLane {
         const int L1 = 2 * R1 + 1, L3 = 2 * R3 + 1, L23 = (2 * R2 + 1) * L3;
         const int nSub = (L23 + 31) >> 5;
         const float invL3 = 1.0f / (float)L3;
-        for (int pass = BWD ? 1 : 0; pass < 2; pass++) {
+        for (int pass = REFZ ? 1 : 0; pass < 2; pass++) {
             float d2min = 1e10f;
             for (int sub = 0; sub < nSub; sub++) {
                 const int idx = sub * 32 + lane;

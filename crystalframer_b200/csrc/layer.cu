@@ -388,6 +388,7 @@ static void layer_attn_args(cfb::AtArgs& A, const cfb200_layer_desc* L, const cf
         A.frame[0] = St->frames; A.frame[1] = St->frames + fr; A.frame[2] = St->frames + 2 * fr;
     }
     A.list = G->pair_list; A.cache_range = G->cache_range;
+    A.val = St->val; A.px = St->px; A.upool = St->upool;
 }
 
 int cfb200_encoder_layer_fwd(const cfb200_layer_desc* L, const cfb200_layer_weights* W, const cfb200_geometry* G,
@@ -467,6 +468,7 @@ int cfb200_encoder_layer_fwd(const cfb200_layer_desc* L, const cfb200_layer_weig
             A.part_spool = reinterpret_cast<float*>(workspace);
             A.part_out = A.part_spool + rows * 256;
             A.part_lse = A.part_out + rows * 16;
+            A.part_upool = A.part_lse + rows;
             // this layer's task table: which entries of the queue this layer's coefficients leave whole, cut or unused
             if ((rc = cfb::attn_plan(G->order, G->split, St->a, G->e_start, N, A.n_entries, H, A.chunk_count,
                                      reinterpret_cast<int4*>(St->tasks), st)) != CFB200_OK)

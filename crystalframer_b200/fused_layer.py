@@ -31,6 +31,9 @@ FUSED_FORWARD_CALLS = ("cfb200_encoder_layer_fwd",)
 # cut the longest (atom, head) tasks of the attention kernels into chunks (see cfb200_batch_geometry); a switch for
 # tests and measurements
 SPLIT_TASKS = True
+# training forward leaves per-pair value encodings for the backward pass (no second lattice sum); a switch for tests
+# and measurements, and for batches whose (E,H,17) floats per layer do not fit
+SAVE_PAIR_RESULTS = True
 # test hook: a list here receives a copy of every layer's frames (3,N,H,3) as the forward computes them
 FRAME_TAP = None
 
@@ -140,11 +143,16 @@ class LayerGeometry:
         return self._ws
 
 
-def _state_layout(N, E, H, D, F, frames, tasks_bytes=0):
-    """Offsets (floats) of the activations a layer's forward leaves for its backward, in one buffer."""
+def _state_layout(N, E, H, D, F, frames, tasks_bytes=0, pair_results=False):
+    """Offsets (floats) of the activations a layer's forward leaves for its backward, in one buffer.
+    ``pair_results``: room for the per-pair value encodings (val, px, upool) with which the backward pass needs no
+    second lattice sum."""
+    hd = D // H
     sizes = (("q", N * D), ("q_scaled", N * D), ("k", N * D), ("v", N * D), ("a", N * H),
              ("frames", 9 * N * H if frames else 0), ("z", E * H), ("spool", N * H * 256), ("attn", N * D),
-             ("lse", N * H), ("x1", N * D), ("h", N * F), ("tasks", tasks_bytes // 4))
+             ("lse", N * H), ("x1", N * D), ("h", N * F), ("tasks", tasks_bytes // 4),
+             ("val", E * H * hd if pair_results else 0), ("px", E * H if pair_results else 0),
+             ("upool", N * D if pair_results else 0))
     off, total = {}, 0
     for name, n in sizes:
         off[name] = total if n else None
@@ -180,7 +188,10 @@ class FusedEncoderLayerFunc(torch.autograd.Function):
                               seed1, seed2)
         W = _lib.LayerWeights(*[None if p is None else _lib.ptr(p) for p in params])
         tasks_bytes = int(_lib.lib().cfb200_attn_tasks_bytes(N)) if geo.c.split else 0
-        off, total = _state_layout(N, E, H, D, F, method != 0, tasks_bytes)
+        # with gradients wanted the forward stores per-pair results (68 bytes per pair and head) and the backward
+        # needs no second lattice sum; without, the lighter forward runs
+        save_pairs = SAVE_PAIR_RESULTS and any(ctx.needs_input_grad)
+        off, total = _state_layout(N, E, H, D, F, method != 0, tasks_bytes, save_pairs)
         state = torch.empty(total, dtype=torch.float32, device=dev)
         base = state.data_ptr()
         St = _lib.LayerState(*[None if off[f] is None else base + 4 * off[f] for f, _ in _lib.LayerState._fields_])

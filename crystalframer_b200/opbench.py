@@ -76,13 +76,15 @@ def run_once_fused(I):
         I["counters"] = torch.zeros(H, dtype=torch.int32, device=dev)
     W = [w[0] for w in I["W"]]
     out, z, lse, spool = (torch.empty(s, device=dev) for s in ((N, H, hd), (E, H), (N, H), (N, H, 256)))
+    # per-pair results the forward leaves for the backward (None: the backward recomputes the lattice sums)
+    saved = [torch.empty(s, device=dev) for s in ((E, H, hd), (E, H), (N, H, hd))] if I.get("save_pairs", True) else [None] * 3
     common = (p(qs), p(k), p(v), p(a), p(I["pos_ij"]), p(I["tv"]), p(I["rvlen"]), ip(I["batch"]), ip(I["edges"]),
               ip(I["e_start"]), p(I["order"], torch.int32), p(I["counters"], torch.int32), N, E, 14.0, -3.5, p(W[0]),
               p(W[1]), p(W[2]), p(W[3]), p(f1), p(f2), p(f3), p(plist), prange)
-    _lib.invoke("cfb200_attn_fused_fwd", 1, dev, *common, p(out), p(z), p(lse), p(spool), 0)
+    _lib.invoke("cfb200_attn_fused_fwd", 1, dev, *common, p(out), p(z), p(lse), p(spool), *[p(x) for x in saved], 0)
     gq, gk, gv, ga, gz = (torch.empty(s, device=dev) for s in ((N, H, hd), (N, H, hd), (N, H, hd), (N, H), (E, H)))
     _lib.invoke("cfb200_attn_fused_bwd", 2, dev, *common, p(out), p(z), p(lse), p(I["go"]), p(gq), p(gk), p(gv), p(ga),
-                p(gz), 0)
+                p(gz), *[p(x) for x in saved], 0)
     gW = torch.bmm(I["go"].permute(1, 2, 0), spool.permute(1, 0, 2))
     return out, gW
 
@@ -95,10 +97,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--noise", type=float, default=1e-5)
     ap.add_argument("--fused", action="store_true", help="time the fused attention entry points")
+    ap.add_argument("--recompute", action="store_true",
+                    help="with --fused: lighter forward, backward recomputes the lattice sums (no per-pair results kept)")
     args = ap.parse_args()
     dev = torch.device("cuda:0")
     F.compile_kernels(2, 8, 16, 64, 64, 16, True, 0, 1.0, 4.0, 1.0, 1.0, args.noise)
     I = make_inputs(args.workload, args.crystals, dev)
+    I["save_pairs"] = not args.recompute
     step = run_once_fused if args.fused else run_once
     for _ in range(args.warmup):
         step(I)

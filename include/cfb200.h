@@ -314,7 +314,11 @@ int cfb200_framed_proj_bwd_cached(const float* a_ik, const float* pos_ij, const 
  * the angle coefficient -- the weight gradients are  gW[h] (16 x 256) = sum_i gout[i,h,:]^T spool[i,h,:],
  * a GEMM left to the caller.
  * The backward takes the forward's out, z, lse and the upstream gout (N,H,16) and returns gq_scaled, gk,
- * gv (N,H,16), ga (N,H) and gz (E,H) (scratch the column pass reads; also the gradient of the logit bias). */
+ * gv (N,H,16), ga (N,H) and gz (E,H) (scratch the column pass reads; also the gradient of the logit bias).
+ * val (E,H,16), px (E,H) and upool (N,H,16), all three or none: with them the forward also stores, per (pair,
+ * head), the value encoding W s and sum p d^2 (68 bytes), and per (atom, head) the projection of the
+ * attention-pooled basis sums weighted with d^2; the backward, given the same three, is a plain ragged-attention
+ * backward.  Without them the forward is lighter and the backward recomputes the lattice sums. */
 int cfb200_attn_fused_fwd(const float* q_scaled, const float* k, const float* v, const float* a_ik,
                           const float* pos_ij, const float* tvecs, const float* rvlen,
                           const int64_t* batch, const int64_t* edges, const int64_t* e_start,
@@ -323,7 +327,7 @@ int cfb200_attn_fused_fwd(const float* q_scaled, const float* k, const float* v,
                           const float* W_ang2, const float* W_ang3, const float* frame1,
                           const float* frame2, const float* frame3, const float* pair_list,
                           int cache_range, float* out, float* z, float* lse, float* spool,
-                          int unwindowed, void* stream);
+                          float* val, float* px, float* upool, int unwindowed, void* stream);
 int cfb200_attn_fused_bwd(const float* q_scaled, const float* k, const float* v, const float* a_ik,
                           const float* pos_ij, const float* tvecs, const float* rvlen,
                           const int64_t* batch, const int64_t* edges, const int64_t* e_start,
@@ -333,7 +337,8 @@ int cfb200_attn_fused_bwd(const float* q_scaled, const float* k, const float* v,
                           const float* frame2, const float* frame3, const float* pair_list,
                           int cache_range, const float* out, const float* z, const float* lse,
                           const float* gout, float* gq_scaled, float* gk, float* gv, float* ga,
-                          float* gz, int unwindowed, void* stream);
+                          float* gz, const float* val, const float* px, const float* upool, int unwindowed,
+                          void* stream);
 
 /* Replaces FusedDotProductAttentionCUDA.forward (models/cuda_funcs/fused_dpa.py:17-64;
  * kernel fused_dpa_fwd.cu).  q_scaled, k, v (N,H,head_dim); z (E,H) or NULL; values
@@ -435,10 +440,14 @@ typedef struct cfb200_geometry {
 /* Activations a layer's forward leaves for its backward (caller-allocated): q, q_scaled, k, v, attn, x1
  * (N,D); a, lse (N,H); frames (3,N,H,3) (NULL for frame_method 0); z (E,H); spool (N,H,256); h (N,F); tasks:
  * cfb200_attn_tasks_bytes(N) bytes, 16-byte aligned, the layer's task table when the geometry carries a chunked
- * queue (NULL otherwise, or to run the layer on the plain queue). */
+ * queue (NULL otherwise, or to run the layer on the plain queue); val (E,H,16), px (E,H) and upool (N,H,16):
+ * results of the forward lattice sum with which the backward pass needs no second lattice sum (all three or none:
+ * with NULL the forward is lighter and the backward recomputes -- the choice for inference and when memory is
+ * short). */
 typedef struct cfb200_layer_state {
     float *q, *q_scaled, *k, *v, *a, *frames, *z, *spool, *attn, *lse, *x1, *h;
     void* tasks;
+    float *val, *px, *upool;
 } cfb200_layer_state;
 
 /* frame_method: 0 = none (plain Crystalformer encoding), 1 = max frames, 2 = weighted-PCA frames, 3 = static max

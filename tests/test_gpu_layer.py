@@ -130,7 +130,8 @@ def test_one_call_layer_matches_operator_path(frame_method, workload, nc):
     assert _lib.read_status(dev) == 0
 
 
-def test_chunked_tasks_change_nothing_but_rounding():
+@pytest.mark.parametrize("save_pairs", [True, False])
+def test_chunked_tasks_change_nothing_but_rounding(save_pairs):
     """A batch with dense 48-64 atom cells among small crystals: the work queue cuts their atoms' tasks into chunks
     (partial results merged in chunk order).  Outputs and gradients equal the uncut run to rounding, and two cut runs
     are bit-identical however the chunks were scheduled."""
@@ -154,6 +155,7 @@ def test_chunked_tasks_change_nothing_but_rounding():
         seen.append(g)
         return g
     fused_layer.LayerGeometry.from_raw = classmethod(spy)
+    fused_layer.SAVE_PAIR_RESULTS = save_pairs         # backward from stored per-pair results, or by recomputation
     results = []
     try:
         for split in (False, True, True):
@@ -166,6 +168,7 @@ def test_chunked_tasks_change_nothing_but_rounding():
             results.append((out.detach().clone(), {n: p.grad.detach().clone() for n, p in model.named_parameters() if p.grad is not None}))
     finally:
         fused_layer.SPLIT_TASKS = True
+        fused_layer.SAVE_PAIR_RESULTS = True
         fused_layer.LayerGeometry.from_raw = classmethod(orig)
     assert len(seen) == 3 and seen[0].split is None
     header = seen[1].split[:4].cpu().numpy()

@@ -391,10 +391,12 @@ def test_whole_model_against_cpu_oracle(layers, frame_method, fused):
             assert not bad.any(), f"{n}: max abs diff {np.abs(g - c).max():.3e} at scale {scale:.3e}"
 
 
+@pytest.mark.parametrize("saved", [False, True])
 @pytest.mark.parametrize("workload,nc,use_list", [("cfg1", None, True), ("cfg2", 24, True), ("cfg2", 24, False)])
-def test_fused_attention_entry_points(workload, nc, use_list):
-    """cfb200_attn_fused_fwd / _bwd (lattice sums + value encoding + attention in one pass, the value
-    encoding never materialised) against the CPU oracle's chain of the separate operators."""
+def test_fused_attention_entry_points(workload, nc, use_list, saved):
+    """cfb200_attn_fused_fwd / _bwd (lattice sums + value encoding + attention in one pass) against the CPU oracle's
+    chain of the separate operators.  saved: the forward keeps per-pair results and the backward uses them; else the
+    lighter forward, and the backward recomputes the lattice sums."""
     dev = _cuda()
     from oracle import oracle as O
     from crystalframer_b200 import _lib
@@ -435,19 +437,25 @@ def test_fused_attention_entry_points(workload, nc, use_list):
     common = (p(q_), p(k_), p(v_), p(a_), p(g["pos_ij"]), p(g["tvecs"]), p(g["rvlen"]), ip(g["batch"]), ip(g["edges"]),
               ip(e_start), p(order, torch.int32), p(counters, torch.int32), N, E, 14.0, -3.5, p(W[0]), p(W[1]), p(W[2]),
               p(W[3]), p(f[0]), p(f[1]), p(f[2]), p(plist), 2)
-    _lib.invoke("cfb200_attn_fused_fwd", 1, dev, *common, p(out), p(z), p(lse), p(spool), 0)
+    keep = [torch.empty(s, device=dev) for s in ((E, H, hd), (E, H), (N, H, hd))] if saved else [None] * 3
+    kp = [p(x) for x in keep]
+    _lib.invoke("cfb200_attn_fused_fwd", 1, dev, *common, p(out), p(z), p(lse), p(spool), *kp, 0)
+    if saved:
+        _close("values", keep[0].cpu().numpy(), v_w)         # the stored value encoding is the operator's output
     _close("z", z.cpu().numpy(), z_w)
     _close("out", out.cpu().numpy(), out_w)
     gq, gk, gv, ga, gz = (torch.empty(s, device=dev) for s in ((N, H, hd), (N, H, hd), (N, H, hd), (N, H), (E, H)))
     _lib.invoke("cfb200_attn_fused_bwd", 2, dev, *common, p(out), p(z), p(lse), p(t(go)), p(gq), p(gk), p(gv), p(ga), p(gz),
-                0)
+                *kp, 0)
     # atoms are drawn from a work queue, so which warp computes which atom varies from run to run; no sum
     # crosses atoms, hence every output must repeat bit for bit
     out_b, z_b, lse_b, spool_b = (torch.empty_like(x) for x in (out, z, lse, spool))
-    _lib.invoke("cfb200_attn_fused_fwd", 1, dev, *common, p(out_b), p(z_b), p(lse_b), p(spool_b), 0)
+    keep_b = [torch.empty_like(x) for x in keep] if saved else [None] * 3
+    _lib.invoke("cfb200_attn_fused_fwd", 1, dev, *common, p(out_b), p(z_b), p(lse_b), p(spool_b), *[p(x) for x in keep_b], 0)
+    assert not saved or all(torch.equal(x, y) for x, y in zip(keep, keep_b))
     assert all(torch.equal(x, y) for x, y in ((out, out_b), (z, z_b), (lse, lse_b), (spool, spool_b)))
     again = [torch.empty_like(x) for x in (gq, gk, gv, ga, gz)]
-    _lib.invoke("cfb200_attn_fused_bwd", 2, dev, *common, p(out), p(z), p(lse), p(t(go)), *[p(x) for x in again], 0)
+    _lib.invoke("cfb200_attn_fused_bwd", 2, dev, *common, p(out), p(z), p(lse), p(t(go)), *[p(x) for x in again], *kp, 0)
     assert all(torch.equal(x, y) for x, y in zip((gq, gk, gv, ga, gz), again))
     _close("gq", gq.cpu().numpy(), gq_w)
     _close("gk", gk.cpu().numpy(), gk_w)
