@@ -51,7 +51,7 @@ FLOP_PROJ_FWD, FLOP_PROJ_BWD = 8192.0, 16384.0
 FLOP_ATT_FWD, FLOP_ATT_BWD = 70.0, 170.0          # ragged attention per (pair, head)
 # DRAM bytes (read + write) of one launch of the fused attention kernels on batch 0 of this benchmark, as the
 # profiler counted them (dram__bytes_read.sum + dram__bytes_write.sum; one kernel, two launches captured)
-NCU_TRAFFIC_BYTES = {"attn_fwd_kernel": 58.2e6, "attn_bwd_kernel": 53.2e6}
+NCU_TRAFFIC_BYTES = {}
 
 
 def parse():
@@ -503,25 +503,38 @@ def run_ours(args, rank, world, local_rank):
     kern = {}
     for name, (calls, total) in list(ktimes.items()) + list(stages.items()):
         kern[name] = {"calls": calls, "ms_total": round(total, 3), "ms_avg": round(total / max(calls, 1), 4)}
-    # the dominant kernel: the backward of the fused lattice-sum attention (attn_bwd_kernel), timed by CUDA events
-    # around its launch inside cfb200_encoder_layer_bwd
-    bwd_name, fwd_name = "attn_bwd_kernel", "attn_fwd_kernel"
-    bwd_ms, fwd_ms = per_launch(bwd_name), per_launch(fwd_name)
-    flops_bwd = avg_terms * FLOP_TERM_BWD + pairs_heads * (FLOP_PROJ_BWD + FLOP_ATT_BWD)
+    # The dominant kernel: the training forward of the fused lattice-sum attention (attn_fwd_train_kernel), timed by
+    # CUDA events around its launch inside cfb200_encoder_layer_fwd.  It performs the lattice sums of BOTH sweeps the
+    # reference's algorithm makes per layer (its forward kernels and the recomputation in its backward kernels): the
+    # backward kernel here (attn_bwd_saved_kernel) repeats none of it.  `achieved` therefore counts the term work of
+    # both sweeps plus the forward projection and attention; `forward_only` beside it counts the forward sweep alone,
+    # and `layer` the whole attention path of a layer (forward, backward and column kernels) against all its
+    # algorithmic work.
+    fwd_name, bwd_name = "attn_fwd_train_kernel", "attn_bwd_saved_kernel"
+    fwd_ms, bwd_ms, cols_ms = per_launch("attn_fwd_kernel"), per_launch("attn_bwd_kernel"), per_launch("attn_bwd_cols_kernel")
     flops_fwd = avg_terms * FLOP_TERM_FWD + pairs_heads * (FLOP_PROJ_FWD + FLOP_ATT_FWD)
-    ach = flops_bwd / (bwd_ms * 1e-3) / 1e12
-    roofline = {"kernel": bwd_name, "bound": "fp32+sfu",
+    flops_bwd = avg_terms * FLOP_TERM_BWD + pairs_heads * (FLOP_PROJ_BWD + FLOP_ATT_BWD)
+    flops_dom = flops_fwd + avg_terms * FLOP_TERM_BWD
+    tf = lambda flop, ms_: flop / (max(ms_, 1e-9) * 1e-3) / 1e12
+    ach = tf(flops_dom, fwd_ms)
+    layer_ms = fwd_ms + bwd_ms + cols_ms
+    roofline = {"kernel": fwd_name, "bound": "fp32+sfu",
                 "achieved": ach, "peak": peaks["fp32_tflops"], "unit": "TFLOP/s", "frac": ach / peaks["fp32_tflops"],
                 "peak_source": "FP32 FMA throughput measured on this device by cfb200_probe_throughput",
-                "algorithmic_flop_per_launch": flops_bwd, "terms_per_launch": avg_terms, "ms_per_launch": bwd_ms,
-                "sfu_achieved_tops": avg_terms * SFU_TERM / (bwd_ms * 1e-3) / 1e12, "sfu_peak_tops": peaks["sfu_tops"],
+                "algorithmic_flop_per_launch": flops_dom, "terms_per_launch": avg_terms, "ms_per_launch": fwd_ms,
+                "counts": "lattice-sum terms of both sweeps of the reference's layer (516 + 738 flop per term: this kernel "
+                          "leaves nothing of them to the backward pass) + forward projection and attention per (pair, head)",
+                "sfu_achieved_tops": avg_terms * 2 * SFU_TERM / (fwd_ms * 1e-3) / 1e12, "sfu_peak_tops": peaks["sfu_tops"],
                 # DRAM read + write bytes of ONE launch of this kernel on this workload's first batch, from a profiler
                 # capture of this command (one kernel, two launches); None until such a capture has been taken
-                "traffic": NCU_TRAFFIC_BYTES.get(bwd_name),
+                "traffic": NCU_TRAFFIC_BYTES.get(fwd_name),
                 "traffic_unit": "bytes per launch (DRAM read + write)",
-                "forward": {"kernel": fwd_name, "ms_per_launch": fwd_ms, "achieved": flops_fwd / (fwd_ms * 1e-3) / 1e12,
-                            "frac": flops_fwd / (fwd_ms * 1e-3) / 1e12 / peaks["fp32_tflops"],
-                            "traffic": NCU_TRAFFIC_BYTES.get(fwd_name)}}
+                "forward_only": {"algorithmic_flop_per_launch": flops_fwd, "achieved": tf(flops_fwd, fwd_ms),
+                                 "frac": tf(flops_fwd, fwd_ms) / peaks["fp32_tflops"]},
+                "layer": {"kernels": [fwd_name, bwd_name, "dpa_bwd_cols_kernel"], "ms": layer_ms,
+                          "algorithmic_flop": flops_fwd + flops_bwd, "achieved": tf(flops_fwd + flops_bwd, layer_ms),
+                          "frac": tf(flops_fwd + flops_bwd, layer_ms) / peaks["fp32_tflops"]},
+                "backward": {"kernel": bwd_name, "ms_per_launch": bwd_ms, "traffic": NCU_TRAFFIC_BYTES.get(bwd_name)}}
     # the HBM-bound kernels of the path (ragged attention): algorithmic bytes over CUDA-event time against the
     # copy bandwidth measured on this pool (MEASURED_PEAKS.json beside this file; 6650 GB/s if it is absent)
     hbm_peak, hbm_src = 6650.0, "fallback"

@@ -67,6 +67,7 @@ SIGNATURES = {
     "cfb200_lattice_frames": (ctypes.c_int, [vp] * 6 + [i64, i64, f32, u64, u64, u64] + [vp] * 4),
     "cfb200_max_frames": (ctypes.c_int, [vp] * 9 + [i64, i64, f32, u64, u64] + [vp] * 4),
     "cfb200_pair_cache": (ctypes.c_int, [vp] * 4 + [i64, i64, ctypes.c_int, vp, vp, vp]),
+    "cfb200_pca_frames": (ctypes.c_int, [vp, vp, i64, i64, u64, vp, vp, vp, vp]),
     "cfb200_max_frame_cached": (ctypes.c_int, [ctypes.c_int] + [vp] * 9 + [i64, i64, f32, u64] + [vp] * 6 + [ctypes.c_int, vp]),
     "cfb200_max_frames_cached": (ctypes.c_int, [vp] * 9 + [i64, i64, f32, u64, u64] + [vp] * 5 + [ctypes.c_int, vp]),
     "cfb200_framed_proj_fwd_cached": (ctypes.c_int, [vp] * 6 + [i64, i64, f32, f32] + [vp] * 11 + [ctypes.c_int, vp]),

@@ -7,7 +7,7 @@ arguments, same parameter names, shapes and initialisation (so released checkpoi
 data-dependent ``gauss_scale`` state.  Input / output projections and the Gaussian-coefficient
 pipeline stay in PyTorch; everything between them runs in libcfb200.
 
-Only the real-space domain is implemented, with frame methods "max", "max_static", "lattice" and
+Only the real-space domain is implemented, with frame methods "max", "max_static", "lattice", "pca",
 "weighted_pca" (CrystalFramer) and "no" (plain Crystalformer distance encoding).
 """
 import math
@@ -21,7 +21,7 @@ from torch.nn.init import constant_, normal_, xavier_uniform_
 from torch.nn.modules.linear import NonDynamicallyQuantizableLinear
 
 from .cuda_funcs import (ComputeFrame1MaximumMethodCUDA, ComputeFrame1MaximumStaticMethodCUDA,
-                         ComputeFrame2MaximumMethodCUDA, ComputeFrame2MaximumStaticMethodCUDA, ComputeLatticeFrameCUDA,
+                         ComputeFrame2MaximumMethodCUDA, ComputeFrame2MaximumStaticMethodCUDA, ComputeLatticeFrameCUDA, ComputePCAFrame,
                          FusedDotProductAttentionCUDA, RealEncodingWithFramedProjFuncCUDA,
                          RealPeriodicEncodingWithProjFuncCUDA, max_frames_fused, max_static_frames_fused,
                          weighted_pca_frames)
@@ -87,6 +87,15 @@ def compute_real_domain_attn_frame_proj(q, k, v, batch_q, batch_kv, edges, pos, 
             f1, f2, f3 = ComputeLatticeFrameCUDA.apply(q / math.sqrt(q.shape[-1]), k, None, alpha, pos, dist2_min, tvecs,
                                                        batch_q, edges, K, dist_max, wscale, *rv_args)
         W1, W2, W3 = proj_angle1, proj_angle2, proj_angle3
+    elif params.frame_method == "pca":
+        # models/indexed_lattice_multi_head_attention_cuda.py:522-534
+        with torch.no_grad():
+            f1, f2, f3 = ComputePCAFrame.apply(q / math.sqrt(q.shape[-1]), k, None, alpha, pos, dist2_min, tvecs,
+                                               batch_q, edges, K, dist_max, wscale, *rv_args)
+        W1, W2, W3 = proj_angle1, proj_angle2, proj_angle3
+        from . import fused_layer
+        if fused_layer.FRAME_TAP is not None:
+            fused_layer.FRAME_TAP.append(torch.stack([f1, f2, f3]).clone())
     elif params.frame_method == "weighted_pca":
         with torch.no_grad():
             qs = q / math.sqrt(q.shape[-1])

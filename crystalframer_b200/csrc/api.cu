@@ -289,6 +289,16 @@ int cfb200_pair_cache(const float* pos_ij, const float* tvecs, const int64_t* ba
     return cfb::pair_cache(pos_ij, tvecs, batch, edges, E, range, pair_cache, pair_list, S(stream));
 }
 
+int cfb200_pca_frames(const float* pos_ij, const int64_t* e_start, int64_t N, int64_t E, uint64_t seed, float* frame1,
+                      float* frame2, float* frame3, void* stream)
+{
+    if (!g_configured) return CFB200_E_NOT_CONFIGURED;
+    if (N < 0 || E < 0) return CFB200_E_SHAPE;
+    if (N == 0) return CFB200_OK;
+    if (!e_start || (E > 0 && !pos_ij) || !frame1 || !frame2 || !frame3) return CFB200_E_NULL;
+    return cfb::pca_frames(pos_ij, e_start, N, g_cfg.num_heads, seed, frame1, frame2, frame3, S(stream));
+}
+
 int cfb200_max_frame_cached(int axis, const float* q_scaled, const float* k, const float* a_ik, const float* pos_ij,
                             const float* tvecs, const float* rvlen, const int64_t* batch, const int64_t* edges,
                             const int64_t* e_start, int64_t N, int64_t E, float cutoff_radius, uint64_t seed,

@@ -354,7 +354,7 @@ static int layer_check(const cfb200_layer_desc* L, const cfb200_layer_weights* W
     const int H = g_cfg.num_heads;
     if (L->d_model != H * g_cfg.head_dim || g_cfg.head_dim != 16 || g_cfg.dist_dim != 64 || L->ff_dim <= 0 || (L->ff_dim & 3))
         return CFB200_E_UNSUPPORTED;
-    if (L->frame_method < 0 || L->frame_method > 4) return CFB200_E_UNSUPPORTED;
+    if (L->frame_method < 0 || L->frame_method > 5) return CFB200_E_UNSUPPORTED;
     if (L->frame_method != 0 && g_cfg.angle_dim == 0) return CFB200_E_UNSUPPORTED;
     if (G->N < 0 || G->E < 0) return CFB200_E_SHAPE;
     if (G->N > 0x7fffffff) return CFB200_E_TOO_LARGE;
@@ -448,6 +448,9 @@ int cfb200_encoder_layer_fwd(const cfb200_layer_desc* L, const cfb200_layer_weig
         TmScope tm(CFB200_TM_FRAMES, st);
         rc = cfb200_lattice_frames(St->a, G->tvecs, G->rvlen, G->batch, G->edges, G->e_start, N, E, L->cutoff_radius, L->seed1,
                                    L->seed2, L->seed1 ^ L->seed2, St->frames, St->frames + fr, St->frames + 2 * fr, stream);
+    } else if (L->frame_method == 5) {
+        TmScope tm(CFB200_TM_FRAMES, st);
+        rc = cfb200_pca_frames(G->pos_ij, G->e_start, N, E, L->seed1, St->frames, St->frames + fr, St->frames + 2 * fr, stream);
     } else if (L->frame_method == 2) {
         TmScope tm(CFB200_TM_FRAMES, st);
         rc = cfb200_sigma_frames(St->q_scaled, St->k, St->a, G->pos_ij, G->tvecs, G->rvlen, G->batch, G->edges, G->e_start, N, E,

@@ -210,6 +210,63 @@ __global__ void __launch_bounds__(128) sigma_frames_kernel(const SgArgs A, const
     for (int c = 0; c < 3; c++) { o1[c] = Fm[0][c] * flip; o2[c] = Fm[1][c] * flip; o3[c] = Fm[2][c] * flip; }
 }
 
+// "pca" frames (replaces ComputePCAFrame, models/cuda_funcs/calc_pca_frame.py:22-76 of the reference, which is
+// torch_scatter + torch.linalg.eigh + torch.randint): warp = atom.  The scatter matrix of the atom's pair
+// separations in the home cell about their mean, sum_j (r_ij - mean)(r_ij - mean)^T, its eigenvectors by ascending
+// eigenvalue as the three axes -- the same for every head -- then per (atom, head) a hash-drawn sign per axis and all
+// three times the determinant of the signed triple (the reference draws the signs with torch.randint, and its
+// eigenvectors' own signs are LAPACK's: neither is pinned; here an eigenvector's largest component is positive before
+// the drawn sign).  No lattice translations enter.
+__global__ void __launch_bounds__(128) pca_frames_kernel(const float* __restrict__ pos_ij, const int64_t* __restrict__ e_start,
+                                                         int64_t N, int H, uint64_t seed, float* __restrict__ f1,
+                                                         float* __restrict__ f2, float* __restrict__ f3)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t i = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (i >= N) return;
+    const int64_t e0 = e_start[i], e1 = e_start[i + 1];
+    float sx = 0.f, sy = 0.f, sz = 0.f;
+    for (int64_t e = e0 + lane; e < e1; e += 32) { sx += __ldg(pos_ij + 3 * e); sy += __ldg(pos_ij + 3 * e + 1); sz += __ldg(pos_ij + 3 * e + 2); }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        sx += __shfl_xor_sync(0xffffffffu, sx, o); sy += __shfl_xor_sync(0xffffffffu, sy, o); sz += __shfl_xor_sync(0xffffffffu, sz, o);
+    }
+    const float inv_n = e1 > e0 ? 1.0f / (float)(e1 - e0) : 0.f;
+    const float mx = sx * inv_n, my = sy * inv_n, mz = sz * inv_n;
+    float c[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int64_t e = e0 + lane; e < e1; e += 32) {
+        const float x = __ldg(pos_ij + 3 * e) - mx, y = __ldg(pos_ij + 3 * e + 1) - my, z = __ldg(pos_ij + 3 * e + 2) - mz;
+        c[0] = fmaf(x, x, c[0]); c[1] = fmaf(x, y, c[1]); c[2] = fmaf(x, z, c[2]);
+        c[3] = fmaf(y, y, c[3]); c[4] = fmaf(y, z, c[4]); c[5] = fmaf(z, z, c[5]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int m = 0; m < 6; m++) c[m] += __shfl_xor_sync(0xffffffffu, c[m], o);
+    float M[3][3], w[3], V[3][3];
+    M[0][0] = c[0]; M[0][1] = M[1][0] = c[1]; M[0][2] = M[2][0] = c[2]; M[1][1] = c[3]; M[1][2] = M[2][1] = c[4]; M[2][2] = c[5];
+    eigh3(M, w, V);                                      // every lane: the same small computation
+    for (int h = lane; h < H; h += 32) {
+        float Fm[3][3];                                  // Fm[r] = axis r = column r of V with its drawn sign
+        for (int r = 0; r < 3; r++) {
+            const float sgn = hash_uniform(seed, (uint64_t)(i * H + h), (uint32_t)r) > 0.5f ? 1.0f : -1.0f;
+            for (int k = 0; k < 3; k++) Fm[r][k] = V[k][r] * sgn;
+        }
+        const float det = Fm[0][0] * (Fm[1][1] * Fm[2][2] - Fm[1][2] * Fm[2][1]) - Fm[0][1] * (Fm[1][0] * Fm[2][2] - Fm[1][2] * Fm[2][0])
+                          + Fm[0][2] * (Fm[1][0] * Fm[2][1] - Fm[1][1] * Fm[2][0]);
+        float* o1 = f1 + (i * H + h) * 3; float* o2 = f2 + (i * H + h) * 3; float* o3 = f3 + (i * H + h) * 3;
+        for (int k = 0; k < 3; k++) { o1[k] = Fm[0][k] * det; o2[k] = Fm[1][k] * det; o3[k] = Fm[2][k] * det; }
+    }
+}
+
+int pca_frames(const float* pos_ij, const int64_t* e_start, int64_t N, int H, uint64_t seed, float* f1, float* f2, float* f3,
+               cudaStream_t st)
+{
+    if (N == 0) return CFB200_OK;
+    pca_frames_kernel<<<(unsigned)((N + 3) / 4), 128, 0, st>>>(pos_ij, e_start, N, H, seed, f1, f2, f3);
+    return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
+}
+
 // the per-pair records alone (what the reference's real_enc_sigma_fwd.cu leaves, plus the logit it omits)
 int sigma_edges(const SgArgs& A, const Params& P, cudaStream_t st)
 {

@@ -215,3 +215,30 @@ class ComputeLatticeFrameCUDA(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g1, g2, g3):
         return (None,) * 14
+
+
+class ComputePCAFrame(torch.autograd.Function):
+    """Drop-in for models/cuda_funcs/calc_pca_frame.py:22-80: frames from the principal axes of an atom's pair
+    separations in the home cell -- (frame_first, frame_second, frame_third), each (N,H,3), by ascending eigenvalue,
+    with a drawn sign per axis and head and the triple times its determinant.  The signs come from one draw of
+    torch's generator hashed per (atom, head, axis) (the reference takes three torch.randint tensors), and the
+    eigenvectors' own signs are fixed by "largest component positive" (the reference's are LAPACK's): the axes
+    agree with the reference's up to sign."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, a_ik, rpos_ij_e, dist2_min_e, tvecs_n, batch_i, edge_ij_e, K, dist_max, wscale,
+                rvlen_n=None, cutoff_radius=None):
+        N, H = a_ik.shape
+        E = edge_ij_e.shape[1]
+        dev = a_ik.device
+        pos = f32c(rpos_ij_e)
+        e_start = csr_offsets(edge_ij_e.contiguous(), N)
+        seed = int(torch.randint(0, 2 ** 62, (1,)).item())
+        f = torch.empty((3, N, H, 3), device=dev, dtype=torch.float32)
+        p, ip = _lib.ptr, _lib.iptr
+        _lib.invoke("cfb200_pca_frames", 1, dev, p(pos), ip(e_start), N, E, seed, p(f[0]), p(f[1]), p(f[2]))
+        return f[0], f[1], f[2]
+
+    @staticmethod
+    def backward(ctx, gframe_first, gframe_second, gframe_third):
+        return (None,) * 14

@@ -37,7 +37,7 @@ SAVE_PAIR_RESULTS = True
 # test hook: a list here receives a copy of every layer's frames (3,N,H,3) as the forward computes them
 FRAME_TAP = None
 
-FRAME_METHODS = {"no": 0, "max": 1, "weighted_pca": 2, "max_static": 3, "lattice": 4}
+FRAME_METHODS = {"no": 0, "max": 1, "weighted_pca": 2, "max_static": 3, "lattice": 4, "pca": 5}
 WEIGHT_FIELDS = ("q_proj", "k_proj", "v_proj", "in_bias", "lattice_pos", "gauss_scale", "out_proj", "out_bias",
                  "pe_dist", "pe_ang1", "pe_ang2", "pe_ang3", "ff1", "ff1_bias", "ff2", "ff2_bias")
 GRAD_FIELDS = tuple(f for f in WEIGHT_FIELDS if f != "gauss_scale")
@@ -182,6 +182,8 @@ class FusedEncoderLayerFunc(torch.autograd.Function):
         elif method == 4:
             seed1, seed2 = _draw_seed(), _draw_seed()
             _draw_seed()                       # the reference draws three seeds for its three lattice kernels
+        elif method == 5:
+            seed1, seed2 = int(torch.randint(0, 2 ** 62, (1,)).item()), 0      # as cuda_funcs.ComputePCAFrame
         else:
             seed1 = seed2 = 0
         desc = _lib.LayerDesc(D, F, method, meta["lb"], meta["beta"], meta["scale_real"], meta["dist_max"], meta["cutoff"],
@@ -198,7 +200,7 @@ class FusedEncoderLayerFunc(torch.autograd.Function):
         out = torch.empty_like(x)
         nbytes = int(_lib.lib().cfb200_encoder_layer_workspace_bytes(N, E, D, F, method))
         ws = geo.workspace(nbytes, dev)
-        _lib.invoke("cfb200_encoder_layer_fwd", 8 + (method in (1, 3, 4)) + 2 * (method == 2), dev, ctypes.byref(desc),
+        _lib.invoke("cfb200_encoder_layer_fwd", 8 + (method in (1, 3, 4, 5)) + 2 * (method == 2), dev, ctypes.byref(desc),
                     ctypes.byref(W), ctypes.byref(geo.c), x.data_ptr(), ctypes.byref(St), out.data_ptr(), ws.data_ptr(),
                     ws.numel())
         if FRAME_TAP is not None and method != 0:

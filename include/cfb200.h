@@ -123,6 +123,15 @@ int cfb200_max_frame(int axis, const float* q_scaled, const float* k, const floa
  * arg-max and the second axis' score is (d^2 - d^2_min) + log(max(1 - |cos|, 1e-5)) without the Gaussian
  * coefficient.  cfb200_max_frames_static: both axes and the Gram-Schmidt completion in one launch (pair_cache
  * optional, as in cfb200_max_frames_cached). */
+/* The "pca" frame method: replaces ComputePCAFrame (models/cuda_funcs/calc_pca_frame.py:22-76).  Per atom the
+ * eigenvectors, by ascending eigenvalue, of the scatter matrix of its pair separations in the home cell (pos_ij
+ * about their mean; no lattice translations); per (atom, head) a drawn sign per axis, then all three axes times the
+ * determinant of the signed triple.  The signs come from a hash of (seed, atom, head, axis) where the reference uses
+ * torch.randint, and an eigenvector's own sign is fixed by "largest component positive" where the reference has
+ * LAPACK's: the axes agree with the reference's up to sign. */
+int cfb200_pca_frames(const float* pos_ij, const int64_t* e_start, int64_t N, int64_t E, uint64_t seed,
+                      float* frame1, float* frame2, float* frame3, void* stream);
+
 int cfb200_max_frame_static(int axis, const float* a_ik, const float* pos_ij, const float* tvecs,
                             const float* rvlen, const int64_t* batch, const int64_t* edges,
                             const int64_t* e_start, int64_t N, int64_t E, float cutoff_radius, uint64_t seed,
@@ -451,8 +460,9 @@ typedef struct cfb200_layer_state {
 } cfb200_layer_state;
 
 /* frame_method: 0 = none (plain Crystalformer encoding), 1 = max frames, 2 = weighted-PCA frames, 3 = static max
- * frames, 4 = lattice frames.  seed1, seed2: noise seeds of the two max-frame axes (lattice frames: of the first two
- * searches, the third uses seed1 ^ seed2), or noise seed and sign seed of the weighted-PCA frames. */
+ * frames, 4 = lattice frames, 5 = pca frames.  seed1, seed2: noise seeds of the two max-frame axes (lattice frames:
+ * of the first two searches, the third uses seed1 ^ seed2), noise seed and sign seed of the weighted-PCA frames, or
+ * (seed1) the sign seed of the pca frames. */
 typedef struct cfb200_layer_desc {
     int32_t d_model, ff_dim, frame_method;
     float gauss_lb, beta, scale_real, dist_max, cutoff_radius;

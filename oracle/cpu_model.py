@@ -62,6 +62,8 @@ def draw_frame_seeds(frame_method):
         draw()
         seed_noise = draw()
         return seed_noise, int(torch.randint(0, 2 ** 62, (1,)).item())
+    if frame_method == "pca":          # no numpy draw (the reference's Function takes none); one torch draw for the signs
+        return int(torch.randint(0, 2 ** 62, (1,)).item()), 0
     return draw(), draw()
 
 
@@ -97,6 +99,11 @@ def attention_layer(attn, x, geo, cfg, frames=None):
         else:
             f1, f2, f3 = (torch.from_numpy(x) for x in O.lattice_frames(cfg, npy(a), npy(geo["tvecs"]), npy(geo["rvlen"]),
                                                                         npy(geo["batch"]), npy(geo["edges"]), npy(e_start)))
+    elif method == "pca":
+        seed, _ = draw_frame_seeds(method)
+        e_start = OF._e_start(geo["edges"], N)
+        fr, _, _ = O.pca_frames(geo["pos_ij"].detach().numpy(), e_start.numpy(), H, seed)
+        f1, f2, f3 = (torch.from_numpy(fr[x]) for x in range(3))
     elif method == "weighted_pca":
         seed_noise, seed_sign = draw_frame_seeds(method)
         npy = lambda t: t.detach().contiguous().numpy()

@@ -366,6 +366,35 @@ def hash_uniform(seed, tid, draw):
     return np.float32(((x >> 40) + 1)) * np.float32(1.0 / 16777216.0)
 
 
+def pca_frames(pos_ij, e_start, H, seed=0):
+    """The "pca" frame method (models/cuda_funcs/calc_pca_frame.py:22-76 of the reference): per atom the scatter
+    matrix of its pair separations in the home cell about their mean, sum_j (r_ij - mean)(r_ij - mean)^T, and its
+    eigenvectors by ascending eigenvalue as the three axes (columns of the eigenvector matrix, :47-60), the same for
+    every head; per (atom, head) a sign per axis and all three axes times the determinant of the signed triple
+    (:52-66).  The reference draws the signs with torch.randint and inherits LAPACK's eigenvector signs; here, as in
+    the library, an eigenvector's largest component is positive before a hash-drawn sign.  Returns frames (3,N,H,3)
+    float32, the scatter matrices (N,3,3) and their eigenvalues (N,3) in float64."""
+    pos_ij = np.asarray(pos_ij, np.float64)
+    N = len(e_start) - 1
+    frames = np.zeros((3, N, H, 3), np.float32)
+    mats, evals = np.zeros((N, 3, 3)), np.zeros((N, 3))
+    for i in range(N):
+        r = pos_ij[int(e_start[i]):int(e_start[i + 1])]
+        d = r - r.mean(0, keepdims=True) if len(r) else r
+        M = d.T @ d
+        w, V = np.linalg.eigh(M)
+        for c in range(3):
+            if V[int(np.argmax(np.abs(V[:, c]))), c] < 0:
+                V[:, c] = -V[:, c]
+        mats[i], evals[i] = M, w
+        for h in range(H):
+            F = np.stack([V[:, c] * (1.0 if hash_uniform(seed, i * H + h, c) > 0.5 else -1.0) for c in range(3)])
+            F = F * np.linalg.det(F.T)
+            for c in range(3):
+                frames[c, i, h] = F[c]
+    return frames, mats, evals
+
+
 def weighted_pca_frames(cfg, q_scaled, k, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, seed_noise=0,
                         seed_sign=0):
     """Per (atom, head): attention-pooled second-moment matrix (softmax over the atom's pairs of

@@ -33,6 +33,7 @@ FUNCTIONS = {
     "calc_maximum_frame.py": ["ComputeFrame1MaximumMethodCUDA", "ComputeFrame2MaximumMethodCUDA"],
     "calc_maximum_static_frame.py": ["ComputeFrame1MaximumStaticMethodCUDA", "ComputeFrame2MaximumStaticMethodCUDA"],
     "calc_lattice_frame.py": ["ComputeLatticeFrameCUDA"],
+    "calc_pca_frame.py": ["ComputePCAFrame"],
     "fused_dpa.py": ["FusedDotProductAttentionCUDA"],
     "fused_dpa_sigmamat.py": ["FusedDotProductAttentionSigmaMatCUDA"],
     "irregular_mean.py": ["IrregularMeanCUDA"],

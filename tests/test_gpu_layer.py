@@ -88,7 +88,7 @@ def test_batch_geometry_against_oracle():
 
 @pytest.mark.parametrize("frame_method,workload,nc", [("max", "cfg2", 16), ("max", "cfg1", None), ("no", "cfg2", 16),
                                                       ("weighted_pca", "cfg1", None), ("max_static", "cfg1", None),
-                                                      ("lattice", "cfg2", 16)])
+                                                      ("lattice", "cfg2", 16), ("pca", "cfg2", 16)])
 def test_one_call_layer_matches_operator_path(frame_method, workload, nc):
     """Same model, same batch: operator by operator (reference-signature Functions, torch linear layers, autograd)
     against one library call per layer with hand-written backward."""

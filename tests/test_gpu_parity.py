@@ -311,7 +311,7 @@ def test_mean_pool():
 
 @pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("layers,frame_method", [(1, "max"), (4, "max"), (2, "no"), (2, "weighted_pca"), (2, "max_static"),
-                                                 (2, "lattice")])
+                                                 (2, "lattice"), (2, "pca")])
 def test_whole_model_against_cpu_oracle(layers, frame_method, fused):
     """Forward and backward of the whole model (species embedding, encoder layers, mean pooling,
     MLP head) on the GPU against the same weights run on the host cores through the oracle:
@@ -320,7 +320,7 @@ def test_whole_model_against_cpu_oracle(layers, frame_method, fused):
     ``fused=False``: the first training forward, which measures the coefficient statistics and runs
     operator by operator.  ``fused=True``: the statistics are in place, so every layer runs as the
     one-node fused layer -- the path the benchmark times; the test checks that it was taken.
-    Weighted-PCA frames are compared in their own tests (eigenvectors are not comparable where
+    Weighted-PCA and pca frames are compared in their own tests (eigenvectors are not comparable where
     eigenvalues nearly coincide); here the CPU model receives the frames the GPU constructed, so
     everything downstream of the frames is compared."""
     dev = _cuda()
@@ -358,7 +358,7 @@ def test_whole_model_against_cpu_oracle(layers, frame_method, fused):
     n_fused = sum(1 for c in calls if c in fused_layer.FUSED_FORWARD_CALLS)
     assert n_fused == (layers if fused else 0), (n_fused, sorted(set(calls)))
     frames = None
-    if frame_method == "weighted_pca":
+    if frame_method in ("weighted_pca", "pca"):
         assert len(tap) == layers
         frames = [f.cpu() for f in tap]
     out_c = cpu_model.forward(cpu, b, backend="port", frames=frames)
@@ -389,6 +389,44 @@ def test_whole_model_against_cpu_oracle(layers, frame_method, fused):
             assert bad.sum() <= 2 and np.abs(g - c).max() <= 5e-2 * scale, f"{n}: {bad.sum()} entries differ"
         else:
             assert not bad.any(), f"{n}: max abs diff {np.abs(g - c).max():.3e} at scale {scale:.3e}"
+
+
+def test_pca_frames():
+    """cfb200_pca_frames through the drop-in Function against the oracle: the axes are the eigenvectors of the
+    scatter matrix of each atom's pair separations (ascending eigenvalue), identical for all heads up to the drawn
+    signs, orthonormal and right-handed; where the eigenvalues are well separated the axes equal the oracle's, signs
+    included."""
+    dev = _cuda()
+    from oracle import oracle as O
+    F = _configure()
+    P = make_problem("cfg2", num_crystals=24)
+    g = _geometry(P, dev)
+    N, H = P["a"].shape
+    qs = _t((P["q"] / 4.0).astype(np.float32), dev)
+    torch.manual_seed(7)
+    f1, f2, f3 = F.ComputePCAFrame.apply(qs, _t(P["k"], dev), None, _t(P["a"], dev), g["pos_ij"], None, g["tvecs"], g["batch"],
+                                         g["edges"], 64, 14.0, 1.0, g["rvlen"], -3.5)
+    torch.manual_seed(7)
+    seed = int(torch.randint(0, 2 ** 62, (1,)).item())
+    want, mats, evals = O.pca_frames(P["geo"]["pos_ij"], P["geo"]["e_start"], H, seed)
+    got = np.stack([f1.cpu().numpy(), f2.cpu().numpy(), f3.cpu().numpy()])          # (3,N,H,3)
+    Fm = np.moveaxis(got, 0, 2).astype(np.float64)                                     # (N,H,axis,component)
+    gram = Fm @ np.swapaxes(Fm, -1, -2)
+    assert np.abs(gram - np.eye(3)).max() < 1e-4 and np.abs(np.linalg.det(Fm) - 1.0).max() < 1e-4
+    scale = np.maximum(evals[:, 2], 1e-12)
+    gaps = np.minimum(evals[:, 1] - evals[:, 0], evals[:, 2] - evals[:, 1]) / scale
+    clear = gaps > 1e-2                                                                # atoms with three distinct axes
+    assert clear.sum() > N // 2
+    for r in range(3):                                                                  # eigenvector equation
+        v = Fm[:, 0, r, :]
+        resid = np.einsum("nij,nj->ni", mats, v) - evals[:, r, None] * v
+        assert (np.abs(resid).max(1)[clear] <= 2e-4 * scale[clear]).all()
+    dots = np.abs((got.astype(np.float64) * want.astype(np.float64)).sum(-1))            # (3,N,H)
+    assert (dots[:, clear] > 1.0 - 1e-4).all()
+    same = np.abs(got - want).max(axis=(0, 3)) < 1e-3                                   # (N,H): signs included
+    assert same[clear].mean() > 0.9
+    from crystalframer_b200 import _lib
+    assert _lib.read_status(dev) == 0
 
 
 @pytest.mark.parametrize("saved", [False, True])

@@ -345,3 +345,26 @@ def test_static_and_lattice_frames_against_reference_kernels():
         want = O.lattice_frames(cfg, P["a"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"], geo["e_start"])
         for x in range(3):
             assert np.array_equal(got[x].numpy(), want[x]), (workload, x)
+
+
+def test_pca_frames_are_principal_axes():
+    """oracle.pca_frames (models/cuda_funcs/calc_pca_frame.py:22-76): eigenvectors of the scatter matrix of each
+    atom's pair separations, ascending eigenvalue, orthonormal, right-handed, heads differing by signs only."""
+    from crystalframer_b200 import synth
+    b = synth.make_workload("cfg1")
+    g = O.lattice_geometry(b.pos, b.trans_vec, b.sizes)
+    fr, mats, evals = O.pca_frames(g["pos_ij"], g["e_start"], 4, seed=3)
+    N = b.num_atoms
+    assert fr.shape == (3, N, 4, 3) and (np.diff(evals, axis=1) >= -1e-9).all()
+    Fm = np.moveaxis(fr, 0, 2).astype(np.float64)
+    assert np.abs(Fm @ np.swapaxes(Fm, -1, -2) - np.eye(3)).max() < 1e-5
+    assert np.abs(np.linalg.det(Fm) - 1.0).max() < 1e-5
+    for r in range(3):
+        v = Fm[:, 0, r, :]
+        assert np.abs(np.einsum("nij,nj->ni", mats, v) - evals[:, r, None] * v).max() < 1e-4 * max(1.0, evals.max())
+        assert np.abs(np.abs((Fm[:, :1, r] * Fm[:, :, r]).sum(-1)) - 1.0).max() < 1e-5      # heads: same axis up to sign
+    # by hand for one atom: scatter matrix about the mean of its separations
+    e0, e1 = int(g["e_start"][5]), int(g["e_start"][6])
+    r5 = g["pos_ij"][e0:e1].astype(np.float64)
+    d = r5 - r5.mean(0)
+    assert np.allclose(mats[5], d.T @ d)
