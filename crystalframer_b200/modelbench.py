@@ -1,6 +1,6 @@
 """Model-level timing of one training step for any workload and frame method.
 
-    python -m crystalframer_b200.modelbench [--workload cfg4] [--frame-method max|max_static|lattice|weighted_pca|no]
+    python -m crystalframer_b200.modelbench [--workload cfg4] [--frame-method max|max_static|lattice|pca|weighted_pca|no]
                                             [--layers 4] [--steps 5] [--crystals N]
 
 ``bench.py`` at the repository root times the benchmark configuration (cfg3, max frames); this tool
@@ -21,7 +21,7 @@ from .latticeformer import Latticeformer, ModelParams
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="cfg4")
-    ap.add_argument("--frame-method", default="weighted_pca", choices=["max", "max_static", "lattice", "weighted_pca", "no"])
+    ap.add_argument("--frame-method", default="weighted_pca", choices=["max", "max_static", "lattice", "pca", "weighted_pca", "no"])
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
