@@ -561,9 +561,7 @@ __global__ void __launch_bounds__(at_warps(true) * 32, kAtBwdBlocks) attn_bwd_ke
 
 static int at_grid_x(int64_t N, int H, bool bwd)
 {
-    int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int sms = sm_count();
     int64_t want = ((int64_t)sms * (bwd ? kAtBwdBlocks : kAtFwdBlocks)) / H;
     if (want < 1) want = 1;
     const int64_t need = (N + at_warps(bwd) - 1) / at_warps(bwd);

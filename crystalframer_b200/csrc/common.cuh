@@ -34,6 +34,20 @@ struct Params {
     float a_interval, a_step, a_sigma_inv, a_cut;   // a_cut = cut_sigma * angle_sigma
 };
 
+// Multiprocessors of the current device (asked once per device and host thread: the query costs as much as a launch).
+inline int sm_count()
+{
+    thread_local int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int sms = 148;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+        cached[dev] = sms;
+    }
+    return cached[dev];
+}
+
 // Device status word (bits CFB200_ST_*).  The library is built as one translation unit.
 __device__ int g_status = 0;
 

@@ -322,9 +322,7 @@ __global__ void reduce_gw_kernel(const float* __restrict__ part, int nPart, int 
 
 static int grid_x_for(int64_t E, int H, bool bwd)
 {
-    int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int sms = sm_count();
     const int64_t chunks = (E + fp_slots(bwd) - 1) / fp_slots(bwd);
     int64_t want = ((int64_t)sms * fp_blocks_per_sm(bwd)) / H;
     if (want < 1) want = 1;

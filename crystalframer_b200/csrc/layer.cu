@@ -253,6 +253,32 @@ struct Carver {
 
 inline int64_t pad256(int64_t b) { return (b + 255) & ~(int64_t)255; }
 
+// A second stream per host thread and device, on which the layer backward runs the weight gradients that are ready
+// early beside the attention backward (fork and join by events, so the caller's stream sees one ordered call).
+// Created on first use; CFB200_SIDE_STREAM=0 keeps everything on the caller's stream.
+struct SideLane { cudaStream_t stream = nullptr; cudaEvent_t fork = nullptr, join = nullptr; bool failed = false; };
+thread_local SideLane g_side[64];
+
+SideLane* side_lane()
+{
+    static const bool enabled = [] { const char* e = getenv("CFB200_SIDE_STREAM"); return !(e && e[0] == '0'); }();
+    if (!enabled) return nullptr;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    SideLane& L = g_side[dev];
+    if (L.failed) return nullptr;
+    if (L.stream == nullptr) {
+        if (cudaStreamCreateWithFlags(&L.stream, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&L.fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&L.join, cudaEventDisableTiming) != cudaSuccess) {
+            L.failed = true;
+            L.stream = nullptr;
+            return nullptr;
+        }
+    }
+    return &L;
+}
+
 // outputs of all weight / bias gradients of one layer (floats), for the partial-sum scratch
 int64_t layer_grad_outputs(int D, int F, int H, bool angles)
 {
@@ -548,6 +574,41 @@ int cfb200_encoder_layer_bwd(const cfb200_layer_desc* L, const cfb200_layer_weig
     g.seg[0] = {gx1, W->out_proj, D, D, D}; g.nseg = 1; g.M = (int)N; g.N = D; g.C = go; g.ldc = D;
     if ((rc = cfb::gemm(g, true, st)) != CFB200_OK) return rc;
     }
+    // Weight and bias gradients whose inputs exist by now (feed-forward, output projection, value-encoding weights:
+    // out[P,Q] = A^T B over the atoms) run on the side stream beside the attention backward below.
+    const int64_t early_out = ((int64_t)D * F + D + 3) + ((int64_t)F * D + F + 3) + ((int64_t)D * D + D + 3) +
+                              (ang ? 4 : 1) * ((int64_t)H * 16 * 64 + 3);
+    const int64_t early_floats = (cfb::wgrad_workspace_floats(N, early_out) + 3) & ~(int64_t)3;
+    SideLane* lane = side_lane();
+    {
+        cudaStream_t sw = st;
+        if (lane != nullptr) {
+            if (cudaEventRecord(lane->fork, st) != cudaSuccess || cudaStreamWaitEvent(lane->stream, lane->fork, 0) != cudaSuccess)
+                return CFB200_E_CUDA;
+            sw = lane->stream;
+        }
+        TmScope tm_w(CFB200_TM_WGRAD, sw);
+        cfb::WgArgs Wg;
+        memset(&Wg, 0, sizeof(Wg));
+        Wg.M = (int)N; Wg.ws = wg; Wg.accumulate = accumulate;
+        auto add = [&](const float* A, int lda, int Pn, const float* B, int ldb, int Qn, float* out, int ldo, float* bias) {
+            cfb::WgProblem& p = Wg.prob[Wg.nprob++];
+            p.A = A; p.B = B; p.out = out; p.bias_out = bias; p.lda = lda; p.ldb = ldb; p.ldo = ldo; p.P = Pn; p.Q = Qn; p.nb = 1;
+        };
+        add(g_out, D, D, St->h, F, F, Gr->ff2, F, Gr->ff2_bias);
+        add(gh, F, F, St->x1, D, D, Gr->ff1, D, Gr->ff1_bias);
+        add(gx1, D, D, St->attn, D, D, Gr->out_proj, D, Gr->out_bias);
+        // value-encoding weights: gW_b[h] (16 x 64) = sum_i go[i,h,:]^T spool[i,h,64b:64b+64]
+        float* gpe[4] = {Gr->pe_dist, Gr->pe_ang1, Gr->pe_ang2, Gr->pe_ang3};
+        for (int b = 0; b < (ang ? 4 : 1); b++) {
+            cfb::WgProblem& p = Wg.prob[Wg.nprob++];
+            p.A = go; p.lda = D; p.P = 16; p.sA = 16;
+            p.B = St->spool + 64 * b; p.ldb = H * 256; p.Q = 64; p.sB = 256;
+            p.out = gpe[b]; p.ldo = 64; p.sO = 16 * 64; p.nb = H; p.bias_out = nullptr;
+        }
+        if ((rc = cfb::wgrad(Wg, early_floats, sw)) != CFB200_OK) return rc;
+        if (lane != nullptr && cudaEventRecord(lane->join, sw) != cudaSuccess) return CFB200_E_CUDA;
+    }
     // attention, lattice sums
     {
         cfb::AtArgs A;
@@ -582,30 +643,23 @@ int cfb200_encoder_layer_bwd(const cfb200_layer_desc* L, const cfb200_layer_weig
         g.nseg = 3; g.M = (int)N; g.N = D; g.C = g_x; g.ldc = D; g.resid = gx1; g.ldr = D;
         if ((rc = cfb::gemm(g, true, st)) != CFB200_OK) return rc;
     }
-    TmScope tm_w(CFB200_TM_WGRAD, st);
-    // weight and bias gradients of the whole layer: out[P,Q] = A^T B over the atoms
-    cfb::WgArgs Wg;
-    memset(&Wg, 0, sizeof(Wg));
-    Wg.M = (int)N; Wg.ws = wg; Wg.accumulate = accumulate;
-    auto add = [&](const float* A, int lda, int Pn, const float* B, int ldb, int Qn, float* out, int ldo, float* bias) {
-        cfb::WgProblem& p = Wg.prob[Wg.nprob++];
-        p.A = A; p.B = B; p.out = out; p.bias_out = bias; p.lda = lda; p.ldb = ldb; p.ldo = ldo; p.P = Pn; p.Q = Qn; p.nb = 1;
-    };
-    add(g_out, D, D, St->h, F, F, Gr->ff2, F, Gr->ff2_bias);
-    add(gh, F, F, St->x1, D, D, Gr->ff1, D, Gr->ff1_bias);
-    add(gx1, D, D, St->attn, D, D, Gr->out_proj, D, Gr->out_bias);
-    add(gq, D, D, x, D, D, Gr->q_proj, D, Gr->in_bias);
-    add(gk, D, D, x, D, D, Gr->k_proj, D, Gr->in_bias + D);
-    add(gv, D, D, x, D, D, Gr->v_proj, D, Gr->in_bias + 2 * D);
-    // value-encoding weights: gW_b[h] (16 x 64) = sum_i go[i,h,:]^T spool[i,h,64b:64b+64]
-    float* gpe[4] = {Gr->pe_dist, Gr->pe_ang1, Gr->pe_ang2, Gr->pe_ang3};
-    for (int b = 0; b < (ang ? 4 : 1); b++) {
-        cfb::WgProblem& p = Wg.prob[Wg.nprob++];
-        p.A = go; p.lda = D; p.P = 16; p.sA = 16;
-        p.B = St->spool + 64 * b; p.ldb = H * 256; p.Q = 64; p.sB = 256;
-        p.out = gpe[b]; p.ldo = 64; p.sO = 16 * 64; p.nb = H; p.bias_out = nullptr;
+    // weight and bias gradients of the in-projections (their inputs are the last results of the chain above)
+    {
+        TmScope tm_w(CFB200_TM_WGRAD, st);
+        cfb::WgArgs Wg;
+        memset(&Wg, 0, sizeof(Wg));
+        Wg.M = (int)N; Wg.ws = wg + early_floats; Wg.accumulate = accumulate;
+        auto add = [&](const float* A, int lda, int Pn, const float* B, int ldb, int Qn, float* out, int ldo, float* bias) {
+            cfb::WgProblem& p = Wg.prob[Wg.nprob++];
+            p.A = A; p.B = B; p.out = out; p.bias_out = bias; p.lda = lda; p.ldb = ldb; p.ldo = ldo; p.P = Pn; p.Q = Qn; p.nb = 1;
+        };
+        add(gq, D, D, x, D, D, Gr->q_proj, D, Gr->in_bias);
+        add(gk, D, D, x, D, D, Gr->k_proj, D, Gr->in_bias + D);
+        add(gv, D, D, x, D, D, Gr->v_proj, D, Gr->in_bias + 2 * D);
+        if ((rc = cfb::wgrad(Wg, wg_floats - early_floats, st)) != CFB200_OK) return rc;
     }
-    if ((rc = cfb::wgrad(Wg, wg_floats, st)) != CFB200_OK) return rc;
+    // the early weight gradients must be complete when this call's work is (the next call reuses the workspace)
+    if (lane != nullptr && cudaStreamWaitEvent(st, lane->join, 0) != cudaSuccess) return CFB200_E_CUDA;
     if (accumulate) {
         cfb::axpy_kernel<<<(D + 127) / 128, 128, 0, st>>>(Gr->lattice_pos, gw_tmp, D);
         if (cudaGetLastError() != cudaSuccess) return CFB200_E_CUDA;

@@ -42,14 +42,23 @@ PAIR_LIST_BYTES_PER_PAIR = 5 * 128 * 4   # five planes of 128 floats: 2.5 KB of 
 PAIR_LIST_MAX_PAIRS = 4_000_000          # hard cap (10 GB); below it the list also has to fit a quarter of the free memory
 
 
+_FREE_MEMORY = {}          # device -> (free bytes at the last query, requests it may still serve)
+
+
 def pair_list_fits(num_pairs, device):
     """Whether the per-pair translation lists of a batch may be built: the batch's lists (2.5 KB per pair, e.g. 133 MB
     for 52 k pairs, 3.6 GB for the 1.4 M pairs of a large-cell batch) must stay under a quarter of the device memory
     that is free right now and under the hard cap; otherwise the kernels sweep the translations instead."""
     if num_pairs > PAIR_LIST_MAX_PAIRS:
         return False
-    free, _ = torch.cuda.mem_get_info(device)
-    return num_pairs * PAIR_LIST_BYTES_PER_PAIR <= free // 4
+    need = num_pairs * PAIR_LIST_BYTES_PER_PAIR
+    # the driver query costs as much as several kernel launches: a recent answer serves requests far below it
+    key = (device.type, device.index)
+    free, uses = _FREE_MEMORY.get(key, (0, 0))
+    if uses <= 0 or need > free // 32:
+        free, uses = torch.cuda.mem_get_info(device)[0], 64
+    _FREE_MEMORY[key] = (free, uses - 1)
+    return need <= free // 4
 
 
 def pair_geometry(rpos_ij_e, tvecs_n, batch_i, edge_ij_e, cutoff):
