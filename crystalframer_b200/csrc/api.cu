@@ -133,7 +133,9 @@ int cfb200_configure(const cfb200_config* cfg)
 {
     if (cfg == nullptr) return CFB200_E_NULL;
     const cfb200_config& c = *cfg;
-    if (c.head_dim != 16 || c.dist_dim != 64 || !(c.angle_dim == 0 || c.angle_dim == 64)) return CFB200_E_UNSUPPORTED;
+    // kernel instances: head dimension 16, 64 distance Gaussians, up to 64 angle Gaussians per axis in fours
+    if (c.head_dim != 16 || c.dist_dim != 64 || c.angle_dim < 0 || c.angle_dim > 64 || (c.angle_dim & 3))
+        return CFB200_E_UNSUPPORTED;
     if (c.num_heads < 1 || c.num_heads > 32 || (32 % c.num_heads) != 0) return CFB200_E_UNSUPPORTED;
     if (c.lattice_range < 0 || c.lattice_range > CFB200_MAX_RANGE || c.minimum_range < 0 ||
         c.minimum_range > CFB200_MAX_RANGE) return CFB200_E_UNSUPPORTED;

@@ -134,7 +134,8 @@ __global__ void __launch_bounds__(at_warps(false) * 32, kAtFwdBlocks) attn_fwd_k
     for (int idx = threadIdx.x; idx < kAtHd * kAtK / 4; idx += at_warps(false) * 32) {
         const int o = idx >> 6, k4 = idx & 63, b = k4 >> 4, d4 = k4 & 15;
         float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (A.W[b] != nullptr) w = __ldg(reinterpret_cast<const float4*>(A.W[b] + ((size_t)h * kAtHd + o) * 64) + d4);
+        const int width = b == 0 ? 64 : P.angle_dim;          // columns this basis' weights hold (zero beyond)
+        if (A.W[b] != nullptr && 4 * d4 < width) w = __ldg(reinterpret_cast<const float4*>(A.W[b] + ((size_t)h * kAtHd + o) * width) + d4);
         reinterpret_cast<float4*>(W_s)[o * (kAtWfStride / 4) + k4] = w;
     }
     LatticeLane<0, ANG> L;
@@ -270,7 +271,8 @@ __global__ void __launch_bounds__(kAtTrainWarps * 32, 2) attn_fwd_train_kernel(c
     for (int idx = threadIdx.x; idx < kAtHd * kAtK / 4; idx += kAtTrainWarps * 32) {
         const int o = idx >> 6, k4 = idx & 63, b = k4 >> 4, d4 = k4 & 15;
         float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (A.W[b] != nullptr) w = __ldg(reinterpret_cast<const float4*>(A.W[b] + ((size_t)h * kAtHd + o) * 64) + d4);
+        const int width = b == 0 ? 64 : P.angle_dim;          // columns this basis' weights hold (zero beyond)
+        if (A.W[b] != nullptr && 4 * d4 < width) w = __ldg(reinterpret_cast<const float4*>(A.W[b] + ((size_t)h * kAtHd + o) * width) + d4);
         reinterpret_cast<float4*>(W_s)[o * (kAtWfStride / 4) + k4] = w;
     }
     LatticeLane<2, ANG> L;
@@ -450,7 +452,8 @@ __global__ void __launch_bounds__(at_warps(true) * 32, kAtBwdBlocks) attn_bwd_ke
     for (int idx = threadIdx.x; idx < kAtHd * kAtK / 4; idx += at_warps(true) * 32) {
         const int o = idx >> 6, k4 = idx & 63, b = k4 >> 4, d4 = k4 & 15;
         float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (A.W[b] != nullptr) w = __ldg(reinterpret_cast<const float4*>(A.W[b] + ((size_t)h * kAtHd + o) * 64) + d4);
+        const int width = b == 0 ? 64 : P.angle_dim;          // columns this basis' weights hold (zero beyond)
+        if (A.W[b] != nullptr && 4 * d4 < width) w = __ldg(reinterpret_cast<const float4*>(A.W[b] + ((size_t)h * kAtHd + o) * width) + d4);
         const int k = k4 * 4;
         W_s[(k + 0) * kAtWtStride + o] = w.x; W_s[(k + 1) * kAtWtStride + o] = w.y;
         W_s[(k + 2) * kAtWtStride + o] = w.z; W_s[(k + 3) * kAtWtStride + o] = w.w;

@@ -44,7 +44,7 @@ struct FpArgs {
     const float* a_ik; const float* pos_ij; const float* tvecs; const float* rvlen;
     const int64_t* batch; const int64_t* edges;
     int64_t N, E;
-    const float* W[4];        // distance, axis 1..3; each (H,16,64)
+    const float* W[4];        // distance (H,16,64), axis 1..3 (H,16,angle_dim)
     const float* frame[3];    // each (N,H,3)
     float* z; float* values;                     // forward outputs
     const float* z_in; const float* gz; const float* gv;   // backward inputs
@@ -92,8 +92,9 @@ __global__ void __launch_bounds__(kFpThreads, fp_blocks_per_sm(BWD)) framed_proj
     for (int idx = threadIdx.x; idx < kHd * kFpK / 4; idx += kFpThreads) {
         const int o = idx >> 6, k4 = idx & 63, b = k4 >> 4, d4 = k4 & 15;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (A.W[b] != nullptr)
-            v = __ldg(reinterpret_cast<const float4*>(A.W[b] + ((size_t)h * kHd + o) * 64) + d4);
+        const int width = b == 0 ? 64 : P.angle_dim;          // columns this basis' weights hold (zero beyond)
+        if (A.W[b] != nullptr && 4 * d4 < width)
+            v = __ldg(reinterpret_cast<const float4*>(A.W[b] + ((size_t)h * kHd + o) * width) + d4);
         if (!BWD) {
             reinterpret_cast<float4*>(W_s)[o * (kWfStride / 4) + k4] = v;
         } else {
@@ -305,7 +306,7 @@ __global__ void reduce_ga_kernel(const float* __restrict__ ga_e, const int64_t* 
 }
 
 // weight gradients: ordered sum over the per-block partials, split into the four tensors
-__global__ void reduce_gw_kernel(const float* __restrict__ part, int nPart, int H, float* gWd, float* gW1,
+__global__ void reduce_gw_kernel(const float* __restrict__ part, int nPart, int H, int angle_dim, float* gWd, float* gW1,
                                  float* gW2, float* gW3)
 {
     const int tid = blockIdx.x * blockDim.x + threadIdx.x;   // (h, o, k)
@@ -314,7 +315,8 @@ __global__ void reduce_gw_kernel(const float* __restrict__ part, int nPart, int 
     for (int x = 0; x < nPart; x++) s += part[(size_t)x * H * kHd * kFpK + tid];
     const int k = tid & (kFpK - 1), ho = tid >> 8, b = k >> 6, dim = k & 63;
     float* dst = b == 0 ? gWd : (b == 1 ? gW1 : (b == 2 ? gW2 : gW3));
-    if (dst != nullptr) dst[ho * 64 + dim] = s;
+    const int width = b == 0 ? 64 : angle_dim;                 // the angle weights are (H,16,angle_dim)
+    if (dst != nullptr && dim < width) dst[ho * width + dim] = s;
 }
 
 // Resident blocks along x: the kernel is persistent (each block strides over the chunks), so the
@@ -381,7 +383,7 @@ int framed_proj_bwd(FpArgs A, const Params& P, const int64_t* e_start, float* ga
         reduce_ga_kernel<<<(unsigned)((nt + 255) / 256), 256, 0, st>>>(A.ga_e, e_start, A.N, P.H, ga);
     }
     const int nw = P.H * kHd * kFpK;
-    reduce_gw_kernel<<<(nw + 255) / 256, 256, 0, st>>>(A.gW_part, nPart, P.H, gW[0], gW[1], gW[2], gW[3]);
+    reduce_gw_kernel<<<(nw + 255) / 256, 256, 0, st>>>(A.gW_part, nPart, P.H, P.angle_dim, gW[0], gW[1], gW[2], gW[3]);
     return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
 }
 

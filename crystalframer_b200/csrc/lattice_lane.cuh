@@ -42,7 +42,8 @@ struct LatticeLane {
         lane = lane_;
         const float dstep = P.d_step * kLlSqrtLog2e, astep = P.a_step * kLlSqrtLog2e;
         cd_lo = (float)(lane + 1) * dstep; cd_hi = (float)(lane + 33) * dstep;
-        ca_lo = (float)(63 - lane) * astep; ca_hi = (float)(31 - lane) * astep;
+        // angle Gaussian k sits at (angle_dim - 1 - k) steps; this lane owns k = lane and k = lane + 32
+        ca_lo = (float)(P.angle_dim - 1 - lane) * astep; ca_hi = (float)(P.angle_dim - 33 - lane) * astep;
         win_d = (unsigned)P.win_dist; win_a = (unsigned)P.win_ang;
         inv_d_interval = 1.0f / P.d_interval; d_cut_scaled = P.d_cut / P.d_interval;
         xd_scale = dstep / P.d_interval;
@@ -99,7 +100,7 @@ struct LatticeLane {
                     int lo = 0;
                     if (P.windowed_ang) {
                         const float en = fmaf(cosv + 1.0f + P.a_cut, inv_a_interval, 1.0f);
-                        int end = (int)fminf(en, 64.0f);
+                        int end = (int)fminf(en, (float)P.angle_dim);
                         end = max(end, P.win_ang);
                         lo = end - P.win_ang;
                     }

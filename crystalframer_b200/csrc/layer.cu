@@ -603,8 +603,9 @@ int cfb200_encoder_layer_bwd(const cfb200_layer_desc* L, const cfb200_layer_weig
         for (int b = 0; b < (ang ? 4 : 1); b++) {
             cfb::WgProblem& p = Wg.prob[Wg.nprob++];
             p.A = go; p.lda = D; p.P = 16; p.sA = 16;
-            p.B = St->spool + 64 * b; p.ldb = H * 256; p.Q = 64; p.sB = 256;
-            p.out = gpe[b]; p.ldo = 64; p.sO = 16 * 64; p.nb = H; p.bias_out = nullptr;
+            const int width = b == 0 ? 64 : g_cfg.angle_dim;          // the angle weights are (H,16,angle_dim)
+            p.B = St->spool + 64 * b; p.ldb = H * 256; p.Q = width; p.sB = 256;
+            p.out = gpe[b]; p.ldo = width; p.sO = 16 * width; p.nb = H; p.bias_out = nullptr;
         }
         if ((rc = cfb::wgrad(Wg, early_floats, sw)) != CFB200_OK) return rc;
         if (lane != nullptr && cudaEventRecord(lane->join, sw) != cudaSuccess) return CFB200_E_CUDA;

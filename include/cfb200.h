@@ -6,8 +6,11 @@
  * models/cuda_funcs/kernel_manager.py:14-167 and the _to_cupy helpers of each Function):
  *   - every pointer is a device pointer on the current device unless it says "host";
  *     all reals are contiguous float32, all indices contiguous int64 (as the reference);
- *   - the library allocates nothing and never synchronises: work is enqueued on `stream`
- *     (a cudaStream_t passed as void*), scratch memory is passed in by the caller;
+ *   - the library allocates no device memory and never synchronises: work is enqueued on `stream`
+ *     (a cudaStream_t passed as void*), scratch memory is passed in by the caller
+ *     (cfb200_encoder_layer_bwd creates one more stream and two events per host thread and
+ *     device on first use, for work it forks from and joins back into `stream`;
+ *     CFB200_SIDE_STREAM=0 in the environment keeps it on `stream`);
  *   - a call returns 0 on success or a negative CFB200_E_* code; kernels never trap -- a
  *     condition found on the device (non-negative Gaussian coefficient, clamped lattice
  *     range) sets a bit in a status word read with cfb200_status();

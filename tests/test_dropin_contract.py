@@ -146,3 +146,63 @@ def test_parameter_names_and_shapes_match_the_reference_module():
         for k in [k for k in sys.modules if k == "models" or k.startswith("models.")]:
             del sys.modules[k]
         sys.modules.update({k: v for k, v in saved.items() if v is not None})
+
+
+@pytest.mark.gpu
+def test_reference_module_runs_on_this_package():
+    """The reference's own attention module, unmodified, with ``models.cuda_funcs`` replaced by this package's
+    ``cuda_funcs``, against this package's mirror of it: same state_dict, same inputs, outputs and gradients
+    compared.  Needs a GPU and the reference tree on one machine (skipped where either is missing)."""
+    import importlib
+    import numpy as np
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import crystalframer_b200.cuda_funcs as ours
+    from crystalframer_b200 import synth
+    from crystalframer_b200.attention import CrystalformerMultiheadAttentionCUDA
+    from crystalframer_b200.encoder import build_pair_list, compute_lattice_distances_for_cuda
+    from crystalframer_b200.latticeformer_params import LatticeformerParams
+    dev = torch.device("cuda:0")
+    saved = {k: sys.modules.get(k) for k in list(sys.modules) if k == "models" or k.startswith("models.")}
+    for k in saved:
+        del sys.modules[k]
+    pkg = types.ModuleType("models")
+    pkg.__path__ = [os.path.join(REF, "models")]
+    sys.modules["models"] = pkg
+    sys.modules["models.cuda_funcs"] = ours
+    try:
+        mod = importlib.import_module("models.indexed_lattice_multi_head_attention_cuda")
+        ref_params = importlib.import_module("models.latticeformer_params").LatticeformerParams()
+        mine_params = LatticeformerParams()
+        for P in (ref_params, mine_params):
+            P.domain, P.frame_method = "real", "max"
+            P.value_pe_dist_real, P.value_pe_angle_real = 64, 64
+            P.symm_break_noise = 0.0
+        ours.compile_kernels(2, 8, 16, 64, 64, 16, True, 0, 1.0, 4.0, 1.0, 1.0, 0.0)
+        torch.manual_seed(0)
+        ref = mod.CrystalformerMultiheadAttentionCUDA(128, 8, params=ref_params).to(dev).train()
+        mine = CrystalformerMultiheadAttentionCUDA(128, 8, params=mine_params).to(dev).train()
+        mine.load_state_dict(ref.state_dict())
+        b = synth.make_workload("cfg1")
+        sizes = torch.from_numpy(b.sizes).to(dev)
+        pos, tv = torch.from_numpy(b.pos).to(dev), torch.from_numpy(b.trans_vec).to(dev)
+        edges, _, batch, _ = build_pair_list(sizes, (b.num_atoms, b.num_pairs))
+        pos_ij, dist2_min, tvecs, rvecs, vcell, edges = compute_lattice_distances_for_cuda(pos, batch, tv, sizes, 2)
+        x = torch.randn(b.num_atoms, 128, device=dev)
+        outs = []
+        for m in (ref, mine):
+            np.random.seed(3)
+            xin = x.clone().requires_grad_(True)
+            y, _ = m(xin, xin, xin, batch, batch, edges, pos_ij, dist2_min, tvecs, None, rvecs, vcell, None, False)
+            y.square().sum().backward()
+            outs.append((y.detach(), xin.grad, {n: p.grad for n, p in m.named_parameters() if p.grad is not None}))
+        (y0, gx0, g0), (y1, gx1, g1) = outs
+        assert torch.allclose(y0, y1, rtol=1e-5, atol=1e-6) and torch.allclose(gx0, gx1, rtol=1e-4, atol=1e-6)
+        assert set(g0) == set(g1)
+        for n in g0:
+            assert torch.allclose(g0[n], g1[n], rtol=1e-4, atol=1e-6 * float(g0[n].abs().max()) + 1e-9), n
+    finally:
+        for k in [k for k in sys.modules if k == "models" or k.startswith("models.")]:
+            del sys.modules[k]
+        sys.modules.update({k: v for k, v in saved.items() if v is not None})

@@ -181,17 +181,24 @@ def _frames(P):
     return np.stack([fr["frame1"], fr["frame2"], fr["frame3"]])
 
 
-@pytest.mark.parametrize("workload,nc,angles,wscales", [
-    ("cfg1", None, True, (1.0, 4.0)), ("cfg2", 24, True, (1.0, 4.0)), ("cfg1", None, False, (1.0, 4.0)),
-    ("cfg1", None, True, (1.5, 3.0)),          # other window widths: 13 distance, 25 angle
-    ("cfg1", None, True, (8.0, 8.0)),          # windows wider than the bases: every Gaussian is evaluated
+@pytest.mark.parametrize("workload,nc,angles,wscales,coefs", [
+    ("cfg1", None, 64, (1.0, 4.0), (1.0, 1.0)), ("cfg2", 24, 64, (1.0, 4.0), (1.0, 1.0)), ("cfg1", None, 0, (1.0, 4.0), (1.0, 1.0)),
+    ("cfg1", None, 64, (1.5, 3.0), (1.0, 1.0)),          # other window widths: 13 distance, 25 angle
+    ("cfg1", None, 64, (8.0, 8.0), (1.0, 1.0)),          # windows wider than the bases: every Gaussian is evaluated
+    # the reference's lightweight recipe (train_jarvis_time.sh:41-57): 16 angle Gaussians of width scale 1.0 (un-windowed),
+    # distance coefficient 1.5, angle coefficient 6.0
+    ("cfg1", None, 16, (1.0, 1.0), (1.5, 6.0)), ("cfg2", 24, 16, (1.0, 1.0), (1.5, 6.0)),
+    ("cfg1", None, 48, (1.0, 4.0), (1.0, 1.0)),          # 48 angle Gaussians: windowed (33 of 48), second register slot half used
 ])
-def test_framed_proj_forward_backward(workload, nc, angles, wscales):
+def test_framed_proj_forward_backward(workload, nc, angles, wscales, coefs):
     dev = _cuda()
     from oracle import oracle as O
-    F = _configure(angle_dim=64 if angles else 0, wscale_d=wscales[0], wscale_a=wscales[1])
+    F = _configure(angle_dim=angles, wscale_d=wscales[0], wscale_a=wscales[1], c_dist=coefs[0], c_ang=coefs[1])
     P = make_problem(workload, num_crystals=nc)
-    P["cfg"] = O.Config(wscale_dist=wscales[0], wscale_ang=wscales[1])
+    P["cfg"] = O.Config(wscale_dist=wscales[0], wscale_ang=wscales[1], D_ang=max(angles, 1), c_dist=coefs[0], c_ang=coefs[1])
+    if angles not in (0, 64):
+        bound = (angles ** -0.5) * np.sqrt(6.0 / (angles + 8 * 16))
+        P["W_a"] = P["rng"].uniform(-bound, bound, size=(3, 8, 16, angles)).astype(np.float32)
     g = _geometry(P, dev)
     frames = _frames(P) if angles else None
     W_a = P["W_a"] if angles else None
@@ -206,8 +213,8 @@ def test_framed_proj_forward_backward(workload, nc, angles, wscales):
     else:
         Ws, fs = [None] * 3, [None] * 3
     z, v = F.RealEncodingWithFramedProjFuncCUDA.apply(
-        a, g["pos_ij"], None, g["tvecs"], g["batch"], g["edges"], 64, 14.0, wscales[0], Wd, *Ws, *fs, 64, wscales[1], 0,
-        1.0, 1.0, g["rvlen"], -3.5)
+        a, g["pos_ij"], None, g["tvecs"], g["batch"], g["edges"], 64, 14.0, wscales[0], Wd, *Ws, *fs, angles, wscales[1], 0,
+        coefs[0], coefs[1], g["rvlen"], -3.5)
     _close("z", z.detach().cpu().numpy(), z_w)
     _close("values", v.detach().cpu().numpy(), v_w)
     rng = np.random.default_rng(7)
@@ -313,6 +320,18 @@ def test_mean_pool():
 @pytest.mark.parametrize("layers,frame_method", [(1, "max"), (4, "max"), (2, "no"), (2, "weighted_pca"), (2, "max_static"),
                                                  (2, "lattice"), (2, "pca")])
 def test_whole_model_against_cpu_oracle(layers, frame_method, fused):
+    _whole_model_check(layers, frame_method, fused)
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_whole_model_lightweight_recipe(fused):
+    """The reference's second efficiency recipe (train_jarvis_time.sh:41-57): 16 angle Gaussians of width scale 1.0,
+    distance coefficient 1.5, angle coefficient 6.0, max frames -- the whole model against the CPU oracle."""
+    _whole_model_check(2, "max", fused, value_pe_angle_real=16, value_pe_angle_wscale=1.0, value_pe_dist_coef=1.5,
+                       value_pe_angle_coef=6.0)
+
+
+def _whole_model_check(layers, frame_method, fused, **recipe):
     """Forward and backward of the whole model (species embedding, encoder layers, mean pooling,
     MLP head) on the GPU against the same weights run on the host cores through the oracle:
     8 crystals of 4-16 atoms, float32, symmetry-breaking noise off.
@@ -329,12 +348,15 @@ def test_whole_model_against_cpu_oracle(layers, frame_method, fused):
     from crystalframer_b200.latticeformer import Latticeformer, ModelParams
     from oracle import cpu_model
     torch.manual_seed(0)
-    mp = ModelParams(num_layers=layers, symm_break_noise=0.0, frame_method=frame_method,
-                     value_pe_angle_real=0 if frame_method == "no" else 64)
+    kw = dict(num_layers=layers, symm_break_noise=0.0, frame_method=frame_method,
+              value_pe_angle_real=0 if frame_method == "no" else 64)
+    kw.update(recipe)
+    mp = ModelParams(**kw)
     cpu = Latticeformer(mp).train()
     gpu = copy.deepcopy(cpu).to(dev).train()
     from crystalframer_b200 import cuda_funcs as F
-    F.compile_kernels(2, 8, 16, 64, 0 if frame_method == "no" else 64, 16, True, 0, 1.0, 4.0, 1.0, 1.0, 0.0)
+    F.compile_kernels(2, 8, 16, 64, mp.value_pe_angle_real, 16, True, 0, mp.value_pe_dist_wscale, mp.value_pe_angle_wscale,
+                      mp.value_pe_dist_coef, mp.value_pe_angle_coef, 0.0)
     b = synth.make_workload("cfg1")
     y = np.random.default_rng(0).normal(size=(len(b.sizes), 1)).astype(np.float32)
     tb = data.host_batch(b, y, pinned=False).to(dev, non_blocking=False)
