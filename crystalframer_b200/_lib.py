@@ -89,6 +89,8 @@ SIGNATURES = {
     "cfb200_segment_mean_fwd": (ctypes.c_int, [vp, vp, i64, i64, vp, vp]),
     "cfb200_segment_mean_bwd": (ctypes.c_int, [vp, vp, i64, i64, vp, vp]),
     "cfb200_adamw_clip_step": (ctypes.c_int, [vp] * 4 + [i64, i64] + [f32] * 6 + [ctypes.c_double, ctypes.c_double, vp, vp, vp]),
+    "cfb200_adamw_clip_step_avg": (ctypes.c_int, [vp] * 4 + [i64, i64] + [f32] * 6 + [ctypes.c_double, ctypes.c_double, vp, vp,
+                                                  vp, f32, vp]),
     "cfb200_batch_geometry_workspace_bytes": (i64, [i64]),
     "cfb200_queue_entries": (i64, [i64]),
     "cfb200_split_ints": (i64, [i64]),

@@ -708,6 +708,15 @@ int cfb200_adamw_clip_step(float* params, const float* grads, float* exp_avg, fl
                            float max_norm, double bias_correction1, double bias_correction2, float* scratch,
                            float* grad_norm, void* stream)
 {
+    return cfb200_adamw_clip_step_avg(params, grads, exp_avg, exp_avg_sq, n, decay_end, lr, beta1, beta2, eps, weight_decay,
+                                      max_norm, bias_correction1, bias_correction2, scratch, grad_norm, nullptr, 0.0f, stream);
+}
+
+int cfb200_adamw_clip_step_avg(float* params, const float* grads, float* exp_avg, float* exp_avg_sq, int64_t n,
+                               int64_t decay_end, float lr, float beta1, float beta2, float eps, float weight_decay,
+                               float max_norm, double bias_correction1, double bias_correction2, float* scratch,
+                               float* grad_norm, float* averaged, float average_weight, void* stream)
+{
     if (n < 0 || decay_end < 0 || decay_end > n) return CFB200_E_SHAPE;
     if (n == 0) return CFB200_OK;
     if (!params || !grads || !exp_avg || !exp_avg_sq || !scratch) return CFB200_E_NULL;
@@ -717,6 +726,8 @@ int cfb200_adamw_clip_step(float* params, const float* grads, float* exp_avg, fl
     A.lr = lr; A.beta1 = beta1; A.beta2 = beta2; A.eps = eps; A.weight_decay = weight_decay; A.max_norm = max_norm;
     A.inv_bc1 = (float)(1.0 / bias_correction1); A.inv_sqrt_bc2 = (float)(1.0 / sqrt(bias_correction2));
     A.partial = scratch; A.norm_out = grad_norm;
+    if (averaged != nullptr && !(average_weight > 0.0f && average_weight <= 1.0f)) return CFB200_E_SHAPE;
+    A.avg = averaged; A.avg_weight = average_weight;
     return cfb::adamw_clip_step(A, scratch, S(stream));
 }
 

@@ -10,7 +10,10 @@
 //                 p *= 1 - lr * weight_decay                (elements before decay_end only)
 //                 m  = m + (1 - beta1) (g - m)              v = beta2 v + (1 - beta2) g^2
 //                 p -= (lr / bc1) * m / (sqrt(v) / sqrt(bc2) + eps)
-//             with bc1 = 1 - beta1^t, bc2 = 1 - beta2^t formed by the caller in double.
+//             with bc1 = 1 - beta1^t, bc2 = 1 - beta2^t formed by the caller in double;
+//             optionally the running average of the weights that the reference keeps over its last epochs
+//             (torch.optim.swa_utils.AveragedModel.update_parameters after opt.step, models/regression.py:150-152):
+//                 avg += (p - avg) * avg_weight,  avg_weight = 1 / (models averaged so far + 1).
 // Sums run in a fixed order, so the step is reproducible bit for bit.
 #include "common.cuh"
 
@@ -41,6 +44,7 @@ struct AdamArgs {
     int64_t n, decay_end;
     float lr, beta1, beta2, eps, weight_decay, max_norm, inv_bc1, inv_sqrt_bc2;
     const float* partial; float* norm_out;
+    float* avg; float avg_weight;          // running average of the parameters (NULL: none)
 };
 
 __global__ void __launch_bounds__(kOptThreads) adamw_clip_kernel(const AdamArgs A)
@@ -64,7 +68,9 @@ __global__ void __launch_bounds__(kOptThreads) adamw_clip_kernel(const AdamArgs 
         const float m = fmaf(1.0f - A.beta1, g - A.m[i], A.m[i]);
         const float v = fmaf(A.beta2, A.v[i], (1.0f - A.beta2) * g * g);
         A.m[i] = m; A.v[i] = v;
-        A.p[i] = p - step * m / (sqrtf(v) * A.inv_sqrt_bc2 + A.eps);
+        p -= step * m / (sqrtf(v) * A.inv_sqrt_bc2 + A.eps);
+        A.p[i] = p;
+        if (A.avg != nullptr) { const float s = A.avg[i]; A.avg[i] = fmaf(p - s, A.avg_weight, s); }
     }
 }
 

@@ -20,7 +20,12 @@ class FlatAdamW:
     """``FlatAdamW(decay_params, no_decay_params, lr, betas, eps, weight_decay, max_norm)``; ``step()`` takes
     the gradient sinks plus the parameters' ``.grad``.  Same arithmetic as ``clip_grad_norm_(params, max_norm)``
     followed by ``torch.optim.AdamW.step()`` with ``weight_decay`` on ``decay_params`` only.  Both arguments may
-    be any iterables (generators included); a parameter may appear only once."""
+    be any iterables (generators included); a parameter may appear only once.
+
+    ``step(average=True)`` also keeps the running average of the weights that the reference maintains over its last
+    epochs with ``torch.optim.swa_utils.AveragedModel`` (models/regression.py:150-152), inside the same launch;
+    ``averaged_parameters()`` gives it back in the parameters' shapes and ``swap_averaged()`` exchanges it with the
+    live weights (to evaluate the averaged model and to return to training)."""
 
     def __init__(self, decay_params, no_decay_params=(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2,
                  max_norm=0.0, grad_sink=True):
@@ -58,6 +63,9 @@ class FlatAdamW:
         self.grad_norm = torch.zeros(1, device=dev, dtype=torch.float32)
         self.lr, self.betas, self.eps, self.weight_decay, self.max_norm = lr, betas, eps, weight_decay, max_norm
         self.steps = 0
+        self._offsets = offsets
+        self.averaged = None          # flat running average of the weights, created by the first step(average=True)
+        self.n_averaged = 0
 
     def zero_grad(self, set_to_none=True):
         """Clears the flat gradient buffer (one launch) and drops the parameters' ``.grad``."""
@@ -78,22 +86,47 @@ class FlatAdamW:
             torch._foreach_add_(dst, src)
         return self.grad
 
-    def step(self, world_sum=False):
-        """One update.  ``world_sum``: sum the gradient buffer over the ranks first (one all-reduce)."""
+    def step(self, world_sum=False, average=False):
+        """One update.  ``world_sum``: sum the gradient buffer over the ranks first (one all-reduce).  ``average``:
+        fold the updated weights into the running average (the first such step copies them)."""
         g = self.gather_grads()
         if world_sum and dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
             dist.all_reduce(g)
         self.steps += 1
         b1, b2 = self.betas
         p = _lib.ptr
-        _lib.invoke("cfb200_adamw_clip_step", 2, self.flat.device, p(self.flat), p(g), p(self.exp_avg), p(self.exp_avg_sq),
+        if average and self.averaged is None:
+            self.averaged = torch.zeros_like(self.flat)
+        weight = 1.0 / (self.n_averaged + 1) if average else 0.0
+        _lib.invoke("cfb200_adamw_clip_step_avg", 2, self.flat.device, p(self.flat), p(g), p(self.exp_avg), p(self.exp_avg_sq),
                     self.n, self.decay_end, self.lr, b1, b2, self.eps, self.weight_decay, self.max_norm,
-                    1.0 - b1 ** self.steps, 1.0 - b2 ** self.steps, p(self.scratch), p(self.grad_norm))
+                    1.0 - b1 ** self.steps, 1.0 - b2 ** self.steps, p(self.scratch), p(self.grad_norm),
+                    p(self.averaged) if average else None, weight)
+        if average:
+            self.n_averaged += 1
+
+    def averaged_parameters(self):
+        """The running average in the parameters' shapes (views of the flat average), in ``self.params`` order."""
+        if self.averaged is None:
+            raise RuntimeError("no step(average=True) has been taken")
+        return [self.averaged[o:o + p.numel()].view(p.shape) for p, o in zip(self.params, self._offsets)]
+
+    def swap_averaged(self):
+        """Exchanges the live weights with their running average (the parameters stay views of the same buffer)."""
+        if self.averaged is None:
+            raise RuntimeError("no step(average=True) has been taken")
+        tmp = self.flat.clone()
+        self.flat.copy_(self.averaged)
+        self.averaged.copy_(tmp)
 
     def state_dict(self):
-        return {"steps": self.steps, "exp_avg": self.exp_avg.clone(), "exp_avg_sq": self.exp_avg_sq.clone()}
+        return {"steps": self.steps, "exp_avg": self.exp_avg.clone(), "exp_avg_sq": self.exp_avg_sq.clone(),
+                "n_averaged": self.n_averaged, "averaged": None if self.averaged is None else self.averaged.clone()}
 
     def load_state_dict(self, state):
         self.steps = int(state["steps"])
         self.exp_avg.copy_(state["exp_avg"])
         self.exp_avg_sq.copy_(state["exp_avg_sq"])
+        self.n_averaged = int(state.get("n_averaged", 0))
+        if state.get("averaged") is not None:
+            self.averaged = state["averaged"].clone()

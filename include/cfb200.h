@@ -384,6 +384,16 @@ int cfb200_adamw_clip_step(float* params, const float* grads, float* exp_avg, fl
                            int64_t n, int64_t decay_end, float lr, float beta1, float beta2, float eps,
                            float weight_decay, float max_norm, double bias_correction1,
                            double bias_correction2, float* scratch, float* grad_norm, void* stream);
+/* The same step followed, in the same launch, by the running average of the weights that the reference keeps over
+ * its last epochs (torch.optim.swa_utils.AveragedModel.update_parameters after opt.step(),
+ * models/regression.py:150-152): averaged (n floats) += (params - averaged) * average_weight, with
+ * average_weight = 1 / (number of models averaged so far + 1), so the first update copies the weights.
+ * averaged == NULL: no average (cfb200_adamw_clip_step). */
+int cfb200_adamw_clip_step_avg(float* params, const float* grads, float* exp_avg, float* exp_avg_sq,
+                               int64_t n, int64_t decay_end, float lr, float beta1, float beta2, float eps,
+                               float weight_decay, float max_norm, double bias_correction1,
+                               double bias_correction2, float* scratch, float* grad_norm, float* averaged,
+                               float average_weight, void* stream);
 
 /* ---- one host call per batch and per encoder layer -------------------------------------------
  *

@@ -267,6 +267,39 @@ def test_weight_decay_applies_with_iterator_groups():
         FlatAdamW([m.weight, m.weight], [])
 
 
+def test_running_average_of_weights_matches_torch_swa():
+    """step(average=True) against torch.optim.swa_utils.AveragedModel.update_parameters after every step
+    (models/regression.py:150-152 of the reference), then the exchange with the live weights."""
+    dev = cuda()
+    from torch.optim.swa_utils import AveragedModel
+    from crystalframer_b200.optim import FlatAdamW
+    torch.manual_seed(1)
+    ours = torch.nn.Sequential(torch.nn.Linear(12, 9), torch.nn.ReLU(), torch.nn.Linear(9, 3)).to(dev)
+    theirs = copy.deepcopy(ours)
+    opt_o = FlatAdamW(ours.parameters(), (), lr=1e-2, betas=(0.9, 0.98), weight_decay=1e-5, max_norm=1.0)
+    opt_t = torch.optim.AdamW(theirs.parameters(), lr=1e-2, betas=(0.9, 0.98), weight_decay=1e-5)
+    swa = AveragedModel(theirs)
+    for step in range(5):
+        x = torch.randn(32, 12, device=dev)
+        for m, o in ((ours, opt_o), (theirs, opt_t)):
+            o.zero_grad()
+            m(x).square().mean().backward()
+        opt_o.step(average=step >= 1)                  # averaging starts at the second step
+        torch.nn.utils.clip_grad_norm_(theirs.parameters(), 1.0)
+        opt_t.step()
+        if step >= 1:
+            swa.update_parameters(theirs)
+    assert opt_o.n_averaged == 4
+    for a, b in zip(opt_o.averaged_parameters(), swa.module.parameters()):
+        assert torch.allclose(a, b, rtol=1e-5, atol=1e-7), float((a - b).abs().max())
+    live = [p.detach().clone() for p in ours.parameters()]
+    opt_o.swap_averaged()
+    for p, b in zip(ours.parameters(), swa.module.parameters()):
+        assert torch.allclose(p, b, rtol=1e-5, atol=1e-7)
+    opt_o.swap_averaged()
+    assert all(torch.equal(p, l) for p, l in zip(ours.parameters(), live))
+
+
 def test_sharded_step_equals_whole_batch():
     """One global batch dealt into two shards by attention cost, each shard's loss divided by the GLOBAL crystal
     count, gradient buffers added: the same gradients and the same update as one pass over the whole batch
