@@ -241,8 +241,8 @@ __global__ void __launch_bounds__(at_warps(false) * 32, kAtFwdBlocks) attn_fwd_k
 // projects W s_ij per pair (one 16 x 256 product), pools t beside s, and stores 68 bytes per (pair, head); the
 // backward pass (attn_bwd_saved_kernel) is then a plain ragged attention backward: no second lattice sum.  The
 // attention output sums the stored value encodings directly; the pooled s is still kept for the weight gradients.
-constexpr int kAtTrainWarps = 8;
-constexpr size_t kAtTrainSmem = sizeof(float) * (kAtHd * kAtWfStride + kAtTrainWarps * 8 * 32 + kAtTrainWarps * kAtK);
+constexpr int kAtTrainWarps = 12;
+constexpr size_t kAtTrainSmem = sizeof(float) * (kAtHd * kAtWfStride + kAtTrainWarps * 8 * 32 + kAtTrainWarps * 3 * kAtK);
 
 // out_d = W_d . row: lane = (output d, half of the 256 basis indices); every lane returns the full sum of its d
 __device__ __forceinline__ float project_row(const float* W_s, const float* row, const int lane)
@@ -277,7 +277,9 @@ __global__ void __launch_bounds__(kAtTrainWarps * 32, 2) attn_fwd_train_kernel(c
     }
     LatticeLane<2, ANG> L;
     L.init(P, lane, tbuf + warp * 8 * 32);
-    float* srow = rows + warp * kAtK;
+    float* srow = rows + warp * 3 * kAtK;
+    float* Sp = srow + kAtK + lane;          // pooled basis sums of this lane: Sp[32 r], r < 8; then the d^2-weighted ones
+    float* Tq = Sp + kAtK;
     __syncthreads();
     const int first = TASKS ? kSplitSlots - __ldg(A.chunk_count + h) : 0;
 
@@ -300,9 +302,8 @@ __global__ void __launch_bounds__(kAtTrainWarps * 32, 2) attn_fwd_train_kernel(c
         }
         const float qd = lane < kAtHd ? __ldg(A.qs + (i * H + h) * kAtHd + lane) : 0.f;
         float m = -INFINITY, l = 0.f, V = 0.f;
-        float S[8], Tp[8];                                  // attention-pooled basis sums, plain and d^2-weighted
 #pragma unroll
-        for (int r = 0; r < 8; r++) S[r] = Tp[r] = 0.f;
+        for (int r = 0; r < 8; r++) Sp[32 * r] = Tq[32 * r] = 0.f;        // attention-pooled sums, plain and d^2-weighted
         const int64_t j0 = A.edges[A.E + T.e0];
         for (int64_t e = T.e0; e < T.e1; e++) {
             const int64_t j = j0 + (e - T.e0);
@@ -337,12 +338,12 @@ __global__ void __launch_bounds__(kAtTrainWarps * 32, 2) attn_fwd_train_kernel(c
             const float f = p * inv;
             l = fmaf(l, sc, p);
             V = fmaf(V, sc, p * (vd + val_d));
-            S[0] = fmaf(S[0], sc, f * L.sd[0]); S[1] = fmaf(S[1], sc, f * L.sd[1]);
-            Tp[0] = fmaf(Tp[0], sc, f * L.qd[0]); Tp[1] = fmaf(Tp[1], sc, f * L.qd[1]);
+            Sp[0] = fmaf(Sp[0], sc, f * L.sd[0]); Sp[32] = fmaf(Sp[32], sc, f * L.sd[1]);
+            Tq[0] = fmaf(Tq[0], sc, f * L.qd[0]); Tq[32] = fmaf(Tq[32], sc, f * L.qd[1]);
 #pragma unroll
             for (int x = 0; x < 3; x++) {
-                S[2 + 2 * x] = fmaf(S[2 + 2 * x], sc, f * L.sa[x][0]); S[3 + 2 * x] = fmaf(S[3 + 2 * x], sc, f * L.sa[x][1]);
-                Tp[2 + 2 * x] = fmaf(Tp[2 + 2 * x], sc, f * L.qa[x][0]); Tp[3 + 2 * x] = fmaf(Tp[3 + 2 * x], sc, f * L.qa[x][1]);
+                Sp[64 + 64 * x] = fmaf(Sp[64 + 64 * x], sc, f * L.sa[x][0]); Sp[96 + 64 * x] = fmaf(Sp[96 + 64 * x], sc, f * L.sa[x][1]);
+                Tq[64 + 64 * x] = fmaf(Tq[64 + 64 * x], sc, f * L.qa[x][0]); Tq[96 + 64 * x] = fmaf(Tq[96 + 64 * x], sc, f * L.qa[x][1]);
             }
             m = mn;
         }
@@ -351,12 +352,12 @@ __global__ void __launch_bounds__(kAtTrainWarps * 32, 2) attn_fwd_train_kernel(c
         if (partial) row -= A.N;
         if (lane == 0) (partial ? A.part_lse : A.lse)[row * H + h] = m + logf(l);
         float* sp = (partial ? A.part_spool : A.spool) + (row * H + h) * kAtK;
-        sp[lane] = S[0] * inv_l; sp[32 + lane] = S[1] * inv_l;
-        srow[lane] = Tp[0] * inv_l * P.c_dist; srow[32 + lane] = Tp[1] * inv_l * P.c_dist;
+        sp[lane] = Sp[0] * inv_l; sp[32 + lane] = Sp[32] * inv_l;
+        srow[lane] = Tq[0] * inv_l * P.c_dist; srow[32 + lane] = Tq[32] * inv_l * P.c_dist;
 #pragma unroll
         for (int x = 0; x < 3; x++) {
-            sp[64 + 64 * x + lane] = S[2 + 2 * x] * inv_l * P.c_ang; sp[96 + 64 * x + lane] = S[3 + 2 * x] * inv_l * P.c_ang;
-            srow[64 + 64 * x + lane] = Tp[2 + 2 * x] * inv_l * P.c_ang; srow[96 + 64 * x + lane] = Tp[3 + 2 * x] * inv_l * P.c_ang;
+            sp[64 + 64 * x + lane] = Sp[64 + 64 * x] * inv_l * P.c_ang; sp[96 + 64 * x + lane] = Sp[96 + 64 * x] * inv_l * P.c_ang;
+            srow[64 + 64 * x + lane] = Tq[64 + 64 * x] * inv_l * P.c_ang; srow[96 + 64 * x + lane] = Tq[96 + 64 * x] * inv_l * P.c_ang;
         }
         __syncwarp();
         const float up_d = project_row(W_s, srow, lane);     // W (pooled d^2-weighted sums)
