@@ -4,7 +4,7 @@
 // models/cuda_funcs/calc_maximum_frame.py and the torch ops of
 // models/indexed_lattice_multi_head_attention_cuda.py:475-481 of the reference).
 //
-// grid = (spans of 192 pairs, heads).  A block owns the query atoms whose first pair falls in its
+// grid = (spans of 224 pairs, heads).  A block owns the query atoms whose first pair falls in its
 // span and walks all pairs of those atoms, one pair per thread -- about 200 pairs per block
 // whatever the crystal sizes, so small crystals do not leave lanes idle.  Each thread sweeps the
 // lattice translations of its pair, finds the pair's candidate image and score, and folds
@@ -25,11 +25,13 @@ namespace cfb {
 
 #ifndef CFB_FR_THREADS
 #define CFB_FR_THREADS 256
-#define CFB_FR_PAIRS 192
+#define CFB_FR_PAIRS 224
 #define CFB_FR_BLOCKS 3
 #endif
-constexpr int kFrPairs = CFB_FR_PAIRS;     // pair-list span whose query atoms one block owns; with crystals of up to 64
-                                           // atoms all pairs of the block's atoms fit one round of kFrThreads threads
+constexpr int kFrPairs = CFB_FR_PAIRS;     // pair-list span whose query atoms one block owns: the block's atoms have up to
+                                           // span + (pairs of the last atom - 1) pairs, usually one round of kFrThreads
+                                           // threads, sometimes two (measured: 224 beats 192, which always fits one round
+                                           // for crystals of up to 64 atoms, by 5 %)
 constexpr int kFrThreads = CFB_FR_THREADS;
 constexpr int kFrMaxRows = kFrThreads;     // at most one atom starts per pair of the span (kFrPairs <= kFrThreads)
 constexpr int kFrHd = 16;
@@ -217,7 +219,20 @@ __device__ __forceinline__ Cand second_axis_candidate(const Cell& cell, float a,
         }
     };
     bool sweep = list == nullptr;
-    if (list != nullptr) {
+    if (list != nullptr && is_static) {
+        // The static score grows with the distance: candidates farthest-first from the end of the pair's sorted list
+        // (only offered where the list holds the task's whole box); the search ends at the first entry whose distance
+        // part -- the other part is never positive -- cannot reach the running maximum.
+        const int nT = (2 * list_range + 1) * (2 * list_range + 1) * (2 * list_range + 1);
+        for (int s = nT - 1; s >= 0; s--) {
+            const float d2l = __ldg(list + s);
+            const float g_est = d2l - d2min;
+            const float slack = d2l * 4e-6f + fabsf(g_est) * 2e-6f + 1e-12f;
+            if (g_est + slack + half < best) break;
+            const int code = __float_as_int(__ldg(list + 4 * kListLen + s));
+            score_candidate((code & 255) - list_range, ((code >> 8) & 255) - list_range, ((code >> 16) & 255) - list_range);
+        }
+    } else if (list != nullptr) {
         // Candidates nearest-first from the pair's sorted list.  The Gaussian part of the score only falls
         // along the list and the other part is never positive, so the search ends at the first entry whose
         // Gaussian part -- with a margin for the few ulp between the list's fused arithmetic and the
@@ -395,7 +410,8 @@ __global__ void __launch_bounds__(kFrThreads, CFB_FR_BLOCKS) max_frame_kernel(co
                     if (known < 0.f && A.cache != nullptr && (same_box || (wider && __ldg(&A.cache[e].y) < reach2)))
                         known = __ldg(&A.cache[e].x);
                     // the sorted list serves the search only where the score falls with the distance
-                    const bool hit = A.list != nullptr && !A.is_static && (same_box || (wider && reach2 > 0.f));
+                    // (the static search runs farthest-first, so it needs the list of the task's whole box)
+                    const bool hit = A.list != nullptr && (same_box || (!A.is_static && wider && reach2 > 0.f));
                     cd = second_axis_candidate(cell, row_a[r], R1, R2, R3, P.noise, A.seed2, noise_id,
                                                row_f1[r][0], row_f1[r][1], row_f1[r][2], known,
                                                hit ? A.list + (size_t)e * kListStride : nullptr, A.is_static != 0, C, reach2);

@@ -469,7 +469,7 @@ int cfb200_encoder_layer_fwd(const cfb200_layer_desc* L, const cfb200_layer_weig
         TmScope tm(CFB200_TM_FRAMES, st);
         rc = frames_common(3, St->q_scaled, St->k, St->a, G->pos_ij, G->tvecs, G->rvlen, G->batch, G->edges, G->e_start, N, E,
                            L->cutoff_radius, L->seed1, L->seed2, nullptr, St->frames, St->frames + fr, St->frames + 2 * fr,
-                           nullptr, nullptr, stream, G->pair_cache, nullptr, G->cache_range, 1);
+                           nullptr, nullptr, stream, G->pair_cache, G->pair_list, G->cache_range, 1);
     } else if (L->frame_method == 4) {
         TmScope tm(CFB200_TM_FRAMES, st);
         rc = cfb200_lattice_frames(St->a, G->tvecs, G->rvlen, G->batch, G->edges, G->e_start, N, E, L->cutoff_radius, L->seed1,
