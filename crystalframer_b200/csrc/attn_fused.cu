@@ -244,19 +244,24 @@ __global__ void __launch_bounds__(at_warps(false) * 32, kAtFwdBlocks) attn_fwd_k
 constexpr int kAtTrainWarps = 12;
 constexpr size_t kAtTrainSmem = sizeof(float) * (kAtHd * kAtWfStride + kAtTrainWarps * 8 * 32 + kAtTrainWarps * 3 * kAtK);
 
-// out_d = W_d . row: lane = (output d, half of the 256 basis indices); every lane returns the full sum of its d
+// out_d = W_d . row: lane = (output d, half of the 256 basis indices); every lane returns the full sum of its d.
+// Packed FP32: two products per instruction, two partial sums.
 __device__ __forceinline__ float project_row(const float* W_s, const float* row, const int lane)
 {
     const int d = lane & 15, half = lane >> 4;
-    const float4* wr = reinterpret_cast<const float4*>(W_s + d * kAtWfStride) + half * 32;
-    const float4* sr = reinterpret_cast<const float4*>(row) + half * 32;
-    float acc = 0.f;
+    const ulonglong2* wr = reinterpret_cast<const ulonglong2*>(W_s + d * kAtWfStride) + half * 32;
+    const ulonglong2* sr = reinterpret_cast<const ulonglong2*>(row) + half * 32;
+    f32x2 acc = pack2(0.f, 0.f);
 #pragma unroll 8
     for (int k4 = 0; k4 < 32; k4++) {
-        const float4 w4 = wr[k4], s4 = sr[k4];
-        acc = fmaf(s4.x, w4.x, fmaf(s4.y, w4.y, fmaf(s4.z, w4.z, fmaf(s4.w, w4.w, acc))));
+        const ulonglong2 w4 = wr[k4], s4 = sr[k4];
+        acc = fma2(s4.x, w4.x, acc);
+        acc = fma2(s4.y, w4.y, acc);
     }
-    return acc + __shfl_xor_sync(0xffffffffu, acc, 16);
+    float a0, a1;
+    unpack2(acc, a0, a1);
+    const float sum = a0 + a1;
+    return sum + __shfl_xor_sync(0xffffffffu, sum, 16);
 }
 
 template <bool ANG, bool TASKS>
@@ -278,8 +283,10 @@ __global__ void __launch_bounds__(kAtTrainWarps * 32, 2) attn_fwd_train_kernel(c
     LatticeLane<2, ANG> L;
     L.init(P, lane, tbuf + warp * 8 * 32);
     float* srow = rows + warp * 3 * kAtK;
-    float* Sp = srow + kAtK + lane;          // pooled basis sums of this lane: Sp[32 r], r < 8; then the d^2-weighted ones
-    float* Tq = Sp + kAtK;
+    // pooled basis sums of this lane as four packed pairs (indices l, l + 32 of each basis): Sp[32 x], x < 4; then the
+    // d^2-weighted ones
+    f32x2* Sp = reinterpret_cast<f32x2*>(srow + kAtK) + lane;
+    f32x2* Tq = Sp + kAtK / 2;
     __syncthreads();
     const int first = TASKS ? kSplitSlots - __ldg(A.chunk_count + h) : 0;
 
@@ -303,7 +310,7 @@ __global__ void __launch_bounds__(kAtTrainWarps * 32, 2) attn_fwd_train_kernel(c
         const float qd = lane < kAtHd ? __ldg(A.qs + (i * H + h) * kAtHd + lane) : 0.f;
         float m = -INFINITY, l = 0.f, V = 0.f;
 #pragma unroll
-        for (int r = 0; r < 8; r++) Sp[32 * r] = Tq[32 * r] = 0.f;        // attention-pooled sums, plain and d^2-weighted
+        for (int x = 0; x < 4; x++) Sp[32 * x] = Tq[32 * x] = pack2(0.f, 0.f);        // attention-pooled sums, plain and d^2-weighted
         const int64_t j0 = A.edges[A.E + T.e0];
         for (int64_t e = T.e0; e < T.e1; e++) {
             const int64_t j = j0 + (e - T.e0);
@@ -338,12 +345,15 @@ __global__ void __launch_bounds__(kAtTrainWarps * 32, 2) attn_fwd_train_kernel(c
             const float f = p * inv;
             l = fmaf(l, sc, p);
             V = fmaf(V, sc, p * (vd + val_d));
-            Sp[0] = fmaf(Sp[0], sc, f * L.sd[0]); Sp[32] = fmaf(Sp[32], sc, f * L.sd[1]);
-            Tq[0] = fmaf(Tq[0], sc, f * L.qd[0]); Tq[32] = fmaf(Tq[32], sc, f * L.qd[1]);
+            {
+                const f32x2 sc2 = pack2(sc, sc), f2 = pack2(f, f);
+                Sp[0] = fma2(Sp[0], sc2, mul2(f2, pack2(L.sd[0], L.sd[1])));
+                Tq[0] = fma2(Tq[0], sc2, mul2(f2, pack2(L.qd[0], L.qd[1])));
 #pragma unroll
-            for (int x = 0; x < 3; x++) {
-                Sp[64 + 64 * x] = fmaf(Sp[64 + 64 * x], sc, f * L.sa[x][0]); Sp[96 + 64 * x] = fmaf(Sp[96 + 64 * x], sc, f * L.sa[x][1]);
-                Tq[64 + 64 * x] = fmaf(Tq[64 + 64 * x], sc, f * L.qa[x][0]); Tq[96 + 64 * x] = fmaf(Tq[96 + 64 * x], sc, f * L.qa[x][1]);
+                for (int x = 0; x < 3; x++) {
+                    Sp[32 + 32 * x] = fma2(Sp[32 + 32 * x], sc2, mul2(f2, pack2(L.sa[x][0], L.sa[x][1])));
+                    Tq[32 + 32 * x] = fma2(Tq[32 + 32 * x], sc2, mul2(f2, pack2(L.qa[x][0], L.qa[x][1])));
+                }
             }
             m = mn;
         }
@@ -352,12 +362,17 @@ __global__ void __launch_bounds__(kAtTrainWarps * 32, 2) attn_fwd_train_kernel(c
         if (partial) row -= A.N;
         if (lane == 0) (partial ? A.part_lse : A.lse)[row * H + h] = m + logf(l);
         float* sp = (partial ? A.part_spool : A.spool) + (row * H + h) * kAtK;
-        sp[lane] = Sp[0] * inv_l; sp[32 + lane] = Sp[32] * inv_l;
-        srow[lane] = Tq[0] * inv_l * P.c_dist; srow[32 + lane] = Tq[32] * inv_l * P.c_dist;
+        {
+            float s0, s1, t0, t1;
+            unpack2(Sp[0], s0, s1); unpack2(Tq[0], t0, t1);
+            sp[lane] = s0 * inv_l; sp[32 + lane] = s1 * inv_l;
+            srow[lane] = t0 * inv_l * P.c_dist; srow[32 + lane] = t1 * inv_l * P.c_dist;
 #pragma unroll
-        for (int x = 0; x < 3; x++) {
-            sp[64 + 64 * x + lane] = Sp[64 + 64 * x] * inv_l * P.c_ang; sp[96 + 64 * x + lane] = Sp[96 + 64 * x] * inv_l * P.c_ang;
-            srow[64 + 64 * x + lane] = Tq[64 + 64 * x] * inv_l * P.c_ang; srow[96 + 64 * x + lane] = Tq[96 + 64 * x] * inv_l * P.c_ang;
+            for (int x = 0; x < 3; x++) {
+                unpack2(Sp[32 + 32 * x], s0, s1); unpack2(Tq[32 + 32 * x], t0, t1);
+                sp[64 + 64 * x + lane] = s0 * inv_l * P.c_ang; sp[96 + 64 * x + lane] = s1 * inv_l * P.c_ang;
+                srow[64 + 64 * x + lane] = t0 * inv_l * P.c_ang; srow[96 + 64 * x + lane] = t1 * inv_l * P.c_ang;
+            }
         }
         __syncwarp();
         const float up_d = project_row(W_s, srow, lane);     // W (pooled d^2-weighted sums)

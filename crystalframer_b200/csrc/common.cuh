@@ -58,6 +58,36 @@ __device__ __forceinline__ float ex2_approx(float x)
     return y;
 }
 
+// Packed FP32: two floats in one 64-bit register, one instruction for two fused multiply-adds (fma.rn.f32x2 and its
+// mul twin, sm_100).  Each half is an ordinary IEEE round-to-nearest operation; what is saved is issue slots.
+typedef unsigned long long f32x2;
+
+__device__ __forceinline__ f32x2 pack2(const float lo, const float hi)
+{
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+
+__device__ __forceinline__ void unpack2(const f32x2 v, float& lo, float& hi)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+__device__ __forceinline__ f32x2 fma2(const f32x2 a, const f32x2 b, const f32x2 c)
+{
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+__device__ __forceinline__ f32x2 mul2(const f32x2 a, const f32x2 b)
+{
+    f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 __device__ __forceinline__ float warp_sum(float v)
 {
 #pragma unroll
