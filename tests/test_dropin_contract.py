@@ -206,3 +206,51 @@ def test_reference_module_runs_on_this_package():
         for k in [k for k in sys.modules if k == "models" or k.startswith("models.")]:
             del sys.modules[k]
         sys.modules.update({k: v for k, v in saved.items() if v is not None})
+
+
+def test_whole_model_state_dict_matches_the_reference():
+    """The reference's own ``models.latticeformer.Latticeformer`` (default_jarvis.json), instantiated with this
+    package's ``cuda_funcs`` swapped in, against this package's model: same state_dict keys in the same order and the
+    same shapes, so the reference's checkpoints load here and vice versa."""
+    import importlib
+    import json
+    import crystalframer_b200.cuda_funcs as ours
+    from crystalframer_b200.cuda_funcs import kernel_manager
+    from crystalframer_b200.latticeformer import Latticeformer, ModelParams
+    saved = {k: sys.modules.get(k) for k in list(sys.modules) if k == "models" or k.startswith("models.")}
+    for k in saved:
+        del sys.modules[k]
+    stubbed = []
+    for name in ("torch_scatter", "cupy", "pytorch_pfn_extras", "torch_geometric", "torch_geometric.data", "torch_geometric.nn"):
+        if name not in sys.modules:              # imported at module level by the reference, not used on this path
+            try:
+                importlib.import_module(name)
+            except Exception:
+                sys.modules[name] = types.ModuleType(name)
+                stubbed.append(name)
+    pkg = types.ModuleType("models")
+    pkg.__path__ = [os.path.join(REF, "models")]
+    sys.modules["models"] = pkg
+    sys.modules["models.cuda_funcs"] = ours
+    kernel_manager.DEFER_BINDING = True          # a parameter container: do not bind constants in the CUDA library
+    try:
+        lf = importlib.import_module("models.latticeformer")
+        with open(os.path.join(REF, "params", "crystalframer", "default_jarvis.json")) as f:
+            cfg = json.load(f)
+        params = types.SimpleNamespace(**cfg)
+        if not hasattr(params, "targets"):
+            params.targets = ["e_form"]
+        ref = lf.Latticeformer(params)
+        mine = Latticeformer(ModelParams())
+        a, b = ref.state_dict(), mine.state_dict()
+        assert list(a) == list(b)
+        assert all(a[k].shape == b[k].shape for k in a)
+        mine.load_state_dict(a)
+        ref.load_state_dict(b)
+    finally:
+        kernel_manager.DEFER_BINDING = False
+        for name in stubbed:
+            sys.modules.pop(name, None)
+        for k in [k for k in sys.modules if k == "models" or k.startswith("models.")]:
+            del sys.modules[k]
+        sys.modules.update({k: v for k, v in saved.items() if v is not None})
