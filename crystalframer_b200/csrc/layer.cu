@@ -401,6 +401,9 @@ static void layer_attn_args(cfb::AtArgs& A, const cfb200_layer_desc* L, const cf
     const int64_t fr = G->N * g_cfg.num_heads * 3;
     A.qs = St->q_scaled; A.k = St->k; A.v = St->v; A.a_ik = St->a; A.pos_ij = G->pos_ij; A.tvecs = G->tvecs; A.rvlen = G->rvlen;
     A.batch = G->batch; A.edges = G->edges; A.e_start = G->e_start; A.order = G->order; A.counters = G->counters;
+    if (G->split != nullptr && St->tasks == nullptr) {
+        A.order = G->order + cfb::kSplitSlots;         // the plain queue: the atoms' entries follow the chunk region
+    }
     if (G->split != nullptr && St->tasks != nullptr) {
         // the table's last 256 bytes hold the per-head counts of chunk entries in use
         A.tasks = reinterpret_cast<const int4*>(St->tasks);

@@ -31,6 +31,9 @@ FUSED_FORWARD_CALLS = ("cfb200_encoder_layer_fwd",)
 # cut the longest (atom, head) tasks of the attention kernels into chunks (see cfb200_batch_geometry); a switch for
 # tests and measurements
 SPLIT_TASKS = True
+# give every layer a task table when the geometry carries a chunked queue (False: the layers walk the plain queue of
+# atoms; a switch for tests)
+TASK_TABLE = True
 # training forward leaves per-pair value encodings for the backward pass (no second lattice sum); a switch for tests
 # and measurements, and for batches whose (E,H,17) floats per layer do not fit
 SAVE_PAIR_RESULTS = True
@@ -189,7 +192,7 @@ class FusedEncoderLayerFunc(torch.autograd.Function):
         desc = _lib.LayerDesc(D, F, method, meta["lb"], meta["beta"], meta["scale_real"], meta["dist_max"], meta["cutoff"],
                               seed1, seed2)
         W = _lib.LayerWeights(*[None if p is None else _lib.ptr(p) for p in params])
-        tasks_bytes = int(_lib.lib().cfb200_attn_tasks_bytes(N)) if geo.c.split else 0
+        tasks_bytes = int(_lib.lib().cfb200_attn_tasks_bytes(N)) if geo.c.split and TASK_TABLE else 0
         # with gradients wanted the forward stores per-pair results (68 bytes per pair and head) and the backward
         # needs no second lattice sum; without, the lighter forward runs
         save_pairs = SAVE_PAIR_RESULTS and any(ctx.needs_input_grad)

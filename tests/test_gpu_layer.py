@@ -182,6 +182,36 @@ def test_chunked_tasks_change_nothing_but_rounding(save_pairs):
     assert _lib.read_status(dev) == 0
 
 
+def test_chunked_geometry_without_task_table_is_the_plain_queue():
+    """A geometry built with the chunked queue, layers given no task table: the kernels walk the atoms' entries of the
+    queue (behind its chunk region) exactly as they walk the plain queue -- bit-identical results."""
+    dev = cuda()
+    from crystalframer_b200 import _lib, data, fused_layer, synth
+    from crystalframer_b200.latticeformer import Latticeformer, ModelParams
+    torch.manual_seed(5)
+    model = Latticeformer(ModelParams(num_layers=1, symm_break_noise=0.0)).to(dev).train()
+    b = synth.make_workload("cfg2", num_crystals=24)
+    y = np.random.default_rng(1).normal(size=(len(b.sizes), 1)).astype(np.float32)
+    tb = data.host_batch(b, y, pinned=False).to(dev, non_blocking=False)
+    with torch.no_grad():
+        model(tb)
+    results = []
+    try:
+        for split, table in ((False, True), (True, False)):
+            fused_layer.SPLIT_TASKS, fused_layer.TASK_TABLE = split, table
+            model.zero_grad(set_to_none=True)
+            np.random.seed(11)
+            torch.manual_seed(11)
+            out = model(tb)
+            (out - tb.y).abs().mean().backward()
+            results.append((out.detach().clone(), {n: p.grad.detach().clone() for n, p in model.named_parameters() if p.grad is not None}))
+    finally:
+        fused_layer.SPLIT_TASKS, fused_layer.TASK_TABLE = True, True
+    (o0, g0), (o1, g1) = results
+    assert torch.equal(o0, o1) and all(torch.equal(g0[n], g1[n]) for n in g0)
+    assert _lib.read_status(dev) == 0
+
+
 def _step_models(dev, sink):
     from crystalframer_b200 import data, synth
     from crystalframer_b200.latticeformer import Latticeformer, ModelParams
