@@ -347,9 +347,9 @@ int cfb200_batch_geometry(const float* pos, const float* tvecs, const int64_t* s
     if (rc != CFB200_OK) return rc;
     cfb::cell_kernel<<<(unsigned)((B + 127) / 128), 128, 0, st>>>(tvecs, sizes, B, rvecs, rvlen, vcell, key, inv_vol);
     if (E > 0) cfb::pos_ij_kernel<<<(unsigned)((E + 255) / 256), 256, 0, st>>>(pos, edges, E, pos_ij);
-    // warps that serve one head's queue in the attention kernels (the backward launch, which has the fewer)
+    // warps that serve one head's queue in the training forward, the launch the chunks are cut for
     const int heads = split != nullptr ? g_cfg.num_heads : 1;
-    const int workers = cfb::at_grid_x(N, heads, true) * cfb::at_warps(true);
+    const int workers = cfb::at_grid_x(N, heads, true) * cfb::kAtTrainWarps;
     cfb::atom_order_kernel<<<1, 1024, 0, st>>>(key, inv_vol, sizes, crystal_start, B, N, workers, by_rank, start_of, want_of,
                                                slot_of, order, split);
     if (cudaGetLastError() != cudaSuccess) return CFB200_E_CUDA;
