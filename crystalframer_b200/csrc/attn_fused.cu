@@ -271,15 +271,8 @@ __global__ void __launch_bounds__(kAtTrainWarps * 32, 2) attn_fwd_train_kernel(c
     float* W_s = smem;                                      // [16][260]
     float* tbuf = W_s + kAtHd * kAtWfStride;                // per warp 8 x 32
     float* rows = tbuf + kAtTrainWarps * 8 * 32;            // per warp 256: the basis vector being projected
-    const int h = blockIdx.y, H = P.H;
+    const int H = P.H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int idx = threadIdx.x; idx < kAtHd * kAtK / 4; idx += kAtTrainWarps * 32) {
-        const int o = idx >> 6, k4 = idx & 63, b = k4 >> 4, d4 = k4 & 15;
-        float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
-        const int width = b == 0 ? 64 : P.angle_dim;          // columns this basis' weights hold (zero beyond)
-        if (A.W[b] != nullptr && 4 * d4 < width) w = __ldg(reinterpret_cast<const float4*>(A.W[b] + ((size_t)h * kAtHd + o) * width) + d4);
-        reinterpret_cast<float4*>(W_s)[o * (kAtWfStride / 4) + k4] = w;
-    }
     LatticeLane<2, ANG> L;
     L.init(P, lane, tbuf + warp * 8 * 32);
     float* srow = rows + warp * 3 * kAtK;
@@ -287,8 +280,39 @@ __global__ void __launch_bounds__(kAtTrainWarps * 32, 2) attn_fwd_train_kernel(c
     // d^2-weighted ones
     f32x2* Sp = reinterpret_cast<f32x2*>(srow + kAtK) + lane;
     f32x2* Tq = Sp + kAtK / 2;
-    __syncthreads();
+    __shared__ int head_open;
+
+    // A block serves its own head first and then, turn by turn, the head with the most entries left: the heads' Gaussian
+    // widths differ, so their queues hold up to a fifth more or less work than the average, and the blocks of the light
+    // heads would otherwise sit idle while the heaviest head finishes.  Switching heads costs a reload of the 16 KB of
+    // projection weights.
+    for (int turn = 0; turn < 2 * H; turn++) {
+    int h = blockIdx.y;
+    if (turn > 0) {
+        __syncthreads();                                    // every warp is done with the previous head's weights
+        if (threadIdx.x == 0) {
+            // the head with the most entries left in its queue (a stale count costs a wasted or a missed turn at most)
+            int best = -1, most = 0;
+            for (int hh = 0; hh < H; hh++) {
+                const int limit = TASKS ? (int)(A.n_entries - kSplitSlots) + __ldg(A.chunk_count + hh) : (int)A.N;
+                const int left = limit - atomicAdd(A.counters + hh, 0);
+                if (left > most) { most = left; best = hh; }
+            }
+            head_open = best;
+        }
+        __syncthreads();
+        h = head_open;
+        if (h < 0) break;                                   // every queue is drained
+    }
     const int first = TASKS ? kSplitSlots - __ldg(A.chunk_count + h) : 0;
+    for (int idx = threadIdx.x; idx < kAtHd * kAtK / 4; idx += kAtTrainWarps * 32) {
+        const int o = idx >> 6, k4 = idx & 63, b = k4 >> 4, d4 = k4 & 15;
+        float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+        const int width = b == 0 ? 64 : P.angle_dim;          // columns this basis' weights hold (zero beyond)
+        if (A.W[b] != nullptr && 4 * d4 < width) w = __ldg(reinterpret_cast<const float4*>(A.W[b] + ((size_t)h * kAtHd + o) * width) + d4);
+        reinterpret_cast<float4*>(W_s)[o * (kAtWfStride / 4) + k4] = w;
+    }
+    __syncthreads();
 
     for (;;) {
         const int64_t t = next_task(A.counters + h, lane) + first;
@@ -382,6 +406,7 @@ __global__ void __launch_bounds__(kAtTrainWarps * 32, 2) attn_fwd_train_kernel(c
         }
         __syncwarp();
     }
+    }   // heads in turn
 }
 
 // Backward pass from the results of the training forward: warp = (atom, head), lane = pair (32 at a time).  Per pair
