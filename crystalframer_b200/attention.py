@@ -7,8 +7,9 @@ arguments, same parameter names, shapes and initialisation (so released checkpoi
 data-dependent ``gauss_scale`` state.  Input / output projections and the Gaussian-coefficient
 pipeline stay in PyTorch; everything between them runs in libcfb200.
 
-Only the real-space domain is implemented, with frame methods "max", "max_static", "lattice", "pca",
-"weighted_pca" (CrystalFramer) and "no" (plain Crystalformer distance encoding).
+Domains: "real" with frame methods "max", "max_static", "lattice", "pca", "weighted_pca" (CrystalFramer)
+and "no" (plain Crystalformer distance encoding); "reci" / "RECI" (plain Crystalformer's reciprocal-space
+logit bias, no value encoding), also alternating by layer ("real-reci").  "multihead" is not built.
 """
 import math
 from typing import Optional, Tuple
@@ -23,7 +24,7 @@ from torch.nn.modules.linear import NonDynamicallyQuantizableLinear
 from .cuda_funcs import (ComputeFrame1MaximumMethodCUDA, ComputeFrame1MaximumStaticMethodCUDA,
                          ComputeFrame2MaximumMethodCUDA, ComputeFrame2MaximumStaticMethodCUDA, ComputeLatticeFrameCUDA, ComputePCAFrame,
                          FusedDotProductAttentionCUDA, RealEncodingWithFramedProjFuncCUDA,
-                         RealPeriodicEncodingWithProjFuncCUDA, max_frames_fused, max_static_frames_fused,
+                         RealPeriodicEncodingWithProjFuncCUDA, ReciPeriodicEncodingFuncCUDA, max_frames_fused, max_static_frames_fused,
                          weighted_pca_frames)
 from .latticeformer_params import LatticeformerParams
 
@@ -162,7 +163,16 @@ def gaussian_coefficients(q, lattice_pos_weights, gauss_scale, params, training)
                     gauss_scale[1] = shift
                 gauss_scale._cf_ready = gauss_scale._version
         alpha = (alpha + shift) * scale
-    lb, beta = params.gauss_lb_real, params.positive_func_beta
+    beta = params.positive_func_beta
+    if params.domain in ("reci", "RECI"):
+        # reciprocal-space Gaussians widen where real-space ones narrow
+        # (models/indexed_lattice_multi_head_attention_cuda.py:946-952)
+        lb = params.gauss_lb_reci
+        pos = (1.0 - lb) * F.elu(alpha * (beta / (1.0 - lb))) + 1.0
+        if params.domain == "RECI":
+            pos = 1 / pos
+        return pos * (-0.5 * params.scale_reci ** 2)
+    lb = params.gauss_lb_real
     pos = (1.0 - lb) * F.elu(alpha * (beta / (1.0 - lb))) + 1.0
     return pos * (-0.5 * params.scale_real ** -2)
 
@@ -185,12 +195,16 @@ def crystalformer_multi_head_attention_forward_cuda(
     v = F.linear(value, v_proj_weight, bv).view(value.shape[0], num_heads, hv)
     attn_weights = values = None
     if params is not None and params.domain != "no":
-        if params.domain != "real":
-            raise NotImplementedError(f"domain={params.domain}: only the real-space domain is implemented")
+        if params.domain not in ("real", "reci", "RECI"):
+            raise NotImplementedError(f"domain={params.domain}")
         alpha = gaussian_coefficients(q, lattice_pos_weights, gauss_scale, params, training)
-        attn_weights, values = compute_real_domain_attn_frame_proj(
-            q, k, v, batch_q, batch_kv, edges, pos, dist2_min, tvecs, rvecs, pe_dist_proj, proj_angle1,
-            proj_angle2, proj_angle3, alpha, params, this_epoch)
+        if params.domain == "real":
+            attn_weights, values = compute_real_domain_attn_frame_proj(
+                q, k, v, batch_q, batch_kv, edges, pos, dist2_min, tvecs, rvecs, pe_dist_proj, proj_angle1,
+                proj_angle2, proj_angle3, alpha, params, this_epoch)
+        else:
+            # models/indexed_lattice_multi_head_attention_cuda.py:550-566: logit bias only, no value encoding
+            attn_weights = ReciPeriodicEncodingFuncCUDA.apply(alpha, kr_base, rvecs, vcell, batch_q, edges)
     if not training:
         dropout_p = 0.0
     out, _, _ = _scaled_dot_product_attention(q, k, v, batch_q, batch_kv, edges, attn_weights, values, dropout_p)
@@ -210,7 +224,10 @@ class CrystalformerMultiheadAttentionCUDA(Module):
                  params=LatticeformerParams(), device=None, dtype=None) -> None:
         kw = {"device": device, "dtype": dtype}
         super().__init__()
-        if params.domain not in ("real", "no"):
+        if params.domain not in ("real", "reci", "RECI", "no"):
+            # "multihead": the reference's CUDA module hands queries of all heads and coefficients of half of
+            # them to its frame kernels (models/indexed_lattice_multi_head_attention_cuda.py:953-963); its README
+            # (:157) limits CrystalFramer to the real domain.  Not built.
             raise NotImplementedError(f"domain={params.domain}")
         self.embed_dim = embed_dim
         self.kdim = kdim * num_heads if kdim is not None and kdim > 0 else embed_dim
@@ -232,6 +249,13 @@ class CrystalformerMultiheadAttentionCUDA(Module):
         self.out_proj = NonDynamicallyQuantizableLinear(self.vdim, embed_dim, bias=bias, **kw)
         self.lattice_pos_weights = None
         self.pe_dist_proj = self.pe_wave_proj = self.proj_angle1 = self.proj_angle2 = self.proj_angle3 = None
+        if params.domain in ("reci", "RECI"):
+            # models/indexed_lattice_multi_head_attention_cuda.py:1100-1107
+            if not params.gauss_state.startswith("q"):
+                raise NotImplementedError(f"gauss_state={params.gauss_state}")
+            if params.value_pe_dist_reci > 0 or params.value_pe_wave_reci > 0:
+                raise NotImplementedError("value encodings of the reciprocal domain")
+            self.lattice_pos_weights = Parameter(torch.empty(self.kdim, **kw))
         if params.domain == "real":
             if not params.gauss_state.startswith("q"):
                 raise NotImplementedError(f"gauss_state={params.gauss_state}")

@@ -12,6 +12,7 @@
 #include "pool_index.cu"
 #include "coef.cu"
 #include "sigma.cu"
+#include "reci.cu"
 #include "attn_fused.cu"
 #include "optim.cu"
 #include "linear.cu"
@@ -450,6 +451,34 @@ int cfb200_proj_fwd(const float* a_ik, const float* pos_ij, const float* tvecs, 
     if (values != nullptr && W_dist == nullptr) return CFB200_E_NULL;
     A.z = z; A.values = values;
     return cfb::framed_proj_fwd(A, P, S(stream));
+}
+
+int cfb200_reci_enc_fwd(const float* a_ik, const float* kr_base, const float* rvecs, const float* vcell,
+                        const int64_t* batch, const int64_t* e_start, int64_t N, int64_t H, int64_t E, float* z,
+                        float* sumexp, void* stream)
+{
+    if (!g_configured) return CFB200_E_NOT_CONFIGURED;
+    if (N < 0 || E < 0 || H < 1 || N > INT32_MAX) return CFB200_E_SHAPE;
+    if (N > 0 && (!a_ik || !rvecs || !vcell || !batch || !e_start)) return CFB200_E_NULL;
+    if (E > 0 && (!kr_base || !z || !sumexp)) return CFB200_E_NULL;
+    cfb::ReciArgs A{};
+    A.a = a_ik; A.kr = kr_base; A.rvecs = rvecs; A.vcell = vcell; A.batch = batch; A.e_start = e_start;
+    A.z = z; A.sumexp = sumexp; A.N = (int)N; A.H = (int)H; A.R = g_cfg.lattice_range;
+    return cfb::reci_enc(A, false, S(stream));
+}
+
+int cfb200_reci_enc_bwd(const float* a_ik, const float* kr_base, const float* rvecs, const int64_t* batch,
+                        const int64_t* e_start, const float* gz, const float* sumexp, int64_t N, int64_t H,
+                        int64_t E, float* ga, void* stream)
+{
+    if (!g_configured) return CFB200_E_NOT_CONFIGURED;
+    if (N < 0 || E < 0 || H < 1 || N > INT32_MAX) return CFB200_E_SHAPE;
+    if (N > 0 && (!a_ik || !rvecs || !batch || !e_start || !ga)) return CFB200_E_NULL;
+    if (E > 0 && (!kr_base || !gz || !sumexp)) return CFB200_E_NULL;
+    cfb::ReciArgs A{};
+    A.a = a_ik; A.kr = kr_base; A.rvecs = rvecs; A.batch = batch; A.e_start = e_start;
+    A.gz = gz; A.sumexp_in = sumexp; A.ga = ga; A.N = (int)N; A.H = (int)H; A.R = g_cfg.lattice_range;
+    return cfb::reci_enc(A, true, S(stream));
 }
 
 int cfb200_proj_bwd(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,

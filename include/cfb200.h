@@ -220,6 +220,22 @@ int cfb200_framed_proj_bwd(const float* a_ik, const float* pos_ij, const float* 
                            float* gW_ang1, float* gW_ang2, float* gW_ang3, void* workspace,
                            int64_t workspace_bytes, void* stream);
 
+/* Replaces ReciPeriodicEncodingFuncCUDA (models/cuda_funcs/reci_space_enc.py:17-97; kernels
+ * reci_enc_fwd.cu, reci_enc_bwd.cu): the reciprocal-space lattice sum of the plain Crystalformer's
+ * "reci" / "multihead" domains over n1 in [0, lattice_range], n2, n3 in [-lattice_range, lattice_range]
+ * (lattice_range <= 3, CFB200_E_UNSUPPORTED above).  a_ik (N,H) must be negative; kr_base (E,3) =
+ * rvecs[crystal] @ (pos_j - pos_i); rvecs (B,3,3) reciprocal vectors in rows; vcell (B) cell volumes;
+ * e_start (N+1) CSR offsets of the pairs of each atom (pairs sorted by their first atom).  H is the number of
+ * heads of a_ik (any H >= 1; the "multihead" domain passes half of the configured heads).
+ * Forward: z (E,H) = log(max(sum, 1e-6)) + 1.5 log(-4 pi a) - log(vcell), sumexp (E,H) = sum.
+ * Backward: ga (N,H) from gz (E,H) and the forward's sumexp. */
+int cfb200_reci_enc_fwd(const float* a_ik, const float* kr_base, const float* rvecs, const float* vcell,
+                        const int64_t* batch, const int64_t* e_start, int64_t N, int64_t H, int64_t E,
+                        float* z, float* sumexp, void* stream);
+int cfb200_reci_enc_bwd(const float* a_ik, const float* kr_base, const float* rvecs, const int64_t* batch,
+                        const int64_t* e_start, const float* gz, const float* sumexp, int64_t N,
+                        int64_t H, int64_t E, float* ga, void* stream);
+
 /* Replaces RealPeriodicEncodingWithProjFuncCUDA with frame_method "no"
  * (models/cuda_funcs/real_space_enc_proj.py:21-213; kernels real_enc_proj_fwd.cu,
  * real_enc_proj_bwd.cu): the plain Crystalformer encoding -- lattice-sum bias z (E,H) and the

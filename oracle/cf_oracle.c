@@ -817,3 +817,79 @@ void FN(cfo_mean_bwd)(const real* gout /* (B,D) */, const int64_t* start, int64_
         for (int64_t i = start[c]; i < start[c + 1]; i++)
             for (int64_t d = 0; d < D; d++) gx[i * D + d] = gout[c * D + d] / (real)(start[c + 1] - start[c]);
 }
+
+/* --------------------------------------------------------------------------
+ * Reciprocal-space lattice sum and its gradient:
+ *   models/kernels/reci_enc_fwd.cu:17-67, models/kernels/reci_enc_bwd.cu:19-70,
+ *   models/cuda_funcs/reci_space_enc.py:19-62 (forward), :64-97 (backward).
+ *   sum_ek = sum_n w(n1) exp(a_ik |n G|^2) cos(n . kr_e),  n1 in [0,R] (w = 1 at 0, else 2: the
+ *            summand is even in n), n2, n3 in [-R,R], G the rows of rvecs (reciprocal vectors);
+ *   z_ek   = log(max(sum, 1e-6)) + 1.5 log(-4 pi a) - log(vcell);
+ *   ga_ik  = sum_e gz_ek (sum < 1e-6 ? 0 : 1/sum) sum_n w |nG|^2 exp(a |nG|^2) cos(n . kr)
+ * (the reference's gradient leaves out the term of the normaliser, which is the same for every pair of
+ * an (atom, head) and cancels in the softmax that consumes z).
+ * -------------------------------------------------------------------------- */
+#ifdef REAL_IS_DOUBLE
+#define R_COS cos
+#else
+#define R_COS cosf
+#endif
+
+void FN(cfo_reci_enc_fwd)(const real* a_ik, const real* kr /* (E,3) */, const real* rvecs /* (B,3,3) */,
+                          const real* vcell /* (B) */, const int64_t* batch, const int64_t* edges, int64_t N,
+                          int64_t H, int64_t E, int R, real* z /* (E,H) */, real* sumexp /* (E,H) */)
+{
+    (void)N;
+    for (int64_t e = 0; e < E; e++) {
+        const int64_t i = edges[e], c = batch[i];
+        const real* g = rvecs + c * 9;
+        for (int64_t h = 0; h < H; h++) {
+            const real a = a_ik[i * H + h];
+            real sum = 0;
+            for (int n1 = 0; n1 <= R; n1++) {
+                const real w = n1 == 0 ? (real)1 : (real)2;
+                for (int n2 = -R; n2 <= R; n2++)
+                    for (int n3 = -R; n3 <= R; n3++) {
+                        const real k1 = g[0] * n1 + g[3] * n2 + g[6] * n3;
+                        const real k2 = g[1] * n1 + g[4] * n2 + g[7] * n3;
+                        const real k3 = g[2] * n1 + g[5] * n2 + g[8] * n3;
+                        const real ex = R_EXP(a * (k1 * k1 + k2 * k2 + k3 * k3));
+                        sum += ex * R_COS(kr[e * 3] * n1 + kr[e * 3 + 1] * n2 + kr[e * 3 + 2] * n3) * w;
+                    }
+            }
+            const real four_pi = (real)12.5663706144;
+            z[e * H + h] = R_LOG(R_FMAX(sum, (real)1e-6)) + (real)1.5 * R_LOG(-four_pi * a) - R_LOG(vcell[c]);
+            sumexp[e * H + h] = sum;
+        }
+    }
+}
+
+void FN(cfo_reci_enc_bwd)(const real* a_ik, const real* kr, const real* rvecs, const int64_t* batch,
+                          const int64_t* e_start /* (N+1) */, const real* gz, const real* sumexp, int64_t N,
+                          int64_t H, int R, real* ga /* (N,H) */)
+{
+    for (int64_t i = 0; i < N; i++) {
+        const real* g = rvecs + batch[i] * 9;
+        for (int64_t h = 0; h < H; h++) {
+            const real a = a_ik[i * H + h];
+            real total = 0;
+            for (int64_t e = e_start[i]; e < e_start[i + 1]; e++) {
+                real s = 0;
+                for (int n1 = 0; n1 <= R; n1++) {
+                    const real w = n1 == 0 ? (real)1 : (real)2;
+                    for (int n2 = -R; n2 <= R; n2++)
+                        for (int n3 = -R; n3 <= R; n3++) {
+                            const real k1 = g[0] * n1 + g[3] * n2 + g[6] * n3;
+                            const real k2 = g[1] * n1 + g[4] * n2 + g[7] * n3;
+                            const real k3 = g[2] * n1 + g[5] * n2 + g[8] * n3;
+                            const real kk = k1 * k1 + k2 * k2 + k3 * k3;
+                            s += kk * R_EXP(a * kk) * R_COS(kr[e * 3] * n1 + kr[e * 3 + 1] * n2 + kr[e * 3 + 2] * n3) * w;
+                        }
+                }
+                const real se = sumexp[e * H + h];
+                total += s * gz[e * H + h] * (se < (real)1e-6 ? (real)0 : (real)1 / se);
+            }
+            ga[i * H + h] = total;
+        }
+    }
+}

@@ -50,7 +50,12 @@ def coefficients(attn, q):
                     attn.gauss_scale[0] = scale
                     attn.gauss_scale[1] = shift
         alpha = (alpha + shift) * scale
-    lb, beta = P.gauss_lb_real, P.positive_func_beta
+    beta = P.positive_func_beta
+    if P.domain in ("reci", "RECI"):          # :946-952
+        lb = P.gauss_lb_reci
+        pos = (1.0 - lb) * F.elu(alpha * (beta / (1.0 - lb))) + 1.0
+        return (1 / pos if P.domain == "RECI" else pos) * (-0.5 * P.scale_reci ** 2)
+    lb = P.gauss_lb_real
     return ((1.0 - lb) * F.elu(alpha * (beta / (1.0 - lb))) + 1.0) * (-0.5 * P.scale_real ** -2)
 
 
@@ -80,6 +85,11 @@ def attention_layer(attn, x, geo, cfg, frames=None):
     a = coefficients(attn, q)
     cutoff = attn.params.adaptive_cutoff_sigma
     qs = q / math.sqrt(hd)
+    if attn.params.domain in ("reci", "RECI"):
+        # reciprocal-space logit bias, no value encoding (:550-566)
+        z = OF.Reci.apply(a, geo["kr"], geo["rvecs"], geo["vcell"], geo["batch"], geo["edges"], cfg.lattice_range)
+        out = OF.Attention.apply(qs, k, v, z, torch.zeros((z.shape[0], H, hd), dtype=q.dtype, device=q.device), geo["batch"], geo["edges"])
+        return F.linear(out.reshape(N, H * hd), attn.out_proj.weight, attn.out_proj.bias)
     method = attn.params.frame_method
     if method == "no":
         f1 = f2 = f3 = None
@@ -133,6 +143,9 @@ def forward(model, batch, backend=None, frames=None):
     t = lambda arr: torch.from_numpy(np.ascontiguousarray(arr)).to(dev)
     geo = dict(pos_ij=t(g["pos_ij"]), tvecs=t(batch.trans_vec), batch=t(g["batch"]), edges=t(g["edges"]),
                rvlen=t(g["rvlen"]))
+    if any(d in ("reci", "RECI") for d in model.encoder.lattice_params.domain.split("-")):
+        rvecs, vcell, kr = O.reciprocal_geometry(batch.pos, batch.trans_vec, batch.sizes, g["edges"])
+        geo.update(rvecs=t(rvecs), vcell=t(vcell), kr=t(kr))
     sizes = t(batch.sizes)
     x = model.input_embeddings(t(batch.x))
     for li, layer in enumerate(model.encoder.layers):

@@ -129,6 +129,32 @@ class Attention(torch.autograd.Function):
         return g[0], g[1], g[2], g[3], g[4], None, None
 
 
+class Reci(torch.autograd.Function):
+    """models/cuda_funcs/reci_space_enc.py:17-97"""
+
+    @staticmethod
+    def forward(ctx, a, kr, rvecs, vcell, batch, edges, lattice_range):
+        a_ = a.detach().contiguous()
+        if _state["backend"] == "reference":
+            z, sumexp = _state["rk"].reci_fwd(a_, kr, rvecs, vcell, batch, edges)
+        else:
+            z, sumexp = (torch.from_numpy(x) for x in O.reci_enc_fwd(_np(a_), _np(kr), _np(rvecs), _np(vcell), _np(batch),
+                                                                     _np(edges), lattice_range))
+        ctx.save_for_backward(a_, kr, rvecs, vcell, batch, edges, z, sumexp)
+        ctx.lattice_range = lattice_range
+        return z
+
+    @staticmethod
+    def backward(ctx, gz):
+        a, kr, rvecs, vcell, batch, edges, z, sumexp = ctx.saved_tensors
+        if _state["backend"] == "reference":
+            ga = _state["rk"].reci_bwd(a, kr, rvecs, vcell, batch, edges, z, gz.contiguous(), sumexp)
+        else:
+            ga = torch.from_numpy(O.reci_enc_bwd(_np(a), _np(kr), _np(rvecs), _np(batch), _np(edges), _np(gz), _np(sumexp),
+                                                 ctx.lattice_range))
+        return ga, None, None, None, None, None, None
+
+
 class Mean(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, sizes):

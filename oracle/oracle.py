@@ -338,6 +338,49 @@ def mean_bwd(gout, sizes, dtype=np.float32):
     return gx
 
 
+def reciprocal_geometry(pos, cells, sizes, edges):
+    """Reciprocal vectors, cell volumes and the phase base of every pair
+    (models/indexed_latticeformer_encoder.py:198-205, :239-243): rvecs (B,3,3) = 2 pi cross / vcell,
+    kr (E,3) = rvecs[crystal of i] @ (pos_j - pos_i)."""
+    cells = np.asarray(cells, np.float32)
+    pos = np.asarray(pos, np.float32)
+    vcell = np.einsum("bi,bi->b", cells[:, 0], np.cross(cells[:, 1], cells[:, 2])).astype(np.float32)
+    rvecs = np.stack([np.cross(cells[:, 1], cells[:, 2]), np.cross(cells[:, 2], cells[:, 0]),
+                      np.cross(cells[:, 0], cells[:, 1])], axis=1).astype(np.float32)
+    rvecs = (rvecs * (np.float32(2.0 * math.pi) / vcell)[:, None, None]).astype(np.float32)
+    batch = np.repeat(np.arange(len(sizes)), np.asarray(sizes))
+    pos_ij = pos[edges[1]] - pos[edges[0]]
+    kr = np.einsum("eij,ej->ei", rvecs[batch[edges[0]]], pos_ij).astype(np.float32)
+    return rvecs, vcell, kr
+
+
+def reci_enc_fwd(a_ik, kr, rvecs, vcell, batch, edges, lattice_range=2, dtype=np.float32):
+    """models/cuda_funcs/reci_space_enc.py:19-62: (z (E,H), sumexp (E,H))."""
+    a_ik = _r(a_ik, dtype)
+    N, H = a_ik.shape
+    edges = _i64(edges)
+    E = edges.shape[1]
+    z = np.empty((E, H), dtype)
+    sumexp = np.empty((E, H), dtype)
+    _fn("cfo_reci_enc_fwd", dtype)(_p(a_ik), _p(_r(kr, dtype)), _p(_r(rvecs, dtype)), _p(_r(vcell, dtype)),
+                                   _p(_i64(batch)), _p(edges), ctypes.c_int64(N), ctypes.c_int64(H), ctypes.c_int64(E),
+                                   ctypes.c_int(lattice_range), _p(z), _p(sumexp))
+    return z, sumexp
+
+
+def reci_enc_bwd(a_ik, kr, rvecs, batch, edges, gz, sumexp, lattice_range=2, dtype=np.float32):
+    """models/cuda_funcs/reci_space_enc.py:64-97: ga (N,H)."""
+    a_ik = _r(a_ik, dtype)
+    N, H = a_ik.shape
+    edges = _i64(edges)
+    e_start = np.concatenate([[0], np.cumsum(np.bincount(edges[0], minlength=N))]).astype(np.int64)
+    ga = np.empty((N, H), dtype)
+    _fn("cfo_reci_enc_bwd", dtype)(_p(a_ik), _p(_r(kr, dtype)), _p(_r(rvecs, dtype)), _p(_i64(batch)), _p(e_start),
+                                   _p(_r(gz, dtype)), _p(_r(sumexp, dtype)), ctypes.c_int64(N), ctypes.c_int64(H),
+                                   ctypes.c_int(lattice_range), _p(ga))
+    return ga
+
+
 # ---------------------------------------------------------------------------------------------
 # Weighted-PCA frames (models/indexed_lattice_multi_head_attention_cuda.py:620-725)
 # ---------------------------------------------------------------------------------------------

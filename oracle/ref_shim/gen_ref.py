@@ -35,6 +35,7 @@ KERNELS = [
     "real_enc_sigma_fwd", "fused_dpa_sigmamat_fwd",
     "compute_second_frame_static_each_edge",
     "compute_lattice_first_frame", "compute_lattice_second_frame", "compute_lattice_third_frame",
+    "reci_enc_fwd", "reci_enc_bwd",
 ]
 
 
@@ -108,7 +109,7 @@ def build(reference_root, force=False, consts=None, tag=""):
     cpu_lib = os.path.join(OUT, f"libcfref_cpu{tag}.so")
     gpu_lib = os.path.join(OUT, f"libcfref_gpu{tag}.so")
     sig_json = os.path.join(OUT, f"signatures{tag}.json")
-    stamp = json.dumps(consts, sort_keys=True)
+    stamp = json.dumps(dict(consts, _kernels=" ".join(KERNELS)), sort_keys=True)
     if (not force and os.path.exists(cpu_lib) and os.path.exists(sig_json)
             and json.load(open(sig_json)).get("_consts") == stamp):
         return

@@ -158,6 +158,23 @@ class RefKernels:
                     gz.contiguous(), gv.contiguous(), N, H, E, dist_max, wscale, W_k, 1, rvlen, cutoff, ga, gW)
         return ga, gW.sum(dim=0)
 
+    # ---- models/cuda_funcs/reci_space_enc.py:17-97 -----------------------------------------
+    def reci_fwd(self, a_ik, kr, rvecs, vcell, batch, edges):
+        N, H = a_ik.shape
+        E = edges.shape[1]
+        z = torch.empty((E, H), device=a_ik.device, dtype=a_ik.dtype)
+        sumexp = torch.empty_like(z)
+        self.launch("reci_enc_fwd", (E * H + H - 1) // H, H, a_ik, kr, rvecs, vcell, batch, edges, N, H, E, z, sumexp)
+        return z, sumexp
+
+    def reci_bwd(self, a_ik, kr, rvecs, vcell, batch, edges, z, gz, sumexp):
+        N, H = a_ik.shape
+        E = edges.shape[1]
+        ga = torch.empty_like(a_ik)
+        self.launch("reci_enc_bwd", (N * H + H - 1) // H, H, a_ik, kr, rvecs, vcell, batch, edges,
+                    self.e_start(edges, N), z, gz.contiguous(), sumexp, N, H, E, ga)
+        return ga
+
     # ---- weighted PCA: models/cuda_funcs/real_space_enc_proj.py:80-125, fused_dpa_sigmamat.py ----
     def sigma_fwd(self, a_ik, rpos, tvecs, batch, edges, rvlen, cutoff, seed=0):
         N, H = a_ik.shape

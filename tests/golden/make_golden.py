@@ -15,6 +15,10 @@ here on small seeded inputs and the inputs and outputs are committed:
   _scaled_dot_product_attention; models/indexed_latticeformer_encoder.py: compute_lattice_distances)
   imported with stub modules for its missing GPU-only dependencies: fixed lattice range 2,
   un-windowed distance Gaussians, no frames.
+* ``ref_reci_small.npz`` -- the reciprocal-space encoding: reciprocal vectors, volumes and phase bases from the
+  reference's compute_lattice_distances_for_cuda, z / sumexp / ga from its reci_enc kernels (CPU build), and z and
+  the gradient of the lattice sum from its pure-PyTorch twin (compute_reci_domain_attn with cos_kr, k2 from
+  compute_lattice_distances).
 """
 import os
 import sys
@@ -94,7 +98,7 @@ def kernels_fixture(path):
         lattice_frame3=lat[2].numpy())
 
 
-def pure_fixture(path, ref_root):
+def _import_reference_models(ref_root):
     for name in ("torch_scatter", "cupy", "pytorch_pfn_extras"):
         sys.modules.setdefault(name, types.ModuleType(name))
     cr = types.ModuleType("cupy.random")
@@ -109,6 +113,39 @@ def pure_fixture(path, ref_root):
         from models import indexed_latticeformer_encoder as enc
     finally:
         os.chdir(cwd)
+    return pure, enc
+
+
+def reci_fixture(path, ref_root):
+    pure, enc = _import_reference_models(ref_root)
+    P = small_problem()
+    T = lambda x: torch.from_numpy(np.ascontiguousarray(x))
+    sizes = T(P["sizes"])
+    batch = torch.repeat_interleave(torch.arange(len(sizes)), sizes)
+    pos, cells = T(P["pos"]), T(P["cells"])
+    _, _, kr, rvecs, vcell, edges = enc.compute_lattice_distances_for_cuda(pos, batch, cells, sizes, 2, -3.5, True, True)
+    a = T(P["a"] * 8.0)                    # the reci domain's coefficients are -0.5 scale_reci^2 f: larger than real-space ones
+    rk = R.RefKernels("cpu")
+    z, sumexp = rk.reci_fwd(a, kr, rvecs, vcell, batch, edges)
+    rng = np.random.default_rng(11)
+    gz = T(rng.normal(size=tuple(z.shape)).astype(np.float32))
+    ga = rk.reci_bwd(a, kr, rvecs, vcell, batch, edges, z, gz, sumexp)
+    _, cos_kr, k2, vcell_p, _, edges_p, _ = enc.compute_lattice_distances(pos, batch, cells, sizes, 2, output_dis=False,
+                                                                          output_rec=True)
+    assert torch.equal(edges_p, edges)
+    ap = a.clone().requires_grad_(True)
+    z_pure = pure.compute_reci_domain_attn(ap, cos_kr, k2, vcell_p, edges[0], batch)
+    (z_pure * gz).sum().backward()
+    # the kernels leave out the gradient of the normaliser 1.5 log(-4 pi a), which is 1.5 / a per pair
+    gsum = torch.zeros_like(a).index_add_(0, edges[0], gz)
+    ga_pure = ap.grad - 1.5 / a * gsum
+    np.savez_compressed(path, a=a.numpy(), kr=kr.numpy(), rvecs=rvecs.numpy(), vcell=vcell.numpy(), edges=edges.numpy(),
+                        z=z.numpy(), sumexp=sumexp.numpy(), gz=gz.numpy(), ga=ga.numpy(), z_pure=z_pure.detach().numpy(),
+                        ga_pure=ga_pure.numpy())
+
+
+def pure_fixture(path, ref_root):
+    pure, enc = _import_reference_models(ref_root)
     P = small_problem()
     T = lambda x: torch.from_numpy(np.ascontiguousarray(x))
     sizes = T(P["sizes"])
@@ -131,4 +168,5 @@ if __name__ == "__main__":
         raise SystemExit("reference tree not found: pass its root or set CF_REFERENCE_ROOT")
     kernels_fixture(os.path.join(HERE, "ref_kernels_small.npz"))
     pure_fixture(os.path.join(HERE, "ref_pure_small.npz"), ref_root)
+    reci_fixture(os.path.join(HERE, "ref_reci_small.npz"), ref_root)
     print("fixtures written")

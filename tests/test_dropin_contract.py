@@ -37,6 +37,7 @@ FUNCTIONS = {
     "fused_dpa.py": ["FusedDotProductAttentionCUDA"],
     "fused_dpa_sigmamat.py": ["FusedDotProductAttentionSigmaMatCUDA"],
     "irregular_mean.py": ["IrregularMeanCUDA"],
+    "reci_space_enc.py": ["ReciPeriodicEncodingFuncCUDA"],
 }
 
 

@@ -331,6 +331,90 @@ def test_whole_model_lightweight_recipe(fused):
                        value_pe_angle_coef=6.0)
 
 
+@pytest.mark.parametrize("domain,frame_method", [("real-reci", "max"), ("RECI", "no"), ("reci", "no")])
+def test_whole_model_reciprocal_domains(domain, frame_method):
+    """Layers with the reciprocal-space logit bias (alone, inverted, and alternating with CrystalFramer layers)
+    in the whole model against the CPU oracle."""
+    _whole_model_check(2, frame_method, False, domain=domain)
+
+
+def _reciprocal_inputs(P, scale, H=None):
+    from oracle import oracle as O
+    geo, b = P["geo"], P["batch"]
+    rvecs, vcell, kr = O.reciprocal_geometry(b.pos, b.trans_vec, b.sizes, geo["edges"])
+    a = (P["a"] * scale).astype(np.float32)
+    if H is not None:
+        a = np.ascontiguousarray(np.tile(a, (1, 2))[:, :H] * np.linspace(0.7, 1.3, H, dtype=np.float32))
+    return a, kr, rvecs, vcell
+
+
+@pytest.mark.parametrize("H", [8, 4, 12])
+def test_reciprocal_encoding(H):
+    """cfb200_reci_enc_fwd / _bwd through the drop-in Function against the oracle (float32, and float64 as the
+    judge of disagreements) on 24 crystals, for the configured head count, the half the "multihead" domain would
+    pass, and one that needs two passes over the pairs.  The logit is compared where the lattice sum is not
+    rounding noise (sum > 1e-3: below, log() amplifies the last bits of a sum of 75 terms of order one), the sum
+    itself everywhere; the upstream gradient is zero on those pairs so that the coefficient gradient is
+    well-conditioned too."""
+    dev = _cuda()
+    from oracle import oracle as O
+    F = _configure()
+    P = make_problem("cfg2", num_crystals=24)
+    g = _geometry(P, dev)
+    a, kr, rvecs, vcell = _reciprocal_inputs(P, 9.5, H)
+    at = _t(a, dev).requires_grad_(True)
+    z = F.ReciPeriodicEncodingFuncCUDA.apply(at, _t(kr, dev), _t(rvecs, dev), _t(vcell, dev), g["batch"], g["edges"])
+    zo, so = O.reci_enc_fwd(a, kr, rvecs, vcell, P["geo"]["batch"], P["geo"]["edges"])
+    z64, s64 = O.reci_enc_fwd(a, kr, rvecs, vcell, P["geo"]["batch"], P["geo"]["edges"], dtype=np.float64)
+    ok = s64 > 1e-3
+    assert ok.mean() > 0.5
+    _close("z", z.detach().cpu().numpy()[ok], zo[ok], 1e-4, 1e-4)
+    got_sum = np.exp(z.detach().cpu().numpy().astype(np.float64)
+                     - (1.5 * np.log(-4 * np.pi * a.astype(np.float64)) - np.log(vcell.astype(np.float64))[P["geo"]["batch"], None])[P["geo"]["edges"][0]])
+    assert np.abs(got_sum - np.maximum(s64, 1e-6))[ok].max() <= 3 * np.abs(so - s64)[ok].max() + 1e-5
+    gz = (np.random.default_rng(5).normal(size=zo.shape) * (s64 > 1e-2)).astype(np.float32)
+    z.backward(_t(gz, dev))
+    gao = O.reci_enc_bwd(a, kr, rvecs, P["geo"]["batch"], P["geo"]["edges"], gz, so)
+    ga64 = O.reci_enc_bwd(a, kr, rvecs, P["geo"]["batch"], P["geo"]["edges"], gz, s64, dtype=np.float64)
+    _close_reduction("ga", at.grad.cpu().numpy(), gao, ga64)
+
+
+def test_reciprocal_encoding_golden_and_reference_gpu():
+    """The reciprocal encoding against the committed outputs of the reference's kernels and of its pure-PyTorch
+    twin, and -- where the reference kernels' GPU build is present -- against those kernels on the same GPU."""
+    import os
+    dev = _cuda()
+    F = _configure()
+    G = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_reci_small.npz"))
+    small = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_kernels_small.npz"))
+    batch = _t(np.repeat(np.arange(len(small["sizes"])), small["sizes"]), dev)
+    at = _t(G["a"], dev).requires_grad_(True)
+    args = (_t(G["kr"], dev), _t(G["rvecs"], dev), _t(G["vcell"], dev), batch, _t(G["edges"], dev))
+    z = F.ReciPeriodicEncodingFuncCUDA.apply(at, *args)
+    _close("z", z.detach().cpu().numpy(), G["z"], 1e-5, 1e-5)
+    _close("z (pure twin)", z.detach().cpu().numpy(), G["z_pure"], 1e-4, 1e-5)
+    z.backward(_t(G["gz"], dev))
+    _close("ga", at.grad.cpu().numpy(), G["ga"], 1e-4, 1e-4)
+    _close("ga (pure twin)", at.grad.cpu().numpy(), G["ga_pure"], 1e-4, 1e-4)
+    from oracle import reference as R
+    if not R.available("cuda"):
+        return
+    P = make_problem("cfg2", num_crystals=24)
+    g = _geometry(P, dev)
+    a, kr, rvecs, vcell = _reciprocal_inputs(P, 9.5)
+    rk = R.RefKernels("cuda")
+    at = _t(a, dev).requires_grad_(True)
+    targs = (_t(kr, dev), _t(rvecs, dev), _t(vcell, dev), g["batch"], g["edges"])
+    z = F.ReciPeriodicEncodingFuncCUDA.apply(at, *targs)
+    zr, sr = rk.reci_fwd(at.detach(), *targs)
+    ok = (sr > 1e-3).cpu().numpy()
+    _close("z vs reference kernels", z.detach().cpu().numpy()[ok], zr.cpu().numpy()[ok], 1e-4, 1e-4)
+    gz = (torch.randn_like(zr) * (sr > 1e-2)).contiguous()
+    z.backward(gz)
+    gar = rk.reci_bwd(at.detach(), *targs, zr, gz, sr)
+    _close("ga vs reference kernels", at.grad.cpu().numpy(), gar.cpu().numpy(), 1e-4, 1e-5 * max(1.0, float(gar.abs().max())))
+
+
 def _whole_model_check(layers, frame_method, fused, **recipe):
     """Forward and backward of the whole model (species embedding, encoder layers, mean pooling,
     MLP head) on the GPU against the same weights run on the host cores through the oracle:

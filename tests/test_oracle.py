@@ -368,3 +368,51 @@ def test_pca_frames_are_principal_axes():
     r5 = g["pos_ij"][e0:e1].astype(np.float64)
     d = r5 - r5.mean(0)
     assert np.allclose(mats[5], d.T @ d)
+
+
+def test_golden_reciprocal_encoding():
+    """Reciprocal-space lattice sum: the oracle against the reference's reci_enc kernels and against its
+    pure-PyTorch twin, on the committed fixture (geometry from the reference's own host code)."""
+    G = np.load(os.path.join(GOLD, "ref_reci_small.npz"))
+    small = np.load(os.path.join(GOLD, "ref_kernels_small.npz"))
+    rvecs, vcell, kr = O.reciprocal_geometry(small["pos"], small["cells"], small["sizes"], G["edges"])
+    close("rvecs", rvecs, G["rvecs"], 1e-6, 1e-7)
+    close("vcell", vcell, G["vcell"], 1e-6, 1e-6)
+    close("kr", kr, G["kr"], 1e-5, 1e-6)
+    batch = np.repeat(np.arange(len(small["sizes"])), small["sizes"])
+    z, sumexp = O.reci_enc_fwd(G["a"], G["kr"], G["rvecs"], G["vcell"], batch, G["edges"])
+    close("sumexp", sumexp, G["sumexp"], 1e-5, 1e-6)
+    close("z", z, G["z"], 1e-5, 1e-5)
+    close("z (pure twin)", z, G["z_pure"], 1e-4, 1e-5)
+    ga = O.reci_enc_bwd(G["a"], G["kr"], G["rvecs"], batch, G["edges"], G["gz"], G["sumexp"])
+    close("ga", ga, G["ga"], 1e-5, 1e-5)
+    close("ga (pure twin)", ga, G["ga_pure"], 1e-4, 1e-4)
+    # the double build's sum differentiates to the double build's gradient
+    a64 = G["a"].astype(np.float64)
+    z64, s64 = O.reci_enc_fwd(a64, G["kr"], G["rvecs"], G["vcell"], batch, G["edges"], dtype=np.float64)
+    ga64 = O.reci_enc_bwd(a64, G["kr"], G["rvecs"], batch, G["edges"], G["gz"], s64, dtype=np.float64)
+    h = 1e-6
+    _, sp = O.reci_enc_fwd(a64 + h, G["kr"], G["rvecs"], G["vcell"], batch, G["edges"], dtype=np.float64)
+    _, sm = O.reci_enc_fwd(a64 - h, G["kr"], G["rvecs"], G["vcell"], batch, G["edges"], dtype=np.float64)
+    fd = np.zeros_like(a64)
+    np.add.at(fd, G["edges"][0], G["gz"] * (np.log(sp) - np.log(sm)) / (2 * h))
+    close("ga (finite differences)", ga64, fd, 1e-6, 1e-6)
+
+
+@pytest.mark.skipif(not R.available("cpu"), reason="oracle/_ref not built (reference tree absent)")
+def test_reciprocal_encoding_against_reference_cpu_build(problem_cfg1):
+    P = problem_cfg1
+    geo, b = P["geo"], P["batch"]
+    rvecs, vcell, kr = O.reciprocal_geometry(b.pos, b.trans_vec, b.sizes, geo["edges"])
+    a = (P["a"] * 9.5).astype(np.float32)              # -0.5 scale_reci^2 f against -0.5 scale_real^-2 f
+    rk = R.RefKernels("cpu")
+    T = lambda x: torch.from_numpy(np.ascontiguousarray(x))
+    z, sumexp = rk.reci_fwd(T(a), T(kr), T(rvecs), T(vcell), T(geo["batch"]), T(geo["edges"]))
+    zo, so = O.reci_enc_fwd(a, kr, rvecs, vcell, geo["batch"], geo["edges"])
+    close("sumexp", so, sumexp.numpy(), 1e-5, 1e-6)
+    ok = sumexp.numpy() > 1e-3
+    close("z", zo[ok], z.numpy()[ok], 1e-5, 1e-5)
+    gz = np.random.default_rng(3).normal(size=zo.shape).astype(np.float32)
+    ga = rk.reci_bwd(T(a), T(kr), T(rvecs), T(vcell), T(geo["batch"]), T(geo["edges"]), z, T(gz), sumexp)
+    gao = O.reci_enc_bwd(a, kr, rvecs, geo["batch"], geo["edges"], gz, sumexp.numpy())
+    close("ga", gao, ga.numpy(), 1e-4, 1e-5 * max(1.0, float(ga.abs().max())))
