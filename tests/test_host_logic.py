@@ -84,7 +84,8 @@ def _worker(rank, world, port, q):
     avg = torch.cat([p.grad.flatten() for p in model.parameters()])
     gathered = [torch.zeros_like(local) for _ in range(world)]
     dist.all_gather(gathered, local)
-    q.put((rank, w0, avg, torch.stack(gathered).mean(0)))
+    # numpy arrays travel by value; a tensor would travel as a shared-memory handle that dies with this process
+    q.put((rank, w0.numpy(), avg.numpy(), torch.stack(gathered).mean(0).numpy()))
     dist.destroy_process_group()
 
 
@@ -96,6 +97,7 @@ def test_gradient_allreduce_two_ranks_gloo():
     for p in procs:
         p.start()
     res = sorted([q.get(timeout=120) for _ in procs], key=lambda t: t[0])
+    res = [(r,) + tuple(torch.from_numpy(x) for x in rest) for r, *rest in res]
     for p in procs:
         p.join(60)
     (_, w_a, g_a, m_a), (_, w_b, g_b, m_b) = res
