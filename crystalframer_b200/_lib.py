@@ -77,6 +77,7 @@ SIGNATURES = {
     "cfb200_sigma_frames": (ctypes.c_int, [vp] * 9 + [i64, i64, f32, u64, u64] + [vp] * 4 + [i64, vp]),
     "cfb200_framed_proj_fwd": (ctypes.c_int, [vp] * 6 + [i64, i64, f32, f32] + [vp] * 10),
     "cfb200_framed_proj_bwd": (ctypes.c_int, [vp] * 7 + [i64, i64, f32, f32] + [vp] * 16 + [i64, vp]),
+    "cfb200_deal_by_cost": (ctypes.c_int, [vp, i64, ctypes.c_int32, vp]),
     "cfb200_reci_enc_fwd": (ctypes.c_int, [vp] * 6 + [i64, i64, i64] + [vp] * 3),
     "cfb200_reci_enc_bwd": (ctypes.c_int, [vp] * 7 + [i64, i64, i64] + [vp] * 2),
     "cfb200_proj_fwd": (ctypes.c_int, [vp] * 6 + [i64, i64, f32, f32] + [vp] * 4),

@@ -3,8 +3,11 @@
 #include <math.h>
 #include <stdlib.h>
 #include <string.h>
+#include <algorithm>
 #include <atomic>
 #include <mutex>
+#include <numeric>
+#include <vector>
 #include "common.cuh"
 #include "framed_proj.cu"
 #include "frames.cu"
@@ -451,6 +454,26 @@ int cfb200_proj_fwd(const float* a_ik, const float* pos_ij, const float* tvecs, 
     if (values != nullptr && W_dist == nullptr) return CFB200_E_NULL;
     A.z = z; A.values = values;
     return cfb::framed_proj_fwd(A, P, S(stream));
+}
+
+int cfb200_deal_by_cost(const double* cost, int64_t n, int32_t parts, int32_t* part_of)
+{
+    // Host code: the most expensive item first, each to the group with the smallest total so far (lowest group
+    // index on ties); totals are added in that order in double, so the result does not depend on the machine.
+    if (n < 0 || parts < 1) return CFB200_E_SHAPE;
+    if (n > 0 && (!cost || !part_of)) return CFB200_E_NULL;
+    std::vector<int64_t> order((size_t)n);
+    std::iota(order.begin(), order.end(), (int64_t)0);
+    std::stable_sort(order.begin(), order.end(), [cost](int64_t a, int64_t b) { return cost[a] > cost[b]; });
+    std::vector<double> total((size_t)parts, 0.0);
+    for (int64_t t = 0; t < n; t++) {
+        int best = 0;
+        for (int g = 1; g < parts; g++)
+            if (total[g] < total[best]) best = g;
+        total[best] += cost[order[t]];
+        part_of[order[t]] = best;
+    }
+    return CFB200_OK;
 }
 
 int cfb200_reci_enc_fwd(const float* a_ik, const float* kr_base, const float* rvecs, const float* vcell,

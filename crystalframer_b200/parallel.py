@@ -44,14 +44,18 @@ def partition_by_pair_count(sizes, n_parts, cost=None):
     """Greedy split of crystals into ``n_parts`` groups of nearly equal cost, largest first -- the rule of
     models/latticeformer.py:224-233, whose cost is the squared size (the pair count).  ``cost`` replaces the
     squared sizes by a better estimate (``attention_cost``).  Returns a list of index arrays."""
-    weight = np.asarray(sizes, dtype=np.float64) ** 2 if cost is None else np.asarray(cost, dtype=np.float64)
-    totals = np.zeros(n_parts, np.float64)
-    groups = [[] for _ in range(n_parts)]
-    for item in np.argsort(-weight, kind="stable"):
-        g = int(np.argmin(totals))
-        totals[g] += weight[item]
-        groups[g].append(int(item))
-    return [np.asarray(g, np.int64) for g in groups]
+    weight = np.ascontiguousarray(np.asarray(sizes, dtype=np.float64) ** 2 if cost is None else cost, dtype=np.float64)
+    # the dealing loop runs in the library's host code (cfb200_deal_by_cost): 2 048 crystals over 8 ranks take
+    # microseconds there and several milliseconds as a Python loop, and the call releases the interpreter lock,
+    # which matters to the epoch loader's background thread (data.EpochLoader)
+    from . import _lib
+    part_of = np.empty(len(weight), np.int32)
+    rc = _lib.lib().cfb200_deal_by_cost(weight.ctypes.data, len(weight), int(n_parts), part_of.ctypes.data)
+    if rc != 0:
+        _lib.check(rc, "cfb200_deal_by_cost")
+    order = np.argsort(-weight, kind="stable")
+    dealt = part_of[order]
+    return [order[dealt == g].astype(np.int64) for g in range(n_parts)]
 
 
 def broadcast_state(module, src=0):

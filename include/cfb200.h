@@ -220,6 +220,12 @@ int cfb200_framed_proj_bwd(const float* a_ik, const float* pos_ij, const float* 
                            float* gW_ang1, float* gW_ang2, float* gW_ang3, void* workspace,
                            int64_t workspace_bytes, void* stream);
 
+/* Host code (no device work, no stream): deals n items with the given costs to `parts` groups of nearly equal
+ * total cost -- the most expensive first, each to the group with the smallest total so far (lowest group on
+ * ties, earlier item first among equal costs).  The reference spreads a batch over devices by this rule with the
+ * squared crystal size as cost (models/latticeformer.py:224-233).  part_of (n) receives the group of every item. */
+int cfb200_deal_by_cost(const double* cost, int64_t n, int32_t parts, int32_t* part_of);
+
 /* Replaces ReciPeriodicEncodingFuncCUDA (models/cuda_funcs/reci_space_enc.py:17-97; kernels
  * reci_enc_fwd.cu, reci_enc_bwd.cu): the reciprocal-space lattice sum of the plain Crystalformer's
  * "reci" / "multihead" domains over n1 in [0, lattice_range], n2, n3 in [-lattice_range, lattice_range]

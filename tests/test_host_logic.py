@@ -103,3 +103,57 @@ def test_gradient_allreduce_two_ranks_gloo():
     (_, w_a, g_a, m_a), (_, w_b, g_b, m_b) = res
     assert torch.equal(w_a, w_b)                       # broadcast made the weights identical
     assert torch.allclose(g_a, g_b) and torch.allclose(g_a, m_a, atol=1e-6)
+
+
+def test_dealing_by_cost_is_the_reference_rule():
+    """cfb200_deal_by_cost (host code of the library) against the rule written out as the reference has it
+    (models/latticeformer.py:224-233): descending cost, each item to the group with the smallest total."""
+    from crystalframer_b200.parallel import partition_by_pair_count
+
+    def written_out(weight, parts):
+        totals, groups = np.zeros(parts, np.float64), [[] for _ in range(parts)]
+        for item in np.argsort(-weight, kind="stable"):
+            g = int(np.argmin(totals))
+            totals[g] += weight[item]
+            groups[g].append(int(item))
+        return groups
+
+    rng = np.random.default_rng(0)
+    for n, parts in ((2048, 8), (256, 2), (7, 3), (50, 1), (0, 4)):
+        w = np.round(rng.lognormal(3, 1, n))                  # rounded: many equal costs
+        got = partition_by_pair_count(np.zeros(n), parts, w)
+        assert [g.tolist() for g in got] == written_out(w, parts), (n, parts)
+    sizes = rng.integers(1, 65, 300)
+    got = partition_by_pair_count(sizes, 4)                   # default cost: the pair count
+    assert [g.tolist() for g in got] == written_out(sizes.astype(np.float64) ** 2, 4)
+
+
+def test_epoch_loader_covers_the_set_once_and_collates_like_the_batch_functions():
+    """Structure set + epoch schedule + per-rank shares, on the CPU: every structure of the epoch's full global
+    batches appears exactly once over the ranks, each rank's batch equals the collation of its structures by the
+    batch functions, the schedule is the same on every rank and changes with the epoch."""
+    from crystalframer_b200 import data, synth
+    ds = data.StructureSet.synthetic(1000, 3, chunk=256)
+    assert len(ds) == 1000 and ds.start[-1] == len(ds.pos)
+    first = synth.make_workload("cfg3", seed=3 * 100003, num_crystals=256)
+    pick = np.array([7, 255, 0, 31])
+    got, want = ds.collate(pick), synth.select(first, pick)
+    for f in ("x", "pos", "batch", "trans_vec", "sizes", "z"):
+        assert np.array_equal(getattr(got, f), getattr(want, f)), f
+    world, per_rank = 3, 64
+    seen = []
+    for rank in range(world):
+        loader = data.EpochLoader(ds, per_rank, rank=rank, world=world, device="cpu", epoch=1, seed=9)
+        sched = data.epoch_schedule(len(ds), per_rank * world, 1, 9)
+        assert len(loader) == len(sched) == 1000 // (per_rank * world)
+        for step, tb in enumerate(loader):
+            mine = data.rank_share(ds, sched[step], rank, world)
+            seen.append(mine)
+            want = ds.collate(mine)
+            assert torch.equal(tb.x, torch.from_numpy(want.x)) and torch.equal(tb.pos, torch.from_numpy(want.pos))
+            assert torch.equal(tb.batch, torch.from_numpy(want.batch)) and torch.equal(tb.sizes, torch.from_numpy(want.sizes))
+            assert torch.equal(tb.trans_vec, torch.from_numpy(want.trans_vec)) and tb.num_pairs == want.num_pairs
+            assert torch.equal(tb.y, torch.from_numpy(ds.y[mine]))
+    seen = np.concatenate(seen)
+    assert len(seen) == len(np.unique(seen)) == (1000 // (per_rank * world)) * per_rank * world
+    assert not np.array_equal(data.epoch_schedule(len(ds), 192, 0, 9), data.epoch_schedule(len(ds), 192, 1, 9))
