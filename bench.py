@@ -44,6 +44,7 @@ METRIC = "crystals/sec train fwd+bwd (4-layer max-frame)"
 UNIT = "crystals/s"
 WORKLOAD = "cfg3: 4-layer max-frame training step, 256 crystals/GPU, lognormal sizes (median 8, 1..64), fp32"
 REPEATS = 6          # timed passes of K steps per arm (a pass is a fraction of a second); the fastest is reported
+OVERLAP_EXCHANGE = 0    # several ranks: exchange a layer's gradient slices during the backward of earlier layers
 BATCH = int(os.environ.get("CF_BENCH_BATCH", 256))   # 256 is the benchmark; other values are for diagnosis only
 # algorithmic work per unit: one (pair, head, translation) term and one (pair, head) projection
 FLOP_TERM_FWD, FLOP_TERM_BWD, SFU_TERM = 516.0, 738.0, 110.0
@@ -63,6 +64,8 @@ def parse():
     ap.add_argument("--cpu-crystals", type=int, default=16, help="crystals per CPU-baseline step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gpu-reference", action="store_true")
+    ap.add_argument("--overlap-exchange", type=int, default=OVERLAP_EXCHANGE,
+                    help="N>1: all-reduce each encoder layer's gradient slices beside the backward of the earlier layers")
     return ap.parse_args()
 
 
@@ -369,6 +372,8 @@ def run_ours(args, rank, world, local_rank):
     torch.backends.cudnn.allow_tf32 = False
     model = make_model(2).to(dev).train()
     opt = make_optimizer(model, fused=True)
+    if world > 1 and args.overlap_exchange:
+        opt.overlap_exchange()
     n_host = 4
     host = [data.host_batch(b, y) for b, y in synthetic_batches(n_host, 2, BATCH, rank, world)]
     resident = [hb.to(dev, non_blocking=False) for hb in host]
@@ -555,6 +560,8 @@ def run_ours(args, rank, world, local_rank):
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "global_batch": BATCH * world, "parallelism": f"dp{world}",
+                       "gradient_exchange": ("per layer, beside the backward pass" if world > 1 and args.overlap_exchange
+                                             else "one all-reduce after the backward pass" if world > 1 else "none"),
                        "l2": "256 MB buffer written between timed steps", "optimizer": "AdamW lr 5e-4, clip 1.0, L1 loss",
                        "timing": f"fastest of {REPEATS} passes of K steps per arm; medians beside it",
                        "pass_ms_per_step": [round(x / args.steps, 3) for x in passes],

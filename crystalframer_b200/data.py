@@ -110,9 +110,9 @@ def rank_share(dataset, global_idx, rank, world):
     count), returned in ascending dataset order."""
     if world == 1:
         return np.asarray(global_idx, dtype=np.int64)
-    from .parallel import partition_by_pair_count
-    part = partition_by_pair_count(dataset.sizes[global_idx], world, dataset.cost[global_idx])[rank]
-    return np.sort(np.asarray(global_idx, dtype=np.int64)[part])
+    from .parallel import deal_by_cost
+    global_idx = np.asarray(global_idx, dtype=np.int64)
+    return np.sort(global_idx[deal_by_cost(dataset.cost[global_idx], world) == rank])
 
 
 class _Slot:

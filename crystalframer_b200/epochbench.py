@@ -28,6 +28,9 @@ from .latticeformer import Latticeformer, ModelParams
 from .optim import FlatAdamW
 
 
+SEGMENT = 32
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--structures", type=int, default=65536)
@@ -35,6 +38,8 @@ def main():
     ap.add_argument("--max-steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--depth", type=int, default=2, help="batches the loader keeps in flight")
+    ap.add_argument("--overlap-exchange", type=int, default=0,
+                    help="several ranks: all-reduce each layer's gradient slices beside the backward of earlier layers")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -59,6 +64,8 @@ def main():
     decay = [p for n, p in model.named_parameters() if p.requires_grad and not n.endswith("bias")]
     no_decay = [p for n, p in model.named_parameters() if p.requires_grad and n.endswith("bias")]
     opt = FlatAdamW(decay, no_decay, lr=5e-4, betas=(0.9, 0.98), eps=1e-8, weight_decay=1e-5, max_norm=1.0)
+    if world > 1 and args.overlap_exchange:
+        opt.overlap_exchange()
     global_batch = args.batch * world
 
     def train_step(tb):
@@ -82,9 +89,14 @@ def main():
     barrier()
     t0 = time.perf_counter()
     steps = 0
+    marks = [torch.cuda.Event(enable_timing=True)]
+    marks[0].record()
     for tb in loader:
         losses[steps] = train_step(tb).detach()
         steps += 1
+        if steps % SEGMENT == 0:                     # device time of every SEGMENT steps: the step's cost moves with
+            marks.append(torch.cuda.Event(enable_timing=True))      # the learned Gaussian widths as training goes on
+            marks[-1].record()
     torch.cuda.synchronize()
     mine = time.perf_counter() - t0
     barrier()
@@ -101,7 +113,8 @@ def main():
             "structures_trained": trained, "steps": steps, "crystals_per_gpu_per_step": args.batch,
             "epoch_s": epoch_s, "ms_per_step": epoch_s / max(steps, 1) * 1e3,
             "h2d_bytes_per_step": loader.h2d_bytes / max(steps, 1), "loader_depth": args.depth,
-            "set_generation_s": gen_s, "first_loss": float(losses[0].item()) if steps else None,
+            "ms_per_step_by_segment": [round(a.elapsed_time(b) / SEGMENT, 3) for a, b in zip(marks[:-1], marks[1:])],
+            "segment_steps": SEGMENT, "set_generation_s": gen_s, "first_loss": float(losses[0].item()) if steps else None,
             "last_loss": float(losses[steps - 1].item()) if steps else None, "dtype": "fp32", "data": "synthetic",
             "scaling": "weak"}))
     if world > 1:

@@ -39,6 +39,10 @@ TASK_TABLE = True
 SAVE_PAIR_RESULTS = True
 # test hook: a list here receives a copy of every layer's frames (3,N,H,3) as the forward computes them
 FRAME_TAP = None
+# callable(tensors) invoked by the layer backward right after it has enqueued the kernels that add the layer's
+# weight gradients into their sinks (optim.FlatAdamW.overlap_exchange sets it to start the ranks' exchange of
+# those slices while the backward pass of the earlier layers runs)
+SINKS_FILLED = None
 
 FRAME_METHODS = {"no": 0, "max": 1, "weighted_pca": 2, "max_static": 3, "lattice": 4, "pca": 5}
 WEIGHT_FIELDS = ("q_proj", "k_proj", "v_proj", "in_bias", "lattice_pos", "gauss_scale", "out_proj", "out_bias",
@@ -243,6 +247,8 @@ class FusedEncoderLayerFunc(torch.autograd.Function):
                     ctypes.byref(Gr), 1 if use_sink else 0, ws.data_ptr(), ws.numel())
         if use_sink:
             grads = [None] * 16
+            if SINKS_FILLED is not None:
+                SINKS_FILLED(tuple(dest.values()))       # this layer's gradients are final (enqueued): they may be exchanged
         else:
             grads = [dest.get(f) for f in WEIGHT_FIELDS]
         return (gx, *grads, None, None)

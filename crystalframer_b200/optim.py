@@ -66,6 +66,32 @@ class FlatAdamW:
         self._offsets = offsets
         self.averaged = None          # flat running average of the weights, created by the first step(average=True)
         self.n_averaged = 0
+        self.exchange = None          # parallel.GradientExchange once overlap_exchange() has been called
+
+    def overlap_exchange(self, enable=True):
+        """With several ranks: start the all-reduce of an encoder layer's slices of the flat gradient buffer as soon
+        as that layer's backward has been enqueued, so that it runs beside the backward of the earlier layers;
+        ``step(world_sum=True)`` then only sends what is left (embedding, output head, layers that did not take
+        the one-call path) and waits.  For steps with ONE backward pass between ``zero_grad`` and ``step``: a
+        slice that has been exchanged must not receive further gradients."""
+        from . import fused_layer, parallel
+        if not enable:
+            self.exchange = None
+            fused_layer.SINKS_FILLED = None
+            return
+        self.exchange = parallel.GradientExchange(self.grad)
+        base = self.grad.data_ptr()
+
+        def filled(tensors):
+            if not (dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1):
+                return
+            ranges = []
+            for t in tensors:
+                a = (t.data_ptr() - base) // 4
+                ranges.append((a, a + (t.numel() + ALIGN - 1) // ALIGN * ALIGN))
+            self.exchange.send(ranges)
+
+        fused_layer.SINKS_FILLED = filled
 
     def zero_grad(self, set_to_none=True):
         """Clears the flat gradient buffer (one launch) and drops the parameters' ``.grad``."""
@@ -91,7 +117,12 @@ class FlatAdamW:
         fold the updated weights into the running average (the first such step copies them)."""
         g = self.gather_grads()
         if world_sum and dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
-            dist.all_reduce(g)
+            if self.exchange is not None:
+                self.exchange.finish()
+            else:
+                dist.all_reduce(g)
+        elif self.exchange is not None and self.exchange.work:
+            raise RuntimeError("slices of the gradient buffer were exchanged during backward: call step(world_sum=True)")
         self.steps += 1
         b1, b2 = self.betas
         p = _lib.ptr

@@ -40,19 +40,26 @@ def attention_cost_counted(pos, cells, sizes, a_typical=-0.255, prune=16.0, per_
     return out
 
 
+def deal_by_cost(cost, n_parts):
+    """Group (0..n_parts-1) of every item under the dealing rule of ``partition_by_pair_count``, as one call into the
+    library's host code (cfb200_deal_by_cost): 2 048 crystals over 8 ranks take microseconds there and several
+    milliseconds as a Python loop, and the call releases the interpreter lock, which matters to the epoch loader's
+    background thread (data.EpochLoader)."""
+    from . import _lib
+    weight = np.ascontiguousarray(cost, dtype=np.float64)
+    part_of = np.empty(len(weight), np.int32)
+    rc = _lib.lib().cfb200_deal_by_cost(weight.ctypes.data, len(weight), int(n_parts), part_of.ctypes.data)
+    if rc != 0:
+        _lib.check(rc, "cfb200_deal_by_cost")
+    return part_of
+
+
 def partition_by_pair_count(sizes, n_parts, cost=None):
     """Greedy split of crystals into ``n_parts`` groups of nearly equal cost, largest first -- the rule of
     models/latticeformer.py:224-233, whose cost is the squared size (the pair count).  ``cost`` replaces the
     squared sizes by a better estimate (``attention_cost``).  Returns a list of index arrays."""
     weight = np.ascontiguousarray(np.asarray(sizes, dtype=np.float64) ** 2 if cost is None else cost, dtype=np.float64)
-    # the dealing loop runs in the library's host code (cfb200_deal_by_cost): 2 048 crystals over 8 ranks take
-    # microseconds there and several milliseconds as a Python loop, and the call releases the interpreter lock,
-    # which matters to the epoch loader's background thread (data.EpochLoader)
-    from . import _lib
-    part_of = np.empty(len(weight), np.int32)
-    rc = _lib.lib().cfb200_deal_by_cost(weight.ctypes.data, len(weight), int(n_parts), part_of.ctypes.data)
-    if rc != 0:
-        _lib.check(rc, "cfb200_deal_by_cost")
+    part_of = deal_by_cost(weight, n_parts)
     order = np.argsort(-weight, kind="stable")
     dealt = part_of[order]
     return [order[dealt == g].astype(np.int64) for g in range(n_parts)]
@@ -82,3 +89,45 @@ def allreduce_gradients(params, average=True):
     if average:
         flat.div_(dist.get_world_size())
     torch._foreach_copy_(grads, list(torch._utils._unflatten_dense_tensors(flat, grads)))   # one launch, not one per tensor
+
+
+class GradientExchange:
+    """Sums a flat gradient buffer over the ranks in pieces.  ``send(ranges)`` starts an asynchronous all-reduce of
+    element ranges whose gradients are final -- the communication library runs it on its own stream, ordered after
+    the work already enqueued on the caller's stream, so it overlaps whatever the caller enqueues next (the backward
+    pass of earlier layers); ``finish()`` sends every element not sent yet and makes the caller's stream wait for
+    all of it.  Every rank must send the same ranges in the same order.  The reference exchanges nothing by hand:
+    its replicas' gradients are reduced by nn.parallel / Lightning DDP after the backward pass
+    (models/latticeformer.py:211-273, train.py:97-119)."""
+
+    def __init__(self, flat):
+        self.flat = flat
+        self.sent, self.work = [], []
+
+    @staticmethod
+    def merge(ranges):
+        out = []
+        for a, b in sorted((int(a), int(b)) for a, b in ranges if b > a):
+            if out and a <= out[-1][1]:
+                out[-1][1] = max(out[-1][1], b)
+            else:
+                out.append([a, b])
+        return [(a, b) for a, b in out]
+
+    def send(self, ranges):
+        for a, b in self.merge(ranges):
+            self.work.append(dist.all_reduce(self.flat[a:b], async_op=True))
+            self.sent.append((a, b))
+
+    def finish(self):
+        rest, at = [], 0
+        for a, b in self.merge(self.sent):
+            if a > at:
+                rest.append((at, a))
+            at = max(at, b)
+        if at < self.flat.numel():
+            rest.append((at, self.flat.numel()))
+        self.send(rest)
+        for w in self.work:
+            w.wait()
+        self.sent, self.work = [], []

@@ -15,6 +15,7 @@ import torch
 
 from crystalframer_b200 import cuda_funcs as F
 from crystalframer_b200 import opbench
+from . import oracle as O
 from . import reference as R
 
 
@@ -105,7 +106,25 @@ def main():
         "gW_ang": viol(torch.stack([w.grad[0] for w in W_[1:]]), gWs, max(1.0, float(gWs.abs().max()))),
     }
     b = I["batch_obj"]
+    # reciprocal-space logit bias (plain Crystalformer's "reci" domain): reference kernels and the library
+    rvecs, vcell, kr = (torch.from_numpy(x).to(dev) for x in O.reciprocal_geometry(b.pos, b.trans_vec, b.sizes,
+                                                                                     edges.cpu().numpy()))
+    ar = (a * 9.5).contiguous()                        # -0.5 scale_reci^2 f against -0.5 scale_real^-2 f
+    reci = {}
+    reci["reference_fwd"], (zr, sr) = timed(lambda: rk.reci_fwd(ar, kr, rvecs, vcell, batch, edges), args.iters)
+    gzr = (torch.randn_like(zr) * (sr > 1e-2)).contiguous()
+    reci["reference_bwd"], gar = timed(lambda: rk.reci_bwd(ar, kr, rvecs, vcell, batch, edges, zr, gzr, sr), args.iters)
+    ar_ = ar.detach().requires_grad_(True)
+    reci["library_fwd"], zl = timed(lambda: F.ReciPeriodicEncodingFuncCUDA.apply(ar_, kr, rvecs, vcell, batch, edges), args.iters)
+    reci["library_bwd"], _ = timed(lambda: zl.backward(gzr, retain_graph=True), args.iters)
+    ar_.grad = None
+    zl.backward(gzr)
+    ok = sr > 1e-3
+    checks["reci_z"] = viol(zl.detach()[ok], zr[ok], 10.0)
+    checks["reci_ga"] = viol(ar_.grad, gar, max(1.0, float(gar.abs().max())))
+    res_reci = {k_: round(v_, 4) for k_, v_ in reci.items()}
     print(json.dumps({"impl": "reference CUDA kernels (sm_100a build)", "workload": args.workload, "crystals": len(b.sizes),
+                      "reciprocal_encoding_ms": res_reci,
                       "pairs": b.num_pairs, "ms": {k_: round(v_, 4) for k_, v_ in res.items()},
                       "ms_total": round(sum(res.values()), 4),
                       "parity_vs_library (violating fraction, max abs err)": checks}))

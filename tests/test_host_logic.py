@@ -157,3 +157,45 @@ def test_epoch_loader_covers_the_set_once_and_collates_like_the_batch_functions(
     seen = np.concatenate(seen)
     assert len(seen) == len(np.unique(seen)) == (1000 // (per_rank * world)) * per_rank * world
     assert not np.array_equal(data.epoch_schedule(len(ds), 192, 0, 9), data.epoch_schedule(len(ds), 192, 1, 9))
+
+
+def _exchange_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    sys.path.insert(0, ROOT)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from crystalframer_b200.parallel import GradientExchange
+    g = torch.Generator().manual_seed(7 + rank)
+    flat = torch.randn(1000, generator=g)
+    whole = flat.clone()
+    dist.all_reduce(whole)
+    ex = GradientExchange(flat)
+    ex.send([(640, 704), (128, 256)])            # "layer 3": two slices, given out of order
+    ex.send([(256, 320), (704, 768), (0, 0)])     # "layer 2": adjacent to the first ones; an empty range
+    untouched = flat[320:640].clone()            # not sent yet: still this rank's own values
+    ex.finish()
+    second = flat.clone()
+    ex.finish()                                  # nothing sent since: reduces the whole buffer again
+    q.put((rank, flat.numpy().copy(), whole.numpy().copy(), untouched.numpy().copy(), second.numpy().copy()))
+    dist.destroy_process_group()
+
+
+def test_gradient_exchange_in_pieces_equals_one_allreduce_two_ranks_gloo():
+    from crystalframer_b200.parallel import GradientExchange
+    assert GradientExchange.merge([(5, 9), (0, 3), (3, 4), (8, 12), (20, 20)]) == [(0, 4), (5, 12)]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() + 17) % 1000
+    procs = [ctx.Process(target=_exchange_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted([q.get(timeout=120) for _ in procs], key=lambda t: t[0])
+    for p in procs:
+        p.join(60)
+    for rank, flat, whole, untouched, second in res:
+        g = torch.Generator().manual_seed(7 + rank)
+        own = torch.randn(1000, generator=g).numpy()
+        assert np.array_equal(untouched, own[320:640])                 # finish() had not run yet
+        assert np.allclose(second, whole, rtol=0, atol=1e-6)           # pieces add up to the single all-reduce
+        assert np.allclose(flat, 2 * whole, rtol=0, atol=2e-6)         # a finish() with nothing sent reduces everything
+    assert np.array_equal(res[0][4], res[1][4])                       # both ranks hold the same sums
