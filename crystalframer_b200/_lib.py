@@ -81,6 +81,9 @@ SIGNATURES = {
     "cfb200_reci_enc_fwd": (ctypes.c_int, [vp] * 6 + [i64, i64, i64] + [vp] * 3),
     "cfb200_reci_enc_bwd": (ctypes.c_int, [vp] * 7 + [i64, i64, i64] + [vp] * 2),
     "cfb200_proj_fwd": (ctypes.c_int, [vp] * 6 + [i64, i64, f32, f32] + [vp] * 4),
+    "cfb200_proj_heads_bwd_workspace_bytes": (i64, [i64, i64, i64]),
+    "cfb200_proj_heads_fwd": (ctypes.c_int, [vp] * 6 + [i64, i64, i64, f32, f32] + [vp] * 4),
+    "cfb200_proj_heads_bwd": (ctypes.c_int, [vp] * 7 + [i64, i64, i64, f32, f32] + [vp] * 7 + [i64, vp]),
     "cfb200_proj_bwd": (ctypes.c_int, [vp] * 7 + [i64, i64, f32, f32] + [vp] * 7 + [i64, vp]),
     "cfb200_framed_proj_bwd_noalloc": (ctypes.c_int, [vp] * 7 + [i64, i64, f32, f32] + [vp] * 15 + [vp]),
     "cfb200_attn_fused_fwd": (ctypes.c_int, [vp] * 12 + [i64, i64, f32, f32] + [vp] * 8 + [ctypes.c_int] + [vp] * 7

@@ -9,7 +9,8 @@ pipeline stay in PyTorch; everything between them runs in libcfb200.
 
 Domains: "real" with frame methods "max", "max_static", "lattice", "pca", "weighted_pca" (CrystalFramer)
 and "no" (plain Crystalformer distance encoding); "reci" / "RECI" (plain Crystalformer's reciprocal-space
-logit bias, no value encoding), also alternating by layer ("real-reci").  "multihead" is not built.
+logit bias, no value encoding), also alternating by layer ("real-reci"); "multihead" (first half of the heads in
+real space, second half in reciprocal space) for the plain Crystalformer encoding (frame_method "no").
 """
 import math
 from typing import Optional, Tuple
@@ -164,6 +165,14 @@ def gaussian_coefficients(q, lattice_pos_weights, gauss_scale, params, training)
                 gauss_scale._cf_ready = gauss_scale._version
         alpha = (alpha + shift) * scale
     beta = params.positive_func_beta
+    if params.domain == "multihead":
+        # the first half of the heads attends in real space, the second half in reciprocal space
+        # (models/indexed_lattice_multi_head_attention_cuda.py:953-956)
+        a1, a2 = alpha.chunk(2, 1)
+        lb1, lb2 = params.gauss_lb_real, params.gauss_lb_reci
+        a1 = ((1.0 - lb1) * F.elu(a1 * (beta / (1.0 - lb1))) + 1.0) * (-0.5 * params.scale_real ** -2)
+        a2 = ((1.0 - lb2) * F.elu(a2 * (beta / (1.0 - lb2))) + 1.0) * (-0.5 * params.scale_reci ** 2)
+        return torch.cat([a1, a2], dim=1)
     if params.domain in ("reci", "RECI"):
         # reciprocal-space Gaussians widen where real-space ones narrow
         # (models/indexed_lattice_multi_head_attention_cuda.py:946-952)
@@ -195,10 +204,21 @@ def crystalformer_multi_head_attention_forward_cuda(
     v = F.linear(value, v_proj_weight, bv).view(value.shape[0], num_heads, hv)
     attn_weights = values = None
     if params is not None and params.domain != "no":
-        if params.domain not in ("real", "reci", "RECI"):
+        if params.domain not in ("real", "reci", "RECI", "multihead"):
             raise NotImplementedError(f"domain={params.domain}")
         alpha = gaussian_coefficients(q, lattice_pos_weights, gauss_scale, params, training)
-        if params.domain == "real":
+        if params.domain == "multihead":
+            # models/indexed_lattice_multi_head_attention_cuda.py:953-974
+            half = num_heads // 2
+            a1, a2 = alpha[:, :half].contiguous(), alpha[:, half:].contiguous()
+            w1, v1 = compute_real_domain_attn_frame_proj(
+                q, k, v, batch_q, batch_kv, edges, pos, dist2_min, tvecs, rvecs,
+                None if pe_dist_proj is None else pe_dist_proj[:, :half], proj_angle1, proj_angle2, proj_angle3, a1,
+                params, this_epoch)
+            w2 = ReciPeriodicEncodingFuncCUDA.apply(a2, kr_base, rvecs, vcell, batch_q, edges)
+            attn_weights = torch.cat([w1, w2], dim=1)
+            values = None if v1 is None else torch.cat([v1, torch.zeros_like(v1)], dim=1)
+        elif params.domain == "real":
             attn_weights, values = compute_real_domain_attn_frame_proj(
                 q, k, v, batch_q, batch_kv, edges, pos, dist2_min, tvecs, rvecs, pe_dist_proj, proj_angle1,
                 proj_angle2, proj_angle3, alpha, params, this_epoch)
@@ -224,11 +244,13 @@ class CrystalformerMultiheadAttentionCUDA(Module):
                  params=LatticeformerParams(), device=None, dtype=None) -> None:
         kw = {"device": device, "dtype": dtype}
         super().__init__()
-        if params.domain not in ("real", "reci", "RECI", "no"):
-            # "multihead": the reference's CUDA module hands queries of all heads and coefficients of half of
-            # them to its frame kernels (models/indexed_lattice_multi_head_attention_cuda.py:953-963); its README
-            # (:157) limits CrystalFramer to the real domain.  Not built.
+        if params.domain not in ("real", "reci", "RECI", "multihead", "no"):
             raise NotImplementedError(f"domain={params.domain}")
+        if params.domain == "multihead" and (params.frame_method != "no" or num_heads % 2):
+            # with frames the reference's CUDA module hands queries of all heads and coefficients of half of them to
+            # its frame kernels (models/indexed_lattice_multi_head_attention_cuda.py:953-963); its README (:157)
+            # limits CrystalFramer to the real domain.  Built for the plain Crystalformer encoding only.
+            raise NotImplementedError("domain=multihead needs frame_method='no' and an even number of heads")
         self.embed_dim = embed_dim
         self.kdim = kdim * num_heads if kdim is not None and kdim > 0 else embed_dim
         self.vdim = vdim * num_heads if vdim is not None and vdim > 0 else embed_dim
@@ -256,14 +278,15 @@ class CrystalformerMultiheadAttentionCUDA(Module):
             if params.value_pe_dist_reci > 0 or params.value_pe_wave_reci > 0:
                 raise NotImplementedError("value encodings of the reciprocal domain")
             self.lattice_pos_weights = Parameter(torch.empty(self.kdim, **kw))
-        if params.domain == "real":
+        if params.domain in ("real", "multihead"):
             if not params.gauss_state.startswith("q"):
                 raise NotImplementedError(f"gauss_state={params.gauss_state}")
             self.lattice_pos_weights = Parameter(torch.empty(self.kdim, **kw))
             if params.value_pe_dist_real > 0:
                 self.pe_dist_proj = Parameter(torch.empty(1, num_heads, self.head_dim, params.value_pe_dist_real, **kw))
             if params.value_pe_angle_real > 0:
-                shape = (1, num_heads, self.head_dim, params.value_pe_angle_real)
+                # "multihead" keeps angle weights for its real-space half only (:1088-1097)
+                shape = (1, num_heads if params.domain == "real" else num_heads // 2, self.head_dim, params.value_pe_angle_real)
                 self.proj_angle1 = Parameter(torch.empty(*shape, **kw))
                 self.proj_angle2 = Parameter(torch.empty(*shape, **kw))
                 self.proj_angle3 = Parameter(torch.empty(*shape, **kw))

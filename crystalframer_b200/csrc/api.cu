@@ -439,13 +439,17 @@ int cfb200_framed_proj_fwd_cached(const float* a_ik, const float* pos_ij, const 
     return cfb::framed_proj_fwd(A, P, S(stream));
 }
 
-int cfb200_proj_fwd(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
-                    const int64_t* batch, const int64_t* edges, int64_t N, int64_t E, float dist_max,
-                    float cutoff_radius, const float* W_dist, float* z, float* values, void* stream)
+// The plain encoding for `heads` heads (0: the configured number).  Every per-head array of the call -- a_ik,
+// W_dist, z, values and the gradients -- then has `heads` heads.
+static int proj_fwd_impl(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                         const int64_t* batch, const int64_t* edges, int64_t N, int64_t E, int64_t heads, float dist_max,
+                         float cutoff_radius, const float* W_dist, float* z, float* values, void* stream)
 {
     cfb::Params P;
     int rc = make_params(dist_max, cutoff_radius, P, true);
     if (rc != CFB200_OK) return rc;
+    if (heads < 0 || heads > 65535) return CFB200_E_SHAPE;
+    if (heads > 0) P.H = (int)heads;
     cfb::FpArgs A;
     rc = fp_args(A, a_ik, pos_ij, tvecs, rvlen, batch, edges, N, E, cutoff_radius, W_dist, nullptr, nullptr, nullptr,
                  nullptr, nullptr, nullptr);
@@ -454,6 +458,74 @@ int cfb200_proj_fwd(const float* a_ik, const float* pos_ij, const float* tvecs, 
     if (values != nullptr && W_dist == nullptr) return CFB200_E_NULL;
     A.z = z; A.values = values;
     return cfb::framed_proj_fwd(A, P, S(stream));
+}
+
+static int proj_bwd_impl(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                         const int64_t* batch, const int64_t* edges, const int64_t* e_start, int64_t N, int64_t E,
+                         int64_t heads, float dist_max, float cutoff_radius, const float* W_dist, const float* z,
+                         const float* gz, const float* gvalues, float* ga, float* gW_dist, void* workspace,
+                         int64_t workspace_bytes, void* stream)
+{
+    cfb::Params P;
+    int rc = make_params(dist_max, cutoff_radius, P, true);
+    if (rc != CFB200_OK) return rc;
+    if (heads < 0 || heads > 65535) return CFB200_E_SHAPE;
+    if (heads > 0) P.H = (int)heads;
+    cfb::FpArgs A;
+    rc = fp_args(A, a_ik, pos_ij, tvecs, rvlen, batch, edges, N, E, cutoff_radius, W_dist, nullptr, nullptr, nullptr,
+                 nullptr, nullptr, nullptr);
+    if (rc != CFB200_OK) return rc;
+    if (E > 0 && (!z || !gz || !gvalues || !W_dist || !e_start)) return CFB200_E_NULL;
+    if (N > 0 && (ga == nullptr || e_start == nullptr)) return CFB200_E_NULL;
+    if (gW_dist == nullptr) return CFB200_E_NULL;
+    A.z_in = z; A.gz = gz; A.gv = gvalues;
+    float* gW[4] = {gW_dist, nullptr, nullptr, nullptr};
+    return cfb::framed_proj_bwd(A, P, e_start, ga, gW, workspace, workspace_bytes, S(stream));
+}
+
+int cfb200_proj_fwd(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                    const int64_t* batch, const int64_t* edges, int64_t N, int64_t E, float dist_max,
+                    float cutoff_radius, const float* W_dist, float* z, float* values, void* stream)
+{
+    return proj_fwd_impl(a_ik, pos_ij, tvecs, rvlen, batch, edges, N, E, 0, dist_max, cutoff_radius, W_dist, z, values,
+                         stream);
+}
+
+int cfb200_proj_bwd(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                    const int64_t* batch, const int64_t* edges, const int64_t* e_start, int64_t N, int64_t E,
+                    float dist_max, float cutoff_radius, const float* W_dist, const float* z, const float* gz,
+                    const float* gvalues, float* ga, float* gW_dist, void* workspace, int64_t workspace_bytes,
+                    void* stream)
+{
+    return proj_bwd_impl(a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, N, E, 0, dist_max, cutoff_radius, W_dist, z,
+                         gz, gvalues, ga, gW_dist, workspace, workspace_bytes, stream);
+}
+
+int64_t cfb200_proj_heads_bwd_workspace_bytes(int64_t N, int64_t E, int64_t heads)
+{
+    if (N < 0 || E < 0 || heads < 1 || heads > 65535) return -1;
+    return cfb::framed_proj_bwd_workspace_bytes(N, E, (int)heads);
+}
+
+int cfb200_proj_heads_fwd(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                          const int64_t* batch, const int64_t* edges, int64_t N, int64_t E, int64_t heads,
+                          float dist_max, float cutoff_radius, const float* W_dist, float* z, float* values,
+                          void* stream)
+{
+    if (heads < 1) return CFB200_E_SHAPE;
+    return proj_fwd_impl(a_ik, pos_ij, tvecs, rvlen, batch, edges, N, E, heads, dist_max, cutoff_radius, W_dist, z,
+                         values, stream);
+}
+
+int cfb200_proj_heads_bwd(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                          const int64_t* batch, const int64_t* edges, const int64_t* e_start, int64_t N, int64_t E,
+                          int64_t heads, float dist_max, float cutoff_radius, const float* W_dist, const float* z,
+                          const float* gz, const float* gvalues, float* ga, float* gW_dist, void* workspace,
+                          int64_t workspace_bytes, void* stream)
+{
+    if (heads < 1) return CFB200_E_SHAPE;
+    return proj_bwd_impl(a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, N, E, heads, dist_max, cutoff_radius, W_dist,
+                         z, gz, gvalues, ga, gW_dist, workspace, workspace_bytes, stream);
 }
 
 int cfb200_deal_by_cost(const double* cost, int64_t n, int32_t parts, int32_t* part_of)
@@ -502,27 +574,6 @@ int cfb200_reci_enc_bwd(const float* a_ik, const float* kr_base, const float* rv
     A.a = a_ik; A.kr = kr_base; A.rvecs = rvecs; A.batch = batch; A.e_start = e_start;
     A.gz = gz; A.sumexp_in = sumexp; A.ga = ga; A.N = (int)N; A.H = (int)H; A.R = g_cfg.lattice_range;
     return cfb::reci_enc(A, true, S(stream));
-}
-
-int cfb200_proj_bwd(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
-                    const int64_t* batch, const int64_t* edges, const int64_t* e_start, int64_t N, int64_t E,
-                    float dist_max, float cutoff_radius, const float* W_dist, const float* z, const float* gz,
-                    const float* gvalues, float* ga, float* gW_dist, void* workspace, int64_t workspace_bytes,
-                    void* stream)
-{
-    cfb::Params P;
-    int rc = make_params(dist_max, cutoff_radius, P, true);
-    if (rc != CFB200_OK) return rc;
-    cfb::FpArgs A;
-    rc = fp_args(A, a_ik, pos_ij, tvecs, rvlen, batch, edges, N, E, cutoff_radius, W_dist, nullptr, nullptr, nullptr,
-                 nullptr, nullptr, nullptr);
-    if (rc != CFB200_OK) return rc;
-    if (E > 0 && (!z || !gz || !gvalues || !W_dist || !e_start)) return CFB200_E_NULL;
-    if (N > 0 && (ga == nullptr || e_start == nullptr)) return CFB200_E_NULL;
-    if (gW_dist == nullptr) return CFB200_E_NULL;
-    A.z_in = z; A.gz = gz; A.gv = gvalues;
-    float* gW[4] = {gW_dist, nullptr, nullptr, nullptr};
-    return cfb::framed_proj_bwd(A, P, e_start, ga, gW, workspace, workspace_bytes, S(stream));
 }
 
 int cfb200_framed_proj_bwd(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,

@@ -75,8 +75,10 @@ class RealPeriodicEncodingWithProjFuncCUDA(torch.autograd.Function):
         cfg = current_config()
         N, H = a_ik.shape
         E = edge_ij_e.shape[1]
-        if H != cfg.num_heads or abs(float(wscale) - cfg.dist_wscale) > 1e-6 * max(1.0, abs(cfg.dist_wscale)):
+        if abs(float(wscale) - cfg.dist_wscale) > 1e-6 * max(1.0, abs(cfg.dist_wscale)):
             raise RuntimeError("call-time scalars differ from those bound by compile_kernels")
+        # H may be smaller than the bound head count: the "multihead" domain encodes half of the heads in real space
+        # (models/indexed_lattice_multi_head_attention_cuda.py:953-963); the weights then have H heads as well
         dev = a_ik.device
         a, pos, tv = f32c(a_ik), f32c(rpos_ij_e), f32c(tvecs_n)
         batch, edges, rv = batch_i.contiguous(), edge_ij_e.contiguous(), f32c(rvlen_n)
@@ -86,8 +88,10 @@ class RealPeriodicEncodingWithProjFuncCUDA(torch.autograd.Function):
         z = torch.empty((E, H), device=dev, dtype=torch.float32)
         v = torch.empty((E, H, Wd.shape[-2]), device=dev, dtype=torch.float32) if want_v else None
         p, ip = _lib.ptr, _lib.iptr
-        _lib.invoke("cfb200_proj_fwd", 1, dev, p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), N, E, float(dist_max),
-                    cutoff, p(Wd), p(z), p(v))
+        if Wd is not None and Wd.shape[0] != H:
+            raise RuntimeError(f"W_k has {Wd.shape[0]} heads, a_ik {H}")
+        _lib.invoke("cfb200_proj_heads_fwd", 1, dev, p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), N, E, H,
+                    float(dist_max), cutoff, p(Wd), p(z), p(v))
         ctx.save_for_backward(a, pos, tv, batch, edges, rv, Wd, z)
         ctx.meta = (float(dist_max), cutoff, rvlen_n is not None, None if W_k is None else tuple(W_k.shape))
         ctx.mark_non_differentiable()
@@ -111,11 +115,11 @@ class RealPeriodicEncodingWithProjFuncCUDA(torch.autograd.Function):
         ga = torch.empty((N, H), device=dev, dtype=torch.float32)
         gWd = torch.empty_like(Wd)
         e_start = csr_offsets(edges, N)
-        nbytes = _lib.lib().cfb200_framed_proj_bwd_workspace_bytes(N, E)
+        nbytes = _lib.lib().cfb200_proj_heads_bwd_workspace_bytes(N, E, H)
         ws = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=dev)
         p, ip = _lib.ptr, _lib.iptr
-        _lib.invoke("cfb200_proj_bwd", 3, dev, p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), ip(e_start), N, E,
-                    dist_max, cutoff, p(Wd), p(z), p(gz), p(gv), p(ga), p(gWd), ws.data_ptr(), int(nbytes))
+        _lib.invoke("cfb200_proj_heads_bwd", 3, dev, p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), ip(e_start), N, E,
+                    H, dist_max, cutoff, p(Wd), p(z), p(gz), p(gv), p(ga), p(gWd), ws.data_ptr(), int(nbytes))
         out = [None] * (15 if has_rv else 13)
         out[0] = ga
         out[9] = gWd.reshape(shape_d)

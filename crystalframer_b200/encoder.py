@@ -222,7 +222,7 @@ class CrystalformerEncoderCUDA(Module):
         batch = batch - batch[0]
         pos_ij, dist2_min, kr_base, rvecs, vcell, edges = compute_lattice_distances_for_cuda(
             pos, batch, trans, sizes, self.lattice_params.lattice_range, -1, output_real=True,
-            output_reci=any(d in ("reci", "RECI") for d in self.lattice_params.domain.split("-")), num_pairs=num_pairs)
+            output_reci=any(d in ("reci", "RECI", "multihead") for d in self.lattice_params.domain.split("-")), num_pairs=num_pairs)
         out = src
         for layer in self.layers:
             out = layer(out, batch, edges, pos_ij, dist2_min, trans, kr_base, rvecs, vcell, onehot, this_epoch)

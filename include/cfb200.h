@@ -220,6 +220,22 @@ int cfb200_framed_proj_bwd(const float* a_ik, const float* pos_ij, const float* 
                            float* gW_ang1, float* gW_ang2, float* gW_ang3, void* workspace,
                            int64_t workspace_bytes, void* stream);
 
+/* cfb200_proj_fwd / cfb200_proj_bwd for `heads` heads instead of the configured number: a_ik (N,heads),
+ * W_dist (heads,head_dim,dist_dim), z (E,heads), values (E,heads,head_dim) and the gradients likewise.  The
+ * "multihead" domain of the plain Crystalformer gives half of the heads to the real-space encoding and half
+ * to the reciprocal one (models/indexed_lattice_multi_head_attention_cuda.py:953-963). */
+int64_t cfb200_proj_heads_bwd_workspace_bytes(int64_t N, int64_t E, int64_t heads);
+int cfb200_proj_heads_fwd(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                          const int64_t* batch, const int64_t* edges, int64_t N, int64_t E, int64_t heads,
+                          float dist_max, float cutoff_radius, const float* W_dist, float* z,
+                          float* values, void* stream);
+int cfb200_proj_heads_bwd(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                          const int64_t* batch, const int64_t* edges, const int64_t* e_start, int64_t N,
+                          int64_t E, int64_t heads, float dist_max, float cutoff_radius,
+                          const float* W_dist, const float* z, const float* gz, const float* gvalues,
+                          float* ga, float* gW_dist, void* workspace, int64_t workspace_bytes,
+                          void* stream);
+
 /* Host code (no device work, no stream): deals n items with the given costs to `parts` groups of nearly equal
  * total cost -- the most expensive first, each to the group with the smallest total so far (lowest group on
  * ties, earlier item first among equal costs).  The reference spreads a batch over devices by this rule with the

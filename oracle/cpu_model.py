@@ -51,6 +51,12 @@ def coefficients(attn, q):
                     attn.gauss_scale[1] = shift
         alpha = (alpha + shift) * scale
     beta = P.positive_func_beta
+    if P.domain == "multihead":               # :953-956
+        a1, a2 = alpha.chunk(2, 1)
+        lb1, lb2 = P.gauss_lb_real, P.gauss_lb_reci
+        a1 = ((1.0 - lb1) * F.elu(a1 * (beta / (1.0 - lb1))) + 1.0) * (-0.5 * P.scale_real ** -2)
+        a2 = ((1.0 - lb2) * F.elu(a2 * (beta / (1.0 - lb2))) + 1.0) * (-0.5 * P.scale_reci ** 2)
+        return torch.cat([a1, a2], dim=1)
     if P.domain in ("reci", "RECI"):          # :946-952
         lb = P.gauss_lb_reci
         pos = (1.0 - lb) * F.elu(alpha * (beta / (1.0 - lb))) + 1.0
@@ -91,6 +97,17 @@ def attention_layer(attn, x, geo, cfg, frames=None):
         out = OF.Attention.apply(qs, k, v, z, torch.zeros((z.shape[0], H, hd), dtype=q.dtype, device=q.device), geo["batch"], geo["edges"])
         return F.linear(out.reshape(N, H * hd), attn.out_proj.weight, attn.out_proj.bias)
     method = attn.params.frame_method
+    if attn.params.domain == "multihead":
+        # first half of the heads: plain real-space encoding; second half: reciprocal-space bias, no values (:953-974)
+        half = H // 2
+        z1, v1 = OF.FramedProj.apply(a[:, :half].contiguous(), geo["pos_ij"], geo["tvecs"], geo["batch"], geo["edges"],
+                                     geo["rvlen"], cutoff, cfg.dist_max, attn.pe_dist_proj[:, :half], None, None, None,
+                                     None, None, None)
+        z2 = OF.Reci.apply(a[:, half:].contiguous(), geo["kr"], geo["rvecs"], geo["vcell"], geo["batch"], geo["edges"],
+                           cfg.lattice_range)
+        out = OF.Attention.apply(qs, k, v, torch.cat([z1, z2], dim=1), torch.cat([v1, torch.zeros_like(v1)], dim=1),
+                                 geo["batch"], geo["edges"])
+        return F.linear(out.reshape(N, H * hd), attn.out_proj.weight, attn.out_proj.bias)
     if method == "no":
         f1 = f2 = f3 = None
     elif frames is not None:
@@ -143,7 +160,7 @@ def forward(model, batch, backend=None, frames=None):
     t = lambda arr: torch.from_numpy(np.ascontiguousarray(arr)).to(dev)
     geo = dict(pos_ij=t(g["pos_ij"]), tvecs=t(batch.trans_vec), batch=t(g["batch"]), edges=t(g["edges"]),
                rvlen=t(g["rvlen"]))
-    if any(d in ("reci", "RECI") for d in model.encoder.lattice_params.domain.split("-")):
+    if any(d in ("reci", "RECI", "multihead") for d in model.encoder.lattice_params.domain.split("-")):
         rvecs, vcell, kr = O.reciprocal_geometry(batch.pos, batch.trans_vec, batch.sizes, g["edges"])
         geo.update(rvecs=t(rvecs), vcell=t(vcell), kr=t(kr))
     sizes = t(batch.sizes)

@@ -7,6 +7,8 @@ restatement in ``cf_oracle.c``.  Host glue between kernels follows the reference
 (models/cuda_funcs/*.py), cited in ``reference.py`` and ``oracle.py``.
 """
 import numpy as np
+import dataclasses
+
 import torch
 
 from . import oracle as O
@@ -65,7 +67,7 @@ def max_frames(q_scaled, k, a, pos_ij, tvecs, batch, edges, rvlen, cutoff):
 class FramedProj(torch.autograd.Function):
     @staticmethod
     def forward(ctx, a, pos_ij, tvecs, batch, edges, rvlen, cutoff, dist_max, Wd, W1, W2, W3, f1, f2, f3):
-        cfg = _state["cfg"]
+        cfg = dataclasses.replace(_state["cfg"], H=a.shape[1])      # the "multihead" domain passes half of the heads
         ang = W1 is not None
         a_, Wd_ = a.detach().contiguous(), Wd.detach().contiguous()
         Ws = torch.stack([W1, W2, W3]).detach().contiguous() if ang else None      # (3,1,H,hd,D)
@@ -85,7 +87,7 @@ class FramedProj(torch.autograd.Function):
     def backward(ctx, gz, gv):
         a, pos_ij, tvecs, batch, edges, rvlen, Wd, Ws, fr, z = ctx.saved_tensors
         cutoff, dist_max = ctx.meta
-        cfg = _state["cfg"]
+        cfg = dataclasses.replace(_state["cfg"], H=a.shape[1])
         ang = Ws is not None
         if _state["backend"] == "reference":
             ga, gWd, gWs = _state["rk"].framed_proj_bwd(a, pos_ij, tvecs, batch, edges, dist_max, cfg.wscale_dist, Wd,

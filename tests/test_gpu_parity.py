@@ -331,10 +331,11 @@ def test_whole_model_lightweight_recipe(fused):
                        value_pe_angle_coef=6.0)
 
 
-@pytest.mark.parametrize("domain,frame_method", [("real-reci", "max"), ("RECI", "no"), ("reci", "no")])
+@pytest.mark.parametrize("domain,frame_method", [("real-reci", "max"), ("RECI", "no"), ("reci", "no"), ("multihead", "no")])
 def test_whole_model_reciprocal_domains(domain, frame_method):
-    """Layers with the reciprocal-space logit bias (alone, inverted, and alternating with CrystalFramer layers)
-    in the whole model against the CPU oracle."""
+    """Layers with the reciprocal-space logit bias (alone, inverted, alternating with CrystalFramer layers, and on
+    half of the heads beside the plain real-space encoding on the other half) in the whole model against the CPU
+    oracle."""
     _whole_model_check(2, frame_method, False, domain=domain)
 
 
