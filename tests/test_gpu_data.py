@@ -61,3 +61,44 @@ def test_training_step_from_the_loader_equals_the_step_from_a_host_batch():
         assert (p.grad is None) == (q.grad is None), n
         if p.grad is not None:
             assert torch.equal(p.grad, q.grad), n
+
+
+def test_inference_from_a_reference_layout_checkpoint():
+    """A few training steps with the running weight average, exported in the reference's checkpoint layout, loaded
+    into a fresh model the way the reference's demo loads it, evaluated without gradients: the predictions are the
+    averaged model's, rescaled to the targets' units, and the eval forward (lighter kernels, no per-pair results
+    kept) agrees with the training forward of the same weights."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    dev = torch.device("cuda:0")
+    from crystalframer_b200 import checkpoint, data
+    from crystalframer_b200.optim import FlatAdamW
+    ds = data.StructureSet.synthetic(384, 8)
+    torch.manual_seed(1)
+    model = checkpoint.build_model(num_layers=2, symm_break_noise=0.0).to(dev).train()
+    decay = [p for n, p in model.named_parameters() if not n.endswith("bias")]
+    no_decay = [p for n, p in model.named_parameters() if n.endswith("bias")]
+    opt = FlatAdamW(decay, no_decay, lr=5e-4, betas=(0.9, 0.98), weight_decay=1e-5, max_norm=1.0)
+    for tb in data.EpochLoader(ds, 64, device=dev, epoch=0, seed=0):
+        opt.zero_grad()
+        ((model(tb) - tb.y).abs().mean()).backward()
+        opt.step(average=True)
+    avg_state = dict(model.state_dict())
+    by_id = {id(p): a for p, a in zip(opt.params, opt.averaged_parameters())}
+    for name, p in model.named_parameters():
+        if id(p) in by_id:
+            avg_state[name] = by_id[id(p)].detach().clone()
+    ck = checkpoint.reference_checkpoint_of(model, averaged_state=avg_state, target_std=[3.0], target_mean=[0.5],
+                                            n_averaged=opt.n_averaged)
+    fresh = checkpoint.build_model(num_layers=2, symm_break_noise=0.0).to(dev)
+    checkpoint.load_reference_checkpoint(fresh, ck)
+    batches = list(data.EpochLoader(ds, 128, device=dev, epoch=5, seed=0))
+    mae, pred = checkpoint.evaluate(fresh, batches)
+    # the averaged model itself, un-rescaled, in training mode (the forward that keeps per-pair results)
+    opt.swap_averaged()
+    want = torch.cat([model(tb).detach() for tb in batches]) * 3.0 + 0.5
+    opt.swap_averaged()
+    assert pred.shape == want.shape and torch.allclose(pred, want, rtol=1e-4, atol=1e-5), float((pred - want).abs().max())
+    y = torch.cat([tb.y for tb in batches])
+    assert torch.allclose(mae, (pred - y).abs().mean(0))
+    assert fresh.training                                       # evaluate() leaves the module's mode as it found it

@@ -199,3 +199,33 @@ def test_gradient_exchange_in_pieces_equals_one_allreduce_two_ranks_gloo():
         assert np.allclose(second, whole, rtol=0, atol=1e-6)           # pieces add up to the single all-reduce
         assert np.allclose(flat, 2 * whole, rtol=0, atol=2e-6)         # a finish() with nothing sent reduces everything
     assert np.array_equal(res[0][4], res[1][4])                       # both ranks hold the same sums
+
+
+def test_reference_checkpoint_layout_round_trip():
+    """A checkpoint in the layout of the reference's training module (model.*, swa_model.module.*, target_std,
+    target_mean; models/regression.py:30-59) loads as demo.py:67-88 loads it: averaged weights by default, the last
+    linear layer rescaled to the targets' units."""
+    from crystalframer_b200 import checkpoint
+    torch.manual_seed(0)
+    src = checkpoint.build_model(num_layers=2)
+    avg = {k: v + 0.01 for k, v in src.state_dict().items()}
+    ck = checkpoint.reference_checkpoint_of(src, averaged_state=avg, target_std=[2.5], target_mean=[-0.75], n_averaged=7)
+    keys = set(ck["state_dict"])
+    assert {"target_std", "target_mean", "swa_model.n_averaged"} <= keys
+    assert sum(k.startswith("model.") for k in keys) == sum(k.startswith("swa_model.module.") for k in keys) == len(avg)
+    dst = checkpoint.build_model(num_layers=2)
+    std, mean = checkpoint.load_reference_checkpoint(dst, ck)
+    assert float(std) == 2.5 and float(mean) == -0.75
+    for k, v in dst.state_dict().items():
+        if k == "mlp.3.weight":
+            assert torch.allclose(v, avg[k] * 2.5)
+        elif k == "mlp.3.bias":
+            assert torch.allclose(v, avg[k] * 2.5 - 0.75)
+        else:
+            assert torch.equal(v, avg[k]), k
+    live = checkpoint.build_model(num_layers=2)
+    checkpoint.load_reference_checkpoint(live, ck["state_dict"], prefix="model.", denormalize=False)
+    for k, v in live.state_dict().items():
+        assert torch.equal(v, src.state_dict()[k]), k
+    with pytest.raises(KeyError):
+        checkpoint.load_reference_checkpoint(live, ck, prefix="ema.")
