@@ -348,6 +348,7 @@ __global__ void __launch_bounds__(kFrThreads, CFB_FR_BLOCKS) max_frame_kernel(co
     // found on the first axis is kept for the second (for up to three rounds)
     const bool keep_d2 = ee - eb <= 3 * kFrThreads;
     float d2raw0 = -1.f, d2raw1 = -1.f, d2raw2 = -1.f;
+    float dot0 = 0.f, dot1 = 0.f, dot2 = 0.f;           // and so is the pair's q.k
 
     for (int axis = (A.mode == 2 ? 2 : 1); axis <= (A.mode == 1 ? 1 : 2); axis++) {
         if (tid < rows) {
@@ -379,12 +380,19 @@ __global__ void __launch_bounds__(kFrThreads, CFB_FR_BLOCKS) max_frame_kernel(co
                 float dot = 0.f;
                 const float4* q4 = reinterpret_cast<const float4*>(A.q + (i * H + h) * kFrHd);
                 const float4* k4 = reinterpret_cast<const float4*>(A.k + (j * H + h) * kFrHd);
-                if (!A.is_static)
+                const bool dot_known = keep_d2 && axis == 2 && A.mode == 3;
+                if (dot_known) {
+                    dot = round == 0 ? dot0 : (round == 1 ? dot1 : dot2);
+                } else if (!A.is_static) {
 #pragma unroll
-                for (int d4 = 0; d4 < kFrHd / 4; d4++) {
-                    const float4 u = __ldg(q4 + d4), v = __ldg(k4 + d4);
-                    dot = __fmaf_rn(u.x, v.x, dot); dot = __fmaf_rn(u.y, v.y, dot);
-                    dot = __fmaf_rn(u.z, v.z, dot); dot = __fmaf_rn(u.w, v.w, dot);
+                    for (int d4 = 0; d4 < kFrHd / 4; d4++) {
+                        const float4 u = __ldg(q4 + d4), v = __ldg(k4 + d4);
+                        dot = __fmaf_rn(u.x, v.x, dot); dot = __fmaf_rn(u.y, v.y, dot);
+                        dot = __fmaf_rn(u.z, v.z, dot); dot = __fmaf_rn(u.w, v.w, dot);
+                    }
+                    if (keep_d2) {
+                        if (round == 0) dot0 = dot; else if (round == 1) dot1 = dot; else dot2 = dot;
+                    }
                 }
                 const uint64_t noise_id = (uint64_t)(e * H + h);
                 const int pack = row_R[r];
