@@ -344,6 +344,17 @@ int cfb200_sigma_frames(const float* q_scaled, const float* k, const float* a_ik
                         uint64_t seed_sign, float* frame1, float* frame2, float* frame3, void* workspace,
                         int64_t workspace_bytes, void* stream)
 {
+    return cfb200_sigma_frames_cached(q_scaled, k, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, N, E, cutoff_radius,
+                                      seed_noise, seed_sign, frame1, frame2, frame3, workspace, workspace_bytes, nullptr, 0,
+                                      stream);
+}
+
+int cfb200_sigma_frames_cached(const float* q_scaled, const float* k, const float* a_ik, const float* pos_ij,
+                               const float* tvecs, const float* rvlen, const int64_t* batch, const int64_t* edges,
+                               const int64_t* e_start, int64_t N, int64_t E, float cutoff_radius, uint64_t seed_noise,
+                               uint64_t seed_sign, float* frame1, float* frame2, float* frame3, void* workspace,
+                               int64_t workspace_bytes, const float* pair_list, int cache_range, void* stream)
+{
     if (N < 0 || E < 0) return CFB200_E_SHAPE;
     cfb::Params P;
     int rc = make_params(1.0f, cutoff_radius, P);
@@ -357,12 +368,21 @@ int cfb200_sigma_frames(const float* q_scaled, const float* k, const float* a_ik
     A.q = q_scaled; A.k = k; A.a_ik = a_ik; A.pos_ij = pos_ij; A.tvecs = tvecs; A.rvlen = rvlen; A.batch = batch;
     A.edges = edges; A.e_start = e_start; A.N = N; A.E = E; A.seed_noise = seed_noise; A.seed_sign = seed_sign;
     A.ws = reinterpret_cast<float*>(workspace); A.frame1 = frame1; A.frame2 = frame2; A.frame3 = frame3;
+    A.list = pair_list; A.cache_range = cache_range;
     return cfb::sigma_frames(A, P, S(stream));
 }
 
 int cfb200_sigma_edges(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen, const int64_t* batch,
                        const int64_t* edges, int64_t N, int64_t E, float cutoff_radius, uint64_t seed_noise, float* records,
                        void* stream)
+{
+    return cfb200_sigma_edges_cached(a_ik, pos_ij, tvecs, rvlen, batch, edges, N, E, cutoff_radius, seed_noise, records,
+                                     nullptr, 0, stream);
+}
+
+int cfb200_sigma_edges_cached(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                              const int64_t* batch, const int64_t* edges, int64_t N, int64_t E, float cutoff_radius,
+                              uint64_t seed_noise, float* records, const float* pair_list, int cache_range, void* stream)
 {
     if (N < 0 || E < 0) return CFB200_E_SHAPE;
     cfb::Params P;
@@ -375,6 +395,7 @@ int cfb200_sigma_edges(const float* a_ik, const float* pos_ij, const float* tvec
     memset(&A, 0, sizeof(A));
     A.a_ik = a_ik; A.pos_ij = pos_ij; A.tvecs = tvecs; A.rvlen = rvlen; A.batch = batch; A.edges = edges; A.N = N; A.E = E;
     A.seed_noise = seed_noise; A.ws = records;
+    A.list = pair_list; A.cache_range = cache_range;
     return cfb::sigma_edges(A, P, S(stream));
 }
 

@@ -482,9 +482,9 @@ int cfb200_encoder_layer_fwd(const cfb200_layer_desc* L, const cfb200_layer_weig
         rc = cfb200_pca_frames(G->pos_ij, G->e_start, N, E, L->seed1, St->frames, St->frames + fr, St->frames + 2 * fr, stream);
     } else if (L->frame_method == 2) {
         TmScope tm(CFB200_TM_FRAMES, st);
-        rc = cfb200_sigma_frames(St->q_scaled, St->k, St->a, G->pos_ij, G->tvecs, G->rvlen, G->batch, G->edges, G->e_start, N, E,
-                                 L->cutoff_radius, L->seed1, L->seed2, St->frames, St->frames + fr, St->frames + 2 * fr,
-                                 workspace, workspace_bytes, stream);
+        rc = cfb200_sigma_frames_cached(St->q_scaled, St->k, St->a, G->pos_ij, G->tvecs, G->rvlen, G->batch, G->edges,
+                                        G->e_start, N, E, L->cutoff_radius, L->seed1, L->seed2, St->frames, St->frames + fr,
+                                        St->frames + 2 * fr, workspace, workspace_bytes, G->pair_list, G->cache_range, stream);
     }
     if (rc != CFB200_OK) return rc;
     // lattice sums, value encoding and attention

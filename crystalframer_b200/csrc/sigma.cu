@@ -24,30 +24,27 @@ struct SgArgs {
     uint64_t seed_noise, seed_sign;
     float* ws;                       // (E,H,11): z, six moments, nearest d^2, nearest direction
     float* frame1; float* frame2; float* frame3;
+    const float* list;               // optional per-pair sorted translation lists (pair_list_kernel), box (cache_range)^3
+    int cache_range;
 };
 
-// thread = (pair, head)
-__global__ void __launch_bounds__(256) sigma_edges_kernel(const SgArgs A, const Params P)
+// One (pair, head) by a sweep over its whole box of translations: two passes (nearest distance, then weights and
+// moments), the nearest non-zero image on the way.  The mapping of the reference's real_enc_sigma_fwd.cu; here it
+// serves the pairs whose box the sorted list does not cover.
+__device__ void sigma_pair_sweep(const SgArgs& A, const Params& P, const int64_t e, const int h, const int64_t c,
+                                 const float a, const int R1, const int R2, const int R3)
 {
-    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int H = P.H;
-    if (tid >= A.E * H) return;
-    const int64_t e = tid / H;
-    const int h = (int)(tid - e * H);
-    const int64_t i = A.edges[e], c = A.batch[i];
+    const int64_t tid = e * H + h;
     const float rx = __ldg(A.pos_ij + 3 * e), ry = __ldg(A.pos_ij + 3 * e + 1), rz = __ldg(A.pos_ij + 3 * e + 2);
     const float* Tc = A.tvecs + 9 * c;
     const float t1x = __ldg(Tc), t1y = __ldg(Tc + 1), t1z = __ldg(Tc + 2);
     const float t2x = __ldg(Tc + 3), t2y = __ldg(Tc + 4), t2z = __ldg(Tc + 5);
     const float t3x = __ldg(Tc + 6), t3y = __ldg(Tc + 7), t3z = __ldg(Tc + 8);
-    const float a = __ldg(A.a_ik + i * H + h);
-    int R[3];
-#pragma unroll
-    for (int d = 0; d < 3; d++) R[d] = lattice_range_1d(P, a, P.cutoff_radius != 0.0f ? __ldg(A.rvlen + 3 * c + d) : 0.0f);
     float d2min = 1e10f;
-    for (int n1 = -R[0]; n1 <= R[0]; n1++)
-        for (int n2 = -R[1]; n2 <= R[1]; n2++)
-            for (int n3 = -R[2]; n3 <= R[2]; n3++) {
+    for (int n1 = -R1; n1 <= R1; n1++)
+        for (int n2 = -R2; n2 <= R2; n2++)
+            for (int n3 = -R3; n3 <= R3; n3++) {
                 const float dx = fmaf(t3x, (float)n3, fmaf(t2x, (float)n2, fmaf(t1x, (float)n1, rx)));
                 const float dy = fmaf(t3y, (float)n3, fmaf(t2y, (float)n2, fmaf(t1y, (float)n1, ry)));
                 const float dz = fmaf(t3z, (float)n3, fmaf(t2z, (float)n2, fmaf(t1z, (float)n1, rz)));
@@ -56,9 +53,9 @@ __global__ void __launch_bounds__(256) sigma_edges_kernel(const SgArgs A, const 
     float sum = 0.f, m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f, m4 = 0.f, m5 = 0.f;
     float best = 1e8f, bx = 0.f, by = 0.f, bz = 0.f;
     int t = 0;
-    for (int n1 = -R[0]; n1 <= R[0]; n1++)
-        for (int n2 = -R[1]; n2 <= R[1]; n2++)
-            for (int n3 = -R[2]; n3 <= R[2]; n3++, t++) {
+    for (int n1 = -R1; n1 <= R1; n1++)
+        for (int n2 = -R2; n2 <= R2; n2++)
+            for (int n3 = -R3; n3 <= R3; n3++, t++) {
                 const float dx = fmaf(t3x, (float)n3, fmaf(t2x, (float)n2, fmaf(t1x, (float)n1, rx)));
                 const float dy = fmaf(t3y, (float)n3, fmaf(t2y, (float)n2, fmaf(t1y, (float)n1, ry)));
                 const float dz = fmaf(t3z, (float)n3, fmaf(t2z, (float)n2, fmaf(t1z, (float)n1, rz)));
@@ -82,6 +79,131 @@ __global__ void __launch_bounds__(256) sigma_edges_kernel(const SgArgs A, const 
     o[7] = best;
     const float rn = rsqrtf(fmaxf(bx * bx + by * by + bz * bz, 1e-30f));
     o[8] = bx * rn; o[9] = by * rn; o[10] = bz * rn;
+}
+
+// thread = (pair, head): every pair by the sweep (no sorted lists at hand, or a head count that does not divide 32)
+__global__ void __launch_bounds__(256) sigma_edges_kernel(const SgArgs A, const Params P)
+{
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int H = P.H;
+    if (tid >= A.E * H) return;
+    const int64_t e = tid / H;
+    const int h = (int)(tid - e * H);
+    const int64_t i = A.edges[e], c = A.batch[i];
+    const float a = __ldg(A.a_ik + i * H + h);
+    int R[3];
+#pragma unroll
+    for (int d = 0; d < 3; d++) R[d] = lattice_range_1d(P, a, P.cutoff_radius != 0.0f ? __ldg(A.rvlen + 3 * c + d) : 0.0f);
+    sigma_pair_sweep(A, P, e, h, c, a, R[0], R[1], R[2]);
+}
+
+// warp = pair, lane = (slot, head) with 32 / H slots per head.  The weight exp(a (d^2 - d^2_min)) falls with the
+// distance, so the translations that matter to a (pair, head) -- those above the pruning threshold of the lattice-sum
+// kernels, and the nearest non-zero image with whatever lies within the noise amplitude of it -- are a prefix of the
+// pair's sorted list, which all heads share: the slots of a head walk that prefix in turns (typically 3-4 entries
+// each instead of two sweeps over 125 translations), their partial sums meet by shuffles.  A (pair, head) whose box
+// is larger than the listed one and whose prefix could reach outside it falls back to the sweep.
+constexpr int kSgListWarps = 8;
+
+__global__ void __launch_bounds__(kSgListWarps * 32) sigma_edges_list_kernel(const SgArgs A, const Params P)
+{
+    const int H = P.H, lane = threadIdx.x & 31;
+    const int64_t e = (int64_t)blockIdx.x * kSgListWarps + (threadIdx.x >> 5);
+    if (e >= A.E) return;
+    const int h = lane % H, slot = lane / H, slots = 32 / H;
+    const int64_t i = A.edges[e], c = A.batch[i];
+    const float a = __ldg(A.a_ik + i * H + h);
+    int R1, R2, R3;
+    {
+        const bool cut = P.cutoff_radius != 0.0f;
+        R1 = lattice_range_1d(P, a, cut ? __ldg(A.rvlen + 3 * c) : 0.0f);
+        R2 = lattice_range_1d(P, a, cut ? __ldg(A.rvlen + 3 * c + 1) : 0.0f);
+        R3 = lattice_range_1d(P, a, cut ? __ldg(A.rvlen + 3 * c + 2) : 0.0f);
+    }
+    const float* list = A.list + (size_t)e * kListStride;
+    // the pair's first 32 distances: the smallest, and the smallest that counts as non-zero
+    const float dl = __ldg(list + lane);
+    const float d2min = __shfl_sync(0xffffffffu, dl, 0);
+    const unsigned nz = __ballot_sync(0xffffffffu, dl > 1.0001e-5f && dl < 1e29f);
+    const unsigned unclear = __ballot_sync(0xffffffffu, dl > 0.9999e-5f && dl <= 1.0001e-5f);
+    const float d2nz = nz != 0u ? __shfl_sync(0xffffffffu, dl, __ffs(nz) - 1) : -1.f;
+    Cell cell;
+    {
+        const float* Tc = A.tvecs + 9 * c;
+        cell.t1x = __ldg(Tc); cell.t1y = __ldg(Tc + 1); cell.t1z = __ldg(Tc + 2);
+        cell.t2x = __ldg(Tc + 3); cell.t2y = __ldg(Tc + 4); cell.t2z = __ldg(Tc + 5);
+        cell.t3x = __ldg(Tc + 6); cell.t3y = __ldg(Tc + 7); cell.t3z = __ldg(Tc + 8);
+        cell.rx = __ldg(A.pos_ij + 3 * e); cell.ry = __ldg(A.pos_ij + 3 * e + 1); cell.rz = __ldg(A.pos_ij + 3 * e + 2);
+    }
+    const int C = A.cache_range;
+    const bool same_box = R1 == C && R2 == C && R3 == C;
+    const bool wider = !same_box && R1 >= C && R2 >= C && R3 >= C;
+    const float reach2 = wider ? box_reach2(cell, C) : 1e38f;
+    // list distances and the sweep's differ in the last bits (another order of the fused operations): margins
+    const float w_limit = a < 0.f ? d2min + P.prune / (-a) : 1e38f;
+    const float nz_limit = d2nz + fabsf(P.noise) + fabsf(d2nz) * 8e-6f + 1e-12f;
+    const float far = fmaxf(w_limit, nz_limit);
+    const bool usable = a < 0.f && d2nz >= 0.f && unclear == 0u && (same_box || (wider && far < reach2));
+    if (!usable) {
+        if (slot == 0) sigma_pair_sweep(A, P, e, h, c, a, R1, R2, R3);
+    }
+    // (no early exit: the shuffles below are warp-wide; lanes of a head that took the sweep carry zeros)
+    float sum = 0.f, m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f, m4 = 0.f, m5 = 0.f;
+    float best = 1e8f, bx = 0.f, by = 0.f, bz = 0.f;
+    int best_t = 0x7fffffff;
+    if (usable) {
+        const int64_t tid = e * H + h;
+        const int L2 = 2 * R2 + 1, L3 = 2 * R3 + 1;
+        for (int s = slot; s < kListLen; s += slots) {
+            const float d2l = __ldg(list + s);
+            if (!(d2l <= far)) break;                       // sorted: nothing behind it matters either
+            if (d2l <= w_limit) {
+                const float dx = __ldg(list + kListLen + s), dy = __ldg(list + 2 * kListLen + s), dz = __ldg(list + 3 * kListLen + s);
+                const float w = ex2_approx(a * (d2l - d2min) * kLog2e);
+                sum += w;
+                const float wx = dx * w, wy = dy * w, wz = dz * w;
+                m0 = fmaf(dx, wx, m0); m1 = fmaf(dx, wy, m1); m2 = fmaf(dx, wz, m2);
+                m3 = fmaf(dy, wy, m3); m4 = fmaf(dy, wz, m4); m5 = fmaf(dz, wz, m5);
+            }
+            if (d2l > 0.9999e-5f && d2l <= nz_limit) {
+                // a candidate for the nearest non-zero image: the sweep's own arithmetic decides
+                const int code = __float_as_int(__ldg(list + 4 * kListLen + s));
+                const int n1 = (code & 255) - C, n2 = ((code >> 8) & 255) - C, n3 = ((code >> 16) & 255) - C;
+                const float dx = fmaf(cell.t3x, (float)n3, fmaf(cell.t2x, (float)n2, fmaf(cell.t1x, (float)n1, cell.rx)));
+                const float dy = fmaf(cell.t3y, (float)n3, fmaf(cell.t2y, (float)n2, fmaf(cell.t1y, (float)n1, cell.ry)));
+                const float dz = fmaf(cell.t3z, (float)n3, fmaf(cell.t2z, (float)n2, fmaf(cell.t1z, (float)n1, cell.rz)));
+                const float d2 = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
+                if (d2 > 1e-5f) {
+                    const int t = ((n1 + R1) * L2 + (n2 + R2)) * L3 + (n3 + R3);
+                    float cand = d2;
+                    if (P.noise != 0.0f)
+                        cand = d2 + (float)(((double)hash_uniform(A.seed_noise, (uint64_t)tid, (uint32_t)t) - 0.5) * (double)P.noise);
+                    if (cand < best || (cand == best && t < best_t)) { best = cand; best_t = t; bx = dx; by = dy; bz = dz; }
+                }
+            }
+        }
+    }
+    // the slots of a head meet: lanes h, h + H, h + 2H, ...
+    for (int o = H; o < 32; o <<= 1) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        m0 += __shfl_xor_sync(0xffffffffu, m0, o); m1 += __shfl_xor_sync(0xffffffffu, m1, o);
+        m2 += __shfl_xor_sync(0xffffffffu, m2, o); m3 += __shfl_xor_sync(0xffffffffu, m3, o);
+        m4 += __shfl_xor_sync(0xffffffffu, m4, o); m5 += __shfl_xor_sync(0xffffffffu, m5, o);
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int ot = __shfl_xor_sync(0xffffffffu, best_t, o);
+        const float ox = __shfl_xor_sync(0xffffffffu, bx, o), oy = __shfl_xor_sync(0xffffffffu, by, o),
+                    oz = __shfl_xor_sync(0xffffffffu, bz, o);
+        if (ob < best || (ob == best && ot < best_t)) { best = ob; best_t = ot; bx = ox; by = oy; bz = oz; }
+    }
+    if (usable && slot == 0) {
+        const float inv = 1.0f / sum;
+        float* o = A.ws + (e * H + h) * 11;
+        o[0] = logf(sum) + d2min * a;
+        o[1] = m0 * inv; o[2] = m1 * inv; o[3] = m2 * inv; o[4] = m3 * inv; o[5] = m4 * inv; o[6] = m5 * inv;
+        o[7] = best;
+        const float rn = rsqrtf(fmaxf(bx * bx + by * by + bz * bz, 1e-30f));
+        o[8] = bx * rn; o[9] = by * rn; o[10] = bz * rn;
+    }
 }
 
 // eigen-decomposition of a symmetric 3x3 matrix by cyclic Jacobi rotations; eigenvalues ascending,
@@ -267,20 +389,28 @@ int pca_frames(const float* pos_ij, const int64_t* e_start, int64_t N, int H, ui
     return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
 }
 
+static void launch_sigma_edges(const SgArgs& A, const Params& P, cudaStream_t st)
+{
+    if (A.list != nullptr && P.H <= 32 && 32 % P.H == 0) {
+        sigma_edges_list_kernel<<<(unsigned)((A.E + kSgListWarps - 1) / kSgListWarps), kSgListWarps * 32, 0, st>>>(A, P);
+    } else {
+        const int64_t n1 = A.E * P.H;
+        sigma_edges_kernel<<<(unsigned)((n1 + 255) / 256), 256, 0, st>>>(A, P);
+    }
+}
+
 // the per-pair records alone (what the reference's real_enc_sigma_fwd.cu leaves, plus the logit it omits)
 int sigma_edges(const SgArgs& A, const Params& P, cudaStream_t st)
 {
     if (A.N == 0 || A.E == 0) return CFB200_OK;
-    const int64_t n1 = A.E * P.H;
-    sigma_edges_kernel<<<(unsigned)((n1 + 255) / 256), 256, 0, st>>>(A, P);
+    launch_sigma_edges(A, P, st);
     return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
 }
 
 int sigma_frames(const SgArgs& A, const Params& P, cudaStream_t st)
 {
     if (A.N == 0 || A.E == 0) return CFB200_OK;
-    const int64_t n1 = A.E * P.H;
-    sigma_edges_kernel<<<(unsigned)((n1 + 255) / 256), 256, 0, st>>>(A, P);
+    launch_sigma_edges(A, P, st);
     const int64_t n2 = A.N * P.H;
     sigma_frames_kernel<<<(unsigned)((n2 + 3) / 4), 128, 0, st>>>(A, P);
     return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;

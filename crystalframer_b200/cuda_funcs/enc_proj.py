@@ -3,7 +3,7 @@ per-pair second moments of the weighted-PCA frames."""
 import torch
 
 from .. import _lib
-from .common import csr_offsets, f32c
+from .common import csr_offsets, f32c, pair_geometry
 from .framed_proj import _w3
 from .kernel_manager import current_config
 from .max_frame import _draw_seed
@@ -21,8 +21,9 @@ def _sigma_records(a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_n, cutoff
     seed_noise = _draw_seed()       # ... and one for real_enc_sigma_fwd.cu (models/cuda_funcs/real_space_enc_proj.py:88,98)
     rec = torch.empty((E, H, 11), device=dev, dtype=torch.float32)
     p, ip = _lib.ptr, _lib.iptr
-    _lib.invoke("cfb200_sigma_edges", 1, dev, p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), N, E, cutoff, seed_noise,
-                p(rec))
+    _, plist, prange = pair_geometry(rpos_ij_e, tvecs_n, batch_i, edge_ij_e, cutoff)
+    _lib.invoke("cfb200_sigma_edges_cached", 1, dev, p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), N, E, cutoff,
+                seed_noise, p(rec), p(plist), prange)
     return rec, seed_noise
 
 

@@ -114,8 +114,10 @@ def weighted_pca_frames(q, k, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvle
     nbytes = int(_lib.lib().cfb200_sigma_frames_workspace_bytes(N, E))
     ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
     p, ip = _lib.ptr, _lib.iptr
-    _lib.invoke("cfb200_sigma_frames", 2, dev, p(qq), p(kk), p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges),
-                ip(e_start), N, E, cutoff, seed_noise, seed_sign, p(f[0]), p(f[1]), p(f[2]), ws.data_ptr(), nbytes)
+    _, plist, prange = pair_geometry(rpos_ij_e, tvecs_n, batch_i, edge_ij_e, cutoff)
+    _lib.invoke("cfb200_sigma_frames_cached", 2, dev, p(qq), p(kk), p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges),
+                ip(e_start), N, E, cutoff, seed_noise, seed_sign, p(f[0]), p(f[1]), p(f[2]), ws.data_ptr(), nbytes,
+                p(plist), prange)
     return f[0], f[1], f[2], seed_noise, seed_sign
 
 

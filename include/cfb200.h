@@ -192,6 +192,22 @@ int cfb200_sigma_frames(const float* q_scaled, const float* k, const float* a_ik
                         float* frame2, float* frame3, void* workspace, int64_t workspace_bytes,
                         void* stream);
 
+/* cfb200_sigma_frames / cfb200_sigma_edges with the per-pair sorted translation lists of cfb200_pair_cache
+ * (pair_list (E,5,128), valid for lattice ranges (cache_range)^3; NULL: every pair is swept): the translations that
+ * carry weight are a prefix of a pair's list, shared by all heads; pairs whose box the list does not cover are
+ * swept as before.  Needs a head count that divides 32 to use the lists. */
+int cfb200_sigma_frames_cached(const float* q_scaled, const float* k, const float* a_ik, const float* pos_ij,
+                               const float* tvecs, const float* rvlen, const int64_t* batch,
+                               const int64_t* edges, const int64_t* e_start, int64_t N, int64_t E,
+                               float cutoff_radius, uint64_t seed_noise, uint64_t seed_sign,
+                               float* frame1, float* frame2, float* frame3, void* workspace,
+                               int64_t workspace_bytes, const float* pair_list, int cache_range,
+                               void* stream);
+int cfb200_sigma_edges_cached(const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
+                              const int64_t* batch, const int64_t* edges, int64_t N, int64_t E,
+                              float cutoff_radius, uint64_t seed_noise, float* records,
+                              const float* pair_list, int cache_range, void* stream);
+
 /* Replaces RealEncodingWithFramedProjFuncCUDA.forward
  * (models/cuda_funcs/real_space_framed_proj.py:21-120; kernels
  * real_enc_frame_proj_fwd_length.cu, real_enc_frame_proj_fwd_angle.cu).

@@ -612,3 +612,45 @@ def test_fused_attention_entry_points(workload, nc, use_list, saved):
     for x in range(3):
         _close_reduction(f"gW_ang{x + 1}", gW[:, :, 64 * (x + 1):64 * (x + 2)], gWa_w[x], gWa_64[x])
     assert _lib.read_status() == 0
+
+
+@pytest.mark.parametrize("noise", [0.0, 1e-5])
+@pytest.mark.parametrize("workload,nc", [("cfg1", None), ("cfg2", 48)])
+def test_second_moment_records_with_and_without_sorted_lists(workload, nc, noise):
+    """cfb200_sigma_edges_cached -- warp per pair over the prefix of the pair's sorted translation list -- and the
+    sweep over the whole box (no list) against the oracle: logit and the six weight-averaged second moments within
+    tolerance (the list kernel leaves out translations below the pruning threshold of the lattice-sum kernels),
+    the nearest non-zero image (its distance with the noise term, its direction) identical between the two kernels
+    and equal to the oracle's.  The small cells of the second workload have boxes wider than the listed one."""
+    dev = _cuda()
+    from crystalframer_b200 import _lib
+    from crystalframer_b200.cuda_funcs.common import pair_geometry
+    from oracle import oracle as O
+    _configure(noise=noise)
+    P = make_problem(workload, num_crystals=nc, noise=noise)
+    g = _geometry(P, dev)
+    N, H = P["a"].shape
+    E = P["geo"]["edges"].shape[1]
+    a = _t(P["a"], dev)
+    seed = 0x1234ABCD5678
+    _, plist, prange = pair_geometry(g["pos_ij"], g["tvecs"], g["batch"], g["edges"], -3.5)
+    assert plist is not None and prange == 2
+    p, ip = _lib.ptr, _lib.iptr
+    rec = {}
+    for name, lst in (("list", plist), ("sweep", None)):
+        out = torch.full((E, H, 11), float("nan"), device=dev)
+        _lib.invoke("cfb200_sigma_edges_cached", 1, dev, p(a), p(g["pos_ij"]), p(g["tvecs"]), p(g["rvlen"]), ip(g["batch"]),
+                    ip(g["edges"]), N, E, -3.5, seed, p(out), p(lst), prange)
+        rec[name] = out.cpu().numpy()
+        assert np.isfinite(rec[name]).all(), name
+    cfg = O.Config(symm_break_noise=noise)
+    z, sig, nd2, ndir = O.sigma_edges(cfg, P["a"], P["geo"]["pos_ij"], P["batch"].trans_vec, P["geo"]["rvlen"],
+                                      P["geo"]["batch"], P["geo"]["edges"], seed=seed)
+    scale = max(1.0, float(np.abs(sig).max()))
+    for name in ("list", "sweep"):
+        _close(f"z ({name})", rec[name][..., 0], z, 1e-4, 1e-5)
+        _close(f"moments ({name})", rec[name][..., 1:7], sig, 1e-4, 1e-5 * scale)
+        _close(f"nearest d2 ({name})", rec[name][..., 7], nd2, 1e-6, 1e-7)
+        _close(f"nearest direction ({name})", rec[name][..., 8:11], ndir, 1e-5, 1e-6)
+    assert np.array_equal(rec["list"][..., 7:11], rec["sweep"][..., 7:11])
+    _configure(noise=0.0)
