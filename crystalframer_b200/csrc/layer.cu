@@ -639,17 +639,16 @@ int cfb200_encoder_layer_bwd(const cfb200_layer_desc* L, const cfb200_layer_weig
         C.ga = ga; C.gqs = gqs; C.gq = gq; C.gw = gw_lat; C.partial = coef_part;
         if ((rc = cfb::coef_bwd(C, st)) != CFB200_OK) return rc;
     }
-    // g_x = gx1 + gq Wq + gk Wk + gv Wv
+    // Weight and bias gradients of the in-projections (their inputs are the last results of the chain above) on the
+    // side stream, behind the early group, beside the data-gradient product below.
     {
-        TmScope tm(CFB200_TM_LINEAR_BWD, st);
-        memset(&g, 0, sizeof(g));
-        g.seg[0] = {gq, W->q_proj, D, D, D}; g.seg[1] = {gk, W->k_proj, D, D, D}; g.seg[2] = {gv, W->v_proj, D, D, D};
-        g.nseg = 3; g.M = (int)N; g.N = D; g.C = g_x; g.ldc = D; g.resid = gx1; g.ldr = D;
-        if ((rc = cfb::gemm(g, true, st)) != CFB200_OK) return rc;
-    }
-    // weight and bias gradients of the in-projections (their inputs are the last results of the chain above)
-    {
-        TmScope tm_w(CFB200_TM_WGRAD, st);
+        cudaStream_t sw = st;
+        if (lane != nullptr) {
+            if (cudaEventRecord(lane->fork, st) != cudaSuccess || cudaStreamWaitEvent(lane->stream, lane->fork, 0) != cudaSuccess)
+                return CFB200_E_CUDA;
+            sw = lane->stream;
+        }
+        TmScope tm_w(CFB200_TM_WGRAD, sw);
         cfb::WgArgs Wg;
         memset(&Wg, 0, sizeof(Wg));
         Wg.M = (int)N; Wg.ws = wg + early_floats; Wg.accumulate = accumulate;
@@ -660,9 +659,19 @@ int cfb200_encoder_layer_bwd(const cfb200_layer_desc* L, const cfb200_layer_weig
         add(gq, D, D, x, D, D, Gr->q_proj, D, Gr->in_bias);
         add(gk, D, D, x, D, D, Gr->k_proj, D, Gr->in_bias + D);
         add(gv, D, D, x, D, D, Gr->v_proj, D, Gr->in_bias + 2 * D);
-        if ((rc = cfb::wgrad(Wg, wg_floats - early_floats, st)) != CFB200_OK) return rc;
+        if ((rc = cfb::wgrad(Wg, wg_floats - early_floats, sw)) != CFB200_OK) return rc;
+        // the side stream works in order: this record also stands for the early group
+        if (lane != nullptr && cudaEventRecord(lane->join, sw) != cudaSuccess) return CFB200_E_CUDA;
     }
-    // the early weight gradients must be complete when this call's work is (the next call reuses the workspace)
+    // g_x = gx1 + gq Wq + gk Wk + gv Wv
+    {
+        TmScope tm(CFB200_TM_LINEAR_BWD, st);
+        memset(&g, 0, sizeof(g));
+        g.seg[0] = {gq, W->q_proj, D, D, D}; g.seg[1] = {gk, W->k_proj, D, D, D}; g.seg[2] = {gv, W->v_proj, D, D, D};
+        g.nseg = 3; g.M = (int)N; g.N = D; g.C = g_x; g.ldc = D; g.resid = gx1; g.ldr = D;
+        if ((rc = cfb::gemm(g, true, st)) != CFB200_OK) return rc;
+    }
+    // the weight gradients must be complete when this call's work is (the next call reuses the workspace)
     if (lane != nullptr && cudaStreamWaitEvent(st, lane->join, 0) != cudaSuccess) return CFB200_E_CUDA;
     if (accumulate) {
         cfb::axpy_kernel<<<(D + 127) / 128, 128, 0, st>>>(Gr->lattice_pos, gw_tmp, D);
