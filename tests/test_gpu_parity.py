@@ -416,7 +416,17 @@ def test_reciprocal_encoding_golden_and_reference_gpu():
     _close("ga vs reference kernels", at.grad.cpu().numpy(), gar.cpu().numpy(), 1e-4, 1e-5 * max(1.0, float(gar.abs().max())))
 
 
-def _whole_model_check(layers, frame_method, fused, **recipe):
+def test_whole_model_largest_cell_and_single_atoms():
+    """The one-call layers on a batch that holds the reference's largest cell (320 atoms, 102 400 pairs: its atoms'
+    tasks are cut into chunks) beside single-atom crystals and a small one, against the CPU oracle."""
+    from crystalframer_b200 import synth
+    big = synth.make_batch(1, 9, size_dist="uniform", size_lo=320, size_hi=320, len_lo=18.0, len_hi=22.0)
+    ones = synth.make_batch(3, 10, size_dist="uniform", size_lo=1, size_hi=1, len_lo=3.0, len_hi=6.0)
+    small = synth.make_batch(1, 11, size_dist="uniform", size_lo=7, size_hi=7, len_lo=4.0, len_hi=8.0)
+    _whole_model_check(1, "max", True, batch=synth.concat([ones, big, small]))
+
+
+def _whole_model_check(layers, frame_method, fused, batch=None, **recipe):
     """Forward and backward of the whole model (species embedding, encoder layers, mean pooling,
     MLP head) on the GPU against the same weights run on the host cores through the oracle:
     8 crystals of 4-16 atoms, float32, symmetry-breaking noise off.
@@ -442,7 +452,7 @@ def _whole_model_check(layers, frame_method, fused, **recipe):
     from crystalframer_b200 import cuda_funcs as F
     F.compile_kernels(2, 8, 16, 64, mp.value_pe_angle_real, 16, True, 0, mp.value_pe_dist_wscale, mp.value_pe_angle_wscale,
                       mp.value_pe_dist_coef, mp.value_pe_angle_coef, 0.0)
-    b = synth.make_workload("cfg1")
+    b = synth.make_workload("cfg1") if batch is None else batch
     y = np.random.default_rng(0).normal(size=(len(b.sizes), 1)).astype(np.float32)
     tb = data.host_batch(b, y, pinned=False).to(dev, non_blocking=False)
     if fused:
