@@ -73,6 +73,8 @@ SIGNATURES = {
     "cfb200_framed_proj_fwd_cached": (ctypes.c_int, [vp] * 6 + [i64, i64, f32, f32] + [vp] * 11 + [ctypes.c_int, vp]),
     "cfb200_framed_proj_bwd_cached": (ctypes.c_int, [vp] * 7 + [i64, i64, f32, f32] + [vp] * 16 + [i64, vp, ctypes.c_int, vp]),
     "cfb200_sigma_edges": (ctypes.c_int, [vp] * 6 + [i64, i64, f32, u64, vp, vp]),
+    "cfb200_max_frame3_workspace_bytes": (i64, [i64, i64]),
+    "cfb200_max_frame3": (ctypes.c_int, [vp] * 9 + [i64, i64, f32, u64] + [vp] * 5 + [i64, vp]),
     "cfb200_sigma_edges_cached": (ctypes.c_int, [vp] * 6 + [i64, i64, f32, u64, vp, vp, ctypes.c_int, vp]),
     "cfb200_sigma_frames_cached": (ctypes.c_int, [vp] * 9 + [i64, i64, f32, u64, u64] + [vp] * 4 + [i64, vp, ctypes.c_int, vp]),
     "cfb200_sigma_frames_workspace_bytes": (i64, [i64, i64]),

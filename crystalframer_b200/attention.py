@@ -7,7 +7,7 @@ arguments, same parameter names, shapes and initialisation (so released checkpoi
 data-dependent ``gauss_scale`` state.  Input / output projections and the Gaussian-coefficient
 pipeline stay in PyTorch; everything between them runs in libcfb200.
 
-Domains: "real" with frame methods "max", "max_static", "lattice", "pca", "weighted_pca" (CrystalFramer)
+Domains: "real" with frame methods "max", "max_static", "max_wo_orthogonal", "lattice", "pca", "weighted_pca" (CrystalFramer)
 and "no" (plain Crystalformer distance encoding); "reci" / "RECI" (plain Crystalformer's reciprocal-space
 logit bias, no value encoding), also alternating by layer ("real-reci"); "multihead" (first half of the heads in
 real space, second half in reciprocal space) for the plain Crystalformer encoding (frame_method "no").
@@ -22,7 +22,7 @@ from torch.nn import Module, Parameter
 from torch.nn.init import constant_, normal_, xavier_uniform_
 from torch.nn.modules.linear import NonDynamicallyQuantizableLinear
 
-from .cuda_funcs import (ComputeFrame1MaximumMethodCUDA, ComputeFrame1MaximumStaticMethodCUDA,
+from .cuda_funcs import (ComputeFrame1MaximumMethodCUDA, ComputeFrame1MaximumStaticMethodCUDA, ComputeFrame3MaximumMethodCUDA,
                          ComputeFrame2MaximumMethodCUDA, ComputeFrame2MaximumStaticMethodCUDA, ComputeLatticeFrameCUDA, ComputePCAFrame,
                          FusedDotProductAttentionCUDA, RealEncodingWithFramedProjFuncCUDA,
                          RealPeriodicEncodingWithProjFuncCUDA, ReciPeriodicEncodingFuncCUDA, max_frames_fused, max_static_frames_fused,
@@ -43,9 +43,22 @@ def _scaled_dot_product_attention(q, k, v, batch, batch_kv, edges, attn_weights=
 
 def compute_frame_maximum_method_(q, k, v, alpha, pos, dist2_min, tvecs, batch, edges, proj, K, dist_max, wscale,
                                   frame_method, this_epoch=None, rvecs=None, cutoff=None):
-    """models/indexed_lattice_multi_head_attention_cuda.py:435-493 for frame_method "max" and "max_static"."""
-    if frame_method not in ("max", "max_static"):
+    """models/indexed_lattice_multi_head_attention_cuda.py:435-493 for frame_method "max", "max_static" and
+    "max_wo_orthogonal"."""
+    if frame_method not in ("max", "max_static", "max_wo_orthogonal"):
         raise NotImplementedError(f"frame_method={frame_method}")
+    if frame_method == "max_wo_orthogonal":
+        # the second axis stays as selected, the third is selected like the first two (:449-455, :483-488)
+        rvlen = torch.norm(rvecs, 2, dim=-1) if cutoff is not None else None
+        adap = (rvlen, cutoff) if cutoff is not None else ()
+        with torch.no_grad():
+            qs = q / math.sqrt(q.shape[-1])
+            f1 = ComputeFrame1MaximumMethodCUDA.apply(qs, k, v, alpha, pos, dist2_min, tvecs, batch, edges, K, dist_max, wscale, *adap)
+            f2 = ComputeFrame2MaximumMethodCUDA.apply(qs, k, v, alpha, pos, dist2_min, tvecs, batch, edges, K, dist_max, wscale,
+                                                      f1, *adap)
+            f3 = ComputeFrame3MaximumMethodCUDA.apply(qs, k, v, alpha, pos, dist2_min, tvecs, batch, edges, K, dist_max, wscale,
+                                                      f1, f2, *adap)
+        return f1, f2, f3
     rvlen = torch.norm(rvecs, 2, dim=-1) if cutoff is not None else None
     qs = q / math.sqrt(q.shape[-1])
     if FUSED_FRAMES:
@@ -79,7 +92,7 @@ def compute_real_domain_attn_frame_proj(q, k, v, batch_q, batch_kv, edges, pos, 
     elif params.adaptive_cutoff_sigma > 0:
         adap = (rvecs, params.scale_real * params.gauss_lb_real ** (-0.5) * params.adaptive_cutoff_sigma)
     rv_args = (torch.norm(adap[0], 2, dim=-1), adap[1]) if adap else ()
-    if params.frame_method in ("max", "max_static"):
+    if params.frame_method in ("max", "max_static", "max_wo_orthogonal"):
         f1, f2, f3 = compute_frame_maximum_method_(q, k, None, alpha, pos, dist2_min, tvecs, batch_q, edges,
                                                    pe_dist_proj, K, dist_max, wscale, params.frame_method, this_epoch, *adap)
         W1, W2, W3 = proj_angle1, proj_angle2, proj_angle3

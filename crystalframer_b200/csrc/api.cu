@@ -235,6 +235,36 @@ int cfb200_max_frame(int axis, const float* q_scaled, const float* k, const floa
                          sel_edge, sel_image, stream);
 }
 
+int64_t cfb200_max_frame3_workspace_bytes(int64_t N, int64_t E)
+{
+    if (!g_configured || N < 0 || E < 0) return -1;
+    return (int64_t)((size_t)E * g_cfg.num_heads * 4 * sizeof(float));
+}
+
+int cfb200_max_frame3(const float* q_scaled, const float* k, const float* a_ik, const float* pos_ij, const float* tvecs,
+                      const float* rvlen, const int64_t* batch, const int64_t* edges, const int64_t* e_start, int64_t N,
+                      int64_t E, float cutoff_radius, uint64_t seed, const float* frame1, const float* frame2,
+                      float* frame3, int64_t* sel_edge, void* workspace, int64_t workspace_bytes, void* stream)
+{
+    if (N < 0 || E < 0) return CFB200_E_SHAPE;
+    cfb::Params P;
+    int rc = make_params(1.0f, cutoff_radius, P);
+    if (rc != CFB200_OK) return rc;
+    if (g_cfg.head_dim != 16) return CFB200_E_UNSUPPORTED;
+    if (N == 0 || E == 0) return CFB200_OK;
+    if (!q_scaled || !k || !a_ik || !pos_ij || !tvecs || !batch || !edges || !e_start || !frame1 || !frame2 || !frame3)
+        return CFB200_E_NULL;
+    if (cutoff_radius != 0.0f && rvlen == nullptr) return CFB200_E_NULL;
+    if (workspace == nullptr || workspace_bytes < cfb200_max_frame3_workspace_bytes(N, E)) return CFB200_E_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 15) != 0) return CFB200_E_SHAPE;
+    cfb::Fr3Args A;
+    memset(&A, 0, sizeof(A));
+    A.q = q_scaled; A.k = k; A.a_ik = a_ik; A.pos_ij = pos_ij; A.tvecs = tvecs; A.rvlen = rvlen; A.batch = batch;
+    A.edges = edges; A.e_start = e_start; A.frame1 = frame1; A.frame2 = frame2; A.N = N; A.E = E; A.seed = seed;
+    A.cand = reinterpret_cast<float*>(workspace); A.frame3 = frame3; A.sel_edge = sel_edge;
+    return cfb::third_axis(A, P, S(stream));
+}
+
 int cfb200_max_frame_static(int axis, const float* a_ik, const float* pos_ij, const float* tvecs, const float* rvlen,
                             const int64_t* batch, const int64_t* edges, const int64_t* e_start, int64_t N, int64_t E,
                             float cutoff_radius, uint64_t seed, const float* frame1, float* frame, int64_t* sel_edge,

@@ -721,4 +721,137 @@ int max_frame(const FrArgs& A, const Params& P, cudaStream_t st)
     return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
 }
 
+// ---- third axis of the frame method "max_wo_orthogonal" (compute_third_frame_each_edge.cu:93-150,
+// models/cuda_funcs/calc_maximum_frame.py:173-245): an ablation of the reference that keeps the second axis
+// un-orthogonalised and selects a third one like the first two, with log(max(|det(f1, f2, u)|, 1e-5)) in place of the
+// collinearity term and |det| > 1e-5 as the condition.  Not on the hot path: thread = (pair, head) sweeps the box with
+// the reference's arithmetic (non-fused operations, so a CPU reproduces the selection), warp = (atom, head) takes the
+// arg-max of q.k + value over the atom's pairs, lowest pair on equal scores.
+struct Fr3Args {
+    const float* q; const float* k; const float* a_ik; const float* pos_ij; const float* tvecs; const float* rvlen;
+    const int64_t* batch; const int64_t* edges; const int64_t* e_start;
+    const float* frame1; const float* frame2;
+    int64_t N, E;
+    uint64_t seed;
+    float* cand;            // scratch (E,H,4): direction, value
+    float* frame3; int64_t* sel_edge;
+};
+
+__global__ void __launch_bounds__(256) third_axis_edges_kernel(const Fr3Args A, const Params P)
+{
+    const int H = P.H;
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (tid >= A.E * H) return;
+    const int64_t e = tid / H;
+    const int h = (int)(tid - e * H);
+    const int64_t i = A.edges[e], c = A.batch[i];
+    Cell cell;
+    const float* Tc = A.tvecs + 9 * c;
+    cell.t1x = __ldg(Tc); cell.t1y = __ldg(Tc + 1); cell.t1z = __ldg(Tc + 2);
+    cell.t2x = __ldg(Tc + 3); cell.t2y = __ldg(Tc + 4); cell.t2z = __ldg(Tc + 5);
+    cell.t3x = __ldg(Tc + 6); cell.t3y = __ldg(Tc + 7); cell.t3z = __ldg(Tc + 8);
+    cell.rx = __ldg(A.pos_ij + 3 * e); cell.ry = __ldg(A.pos_ij + 3 * e + 1); cell.rz = __ldg(A.pos_ij + 3 * e + 2);
+    const float a = __ldg(A.a_ik + i * H + h);
+    const bool cut = P.cutoff_radius != 0.0f;
+    const int R1 = lattice_range_1d(P, a, cut ? __ldg(A.rvlen + 3 * c) : 0.0f);
+    const int R2 = lattice_range_1d(P, a, cut ? __ldg(A.rvlen + 3 * c + 1) : 0.0f);
+    const int R3 = lattice_range_1d(P, a, cut ? __ldg(A.rvlen + 3 * c + 2) : 0.0f);
+    const float* f1 = A.frame1 + (i * H + h) * 3;
+    const float* f2 = A.frame2 + (i * H + h) * 3;
+    const float f1x = __ldg(f1), f1y = __ldg(f1 + 1), f1z = __ldg(f1 + 2);
+    const float f2x = __ldg(f2), f2y = __ldg(f2 + 1), f2z = __ldg(f2 + 2);
+    float d2min = 1e10f;
+    for (int n1 = -R1; n1 <= R1; n1++)
+        for (int n2 = -R2; n2 <= R2; n2++)
+            for (int n3 = -R3; n3 <= R3; n3++) {
+                float dx, dy, dz, d2;
+                separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
+                if (d2 > kTiny) d2min = fminf(d2min, d2);
+            }
+    float best = -1e15f, ux = 0.f, uy = 0.f, uz = 0.f, value = -1e15f;
+    const float half = 0.5f * P.noise;
+    int t = 0;
+    for (int n1 = -R1; n1 <= R1; n1++)
+        for (int n2 = -R2; n2 <= R2; n2++)
+            for (int n3 = -R3; n3 <= R3; n3++, t++) {
+                float dx, dy, dz, d2;
+                separation(cell, (float)n1, (float)n2, (float)n3, dx, dy, dz, d2);
+                if (!(d2 > kTiny)) continue;
+                const float gauss = __fmul_rn(a, __fsub_rn(d2, d2min));
+                if (gauss + half + 1e-6f < best) continue;              // the logarithm is not positive (|det| <= 1 up to rounding)
+                const float d = __fsqrt_rn(d2);
+                const float vx = __fdiv_rn(dx, d), vy = __fdiv_rn(dy, d), vz = __fdiv_rn(dz, d);
+                float det = __fmul_rn(__fmul_rn(f1x, f2y), vz);
+                det = __fadd_rn(det, __fmul_rn(__fmul_rn(f1y, f2z), vx));
+                det = __fadd_rn(det, __fmul_rn(__fmul_rn(f1z, f2x), vy));
+                det = __fsub_rn(det, __fmul_rn(__fmul_rn(f1z, f2y), vx));
+                det = __fsub_rn(det, __fmul_rn(__fmul_rn(f1y, f2x), vz));
+                det = __fsub_rn(det, __fmul_rn(__fmul_rn(f1x, f2z), vy));
+                const float mag = fabsf(det);
+                if (!(mag > kTiny)) continue;
+                const float score = __fadd_rn(gauss, logf(mag));
+                const float noisy = P.noise == 0.0f ? score : __fadd_rn(score, noise_term(P.noise, A.seed, (uint64_t)tid, (uint32_t)t));
+                if (noisy > best) {
+                    best = noisy;
+                    ux = vx; uy = vy; uz = vz;
+                    value = __fadd_rn(score, __fmul_rn(a, d2min));
+                }
+            }
+    reinterpret_cast<float4*>(A.cand)[tid] = make_float4(ux, uy, uz, value);
+}
+
+__global__ void __launch_bounds__(256) third_axis_select_kernel(const Fr3Args A, const Params P)
+{
+    const int H = P.H, lane = threadIdx.x & 31;
+    const int64_t w = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w >= A.N * H) return;
+    const int64_t i = w / H;
+    const int h = (int)(w - i * H);
+    const int64_t e0 = A.e_start[i], e1 = A.e_start[i + 1];
+    const float4* q4 = reinterpret_cast<const float4*>(A.q + (i * H + h) * kFrHd);
+    unsigned long long best = make_key(-1e10f, 0u);          // a score must exceed -1e10 to be selected
+    for (int64_t e = e0 + lane; e < e1; e += 32) {
+        const int64_t j = A.edges[A.E + e];
+        const float4* k4 = reinterpret_cast<const float4*>(A.k + (j * H + h) * kFrHd);
+        float dot = 0.f;
+#pragma unroll
+        for (int d4 = 0; d4 < kFrHd / 4; d4++) {
+            const float4 u = __ldg(q4 + d4), v = __ldg(k4 + d4);
+            dot = __fmaf_rn(u.x, v.x, dot); dot = __fmaf_rn(u.y, v.y, dot);
+            dot = __fmaf_rn(u.z, v.z, dot); dot = __fmaf_rn(u.w, v.w, dot);
+        }
+        const float s = __fadd_rn(dot, reinterpret_cast<const float4*>(A.cand)[e * H + h].w);
+        if (s > -1e10f) {
+            const unsigned long long key = make_key(s, (unsigned)(e - e0));
+            best = key > best ? key : best;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+    }
+    if (lane == 0) {
+        float* out = A.frame3 + (i * H + h) * 3;
+        if (best == make_key(-1e10f, 0u)) {
+            out[0] = out[1] = out[2] = 0.f;
+            if (A.sel_edge) A.sel_edge[i * H + h] = -1;
+        } else {
+            const int64_t e = e0 + (int64_t)(0xFFFFFFFFu - (unsigned)(best & 0xffffffffull));
+            const float4 c = reinterpret_cast<const float4*>(A.cand)[e * H + h];
+            out[0] = c.x; out[1] = c.y; out[2] = c.z;
+            if (A.sel_edge) A.sel_edge[i * H + h] = e;
+        }
+    }
+}
+
+int third_axis(const Fr3Args& A, const Params& P, cudaStream_t st)
+{
+    if (A.N == 0 || A.E == 0) return CFB200_OK;
+    const int64_t n1 = A.E * P.H, n2 = A.N * P.H;
+    third_axis_edges_kernel<<<(unsigned)((n1 + 255) / 256), 256, 0, st>>>(A, P);
+    third_axis_select_kernel<<<(unsigned)((n2 + 7) / 8), 256, 0, st>>>(A, P);
+    return cudaGetLastError() == cudaSuccess ? CFB200_OK : CFB200_E_CUDA;
+}
+
 }  // namespace cfb

@@ -4,6 +4,7 @@ from .kernel_manager import KernelManager, compile_kernels, current_config
 from .framed_proj import RealEncodingWithFramedProjFuncCUDA
 from .enc_proj import RealPeriodicEncodingWithProjFuncCUDA
 from .max_frame import (ComputeFrame1MaximumMethodCUDA, ComputeFrame1MaximumStaticMethodCUDA, ComputeFrame2MaximumMethodCUDA,
+                        ComputeFrame3MaximumMethodCUDA, max_frame3_with_selection,
                         ComputeFrame2MaximumStaticMethodCUDA, ComputeLatticeFrameCUDA, ComputePCAFrame, max_frame_with_selection,
                         max_frames_fused, max_static_frame_with_selection, max_static_frames_fused, weighted_pca_frames)
 from .fused_dpa import FusedDotProductAttentionCUDA, FusedDotProductAttentionSigmaMatCUDA, attention_probabilities
@@ -18,7 +19,8 @@ CUPY_AVAILABLE = True
 __all__ = [
     "KernelManager", "compile_kernels", "current_config", "FusedDotProductAttentionCUDA",
     "FusedDotProductAttentionSigmaMatCUDA",
-    "ComputeFrame1MaximumMethodCUDA", "ComputeFrame2MaximumMethodCUDA", "RealEncodingWithFramedProjFuncCUDA",
+    "ComputeFrame1MaximumMethodCUDA", "ComputeFrame2MaximumMethodCUDA", "ComputeFrame3MaximumMethodCUDA",
+    "max_frame3_with_selection", "RealEncodingWithFramedProjFuncCUDA",
     "ComputeFrame1MaximumStaticMethodCUDA", "ComputeFrame2MaximumStaticMethodCUDA", "ComputeLatticeFrameCUDA", "ComputePCAFrame",
     "max_static_frame_with_selection", "max_static_frames_fused",
     "RealPeriodicEncodingWithProjFuncCUDA", "ReciPeriodicEncodingFuncCUDA",

@@ -63,6 +63,42 @@ class ComputeFrame2MaximumMethodCUDA(torch.autograd.Function):
         return (None,) * 15
 
 
+def max_frame3_with_selection(q, k, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_n, cutoff_radius, frame1, frame2):
+    """Third axis of "max_wo_orthogonal" and the pair it was taken from: (frame3 (N,H,3), sel_edge (N,H))."""
+    N, H = a_ik.shape
+    E = edge_ij_e.shape[1]
+    dev = a_ik.device
+    a, qq, kk = f32c(a_ik), f32c(q), f32c(k)
+    pos, tv, rv = f32c(rpos_ij_e), f32c(tvecs_n), f32c(rvlen_n)
+    batch, edges = batch_i.contiguous(), edge_ij_e.contiguous()
+    e_start = csr_offsets(edges, N)
+    cutoff = 0.0 if cutoff_radius is None or rvlen_n is None else float(cutoff_radius)
+    seed = _draw_seed()
+    f3 = torch.empty((N, H, 3), device=dev, dtype=torch.float32)
+    sel = torch.empty((N, H), device=dev, dtype=torch.int64)
+    nbytes = int(_lib.lib().cfb200_max_frame3_workspace_bytes(N, E))
+    ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
+    p, ip = _lib.ptr, _lib.iptr
+    _lib.invoke("cfb200_max_frame3", 2, dev, p(qq), p(kk), p(a), p(pos), p(tv), p(rv), ip(batch), ip(edges), ip(e_start),
+                N, E, cutoff, seed, p(f32c(frame1)), p(f32c(frame2)), p(f3), ip(sel), ws.data_ptr(), nbytes)
+    return f3, sel
+
+
+class ComputeFrame3MaximumMethodCUDA(torch.autograd.Function):
+    """Drop-in for models/cuda_funcs/calc_maximum_frame.py:173-245: third axis (N,H,3) of the frame method
+    "max_wo_orthogonal", selected like the first two with the triple product of the three axes in the score."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, a_ik, rpos_ij_e, dist2_min_e, tvecs_n, batch_i, edge_ij_e, K, dist_max, wscale,
+                frame1, frame2, rvlen_n=None, cutoff_radius=None):
+        return max_frame3_with_selection(q, k, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_n, cutoff_radius,
+                                         frame1, frame2)[0]
+
+    @staticmethod
+    def backward(ctx, gframevec):
+        return (None,) * 16
+
+
 def max_frame_with_selection(axis, q, k, a_ik, rpos_ij_e, tvecs_n, batch_i, edge_ij_e, rvlen_n, cutoff_radius,
                              frame1=None):
     """Frame axis plus the integer selection behind it: (frame, pair index (N,H) int64,

@@ -192,6 +192,20 @@ int cfb200_sigma_frames(const float* q_scaled, const float* k, const float* a_ik
                         float* frame2, float* frame3, void* workspace, int64_t workspace_bytes,
                         void* stream);
 
+/* Replaces ComputeFrame3MaximumMethodCUDA (models/cuda_funcs/calc_maximum_frame.py:173-245; kernel
+ * compute_third_frame_each_edge.cu), the third axis of the frame method "max_wo_orthogonal": per (pair, head) the
+ * image maximising a (d^2 - d^2_min) + log|det(frame1, frame2, u)| among the images with |det| > 1e-5, then per
+ * (atom, head) the pair maximising q.k + that value (lowest pair on equal scores).  frame1, frame2 (N,H,3): the first
+ * axis and the UN-orthogonalised second axis (cfb200_max_frame with axis 1 and 2).  frame3 (N,H,3) out; sel_edge
+ * (N,H) optional.  Where no image of any pair qualifies the frame is zero and sel_edge -1 (the reference leaves its
+ * outputs unwritten there).  workspace: cfb200_max_frame3_workspace_bytes(N,E) bytes, 16-byte aligned. */
+int64_t cfb200_max_frame3_workspace_bytes(int64_t N, int64_t E);
+int cfb200_max_frame3(const float* q_scaled, const float* k, const float* a_ik, const float* pos_ij,
+                      const float* tvecs, const float* rvlen, const int64_t* batch, const int64_t* edges,
+                      const int64_t* e_start, int64_t N, int64_t E, float cutoff_radius, uint64_t seed,
+                      const float* frame1, const float* frame2, float* frame3, int64_t* sel_edge,
+                      void* workspace, int64_t workspace_bytes, void* stream);
+
 /* cfb200_sigma_frames / cfb200_sigma_edges with the per-pair sorted translation lists of cfb200_pair_cache
  * (pair_list (E,5,128), valid for lattice ranges (cache_range)^3; NULL: every pair is swept): the translations that
  * carry weight are a prefix of a pair's list, shared by all heads; pairs whose box the list does not cover are

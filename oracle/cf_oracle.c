@@ -531,6 +531,67 @@ void FN(cfo_frame2_static_edges)(const cfo_config* cfg, const real* a_ik, const 
     FN(frame2_edges_impl)(cfg, 1, a_ik, rpos, tvecs, rvlen, batch_i, edges, N, E, seed, frame1, dir, value, sel_image);
 }
 
+/* Third axis of the frame method "max_wo_orthogonal" (models/kernels/compute_third_frame_each_edge.cu:93-150,
+ * models/cuda_funcs/calc_maximum_frame.py:173-245): per (pair, head) the image maximising
+ * a (d^2 - d^2_min) + log(max(|det(f1, f2, u)|, 1e-5)) among the images with |det| > 1e-5, u the unit vector to the
+ * image; value = score + a d^2_min.  Where no image qualifies the reference leaves its outputs unwritten; here the
+ * direction is zero and the value -1e15, which no selection picks.  Noise: the symmetric rule of the second axis. */
+void FN(cfo_frame3_edges)(const cfo_config* cfg, const real* a_ik, const real* rpos, const real* tvecs,
+                          const float* rvlen, const int64_t* batch_i, const int64_t* edges, int64_t N, int64_t E,
+                          uint64_t seed, const real* frame1 /* (N,H,3) */, const real* frame2 /* (N,H,3) */,
+                          real* dir, real* value, int32_t* sel_image)
+{
+    const int H = cfg->H;
+    (void)N;
+#pragma omp parallel for schedule(dynamic, 64)
+    for (int64_t e = 0; e < E; e++) {
+        const int64_t i = edges[e], c = batch_i[i];
+        const real* r = rpos + 3 * e;
+        const real* T = tvecs + 9 * c;
+        for (int k = 0; k < H; k++) {
+            const real a = a_ik[i * H + k];
+            const real* f1 = frame1 + (i * H + k) * 3;
+            const real* f2 = frame2 + (i * H + k) * 3;
+            int R[3];
+            lattice_range(cfg, (float)a, rvlen + 3 * c, R);
+            real d2min = (real)1e10;
+            FOR_TRANSLATIONS(R) {
+                SEPARATION(r, T); (void)dx; (void)dy; (void)dz;
+                if ((double)d2 > 1e-5) d2min = R_FMIN(d2min, d2);
+            }
+            real max_val = (real)-1e15, bx = 0, by = 0, bz = 0, bval = (real)-1e15;
+            int32_t t = 0, best = -1;
+            FOR_TRANSLATIONS(R) {
+                SEPARATION(r, T);
+                real d = R_SQRT(d2);
+                if ((double)d2 > 1e-5) {
+                    real ux = dx / d, uy = dy / d, uz = dz / d;
+                    real det = f1[0] * f2[1] * uz + f1[1] * f2[2] * ux + f1[2] * f2[0] * uy - f1[2] * f2[1] * ux -
+                               f1[1] * f2[0] * uz - f1[0] * f2[2] * uy;
+                    real mag = R_FABS(det);
+                    real clipped = ((double)mag > 1e-5) ? mag : (real)1e-5;
+                    real score = a * (d2 - d2min) + R_LOG(clipped);
+                    real noisy = score;
+                    if (cfg->symm_break_noise != 0.0f)
+                        noisy = score + (real)(float)(((double)cfo_uniform(seed, (uint64_t)(e * H + k), (uint32_t)t) - 0.5) *
+                                                      (double)cfg->symm_break_noise);
+                    if (noisy > max_val && (double)mag > 1e-5) {
+                        max_val = noisy;
+                        bx = ux; by = uy; bz = uz;
+                        bval = score + a * d2min;
+                        best = t;
+                    }
+                }
+                t++;
+            }
+            real* o = dir + (e * H + k) * 3;
+            o[0] = bx; o[1] = by; o[2] = bz;
+            value[e * H + k] = bval;
+            sel_image[e * H + k] = best;
+        }
+    }
+}
+
 /* --------------------------------------------------------------------------
  * Lattice frames: the three shortest lattice vectors of the atom's cell, per (atom, head)
  * (models/kernels/compute_lattice_first_frame.cu:86-110, compute_lattice_second_frame.cu:95-130,

@@ -116,6 +116,12 @@ def attention_layer(attn, x, geo, cfg, frames=None):
         with torch.no_grad():
             f1, f2, f3 = OF.max_frames(qs.detach().contiguous(), k.detach().contiguous(), a.detach().contiguous(),
                                        geo["pos_ij"], geo["tvecs"], geo["batch"], geo["edges"], geo["rvlen"], cutoff)
+    elif method == "max_wo_orthogonal":
+        npy = lambda t: t.detach().contiguous().numpy()
+        e_start = OF._e_start(geo["edges"], N)
+        fr = O.max_frames_wo_orthogonal(cfg, npy(qs), npy(k), npy(a), npy(geo["pos_ij"]), npy(geo["tvecs"]), npy(geo["rvlen"]),
+                                        npy(geo["batch"]), npy(geo["edges"]), npy(e_start))
+        f1, f2, f3 = (torch.from_numpy(fr[n]) for n in ("frame1", "frame2", "frame3"))
     elif method in ("max_static", "lattice"):
         npy = lambda t: t.detach().contiguous().numpy()
         e_start = OF._e_start(geo["edges"], N)

@@ -196,7 +196,8 @@ def _frame_edges(name, cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, seed, fram
     args = [ctypes.byref(c), _p(a), _p(_r(pos_ij, dtype)), _p(_r(tvecs, dtype)), _p(_f32(rvlen)),
             _p(_i64(batch)), _p(_i64(edges)), ctypes.c_int64(N), ctypes.c_int64(E), ctypes.c_uint64(seed)]
     if frame1 is not None:
-        args.append(_p(_r(frame1, dtype)))
+        for f in (frame1 if isinstance(frame1, (tuple, list)) else (frame1,)):
+            args.append(_p(_r(f, dtype)))
     args += [_p(d), _p(val), _p(img)]
     _fn(name, dtype)(*args)
     return d, val, img
@@ -212,6 +213,26 @@ def frame2_edges(cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, frame1, seed=0, 
 
 def frame2_static_edges(cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, frame1, seed=0, dtype=np.float32):
     return _frame_edges("cfo_frame2_static_edges", cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, seed, frame1, dtype)
+
+
+def frame3_edges(cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, frame1, frame2, seed=0, dtype=np.float32):
+    """Third-axis candidates of "max_wo_orthogonal" (models/kernels/compute_third_frame_each_edge.cu)."""
+    return _frame_edges("cfo_frame3_edges", cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, seed, (frame1, frame2), dtype)
+
+
+def max_frames_wo_orthogonal(cfg, q_scaled, k, a_ik, pos_ij, tvecs, rvlen, batch, edges, e_start, seeds=(0, 0, 0),
+                             dtype=np.float32):
+    """Frame method "max_wo_orthogonal" (models/indexed_lattice_multi_head_attention_cuda.py:449-461, :483-488):
+    the first axis and the un-orthogonalised second axis of "max", and a third axis selected like them with the
+    triple product in place of the collinearity term."""
+    d1, v1, _ = frame1_edges(cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, seeds[0], dtype)
+    f1, sel1 = frame_select(cfg, q_scaled, k, edges, e_start, d1, v1, dtype)
+    d2, v2, _ = frame2_edges(cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, f1, seeds[1], dtype)
+    f2, sel2 = frame_select(cfg, q_scaled, k, edges, e_start, d2, v2, dtype)
+    d3, v3, img3 = frame3_edges(cfg, a_ik, pos_ij, tvecs, rvlen, batch, edges, f1, f2, seeds[2], dtype)
+    f3, sel3 = frame_select(cfg, q_scaled, k, edges, e_start, d3, v3, dtype)
+    hh = np.arange(cfg.H)[None, :]
+    return dict(frame1=f1, frame2=f2, frame3=f3, sel_edge1=sel1, sel_edge2=sel2, sel_edge3=sel3, sel_image3=img3[sel3, hh])
 
 
 def frame_select(cfg, q, k, edges, e_start, direction, value, dtype=np.float32):

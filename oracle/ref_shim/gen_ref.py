@@ -36,6 +36,7 @@ KERNELS = [
     "compute_second_frame_static_each_edge",
     "compute_lattice_first_frame", "compute_lattice_second_frame", "compute_lattice_third_frame",
     "reci_enc_fwd", "reci_enc_bwd",
+    "compute_third_frame_each_edge",
 ]
 
 

@@ -233,6 +233,25 @@ class RefKernels:
         hh = torch.arange(H, device=a_ik.device)[None, :].expand(N, H)
         return torch.stack([dx[arg, hh], dy[arg, hh], dz[arg, hh]], dim=-1), arg
 
+    # ---- models/cuda_funcs/calc_maximum_frame.py:173-245 (frame method "max_wo_orthogonal") ----
+    def frame3(self, q_scaled, k, a_ik, rpos, tvecs, batch, edges, rvlen, cutoff, frame1, frame2, seed=0):
+        """The reference allocates the per-pair outputs with torch.empty and its kernel leaves them unwritten where no
+        image qualifies; here they start as zero directions with value -1e15, which the arg-max never picks."""
+        N, H = a_ik.shape
+        E = edges.shape[1]
+        kw = dict(device=a_ik.device, dtype=a_ik.dtype)
+        state = torch.empty(E * H * 48, dtype=torch.uint8, device=a_ik.device)
+        f1 = [frame1[:, :, d].contiguous() for d in range(3)]
+        f2 = [frame2[:, :, d].contiguous() for d in range(3)]
+        dx, dy, dz = (torch.zeros(E, H, **kw) for _ in range(3))
+        val = torch.full((E, H), -1e15, **kw)
+        # the kernel takes the head from threadIdx.x: one block per pair (calc_maximum_frame.py:196,205)
+        self.launch("compute_third_frame_each_edge", E, H, a_ik, rpos, None, tvecs, batch, edges, N, H, E, 64, 14.0, 1.0,
+                    rvlen, cutoff, state, seed, f1[0], f1[1], f1[2], f2[0], f2[1], f2[2], dx, dy, dz, val)
+        arg = segment_argmax(self._edge_scores(q_scaled, k, edges, val), edges[0], N)
+        hh = torch.arange(H, device=a_ik.device)[None, :].expand(N, H)
+        return torch.stack([dx[arg, hh], dy[arg, hh], dz[arg, hh]], dim=-1), arg
+
     # ---- models/cuda_funcs/calc_maximum_static_frame.py:24-170: as frame1 / frame2 without q.k, static second kernel ----
     def frame1_static(self, a_ik, rpos, tvecs, batch, edges, rvlen, cutoff, seed=0):
         N, H = a_ik.shape

@@ -30,7 +30,7 @@ pytestmark = pytest.mark.skipif(REF is None, reason="reference tree not present 
 FUNCTIONS = {
     "real_space_framed_proj.py": ["RealEncodingWithFramedProjFuncCUDA"],
     "real_space_enc_proj.py": ["RealPeriodicEncodingWithProjFuncCUDA"],
-    "calc_maximum_frame.py": ["ComputeFrame1MaximumMethodCUDA", "ComputeFrame2MaximumMethodCUDA"],
+    "calc_maximum_frame.py": ["ComputeFrame1MaximumMethodCUDA", "ComputeFrame2MaximumMethodCUDA", "ComputeFrame3MaximumMethodCUDA"],
     "calc_maximum_static_frame.py": ["ComputeFrame1MaximumStaticMethodCUDA", "ComputeFrame2MaximumStaticMethodCUDA"],
     "calc_lattice_frame.py": ["ComputeLatticeFrameCUDA"],
     "calc_pca_frame.py": ["ComputePCAFrame"],

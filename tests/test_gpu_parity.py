@@ -323,6 +323,37 @@ def test_whole_model_against_cpu_oracle(layers, frame_method, fused):
     _whole_model_check(layers, frame_method, fused)
 
 
+def test_whole_model_without_orthogonalisation():
+    """Frame method "max_wo_orthogonal" (second axis as selected, third axis selected with the triple product): the
+    whole model against the CPU oracle; it runs operator by operator."""
+    _whole_model_check(2, "max_wo_orthogonal", False)
+
+
+@pytest.mark.parametrize("workload,nc", [("cfg1", None), ("cfg2", 24)])
+def test_third_axis_selection(workload, nc):
+    """cfb200_max_frame3 through the drop-in Function: selected pair and direction against the oracle (bit-exact but
+    for the few atoms where the logarithm's last bit decides), all three axes linearly independent."""
+    dev = _cuda()
+    from oracle import oracle as O
+    F = _configure()
+    P = make_problem(workload, num_crystals=nc)
+    g = _geometry(P, dev)
+    qs = (P["q"] / 4.0).astype(np.float32)
+    want = O.max_frames_wo_orthogonal(P["cfg"], qs, P["k"], P["a"], P["geo"]["pos_ij"], P["batch"].trans_vec,
+                                      P["geo"]["rvlen"], P["geo"]["batch"], P["geo"]["edges"], P["geo"]["e_start"])
+    f1, f2 = _t(want["frame1"], dev), _t(want["frame2"], dev)
+    f3, sel = F.max_frame3_with_selection(_t(qs, dev), _t(P["k"], dev), _t(P["a"], dev), g["pos_ij"], g["tvecs"], g["batch"],
+                                          g["edges"], g["rvlen"], -3.5, f1, f2)
+    same = sel.cpu().numpy() == want["sel_edge3"]
+    assert same.mean() >= 0.999, same.mean()
+    assert np.array_equal(f3.cpu().numpy()[same], want["frame3"][same])
+    M = np.stack([want["frame1"], want["frame2"], f3.cpu().numpy()], axis=-2).astype(np.float64)
+    assert (np.abs(np.linalg.det(M)) > 1e-5).all()
+    out = F.ComputeFrame3MaximumMethodCUDA.apply(_t(qs, dev), _t(P["k"], dev), None, _t(P["a"], dev), g["pos_ij"], None,
+                                                 g["tvecs"], g["batch"], g["edges"], 64, 14.0, 1.0, f1, f2, g["rvlen"], -3.5)
+    assert torch.equal(out, f3)
+
+
 @pytest.mark.parametrize("fused", [False, True])
 def test_whole_model_lightweight_recipe(fused):
     """The reference's second efficiency recipe (train_jarvis_time.sh:41-57): 16 angle Gaussians of width scale 1.0,

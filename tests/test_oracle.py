@@ -416,3 +416,28 @@ def test_reciprocal_encoding_against_reference_cpu_build(problem_cfg1):
     ga = rk.reci_bwd(T(a), T(kr), T(rvecs), T(vcell), T(geo["batch"]), T(geo["edges"]), z, T(gz), sumexp)
     gao = O.reci_enc_bwd(a, kr, rvecs, geo["batch"], geo["edges"], gz, sumexp.numpy())
     close("ga", gao, ga.numpy(), 1e-4, 1e-5 * max(1.0, float(ga.abs().max())))
+
+
+@pytest.mark.skipif(not R.available("cpu"), reason="oracle/_ref not built (reference tree absent)")
+def test_third_axis_without_orthogonalisation_against_reference_cpu_build(problem_cfg1):
+    """Frame method "max_wo_orthogonal": the third-axis search (triple product with the first two axes in place of
+    the collinearity term) against the reference's compute_third_frame_each_edge kernel -- selected pair identical,
+    direction bit-identical."""
+    P = problem_cfg1
+    geo, b = P["geo"], P["batch"]
+    cfg = P["cfg"]
+    rk = R.RefKernels("cpu")
+    T = lambda x: torch.from_numpy(np.ascontiguousarray(x))
+    qs = (P["q"] / 4.0).astype(np.float32)
+    a, r, tv, bt, e, rv = T(P["a"]), T(geo["pos_ij"]), T(b.trans_vec), T(geo["batch"]), T(geo["edges"]), T(geo["rvlen"])
+    fr = O.max_frames_wo_orthogonal(cfg, qs, P["k"], P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"],
+                                    geo["edges"], geo["e_start"])
+    f1, _ = rk.frame1(T(qs), T(P["k"]), a, r, tv, bt, e, rv, -3.5)
+    f2, _ = rk.frame2(T(qs), T(P["k"]), a, r, tv, bt, e, rv, -3.5, f1)
+    assert np.array_equal(f1.numpy(), fr["frame1"]) and np.array_equal(f2.numpy(), fr["frame2"])
+    f3, sel3 = rk.frame3(T(qs), T(P["k"]), a, r, tv, bt, e, rv, -3.5, f1, f2)
+    assert np.array_equal(sel3.numpy(), fr["sel_edge3"])
+    assert np.array_equal(f3.numpy(), fr["frame3"])
+    # the three axes span space: |det| > 1e-5 by construction of the search
+    M = np.stack([fr["frame1"], fr["frame2"], fr["frame3"]], axis=-2).astype(np.float64)
+    assert (np.abs(np.linalg.det(M)) > 1e-5).all()
