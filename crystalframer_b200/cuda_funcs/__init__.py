@@ -10,6 +10,7 @@ from .max_frame import (ComputeFrame1MaximumMethodCUDA, ComputeFrame1MaximumStat
 from .fused_dpa import FusedDotProductAttentionCUDA, FusedDotProductAttentionSigmaMatCUDA, attention_probabilities
 from .irregular_mean import IrregularMeanCUDA
 from .reci_enc import ReciPeriodicEncodingFuncCUDA
+from .real_enc import RealPeriodicEncodingFuncCUDA
 from .common import csr_offsets, register_csr
 
 # the reference exports this flag (models/cuda_funcs/__init__.py:2-9); here it says whether the
@@ -23,7 +24,7 @@ __all__ = [
     "max_frame3_with_selection", "RealEncodingWithFramedProjFuncCUDA",
     "ComputeFrame1MaximumStaticMethodCUDA", "ComputeFrame2MaximumStaticMethodCUDA", "ComputeLatticeFrameCUDA", "ComputePCAFrame",
     "max_static_frame_with_selection", "max_static_frames_fused",
-    "RealPeriodicEncodingWithProjFuncCUDA", "ReciPeriodicEncodingFuncCUDA",
+    "RealPeriodicEncodingWithProjFuncCUDA", "ReciPeriodicEncodingFuncCUDA", "RealPeriodicEncodingFuncCUDA",
     "IrregularMeanCUDA", "max_frame_with_selection", "max_frames_fused", "weighted_pca_frames", "attention_probabilities",
     "csr_offsets", "register_csr", "CUPY_AVAILABLE",
 ]

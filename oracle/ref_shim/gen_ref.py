@@ -37,6 +37,7 @@ KERNELS = [
     "compute_lattice_first_frame", "compute_lattice_second_frame", "compute_lattice_third_frame",
     "reci_enc_fwd", "reci_enc_bwd",
     "compute_third_frame_each_edge",
+    "real_enc_fwd", "real_enc_bwd",
 ]
 
 

@@ -175,6 +175,24 @@ class RefKernels:
                     self.e_start(edges, N), z, gz.contiguous(), sumexp, N, H, E, ga)
         return ga
 
+    # ---- models/cuda_funcs/real_space_enc.py:17-245: logit and un-projected value sums ----
+    def real_enc_fwd(self, a_ik, rpos, tvecs, batch, edges, K, dist_max, wscale, rvlen, cutoff):
+        N, H = a_ik.shape
+        E = edges.shape[1]
+        z = torch.empty((E, H), device=a_ik.device, dtype=a_ik.dtype)
+        v = torch.empty((E, H, K), device=a_ik.device, dtype=a_ik.dtype)
+        self.launch("real_enc_fwd", (E * H + H - 1) // H, H, a_ik, rpos, None, tvecs, batch, edges, N, H, E, K, dist_max,
+                    wscale, rvlen, cutoff, z, v)
+        return z, v
+
+    def real_enc_bwd(self, a_ik, rpos, tvecs, batch, edges, K, dist_max, wscale, rvlen, cutoff, z, gz, gv):
+        N, H = a_ik.shape
+        E = edges.shape[1]
+        ga = torch.empty_like(a_ik)
+        self.launch("real_enc_bwd", (N * H + H - 1) // H, H, a_ik, rpos, None, tvecs, batch, edges, self.e_start(edges, N),
+                    z, gz.contiguous(), gv.contiguous(), N, H, E, K, dist_max, wscale, rvlen, cutoff, ga)
+        return ga
+
     # ---- weighted PCA: models/cuda_funcs/real_space_enc_proj.py:80-125, fused_dpa_sigmamat.py ----
     def sigma_fwd(self, a_ik, rpos, tvecs, batch, edges, rvlen, cutoff, seed=0):
         N, H = a_ik.shape

@@ -38,6 +38,7 @@ FUNCTIONS = {
     "fused_dpa_sigmamat.py": ["FusedDotProductAttentionSigmaMatCUDA"],
     "irregular_mean.py": ["IrregularMeanCUDA"],
     "reci_space_enc.py": ["ReciPeriodicEncodingFuncCUDA"],
+    "real_space_enc.py": ["RealPeriodicEncodingFuncCUDA"],
 }
 
 

@@ -695,3 +695,48 @@ def test_second_moment_records_with_and_without_sorted_lists(workload, nc, noise
         _close(f"nearest direction ({name})", rec[name][..., 8:11], ndir, 1e-5, 1e-6)
     assert np.array_equal(rec["list"][..., 7:11], rec["sweep"][..., 7:11])
     _configure(noise=0.0)
+
+
+@pytest.mark.parametrize("projected", [False, True])
+def test_plain_real_space_encoding_function(projected):
+    """RealPeriodicEncodingFuncCUDA: logit and the value sums of all 64 distance Gaussians, un-projected (E,H,64) or
+    projected by W_k (E,H,16), and the gradients of the coefficients (and of W_k), against the oracle's un-windowed
+    encoding."""
+    dev = _cuda()
+    from oracle import oracle as O
+    F = _configure(angle_dim=0)
+    P = make_problem("cfg1")
+    g = _geometry(P, dev)
+    geo, b = P["geo"], P["batch"]
+    cfg = O.Config(cut_sigma=32, D_ang=0)
+    a = _t(P["a"], dev).requires_grad_(True)
+    W = _t(P["W_d"][None], dev).requires_grad_(True) if projected else None
+    z, v = F.RealPeriodicEncodingFuncCUDA.apply(a, g["pos_ij"], None, g["tvecs"], g["batch"], g["edges"], 64, 14.0, 1.0, W,
+                                                g["rvlen"], -3.5)
+    rng = np.random.default_rng(31)
+    gz = rng.normal(size=tuple(z.shape)).astype(np.float32)
+    gv = rng.normal(size=tuple(v.shape)).astype(np.float32)
+    (z * _t(gz, dev)).sum().add((v * _t(gv, dev)).sum()).backward()
+    args = (cfg, P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"])
+    if projected:
+        zo, vo = O.framed_proj_fwd(*args, P["W_d"], None, None)
+        ga_o, gW_o, _ = O.framed_proj_bwd(*args, geo["e_start"], P["W_d"], None, None, zo, gz, gv)
+        ga64, gW64, _ = O.framed_proj_bwd(*args, geo["e_start"], P["W_d"], None, None, zo, gz, gv, dtype=np.float64)
+        _close_reduction("gW", W.grad.cpu().numpy()[0], gW_o, gW64)
+    else:
+        vo = np.empty((geo["edges"].shape[1], 8, 64), np.float32)
+        ga_o = np.zeros_like(P["a"])
+        ga64 = np.zeros(P["a"].shape, np.float64)
+        for blk in range(4):
+            S = np.zeros((8, 16, 64), np.float32)
+            S[:, np.arange(16), 16 * blk + np.arange(16)] = 1.0
+            zo, vb = O.framed_proj_fwd(*args, S, None, None)
+            vo[..., 16 * blk:16 * blk + 16] = vb
+            gzb = gz if blk == 0 else np.zeros_like(gz)
+            gvb = np.ascontiguousarray(gv[..., 16 * blk:16 * blk + 16])
+            ga_o += O.framed_proj_bwd(*args, geo["e_start"], S, None, None, zo, gzb, gvb)[0]
+            ga64 += O.framed_proj_bwd(*args, geo["e_start"], S, None, None, zo, gzb, gvb, dtype=np.float64)[0]
+    _close("z", z.detach().cpu().numpy(), zo)
+    _close("values", v.detach().cpu().numpy(), vo)
+    _close_reduction("ga", a.grad.cpu().numpy(), ga_o, ga64)
+    _configure()

@@ -441,3 +441,40 @@ def test_third_axis_without_orthogonalisation_against_reference_cpu_build(proble
     # the three axes span space: |det| > 1e-5 by construction of the search
     M = np.stack([fr["frame1"], fr["frame2"], fr["frame3"]], axis=-2).astype(np.float64)
     assert (np.abs(np.linalg.det(M)) > 1e-5).all()
+
+
+def _selector_weights(H, hd, K):
+    out = []
+    for b in range(K // hd):
+        S = np.zeros((H, hd, K), np.float32)
+        r = np.arange(hd)
+        S[:, r, hd * b + r] = 1.0
+        out.append(S)
+    return out
+
+
+@pytest.mark.skipif(not R.available("cpu"), reason="oracle/_ref not built (reference tree absent)")
+def test_unprojected_value_sums_against_reference_cpu_build(problem_cfg1):
+    """real_enc_fwd / real_enc_bwd (logit + the 64 un-projected value sums per (pair, head)) against the oracle's
+    un-windowed encoding read out through selector weights (basis functions 16 b .. 16 b + 15 unchanged)."""
+    P = problem_cfg1
+    geo, b = P["geo"], P["batch"]
+    cfg = O.Config(cut_sigma=32, D_ang=0)
+    rk = R.RefKernels("cpu")
+    T = lambda x: torch.from_numpy(np.ascontiguousarray(x))
+    a, r, tv, bt, e, rv = T(P["a"]), T(geo["pos_ij"]), T(b.trans_vec), T(geo["batch"]), T(geo["edges"]), T(geo["rvlen"])
+    z, v = rk.real_enc_fwd(a, r, tv, bt, e, 64, 14.0, 1.0, rv, -3.5)
+    rng = np.random.default_rng(23)
+    gz = rng.normal(size=tuple(z.shape)).astype(np.float32)
+    gv = rng.normal(size=tuple(v.shape)).astype(np.float32)
+    ga = rk.real_enc_bwd(a, r, tv, bt, e, 64, 14.0, 1.0, rv, -3.5, z, T(gz), T(gv))
+    ga_o = np.zeros_like(P["a"])
+    for blk, S in enumerate(_selector_weights(8, 16, 64)):
+        zo, vo = O.framed_proj_fwd(cfg, P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"], S, None, None)
+        close("z", zo, z.numpy(), 1e-6, 1e-6)
+        close(f"values {blk}", vo, v.numpy()[..., 16 * blk:16 * blk + 16], 1e-5, 1e-6)
+        g, _, _ = O.framed_proj_bwd(cfg, P["a"], geo["pos_ij"], b.trans_vec, geo["rvlen"], geo["batch"], geo["edges"],
+                                    geo["e_start"], S, None, None, zo, gz if blk == 0 else np.zeros_like(gz),
+                                    np.ascontiguousarray(gv[..., 16 * blk:16 * blk + 16]))
+        ga_o += g
+    close("ga", ga_o, ga.numpy(), 1e-4, 1e-5 * max(1.0, float(ga.abs().max())))
