@@ -388,3 +388,42 @@ def test_dense_layer_kernels(M, N, K, kn):
     _lib.invoke("cfb200_linear", 1, dev, p(xd), p(wd), p(bd), p(rd), M, N, K, 1, kn, p(y))
     close("relu(x W + b + r)", y.cpu().numpy(), torch.relu(ref + b.double() + r.double()).numpy(), 1e-5, 2e-5)
     assert _lib.read_status(dev) == 0
+
+
+def test_training_steps_repeat_bit_for_bit():
+    """Two runs of three training steps of the 4-layer model on the benchmark's batch (256 crystals: chunked tasks,
+    blocks moving across heads, weight gradients on the side stream) from the same weights and optimiser state:
+    every parameter must come out identical -- which warp or block computes what varies from run to run, the
+    order of every sum does not."""
+    dev = cuda()
+    import copy
+    from crystalframer_b200 import data, synth
+    from crystalframer_b200.latticeformer import Latticeformer, ModelParams
+    from crystalframer_b200.optim import FlatAdamW
+    torch.manual_seed(5)
+    model = Latticeformer(ModelParams(symm_break_noise=0.0)).to(dev).train()
+    b = synth.make_workload("cfg3", seed=2)
+    y = np.random.default_rng(2).normal(size=(len(b.sizes), 1)).astype(np.float32)
+    tb = data.host_batch(b, y, pinned=False).to(dev, non_blocking=False)
+    with torch.no_grad():
+        model(tb)                                   # coefficient statistics; later forwards take the one-call layers
+    decay = [p for n, p in model.named_parameters() if p.requires_grad and not n.endswith("bias")]
+    no_decay = [p for n, p in model.named_parameters() if p.requires_grad and n.endswith("bias")]
+    opt = FlatAdamW(decay, no_decay, lr=5e-4, betas=(0.9, 0.98), weight_decay=1e-5, max_norm=1.0)
+    start_model = {k: v.detach().clone() for k, v in model.state_dict().items()}
+    start_opt = copy.deepcopy(opt.state_dict())
+    runs = []
+    for _ in range(2):
+        model.load_state_dict(start_model)
+        opt.load_state_dict(copy.deepcopy(start_opt))
+        losses = []
+        for step in range(3):
+            opt.zero_grad()
+            loss = (model(tb) - tb.y).abs().mean()
+            loss.backward()
+            opt.step()
+            losses.append(loss.detach().clone())
+        runs.append((torch.stack(losses), opt.flat.clone(), opt.grad.clone()))
+    assert torch.equal(runs[0][0], runs[1][0]), (runs[0][0], runs[1][0])
+    assert torch.equal(runs[0][2], runs[1][2])      # the last step's gradients
+    assert torch.equal(runs[0][1], runs[1][1])      # all parameters
