@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(256) sigma_edges_kernel(const SgArgs A, const 
 // kernels, and the nearest non-zero image with whatever lies within the noise amplitude of it -- are a prefix of the
 // pair's sorted list, which all heads share: the slots of a head walk that prefix in turns (typically 3-4 entries
 // each instead of two sweeps over 125 translations), their partial sums meet by shuffles.  A (pair, head) whose box
-// is larger than the listed one and whose prefix could reach outside it falls back to the sweep.
+// is larger than the listed one and whose prefix could reach outside it sweeps that box, its slots sharing the planes.
 constexpr int kSgListWarps = 8;
 
 __global__ void __launch_bounds__(kSgListWarps * 32) sigma_edges_list_kernel(const SgArgs A, const Params P)
@@ -144,16 +144,52 @@ __global__ void __launch_bounds__(kSgListWarps * 32) sigma_edges_list_kernel(con
     const float nz_limit = d2nz + fabsf(P.noise) + fabsf(d2nz) * 8e-6f + 1e-12f;
     const float far = fmaxf(w_limit, nz_limit);
     const bool usable = a < 0.f && d2nz >= 0.f && unclear == 0u && (same_box || (wider && far < reach2));
-    if (!usable) {
-        if (slot == 0) sigma_pair_sweep(A, P, e, h, c, a, R1, R2, R3);
+    // A head whose list does not serve sweeps its whole box, the slots taking the planes n1 in turns: first the
+    // smallest distance (the slots' minima meet by shuffles, which every lane of the warp executes), then weights,
+    // moments and the nearest non-zero image with the sweep's own arithmetic.
+    float d2ref = d2min;
+    {
+        float dmin = 1e10f;
+        if (!usable)
+            for (int n1 = -R1 + slot; n1 <= R1; n1 += slots)
+                for (int n2 = -R2; n2 <= R2; n2++)
+                    for (int n3 = -R3; n3 <= R3; n3++) {
+                        const float dx = fmaf(cell.t3x, (float)n3, fmaf(cell.t2x, (float)n2, fmaf(cell.t1x, (float)n1, cell.rx)));
+                        const float dy = fmaf(cell.t3y, (float)n3, fmaf(cell.t2y, (float)n2, fmaf(cell.t1y, (float)n1, cell.ry)));
+                        const float dz = fmaf(cell.t3z, (float)n3, fmaf(cell.t2z, (float)n2, fmaf(cell.t1z, (float)n1, cell.rz)));
+                        dmin = fminf(dmin, fmaf(dz, dz, fmaf(dy, dy, dx * dx)));
+                    }
+        for (int o = H; o < 32; o <<= 1) dmin = fminf(dmin, __shfl_xor_sync(0xffffffffu, dmin, o));
+        if (!usable) d2ref = dmin;
     }
-    // (no early exit: the shuffles below are warp-wide; lanes of a head that took the sweep carry zeros)
     float sum = 0.f, m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f, m4 = 0.f, m5 = 0.f;
     float best = 1e8f, bx = 0.f, by = 0.f, bz = 0.f;
     int best_t = 0x7fffffff;
+    const int64_t tid = e * H + h;
+    const int L2 = 2 * R2 + 1, L3 = 2 * R3 + 1;
+    if (!usable) {
+        for (int n1 = -R1 + slot; n1 <= R1; n1 += slots)
+            for (int n2 = -R2; n2 <= R2; n2++)
+                for (int n3 = -R3; n3 <= R3; n3++) {
+                    const float dx = fmaf(cell.t3x, (float)n3, fmaf(cell.t2x, (float)n2, fmaf(cell.t1x, (float)n1, cell.rx)));
+                    const float dy = fmaf(cell.t3y, (float)n3, fmaf(cell.t2y, (float)n2, fmaf(cell.t1y, (float)n1, cell.ry)));
+                    const float dz = fmaf(cell.t3z, (float)n3, fmaf(cell.t2z, (float)n2, fmaf(cell.t1z, (float)n1, cell.rz)));
+                    const float d2 = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
+                    const float w = ex2_approx(a * (d2 - d2ref) * kLog2e);
+                    sum += w;
+                    const float wx = dx * w, wy = dy * w, wz = dz * w;
+                    m0 = fmaf(dx, wx, m0); m1 = fmaf(dx, wy, m1); m2 = fmaf(dx, wz, m2);
+                    m3 = fmaf(dy, wy, m3); m4 = fmaf(dy, wz, m4); m5 = fmaf(dz, wz, m5);
+                    if (d2 > 1e-5f && d2 - 0.5f * fabsf(P.noise) <= best) {
+                        const int t = ((n1 + R1) * L2 + (n2 + R2)) * L3 + (n3 + R3);
+                        float cand = d2;
+                        if (P.noise != 0.0f)
+                            cand = d2 + (float)(((double)hash_uniform(A.seed_noise, (uint64_t)tid, (uint32_t)t) - 0.5) * (double)P.noise);
+                        if (cand < best || (cand == best && t < best_t)) { best = cand; best_t = t; bx = dx; by = dy; bz = dz; }
+                    }
+                }
+    }
     if (usable) {
-        const int64_t tid = e * H + h;
-        const int L2 = 2 * R2 + 1, L3 = 2 * R3 + 1;
         for (int s = slot; s < kListLen; s += slots) {
             const float d2l = __ldg(list + s);
             if (!(d2l <= far)) break;                       // sorted: nothing behind it matters either
@@ -195,10 +231,10 @@ __global__ void __launch_bounds__(kSgListWarps * 32) sigma_edges_list_kernel(con
                     oz = __shfl_xor_sync(0xffffffffu, bz, o);
         if (ob < best || (ob == best && ot < best_t)) { best = ob; best_t = ot; bx = ox; by = oy; bz = oz; }
     }
-    if (usable && slot == 0) {
+    if (slot == 0) {
         const float inv = 1.0f / sum;
         float* o = A.ws + (e * H + h) * 11;
-        o[0] = logf(sum) + d2min * a;
+        o[0] = logf(sum) + d2ref * a;
         o[1] = m0 * inv; o[2] = m1 * inv; o[3] = m2 * inv; o[4] = m3 * inv; o[5] = m4 * inv; o[6] = m5 * inv;
         o[7] = best;
         const float rn = rsqrtf(fmaxf(bx * bx + by * by + bz * bz, 1e-30f));
