@@ -49,14 +49,32 @@ class Latticeformer(nn.Module):
             model_dim, params.head_num, activation=params.t_activation, num_encoder_layers=num_layers,
             dim_feedforward=params.ff_dim, dropout=params.dropout, t_fixup_init=params.t_fixup_init,
             no_layer_norm=params.t_fixup_init, lattice_params=lattice_params, k_dim=params.k_dim, v_dim=params.v_dim)
-        if params.pre_pooling_op != "no" or params.norm_type not in ("no", "id"):
-            raise NotImplementedError("only pre_pooling_op='no' with norm_type='no' is wired up")
-        self.pooling_layer = {"avr": pooling.avr_pool, "max": pooling.max_pool}[params.pooling]
+        # per-atom projection before pooling and normalisation inside the head (models/latticeformer.py:138-190); the
+        # reference's parameter files use "no" / "no" throughout
+        norms = {"bn": nn.BatchNorm1d, "ln": nn.LayerNorm, "in": nn.InstanceNorm1d, "id": nn.Identity, "no": nn.Identity}
+        if params.norm_type not in norms:
+            raise NotImplementedError(f"norm_type: {params.norm_type}")
+        norm = norms[params.norm_type]
         emb = list(params.embedding_dim)
-        dims = [model_dim] + emb
+        pooled_dim = model_dim
+        self.proj_before_pooling = None
+        if params.pre_pooling_op in ("w+bn+relu", "w+relu"):
+            pooled_dim = emb.pop(0)
+            if not emb:
+                raise ValueError("pre_pooling_op takes the first entry of embedding_dim; the head needs one more")
+            mods = [nn.Linear(model_dim, pooled_dim)]
+            if params.pre_pooling_op == "w+bn+relu":
+                mods.append(norm(pooled_dim))
+            self.proj_before_pooling = nn.Sequential(*mods, nn.ReLU(True))
+        elif params.pre_pooling_op == "relu":
+            self.proj_before_pooling = nn.ReLU(True)
+        elif params.pre_pooling_op != "no":
+            raise NotImplementedError(f"pre_pooling_op: {params.pre_pooling_op}")
+        self.pooling_layer = {"avr": pooling.avr_pool, "max": pooling.max_pool}[params.pooling]
+        dims = [pooled_dim] + emb
         layers = []
         for di, do in zip(dims[:-1], dims[1:]):
-            layers += [nn.Linear(di, do), nn.Identity(), nn.ReLU(True)]
+            layers += [nn.Linear(di, do), norm(do), nn.ReLU(True)]
         final_dim = 1 if isinstance(params.targets, str) else len(params.targets)
         layers.append(nn.Linear(dims[-1], final_dim))
         self.mlp = nn.Sequential(*layers)
@@ -65,5 +83,7 @@ class Latticeformer(nn.Module):
         x = self.input_embeddings(data.x)
         x = self.encoder(x, data.pos, data.batch, data.trans_vec, data.sizes, this_epoch=this_epoch,
                          num_pairs=getattr(data, "num_pairs", None))
+        if self.proj_before_pooling is not None:
+            x = self.proj_before_pooling(x)
         x = self.pooling_layer(x, data.batch, data.sizes)
         return self.mlp(x)

@@ -176,5 +176,9 @@ def forward(model, batch, backend=None, frames=None):
         x = layer.norm2(x + layer.linear2(layer.activation(layer.linear1(x))))
     if model.encoder.norm is not None:
         x = model.encoder.norm(x)
+    if getattr(model, "proj_before_pooling", None) is not None:
+        x = model.proj_before_pooling(x)                    # models/latticeformer.py:282
+    if getattr(model.params, "pooling", "avr") != "avr":
+        raise NotImplementedError("the oracle model pools by the mean")
     x = OF.Mean.apply(x, sizes)
     return model.mlp(x)

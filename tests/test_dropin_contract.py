@@ -249,6 +249,21 @@ def test_whole_model_state_dict_matches_the_reference():
         assert all(a[k].shape == b[k].shape for k in a)
         mine.load_state_dict(a)
         ref.load_state_dict(b)
+        # the head's options (per-atom projection before pooling, normalisation), which no parameter file of the
+        # reference switches on, and the reciprocal-space domains
+        for over in (dict(pre_pooling_op="w+bn+relu", norm_type="bn", embedding_dim=[96, 64]),
+                     dict(pre_pooling_op="w+relu", norm_type="ln", embedding_dim=[128, 32]),
+                     dict(pre_pooling_op="relu", norm_type="no"), dict(pooling="max"),
+                     dict(domain="real-reci"), dict(domain="multihead", frame_method="no", value_pe_angle_real=0)):
+            cfg2 = dict(cfg, **{k: (list(v) if isinstance(v, list) else v) for k, v in over.items()})
+            p2 = types.SimpleNamespace(**cfg2)
+            if not hasattr(p2, "targets"):
+                p2.targets = ["e_form"]
+            ref2 = lf.Latticeformer(p2)
+            mine2 = Latticeformer(ModelParams(**{k: (list(v) if isinstance(v, list) else v) for k, v in over.items()}))
+            a2, b2 = ref2.state_dict(), mine2.state_dict()
+            assert list(a2) == list(b2), (over, [k for k in a2 if k not in b2], [k for k in b2 if k not in a2])
+            assert all(a2[k].shape == b2[k].shape for k in a2), over
     finally:
         kernel_manager.DEFER_BINDING = False
         for name in stubbed:
