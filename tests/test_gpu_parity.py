@@ -323,6 +323,12 @@ def test_whole_model_against_cpu_oracle(layers, frame_method, fused):
     _whole_model_check(layers, frame_method, fused)
 
 
+def test_whole_model_with_head_options():
+    """The reference's head options -- a per-atom projection before pooling, layer normalisation inside the head --
+    around the one-call layers, against the CPU oracle."""
+    _whole_model_check(1, "max", True, pre_pooling_op="w+relu", norm_type="ln", embedding_dim=[96, 64])
+
+
 def test_whole_model_without_orthogonalisation():
     """Frame method "max_wo_orthogonal" (second axis as selected, third axis selected with the triple product): the
     whole model against the CPU oracle; it runs operator by operator."""
