@@ -38,6 +38,12 @@ class Latticeformer(nn.Module):
         super().__init__()
         self.params = params
         model_dim, num_layers = params.model_dim, params.num_layers
+        # options of the reference that every parameter file of it leaves off and that are not wired up here
+        # (models/latticeformer.py:200-207: CGCNN atom features from a data file, GradientScaler on the embeddings)
+        if getattr(params, "use_cgcnn_feat", False):
+            raise NotImplementedError("use_cgcnn_feat")
+        if getattr(params, "scale_grad", 0.0) > 0:
+            raise NotImplementedError("scale_grad > 0")
         lattice_params = LatticeformerParams()
         lattice_params.parseFromArgs(params)
         self.input_embeddings = nn.Linear(self.ATOM_FEAT_DIM, model_dim, bias=False)
