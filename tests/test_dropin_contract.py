@@ -271,3 +271,19 @@ def test_whole_model_state_dict_matches_the_reference():
         for k in [k for k in sys.modules if k == "models" or k.startswith("models.")]:
             del sys.modules[k]
         sys.modules.update({k: v for k, v in saved.items() if v is not None})
+
+
+def test_every_exported_function_of_the_reference_package_is_offered():
+    """The names the reference's ``models/cuda_funcs/__init__.py`` exports, read from its source: all but ``Kernel``
+    (its holder of a CuPy RawKernel; kernels are prebuilt here) exist in this package."""
+    import crystalframer_b200.cuda_funcs as ours
+    tree = ast.parse(open(os.path.join(REF, "models", "cuda_funcs", "__init__.py")).read())
+    names = None
+    for node in tree.body:
+        if isinstance(node, ast.Assign) and any(getattr(t, "id", None) == "__all__" for t in node.targets):
+            names = [elt.value for elt in node.value.elts]
+    assert names, "no __all__ in the reference package"
+    missing = [n for n in names if n != "Kernel" and not hasattr(ours, n)]
+    assert not missing, missing
+    classes = [n for n in names if n.endswith("CUDA") or n == "ComputePCAFrame"]
+    assert len(classes) >= 14 and all(hasattr(getattr(ours, n), "apply") for n in classes)
