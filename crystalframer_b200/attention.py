@@ -157,14 +157,23 @@ def reset_gauss_scale(module):
                 gs.zero_()
 
 
-def gaussian_coefficients(q, lattice_pos_weights, gauss_scale, params, training):
+GAUSS_STATES = ("q", "q-headdim", "q-kdim", "1", "x", "x-norm", "x-xavier")
+
+
+def gaussian_coefficients(q, lattice_pos_weights, gauss_scale, params, training, query=None):
     """models/indexed_lattice_multi_head_attention_cuda.py:896-940: per (atom, head) coefficient
     a < 0 of exp(a d^2), from q and the learned per-head direction, normalised with statistics
-    that are measured once (first training forward) and then stored in ``gauss_scale``."""
+    that are measured once (first training forward) and then stored in ``gauss_scale``.  ``gauss_state`` "q*": from
+    the projected query; "1": one learned constant per head; "x*": from the layer's input ``query`` (N, embed_dim)."""
     N, H, hd = q.shape
-    if not params.gauss_state.startswith("q"):
+    if params.gauss_state not in GAUSS_STATES:
         raise NotImplementedError(f"gauss_state={params.gauss_state}")
-    alpha = (q.reshape(N, H, 1, hd) @ lattice_pos_weights.reshape(H, hd, 1)).view(N, H)
+    if params.gauss_state.startswith("q"):
+        alpha = (q.reshape(N, H, 1, hd) @ lattice_pos_weights.reshape(H, hd, 1)).view(N, H)
+    elif params.gauss_state == "1":
+        alpha = (torch.ones_like(q).reshape(N, H, 1, hd) @ lattice_pos_weights.reshape(H, hd, 1)).view(N, H)
+    else:
+        alpha = F.linear(query, lattice_pos_weights).view(N, H)
     if params.normalize_gauss:
         if gauss_scale_ready(gauss_scale):
             scale, shift = gauss_scale[0], gauss_scale[1]
@@ -219,7 +228,7 @@ def crystalformer_multi_head_attention_forward_cuda(
     if params is not None and params.domain != "no":
         if params.domain not in ("real", "reci", "RECI", "multihead"):
             raise NotImplementedError(f"domain={params.domain}")
-        alpha = gaussian_coefficients(q, lattice_pos_weights, gauss_scale, params, training)
+        alpha = gaussian_coefficients(q, lattice_pos_weights, gauss_scale, params, training, query)
         if params.domain == "multihead":
             # models/indexed_lattice_multi_head_attention_cuda.py:953-974
             half = num_heads // 2
@@ -286,15 +295,15 @@ class CrystalformerMultiheadAttentionCUDA(Module):
         self.pe_dist_proj = self.pe_wave_proj = self.proj_angle1 = self.proj_angle2 = self.proj_angle3 = None
         if params.domain in ("reci", "RECI"):
             # models/indexed_lattice_multi_head_attention_cuda.py:1100-1107
-            if not params.gauss_state.startswith("q"):
-                raise NotImplementedError(f"gauss_state={params.gauss_state}")
             if params.value_pe_dist_reci > 0 or params.value_pe_wave_reci > 0:
                 raise NotImplementedError("value encodings of the reciprocal domain")
-            self.lattice_pos_weights = Parameter(torch.empty(self.kdim, **kw))
-        if params.domain in ("real", "multihead"):
-            if not params.gauss_state.startswith("q"):
+        if params.domain in ("real", "multihead", "reci", "RECI"):
+            # models/indexed_lattice_multi_head_attention_cuda.py:1060-1071
+            if params.gauss_state not in GAUSS_STATES:
                 raise NotImplementedError(f"gauss_state={params.gauss_state}")
-            self.lattice_pos_weights = Parameter(torch.empty(self.kdim, **kw))
+            shape = (num_heads, embed_dim) if params.gauss_state.startswith("x") else (self.kdim,)
+            self.lattice_pos_weights = Parameter(torch.empty(*shape, **kw))
+        if params.domain in ("real", "multihead"):
             if params.value_pe_dist_real > 0:
                 self.pe_dist_proj = Parameter(torch.empty(1, num_heads, self.head_dim, params.value_pe_dist_real, **kw))
             if params.value_pe_angle_real > 0:
@@ -312,8 +321,13 @@ class CrystalformerMultiheadAttentionCUDA(Module):
             constant_(self.in_proj_bias, 0.)
             constant_(self.out_proj.bias, 0.)
         if self.lattice_pos_weights is not None:
-            std = (self.kdim) ** -0.5 if self.params.gauss_state == "q-kdim" else (self.kdim // self.num_heads) ** -0.5
-            normal_(self.lattice_pos_weights, 0., std)
+            state = self.params.gauss_state                   # :1121-1130
+            if state == "x-xavier":
+                xavier_uniform_(self.lattice_pos_weights)
+            else:
+                std = self.kdim ** -0.5 if state == "q-kdim" else self.embed_dim ** -0.5 if state.startswith("x") else \
+                    (self.kdim // self.num_heads) ** -0.5
+                normal_(self.lattice_pos_weights, 0., std)
         with torch.no_grad():
             for P in (self.pe_dist_proj, self.proj_angle1, self.proj_angle2, self.proj_angle3):
                 if P is not None:

@@ -34,11 +34,16 @@ def oracle_config(model):
                     cutoff_radius=p.adaptive_cutoff_sigma, symm_break_noise=0.0)
 
 
-def coefficients(attn, q):
-    """models/indexed_lattice_multi_head_attention_cuda.py:896-940"""
+def coefficients(attn, q, x=None):
+    """models/indexed_lattice_multi_head_attention_cuda.py:896-940; ``x``: the layer's input, for gauss_state "x*"."""
     P = attn.params
     N, H, hd = q.shape
-    alpha = (q.reshape(N, H, 1, hd) @ attn.lattice_pos_weights.reshape(H, hd, 1)).view(N, H)
+    if P.gauss_state.startswith("q"):
+        alpha = (q.reshape(N, H, 1, hd) @ attn.lattice_pos_weights.reshape(H, hd, 1)).view(N, H)
+    elif P.gauss_state == "1":
+        alpha = (torch.ones_like(q).reshape(N, H, 1, hd) @ attn.lattice_pos_weights.reshape(H, hd, 1)).view(N, H)
+    else:
+        alpha = F.linear(x, attn.lattice_pos_weights).view(N, H)
     if P.normalize_gauss:
         if bool(attn.gauss_scale[0] > 0):
             scale, shift = attn.gauss_scale[0], attn.gauss_scale[1]
@@ -88,7 +93,7 @@ def attention_layer(attn, x, geo, cfg, frames=None):
     q = F.linear(x, attn.q_proj_weight, bq).view(N, H, hd)
     k = F.linear(x, attn.k_proj_weight, bk).view(N, H, hd)
     v = F.linear(x, attn.v_proj_weight, bv).view(N, H, hd)
-    a = coefficients(attn, q)
+    a = coefficients(attn, q, x)
     cutoff = attn.params.adaptive_cutoff_sigma
     qs = q / math.sqrt(hd)
     if attn.params.domain in ("reci", "RECI"):

@@ -254,7 +254,8 @@ def test_whole_model_state_dict_matches_the_reference():
         for over in (dict(pre_pooling_op="w+bn+relu", norm_type="bn", embedding_dim=[96, 64]),
                      dict(pre_pooling_op="w+relu", norm_type="ln", embedding_dim=[128, 32]),
                      dict(pre_pooling_op="relu", norm_type="no"), dict(pooling="max"),
-                     dict(domain="real-reci"), dict(domain="multihead", frame_method="no", value_pe_angle_real=0)):
+                     dict(domain="real-reci"), dict(domain="multihead", frame_method="no", value_pe_angle_real=0),
+                     dict(gauss_state="x"), dict(gauss_state="1"), dict(gauss_state="x-xavier"), dict(gauss_state="q-kdim")):
             cfg2 = dict(cfg, **{k: (list(v) if isinstance(v, list) else v) for k, v in over.items()})
             p2 = types.SimpleNamespace(**cfg2)
             if not hasattr(p2, "targets"):

@@ -329,6 +329,13 @@ def test_whole_model_with_head_options():
     _whole_model_check(1, "max", True, pre_pooling_op="w+relu", norm_type="ln", embedding_dim=[96, 64])
 
 
+@pytest.mark.parametrize("gauss_state", ["x", "1"])
+def test_whole_model_other_coefficient_sources(gauss_state):
+    """Gaussian coefficients from the layer's input ("x") or one learned constant per head ("1") instead of the
+    projected query: the whole model, operator by operator, against the CPU oracle."""
+    _whole_model_check(1, "max", False, gauss_state=gauss_state)
+
+
 def test_whole_model_without_orthogonalisation():
     """Frame method "max_wo_orthogonal" (second axis as selected, third axis selected with the triple product): the
     whole model against the CPU oracle; it runs operator by operator."""
